@@ -278,13 +278,13 @@ std::vector<at::Tensor> ce_fwd(const at::Tensor& logits, const at::Tensor& targe
   return {loss, lse, row_loss};
 }
 void ce_bwd(at::Tensor& logits, const at::Tensor& target, const at::Tensor& lse,
-            const at::Tensor& grad_out, int64_t V) {
+            const at::Tensor& grad_out, int64_t V, bool ignore_oob) {
   c10::cuda::CUDAGuard guard(logits.device());
   TORCH_CHECK(grad_out.scalar_type() == at::kFloat && grad_out.numel() == 1, "ce_bwd: fp32 scalar");
   check_rc(itb_ce_bwd(logits.data_ptr(), dt(logits), logits.stride(0),
                       reinterpret_cast<const long long*>(target.data_ptr<int64_t>()),
                       lse.data_ptr<float>(), grad_out.data_ptr<float>(), logits.size(0), V,
-                      cur_stream()),
+                      ignore_oob, cur_stream()),
            "ce_bwd");
 }
 

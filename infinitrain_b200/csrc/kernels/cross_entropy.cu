@@ -132,12 +132,16 @@ ce_fwd_kernel(const T* __restrict__ logits, long long ld, const long long* __res
 template <typename T>
 __global__ void __launch_bounds__(kCeThreads)
 ce_bwd_kernel(T* __restrict__ logits, long long ld, const long long* __restrict__ target,
-              const float* __restrict__ lse, const float* __restrict__ grad_out, int rows, int V) {
+              const float* __restrict__ lse, const float* __restrict__ grad_out, int rows, int V,
+              int ignore_oob) {
   const int r = blockIdx.x;
   T* row = logits + static_cast<long long>(r) * ld;
   const long long t = target[r];
   const bool valid = t >= 0 && t < V;
-  const float g = valid ? (grad_out ? *grad_out : 1.f) / rows : 0.f;
+  // ignore_oob: a row whose target is out of range contributes nothing (ignored label).
+  // Otherwise (vocabulary-parallel shard) the row still receives the softmax term; only the
+  // one-hot term is absent because another shard owns the target column.
+  const float g = (valid || !ignore_oob) ? (grad_out ? *grad_out : 1.f) / rows : 0.f;
   const float l = lse[r];
   const int ldi = static_cast<int>(ld);
   const int nvec = V / 8;
@@ -185,14 +189,14 @@ extern "C" int itb_ce_fwd(const void* logits, int dtype, long long ld, const lon
 }
 
 extern "C" int itb_ce_bwd(void* logits, int dtype, long long ld, const long long* target,
-                          const float* lse, const float* grad_out, int rows, int V,
+                          const float* lse, const float* grad_out, int rows, int V, int ignore_oob,
                           cudaStream_t s) {
   if (rows <= 0) return 0;
   if (dtype == kItbBF16)
     ce_bwd_kernel<__nv_bfloat16><<<rows, kCeThreads, 0, s>>>(static_cast<__nv_bfloat16*>(logits), ld,
-                                                             target, lse, grad_out, rows, V);
+                                                             target, lse, grad_out, rows, V, ignore_oob);
   else
     ce_bwd_kernel<float><<<rows, kCeThreads, 0, s>>>(static_cast<float*>(logits), ld, target, lse,
-                                                     grad_out, rows, V);
+                                                     grad_out, rows, V, ignore_oob);
   return static_cast<int>(cudaGetLastError());
 }

@@ -101,9 +101,11 @@ int itb_embedding_bwd(const long long* idx, const void* dout, int dout_dtype, fl
 int itb_ce_fwd(const void* logits, int dtype, long long ld, const long long* target, float* row_loss,
                float* lse, float* loss_mean, int rows, int V, cudaStream_t stream);
 // dlogits = (softmax - onehot) * (*grad_out) / rows, written over the logits buffer (columns
-// V..ld-1 are zeroed).
+// V..ld-1 are zeroed).  softmax = exp(logit - lse[row]), so a vocabulary shard passes the GLOBAL
+// log-sum-exp.  ignore_oob != 0: rows whose target is outside [0, V) get a zero gradient;
+// ignore_oob == 0: they get the softmax term without the one-hot (the target lives on another shard).
 int itb_ce_bwd(void* logits, int dtype, long long ld, const long long* target, const float* lse,
-               const float* grad_out, int rows, int V, cudaStream_t stream);
+               const float* grad_out, int rows, int V, int ignore_oob, cudaStream_t stream);
 
 // ------------------------------------------------------------------ optimizer
 // One launch over a flat buffer: Adam / AdamW with fp32 master weights and optional bf16 shadow.

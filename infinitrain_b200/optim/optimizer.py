@@ -1,0 +1,168 @@
+"""Optimizers: SGD and Adam / AdamW.
+
+Reference: infini_train/include/optimizer.h:35-68, infini_train/src/optimizer.cc:23-105 (one kernel
+launch per parameter tensor, Adam without weight decay, state in the parameter dtype, ``t``
+incremented even when every gradient is missing, positional state-dict keys ``adam.m.<i>``,
+``adam.v.<i>``, ``adam.t``).
+
+On CUDA with fp32 parameters the optimizer is FUSED: the parameters are moved into one flat
+:class:`ParamAndGradBuffer` (fp32 master + fp32 gradients + bf16 shadow) and ``Step`` is a single
+kernel launch that updates m, v and the master weights and writes the bf16 copy the GEMMs read.
+``weight_decay`` adds the decoupled AdamW term (0 reproduces the reference's update exactly).
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from .. import _ext
+from ..ops import functional as ops
+
+OptimizerCreator = Callable[[Sequence[torch.nn.Parameter]], "Optimizer"]
+
+
+class Optimizer:
+    def __init__(self, params: Sequence[torch.nn.Parameter]):
+        self.params: List[torch.nn.Parameter] = list(params)
+        self._flat = None   # ParamAndGradBuffer when the fused path is active
+
+    # ------------------------------------------------------------------ gradients
+    def ZeroGrad(self, set_to_none: bool = True) -> None:
+        if self._flat is not None:
+            # Gradients are views of one flat buffer: a single memset; the views stay in place.
+            self._flat.zero_grads()
+            return
+        for p in self.params:
+            if set_to_none:
+                p.grad = None
+            elif p.grad is not None:
+                p.grad.zero_()
+
+    def Step(self) -> None:
+        raise NotImplementedError
+
+    def StateDict(self) -> "OrderedDict[str, torch.Tensor]":
+        return OrderedDict()
+
+    def LoadStateDict(self, state_dict: Dict[str, torch.Tensor]) -> None:
+        pass
+
+    # torch-style aliases
+    zero_grad = ZeroGrad
+    step = Step
+
+    # ------------------------------------------------------------------ fused path set-up
+    def _maybe_flatten(self, fused: Optional[bool]):
+        from ..parallel.ddp.param_and_grad_buffer import ParamAndGradBuffer
+
+        can = (len(self.params) > 0 and all(p.is_cuda and p.dtype == torch.float32 for p in self.params)
+               and _ext.available())
+        if fused is None:
+            fused = can
+        if not fused:
+            return
+        if not can:
+            raise ValueError("fused optimizer needs CUDA fp32 parameters and the native extension")
+        existing = getattr(self.params[0], "_itb_flat_buffer", None)
+        if existing is not None and all(getattr(p, "_itb_flat_buffer", None) is existing for p in self.params) \
+                and len(existing.params) == len(self.params):
+            self._flat = existing     # e.g. built by DistributedDataParallel
+            return
+        self._flat = ParamAndGradBuffer(self.params)
+        for p in self.params:
+            p._itb_flat_buffer = self._flat
+
+
+class SGD(Optimizer):
+    def __init__(self, params, learning_rate: float, fused: Optional[bool] = None):
+        super().__init__(params)
+        self.learning_rate = learning_rate
+        self._maybe_flatten(fused)
+
+    def Step(self) -> None:
+        if self._flat is not None:
+            C = _ext.load()
+            C.sgd(self._flat.param_buffer, self._flat.grad_buffer, self._flat.shadow_buffer, self.learning_rate, 1.0)
+            ops._counters["launches"] += 1
+            self._flat.mark_shadows_fresh()
+            return
+        with torch.no_grad():
+            for p in self.params:
+                if p.grad is None:
+                    continue
+                p.add_(p.grad.to(p.dtype), alpha=-self.learning_rate)
+
+    @staticmethod
+    def Create(learning_rate: float, **kw) -> OptimizerCreator:
+        return lambda params: SGD(params, learning_rate, **kw)
+
+
+class Adam(Optimizer):
+    def __init__(self, params, learning_rate: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999,
+                 eps: float = 1e-8, weight_decay: float = 0.0, fused: Optional[bool] = None):
+        super().__init__(params)
+        self.t = 0
+        self.learning_rate, self.beta1, self.beta2, self.eps = learning_rate, beta1, beta2, eps
+        self.weight_decay = weight_decay
+        self._maybe_flatten(fused)
+        if self._flat is not None:
+            self._m_flat = torch.zeros_like(self._flat.param_buffer)
+            self._v_flat = torch.zeros_like(self._flat.param_buffer)
+            self.m = [self._m_flat[s:e].view(p.shape) for p, (s, e, _) in zip(self.params, self._flat.layout.param_ranges)]
+            self.v = [self._v_flat[s:e].view(p.shape) for p, (s, e, _) in zip(self.params, self._flat.layout.param_ranges)]
+        else:
+            self.m = [torch.zeros_like(p) for p in self.params]
+            self.v = [torch.zeros_like(p) for p in self.params]
+
+    def Step(self) -> None:
+        self.t += 1
+        bc1 = 1.0 - self.beta1 ** self.t
+        bc2 = 1.0 - self.beta2 ** self.t
+        if self._flat is not None:
+            C = _ext.load()
+            C.adamw(self._flat.param_buffer, self._flat.grad_buffer, self._m_flat, self._v_flat,
+                    self._flat.shadow_buffer, self.learning_rate, self.beta1, self.beta2, self.eps,
+                    self.weight_decay, bc1, bc2, 1.0)
+            ops._counters["launches"] += 1
+            self._flat.mark_shadows_fresh()
+            return
+        with torch.no_grad():
+            for p, m, v in zip(self.params, self.m, self.v):
+                if p.grad is None:
+                    continue
+                g = p.grad.to(p.dtype)
+                m.mul_(self.beta1).add_(g, alpha=1.0 - self.beta1)
+                v.mul_(self.beta2).addcmul_(g, g, value=1.0 - self.beta2)
+                upd = (m / bc1) / ((v / bc2).sqrt() + self.eps)
+                if self.weight_decay:
+                    upd = upd + self.weight_decay * p
+                p.add_(upd, alpha=-self.learning_rate)
+
+    @staticmethod
+    def Create(learning_rate: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+               weight_decay: float = 0.0, **kw) -> OptimizerCreator:
+        return lambda params: Adam(params, learning_rate, beta1, beta2, eps, weight_decay, **kw)
+
+    def StateDict(self):
+        out = OrderedDict()
+        for i, (m, v) in enumerate(zip(self.m, self.v)):
+            out[f"adam.m.{i}"] = m
+            out[f"adam.v.{i}"] = v
+        out["adam.t"] = torch.tensor(self.t, dtype=torch.int64)
+        return out
+
+    def LoadStateDict(self, state_dict):
+        for i, (m, v) in enumerate(zip(self.m, self.v)):
+            for key, dst in ((f"adam.m.{i}", m), (f"adam.v.{i}", v)):
+                if key not in state_dict:
+                    raise KeyError(f"Missing optimizer state: {key}")
+                with torch.no_grad():
+                    dst.copy_(state_dict[key].to(dst.device))
+        if "adam.t" not in state_dict:
+            raise KeyError("Missing optimizer state: adam.t")
+        self.t = int(state_dict["adam.t"].item())
+
+
+AdamW = Adam

@@ -214,7 +214,7 @@ def test_cross_entropy(C, rows, V, ld, dtype):
     loss, lse, row_loss = C.ce_fwd(buf, tgt, V)
     assert abs(loss.item() - ref.item()) < 1e-3 * max(1.0, abs(ref.item()))
     (ref * 0.5).backward()
-    C.ce_bwd(buf, tgt, lse, torch.full((1,), 0.5, device="cuda"), V)
+    C.ce_bwd(buf, tgt, lse, torch.full((1,), 0.5, device="cuda"), V, True)
     assert _rel(buf[:, :V], lr.grad) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
     if ld > V:
         assert buf[:, V:].abs().max().item() == 0
