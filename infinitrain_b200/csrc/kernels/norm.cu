@@ -276,18 +276,27 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
   for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) prow[i] = sh[i];
 }
 
-// out[c] (+)= sum_r partial[r, c]; one thread per column, coalesced across the block.
-__global__ void partial_reduce_kernel(const float* __restrict__ partial, int prow_stride, int nrows,
-                                      float* __restrict__ out_a, float* __restrict__ out_b, int C,
-                                      int accumulate) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * C) return;
+// out[c] (+)= sum_r partial[r, c]: a block of 32 columns x 8 row lanes; the row lanes are combined
+// in shared memory.
+__global__ void __launch_bounds__(256)
+partial_reduce_kernel(const float* __restrict__ partial, int prow_stride, int nrows,
+                      float* __restrict__ out_a, float* __restrict__ out_b, int C, int accumulate) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s = 0.f;
+  if (c < 2 * C)
+    for (int r = ry; r < nrows; r += 8) s += partial[static_cast<long long>(r) * prow_stride + c];
+  sh[ry][cx] = s;
+  __syncthreads();
+  if (ry != 0 || c >= 2 * C) return;
+  float t = 0.f;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) t += sh[r][cx];
   float* out = c < C ? out_a : out_b;
   if (!out) return;
-  float s = 0.f;
-  for (int r = 0; r < nrows; ++r) s += partial[static_cast<long long>(r) * prow_stride + c];
-  int oc = c < C ? c : c - C;
-  out[oc] = accumulate ? out[oc] + s : s;
+  const int oc = c < C ? c : c - C;
+  out[oc] = accumulate ? out[oc] + t : t;
 }
 
 static int norm_grid(int rows) {
@@ -354,7 +363,7 @@ static int norm_bwd_dispatch(const void* dy, int dyd, const void* x, int xd, con
 #undef LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  partial_reduce_kernel<<<(2 * C + 255) / 256, 256, 0, s>>>(partial, 2 * C, grid, dgamma, dbeta, C,
+  partial_reduce_kernel<<<(2 * C + 31) / 32, 256, 0, s>>>(partial, 2 * C, grid, dgamma, dbeta, C,
                                                            accumulate);
   return static_cast<int>(cudaGetLastError());
 }

@@ -276,32 +276,62 @@ __global__ void cast_kernel(const TS* __restrict__ src, TD* __restrict__ dst, lo
 }
 
 // ------------------------------------------------------------------ column sum (bias gradient)
-// Stage 1: block (bx, by) sums rows [by*rows_per, ...) of 8-wide column groups into partial[by, :].
-// A warp reads 32 consecutive 16-byte groups of one row: fully coalesced.
-constexpr int kColsumRowsPerBlock = 256;
+// Stage 1: a block of 32 x 8 threads covers 256 columns (32 groups of 8) and kColsumRowsPerBlock
+// rows; thread (cx, ry) sums rows ry, ry + 8, ... of its 8 columns (a warp reads 512 contiguous
+// bytes of one row), the 8 row lanes are combined in shared memory and the block writes one
+// partial row.  Stage 2 sums the partial rows.
+constexpr int kColsumRowsPerBlock = 128;
 template <typename T>
-__global__ void colsum_stage1_kernel(const T* __restrict__ x, long long ld,
-                                     float* __restrict__ partial, int rows, int N) {
-  const int cg = blockIdx.x * blockDim.x + threadIdx.x;  // column group of 8
-  if (cg * 8 >= N) return;
+__global__ void __launch_bounds__(256)
+colsum_stage1_kernel(const T* __restrict__ x, long long ld, float* __restrict__ partial, int rows,
+                     int N) {
+  __shared__ float sh[8][32][9];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int cg = blockIdx.x * 32 + cx;  // column group of 8
+  const bool col_ok = cg * 8 < N;
   const int r0 = blockIdx.y * kColsumRowsPerBlock;
   const int r1 = min(rows, r0 + kColsumRowsPerBlock);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int r = r0; r < r1; ++r) {
-    float v[8];
-    Vec8<T>::load(x + static_cast<long long>(r) * ld + cg * 8, v);
+  if (col_ok) {
+    for (int r = r0 + ry; r < r1; r += 8) {
+      float v[8];
+      Vec8<T>::load(x + static_cast<long long>(r) * ld + cg * 8, v);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] += v[e];
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
   }
-  Vec8<float>::store(partial + static_cast<long long>(blockIdx.y) * N + cg * 8, acc);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) sh[ry][cx][e] = acc[e];
+  __syncthreads();
+  // 256 threads -> 256 columns of this block
+  const int c = threadIdx.x;           // column within the block
+  const int gcx = c >> 3, ge = c & 7;
+  const int col = blockIdx.x * 256 + c;
+  if (col < N) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) s += sh[r][gcx][ge];
+    partial[static_cast<long long>(blockIdx.y) * N + col] = s;
+  }
 }
-__global__ void colsum_stage2_kernel(const float* __restrict__ partial, int nparts,
-                                     float* __restrict__ out, int N, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
+// out[c] (+)= sum_r partial[r, c]: 32 columns x 8 row lanes per block.
+__global__ void __launch_bounds__(256)
+colsum_stage2_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out, int N,
+                     int accumulate) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int r = 0; r < nparts; ++r) s += partial[static_cast<long long>(r) * N + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < N)
+    for (int r = ry; r < nparts; r += 8) s += partial[static_cast<long long>(r) * N + c];
+  sh[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += sh[r][cx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 }  // namespace itb
@@ -452,13 +482,13 @@ extern "C" int itb_colsum(const void* x, int dtype, long long ld, float* out, fl
   if (rows <= 0 || N <= 0) return 0;
   if (N % 8 || ld % 8) return -3;
   const int nparts = itb_colsum_partial_rows(rows);
-  dim3 grid((N / 8 + 127) / 128, nparts);
+  dim3 grid((N + 255) / 256, nparts);
   if (dtype == kItbBF16)
-    colsum_stage1_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
+    colsum_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
                                                              ld, partial, rows, N);
   else
-    colsum_stage1_kernel<float><<<grid, 128, 0, s>>>(static_cast<const float*>(x), ld, partial, rows,
+    colsum_stage1_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), ld, partial, rows,
                                                      N);
-  colsum_stage2_kernel<<<(N + 255) / 256, 256, 0, s>>>(partial, nparts, out, N, accumulate);
+  colsum_stage2_kernel<<<(N + 31) / 32, 256, 0, s>>>(partial, nparts, out, N, accumulate);
   return static_cast<int>(cudaGetLastError());
 }

@@ -73,7 +73,9 @@ class Module(torch.nn.Module):
     def mutable_module(self, name: str):
         return self._modules[name]
 
-    def module(self, name: str):
+    def GetModule(self, name: str):
+        """The reference's ``module(name)`` accessor (that name is left free for child modules called
+        "module", which DistributedDataParallel and PipelineParallel use)."""
         return self._modules[name]
 
     def NamedModules(self, memory: Optional[set] = None, prefix: str = "", remove_duplicate: bool = True):

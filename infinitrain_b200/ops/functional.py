@@ -186,6 +186,12 @@ def _wgrad(C, dy2, x2, weight, N, K, M):
     """dW[N,K] = dy^T x in fp32.  Accumulates straight into ``weight.main_grad`` when the parameter
     has one (flat DDP / ZeRO gradient buffers) and then fires its grad-ready hooks."""
     main = getattr(weight, "main_grad", None)
+    if main is None and getattr(weight, "_itb_main_grad_fn", None) is not None:
+        main = weight._itb_main_grad_fn()
+    if getattr(weight, "_itb_shared", False):
+        # A parameter used by several ops (tied embedding / head) receives the rest of its gradient
+        # through autograd; its ready hook must fire once, after the last contribution.
+        main = None
     if main is not None:
         C.gemm(dy2, True, x2, True, N, K, M, main, None, None, None, None, C.GEMM_OUT_F32 | C.GEMM_ATOMIC, 0)
         _counters["launches"] += 1

@@ -26,7 +26,8 @@ OptimizerCreator = Callable[[Sequence[torch.nn.Parameter]], "Optimizer"]
 class Optimizer:
     def __init__(self, params: Sequence[torch.nn.Parameter]):
         self.params: List[torch.nn.Parameter] = list(params)
-        self._flat = None   # ParamAndGradBuffer when the fused path is active
+        self._flat = None   # ParamAndGradBuffer when the fused flat path is active
+        self._per_tensor_fused = False
 
     # ------------------------------------------------------------------ gradients
     def ZeroGrad(self, set_to_none: bool = True) -> None:
@@ -61,6 +62,12 @@ class Optimizer:
                and _ext.available())
         if fused is None:
             fused = can
+        self._per_tensor_fused = False
+        if fused and can and any(getattr(p, "_itb_no_flatten", False) for p in self.params):
+            # Parameters that are already slices of somebody's flat buffer (ZeRO shards) are
+            # updated where they are: one fused launch per tensor.
+            self._per_tensor_fused = True
+            return
         if not fused:
             return
         if not can:
@@ -87,6 +94,14 @@ class SGD(Optimizer):
             C.sgd(self._flat.param_buffer, self._flat.grad_buffer, self._flat.shadow_buffer, self.learning_rate, 1.0)
             ops._counters["launches"] += 1
             self._flat.mark_shadows_fresh()
+            return
+        if self._per_tensor_fused:
+            C = _ext.load()
+            for p in self.params:
+                if p.grad is None:
+                    continue
+                C.sgd(p.data, p.grad, getattr(p, "_itb_shadow", None), self.learning_rate, 1.0)
+                ops._counters["launches"] += 1
             return
         with torch.no_grad():
             for p in self.params:
@@ -127,6 +142,15 @@ class Adam(Optimizer):
                     self.weight_decay, bc1, bc2, 1.0)
             ops._counters["launches"] += 1
             self._flat.mark_shadows_fresh()
+            return
+        if self._per_tensor_fused:
+            C = _ext.load()
+            for p, m, v in zip(self.params, self.m, self.v):
+                if p.grad is None:
+                    continue
+                C.adamw(p.data, p.grad, m, v, getattr(p, "_itb_shadow", None), self.learning_rate, self.beta1,
+                        self.beta2, self.eps, self.weight_decay, bc1, bc2, 1.0)
+                ops._counters["launches"] += 1
             return
         with torch.no_grad():
             for p, m, v in zip(self.params, self.m, self.v):

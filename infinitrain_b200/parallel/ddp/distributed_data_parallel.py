@@ -1,0 +1,154 @@
+"""DistributedDataParallel: the module wrapper that keeps gradients of data-parallel replicas equal.
+
+Reference: infini_train/src/nn/parallel/ddp/distributed_data_parallel.cc (modes :40-65,
+ZeRO buffers :68-123, ZeRO-2 bypass hook :126-165, forward :208-218).
+
+Three modes, chosen by the configuration exactly as in the reference:
+* ``gradient_bucketing_enabled=False``: one all-reduce(avg) per parameter, issued from its
+  post-accumulate hook;
+* ZeRO-0 (default): :class:`Reducer` — size-capped buckets reduced asynchronously during backward;
+* ZeRO-1 / ZeRO-2: :class:`ParamAndGradBuffer` + bucket groups — gradients are reduce-scattered to
+  the owner shard and :class:`DistributedOptimizer` updates the shard and all-gathers parameters.
+  ZeRO-3 is not supported (nor is it in the reference).
+
+Construction broadcasts rank 0's parameters so that replicas start identical.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ...nn.module import Module
+from .. import global_env as genv
+from ..process_group import ProcessGroup, ProcessGroupFactory, ReduceOpType
+from .config import DistributedDataParallelConfig
+from .param_and_grad_buffer import ParamAndGradBuffer, ParamAndGradBucketGroup, PartitionBuckets
+from .reducer import ComputeBucketAssignmentBySize, Reducer, kBytesPerMB
+
+
+class DistributedDataParallel(Module):
+    kType = "DistributedDataParallel"
+    kModuleName = "module"
+
+    def __init__(self, module: torch.nn.Module, rank=None, config: Optional[DistributedDataParallelConfig] = None,
+                 process_group: Optional[ProcessGroup] = None, broadcast_parameters: bool = True):
+        super().__init__(self.kType)
+        self.add_module(self.kModuleName, module)
+        self.config = config or DistributedDataParallelConfig()
+        if self.config.zero_stage >= 3:
+            raise NotImplementedError("ZeRO-3 (parameter partitioning) is not supported")
+        self.pg = process_group if process_group is not None else ProcessGroupFactory.Instance().dp_group()
+        self.dp_size = self.pg.world_size if self.pg is not None else 1
+        self.reducer: Optional[Reducer] = None
+        self.param_grad_buffers: List[ParamAndGradBuffer] = []
+        self.bucket_groups: List[ParamAndGradBucketGroup] = []
+        self.param_to_group = {}
+        self._hook_handles = []
+        params = [p for p in module.parameters() if p.requires_grad]
+        self._params = params
+        if broadcast_parameters and self.dp_size > 1:
+            with torch.no_grad():
+                for p in module.parameters():
+                    self.pg.BroadCast(p.data, 0)
+                for b in module.buffers():
+                    if b.is_floating_point():
+                        self.pg.BroadCast(b.data, 0)
+        if not params:
+            return
+        if self.config.zero_stage >= 1:
+            self._build_param_and_grad_buffers(params)
+        elif self.config.gradient_bucketing_enabled:
+            self._build_reducer(params)
+        else:
+            for p in params:
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._allreduce_hook))
+
+    # ------------------------------------------------------------------ mode: per-parameter
+    def _allreduce_hook(self, p):
+        if self.dp_size > 1 and p.grad is not None:
+            self.pg.AllReduce(p.grad, ReduceOpType.kAvg, async_op=False)
+
+    # ------------------------------------------------------------------ mode: reducer (ZeRO-0)
+    def _build_reducer(self, params):
+        limits = [self.config.first_bucket_cap_mb * kBytesPerMB, self.config.normal_bucket_cap_mb * kBytesPerMB]
+        flat = None
+        if all(p.is_cuda and p.dtype == torch.float32 for p in params):
+            # One flat fp32 parameter / gradient buffer (+ bf16 shadow) shared with the fused
+            # optimizer; buckets are contiguous slices of it.
+            flat = ParamAndGradBuffer(params, self.pg, DistributedDataParallelConfig(zero_stage=0))
+            for p in params:
+                p._itb_flat_buffer = flat
+            self.param_grad_buffers = [flat]
+        indices = ComputeBucketAssignmentBySize(params, limits)
+        allreduce_fn = None
+        if self.config.use_fused_nvlink_kernels and flat is not None and self.dp_size > 1:
+            from .. import symm
+
+            allreduce_fn = symm.make_bucket_allreduce(self.pg, flat)
+        self.reducer = Reducer(params, indices, self.pg, self.config, allreduce_fn=allreduce_fn, flat_buffer=flat)
+        self.reducer.AttachHooksToParameters()
+
+    # ------------------------------------------------------------------ mode: ZeRO-1/2
+    def _build_param_and_grad_buffers(self, params):
+        buf = ParamAndGradBuffer(params, self.pg, self.config)
+        self.param_grad_buffers = [buf]
+        for p in params:
+            p._itb_flat_buffer = buf
+        self.bucket_groups = PartitionBuckets(self.param_grad_buffers, self.pg, self.config)
+        for i, g in enumerate(self.bucket_groups):
+            for pid, p in g.params.items():
+                self.param_to_group[pid] = g
+        # Parameter all-gathers are chained in forward order (reverse of the bucket order).
+        for i in range(len(self.bucket_groups) - 1, 0, -1):
+            self.bucket_groups[i].SetNextParamGatherBucketGroup(self.bucket_groups[i - 1])
+        for p in params:
+            if self.config.zero_stage >= 2:
+                g = self.param_to_group[id(p)]
+                p._itb_main_grad_fn = (lambda g=g, p=p: g.full_grad_view(p))
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._zero2_hook))
+            else:
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._on_grad_ready))
+            p._itb_grad_ready_hooks = [self._on_grad_ready]
+
+    def _zero2_hook(self, p):
+        """ZeRO-2: move the freshly accumulated gradient into the bucket's temporary full buffer and
+        drop ``param.grad`` so that no persistent full-size gradient exists."""
+        g = self.param_to_group[id(p)]
+        if p.grad is not None:
+            g.AccumulateParamGrad(p, p.grad)
+            p.grad = None
+        g.RegisterGradReady(p)
+
+    def _on_grad_ready(self, p):
+        g = self.param_to_group.get(id(p))
+        if g is not None:
+            g.RegisterGradReady(p)
+
+    # ------------------------------------------------------------------ forward
+    def Forward(self, *inputs, **kwargs):
+        out = self._modules[self.kModuleName](*inputs, **kwargs)
+        if self.reducer is not None and torch.is_grad_enabled():
+            self.reducer.PrepareForBackward()
+        return out
+
+    def Parameters(self):
+        return list(self._modules[self.kModuleName].parameters())
+
+    def StateDict(self):
+        m = self._modules[self.kModuleName]
+        return m.StateDict() if hasattr(m, "StateDict") else m.state_dict(keep_vars=True)
+
+    def LoadStateDict(self, sd):
+        m = self._modules[self.kModuleName]
+        m.LoadStateDict(sd)
+        for buf in self.param_grad_buffers:
+            buf.refresh_shadow()
+
+    def FinishGradSync(self):
+        """Waits for every outstanding gradient collective (also launches those whose parameters
+        received no gradient)."""
+        if self.reducer is not None:
+            self.reducer.Flush()
+        for g in self.bucket_groups:
+            g.FinishGradSync()

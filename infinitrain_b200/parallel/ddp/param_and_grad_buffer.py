@@ -219,6 +219,7 @@ class ParamAndGradBucketGroup:
         self.grad_reduce_works: List[Optional[Work]] = []
         self.param_gather_works: List[Optional[Work]] = []
         self.grad_reduce_dispatched = False
+        self.grad_sync_done = False          # set by FinishGradSync, cleared by Reset (once per step)
         self.param_gather_dispatched = False
         self.is_last_microbatch = True
         self.next_param_gather_group: Optional["ParamAndGradBucketGroup"] = None
@@ -237,6 +238,7 @@ class ParamAndGradBucketGroup:
         self.param_gather_works.clear()
         self.is_last_microbatch = True
         self.grad_reduce_dispatched = False
+        self.grad_sync_done = False
         self.param_gather_dispatched = False
         if self.config.zero_stage >= 2:
             self.temp_full_grad = [None] * len(self.buckets)
@@ -300,6 +302,8 @@ class ParamAndGradBucketGroup:
         self.params_with_grad.clear()
 
     def FinishGradSync(self):
+        if self.grad_sync_done:
+            return   # already reduced this step: a second reduce-scatter would mix reduced and raw data
         if not self.grad_reduce_dispatched:
             self.StartGradSync()
         for w in self.grad_reduce_works:
@@ -309,6 +313,7 @@ class ParamAndGradBucketGroup:
         if self.config.zero_stage >= 2:
             self.temp_full_grad = [None] * len(self.buckets)
         self.grad_reduce_dispatched = False
+        self.grad_sync_done = True
 
     # ------------------------------------------------------------------ parameter sync
     def StartParamSync(self, force_sync: bool = False):

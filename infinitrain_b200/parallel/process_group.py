@@ -171,7 +171,10 @@ class ProcessGroup:
         if self._trivial():
             output.copy_(input)
             return Work() if async_op else None
-        h = dist.all_gather_into_tensor(output, input.contiguous(), group=self.pg, async_op=True)
+        inp = input.contiguous()
+        if self.backend != "nccl":
+            inp = inp.clone()   # only NCCL defines the in-place form (input a slice of output)
+        h = dist.all_gather_into_tensor(output, inp, group=self.pg, async_op=True)
         return self._wrap(h, async_op, None, output.device)
 
     def ReduceScatter(self, output: torch.Tensor, input: torch.Tensor, op: ReduceOpType = ReduceOpType.kSum,
