@@ -1,0 +1,243 @@
+// Collectives written as CUDA kernels that move data over NVLink / NVSwitch themselves, fused with
+// the arithmetic that surrounds them.  Every rank launches the same kernel on its own GPU; the
+// buffers live in symmetric memory (same allocation on every rank, peer-mapped, plus an NVLS
+// multicast mapping when the switch offers one).
+//
+//   * all-reduce(avg) of a gradient bucket in place                      (DDP reducer, ZeRO-0)
+//   * reduce-scatter + scale + AdamW on the owner shard + broadcast of the updated fp32 weights and
+//     their bf16 shadow to every rank                                     (ZeRO-1/2 optimizer step)
+//
+// The reference issues ncclAllReduce / ncclReduceScatter / ncclAllGather from the host on a side
+// stream and runs Adam as separate per-tensor launches (infini_train/src/nn/parallel/
+// process_group.cc:128-195, ddp/param_and_grad_buffer.cc:237-378, src/optimizer.cc:53-71).
+//
+// Two data paths, chosen per launch: `multimem` (multimem.ld_reduce sums the value of every rank
+// inside the switch, multimem.st writes to every rank at once) and plain peer pointers (each rank
+// reads its slice from every peer and stores the result to every peer).
+//
+// Ranks synchronise through flag words in symmetric memory: block b of rank r writes the launch's
+// epoch into slot [b][r] of every peer and waits until its own slots [b][*] have reached that
+// epoch.  Epochs only grow, so no flag is ever reset.  Every wait is bounded: when it gives up the
+// block records an error code in the status word and skips its work; the host checks the word.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "comm.h"
+
+namespace itb {
+
+constexpr int kCommThreads = 512;
+// ~2^24 polls with a short sleep: of the order of a few seconds of skew tolerated between ranks.
+constexpr unsigned kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Block-wide barrier across ranks on channel `ch`.  Returns false when a peer did not arrive.
+__device__ __forceinline__ bool rank_barrier(const ItbPeerPtrs& flags, int rank, int world, int ch,
+                                             int epoch, int* err, int code) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();  // also orders this block's earlier memory traffic before the signal below
+  if (threadIdx.x < world) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(static_cast<int*>(flags.p[peer]) + ch * kItbMaxRanks + rank, epoch);
+    const int* mine = static_cast<const int*>(flags.p[rank]) + ch * kItbMaxRanks + peer;
+    bool ok = false;
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+      if (ld_acquire_sys(mine) - epoch >= 0) {
+        ok = true;
+        break;
+      }
+      if (i > 32) __nanosleep(100);
+    }
+    if (!ok) {
+      atomicCAS(err, 0, code);
+      ok_flag = 0;
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+__device__ __forceinline__ float4 mm_ld_reduce_f32x4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void mm_st_f32x4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "f"(v.x),
+               "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void mm_st_bf16x8(__nv_bfloat16* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <bool kMC>
+__device__ __forceinline__ float4 reduce4(const ItbPeerPtrs& bufs, const float* mc, long long i,
+                                          int world) {
+  if (kMC) return mm_ld_reduce_f32x4(mc + i);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+  for (int r = 0; r < world; ++r) {
+    const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(bufs.p[r]) + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  return acc;
+}
+template <bool kMC>
+__device__ __forceinline__ void bcast4(const ItbPeerPtrs& bufs, float* mc, long long i, int world,
+                                       float4 v) {
+  if (kMC) {
+    mm_st_f32x4(mc + i, v);
+  } else {
+#pragma unroll 1
+    for (int r = 0; r < world; ++r)
+      *reinterpret_cast<float4*>(static_cast<float*>(bufs.p[r]) + i) = v;
+  }
+}
+
+// ------------------------------------------------------------------ all-reduce (average)
+// In place on elements [off, off + n) of a symmetric fp32 buffer; n and off multiples of 4.
+template <bool kMC>
+__global__ void __launch_bounds__(kCommThreads)
+allreduce_scale_kernel(ItbPeerPtrs bufs, float* mc, ItbPeerPtrs flags, long long off, long long n,
+                       int rank, int world, int ch0, int epoch, float scale, int* err) {
+  const int ch = ch0 + blockIdx.x;
+  if (!rank_barrier(flags, rank, world, ch, epoch, err, 201)) return;
+  // slice of this rank, in units of 4 elements
+  const long long nv = n / 4;
+  const long long per = (nv + world - 1) / world;
+  const long long v0 = min(nv, per * rank), v1 = min(nv, v0 + per);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long v = v0 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < v1;
+       v += stride) {
+    const long long i = off + v * 4;
+    float4 s = reduce4<kMC>(bufs, mc, i, world);
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    bcast4<kMC>(bufs, mc, i, world, s);
+  }
+  rank_barrier(flags, rank, world, ch, epoch + 1, err, 202);
+}
+
+// ------------------------------------------------------------------ reduce-scatter + AdamW + broadcast
+// Bucket = elements [off, off + n) of the symmetric gradient / parameter / shadow buffers; rank r
+// owns [off + r n / world, off + (r+1) n / world).  m and v hold the owner shard only.
+template <bool kMC>
+__global__ void __launch_bounds__(kCommThreads)
+rs_adamw_bcast_kernel(ItbPeerPtrs grads, const float* mc_grads, ItbPeerPtrs params, float* mc_params,
+                      ItbPeerPtrs shadows, __nv_bfloat16* mc_shadows, float* __restrict__ m,
+                      float* __restrict__ v, ItbPeerPtrs flags, long long off, long long n, int rank,
+                      int world, int ch0, int epoch, ItbAdamHyper h, int* err) {
+  const int ch = ch0 + blockIdx.x;
+  if (!rank_barrier(flags, rank, world, ch, epoch, err, 203)) return;
+  const long long shard = n / world;           // multiple of 8 by construction of the buckets
+  const long long s0 = off + shard * rank;
+  const long long nv = shard / 8;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const float* my_params = static_cast<const float*>(params.p[rank]);
+  for (long long k = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; k < nv;
+       k += stride) {
+    const long long i = s0 + k * 8;   // index in the flat buffers
+    const long long j = k * 8;        // index in the shard-local state
+    float g[8], p[8], mm[8], vv[8];
+    *reinterpret_cast<float4*>(g) = reduce4<kMC>(grads, mc_grads, i, world);
+    *reinterpret_cast<float4*>(g + 4) = reduce4<kMC>(grads, mc_grads, i + 4, world);
+    *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(my_params + i);
+    *reinterpret_cast<float4*>(p + 4) = *reinterpret_cast<const float4*>(my_params + i + 4);
+    *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(m + j);
+    *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(m + j + 4);
+    *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(v + j);
+    *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(v + j + 4);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float ge = g[e] * h.grad_scale;
+      mm[e] = h.beta1 * mm[e] + (1.f - h.beta1) * ge;
+      vv[e] = h.beta2 * vv[e] + (1.f - h.beta2) * ge * ge;
+      const float mhat = mm[e] * h.inv_bc1, vhat = vv[e] * h.inv_bc2;
+      p[e] -= h.lr * (mhat / (sqrtf(vhat) + h.eps) + h.weight_decay * p[e]);
+    }
+    *reinterpret_cast<float4*>(m + j) = *reinterpret_cast<float4*>(mm);
+    *reinterpret_cast<float4*>(m + j + 4) = *reinterpret_cast<float4*>(mm + 4);
+    *reinterpret_cast<float4*>(v + j) = *reinterpret_cast<float4*>(vv);
+    *reinterpret_cast<float4*>(v + j + 4) = *reinterpret_cast<float4*>(vv + 4);
+    bcast4<kMC>(params, mc_params, i, world, *reinterpret_cast<float4*>(p));
+    bcast4<kMC>(params, mc_params, i + 4, world, *reinterpret_cast<float4*>(p + 4));
+    uint4 sh;
+    __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&sh);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) hb[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+    if (kMC) {
+      mm_st_bf16x8(mc_shadows + i, sh);
+    } else {
+#pragma unroll 1
+      for (int r = 0; r < world; ++r)
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(shadows.p[r]) + i) = sh;
+    }
+  }
+  rank_barrier(flags, rank, world, ch, epoch + 1, err, 204);
+}
+
+}  // namespace itb
+
+using namespace itb;
+
+extern "C" int itb_comm_blocks(long long n_elements_per_rank) {
+  long long b = (n_elements_per_rank / 4 + kCommThreads - 1) / kCommThreads;
+  if (b < 1) b = 1;
+  if (b > kItbMaxCommBlocks) b = kItbMaxCommBlocks;
+  return static_cast<int>(b);
+}
+
+extern "C" int itb_nvl_allreduce_scale(const ItbPeerPtrs* bufs, void* mc, const ItbPeerPtrs* flags,
+                                       long long off, long long n, int rank, int world, int ch0,
+                                       int epoch, float scale, int* err, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if ((off | n) & 3) return -3;
+  if (world < 1 || world > kItbMaxRanks) return -4;
+  const int blocks = itb_comm_blocks((n + world - 1) / world);
+  if (mc)
+    allreduce_scale_kernel<true><<<blocks, kCommThreads, 0, s>>>(
+        *bufs, static_cast<float*>(mc), *flags, off, n, rank, world, ch0, epoch, scale, err);
+  else
+    allreduce_scale_kernel<false><<<blocks, kCommThreads, 0, s>>>(*bufs, nullptr, *flags, off, n,
+                                                                  rank, world, ch0, epoch, scale, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int itb_nvl_rs_adamw_bcast(const ItbPeerPtrs* grads, const void* mc_grads,
+                                      const ItbPeerPtrs* params, void* mc_params,
+                                      const ItbPeerPtrs* shadows, void* mc_shadows, float* m, float* v,
+                                      const ItbPeerPtrs* flags, long long off, long long n, int rank,
+                                      int world, int ch0, int epoch, const ItbAdamHyper* h, int* err,
+                                      cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (world < 1 || world > kItbMaxRanks) return -4;
+  if (n % (8LL * world) || (off & 7)) return -3;
+  const bool mc = mc_grads && mc_params && mc_shadows;
+  const int blocks = itb_comm_blocks(n / world / 2);
+  if (mc)
+    rs_adamw_bcast_kernel<true><<<blocks, kCommThreads, 0, s>>>(
+        *grads, static_cast<const float*>(mc_grads), *params, static_cast<float*>(mc_params),
+        *shadows, static_cast<__nv_bfloat16*>(mc_shadows), m, v, *flags, off, n, rank, world, ch0,
+        epoch, *h, err);
+  else
+    rs_adamw_bcast_kernel<false><<<blocks, kCommThreads, 0, s>>>(
+        *grads, nullptr, *params, nullptr, *shadows, nullptr, m, v, *flags, off, n, rank, world, ch0,
+        epoch, *h, err);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -41,6 +41,7 @@ class DistributedDataParallel(Module):
         self.pg = process_group if process_group is not None else ProcessGroupFactory.Instance().dp_group()
         self.dp_size = self.pg.world_size if self.pg is not None else 1
         self.reducer: Optional[Reducer] = None
+        self.nvlink_ctx = None
         self.param_grad_buffers: List[ParamAndGradBuffer] = []
         self.bucket_groups: List[ParamAndGradBucketGroup] = []
         self.param_to_group = {}
@@ -73,25 +74,44 @@ class DistributedDataParallel(Module):
     def _build_reducer(self, params):
         limits = [self.config.first_bucket_cap_mb * kBytesPerMB, self.config.normal_bucket_cap_mb * kBytesPerMB]
         flat = None
+        allreduce_fn = None
         if all(p.is_cuda and p.dtype == torch.float32 for p in params):
             # One flat fp32 parameter / gradient buffer (+ bf16 shadow) shared with the fused
             # optimizer; buckets are contiguous slices of it.
-            flat = ParamAndGradBuffer(params, self.pg, DistributedDataParallelConfig(zero_stage=0))
+            ctx = self._nvlink_context(params[0].device)
+            flat = ParamAndGradBuffer(params, self.pg, DistributedDataParallelConfig(zero_stage=0),
+                                      allocator=ctx.alloc if ctx is not None else None)
             for p in params:
                 p._itb_flat_buffer = flat
             self.param_grad_buffers = [flat]
-        indices = ComputeBucketAssignmentBySize(params, limits)
-        allreduce_fn = None
-        if self.config.use_fused_nvlink_kernels and flat is not None and self.dp_size > 1:
-            from .. import symm
+            if ctx is not None:
+                from .. import symm
 
-            allreduce_fn = symm.make_bucket_allreduce(self.pg, flat)
+                fused = symm.BucketAllReduce(ctx, flat.grad_buffer)
+
+                def allreduce_fn(contents, fused=fused, pg=self.pg):
+                    work = fused(contents)
+                    return work if work is not None else pg.AllReduce(contents, ReduceOpType.kAvg, async_op=True)
+        indices = ComputeBucketAssignmentBySize(params, limits)
         self.reducer = Reducer(params, indices, self.pg, self.config, allreduce_fn=allreduce_fn, flat_buffer=flat)
         self.reducer.AttachHooksToParameters()
 
     # ------------------------------------------------------------------ mode: ZeRO-1/2
+    def _nvlink_context(self, device):
+        """The symmetric-memory context of the data-parallel group, or None when the fused NVLink
+        kernels are off or unavailable (CPU ranks, gloo, more than 8 ranks)."""
+        if not self.config.use_fused_nvlink_kernels:
+            return None
+        from .. import symm
+
+        if not symm.nvlink_available(self.pg, device):
+            return None
+        self.nvlink_ctx = symm.NvlinkContext.get(self.pg, device)
+        return self.nvlink_ctx
+
     def _build_param_and_grad_buffers(self, params):
-        buf = ParamAndGradBuffer(params, self.pg, self.config)
+        ctx = self._nvlink_context(params[0].device) if all(p.is_cuda and p.dtype == torch.float32 for p in params) else None
+        buf = ParamAndGradBuffer(params, self.pg, self.config, allocator=ctx.alloc if ctx is not None else None)
         self.param_grad_buffers = [buf]
         for p in params:
             p._itb_flat_buffer = buf
@@ -103,7 +123,7 @@ class DistributedDataParallel(Module):
         for i in range(len(self.bucket_groups) - 1, 0, -1):
             self.bucket_groups[i].SetNextParamGatherBucketGroup(self.bucket_groups[i - 1])
         for p in params:
-            if self.config.zero_stage >= 2:
+            if buf.zero2_temp_grads:
                 g = self.param_to_group[id(p)]
                 p._itb_main_grad_fn = (lambda g=g, p=p: g.full_grad_view(p))
                 self._hook_handles.append(p.register_post_accumulate_grad_hook(self._zero2_hook))

@@ -42,7 +42,7 @@ class DistributedOptimizer(Optimizer):
                 s, e = g.buffer.shard_range(bucket, g.rank_in_pg)
                 shard = torch.nn.Parameter(bucket.param_data[s:e], requires_grad=True)
                 shard._itb_no_flatten = True   # already a slice of a flat buffer: update it in place
-                if g.config.zero_stage >= 2:
+                if g.zero2:
                     shard.grad = g.grad_shard_buffers[bi]
                 else:
                     shard.grad = bucket.grad_data[s:e]
@@ -51,6 +51,34 @@ class DistributedOptimizer(Optimizer):
                 self.shard_params.append(shard)
                 self.shard_meta.append((g, bi, s, e))
         self.base_optimizer = creator(self.shard_params)
+        self.fused = self._install_fused_steps(chunks)
+
+    def _install_fused_steps(self, chunks) -> bool:
+        """With the NVLink kernels, a bucket's reduce-scatter, its AdamW update and the broadcast of
+        the updated weights are ONE kernel launched as soon as the bucket's gradients are ready, i.e.
+        the optimizer step overlaps the rest of backward.  Needs an Adam base optimizer."""
+        from ...optim.optimizer import Adam
+        from .. import symm
+
+        base = self.base_optimizer
+        if not isinstance(base, Adam) or not all(getattr(ch, "nvlink_ctx", None) is not None for ch in chunks):
+            return False
+        k = 0
+        for ch in chunks:
+            ctx = ch.nvlink_ctx
+            for g in ch.bucket_groups:
+                steps = []
+                for bucket in g.buckets:
+                    steps.append(symm.FusedZeroBucketStep(ctx, g.buffer, bucket, base.m[k], base.v[k]))
+                    k += 1
+                g.fused_steps = steps
+                g.fused_hyper_fn = self._fused_hyper
+        return True
+
+    def _fused_hyper(self):
+        b = self.base_optimizer
+        t = b.t + 1   # the step these launches belong to (Step() increments t afterwards)
+        return (b.learning_rate, b.beta1, b.beta2, b.eps, b.weight_decay, 1.0 - b.beta1 ** t, 1.0 - b.beta2 ** t, 1.0)
 
     def ZeroGrad(self, set_to_none: bool = True) -> None:
         for buf in self.buffers:
@@ -81,6 +109,12 @@ class DistributedOptimizer(Optimizer):
 
     def Step(self) -> None:
         self.FinishGradSync()
+        if self.fused:
+            # Every bucket was reduced, updated and broadcast by its fused kernel during backward.
+            self.base_optimizer.t += 1
+            for buf in self.buffers:
+                buf.mark_shadows_fresh()
+            return
         self.base_optimizer.Step()
         self.StartParamSync()
         self.FinishParamSync(skip_next_bucket_dispatch=True)

@@ -136,7 +136,10 @@ class ParamAndGradBuffer:
         self.param_buffer = alloc(self.numel, torch.float32, dev)
         # ZeRO-2 keeps no persistent full gradient buffer: full-bucket buffers live only from the
         # first gradient of a bucket to the end of its reduce-scatter.
-        self.grad_buffer = None if zero >= 2 else alloc(self.numel, torch.float32, dev)
+        # (The NVLink kernels read peers' gradients in place, so with them the buffer stays.)
+        keep_full_grads = zero < 2 or allocator is not None
+        self.grad_buffer = alloc(self.numel, torch.float32, dev) if keep_full_grads else None
+        self.zero2_temp_grads = zero >= 2 and not keep_full_grads
         if with_shadow is None:
             with_shadow = dev.type == "cuda"
         self.shadow_buffer = alloc(self.numel, torch.bfloat16, dev) if with_shadow else None
@@ -226,7 +229,13 @@ class ParamAndGradBucketGroup:
         # ZeRO-2: persistent 1/dp gradient shard per bucket + temporary full-bucket buffers.
         self.grad_shard_buffers: List[Optional[torch.Tensor]] = [None] * len(self.buckets)
         self.temp_full_grad: List[Optional[torch.Tensor]] = [None] * len(self.buckets)
-        if config.zero_stage >= 2:
+        self.zero2 = config.zero_stage >= 2 and buffer.grad_buffer is None
+        # Fused NVLink path: one callable per bucket that performs reduce-scatter + optimizer update
+        # + parameter broadcast, and a callable that returns the optimizer's hyper-parameters.
+        self.fused_steps: Optional[list] = None
+        self.fused_hyper_fn = None
+        self.fused_updated = False
+        if self.zero2:
             for i, b in enumerate(self.buckets):
                 self.grad_shard_buffers[i] = torch.zeros(b.numel // self.pg_size, dtype=torch.float32,
                                                          device=buffer.device)
@@ -240,7 +249,8 @@ class ParamAndGradBucketGroup:
         self.grad_reduce_dispatched = False
         self.grad_sync_done = False
         self.param_gather_dispatched = False
-        if self.config.zero_stage >= 2:
+        self.fused_updated = False
+        if self.zero2:
             self.temp_full_grad = [None] * len(self.buckets)
 
     # ------------------------------------------------------------------ ZeRO-2 gradient stash
@@ -278,8 +288,16 @@ class ParamAndGradBucketGroup:
             return
         op = ReduceOpType.kAvg if self.config.average_in_collective else ReduceOpType.kSum
         async_op = self.config.overlap_grad_reduce
+        if self.fused_steps is not None and self.fused_hyper_fn is not None:
+            hyper = self.fused_hyper_fn()
+            for step in self.fused_steps:
+                self.grad_reduce_works.append(step(*hyper))
+            self.fused_updated = True
+            self.grad_reduce_dispatched = True
+            self.params_with_grad.clear()
+            return
         for i, bucket in enumerate(self.buckets):
-            if self.config.zero_stage >= 2:
+            if self.zero2:
                 full = self.temp_full_grad[i]
                 if full is None:
                     full = torch.zeros(bucket.numel, dtype=torch.float32, device=self.buffer.device)
@@ -310,7 +328,7 @@ class ParamAndGradBucketGroup:
             if w is not None:
                 w.WaitNonBlocking()
         self.grad_reduce_works.clear()
-        if self.config.zero_stage >= 2:
+        if self.zero2:
             self.temp_full_grad = [None] * len(self.buckets)
         self.grad_reduce_dispatched = False
         self.grad_sync_done = True

@@ -1,0 +1,156 @@
+"""Worker of the multi-GPU tests; launched with torchrun, one process per GPU."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def setup():
+    from infinitrain_b200.parallel import global_env as genv
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    genv.InitAllEnv(world_size=world, rank=rank)
+    ProcessGroupFactory.Instance().Init(device=dev, timeout_s=120)
+    return rank, world, dev
+
+
+def collectives():
+    import torch.distributed as dist
+
+    from infinitrain_b200.parallel import symm
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory
+
+    rank, world, dev = setup()
+    pg = ProcessGroupFactory.Instance().dp_group()
+    ctx = symm.NvlinkContext.get(pg, dev)
+    n = 1 << 20
+    buf = ctx.alloc(n + 1024, torch.float32, dev)
+    torch.manual_seed(rank)
+    for it in range(3):
+        buf[:n].normal_()
+        ref = buf[:n].clone()
+        dist.all_reduce(ref, op=dist.ReduceOp.AVG)
+        ar = symm.BucketAllReduce(ctx, buf)
+        w = ar(buf[256:n])   # a slice, as DDP buckets are
+        assert w is not None
+        w.WaitNonBlocking()
+        torch.cuda.synchronize()
+        err = (buf[256:n] - ref[256:]).abs().max().item()
+        assert err < 1e-5, err
+    assert ctx.status() == 0
+    # fused reduce-scatter + AdamW + broadcast against NCCL + the single-GPU AdamW kernel
+    C = ctx.C
+    nb = 8 * world * 1000
+    grads = ctx.alloc(nb, torch.float32, dev)
+    params = ctx.alloc(nb, torch.float32, dev)
+    shadow = ctx.alloc(nb, torch.bfloat16, dev)
+    torch.manual_seed(100)
+    init = torch.randn(nb, device=dev)
+    params.copy_(init)
+    torch.manual_seed(rank + 1)
+    grads.normal_()
+    gref = grads.clone()
+    dist.all_reduce(gref, op=dist.ReduceOp.AVG)
+    pref = init.clone()
+    mref, vref = torch.zeros(nb, device=dev), torch.zeros(nb, device=dev)
+    C.adamw(pref, gref, mref, vref, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0)
+
+    class _B:  # minimal stand-ins for ParamAndGradBuffer / bucket
+        grad_buffer, param_buffer, shadow_buffer = grads, params, shadow
+
+    class _K:
+        offset, numel = 0, nb
+
+    m = torch.zeros(nb // world, device=dev)
+    v = torch.zeros(nb // world, device=dev)
+    step = symm.FusedZeroBucketStep(ctx, _B, _K, m, v)
+    step(1e-2, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0 / world).WaitNonBlocking()
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert torch.allclose(params, pref, atol=1e-6, rtol=1e-5), (params - pref).abs().max().item()
+    assert torch.equal(shadow, pref.bfloat16()) or (shadow.float() - pref).abs().max().item() < 1e-2
+    assert ctx.status() == 0
+    if rank == 0:
+        print("COLLECTIVES OK multimem=%d" % int(ctx.ptrs(buf)[1] != 0))
+
+
+def ddp(mode):
+    import torch.distributed as dist
+
+    from infinitrain_b200.autocast import AutocastGuard
+    from infinitrain_b200.datatype import DataType
+    from infinitrain_b200.device import DeviceType
+    from infinitrain_b200.models import GPT2
+    from infinitrain_b200.nn import CrossEntropyLoss, init
+    from infinitrain_b200.optim import Adam
+    from infinitrain_b200.parallel.ddp.config import DistributedDataParallelConfig
+    from infinitrain_b200.parallel.ddp.distributed_data_parallel import DistributedDataParallel
+    from infinitrain_b200.parallel.ddp.distributed_optimizer import DistributedOptimizer
+
+    rank, world, dev = setup()
+    zero = int(mode[4])
+    fused = not mode.endswith("nccl")
+
+    def make():
+        torch.manual_seed(0)
+        init.manual_seed(42)
+        return GPT2("gpt2", n_layer=2, block_size=128).to(dev)
+
+    B, T, steps = 4, 128, 4
+    g = torch.Generator().manual_seed(5)
+    x = torch.randint(0, 50257, (B * world, T), generator=g).to(dev)
+    y = torch.randint(0, 50257, (B * world, T), generator=g).to(dev)
+    loss_fn = CrossEntropyLoss()
+
+    def run(model, opt, xs, ys, ddp_mod=None):
+        out = []
+        for _ in range(steps):
+            opt.ZeroGrad()
+            with AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16):
+                loss = loss_fn(model(xs), ys)
+            loss.backward()
+            if ddp_mod is not None:
+                ddp_mod.FinishGradSync()
+            opt.Step()
+            out.append(loss.detach().clone())
+        return torch.stack(out)
+
+    # oracle: single GPU, whole batch
+    ref_model = make()
+    ref_losses = run(ref_model, Adam(ref_model.Parameters(), 1e-3), x, y)
+    ref_params = [p.detach().clone() for p in ref_model.Parameters()]
+
+    model = make()
+    cfg = DistributedDataParallelConfig(zero_stage=zero, use_fused_nvlink_kernels=fused)
+    ddp_mod = DistributedDataParallel(model, config=cfg)
+    creator = Adam.Create(1e-3)
+    opt = DistributedOptimizer(creator, ddp_mod.Parameters(), ddp_mod) if zero >= 1 else creator(ddp_mod.Parameters())
+    if fused:
+        assert ddp_mod.nvlink_ctx is not None, "fused NVLink kernels expected"
+    losses = run(ddp_mod, opt, x.chunk(world)[rank], y.chunk(world)[rank], ddp_mod)
+    dist.all_reduce(losses, op=dist.ReduceOp.AVG)
+    assert (losses - ref_losses).abs().max().item() < 2e-2, (losses, ref_losses)
+    worst = 0.0
+    for p, r in zip(ddp_mod.Parameters(), ref_params):
+        worst = max(worst, ((p - r).norm() / (r.norm() + 1e-9)).item())
+    assert worst < 2e-2, worst
+    if ddp_mod.nvlink_ctx is not None:
+        assert ddp_mod.nvlink_ctx.status() == 0
+    if rank == 0:
+        print(f"DDP OK mode={mode} worst_rel={worst:.2e} losses={losses.tolist()}")
+
+
+if __name__ == "__main__":
+    if sys.argv[1] == "collectives":
+        collectives()
+    else:
+        ddp(sys.argv[2])
+    import torch.distributed as dist
+
+    dist.barrier()
+    dist.destroy_process_group()
