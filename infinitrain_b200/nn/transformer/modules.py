@@ -251,7 +251,11 @@ class TransformerModel(Module):
         self.add_module(self.kTransformerModelName, ModuleDict(transformer))
         if config.tie_weights and pp == 1:
             # One Parameter object serves both the embedding lookup and the output projection.
-            self._modules[kPPFirstStageName].wte.weight = self._modules[kPPLastStageName].lm_head.weight
+            shared = self._modules[kPPLastStageName].lm_head.weight
+            self._modules[kPPFirstStageName].wte.weight = shared
+            # Two ops produce gradient for this tensor: both go through autograd so that the
+            # parameter's grad-ready hook fires once, after the last contribution.
+            shared._itb_shared = True
 
     # ------------------------------------------------------------------ pipeline pieces
     def first_stage(self):

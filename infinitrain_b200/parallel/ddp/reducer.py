@@ -94,6 +94,7 @@ class Reducer:
         self.has_rebuilt = False
         self.need_rebuild = False
         self._index_of = {id(p): i for i, p in enumerate(self.params)}
+        self._marked = set()
         self._hook_handles = []
         self.InitializeBuckets(bucket_indices)
 
@@ -163,6 +164,7 @@ class Reducer:
         self.RebindGradViews()
         self.next_bucket = 0
         self.expect_hooks = True
+        self._marked = set()
         for b in self.buckets:
             b.pending = sum(1 for i in b.variable_indices if self.params[i].requires_grad)
             b.work = None
@@ -188,8 +190,12 @@ class Reducer:
                 p.main_grad = view
 
     def MarkVariableReadyDense(self, index: int):
-        if not self.expect_hooks:
+        if not self.expect_hooks or index in self._marked:
+            # A parameter is counted once per backward pass: weights whose gradient GEMM accumulates
+            # straight into the bucket report from there, and autograd's accumulate hook may fire
+            # for them again with an undefined gradient.
             return
+        self._marked.add(index)
         if not self.has_rebuilt:
             self.grad_ready_order.append(index)
         b, j = self.locator[index]
