@@ -492,3 +492,52 @@ extern "C" int itb_colsum(const void* x, int dtype, long long ld, float* out, fl
   colsum_stage2_kernel<<<(N + 31) / 32, 256, 0, s>>>(partial, nparts, out, N, accumulate);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------ column sum without allocation
+// Same two kernels as itb_colsum, with the stage-1 partial sums in a fixed device array instead of a
+// caller-provided buffer (see no_alloc.h for who needs this and for the rules).
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_colsum_static_scratch[kItbColsumStaticMaxPartials];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of g_colsum_static_scratch per device ordinal.  In host code the array's name is
+// only a handle for the runtime, not a device pointer: the address must be looked up.
+float* g_scratch_addr[kMaxDevices] = {nullptr};
+
+int colsum_static_scratch(float** out_ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return -6;
+  if (!g_scratch_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_colsum_static_scratch);  // for the CURRENT device
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *out_ptr = g_scratch_addr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int itb_colsum_static(const void* x, int dtype, long long ld, float* out, int rows, int N,
+                                 int accumulate, cudaStream_t s) {
+  if (rows <= 0 || N <= 0) return 0;
+  if (N % 8 || ld % 8) return -3;
+  if (dtype != kItbBF16 && dtype != kItbF32) return -4;
+  const int nparts = itb_colsum_partial_rows(rows);
+  if (static_cast<long long>(nparts) * N > kItbColsumStaticMaxPartials) return kItbErrScratchTooSmall;
+  float* partial = nullptr;
+  if (int rc = colsum_static_scratch(&partial)) return rc;
+  dim3 grid((N + 255) / 256, nparts);
+  if (dtype == kItbBF16)
+    colsum_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
+                                                             ld, partial, rows, N);
+  else
+    colsum_stage1_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), ld, partial, rows,
+                                                     N);
+  colsum_stage2_kernel<<<(N + 31) / 32, 256, 0, s>>>(partial, nparts, out, N, accumulate);
+  return static_cast<int>(cudaGetLastError());
+}
