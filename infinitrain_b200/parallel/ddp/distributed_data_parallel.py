@@ -67,7 +67,7 @@ class DistributedDataParallel(Module):
 
     # ------------------------------------------------------------------ mode: per-parameter
     def _allreduce_hook(self, p):
-        if self.dp_size > 1 and p.grad is not None:
+        if self.dp_size > 1 and p.grad is not None and getattr(self, "_sync_enabled", True):
             self.pg.AllReduce(p.grad, ReduceOpType.kAvg, async_op=False)
 
     # ------------------------------------------------------------------ mode: reducer (ZeRO-0)
@@ -145,10 +145,32 @@ class DistributedDataParallel(Module):
         if g is not None:
             g.RegisterGradReady(p)
 
+    # ------------------------------------------------------------------ gradient accumulation
+    def no_sync(self):
+        """Context in which backward passes only accumulate gradients locally (micro-batches before
+        the last one); the synchronisation is armed again on exit."""
+        ddp = self
+
+        class _NoSync:
+            def __enter__(self_inner):
+                ddp._sync_enabled = False
+                if ddp.reducer is not None:
+                    ddp.reducer.expect_hooks = False
+                for g in ddp.bucket_groups:
+                    g.is_last_microbatch = False
+
+            def __exit__(self_inner, *exc):
+                ddp._sync_enabled = True
+                for g in ddp.bucket_groups:
+                    g.is_last_microbatch = True
+                return False
+
+        return _NoSync()
+
     # ------------------------------------------------------------------ forward
     def Forward(self, *inputs, **kwargs):
         out = self._modules[self.kModuleName](*inputs, **kwargs)
-        if self.reducer is not None and torch.is_grad_enabled():
+        if self.reducer is not None and torch.is_grad_enabled() and getattr(self, "_sync_enabled", True):
             self.reducer.PrepareForBackward()
         return out
 
