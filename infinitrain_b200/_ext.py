@@ -42,7 +42,7 @@ def sources() -> list[Path]:
 def _headers() -> list[Path]:
     out = []
     for pat in ("common/*.cuh", "common/*.h", "kernels/*.h", "kernels/*.cuh", "comm/*.h", "comm/*.cuh",
-                "runtime/*.h"):
+                "runtime/*.h", "launcher/*.cc"):
         out += sorted(_CSRC.glob(pat))
     return out
 
@@ -107,8 +107,21 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         link += [f"-L{d}", f"-Wl,-rpath,{d}"]
     link += ["-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda", "-lcudart"]
     _run(link)
+    build_launcher()
     _HASH.write_text(source_hash())
     return _SO
+
+
+def launcher_path() -> Path:
+    return _PKG / "bin" / "infini_run"
+
+
+def build_launcher() -> Path:
+    """Compile the standalone C++ launcher (one process per local rank, rendezvous environment)."""
+    out = launcher_path()
+    out.parent.mkdir(parents=True, exist_ok=True)
+    _run(["g++", "-O2", "-std=c++17", str(_CSRC / "launcher" / "infini_run.cc"), "-o", str(out)])
+    return out
 
 
 def load(required: bool | None = None):

@@ -1,0 +1,157 @@
+"""Checkpoints: binary state-dict files, trainer state, save / resume / pruning.
+
+Reference: infini_train/src/checkpoint/checkpoint.cc:112-215, checkpoint_manager.cc:21-120.
+A checkpoint directory holds ``model.ckpt``, ``optimizer.ckpt`` (optional) and
+``trainer_state.json``; with more than one rank every rank saves its own shard under
+``rank_%06d``.  State-dict files use the reference's layout (magic 0x54504B43, version 1) and are
+written by the native runtime through a temporary file + rename.  ``trainer_state.json`` is valid JSON
+here (the reference omits a comma); the reader accepts both.  Resume validates the model shape and
+the (ddp, tp, sp, pp) topology; ``allow_dp_resize`` relaxes the data-parallel check for model-only
+restores.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+import shutil
+import time
+from collections import OrderedDict
+from dataclasses import asdict, dataclass
+from typing import Dict, Optional
+
+import torch
+
+from .. import _ext
+from ..parallel import global_env as genv
+
+
+@dataclass
+class TrainerState:
+    global_step: int = 0
+    consumed_batches: int = 0
+    last_lr: float = 0.0
+    n_layer: int = 0
+    n_head: int = 0
+    n_kv_head: int = 0
+    n_embd: int = 0
+    vocab_size: int = 0
+    ddp_size: int = 1
+    tp_size: int = 1
+    sp_size: int = 1
+    pp_size: int = 1
+
+
+def _native():
+    C = _ext.load(required=False)
+    if C is None:
+        raise RuntimeError("checkpoint IO needs the native runtime (infinitrain_b200._C)")
+    return C
+
+
+class Checkpoint:
+    @staticmethod
+    def SaveStateDict(path: str, state_dict: Dict[str, torch.Tensor]) -> None:
+        names = list(state_dict.keys())
+        _native().save_state_dict(path, names, [state_dict[k].detach() for k in names])
+
+    @staticmethod
+    def LoadStateDict(path: str) -> "OrderedDict[str, torch.Tensor]":
+        return OrderedDict(_native().load_state_dict(path))
+
+    @staticmethod
+    def SaveTrainerState(path: str, state: TrainerState) -> None:
+        order = ["n_layer", "n_head", "n_kv_head", "n_embd", "vocab_size", "global_step", "consumed_batches", "last_lr",
+                 "ddp_size", "tp_size", "sp_size", "pp_size"]
+        d = asdict(state)
+        with open(path, "w") as f:
+            f.write("{\n" + ",\n".join(f'  "{k}": {d[k]}' for k in order) + "\n}\n")
+
+    @staticmethod
+    def LoadTrainerState(path: str) -> TrainerState:
+        text = open(path).read()
+        st = TrainerState()
+        for k, v in asdict(st).items():
+            m = re.search(r'"%s"\s*:\s*(-?[0-9.eE+-]+)' % re.escape(k), text)   # tolerant field scan
+            if m:
+                setattr(st, k, type(v)(float(m.group(1))) if isinstance(v, int) else float(m.group(1)))
+        return st
+
+    @staticmethod
+    def Save(checkpoint_dir: str, model, optimizer, state: TrainerState, save_optimizer_state: bool = True) -> None:
+        os.makedirs(checkpoint_dir, exist_ok=True)
+        sd = model.StateDict() if hasattr(model, "StateDict") else model.state_dict()
+        Checkpoint.SaveStateDict(os.path.join(checkpoint_dir, "model.ckpt"), sd)
+        if save_optimizer_state and optimizer is not None:
+            osd = optimizer.StateDict()
+            if osd:
+                Checkpoint.SaveStateDict(os.path.join(checkpoint_dir, "optimizer.ckpt"), osd)
+        Checkpoint.SaveTrainerState(os.path.join(checkpoint_dir, "trainer_state.json"), state)
+
+    @staticmethod
+    def Load(checkpoint_dir: str, model, optimizer, load_optimizer_state: bool = True) -> TrainerState:
+        sd = Checkpoint.LoadStateDict(os.path.join(checkpoint_dir, "model.ckpt"))
+        model.LoadStateDict(sd)
+        if load_optimizer_state and optimizer is not None:
+            opt_path = os.path.join(checkpoint_dir, "optimizer.ckpt")
+            if os.path.exists(opt_path):
+                optimizer.LoadStateDict(Checkpoint.LoadStateDict(opt_path))
+            elif optimizer.StateDict():
+                raise FileNotFoundError(f"Optimizer checkpoint not found at: {opt_path}")
+        return Checkpoint.LoadTrainerState(os.path.join(checkpoint_dir, "trainer_state.json"))
+
+
+def _rank_dir(root: str, rank: int, world: int) -> str:
+    return os.path.join(root, f"rank_{rank:06d}") if world > 1 else root
+
+
+def SaveCheckpoint(checkpoint_root_dir: str, global_step: int, model, optimizer, model_config, consumed_batches: int = 0,
+                   last_lr: float = 0.0, save_optimizer_state: bool = True, max_checkpoint_keep: int = 0,
+                   rank: Optional[int] = None) -> str:
+    """Writes ``<root>/checkpoint_step_%06d[/rank_%06d]`` and prunes old step directories (rank 0,
+    lexicographic order of the zero-padded names, keep the newest ``max_checkpoint_keep``)."""
+    rank = genv.MyRank() if rank is None else rank
+    world = genv.GetWorldSize()
+    t0 = time.time()
+    step_dir = os.path.join(checkpoint_root_dir, f"checkpoint_step_{global_step:06d}")
+    state = TrainerState(global_step, consumed_batches, last_lr, model_config.n_layer, model_config.n_head,
+                         model_config.n_kv_head, model_config.n_embd, model_config.vocab_size,
+                         genv.GetDataParallelSize(), genv.GetTensorParallelSize(), genv.GetSequenceParallelSize(),
+                         genv.GetPipelineParallelSize())
+    Checkpoint.Save(_rank_dir(step_dir, rank, world), model, optimizer, state, save_optimizer_state)
+    if rank == 0 and max_checkpoint_keep > 0 and os.path.isdir(checkpoint_root_dir):
+        ckpts = sorted(d for d in os.listdir(checkpoint_root_dir)
+                       if d.startswith("checkpoint_step_") and os.path.isdir(os.path.join(checkpoint_root_dir, d)))
+        while len(ckpts) > max_checkpoint_keep:
+            shutil.rmtree(os.path.join(checkpoint_root_dir, ckpts.pop(0)), ignore_errors=True)
+    return step_dir
+
+
+@dataclass
+class ResumeFromCheckpointResult:
+    global_step: int = 0
+    consumed_batches: int = 0
+    last_lr: float = 0.0
+
+
+def ResumeFromCheckpoint(resume_root: str, model, optimizer, model_config, load_optimizer_state: bool = True,
+                         rank: Optional[int] = None, allow_dp_resize: bool = False) -> ResumeFromCheckpointResult:
+    res = ResumeFromCheckpointResult()
+    if not resume_root:
+        return res
+    rank = genv.MyRank() if rank is None else rank
+    d = resume_root
+    rd = os.path.join(resume_root, f"rank_{rank:06d}")
+    if genv.GetWorldSize() > 1 and os.path.isdir(rd):
+        d = rd
+    st = Checkpoint.Load(d, model, optimizer, load_optimizer_state)
+    for k in ("n_layer", "n_head", "n_kv_head", "n_embd", "vocab_size"):
+        if getattr(st, k) != getattr(model_config, k):
+            raise ValueError(f"{k} mismatch: ckpt={getattr(st, k)}, config={getattr(model_config, k)}")
+    topo = {"ddp_size": genv.GetDataParallelSize(), "tp_size": genv.GetTensorParallelSize(),
+            "sp_size": genv.GetSequenceParallelSize(), "pp_size": genv.GetPipelineParallelSize()}
+    for k, cur in topo.items():
+        if getattr(st, k) != cur and not (k == "ddp_size" and allow_dp_resize and not load_optimizer_state):
+            raise ValueError(f"{k.upper()} mismatch: checkpoint has {getattr(st, k)}, but current run has {cur}")
+    res.global_step, res.consumed_batches, res.last_lr = st.global_step, max(st.consumed_batches, 0), st.last_lr
+    return res

@@ -1,0 +1,2 @@
+from .dataset import (DataLoader, Dataset, DistributedDataLoader, TinyShakespeareDataset, write_token_file)
+from .tokenizer import Tokenizer, write_tokenizer_file

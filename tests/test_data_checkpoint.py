@@ -1,0 +1,130 @@
+"""Token files, loaders, tokenizer, checkpoint files and resume (CPU)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from infinitrain_b200 import nn
+from infinitrain_b200.checkpoint import Checkpoint, ResumeFromCheckpoint, SaveCheckpoint, TrainerState
+from infinitrain_b200.data import (DataLoader, DistributedDataLoader, TinyShakespeareDataset, Tokenizer,
+                                   write_token_file, write_tokenizer_file)
+from infinitrain_b200.data.tokenizer import RandomF32, RandomU32
+from infinitrain_b200.optim import SGD, Adam
+
+
+@pytest.fixture(autouse=True)
+def _env():
+    from infinitrain_b200.parallel import global_env as genv
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory
+
+    genv.InitAllEnv(world_size=1, rank=0)
+    ProcessGroupFactory.Reset()
+    ProcessGroupFactory.Instance().Init()
+
+
+@pytest.mark.parametrize("llama3", [False, True])
+def test_token_dataset_and_loaders(tmp_path, llama3):
+    toks = np.arange(1000) % (60000 if not llama3 else 100000)
+    path = os.path.join(tmp_path, "tok.bin")
+    write_token_file(path, toks, llama3)
+    ds = TinyShakespeareDataset(path, 16)
+    assert ds.Size() == 1000 // 16 - 1
+    x, y = ds[3]
+    assert x.dtype == torch.int64 and x.tolist() == list(range(48, 64)) and y.tolist() == list(range(49, 65))
+    dl = DataLoader(ds, 4)
+    xb, yb = next(iter(dl))
+    assert xb.shape == (4, 16) and xb[1, 0].item() == 16 and yb[1, 0].item() == 17
+    # rank r of 2 reads batches r, r+2, ...
+    for r in range(2):
+        it = iter(DistributedDataLoader(ds, 4, r, 2, pin_memory=False))
+        b0, _ = next(it)
+        b1, _ = next(it)
+        assert b0[0, 0].item() == r * 4 * 16 and b1[0, 0].item() == (r + 2) * 4 * 16
+    n0 = sum(1 for _ in DistributedDataLoader(ds, 4, 0, 2, pin_memory=False))
+    n1 = sum(1 for _ in DistributedDataLoader(ds, 4, 1, 2, pin_memory=False))
+    assert n0 + n1 == ds.Size() // 4
+
+
+def test_tokenizer_and_sampler(tmp_path):
+    path = os.path.join(tmp_path, "tok.tokenizer")
+    write_tokenizer_file(path, [b"a", b"bc", b" d"], magic=20240328, version=2, eot=2)
+    t = Tokenizer(path)
+    assert t.vocab_size == 3 and t.GetEndOfText() == 2 and t.Decode(1) == "bc" and t.Decode(9) == "[INVALID_TOKEN]"
+    s = [1337]
+    a, b = RandomU32(s), RandomU32(s)
+    assert a != b and 0 <= RandomF32(s) < 1.0
+    s2 = [1337]
+    assert RandomU32(s2) == a        # deterministic stream
+
+
+def test_state_dict_file_roundtrip(tmp_path):
+    sd = {"w": torch.randn(3, 5), "b": torch.arange(7, dtype=torch.int64), "h": torch.randn(4).bfloat16(),
+          "s": torch.tensor(3.5)}
+    p = os.path.join(tmp_path, "x.ckpt")
+    Checkpoint.SaveStateDict(p, sd)
+    with open(p, "rb") as f:
+        assert int.from_bytes(f.read(4), "little") == 0x54504B43 and int.from_bytes(f.read(4), "little") == 1
+    back = Checkpoint.LoadStateDict(p)
+    assert list(back.keys()) == list(sd.keys())
+    for k in sd:
+        assert back[k].dtype == sd[k].dtype and torch.equal(back[k], sd[k])
+    with open(p, "r+b") as f:        # corrupt the magic: the reader must refuse
+        f.write(b"\0\0\0\0")
+    with pytest.raises(RuntimeError):
+        Checkpoint.LoadStateDict(p)
+
+
+def test_trainer_state_json_tolerant(tmp_path):
+    p = os.path.join(tmp_path, "trainer_state.json")
+    Checkpoint.SaveTrainerState(p, TrainerState(global_step=30, consumed_batches=120, last_lr=1e-4, n_layer=12, vocab_size=50257))
+    import json
+
+    assert json.load(open(p))["global_step"] == 30          # valid JSON
+    # the reference's writer forgets the comma after vocab_size: still readable
+    open(p, "w").write('{\n  "n_layer": 12,\n  "vocab_size": 50257\n  "global_step": 31,\n  "last_lr": 0.0001\n}\n')
+    st = Checkpoint.LoadTrainerState(p)
+    assert st.global_step == 31 and st.vocab_size == 50257 and abs(st.last_lr - 1e-4) < 1e-12
+
+
+def test_checkpoint_resume_continues_identically(tmp_path):
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+
+    cfg = TransformerConfig.GPT2(n_layer=2, n_embd=32, n_head=2, n_kv_head=2, vocab_size=64, original_vocab_size=64,
+                                 block_size=16)
+    torch.manual_seed(0)
+    x = torch.randint(0, 64, (4, 16))
+
+    def steps(model, opt, n):
+        out = []
+        for _ in range(n):
+            opt.ZeroGrad()
+            loss = nn.CrossEntropyLoss()(model(x), x)
+            loss.backward()
+            opt.Step()
+            out.append(loss.item())
+        return out
+
+    m = TransformerModel(cfg)
+    opt = Adam(m.Parameters(), 1e-2)
+    steps(m, opt, 3)
+    root = os.path.join(tmp_path, "ck")
+    SaveCheckpoint(root, 3, m, opt, cfg, consumed_batches=3, last_lr=1e-2, max_checkpoint_keep=2)
+    cont = steps(m, opt, 2)
+    m2 = TransformerModel(cfg)
+    opt2 = Adam(m2.Parameters(), 1e-2)
+    res = ResumeFromCheckpoint(os.path.join(root, "checkpoint_step_000003"), m2, opt2, cfg)
+    assert res.global_step == 3 and res.consumed_batches == 3 and opt2.t == 3
+    assert steps(m2, opt2, 2) == pytest.approx(cont, abs=1e-6)
+    # Adam's t advances even when no gradient exists; SGD has no state
+    opt2.ZeroGrad()
+    opt2.Step()
+    assert int(opt2.StateDict()["adam.t"]) == 6 and SGD(m2.Parameters(), 0.1).StateDict() == {}
+    # pruning keeps the newest two
+    for s in (4, 5, 6):
+        SaveCheckpoint(root, s, m, opt, cfg, max_checkpoint_keep=2)
+    assert sorted(os.listdir(root)) == ["checkpoint_step_000005", "checkpoint_step_000006"]
+    # topology / shape validation
+    bad = TransformerConfig.GPT2(n_layer=3, n_embd=32, n_head=2, n_kv_head=2, vocab_size=64, original_vocab_size=64, block_size=16)
+    with pytest.raises((ValueError, KeyError)):
+        ResumeFromCheckpoint(os.path.join(root, "checkpoint_step_000006"), TransformerModel(bad), None, bad, False)
