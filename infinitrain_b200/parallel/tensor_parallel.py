@@ -438,3 +438,34 @@ class VocabParallelCrossEntropyLoss(Module):
     def Forward(self, logits, target):
         per_tok = VocabParallelCrossEntropy(self.vocab_size_original, self.label_smoothing).Apply(logits, target)
         return per_tok.reshape(-1).mean()
+
+
+def AllReduceSequenceParallelGrads(model: torch.nn.Module) -> int:
+    """Sums, over the tensor-parallel group, the gradients of parameters that are replicated across
+    TP ranks but see only a slice of the sequence under sequence parallelism (norm weights, position
+    table, row-parallel biases, replicated LoRA factors; they carry ``_itb_sp_replicated``).  Call it
+    after backward and before the optimizer step.  Returns the number of tensors reduced.
+
+    The reference does not do this (its replicated parameters drift apart across TP ranks when
+    sequence parallelism is on); without sequence parallelism every rank already holds the full
+    gradient and nothing is done.
+    """
+    grp = _tp()
+    if grp is None or not genv.GetSequenceParallelEnabled():
+        return 0
+    grads = []
+    for p in model.parameters():
+        if getattr(p, "_itb_sp_replicated", False):
+            g = p.grad if p.grad is not None else getattr(p, "main_grad", None)
+            if g is not None:
+                grads.append(g)
+    if not grads:
+        return 0
+    flat = torch.cat([g.reshape(-1).float() for g in grads])
+    grp.AllReduce(flat, ReduceOpType.kSum)
+    off = 0
+    for g in grads:
+        n = g.numel()
+        g.copy_(flat[off:off + n].view_as(g))
+        off += n
+    return len(grads)
