@@ -1,0 +1,91 @@
+"""Precision checker, profiler, hooks, dtype / Scalar rules, log line format (CPU)."""
+import os
+import re
+
+import pytest
+import torch
+
+from infinitrain_b200 import nn
+from infinitrain_b200.datatype import DataType, PromoteDataTypes, Scalar, parse_dtype
+from infinitrain_b200.utils.logging import format_step_line
+from infinitrain_b200.utils.precision_checker import (ComputeMD5, PrecisionCheckConfig, PrecisionCheckEnv,
+                                                      PrecisionChecker, PrecisionCheckLevel)
+from infinitrain_b200.utils.profiler import Profiler
+
+
+def test_dtype_promotion_and_scalar():
+    D = DataType
+    assert PromoteDataTypes(D.kFLOAT16, D.kBFLOAT16) == D.kFLOAT32
+    assert PromoteDataTypes(D.kINT64, D.kBFLOAT16) == D.kBFLOAT16
+    assert PromoteDataTypes(D.kINT32, D.kINT64) == D.kINT64
+    assert PromoteDataTypes(D.kUINT32, D.kINT32) == D.kUINT32          # same size: first operand wins
+    assert PromoteDataTypes(D.kFLOAT32, D.kFLOAT64) == D.kFLOAT64
+    assert parse_dtype("bfloat16") == D.kBFLOAT16 and parse_dtype("float32") == D.kFLOAT32
+    assert Scalar(True).kind == Scalar.Kind.kBool and Scalar(3).kind == Scalar.Kind.kInt64
+    assert Scalar(3, unsigned=True).kind == Scalar.Kind.kUInt64 and Scalar(2.5).kind == Scalar.Kind.kDouble
+    # half types round through fp32 (two-step rounding)
+    v = 1.00390625 + 2 ** -20
+    assert Scalar(v).to(D.kBFLOAT16) == torch.tensor(v, dtype=torch.float32).bfloat16().item()
+    assert Scalar(7.9).to(D.kINT32) == 7 and Scalar(0.0).to(D.kBOOL) is False
+
+
+def test_module_hooks_and_handles():
+    l = nn.Linear(4, 4)
+    calls = []
+    h1 = l.RegisterForwardPreHook(lambda m, i: calls.append("pre"))
+    h2 = l.RegisterForwardPostHook(lambda m, i, o: calls.append("post"))
+    h3 = l.RegisterBackwardPostHook(lambda m, gi, go: calls.append("bwd"))
+    l(torch.randn(2, 4, requires_grad=True)).sum().backward()
+    assert calls == ["pre", "post", "bwd"]
+    h1.Remove(); h2.Remove(); h3.Remove()
+    calls.clear()
+    l(torch.randn(2, 4)).sum().backward()
+    assert calls == []
+
+
+def test_precision_checker_simple_md5_npy(tmp_path):
+    cfg = PrecisionCheckConfig.Parse(f"level=2,format=md5,path={tmp_path},save_tensors=true,md5_tolerance=1e-3")
+    assert cfg.level == PrecisionCheckLevel.FUNCTION and cfg.format == "md5" and cfg.save_tensors
+    env = PrecisionCheckEnv.Instance()
+    env.Init(cfg, rank=0)
+    try:
+        m = nn.Sequential(nn.Linear(4, 4), nn.NewGELU())
+        PrecisionChecker.BuildNameMap(m)
+        for _ in range(2):
+            PrecisionChecker.ResetCounters()
+            m(torch.ones(2, 4, requires_grad=True)).sum().backward()
+        log = open(os.path.join(env.GetOutputPath(), "precision_check_rank_0.log")).read()
+        assert "[Forward Output] 0 #0 (0)" in log and "[Function Output] linear" in log and "Backward GradOutput" in log
+        assert re.search(r": [0-9a-f]{32}\n", log)
+        assert any(f.endswith(".npy") for f in os.listdir(os.path.join(env.GetOutputPath(), "rank_0")))
+    finally:
+        env.Shutdown()
+    a = torch.tensor([1.0, 2.0])
+    assert ComputeMD5(a, 1e-2) == ComputeMD5(a + 1e-4, 1e-2) and ComputeMD5(a) != ComputeMD5(a + 1e-4)
+
+
+def test_profiler_report_and_trace(tmp_path):
+    p = Profiler.Instance()
+    p.Reset()
+    p.Enable()
+    try:
+        p.SetTag("Step_0")
+        nn.Linear(8, 8)(torch.randn(2, 8))
+        with p.RecordRange("AllReduce"):
+            pass
+    finally:
+        p.Disable()
+    rep = p.Report(os.path.join(tmp_path, "rep.txt"), "Count")
+    assert "Tag: Step_0" in rep and "linear" in rep and "AllReduce" in rep
+    p.ExportChromeTrace(os.path.join(tmp_path, "trace.json"))
+    import json
+
+    assert len(json.load(open(os.path.join(tmp_path, "trace.json")))["traceEvents"]) == 2
+
+
+def test_step_line_matches_reference_parsers():
+    line = format_step_line(3, 10, 4.123456, 1e-4, 31.25, 524288.0, 12000, 14000, 8, 1, 1, 1)
+    # regular expressions of the reference's scripts/compare_loss.py and compare_tps.py
+    m1 = re.search(r"step\s+(\d+)/\d+\s+\|\s+train loss\s+([\d.]+)", line)
+    m2 = re.search(r"step\s+(\d+)/\d+\s+\|.*?\|\s+(\d+)\s+tok/s", line)
+    assert m1 and float(m1.group(2)) == 4.123456 and m2 and int(m2.group(2)) == 524288
