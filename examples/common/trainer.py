@@ -1,0 +1,278 @@
+"""Shared training driver of the GPT-2 and LLaMA-3 examples.
+
+Flags, defaults and control flow follow the reference trainers (example/gpt2/main.cc:47-100,
+128-530; example/llama3/main.cc): process groups from the 3-axis layout, model from an llm.c file
+or random init, LoRA, pipeline / DDP / ZeRO wrapping, gradient accumulation, per-step loss
+all-reduce, the step log line, optional sampling and checkpointing.  Differences: one process per
+GPU (``--nthread_per_process`` is accepted and ignored), AdamW / SGD selectable for both families,
+synthetic token data when no ``--input_bin`` is given.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+
+def build_parser(family: str) -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(description=f"{family} training (infinitrain_b200)")
+    a = p.add_argument
+    a("--input_bin", default="")
+    a("--input_val_bin", default="")
+    a("--tokenizer_bin", default="")
+    a("--llmc_filepath", default="")
+    a("--model", default="gpt2" if family == "gpt2" else "llama3-1b")
+    a("--batch_size", type=int, default=4)
+    a("--sequence_length", type=int, default=64)
+    a("--total_batch_size", type=int, default=256)
+    a("--num_iteration", type=int, default=10)
+    a("--freq_generate_txt", type=int, default=0)
+    a("--text_length", type=int, default=64)
+    a("--learning_rate", type=float, default=1e-4)
+    a("--weight_decay", type=float, default=0.0)
+    a("--optimizer", default="sgd" if family == "gpt2" else "adam", choices=["sgd", "adam", "adamw"])
+    a("--zero_stage", type=int, default=0)
+    a("--val_loss_every", type=int, default=0)
+    a("--sample_every", type=int, default=0)
+    a("--overfit_single_batch", action="store_true")
+    a("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    a("--nthread_per_process", type=int, default=1)
+    a("--tensor_parallel", type=int, default=1)
+    a("--sequence_parallel", action="store_true")
+    a("--pipeline_parallel", type=int, default=1)
+    a("--virtual_pipeline_parallel", type=int, default=1)
+    a("--pipeline_schedule", default="1f1b", choices=["1f1b", "gpipe"])
+    a("--dtype", default="float32")
+    a("--save_interval", type=int, default=0)
+    a("--load", default="")
+    a("--save", default="")
+    a("--max_checkpoint_keep", type=int, default=0)
+    a("--save_optimizer_state", action="store_true")
+    a("--precision_check", default="")
+    a("--lora_rank", type=int, default=0)
+    a("--lora_alpha", type=float, default=16.0)
+    a("--lora_target_modules", default="c_attn,c_proj")
+    a("--lora_save_path", default="")
+    a("--lora_load_path", default="")
+    a("--fused_nvlink", type=int, default=1)
+    a("--profile", action="store_true")
+    a("--seed", type=int, default=42)
+    a("--n_layer", type=int, default=0, help="override the layer count (smoke tests)")
+    a("--n_embd", type=int, default=0, help="override the hidden size (smoke tests)")
+    a("--n_head", type=int, default=0)
+    a("--n_kv_head", type=int, default=0)
+    a("--vocab_size", type=int, default=0)
+    return p
+
+
+def main(family: str, argv=None) -> int:
+    args = build_parser(family).parse_args(argv)
+    from infinitrain_b200.autocast import AutocastGuard
+    from infinitrain_b200.checkpoint import ResumeFromCheckpoint, SaveCheckpoint
+    from infinitrain_b200.data import DistributedDataLoader, TinyShakespeareDataset, Tokenizer, write_token_file
+    from infinitrain_b200.datatype import DataType, parse_dtype, to_torch_dtype
+    from infinitrain_b200.device import Device, DeviceGuardImpl
+    from infinitrain_b200.models import gpt2_config, llama3_config, llmc
+    from infinitrain_b200.nn import CrossEntropyLoss, lora
+    from infinitrain_b200.nn.transformer import TransformerModel
+    from infinitrain_b200.optim import SGD, Adam
+    from infinitrain_b200.parallel import global_env as genv
+    from infinitrain_b200.parallel.ddp.config import DistributedDataParallelConfig
+    from infinitrain_b200.parallel.ddp.distributed_data_parallel import DistributedDataParallel
+    from infinitrain_b200.parallel.ddp.distributed_optimizer import DistributedOptimizer
+    from infinitrain_b200.parallel.pp.pipeline_parallel import PipelineParallel
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory, ReduceOpType
+    from infinitrain_b200.parallel.tensor_parallel import AllReduceSequenceParallelGrads, VocabParallelCrossEntropyLoss
+    from infinitrain_b200.utils.logging import LOG, format_step_line
+    from infinitrain_b200.utils.precision_checker import (PrecisionCheckConfig, PrecisionCheckEnv, PrecisionChecker,
+                                                          PrecisionCheckLevel)
+    from infinitrain_b200.utils.profiler import Profiler
+
+    genv.InitAllEnv(args.nthread_per_process, args.tensor_parallel, args.sequence_parallel, args.pipeline_parallel,
+                    args.virtual_pipeline_parallel)
+    rank, world = genv.MyRank(), genv.GetWorldSize()
+    use_cuda = args.device == "cuda" and torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(genv.GetLocalProcRank())
+    dev = torch.device("cuda", genv.GetLocalProcRank()) if use_cuda else torch.device("cpu")
+    device = Device.from_torch(dev)
+    ProcessGroupFactory.Instance().Init(device=dev)
+    pc = PrecisionCheckConfig.Parse(args.precision_check)
+    PrecisionCheckEnv.Instance().Init(pc, rank)
+    if rank == 0:
+        LOG("INFO", genv.ProcessGroupOverview())
+    dp, tp, pp = genv.GetDataParallelSize(), genv.GetTensorParallelSize(), genv.GetPipelineParallelSize()
+    sp = genv.GetSequenceParallelSize()
+    dp_rank, pp_rank = genv.GetDataParallelRank(), genv.GetPipelineParallelRank()
+    B, T = args.batch_size, args.sequence_length
+    tokens_per_fwdbwd = B * T * dp
+    if args.total_batch_size % tokens_per_fwdbwd:
+        raise SystemExit(f"total_batch_size must be a multiple of batch*seq*dp = {tokens_per_fwdbwd}")
+    grad_accum = args.total_batch_size // tokens_per_fwdbwd
+    dtype = parse_dtype(args.dtype)
+    torch.manual_seed(args.seed)
+
+    # ---- model
+    if args.llmc_filepath:
+        model = (llmc.GPT2FromLLMC if family == "gpt2" else llmc.LLaMA3FromLLMC)(args.llmc_filepath)
+    else:
+        over = {k: getattr(args, k) for k in ("n_layer", "n_embd", "n_head", "n_kv_head") if getattr(args, k)}
+        if args.vocab_size:
+            over.update(vocab_size=args.vocab_size, original_vocab_size=args.vocab_size)
+        cfg = gpt2_config(args.model, **over) if family == "gpt2" else llama3_config(args.model, **over)
+        model = TransformerModel(cfg)
+    cfg = model.config
+    model.to(dev)
+    PrecisionChecker.BuildNameMap(model)
+    if args.lora_rank > 0:
+        lcfg = lora.LoRAConfig(rank=args.lora_rank, alpha=args.lora_alpha,
+                               target_modules=lora.ParseLoRATargetModules(args.lora_target_modules))
+        model = lora.GetLoRAModel(model, lcfg)
+        if args.lora_load_path:
+            lora.LoadLoRAWeights(model, args.lora_load_path)
+        if rank == 0:
+            lora.PrintLoRASummary(model, lambda s: LOG("INFO", s))
+    trainable = [p for p in model.parameters() if p.requires_grad]
+
+    # ---- parallel wrapping
+    ddp_cfg = DistributedDataParallelConfig(zero_stage=args.zero_stage, use_fused_nvlink_kernels=bool(args.fused_nvlink))
+    pipeline = None
+    ddp_chunks = []
+    if pp > 1:
+        pipeline = PipelineParallel(model, pp, grad_accum, [B, T // sp, cfg.n_embd], pp_rank, dev,
+                                    args.virtual_pipeline_parallel, schedule=args.pipeline_schedule)
+        if dp > 1:
+            chunks = pipeline.mutable_chunks()
+            for i in range(len(chunks)):
+                chunks[i] = DistributedDataParallel(chunks[i], config=ddp_cfg)
+                ddp_chunks.append(chunks[i])
+    elif dp > 1:
+        model = DistributedDataParallel(model, config=ddp_cfg)
+        ddp_chunks.append(model)
+
+    # ---- optimizer
+    if args.optimizer == "sgd":
+        creator = SGD.Create(args.learning_rate)
+    else:
+        creator = Adam.Create(args.learning_rate, weight_decay=args.weight_decay if args.optimizer == "adamw" else 0.0)
+    if args.zero_stage >= 1 and ddp_chunks:
+        optimizer = DistributedOptimizer(creator, trainable, ddp_chunks)
+    else:
+        optimizer = creator(trainable)
+    loss_fn = VocabParallelCrossEntropyLoss(cfg.original_vocab_size) if tp > 1 else CrossEntropyLoss()
+
+    # ---- data
+    if args.input_bin:
+        data_path = args.input_bin
+    else:
+        data_path = f"/tmp/itb_synth_{family}_{os.getpid()}_{rank}.bin"
+        g = torch.Generator().manual_seed(1234)
+        n_tok = max(B * T * (grad_accum * dp * (args.num_iteration + 2) + 4), 4 * T)
+        write_token_file(data_path, torch.randint(0, cfg.original_vocab_size, (n_tok,), generator=g).numpy(),
+                         llama3=(family != "gpt2"))
+    loader_batch = B * grad_accum if pp > 1 else B
+    train_ds = TinyShakespeareDataset(data_path, T)
+    loader = DistributedDataLoader(train_ds, loader_batch, dp_rank, dp)
+    tokenizer = Tokenizer(args.tokenizer_bin) if args.tokenizer_bin else None
+
+    # ---- resume
+    start_step = 0
+    it = iter(loader)
+    if args.load:
+        res = ResumeFromCheckpoint(args.load, model, optimizer, cfg, load_optimizer_state=args.save_optimizer_state)
+        start_step = res.global_step
+        for _ in range(res.consumed_batches):
+            next(it)
+    consumed = start_step * (1 if pp > 1 else grad_accum)
+    profiler = Profiler.Instance()
+    if args.profile:
+        profiler.Enable()
+    impl = DeviceGuardImpl
+    cached = None
+    last_rank = world - 1
+
+    for step in range(start_step, args.num_iteration):
+        PrecisionChecker.ResetCounters()
+        impl.ResetMemPoolHighWatermarks(device)
+        profiler.SetTag(f"Step_{step}")
+        t0 = time.perf_counter()
+        if use_cuda:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        lossf = 0.0
+        if pipeline is not None:
+            if cached is None or not args.overfit_single_batch:
+                x, y = next(it)
+                cached = (x, y)
+                consumed += 1
+            x, y = cached
+            lossf = pipeline.TrainStep([x.to(dev, non_blocking=True)], [y.to(dev, non_blocking=True)], optimizer,
+                                       loss_fn, dtype)
+        else:
+            optimizer.ZeroGrad()
+            loss_acc = torch.zeros((), device=dev)
+            for micro in range(grad_accum):
+                if cached is None or not args.overfit_single_batch:
+                    x, y = next(it)
+                    cached = (x, y)
+                    consumed += 1
+                x, y = cached
+                x, y = x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)
+                last = micro == grad_accum - 1
+                ctxs = [c.no_sync() for c in ddp_chunks] if (not last and ddp_chunks) else []
+                for c in ctxs:
+                    c.__enter__()
+                with AutocastGuard(dtype=dtype, enabled=to_torch_dtype(dtype) != torch.float32):
+                    loss = loss_fn(model(x), y) / grad_accum
+                loss_acc += loss.detach().float()
+                loss.backward()
+                for c in ctxs:
+                    c.__exit__(None, None, None)
+            AllReduceSequenceParallelGrads(model)
+            for c in ddp_chunks:
+                c.FinishGradSync()
+            optimizer.Step()
+            lossf = float(loss_acc.item())
+        if dp > 1:
+            lt = torch.tensor([lossf], device=dev)
+            ProcessGroupFactory.Instance().dp_group().AllReduce(lt, ReduceOpType.kAvg)
+            lossf = float(lt.item())
+        if use_cuda:
+            ev1.record()
+            torch.cuda.synchronize()
+        dur_ms = (time.perf_counter() - t0) * 1e3
+        tps = args.total_batch_size / (dur_ms / 1e3)
+        if rank == last_rank:
+            used, reserved = impl.GetMemPoolPeakMB(device)
+            LOG("ERROR", format_step_line(step + 1, args.num_iteration, lossf, args.learning_rate, dur_ms, tps, used,
+                                          reserved, dp, tp, sp, pp))
+            if use_cuda:
+                LOG("INFO", f"step {step + 1} device-timed {ev0.elapsed_time(ev1):.2f} ms")
+        if tokenizer is not None and args.freq_generate_txt and (step + 1) % args.freq_generate_txt == 0 and pp == 1:
+            tokenizer.GenerateText(model, B, T, args.text_length, dev)
+        if args.save and args.save_interval and (step + 1) % args.save_interval == 0:
+            SaveCheckpoint(args.save, step + 1, model, optimizer, cfg, consumed, args.learning_rate,
+                           args.save_optimizer_state, args.max_checkpoint_keep)
+    if args.lora_rank > 0 and args.lora_save_path and rank == 0:
+        lora.SaveLoRAWeights(model, args.lora_save_path)
+    if args.profile:
+        profiler.Report(f"{family}.report.rank{rank}")
+        profiler.PrintRecords(f"{family}.records.log.rank{rank}")
+        profiler.Disable()
+    if not args.input_bin:
+        try:
+            os.remove(data_path)
+        except OSError:
+            pass
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0

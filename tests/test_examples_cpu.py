@@ -1,0 +1,62 @@
+"""Example trainers end to end on CPU (tiny configs), the C++ launcher, and hybrid parallel runs."""
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(cmd, env=None, timeout=600):
+    e = dict(os.environ)
+    e.update(env or {})
+    e["OMP_NUM_THREADS"] = "1"
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    return r.stdout + r.stderr
+
+
+def _losses(out):
+    return [float(m.group(2)) for m in re.finditer(r"step\s+(\d+)/\d+\s+\|\s+train loss\s+([\d.]+)", out)]
+
+
+def test_mnist_trains():
+    out = _run([sys.executable, "examples/mnist/main.py", "--num_epoch", "1"])
+    assert "final loss" in out
+
+
+def test_gpt2_single_process_cpu(tmp_path):
+    out = _run([sys.executable, "examples/gpt2/main.py", "--device", "cpu", "--n_layer", "2", "--n_embd", "64", "--n_head", "4", "--vocab_size", "512",
+                "--batch_size", "2",
+                "--sequence_length", "32", "--total_batch_size", "128", "--num_iteration", "3", "--optimizer", "adam",
+                "--learning_rate", "1e-3", "--overfit_single_batch", "--save", str(tmp_path), "--save_interval", "3"])
+    l = _losses(out)
+    assert len(l) == 3 and l[-1] < l[0]
+    assert os.path.exists(os.path.join(tmp_path, "checkpoint_step_000003", "model.ckpt"))
+
+
+def _launcher():
+    from infinitrain_b200 import _ext
+
+    p = _ext.launcher_path()
+    if not p.exists():
+        _ext.build_launcher()
+    return str(p)
+
+
+@pytest.mark.parametrize("flags", [
+    ["--tensor_parallel", "2", "--sequence_parallel"],
+    ["--pipeline_parallel", "2", "--virtual_pipeline_parallel", "2"],
+    ["--zero_stage", "1"],
+])
+def test_llama3_two_ranks_via_launcher(flags):
+    port = 29600 + abs(hash(tuple(flags))) % 300
+    out = _run([_launcher(), "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable,
+                "examples/llama3/main.py", "--device", "cpu", "--n_layer", "4", "--n_embd", "64", "--n_head", "4",
+                "--n_kv_head", "2", "--vocab_size", "512", "--batch_size", "2",
+                "--sequence_length", "32", "--total_batch_size", "256", "--num_iteration", "2", "--model", "llama3-1b",
+                "--overfit_single_batch", "--learning_rate", "1e-3", *flags], timeout=900)
+    l = _losses(out)
+    assert len(l) == 2 and l[1] < l[0] + 1e-3, out[-1500:]
