@@ -99,6 +99,7 @@ def main():
     ap.add_argument("--zero", type=int, default=2)
     ap.add_argument("--model", default="gpt2")
     ap.add_argument("--residual", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--graph", type=int, default=1, help="capture the whole training step in a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -172,6 +173,16 @@ def main():
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    eager_step = train_step
+    if args.graph:
+        from infinitrain_b200.utils.cuda_graph import GraphedTrainStep
+
+        # Capture one complete step (zero-grad, forward, backward with the bucket kernels, optimizer)
+        # and replay it: the host only copies the next tokens into the static input buffers.
+        graphed = GraphedTrainStep(eager_step, (dev_x[0], dev_y[0]), warmup=3)
+        if hasattr(opt, "base_optimizer"):
+            opt.base_optimizer.t -= 0
+        train_step = graphed
     for i in range(args.warmup):
         train_step(dev_x[i % n_host], dev_y[i % n_host])
     barrier()
@@ -226,7 +237,7 @@ def main():
             "config": {"model": "GPT-2 124M (12L, 12H, 768, vocab 50257, ctx 1024, tied embeddings)",
                        "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": T,
                        "parallelism": parallelism, "optimizer": "AdamW lr 1e-4 wd 0.1",
-                       "residual_stream": args.residual,
+                       "residual_stream": args.residual, "cuda_graph": bool(args.graph),
                        "l2": "working set per step (activations + 124M fp32 weights, grads, moments) far exceeds "
                              "the 126 MB L2, so no explicit flush is needed"},
             "clocks": clocks,

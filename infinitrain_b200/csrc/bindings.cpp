@@ -291,8 +291,12 @@ void ce_bwd(at::Tensor& logits, const at::Tensor& target, const at::Tensor& lse,
 // ------------------------------------------------------------------ optimizer
 void adamw(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v,
            const c10::optional<at::Tensor>& shadow, double lr, double b1, double b2, double eps,
-           double wd, double bc1, double bc2, double grad_scale) {
+           double wd, double bc1, double bc2, double grad_scale,
+           const c10::optional<at::Tensor>& dev_hyper) {
   c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(!dev_hyper.has_value() || (dev_hyper->scalar_type() == at::kFloat && dev_hyper->numel() >= 3 &&
+                                         dev_hyper->is_cuda()),
+              "adamw: dev_hyper must be a CUDA fp32 tensor [lr, 1/bc1, 1/bc2]");
   TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(),
               "adamw: contiguous flat buffers required");
   TORCH_CHECK(p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat &&
@@ -302,8 +306,14 @@ void adamw(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v,
               "adamw: size mismatch");
   check_rc(itb_adamw(p.data_ptr<float>(), g.data_ptr(), dt(g), m.data_ptr<float>(),
                      v.data_ptr<float>(), const_cast<void*>(optr(shadow)), p.numel(), lr, b1, b2,
-                     eps, wd, bc1, bc2, grad_scale, cur_stream()),
+                     eps, wd, bc1, bc2, grad_scale, static_cast<const float*>(optr(dev_hyper)),
+                     cur_stream()),
            "adamw");
+}
+void adam_advance(at::Tensor& hyper, double b1, double b2) {
+  c10::cuda::CUDAGuard guard(hyper.device());
+  TORCH_CHECK(hyper.is_cuda() && hyper.scalar_type() == at::kFloat && hyper.numel() >= 4, "adam_advance: fp32[4]");
+  check_rc(itb_adam_advance(hyper.data_ptr<float>(), b1, b2, cur_stream()), "adam_advance");
 }
 void sgd(at::Tensor& p, const at::Tensor& g, const c10::optional<at::Tensor>& shadow, double lr,
          double grad_scale) {
@@ -435,7 +445,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_bwd", &embedding_bwd);
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
-  m.def("adamw", &adamw);
+  m.def("adamw", &adamw, pybind11::arg("p"), pybind11::arg("g"), pybind11::arg("m"), pybind11::arg("v"),
+        pybind11::arg("shadow"), pybind11::arg("lr"), pybind11::arg("b1"), pybind11::arg("b2"),
+        pybind11::arg("eps"), pybind11::arg("wd"), pybind11::arg("bc1"), pybind11::arg("bc2"),
+        pybind11::arg("grad_scale"), pybind11::arg("dev_hyper") = pybind11::none());
+  m.def("adam_advance", &adam_advance);
   m.def("sgd", &sgd);
   m.def("cast_into", &cast_into);
   m.def("colsum", &colsum);

@@ -25,10 +25,12 @@ int itb_comm_blocks(long long n_elements_per_rank);
 // In-place all-reduce of fp32 elements [off, off+n) followed by a multiplication with `scale`
 // (1/world for an average).  `flags` are the symmetric flag words ([channels][kItbMaxRanks] int32
 // per rank); channels ch0 .. ch0 + itb_comm_blocks(...) - 1 are used; `epoch` must grow by 2 between
-// launches that use the same channels.  mc == NULL selects the peer-pointer path.
+// launches that use the same channels.  mc == NULL selects the peer-pointer path.  epoch_ctr
+// (optional, device memory of THIS GPU, one int per channel) replaces `epoch` by a counter the
+// kernel reads and advances itself, so that the launch can be replayed from a CUDA graph.
 int itb_nvl_allreduce_scale(const ItbPeerPtrs* bufs, void* mc, const ItbPeerPtrs* flags,
                             long long off, long long n, int rank, int world, int ch0, int epoch,
-                            float scale, int* err, cudaStream_t stream);
+                            float scale, int* err, int* epoch_ctr, cudaStream_t stream);
 
 // Bucket [off, off+n) of the flat gradient / parameter / bf16-shadow buffers: reduce every rank's
 // gradients for this rank's 1/world shard, scale, AdamW on the shard (m, v: shard-local fp32 state),
@@ -37,7 +39,7 @@ int itb_nvl_rs_adamw_bcast(const ItbPeerPtrs* grads, const void* mc_grads, const
                            void* mc_params, const ItbPeerPtrs* shadows, void* mc_shadows, float* m,
                            float* v, const ItbPeerPtrs* flags, long long off, long long n, int rank,
                            int world, int ch0, int epoch, const ItbAdamHyper* hyper, int* err,
-                           cudaStream_t stream);
+                           int* epoch_ctr, const float* dev_hyper, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

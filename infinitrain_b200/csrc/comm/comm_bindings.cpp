@@ -21,10 +21,11 @@ void check(int rc, const char* what) {
 
 void nvl_allreduce_scale(const std::vector<int64_t>& bufs, int64_t mc, const std::vector<int64_t>& flags,
                          int64_t off, int64_t n, int64_t rank, int64_t world, int64_t ch0, int64_t epoch,
-                         double scale, at::Tensor& err) {
+                         double scale, at::Tensor& err, const c10::optional<at::Tensor>& epoch_ctr) {
   ItbPeerPtrs b = to_ptrs(bufs), f = to_ptrs(flags);
   check(itb_nvl_allreduce_scale(&b, reinterpret_cast<void*>(mc), &f, off, n, rank, world, ch0, epoch,
                                 static_cast<float>(scale), err.data_ptr<int>(),
+                                epoch_ctr.has_value() ? epoch_ctr->data_ptr<int>() : nullptr,
                                 at::cuda::getCurrentCUDAStream().stream()),
         "allreduce_scale");
 }
@@ -35,7 +36,8 @@ void nvl_rs_adamw_bcast(const std::vector<int64_t>& grads, int64_t mc_grads,
                         at::Tensor& v, const std::vector<int64_t>& flags, int64_t off, int64_t n,
                         int64_t rank, int64_t world, int64_t ch0, int64_t epoch, double lr, double b1,
                         double b2, double eps, double wd, double bc1, double bc2, double grad_scale,
-                        at::Tensor& err) {
+                        at::Tensor& err, const c10::optional<at::Tensor>& epoch_ctr,
+                        const c10::optional<at::Tensor>& dev_hyper) {
   ItbPeerPtrs g = to_ptrs(grads), p = to_ptrs(params), s = to_ptrs(shadows), f = to_ptrs(flags);
   TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && m.is_contiguous() &&
                   v.is_contiguous() && m.numel() * world == n && v.numel() * world == n,
@@ -47,7 +49,10 @@ void nvl_rs_adamw_bcast(const std::vector<int64_t>& grads, int64_t mc_grads,
                                reinterpret_cast<void*>(mc_params), &s,
                                reinterpret_cast<void*>(mc_shadows), m.data_ptr<float>(),
                                v.data_ptr<float>(), &f, off, n, rank, world, ch0, epoch, &h,
-                               err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream()),
+                               err.data_ptr<int>(),
+                               epoch_ctr.has_value() ? epoch_ctr->data_ptr<int>() : nullptr,
+                               dev_hyper.has_value() ? dev_hyper->data_ptr<float>() : nullptr,
+                               at::cuda::getCurrentCUDAStream().stream()),
         "rs_adamw_bcast");
 }
 

@@ -116,8 +116,13 @@ __device__ __forceinline__ void bcast4(const ItbPeerPtrs& bufs, float* mc, long 
 template <bool kMC>
 __global__ void __launch_bounds__(kCommThreads)
 allreduce_scale_kernel(ItbPeerPtrs bufs, float* mc, ItbPeerPtrs flags, long long off, long long n,
-                       int rank, int world, int ch0, int epoch, float scale, int* err) {
+                       int rank, int world, int ch0, int epoch, float scale, int* err,
+                       int* __restrict__ epoch_ctr) {
   const int ch = ch0 + blockIdx.x;
+  // Device-side epoch (one counter per channel, private to this GPU): lets a captured CUDA graph
+  // replay the launch; every rank's counter advances in lockstep because every rank replays the
+  // same launches.
+  if (epoch_ctr) epoch = epoch_ctr[ch] + 1;
   if (!rank_barrier(flags, rank, world, ch, epoch, err, 201)) return;
   // slice of this rank, in units of 4 elements
   const long long nv = n / 4;
@@ -132,6 +137,7 @@ allreduce_scale_kernel(ItbPeerPtrs bufs, float* mc, ItbPeerPtrs flags, long long
     bcast4<kMC>(bufs, mc, i, world, s);
   }
   rank_barrier(flags, rank, world, ch, epoch + 1, err, 202);
+  if (epoch_ctr && threadIdx.x == 0) epoch_ctr[ch] = epoch + 1;
 }
 
 // ------------------------------------------------------------------ reduce-scatter + AdamW + broadcast
@@ -142,8 +148,15 @@ __global__ void __launch_bounds__(kCommThreads)
 rs_adamw_bcast_kernel(ItbPeerPtrs grads, const float* mc_grads, ItbPeerPtrs params, float* mc_params,
                       ItbPeerPtrs shadows, __nv_bfloat16* mc_shadows, float* __restrict__ m,
                       float* __restrict__ v, ItbPeerPtrs flags, long long off, long long n, int rank,
-                      int world, int ch0, int epoch, ItbAdamHyper h, int* err) {
+                      int world, int ch0, int epoch, ItbAdamHyper h, int* err,
+                      int* __restrict__ epoch_ctr, const float* __restrict__ dev_hyper) {
   const int ch = ch0 + blockIdx.x;
+  if (epoch_ctr) epoch = epoch_ctr[ch] + 1;
+  if (dev_hyper) {   // [lr, 1/bc1, 1/bc2] refreshed by the host before every graph replay
+    h.lr = dev_hyper[0];
+    h.inv_bc1 = dev_hyper[1];
+    h.inv_bc2 = dev_hyper[2];
+  }
   if (!rank_barrier(flags, rank, world, ch, epoch, err, 203)) return;
   const long long shard = n / world;           // multiple of 8 by construction of the buckets
   const long long s0 = off + shard * rank;
@@ -190,6 +203,7 @@ rs_adamw_bcast_kernel(ItbPeerPtrs grads, const float* mc_grads, ItbPeerPtrs para
     }
   }
   rank_barrier(flags, rank, world, ch, epoch + 1, err, 204);
+  if (epoch_ctr && threadIdx.x == 0) epoch_ctr[ch] = epoch + 1;
 }
 
 }  // namespace itb
@@ -205,17 +219,18 @@ extern "C" int itb_comm_blocks(long long n_elements_per_rank) {
 
 extern "C" int itb_nvl_allreduce_scale(const ItbPeerPtrs* bufs, void* mc, const ItbPeerPtrs* flags,
                                        long long off, long long n, int rank, int world, int ch0,
-                                       int epoch, float scale, int* err, cudaStream_t s) {
+                                       int epoch, float scale, int* err, int* epoch_ctr,
+                                       cudaStream_t s) {
   if (n <= 0) return 0;
   if ((off | n) & 3) return -3;
   if (world < 1 || world > kItbMaxRanks) return -4;
   const int blocks = itb_comm_blocks((n + world - 1) / world);
   if (mc)
     allreduce_scale_kernel<true><<<blocks, kCommThreads, 0, s>>>(
-        *bufs, static_cast<float*>(mc), *flags, off, n, rank, world, ch0, epoch, scale, err);
+        *bufs, static_cast<float*>(mc), *flags, off, n, rank, world, ch0, epoch, scale, err, epoch_ctr);
   else
-    allreduce_scale_kernel<false><<<blocks, kCommThreads, 0, s>>>(*bufs, nullptr, *flags, off, n,
-                                                                  rank, world, ch0, epoch, scale, err);
+    allreduce_scale_kernel<false><<<blocks, kCommThreads, 0, s>>>(
+        *bufs, nullptr, *flags, off, n, rank, world, ch0, epoch, scale, err, epoch_ctr);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -224,7 +239,7 @@ extern "C" int itb_nvl_rs_adamw_bcast(const ItbPeerPtrs* grads, const void* mc_g
                                       const ItbPeerPtrs* shadows, void* mc_shadows, float* m, float* v,
                                       const ItbPeerPtrs* flags, long long off, long long n, int rank,
                                       int world, int ch0, int epoch, const ItbAdamHyper* h, int* err,
-                                      cudaStream_t s) {
+                                      int* epoch_ctr, const float* dev_hyper, cudaStream_t s) {
   if (n <= 0) return 0;
   if (world < 1 || world > kItbMaxRanks) return -4;
   if (n % (8LL * world) || (off & 7)) return -3;
@@ -234,10 +249,10 @@ extern "C" int itb_nvl_rs_adamw_bcast(const ItbPeerPtrs* grads, const void* mc_g
     rs_adamw_bcast_kernel<true><<<blocks, kCommThreads, 0, s>>>(
         *grads, static_cast<const float*>(mc_grads), *params, static_cast<float*>(mc_params),
         *shadows, static_cast<__nv_bfloat16*>(mc_shadows), m, v, *flags, off, n, rank, world, ch0,
-        epoch, *h, err);
+        epoch, *h, err, epoch_ctr, dev_hyper);
   else
     rs_adamw_bcast_kernel<false><<<blocks, kCommThreads, 0, s>>>(
         *grads, nullptr, *params, nullptr, *shadows, nullptr, m, v, *flags, off, n, rank, world, ch0,
-        epoch, *h, err);
+        epoch, *h, err, epoch_ctr, dev_hyper);
   return static_cast<int>(cudaGetLastError());
 }

@@ -110,12 +110,17 @@ int itb_ce_bwd(void* logits, int dtype, long long ld, const long long* target, c
 // ------------------------------------------------------------------ optimizer
 // One launch over a flat buffer: Adam / AdamW with fp32 master weights and optional bf16 shadow.
 //   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;  p -= lr * (m/bc1 / (sqrt(v/bc2) + eps) + wd * p)
-// grad_scale multiplies g first (1/dp, 1/accum).  g is fp32 or bf16.
+// grad_scale multiplies g first (1/dp, 1/accum).  g is fp32 or bf16.  dev_hyper (optional, device
+// memory, [lr, 1/bc1, 1/bc2]) overrides lr / bc1 / bc2 at run time: a captured CUDA graph keeps the
+// pointer and the host refreshes the three floats before every replay.
 int itb_adamw(float* p, const void* g, int g_dtype, float* m, float* v, void* shadow_bf16,
               long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-              float grad_scale, cudaStream_t stream);
+              float grad_scale, const float* dev_hyper, cudaStream_t stream);
 int itb_sgd(float* p, const void* g, int g_dtype, void* shadow_bf16, long long n, float lr,
             float grad_scale, cudaStream_t stream);
+// hyper = [lr, 1/bc1, 1/bc2, t] in device memory: t += 1 and the bias corrections are recomputed
+// on the device (graph-replayable step counter).
+int itb_adam_advance(float* hyper, float b1, float b2, cudaStream_t stream);
 
 // ------------------------------------------------------------------ utilities
 int itb_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long n,

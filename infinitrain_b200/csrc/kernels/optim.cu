@@ -43,7 +43,14 @@ template <typename TG>
 __global__ void adamw_kernel(float* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m,
                              float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, long long n,
                              float lr, float b1, float b2, float eps, float wd, float inv_bc1,
-                             float inv_bc2, float gscale) {
+                             float inv_bc2, float gscale, const float* __restrict__ dev_hyper) {
+  // Hyper-parameters that change from step to step may live in device memory ([lr, 1/bc1, 1/bc2])
+  // so that a captured CUDA graph can be replayed with new values.
+  if (dev_hyper) {
+    lr = dev_hyper[0];
+    inv_bc1 = dev_hyper[1];
+    inv_bc2 = dev_hyper[2];
+  }
   const long long nvec = n / 4;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -103,7 +110,8 @@ using namespace itb;
 
 extern "C" int itb_adamw(float* p, const void* g, int g_dtype, float* m, float* v,
                          void* shadow_bf16, long long n, float lr, float b1, float b2, float eps,
-                         float wd, float bc1, float bc2, float grad_scale, cudaStream_t s) {
+                         float wd, float bc1, float bc2, float grad_scale, const float* dev_hyper,
+                         cudaStream_t s) {
   if (n <= 0) return 0;
   // Vector path needs 16-byte aligned fp32 buffers (8-byte for bf16 gradients / shadow).
   if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) |
@@ -116,11 +124,11 @@ extern "C" int itb_adamw(float* p, const void* g, int g_dtype, float* m, float* 
   if (g_dtype == kItbBF16)
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
         p, static_cast<const __nv_bfloat16*>(g), m, v, static_cast<__nv_bfloat16*>(shadow_bf16), n,
-        lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2, grad_scale);
+        lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2, grad_scale, dev_hyper);
   else
     adamw_kernel<float><<<grid, 256, 0, s>>>(p, static_cast<const float*>(g), m, v,
                                              static_cast<__nv_bfloat16*>(shadow_bf16), n, lr, b1,
-                                             b2, eps, wd, 1.f / bc1, 1.f / bc2, grad_scale);
+                                             b2, eps, wd, 1.f / bc1, 1.f / bc2, grad_scale, dev_hyper);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -136,5 +144,22 @@ extern "C" int itb_sgd(float* p, const void* g, int g_dtype, void* shadow_bf16, 
     sgd_kernel<float><<<grid, 256, 0, s>>>(p, static_cast<const float*>(g),
                                            static_cast<__nv_bfloat16*>(shadow_bf16), n, lr,
                                            grad_scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Device-resident Adam step state: hyper = [lr, 1/bc1, 1/bc2, t].  One thread advances t and
+// recomputes the bias corrections, so that a whole training step (including this launch) can be
+// captured once in a CUDA graph and replayed: nothing step-dependent comes from the host.
+__global__ void adam_advance_kernel(float* __restrict__ hyper, float b1, float b2) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    const double t = static_cast<double>(hyper[3]) + 1.0;
+    hyper[3] = static_cast<float>(t);
+    hyper[1] = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(b1), t)));
+    hyper[2] = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(b2), t)));
+  }
+}
+
+extern "C" int itb_adam_advance(float* hyper, float b1, float b2, cudaStream_t s) {
+  adam_advance_kernel<<<1, 32, 0, s>>>(hyper, b1, b2);
   return static_cast<int>(cudaGetLastError());
 }

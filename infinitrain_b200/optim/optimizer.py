@@ -131,7 +131,38 @@ class Adam(Optimizer):
             self.m = [torch.zeros_like(p) for p in self.params]
             self.v = [torch.zeros_like(p) for p in self.params]
 
+    # ------------------------------------------------------------------ device-resident step state
+    def _dev_hyper(self):
+        """``[lr, 1/bc1, 1/bc2, t]`` on the device (fused paths only).  The step counter and the bias
+        corrections are advanced by a one-thread kernel, so a captured training step replays with
+        the right values and nothing step-dependent is passed from the host."""
+        if getattr(self, "_hyper", None) is None:
+            dev = self.params[0].device
+            self._hyper = torch.tensor([self.learning_rate, 1.0, 1.0, float(self.t)], dtype=torch.float32, device=dev)
+            self._hyper_lr = self.learning_rate
+            self._prepared = False
+        if self._hyper_lr != self.learning_rate:       # learning-rate change: one small synchronous copy
+            self._hyper[0:1].fill_(self.learning_rate)
+            self._hyper_lr = self.learning_rate
+        return self._hyper
+
+    def PrepareStep(self) -> None:
+        """Advances the device-side step counter for the step about to be taken.  Fused ZeRO launches
+        that run during backward need it before ``Step``; ``ZeroGrad`` of the distributed optimizer
+        calls it, ``Step`` calls it when nobody did."""
+        if self._flat is None and not self._per_tensor_fused:
+            return
+        h = self._dev_hyper()
+        if not self._prepared:
+            _ext.load().adam_advance(h, self.beta1, self.beta2)
+            ops._counters["launches"] += 1
+            self._prepared = True
+
     def Step(self) -> None:
+        fused = self._flat is not None or self._per_tensor_fused
+        if fused:
+            self.PrepareStep()
+            self._prepared = False
         self.t += 1
         bc1 = 1.0 - self.beta1 ** self.t
         bc2 = 1.0 - self.beta2 ** self.t
@@ -139,7 +170,7 @@ class Adam(Optimizer):
             C = _ext.load()
             C.adamw(self._flat.param_buffer, self._flat.grad_buffer, self._m_flat, self._v_flat,
                     self._flat.shadow_buffer, self.learning_rate, self.beta1, self.beta2, self.eps,
-                    self.weight_decay, bc1, bc2, 1.0)
+                    self.weight_decay, bc1, bc2, 1.0, self._hyper)
             ops._counters["launches"] += 1
             self._flat.mark_shadows_fresh()
             return
@@ -149,7 +180,7 @@ class Adam(Optimizer):
                 if p.grad is None:
                     continue
                 C.adamw(p.data, p.grad, m, v, getattr(p, "_itb_shadow", None), self.learning_rate, self.beta1,
-                        self.beta2, self.eps, self.weight_decay, bc1, bc2, 1.0)
+                        self.beta2, self.eps, self.weight_decay, bc1, bc2, 1.0, self._hyper)
                 ops._counters["launches"] += 1
             return
         with torch.no_grad():
@@ -187,6 +218,9 @@ class Adam(Optimizer):
         if "adam.t" not in state_dict:
             raise KeyError("Missing optimizer state: adam.t")
         self.t = int(state_dict["adam.t"].item())
+        if getattr(self, "_hyper", None) is not None:
+            self._hyper[3:4].fill_(float(self.t))
+            self._prepared = False
 
 
 AdamW = Adam

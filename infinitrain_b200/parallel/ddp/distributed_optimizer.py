@@ -78,9 +78,13 @@ class DistributedOptimizer(Optimizer):
     def _fused_hyper(self):
         b = self.base_optimizer
         t = b.t + 1   # the step these launches belong to (Step() increments t afterwards)
-        return (b.learning_rate, b.beta1, b.beta2, b.eps, b.weight_decay, 1.0 - b.beta1 ** t, 1.0 - b.beta2 ** t, 1.0)
+        return (b.learning_rate, b.beta1, b.beta2, b.eps, b.weight_decay, 1.0 - b.beta1 ** t, 1.0 - b.beta2 ** t, 1.0,
+                b._dev_hyper())
 
     def ZeroGrad(self, set_to_none: bool = True) -> None:
+        if self.fused:
+            # the bucket kernels that run during backward read the step state: advance it now
+            self.base_optimizer.PrepareStep()
         for buf in self.buffers:
             buf.zero_grads()
         for g in self.bucket_groups:
@@ -112,6 +116,7 @@ class DistributedOptimizer(Optimizer):
         if self.fused:
             # Every bucket was reduced, updated and broadcast by its fused kernel during backward.
             self.base_optimizer.t += 1
+            self.base_optimizer._prepared = False
             for buf in self.buffers:
                 buf.mark_shadows_fresh()
             return

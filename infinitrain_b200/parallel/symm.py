@@ -71,7 +71,9 @@ class NvlinkContext:
         self.err = torch.zeros(4, dtype=torch.int32, device=device)
         self.stream = torch.cuda.Stream(device=device, priority=-1)
         self._next_channel = 0
-        self._epochs: Dict[int, int] = {}
+        # Launch epochs live on the device (one counter per channel, advanced by the kernels), so a
+        # captured CUDA graph can replay the collectives.
+        self.epoch_ctr = torch.zeros(kFlagChannels, dtype=torch.int32, device=device)
         pg.Barrier()
 
     # ------------------------------------------------------------------ memory
@@ -107,14 +109,7 @@ class NvlinkContext:
         if ch + n > kFlagChannels:
             raise RuntimeError("out of NVLink flag channels")
         self._next_channel += n
-        self._epochs[ch] = 0
         return ch
-
-    def next_epoch(self, ch0: int) -> int:
-        """Every launch on a channel group consumes two epochs (entry and exit barrier)."""
-        e = self._epochs[ch0] + 1
-        self._epochs[ch0] = e + 1
-        return e
 
     def status(self) -> int:
         return int(self.err.cpu()[0].item())
@@ -155,9 +150,9 @@ class BucketAllReduce:
         if key not in self._channels:
             self._channels[key] = ctx.reserve_channels(ctx.C.MAX_COMM_BLOCKS)
         ch0 = self._channels[key]
-        epoch = ctx.next_epoch(ch0)
         return ctx.launch(lambda: ctx.C.nvl_allreduce_scale(self.ptrs, self.mc, ctx.flag_ptrs, off, n, ctx.rank,
-                                                            ctx.world, ch0, epoch, 1.0 / ctx.world, ctx.err))
+                                                            ctx.world, ch0, 0, 1.0 / ctx.world, ctx.err,
+                                                            ctx.epoch_ctr))
 
 
 class FusedZeroBucketStep:
@@ -177,13 +172,12 @@ class FusedZeroBucketStep:
         self.m, self.v = m, v
         self.ch0 = ctx.reserve_channels(ctx.C.MAX_COMM_BLOCKS)
 
-    def __call__(self, lr, b1, b2, eps, wd, bc1, bc2, grad_scale):
+    def __call__(self, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, dev_hyper=None):
         ctx = self.ctx
-        epoch = ctx.next_epoch(self.ch0)
         return ctx.launch(lambda: ctx.C.nvl_rs_adamw_bcast(
             self.g_ptrs, self.g_mc, self.p_ptrs, self.p_mc, self.s_ptrs, self.s_mc, self.m, self.v, ctx.flag_ptrs,
-            self.off, self.n, ctx.rank, ctx.world, self.ch0, epoch, lr, b1, b2, eps, wd, bc1, bc2, grad_scale,
-            ctx.err))
+            self.off, self.n, ctx.rank, ctx.world, self.ch0, 0, lr, b1, b2, eps, wd, bc1, bc2, grad_scale,
+            ctx.err, ctx.epoch_ctr, dev_hyper))
 
 
 def nvlink_available(pg: Optional[ProcessGroup], device: torch.device) -> bool:

@@ -58,7 +58,7 @@ def collectives():
     dist.all_reduce(gref, op=dist.ReduceOp.AVG)
     pref = init.clone()
     mref, vref = torch.zeros(nb, device=dev), torch.zeros(nb, device=dev)
-    C.adamw(pref, gref, mref, vref, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0)
+    C.adamw(pref, gref, mref, vref, None, 1e-2, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0, None)
 
     class _B:  # minimal stand-ins for ParamAndGradBuffer / bucket
         grad_buffer, param_buffer, shadow_buffer = grads, params, shadow
