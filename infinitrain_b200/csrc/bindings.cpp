@@ -48,6 +48,11 @@ void kernel_status_reset() {
 }
 
 // ------------------------------------------------------------------ GEMM
+// Kernel choice: 0 = one CTA per 128 x 256 tile, 1 = CTA pairs on 256 x 256 tiles.
+int g_gemm_mode = 1;
+void set_gemm_mode(int64_t mode) { g_gemm_mode = static_cast<int>(mode); }
+int64_t get_gemm_mode() { return g_gemm_mode; }
+
 // C[M,N] = A . B^T-like product; see kernels.h for the layout flags.
 void gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, int64_t M, int64_t N,
           int64_t K, at::Tensor& c, const c10::optional<at::Tensor>& c2,
@@ -106,7 +111,10 @@ void gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, int64_
   g.flags = static_cast<int>(flags);
   g.split_k = static_cast<int>(split_k);
   g.err = status_word(a.get_device()).data_ptr<int>();
-  check_rc(itb_gemm_bf16(&g, cur_stream()), "gemm_bf16_tcgen05");
+  if (g_gemm_mode == 1 && M > 128)
+    check_rc(itb_gemm_bf16_pair(&g, cur_stream()), "gemm_bf16_tcgen05_pair");
+  else
+    check_rc(itb_gemm_bf16(&g, cur_stream()), "gemm_bf16_tcgen05");
 }
 
 // ------------------------------------------------------------------ norms
@@ -432,6 +440,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kernel_status", &kernel_status);
   m.def("kernel_status_reset", &kernel_status_reset);
   m.def("gemm", &gemm);
+  m.def("set_gemm_mode", &set_gemm_mode);
+  m.def("get_gemm_mode", &get_gemm_mode);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

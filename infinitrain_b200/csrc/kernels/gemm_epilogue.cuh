@@ -1,0 +1,170 @@
+// Shared pieces of the tcgen05 GEMM kernels: the device-side argument block and the epilogue that
+// turns 32 fp32 accumulator columns of one output row into the stored result (bias, GELU dual
+// store, GELU derivative, residual add, fp32 / bf16 output, atomic split-K accumulation).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+
+namespace itb {
+
+struct GemmDev {
+  int M, N, K;
+  int k_blocks;        // ceil(K / BK)
+  int split_k;         // >= 1
+  int tiles_m, tiles_n;
+  void* C;             // bf16 or fp32, row-major, leading dimension ldc
+  long long ldc;
+  void* C2;            // second bf16 output: gelu(h) when kGemmGeluDual
+  const float* bias;   // [N] fp32
+  const void* residual;  // same dtype as C, leading dimension ldr
+  long long ldr;
+  const __nv_bfloat16* aux;  // [M, N] bf16 pre-activation for kGemmDGelu
+  long long ld_aux;
+  int flags;
+  int* err;            // device word: 0 ok, else a code of the wait that gave up
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.f + tanhf(u));
+}
+__device__ __forceinline__ float dgelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float x2 = x * x;
+  float u = k0 * (x + k1 * x * x2);
+  float t = tanhf(u);
+  float du = k0 * (1.f + 3.f * k1 * x2);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
+}
+
+// v: 32 consecutive accumulator columns [col0, col0 + 32) of output row `row`.
+__device__ __forceinline__ void gemm_epilogue_chunk(const GemmDev& p, int row, bool row_ok, int col0,
+                                                    float (&v)[32]) {
+  const bool out_f32 = p.flags & kGemmOutF32;
+          const bool full = (col0 + 32 <= p.N);
+          if (p.flags & kGemmBias) {
+  #pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+          }
+          if (row_ok) {
+            if (p.flags & kGemmDGelu) {
+              const __nv_bfloat16* h = p.aux + static_cast<long long>(row) * p.ld_aux + col0;
+              if (full && ((reinterpret_cast<uintptr_t>(h) & 15) == 0)) {
+  #pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 u = *reinterpret_cast<const uint4*>(h + j);
+                  const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&u);
+  #pragma unroll
+                  for (int e = 0; e < 8; ++e) v[j + e] *= dgelu_tanh(__bfloat162float(hb[e]));
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) v[j] *= dgelu_tanh(__bfloat162float(h[j]));
+              }
+            }
+            if (p.flags & kGemmGeluDual) {
+              // C receives the pre-activation, C2 the activation (both bf16).
+              __nv_bfloat16* c1 = static_cast<__nv_bfloat16*>(p.C) +
+                                  static_cast<long long>(row) * p.ldc + col0;
+              __nv_bfloat16* c2 = static_cast<__nv_bfloat16*>(p.C2) +
+                                  static_cast<long long>(row) * p.ldc + col0;
+              if (full && ((reinterpret_cast<uintptr_t>(c1) & 15) == 0) &&
+                  ((reinterpret_cast<uintptr_t>(c2) & 15) == 0)) {
+  #pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 u1, u2;
+                  __nv_bfloat16* b1 = reinterpret_cast<__nv_bfloat16*>(&u1);
+                  __nv_bfloat16* b2 = reinterpret_cast<__nv_bfloat16*>(&u2);
+  #pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    b1[e] = __float2bfloat16(v[j + e]);
+                    // The activation is computed from the rounded pre-activation so that the
+                    // backward pass, which only sees the stored bf16 value, is consistent.
+                    b2[e] = __float2bfloat16(gelu_tanh(__bfloat162float(b1[e])));
+                  }
+                  *reinterpret_cast<uint4*>(c1 + j) = u1;
+                  *reinterpret_cast<uint4*>(c2 + j) = u2;
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) {
+                    __nv_bfloat16 hb = __float2bfloat16(v[j]);
+                    c1[j] = hb;
+                    c2[j] = __float2bfloat16(gelu_tanh(__bfloat162float(hb)));
+                  }
+              }
+            } else if (out_f32) {
+              float* cp = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+              if (p.flags & kGemmResidual) {
+                const float* rp =
+                    static_cast<const float*>(p.residual) + static_cast<long long>(row) * p.ldr + col0;
+                for (int j = 0; j < 32; ++j)
+                  if (full || col0 + j < p.N) v[j] += rp[j];
+              }
+              const bool vec = full && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0);
+              if (p.flags & kGemmAtomic) {
+                if (vec) {
+  #pragma unroll
+                  for (int j = 0; j < 32; j += 4)
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + j),
+                                 "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3])
+                                 : "memory");
+                } else {
+                  for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.N) atomicAdd(cp + j, v[j]);
+                }
+              } else if (p.flags & kGemmAccum) {
+                for (int j = 0; j < 32; ++j)
+                  if (full || col0 + j < p.N) cp[j] += v[j];
+              } else if (vec) {
+  #pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(cp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) cp[j] = v[j];
+              }
+            } else {
+              __nv_bfloat16* cp =
+                  static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+              const bool vec = full && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0);
+              if (p.flags & kGemmResidual) {
+                const __nv_bfloat16* rp = static_cast<const __nv_bfloat16*>(p.residual) +
+                                          static_cast<long long>(row) * p.ldr + col0;
+                if (vec && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+  #pragma unroll
+                  for (int j = 0; j < 32; j += 8) {
+                    uint4 u = *reinterpret_cast<const uint4*>(rp + j);
+                    const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&u);
+  #pragma unroll
+                    for (int e = 0; e < 8; ++e) v[j + e] += __bfloat162float(rb[e]);
+                  }
+                } else {
+                  for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
+                }
+              }
+              if (vec) {
+  #pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 u;
+                  __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&u);
+  #pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    b2[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                  *reinterpret_cast<uint4*>(cp + j) = u;
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) cp[j] = __float2bfloat16(v[j]);
+              }
+            }
+          }
+}
+
+}  // namespace itb

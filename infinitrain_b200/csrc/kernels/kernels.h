@@ -45,6 +45,8 @@ typedef struct {
 } ItbGemmArgs;
 
 int itb_gemm_bf16(const ItbGemmArgs* args, cudaStream_t stream);
+// Same contract, computed by CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles per pair).
+int itb_gemm_bf16_pair(const ItbGemmArgs* args, cudaStream_t stream);
 
 // ------------------------------------------------------------------ normalisation
 // y = (x - mean) * rstd * gamma + beta over the last dimension C of [rows, C].

@@ -7,12 +7,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def C():
+@pytest.fixture(scope="module", params=["pair", "single"])
+def C(request):
+    """Every kernel test runs with both GEMM kernels: CTA pairs (cta_group::2) and single CTAs."""
     from infinitrain_b200 import _ext
 
     mod = _ext.load(required=True)
+    old = mod.get_gemm_mode()
+    mod.set_gemm_mode(1 if request.param == "pair" else 0)
     yield mod
+    mod.set_gemm_mode(old)
     assert mod.kernel_status() == 0, "a kernel wait timed out"
 
 
