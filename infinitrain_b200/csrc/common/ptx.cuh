@@ -87,6 +87,14 @@ __device__ __forceinline__ void tma_store_2d(const void* desc, const void* smem_
                : "l"(desc), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// 2-D tiled reduction shared -> global: global += shared, element-wise (type from the tensor map).
+__device__ __forceinline__ void tma_reduce_add_2d(const void* desc, const void* smem_src, int32_t x,
+                                                  int32_t y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(desc), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
