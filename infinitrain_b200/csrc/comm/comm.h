@@ -41,6 +41,53 @@ int itb_nvl_rs_adamw_bcast(const ItbPeerPtrs* grads, const void* mc_grads, const
                            int world, int ch0, int epoch, const ItbAdamHyper* hyper, int* err,
                            int* epoch_ctr, const float* dev_hyper, cudaStream_t stream);
 
+// ---- tensor-parallel GEMMs fused with all-gather / reduce-scatter (tp_gemm.cu)
+// Activations are [batch * T, cols] with row = b * T + t; under sequence parallelism rank s holds
+// t in [s * Tl, (s + 1) * Tl), Tl = T / world (a multiple of 256).  All pointer tables are
+// symmetric-memory addresses of the same buffer on every rank; counters marked "this GPU" are
+// ordinary device memory that the kernels advance themselves (replayable from a CUDA graph).
+enum { kItbTpPush = 1, kItbTpGateA = 2, kItbTpScatter = 4 };
+
+typedef struct {
+  int mode;                   // kItbTpPush | kItbTpGateA | kItbTpScatter
+  int rank, world;
+  int T, Tl, batch;
+  ItbPeerPtrs started;        // int32[world] on each rank: 1 + index of the latest launch rank r began
+  int* launch_ctr;            // this GPU
+  unsigned* cta_done;         // this GPU, zero between launches
+  // push of the local shard [batch * Tl, push_cols] bf16 into every rank's gathered [batch * T, push_cols]
+  const void* push_src;
+  int push_cols;
+  ItbPeerPtrs gather;
+  void* gather_mc;            // multicast address of the gathered buffer or NULL
+  ItbPeerPtrs push_arrive;    // int32[world] on each rank
+  int* push_total;            // this GPU: arrivals per source the pushes so far add up to
+  int push_lag;               // launches since the gathered buffer was last used (large = never)
+  // loads of A (the gathered buffer) wait for the shard they read
+  const int* gate_arrive;     // this rank's arrival counters of that buffer
+  const int* gate_total;      // this GPU: that buffer's push_total
+  int gate_includes_this_launch;
+  // reduce-scatter of the output rows: slab [world][batch * Tl, N] bf16 on each rank
+  ItbPeerPtrs slab;
+  ItbPeerPtrs rs_arrive;      // int32[world] on each rank
+  int* rs_total;              // this GPU
+  int rs_lag;
+  void* rs_out;               // [batch * Tl, N] bf16 or fp32
+  long long rs_ld_out;
+  int rs_out_f32;
+  const float* rs_bias;       // optional, added once after the sum
+  const void* rs_residual;    // optional bf16 [batch * Tl, N]
+  long long rs_ld_res;
+} ItbTpArgs;
+
+// `gemm` is an ItbGemmArgs (kernels/kernels.h); bf16 output only.  With kItbTpScatter the GEMM's own
+// C / bias / residual are unused.  Returns 0, a CUDA error, or a negative argument error.
+int itb_tp_gemm(const void* gemm, const ItbTpArgs* tp, cudaStream_t stream);
+// Thread blocks the launch for an M x N output uses.
+int itb_tp_gemm_ctas(int M, int N);
+// Holds the stream until `*total` arrivals of every rank have been counted.
+int itb_tp_wait(const int* arrive, const int* total, int world, int* err, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -83,6 +83,9 @@ class NvlinkContext:
         hdl = self._symm_mem.rendezvous(t, group=self.pg.pg)
         t.zero_()
         torch.cuda.synchronize(self.device)
+        # no rank may write into a peer's copy before that peer has finished zeroing it
+        self.pg.Barrier()
+        torch.cuda.synchronize(self.device)
         self._allocs.append((t, hdl))
         return t
 
@@ -192,17 +195,243 @@ def nvlink_available(pg: Optional[ProcessGroup], device: torch.device) -> bool:
 
 
 # --------------------------------------------------------------------------- tensor parallel (fused)
-_TP_CTX = None
+class _SymBuf:
+    """A symmetric workspace of the fused tensor-parallel GEMMs with its arrival counters."""
+
+    def __init__(self, tp: "TpFusedContext", numel: int):
+        nvl = tp.nvl
+        self.t = nvl.alloc(numel, torch.bfloat16)
+        self.ptrs, self.mc = nvl.ptrs(self.t)
+        blk = tp.reserve_flag_block()
+        self.arrive_ptrs = [p + blk * 32 for p in tp.flag_ptrs]      # int32[8] per block
+        self.my_arrive = self.arrive_ptrs[tp.rank]
+        self.total = torch.zeros(1, dtype=torch.int32, device=nvl.device)   # advanced by the kernels
+        self.last_use: Optional[int] = None
 
 
-def fused_tp_enabled(x: torch.Tensor) -> bool:
-    """True when the fused all-gather+GEMM / GEMM+reduce-scatter kernels should serve ``x``."""
-    return bool(x.is_cuda and _TP_CTX is not None)
+class TpFusedContext:
+    """Workspaces, counters and launch bookkeeping of the all-gather+GEMM / GEMM+reduce-scatter
+    kernels of one tensor-parallel group.  Every rank must issue the same sequence of launches."""
+
+    kFlagBlocks = 64
+
+    def __init__(self, nvl: NvlinkContext):
+        self.nvl = nvl
+        self.C = nvl.C
+        self.rank, self.world = nvl.rank, nvl.world
+        self.flags = nvl.alloc(self.kFlagBlocks * 8, torch.int32)
+        self.flag_ptrs, _ = nvl.ptrs(self.flags)
+        self._next_block = 1                     # block 0: `started`
+        self.launch_ctr = torch.zeros(1, dtype=torch.int32, device=nvl.device)
+        self.cta_done = torch.zeros(1, dtype=torch.int32, device=nvl.device)
+        self.launch_index = 0
+        self._bufs: Dict[Tuple[str, int], _SymBuf] = {}
+
+    def reserve_flag_block(self) -> int:
+        if self._next_block >= self.kFlagBlocks:
+            raise RuntimeError("out of tensor-parallel flag blocks")
+        self._next_block += 1
+        return self._next_block - 1
+
+    def buf(self, tag: str, numel: int) -> _SymBuf:
+        key = (tag, numel)
+        if key not in self._bufs:
+            self._bufs[key] = _SymBuf(self, numel)      # collective: all ranks get here together
+        return self._bufs[key]
+
+    def _lag(self, b: _SymBuf) -> int:
+        return (self.launch_index - b.last_use) if b.last_use is not None else (1 << 24)
+
+    def launch(self, a, a_mn, b, b_mn, M, N, K, c, c2, bias, aux, flags, *, batch, T, push=None, push_src=None,
+               gate=None, gate_includes=1, slab=None, rs_out=None, rs_bias=None, rs_residual=None):
+        C = self.C
+        mode = (C.TP_PUSH if push is not None else 0) | (C.TP_GATE_A if gate is not None else 0) | \
+               (C.TP_SCATTER if slab is not None else 0)
+        tp = {"mode": mode, "rank": self.rank, "world": self.world, "T": T, "Tl": T // self.world, "batch": batch,
+              "started": self.flag_ptrs, "launch_ctr": self.launch_ctr, "cta_done": self.cta_done}
+        if push is not None:
+            tp.update(push_src=push_src, gather=push.ptrs, gather_mc=push.mc, push_arrive=push.arrive_ptrs,
+                      push_total=push.total, push_lag=self._lag(push))
+        if gate is not None:
+            tp.update(gate_arrive=gate.my_arrive, gate_total=gate.total, gate_includes_this_launch=gate_includes)
+        if slab is not None:
+            tp.update(slab=slab.ptrs, rs_arrive=slab.arrive_ptrs, rs_total=slab.total, rs_lag=self._lag(slab),
+                      rs_out=rs_out, rs_bias=rs_bias, rs_residual=rs_residual)
+        C.tp_gemm(a, a_mn, b, b_mn, M, N, K, c, c2, bias, aux, flags, tp, self.nvl.err)
+        ops._counters["launches"] += 1
+        for bf in (push, gate, slab):
+            if bf is not None:
+                bf.last_use = self.launch_index
+        self.launch_index += 1
+
+    def wait_arrivals(self, b: _SymBuf):
+        """Holds the current stream until every rank's push into ``b`` has landed."""
+        self.C.tp_wait(b.my_arrive, b.total, self.world, self.nvl.err)
+        ops._counters["launches"] += 1
+
+
+_TP_CTX: Optional[TpFusedContext] = None
+_TP_TRIED = False
+
+
+def _tp_context(device: torch.device) -> Optional[TpFusedContext]:
+    global _TP_CTX, _TP_TRIED
+    if _TP_CTX is None and not _TP_TRIED:
+        _TP_TRIED = True
+        from .process_group import tp_group
+
+        g = tp_group()
+        if os.environ.get("ITB_FUSED_TP", "1") == "1" and nvlink_available(g, device):
+            _TP_CTX = TpFusedContext(NvlinkContext.get(g, device))
+    return _TP_CTX
+
+
+def reset_fused_tp():
+    """Forgets the context (tests that rebuild the process groups)."""
+    global _TP_CTX, _TP_TRIED
+    _TP_CTX, _TP_TRIED = None, False
+
+
+def fused_tp_enabled(x: torch.Tensor, seq_sharded: bool = True) -> bool:
+    """True when the fused all-gather+GEMM / GEMM+reduce-scatter kernels can serve ``x``: a 3-D CUDA
+    activation under bf16 whose per-rank sequence length is a multiple of 256."""
+    if not (x.is_cuda and x.dim() == 3 and ops._use_fused(x) and x.shape[-1] % 8 == 0):
+        return False
+    tp = _tp_context(x.device)
+    if tp is None:
+        return False
+    t_local = x.shape[1] if seq_sharded else x.shape[1] // tp.world
+    return t_local % 256 == 0 and (seq_sharded or x.shape[1] % tp.world == 0)
+
+
+class _AllGatherLinearFn(torch.autograd.Function):
+    """y[B, T, N] = all_gather_T(x[B, T/tp, K]) W^T (+ bias) (optionally GELU), one launch per rank.
+
+    Backward: one launch computes dX = reduce_scatter_T(dY W) and re-gathers x for the weight
+    gradient, which follows as a plain GEMM once the shards have arrived."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, gelu):
+        tp = _TP_CTX
+        C = tp.C
+        B, Tl, K = x.shape
+        T, N = Tl * tp.world, weight.shape[0]
+        M = B * T
+        x2 = ops._as_bf16_2d(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        w = ops.weight_lp(weight)
+        g0 = tp.buf("gather", M * K)
+        ld = ops._pad_cols(N)
+        out = torch.empty((M, ld), device=x.device, dtype=torch.bfloat16)
+        flags = C.GEMM_BIAS if bias is not None else 0
+        pre = None
+        if gelu:
+            pre = torch.empty((M, ld), device=x.device, dtype=torch.bfloat16)
+            tp.launch(g0.t.view(M, K), False, w, False, M, N, K, pre, out, bias, None, flags | C.GEMM_GELU_DUAL,
+                      batch=B, T=T, push=g0, push_src=x2, gate=g0)
+        else:
+            tp.launch(g0.t.view(M, K), False, w, False, M, N, K, out, None, bias, None, flags,
+                      batch=B, T=T, push=g0, push_src=x2, gate=g0)
+        ctx.save_for_backward(x2, weight, pre)
+        ctx.dims = (B, T, Tl, M, N, K, ld)
+        ctx.has_bias, ctx.gelu, ctx.x_dtype = bias is not None, gelu, x.dtype
+        y = out[:, :N] if ld != N else out
+        return y.view(B, T, N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        tp = _TP_CTX
+        C = tp.C
+        x2, weight, pre = ctx.saved_tensors
+        B, T, Tl, M, N, K, ld = ctx.dims
+        dy2 = ops._as_bf16_2d(dy)
+        if ctx.gelu:
+            dyc = dy2 if dy2.is_contiguous() else dy2.contiguous()
+            prec = pre[:, :N] if ld != N else pre
+            dy2 = C.gelu_bwd(dyc, prec if prec.is_contiguous() else prec.contiguous())
+            ops._counters["launches"] += 1
+        w = ops.weight_lp(weight)
+        g1 = tp.buf("regather", M * K)
+        slab = tp.buf("slab", M * K)
+        dx2 = torch.empty((B * Tl, K), device=dy.device, dtype=torch.bfloat16)
+        tp.launch(dy2, False, w, True, M, K, N, None, None, None, None, 0, batch=B, T=T, push=g1, push_src=x2,
+                  slab=slab, rs_out=dx2)
+        dx = dx2.view(B, Tl, K)
+        if ctx.x_dtype != torch.bfloat16:
+            dx = dx.to(ctx.x_dtype)
+        dw = db = None
+        if ctx.needs_input_grad[1]:
+            tp.wait_arrivals(g1)
+            dw = ops._wgrad(C, dy2, g1.t.view(M, K), weight, N, K, M)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = ops._bias_grad(C, dy2, N)
+        return dx, dw, db, None
+
+
+class _LinearReduceScatterFn(torch.autograd.Function):
+    """y[B, T/tp, N] = reduce_scatter_T(x[B, T, K/tp] W^T) + bias + residual, one launch per rank.
+
+    Backward: one launch computes dX = all_gather_T(dY) W; the weight gradient reads the gathered dY
+    that launch left in this rank's workspace."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        tp = _TP_CTX
+        B, T, K = x.shape
+        Tl, N = T // tp.world, weight.shape[0]
+        M = B * T
+        x2 = ops._as_bf16_2d(x)
+        w = ops.weight_lp(weight)
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(B * Tl, N)
+            if res2.dtype != torch.bfloat16 or res2.stride(-1) != 1 or res2.stride(0) % 8 or res2.data_ptr() % 16:
+                res2 = res2.to(torch.bfloat16).contiguous()
+        out = torch.empty((B * Tl, N), device=x.device, dtype=torch.bfloat16)
+        slab = tp.buf("slab", M * N)
+        tp.launch(x2, False, w, False, M, N, K, None, None, None, None, 0, batch=B, T=T, slab=slab, rs_out=out,
+                  rs_bias=bias, rs_residual=res2)
+        ctx.save_for_backward(x2, weight)
+        ctx.dims = (B, T, Tl, M, N, K)
+        ctx.has_bias, ctx.has_res, ctx.x_dtype = bias is not None, residual is not None, x.dtype
+        ctx.res_dtype = residual.dtype if residual is not None else None
+        return out.view(B, Tl, N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        tp = _TP_CTX
+        C = tp.C
+        x2, weight = ctx.saved_tensors
+        B, T, Tl, M, N, K = ctx.dims
+        dy2 = ops._as_bf16_2d(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        w = ops.weight_lp(weight)
+        g0 = tp.buf("gather", M * N)
+        dx2 = torch.empty((M, K), device=dy.device, dtype=torch.bfloat16)
+        tp.launch(g0.t.view(M, N), False, w, True, M, K, N, dx2, None, None, None, 0, batch=B, T=T, push=g0,
+                  push_src=dy2, gate=g0)
+        dx = dx2.view(B, T, K)
+        if ctx.x_dtype != torch.bfloat16:
+            dx = dx.to(ctx.x_dtype)
+        dw = db = dres = None
+        if ctx.needs_input_grad[1]:
+            dw = ops._wgrad(C, g0.t.view(M, N), x2, weight, N, K, M)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = ops._bias_grad(C, dy2, N)
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = dy if dy.dtype == ctx.res_dtype else dy.to(ctx.res_dtype)
+        return dx, dw, db, dres
 
 
 def allgather_linear(x, weight, bias, gelu=False):
-    raise RuntimeError("fused tensor-parallel kernels are not initialised")
+    if _TP_CTX is None:
+        raise RuntimeError("fused tensor-parallel kernels are not initialised")
+    return _AllGatherLinearFn.apply(x, weight, bias, gelu)
 
 
 def linear_reduce_scatter(x, weight, bias, residual):
-    raise RuntimeError("fused tensor-parallel kernels are not initialised")
+    if _TP_CTX is None:
+        raise RuntimeError("fused tensor-parallel kernels are not initialised")
+    return _LinearReduceScatterFn.apply(x, weight, bias, residual)

@@ -260,7 +260,7 @@ class RowParallelLinear(Module):
         grp = _tp()
         if grp is None or not self.reduce_output:
             y = ops.linear(x, self.weight, add_bias, residual=residual)
-        elif self.sequence_parallel and symm.fused_tp_enabled(x):
+        elif self.sequence_parallel and symm.fused_tp_enabled(x, seq_sharded=False):
             y = symm.linear_reduce_scatter(x, self.weight, add_bias, residual)
         else:
             y = ops.linear(x, self.weight, None)

@@ -145,9 +145,79 @@ def ddp(mode):
         print(f"DDP OK mode={mode} worst_rel={worst:.2e} losses={losses.tolist()}")
 
 
+def tp_fused():
+    """Column- and row-parallel linears under sequence parallelism: the fused all-gather+GEMM /
+    GEMM+reduce-scatter launches against the NCCL formulation of the same layers."""
+    import torch.distributed as dist
+
+    from infinitrain_b200.autocast import AutocastGuard
+    from infinitrain_b200.datatype import DataType
+    from infinitrain_b200.device import DeviceType
+    from infinitrain_b200.parallel import global_env as genv
+    from infinitrain_b200.parallel import symm
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory
+    from infinitrain_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    genv.InitAllEnv(world_size=world, rank=rank, tensor_parallel_size=world, sequence_parallel_enabled=True)
+    ProcessGroupFactory.Instance().Init(device=dev, timeout_s=120)
+    B, Tl, H, F = 2, 256, 512, 1024 * world
+    T = Tl * world
+    torch.manual_seed(7)
+    col = ColumnParallelLinear(H, F, bias=True, gather_output=False, input_is_parallel=False,
+                               sequence_parallel=True, device=dev)
+    row = RowParallelLinear(F, H, bias=True, input_is_parallel=True, sequence_parallel=True, device=dev)
+    torch.manual_seed(100 + rank)
+    for prm in list(col.Parameters()) + list(row.Parameters()):
+        prm.data.normal_(0, 0.05)
+    results = {}
+    for fused in ("0", "1"):
+        os.environ["ITB_FUSED_TP"] = fused
+        symm.reset_fused_tp()
+        outs = []
+        for it in range(3):
+            torch.manual_seed(1000 + it * 10 + rank)
+            x = (torch.randn(B, Tl, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
+            res = (torch.randn(B, Tl, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
+            for prm in list(col.Parameters()) + list(row.Parameters()):
+                prm.grad = None
+            with AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16):
+                h = col(x, gelu=(it % 2 == 1))
+                y = row(h, residual=res)
+            assert y.shape == (B, Tl, H), y.shape
+            torch.manual_seed(5000 + it * 10 + rank)
+            gy = (torch.randn_like(y.float()) * 0.1).to(y.dtype)
+            y.backward(gy)
+            outs.append([y.detach().float(), x.grad.float(), res.grad.float()] +
+                        [prm.grad.float().clone() for prm in list(col.Parameters()) + list(row.Parameters())])
+        torch.cuda.synchronize()
+        results[fused] = outs
+        if fused == "1":
+            assert symm._TP_CTX is not None, "fused tensor-parallel context was not created"
+            assert symm._TP_CTX.nvl.status() == 0, symm._TP_CTX.nvl.status()
+            assert symm._TP_CTX.launch_index == 12, symm._TP_CTX.launch_index
+    worst = 0.0
+    names = ["y", "dx", "dres", "col.dw", "col.db", "row.dw", "row.db"]
+    for it, (a_it, b_it) in enumerate(zip(results["0"], results["1"])):
+        for name, a, b in zip(names, a_it, b_it):
+            rel = ((a - b).norm() / (a.norm() + 1e-6)).item()
+            if rel > 2e-2:
+                print(f"[rank {rank}] iteration {it} {name}: rel {rel:.3e}", flush=True)
+            worst = max(worst, rel)
+    t = torch.tensor([worst], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    assert t.item() < 2e-2, t.item()
+    if rank == 0:
+        print(f"TP FUSED OK worst_rel={t.item():.2e}")
+
+
 if __name__ == "__main__":
     if sys.argv[1] == "collectives":
         collectives()
+    elif sys.argv[1] == "tp_fused":
+        tp_fused()
     else:
         ddp(sys.argv[2])
     import torch.distributed as dist

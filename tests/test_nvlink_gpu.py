@@ -40,3 +40,11 @@ def test_ddp_training_matches_single_gpu(mode):
     os.environ["ITB_NVLS"] = "1"
     out = _torchrun("mgpu_worker.py", 2, "ddp", mode)
     assert "DDP OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fused_tensor_parallel_linears_match_nccl(nvls):
+    os.environ["ITB_NVLS"] = nvls
+    out = _torchrun("mgpu_worker.py", 2, "tp_fused")
+    assert "TP FUSED OK" in out
