@@ -94,12 +94,15 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=16)
-    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--batch", type=int, default=None, help="micro-batch per GPU (16 for gpt2, 1 for llama3-*)")
+    ap.add_argument("--seq", type=int, default=None, help="sequence length (1024 for gpt2, 2048 for llama3-*)")
     ap.add_argument("--zero", type=int, default=2)
-    ap.add_argument("--model", default="gpt2")
+    ap.add_argument("--model", default="gpt2", help="gpt2 | llama3-1b | llama3-3b | llama3-8b")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (sequence parallelism on when > 1)")
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the model's own)")
     ap.add_argument("--residual", default="bf16", choices=["bf16", "fp32"])
-    ap.add_argument("--graph", type=int, default=1, help="capture the whole training step in a CUDA graph")
+    ap.add_argument("--graph", type=int, default=None,
+                    help="capture the whole training step in a CUDA graph (default: 1 without tensor parallelism)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -120,7 +123,7 @@ def main():
     from infinitrain_b200.autocast import AutocastGuard
     from infinitrain_b200.datatype import DataType
     from infinitrain_b200.device import DeviceType
-    from infinitrain_b200.models import GPT2
+    from infinitrain_b200.models import GPT2, LLaMA3
     from infinitrain_b200.nn import CrossEntropyLoss
     from infinitrain_b200.ops import functional as ops
     from infinitrain_b200.optim import Adam
@@ -128,16 +131,40 @@ def main():
     from infinitrain_b200.parallel.process_group import ProcessGroupFactory
 
     C = _ext.load(required=True)
-    genv.InitAllEnv(world_size=world, rank=rank)
+    tp = args.tp
+    if args.graph is None:
+        args.graph = 1 if tp == 1 else 0
+    if world % tp:
+        raise SystemExit(f"--tp {tp} does not divide the world size {world}")
+    dp = world // tp
+    genv.InitAllEnv(world_size=world, rank=rank, tensor_parallel_size=tp, sequence_parallel_enabled=tp > 1)
     ProcessGroupFactory.Instance().Init(device=dev)
 
     torch.manual_seed(42)
-    B, T = args.batch, args.seq
-    model = GPT2(args.model, residual_dtype=torch.bfloat16 if args.residual == "bf16" else torch.float32).to(dev)
-    loss_fn = CrossEntropyLoss()
+    llama = args.model.startswith("llama3")
+    B = args.batch or (1 if llama else 16)
+    T = args.seq or (2048 if llama else 1024)
+    res_dtype = torch.bfloat16 if args.residual == "bf16" else torch.float32
+    over = {"n_layer": args.layers} if args.layers else {}
+    with torch.device(dev):
+        model = (LLaMA3(args.model, residual_dtype=res_dtype, **over) if llama
+                 else GPT2(args.model, residual_dtype=res_dtype, **over))
+    model = model.to(dev)
+    mcfg = model.config
+    sp_sync = None
+    if tp > 1:
+        from infinitrain_b200.parallel.tensor_parallel import (AllReduceSequenceParallelGrads,
+                                                               VocabParallelCrossEntropyLoss)
+
+        loss_fn = VocabParallelCrossEntropyLoss(mcfg.original_vocab_size)
+        sp_sync = AllReduceSequenceParallelGrads
+    else:
+        loss_fn = CrossEntropyLoss()
     creator = Adam.Create(1e-4, 0.9, 0.95, 1e-8, weight_decay=0.1)
-    parallelism = "single"
-    if world > 1:
+    parallelism = "single" if world == 1 else (f"tp{tp}+sp" if dp == 1 else f"dp{dp}xtp{tp}+sp")
+    if dp == 1:
+        opt = creator(model.Parameters())
+    elif world > 1:
         from infinitrain_b200.parallel.ddp.config import DistributedDataParallelConfig
         from infinitrain_b200.parallel.ddp.distributed_data_parallel import DistributedDataParallel
         from infinitrain_b200.parallel.ddp.distributed_optimizer import DistributedOptimizer
@@ -148,12 +175,11 @@ def main():
             opt = DistributedOptimizer(creator, model.Parameters(), model)
         else:
             opt = creator(model.Parameters())
-        parallelism = f"dp{world}+zero{args.zero}"
-    else:
-        opt = creator(model.Parameters())
+        parallelism = f"dp{dp}+zero{args.zero}" if tp == 1 else f"dp{dp}xtp{tp}+sp+zero{args.zero}"
 
-    V = 50257
-    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    V = mcfg.original_vocab_size
+    # ranks of one tensor-parallel group read the same tokens
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank // tp)
     n_host = 8
     host_x = [torch.randint(0, V, (B, T), generator=gen).pin_memory() for _ in range(n_host)]
     host_y = [torch.randint(0, V, (B, T), generator=gen).pin_memory() for _ in range(n_host)]
@@ -165,6 +191,8 @@ def main():
         with AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16):
             loss = loss_fn(model(x), y)
         loss.backward()
+        if sp_sync is not None:
+            sp_sync(model)
         opt.Step()
         return loss
 
@@ -225,17 +253,21 @@ def main():
         dev_ms, e2e_ms = t.tolist()
     status = C.kernel_status()
     if rank == 0:
-        tokens = B * T * world * args.steps
+        tokens = B * T * dp * args.steps
         value = tokens / (dev_ms / 1e3)
         e2e = tokens / (e2e_ms / 1e3)
         out = {
-            "metric": "tokens/sec GPT-2 124M training (bf16 autocast, AdamW, DDP + ZeRO-2 for N>1), max over ranks",
+            "metric": ("tokens/sec GPT-2 124M training (bf16 autocast, AdamW, DDP + ZeRO-2 for N>1), max over ranks"
+                       if not llama else
+                       f"tokens/sec {args.model} training (bf16 autocast, AdamW, {parallelism}), max over ranks"),
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
-            "config": {"model": "GPT-2 124M (12L, 12H, 768, vocab 50257, ctx 1024, tied embeddings)",
-                       "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": T,
+            "config": {"model": ("GPT-2 124M (12L, 12H, 768, vocab 50257, ctx 1024, tied embeddings)" if not llama else
+                                 f"{args.model} ({mcfg.n_layer}L, {mcfg.n_embd} wide, "
+                                 f"{mcfg.n_head}q/{mcfg.n_kv_head}kv heads, vocab {V})"),
+                       "global_batch": B * dp, "micro_batch_per_gpu": B, "seq_len": T,
                        "parallelism": parallelism, "optimizer": "AdamW lr 1e-4 wd 0.1",
                        "residual_stream": args.residual, "cuda_graph": bool(args.graph),
                        "l2": "working set per step (activations + 124M fp32 weights, grads, moments) far exceeds "

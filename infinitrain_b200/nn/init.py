@@ -26,12 +26,12 @@ def _fill(t: torch.Tensor, host: torch.Tensor) -> torch.Tensor:
 
 
 def Normal(t: torch.Tensor, mean: float = 0.0, std: float = 1.0, generator=None) -> torch.Tensor:
-    host = torch.empty(t.shape, dtype=torch.float32).normal_(mean, std, generator=generator or _GEN)
+    host = torch.empty(t.shape, dtype=torch.float32, device="cpu").normal_(mean, std, generator=generator or _GEN)
     return _fill(t, host)
 
 
 def Uniform(t: torch.Tensor, a: float = 0.0, b: float = 1.0, generator=None) -> torch.Tensor:
-    host = torch.empty(t.shape, dtype=torch.float32).uniform_(a, b, generator=generator or _GEN)
+    host = torch.empty(t.shape, dtype=torch.float32, device="cpu").uniform_(a, b, generator=generator or _GEN)
     return _fill(t, host)
 
 

@@ -207,6 +207,17 @@ class _SymBuf:
         self.my_arrive = self.arrive_ptrs[tp.rank]
         self.total = torch.zeros(1, dtype=torch.int32, device=nvl.device)   # advanced by the kernels
         self.last_use: Optional[int] = None
+        # the local shard whose gathered copy the buffer holds (kept alive so that its address cannot
+        # be handed to another tensor) and that tensor's version at the push
+        self.content: Optional[Tuple[torch.Tensor, int]] = None
+
+    def holds(self, x2: torch.Tensor) -> bool:
+        """True when the last push into this buffer gathered exactly ``x2`` (same memory, unmodified)."""
+        if self.content is None:
+            return False
+        src, ver = self.content
+        return (src.data_ptr() == x2.data_ptr() and src.shape == x2.shape and src.stride() == x2.stride()
+                and x2._version == ver and src._version == ver)
 
 
 class TpFusedContext:
@@ -262,6 +273,8 @@ class TpFusedContext:
         for bf in (push, gate, slab):
             if bf is not None:
                 bf.last_use = self.launch_index
+        if push is not None:
+            push.content = (push_src, push_src._version)
         self.launch_index += 1
 
     def wait_arrivals(self, b: _SymBuf):
@@ -326,13 +339,16 @@ class _AllGatherLinearFn(torch.autograd.Function):
         out = torch.empty((M, ld), device=x.device, dtype=torch.bfloat16)
         flags = C.GEMM_BIAS if bias is not None else 0
         pre = None
+        # a second linear on the same activation (SwiGLU's gate and up projections) reads the copy
+        # the first one gathered
+        again = g0.holds(x2)
+        kw = dict(batch=B, T=T, gate=g0, gate_includes=0) if again else dict(batch=B, T=T, push=g0, push_src=x2,
+                                                                              gate=g0)
         if gelu:
             pre = torch.empty((M, ld), device=x.device, dtype=torch.bfloat16)
-            tp.launch(g0.t.view(M, K), False, w, False, M, N, K, pre, out, bias, None, flags | C.GEMM_GELU_DUAL,
-                      batch=B, T=T, push=g0, push_src=x2, gate=g0)
+            tp.launch(g0.t.view(M, K), False, w, False, M, N, K, pre, out, bias, None, flags | C.GEMM_GELU_DUAL, **kw)
         else:
-            tp.launch(g0.t.view(M, K), False, w, False, M, N, K, out, None, bias, None, flags,
-                      batch=B, T=T, push=g0, push_src=x2, gate=g0)
+            tp.launch(g0.t.view(M, K), False, w, False, M, N, K, out, None, bias, None, flags, **kw)
         ctx.save_for_backward(x2, weight, pre)
         ctx.dims = (B, T, Tl, M, N, K, ld)
         ctx.has_bias, ctx.gelu, ctx.x_dtype = bias is not None, gelu, x.dtype
@@ -355,14 +371,19 @@ class _AllGatherLinearFn(torch.autograd.Function):
         g1 = tp.buf("regather", M * K)
         slab = tp.buf("slab", M * K)
         dx2 = torch.empty((B * Tl, K), device=dy.device, dtype=torch.bfloat16)
-        tp.launch(dy2, False, w, True, M, K, N, None, None, None, None, 0, batch=B, T=T, push=g1, push_src=x2,
-                  slab=slab, rs_out=dx2)
+        again = g1.holds(x2)
+        if again:
+            tp.launch(dy2, False, w, True, M, K, N, None, None, None, None, 0, batch=B, T=T, slab=slab, rs_out=dx2)
+        else:
+            tp.launch(dy2, False, w, True, M, K, N, None, None, None, None, 0, batch=B, T=T, push=g1, push_src=x2,
+                      slab=slab, rs_out=dx2)
         dx = dx2.view(B, Tl, K)
         if ctx.x_dtype != torch.bfloat16:
             dx = dx.to(ctx.x_dtype)
         dw = db = None
         if ctx.needs_input_grad[1]:
-            tp.wait_arrivals(g1)
+            if not again:
+                tp.wait_arrivals(g1)
             dw = ops._wgrad(C, dy2, g1.t.view(M, K), weight, N, K, M)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = ops._bias_grad(C, dy2, N)

@@ -48,3 +48,10 @@ def test_fused_tensor_parallel_linears_match_nccl(nvls):
     os.environ["ITB_NVLS"] = nvls
     out = _torchrun("mgpu_worker.py", 2, "tp_fused")
     assert "TP FUSED OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 8, reason="needs 8 GPUs")
+def test_fused_tensor_parallel_linears_match_nccl_8_ranks():
+    os.environ["ITB_NVLS"] = "1"
+    out = _torchrun("mgpu_worker.py", 8, "tp_fused")
+    assert "TP FUSED OK" in out
