@@ -109,6 +109,11 @@ def main():
 
     import torch
 
+    if os.environ.get("ITB_BENCH_WATCHDOG_S"):
+        # debugging aid: print every thread's stack and exit if the run takes longer than this
+        import faulthandler
+
+        faulthandler.dump_traceback_later(int(os.environ["ITB_BENCH_WATCHDOG_S"]), exit=True)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -277,8 +282,14 @@ def main():
                     "h2d_bytes_per_step": 2 * B * T * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "final_loss": last, "kernel_status": status,
         }
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
+        if args.graph and tp > 1:
+            # a captured graph that contains NCCL collectives keeps the communicator busy at teardown:
+            # the result is printed, so leave without the collective shutdown
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            os._exit(0)
         torch.distributed.destroy_process_group()
     return 0
 

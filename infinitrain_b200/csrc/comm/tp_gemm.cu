@@ -49,6 +49,7 @@ static int launch_tp(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 }
 
 __global__ void tp_wait_kernel(const int* arrive, const int* total, int world, int* err) {
+  if (*static_cast<volatile int*>(err) != 0) return;
   if (threadIdx.x < world) {
     if (!tp_wait_ge(arrive + threadIdx.x, *total)) atomicCAS(err, 0, 124);
   }

@@ -37,7 +37,7 @@ constexpr uint32_t kTmemCols = 512;                            // two 256-column
 // holds t in [s * Tl, (s + 1) * Tl) of every b as local row b * Tl + (t - s * Tl).
 enum { kTpPush = 1, kTpGateA = 2, kTpScatter = 4 };
 constexpr int kTpMaxRanks = 8;
-constexpr unsigned kTpSpinLimit = 1u << 24;     // polls with a short sleep: several seconds of skew
+constexpr unsigned kTpSpinLimit = 1u << 23;     // polls with a short sleep: seconds of skew
 
 struct TpDev {
   int mode;                 // kTpPush | kTpGateA | kTpScatter
@@ -100,6 +100,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_c2,
                       const __grid_constant__ CUtensorMap tma_e, const GemmDev p, const TpDev tp) {
+  if constexpr (kTp) {
+    // an earlier launch gave up on a peer: do not wait for it again (the status word was written
+    // before this launch began, so both CTAs of a pair read the same value)
+    if (*static_cast<volatile int*>(p.err) != 0) return;
+  }
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));

@@ -168,9 +168,12 @@ def tp_fused():
     torch.manual_seed(7)
     col = ColumnParallelLinear(H, F, bias=True, gather_output=False, input_is_parallel=False,
                                sequence_parallel=True, device=dev)
+    col2 = ColumnParallelLinear(H, F, bias=False, gather_output=False, input_is_parallel=False,
+                                sequence_parallel=True, device=dev)
     row = RowParallelLinear(F, H, bias=True, input_is_parallel=True, sequence_parallel=True, device=dev)
     torch.manual_seed(100 + rank)
-    for prm in list(col.Parameters()) + list(row.Parameters()):
+    params = list(col.Parameters()) + list(col2.Parameters()) + list(row.Parameters())
+    for prm in params:
         prm.data.normal_(0, 0.05)
     results = {}
     for fused in ("0", "1"):
@@ -181,25 +184,27 @@ def tp_fused():
             torch.manual_seed(1000 + it * 10 + rank)
             x = (torch.randn(B, Tl, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
             res = (torch.randn(B, Tl, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
-            for prm in list(col.Parameters()) + list(row.Parameters()):
+            for prm in params:
                 prm.grad = None
             with AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16):
-                h = col(x, gelu=(it % 2 == 1))
+                # two column-parallel linears on one activation (the second reads the copy the first
+                # gathered), as the gate / up projections of a SwiGLU MLP do
+                h = col(x, gelu=(it % 2 == 1)) + col2(x)
                 y = row(h, residual=res)
             assert y.shape == (B, Tl, H), y.shape
             torch.manual_seed(5000 + it * 10 + rank)
             gy = (torch.randn_like(y.float()) * 0.1).to(y.dtype)
             y.backward(gy)
             outs.append([y.detach().float(), x.grad.float(), res.grad.float()] +
-                        [prm.grad.float().clone() for prm in list(col.Parameters()) + list(row.Parameters())])
+                        [prm.grad.float().clone() for prm in params])
         torch.cuda.synchronize()
         results[fused] = outs
         if fused == "1":
             assert symm._TP_CTX is not None, "fused tensor-parallel context was not created"
             assert symm._TP_CTX.nvl.status() == 0, symm._TP_CTX.nvl.status()
-            assert symm._TP_CTX.launch_index == 12, symm._TP_CTX.launch_index
+            assert symm._TP_CTX.launch_index == 18, symm._TP_CTX.launch_index
     worst = 0.0
-    names = ["y", "dx", "dres", "col.dw", "col.db", "row.dw", "row.db"]
+    names = ["y", "dx", "dres", "col.dw", "col.db", "col2.dw", "row.dw", "row.db"]
     for it, (a_it, b_it) in enumerate(zip(results["0"], results["1"])):
         for name, a, b in zip(names, a_it, b_it):
             rel = ((a - b).norm() / (a.norm() + 1e-6)).item()
