@@ -52,6 +52,10 @@ void kernel_status_reset() {
 int g_gemm_mode = 1;
 void set_gemm_mode(int64_t mode) { g_gemm_mode = static_cast<int>(mode); }
 int64_t get_gemm_mode() { return g_gemm_mode; }
+// 1: attention backward on tcgen05 (flash_attn_tc.cu); 0: the mma.sync kernel (flash_attn.cu).
+int g_attn_mode = 1;
+void set_attn_mode(int64_t mode) { g_attn_mode = static_cast<int>(mode); }
+int64_t get_attn_mode() { return g_attn_mode; }
 
 // C[M,N] = A . B^T-like product; see kernels.h for the layout flags.
 void gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, int64_t M, int64_t N,
@@ -420,7 +424,11 @@ void flash_attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tenso
   auto dq_accum = torch::empty({a.B, a.T, a.H, a.D}, f32);
   a.delta = delta.data_ptr<float>();
   a.dq_accum = dq_accum.data_ptr<float>();
-  check_rc(itb_flash_attn_bwd(&a, cur_stream()), "flash_attn_bwd");
+  if (g_attn_mode == 1)
+    check_rc(itb_flash_attn_bwd_tc(&a, status_word(q.get_device()).data_ptr<int>(), cur_stream()),
+             "flash_attn_bwd_tc");
+  else
+    check_rc(itb_flash_attn_bwd(&a, cur_stream()), "flash_attn_bwd");
 }
 
 }  // namespace
@@ -441,6 +449,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kernel_status_reset", &kernel_status_reset);
   m.def("gemm", &gemm);
   m.def("set_gemm_mode", &set_gemm_mode);
+  m.def("set_attn_mode", &set_attn_mode);
+  m.def("get_attn_mode", &get_attn_mode);
   m.def("get_gemm_mode", &get_gemm_mode);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);

@@ -79,6 +79,16 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* desc, ui
       : "r"(smem_u32(smem_dst)), "l"(desc), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// 3-D tiled load global -> shared, completion signalled on an mbarrier of this CTA.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* desc, uint64_t* bar,
+                                            int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(desc), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 // 2-D tiled store shared -> global (bulk group completion).
 __device__ __forceinline__ void tma_store_2d(const void* desc, const void* smem_src, int32_t x,
                                              int32_t y) {

@@ -1,0 +1,476 @@
+// Flash attention backward on the 5th-generation tensor cores (tcgen05, accumulators in TMEM,
+// operands staged by TMA), causal or full, grouped-query heads, head size 64 or 128.
+//
+// One CTA owns 128 keys of one KV head and walks over the 128-row query tiles (and the query heads
+// of the group) that attend to them.  Per tile, with n = key row, m = query row, d = head column:
+//
+//   S^T[n,m]  = K[n,:] . Q[m,:]            tcgen05.mma  K (K-major)  x Q (K-major)   -> TMEM cols 0..127
+//   dP^T[n,m] = V[n,:] . dO[m,:]           tcgen05.mma  V            x dO            -> TMEM cols 128..255
+//   P^T = exp2(S^T c - lse[m]),  dS^T = P^T (dP^T - delta[m])      256 threads, half a key row each;
+//                                          written as bf16 to shared memory in the swizzled operand layout
+//   dV[n,d] += P^T[n,m]  dO[m,d]           tcgen05.mma  P^T (K-major)  x dO (MN-major) -> TMEM cols 256..
+//   dK[n,d] += dS^T[n,m] Q[m,d]            tcgen05.mma  dS^T (K-major) x Q  (MN-major) -> TMEM cols 256+D..
+//   dQ[m,d]  = dS[m,n]   K[n,d]            tcgen05.mma  dS^T read MN-major x K (MN-major) -> TMEM, then added
+//                                          to the fp32 dQ buffer with vector reductions
+//
+// Warp roles: warp 0 issues the TMA loads, warp 1 the MMAs, warps 2-9 do the softmax recomputation
+// and the TMEM read-outs (two warps per TMEM lane quarter, each taking half of the columns).  With
+// head size 64 dQ has TMEM columns of its own, so S^T / dP^T of the next tile are computed while the
+// softmax warps still read dQ out; with head size 128 dQ overwrites the spent S^T.  Every wait is
+// bounded; a wait that gives up records a code in the status word and the CTA drains without
+// touching the tensor pipe again.
+//
+// The reference composes attention from batched cuBLAS matmuls, a mask and a 3-pass softmax and
+// lets autograd differentiate them (infini_train/src/nn/modules/transformer/causal_self_attention.cc:86-130).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "../common/ptx.cuh"
+#include "kernels.h"
+
+namespace itb {
+
+int make_tmap_bf16_3d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t d1, uint64_t d2,
+                      uint64_t ld1, uint64_t ld2, uint32_t box_inner, uint32_t box_d1);
+
+namespace fatc {
+
+constexpr int kThreads = 320;     // TMA warp, MMA warp, 8 softmax / read-out warps
+constexpr int kSoftmaxThreads = 256;
+constexpr int kAtom = 128 * 128;   // bytes of one [128 rows][64 x bf16] swizzled block
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void softmax_warps_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  uint4 u;
+  __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) b2[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+  return u;
+}
+
+template <int D>
+struct BwdCfg {
+  static constexpr int kAtoms = D / 64;
+  static constexpr int kTile = kAtoms * kAtom;          // one [128][D] bf16 tile
+  static constexpr int kQStages = D == 64 ? 2 : 1;
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kTile;
+  static constexpr int kOffQ = 2 * kTile;
+  static constexpr int kOffdO = kOffQ + kQStages * kTile;
+  static constexpr int kOffP = kOffdO + kQStages * kTile;    // [2 m-chunks][128 n][64 m]
+  static constexpr int kOffdS = kOffP + 2 * kAtom;
+  static constexpr int kOffStat = kOffdS + 2 * kAtom;        // lse*log2e [2][128], delta [2][128]
+  static constexpr int kOffBar = kOffStat + 4 * 128 * 4;
+  static constexpr int kSmem = kOffBar + 12 * 8 + 16;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                    const ItbAttnArgs a, int* err) {
+  using Cfg = BwdCfg<D>;
+  constexpr int S = Cfg::kQStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  float* s_lse = reinterpret_cast<float*>(smem + Cfg::kOffStat);
+  float* s_delta = s_lse + 2 * 128;
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
+  uint64_t* q_full = kv_full + 1;
+  uint64_t* q_empty = q_full + 2;
+  uint64_t* s_full = q_empty + 2;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* dq_full = p_full + 1;
+  uint64_t* dq_drained = dq_full + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(dq_drained + 1);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = a.H / a.KV;
+  const int n0 = nb * 128;
+  const int n_qblocks = (a.T + 127) / 128;
+  const int mb_first = a.causal ? nb : 0;
+  const int per_head = n_qblocks - mb_first;
+  const int iters = per_head * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, kSoftmaxThreads);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_drained, kSoftmaxThreads / 32);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tm_S = tmem_base, tm_dP = tmem_base + 128, tm_dV = tmem_base + 256, tm_dK = tmem_base + 256 + D;
+  constexpr bool kAlias = D > 64;     // no TMEM columns left for dQ: it goes over the spent S^T
+  const uint32_t tm_dQ = kAlias ? tmem_base : tmem_base + 256 + 2 * D;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tq);
+      tma_prefetch_desc(&tk);
+      tma_prefetch_desc(&tv);
+      tma_prefetch_desc(&tdo);
+      mbar_expect_tx(kv_full, 2 * Cfg::kTile);
+#pragma unroll
+      for (int at = 0; at < Cfg::kAtoms; ++at) {
+        tma_load_3d(smem + Cfg::kOffK + at * kAtom, &tk, kv_full, hk * D + at * 64, n0, b);
+        tma_load_3d(smem + Cfg::kOffV + at * kAtom, &tv, kv_full, hk * D + at * 64, n0, b);
+      }
+      for (int it = 0; it < iters; ++it) {
+        const int st = it % S;
+        const uint32_t ph = (it / S) & 1;
+        if (!mbar_wait(&q_empty[st], ph ^ 1) || *abort_flag) {
+          atomicCAS(err, 0, 201);
+          *abort_flag = 1;
+          break;
+        }
+        const int h = hk * G + it / per_head, mb = mb_first + it % per_head;
+        mbar_expect_tx(&q_full[st], 2 * Cfg::kTile);
+#pragma unroll
+        for (int at = 0; at < Cfg::kAtoms; ++at) {
+          tma_load_3d(smem + Cfg::kOffQ + st * Cfg::kTile + at * kAtom, &tq, &q_full[st], h * D + at * 64, mb * 128, b);
+          tma_load_3d(smem + Cfg::kOffdO + st * Cfg::kTile + at * kAtom, &tdo, &q_full[st], h * D + at * 64, mb * 128,
+                      b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t id_s = make_idesc_bf16_f32(128, 128, false, false);
+    constexpr uint32_t id_kv = make_idesc_bf16_f32(128, D, false, true);
+    constexpr uint32_t id_q = make_idesc_bf16_f32(128, D, true, true);
+    const uint32_t aK = smem_u32(smem + Cfg::kOffK), aV = smem_u32(smem + Cfg::kOffV);
+    const uint32_t aP = smem_u32(smem + Cfg::kOffP), adS = smem_u32(smem + Cfg::kOffdS);
+    bool ok = mbar_wait(kv_full, 0);
+    if (!ok && lane == 0) atomicCAS(err, 0, 202);
+    auto issue_scores = [&](int it) {     // S^T and dP^T of tile `it`
+      const int st = it % S;
+      const uint32_t aQ = smem_u32(smem + Cfg::kOffQ + st * Cfg::kTile);
+      const uint32_t adO = smem_u32(smem + Cfg::kOffdO + st * Cfg::kTile);
+      if (!mbar_wait(&q_full[st], (it / S) & 1) || *abort_flag) return false;
+      // with aliasing, dQ of the previous tile sits over S^T until the softmax warps have read it out
+      if (kAlias && it > 0 && (!mbar_wait(dq_drained, (it - 1) & 1) || *abort_flag)) return false;
+      tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kAtom + (kk & 3) * 32;
+          umma_f16_ss(tm_S, make_smem_desc_sw128(aK + off, 16, 1024), make_smem_desc_sw128(aQ + off, 16, 1024), id_s,
+                      kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kAtom + (kk & 3) * 32;
+          umma_f16_ss(tm_dP, make_smem_desc_sw128(aV + off, 16, 1024), make_smem_desc_sw128(adO + off, 16, 1024), id_s,
+                      kk > 0);
+        }
+        umma_commit(s_full);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok && iters > 0 && !issue_scores(0)) {
+      if (lane == 0) atomicCAS(err, 0, 203);
+      ok = false;
+    }
+    for (int it = 0; it < iters && ok; ++it) {
+      const int st = it % S;
+      const uint32_t aQ = smem_u32(smem + Cfg::kOffQ + st * Cfg::kTile);
+      const uint32_t adO = smem_u32(smem + Cfg::kOffdO + st * Cfg::kTile);
+      ok = mbar_wait(p_full, it & 1) && !*abort_flag;
+      // its own dQ columns are rewritten below: the previous tile's dQ must have been read out
+      if (ok && !kAlias && it > 0) ok = mbar_wait(dq_drained, (it - 1) & 1) && !*abort_flag;
+      if (!ok) {
+        if (lane == 0) atomicCAS(err, 0, 204);
+        break;
+      }
+      tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {       // contraction over the 128 query rows of the tile
+          const uint32_t koff = (kk >> 2) * kAtom + (kk & 3) * 32;   // K-major operand: P^T / dS^T
+          const uint32_t moff = kk * 2048;                            // MN-major operand: 16 rows down
+          umma_f16_ss(tm_dV, make_smem_desc_sw128(aP + koff, 16, 1024), make_smem_desc_sw128(adO + moff, kAtom, 1024),
+                      id_kv, (it > 0 || kk > 0));
+          umma_f16_ss(tm_dK, make_smem_desc_sw128(adS + koff, 16, 1024), make_smem_desc_sw128(aQ + moff, kAtom, 1024),
+                      id_kv, (it > 0 || kk > 0));
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {       // contraction over the 128 keys
+          const uint32_t moff = kk * 2048;
+          umma_f16_ss(tm_dQ, make_smem_desc_sw128(adS + moff, kAtom, 1024), make_smem_desc_sw128(aK + moff, kAtom, 1024),
+                      id_q, kk > 0);
+        }
+        umma_commit(&q_empty[st]);
+        umma_commit(dq_full);
+      }
+      __syncwarp();
+      if (it + 1 < iters && !issue_scores(it + 1)) {
+        if (lane == 0) atomicCAS(err, 0, 203);
+        ok = false;
+      }
+    }
+    if (!ok) *abort_flag = 1;
+  } else {
+    // ------------------------------------------------------------------ softmax / read-out warps
+    const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;           // which half of the columns this warp takes
+    const int row = qd * 32 + lane;             // key row (softmax) and query row (dQ read-out)
+    const uint32_t lane_addr = static_cast<uint32_t>(qd * 32) << 16;
+    const int tid = (warp - 2) * 32 + lane;     // 0..255, for the per-tile statistics
+    const float sl2 = a.scale * kLog2e;
+    uint8_t* sP = smem + Cfg::kOffP;
+    uint8_t* sdS = smem + Cfg::kOffdS;
+    bool ok = true;
+    // lse * log2(e) (threads 0..127) or delta (threads 128..255) of query row tid & 127 of tile `it`;
+    // rows beyond the sequence get probability 0 (lse = +inf) and delta 0
+    auto load_stat = [&](int it) -> float {
+      const int h = hk * G + it / per_head, mb = mb_first + it % per_head;
+      const int qrow = mb * 128 + (tid & 127);
+      const long long so = (static_cast<long long>(b) * a.H + h) * a.T + qrow;
+      if (tid < 128) return qrow < a.T ? __ldg(a.lse + so) * kLog2e : INFINITY;
+      return qrow < a.T ? __ldg(a.delta + so) : 0.f;
+    };
+    float stat_next = iters > 0 ? load_stat(0) : 0.f;
+    for (int it = 0; it < iters; ++it) {
+      const int h = hk * G + it / per_head, mb = mb_first + it % per_head;
+      const int sb = it & 1;
+      // this tile's statistics were fetched while the previous tile was being processed
+      if (tid < 128)
+        s_lse[sb * 128 + tid] = stat_next;
+      else
+        s_delta[sb * 128 + tid - 128] = stat_next;
+      if (it + 1 < iters) stat_next = load_stat(it + 1);
+      softmax_warps_sync();
+      if (ok) {
+        ok = mbar_wait(s_full, it & 1) && !*abort_flag;
+        if (!ok) {
+          atomicCAS(err, 0, 205);
+          *abort_flag = 1;
+        }
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        const bool diag = a.causal && mb == nb;
+        const bool key_ok = n0 + row < a.T;
+        const float* lse = s_lse + sb * 128;
+        const float* dl = s_delta + sb * 128;
+#pragma unroll 1
+        for (int cg = 2 * half; cg < 2 * half + 2; ++cg) {
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32(tm_S + lane_addr + cg * 32, rs);
+          tmem_ld_32x32(tm_dP + lane_addr + cg * 32, rp);
+          tmem_ld_wait();
+          float pv[32], dv[32];
+#pragma unroll
+          for (int j4 = 0; j4 < 32; j4 += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(lse + cg * 32 + j4);
+            const float4 d4 = *reinterpret_cast<const float4*>(dl + cg * 32 + j4);
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = j4 + e, m = cg * 32 + j;
+              float p = ex2(__uint_as_float(rs[j]) * sl2 - lv[e]);
+              if (!key_ok || (diag && row > m)) p = 0.f;
+              pv[j] = p;
+              dv[j] = p * (__uint_as_float(rp[j]) - dd[e]);
+            }
+          }
+          uint8_t* rowP = sP + (cg >> 1) * kAtom + row * 128;
+          uint8_t* rowS = sdS + (cg >> 1) * kAtom + row * 128;
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            const int pos = (((cg & 1) << 2) + c8) ^ (row & 7);
+            *reinterpret_cast<uint4*>(rowP + pos * 16) = pack8(&pv[c8 * 8]);
+            *reinterpret_cast<uint4*>(rowS + pos * 16) = pack8(&dv[c8 * 8]);
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
+        ok = mbar_wait(dq_full, it & 1) && !*abort_flag;
+        if (!ok) {
+          atomicCAS(err, 0, 206);
+          *abort_flag = 1;
+        }
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        const int qrow = mb * 128 + row;
+        float* dqg = a.dq_accum + ((static_cast<long long>(b) * a.T + qrow) * a.H + h) * D;
+#pragma unroll 1
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tm_dQ + lane_addr + c * 32, r);
+          tmem_ld_wait();
+          if (qrow < a.T) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dqg + c * 32 + j),
+                           "f"(__uint_as_float(r[j]) * a.scale), "f"(__uint_as_float(r[j + 1]) * a.scale),
+                           "f"(__uint_as_float(r[j + 2]) * a.scale), "f"(__uint_as_float(r[j + 3]) * a.scale)
+                           : "memory");
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_drained);
+      }
+    }
+    if (ok) {
+      // dK (scaled) and dV of this CTA's 128 keys; the last dq_full covered the MMAs that wrote them
+      const int krow = n0 + row;
+      __nv_bfloat16* dkg = static_cast<__nv_bfloat16*>(a.dk) + b * a.k_batch_stride +
+                           static_cast<long long>(krow) * a.k_row_stride + hk * D;
+      __nv_bfloat16* dvg = static_cast<__nv_bfloat16*>(a.dv) + b * a.v_batch_stride +
+                           static_cast<long long>(krow) * a.v_row_stride + hk * D;
+#pragma unroll 1
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        uint32_t rk[32], rv[32];
+        tmem_ld_32x32(tm_dK + lane_addr + c * 32, rk);
+        tmem_ld_32x32(tm_dV + lane_addr + c * 32, rv);
+        tmem_ld_wait();
+        if (krow < a.T) {
+          float fk[32], fv[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            fk[j] = __uint_as_float(rk[j]) * a.scale;
+            fv[j] = __uint_as_float(rv[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            *reinterpret_cast<uint4*>(dkg + c * 32 + j) = pack8(&fk[j]);
+            *reinterpret_cast<uint4*>(dvg + c * 32 + j) = pack8(&fv[j]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+__global__ void attn_delta_tc_kernel(const ItbAttnArgs a, int D) {
+  // delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per (b,t,h)
+  const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(a.B) * a.T * a.H;
+  if (w >= total) return;
+  const int h = static_cast<int>(w % a.H);
+  const long long bt = w / a.H;
+  const int t = static_cast<int>(bt % a.T), b = static_cast<int>(bt / a.T);
+  const __nv_bfloat16* o = static_cast<const __nv_bfloat16*>(a.o) + b * a.o_batch_stride +
+                           static_cast<long long>(t) * a.o_row_stride + h * D;
+  const __nv_bfloat16* d = static_cast<const __nv_bfloat16*>(a.dout) + b * a.o_batch_stride +
+                           static_cast<long long>(t) * a.o_row_stride + h * D;
+  float acc = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(o + i);
+    const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(d + i);
+    acc += __bfloat162float(x.x) * __bfloat162float(y.x) + __bfloat162float(x.y) * __bfloat162float(y.y);
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) a.delta[(static_cast<long long>(b) * a.H + h) * a.T + t] = acc;
+}
+
+__global__ void attn_dq_convert_tc_kernel(const ItbAttnArgs a, int D) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;  // 4 elements each
+  const int dv = D / 4;
+  const long long total = static_cast<long long>(a.B) * a.T * a.H * dv;
+  if (i >= total) return;
+  const int c = static_cast<int>(i % dv) * 4;
+  long long r = i / dv;
+  const int h = static_cast<int>(r % a.H);
+  r /= a.H;
+  const int t = static_cast<int>(r % a.T), b = static_cast<int>(r / a.T);
+  const float4 v = *reinterpret_cast<const float4*>(a.dq_accum + i * 4);
+  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.dq) + b * a.q_batch_stride +
+                       static_cast<long long>(t) * a.q_row_stride + h * D + c;
+  uint2 u;
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  u.x = *reinterpret_cast<uint32_t*>(&lo);
+  u.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = u;
+}
+
+template <int D>
+static int bwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
+  using Cfg = BwdCfg<D>;
+  constexpr int smem = Cfg::kSmem + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  int rc = make_tmap_bf16_3d(&tq, a->q, static_cast<uint64_t>(a->H) * D, a->T, a->B, a->q_row_stride,
+                             a->q_batch_stride, 64, 128);
+  if (!rc) rc = make_tmap_bf16_3d(&tk, a->k, static_cast<uint64_t>(a->KV) * D, a->T, a->B, a->k_row_stride,
+                                  a->k_batch_stride, 64, 128);
+  if (!rc) rc = make_tmap_bf16_3d(&tv, a->v, static_cast<uint64_t>(a->KV) * D, a->T, a->B, a->v_row_stride,
+                                  a->v_batch_stride, 64, 128);
+  if (!rc) rc = make_tmap_bf16_3d(&tdo, a->dout, static_cast<uint64_t>(a->H) * D, a->T, a->B, a->o_row_stride,
+                                  a->o_batch_stride, 64, 128);
+  if (rc) return rc;
+  const long long nrow = static_cast<long long>(a->B) * a->T * a->H;
+  cudaError_t e = cudaMemsetAsync(a->dq_accum, 0, nrow * D * sizeof(float), s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  attn_delta_tc_kernel<<<static_cast<int>((nrow * 32 + 255) / 256), 256, 0, s>>>(*a, D);
+  dim3 grid((a->T + 127) / 128, a->KV, a->B);
+  flash_bwd_tc_kernel<D><<<grid, kThreads, smem, s>>>(tq, tk, tv, tdo, *a, err);
+  const long long nvec = nrow * (D / 4);
+  attn_dq_convert_tc_kernel<<<static_cast<int>((nvec + 255) / 256), 256, 0, s>>>(*a, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace fatc
+}  // namespace itb
+
+extern "C" int itb_flash_attn_bwd_tc(const ItbAttnArgs* a, int* err, cudaStream_t s) {
+  if (a->B <= 0 || a->T <= 0) return 0;
+  if (a->H % a->KV) return -3;
+  if ((a->q_row_stride | a->k_row_stride | a->v_row_stride | a->o_row_stride | a->q_batch_stride |
+       a->k_batch_stride | a->v_batch_stride | a->o_batch_stride) & 7)
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
+       reinterpret_cast<uintptr_t>(a->o) | reinterpret_cast<uintptr_t>(a->dq) | reinterpret_cast<uintptr_t>(a->dk) |
+       reinterpret_cast<uintptr_t>(a->dv) | reinterpret_cast<uintptr_t>(a->dout)) & 15)
+    return -2;
+  if (a->D == 64) return itb::fatc::bwd_launch<64>(a, err, s);
+  if (a->D == 128) return itb::fatc::bwd_launch<128>(a, err, s);
+  return -4;
+}
