@@ -52,7 +52,8 @@ void kernel_status_reset() {
 int g_gemm_mode = 1;
 void set_gemm_mode(int64_t mode) { g_gemm_mode = static_cast<int>(mode); }
 int64_t get_gemm_mode() { return g_gemm_mode; }
-// 1: attention backward on tcgen05 (flash_attn_tc.cu); 0: the mma.sync kernel (flash_attn.cu).
+// bit 0: attention backward on tcgen05, bit 1: attention forward on tcgen05 (flash_attn_tc.cu);
+// a cleared bit selects the mma.sync kernel of flash_attn.cu for that pass.
 int g_attn_mode = 1;
 void set_attn_mode(int64_t mode) { g_attn_mode = static_cast<int>(mode); }
 int64_t get_attn_mode() { return g_attn_mode; }
@@ -398,7 +399,11 @@ std::vector<at::Tensor> flash_attn_fwd(const at::Tensor& q, const at::Tensor& k,
   a.o_row_stride = o.stride(1);
   a.o_batch_stride = o.stride(0);
   a.lse = lse.data_ptr<float>();
-  check_rc(itb_flash_attn_fwd(&a, cur_stream()), "flash_attn_fwd");
+  if (g_attn_mode & 2)
+    check_rc(itb_flash_attn_fwd_tc(&a, status_word(q.get_device()).data_ptr<int>(), cur_stream()),
+             "flash_attn_fwd_tc");
+  else
+    check_rc(itb_flash_attn_fwd(&a, cur_stream()), "flash_attn_fwd");
   return {o, lse};
 }
 // dq/dk/dv are written into caller-provided views (e.g. column blocks of one packed dqkv buffer).
@@ -424,7 +429,7 @@ void flash_attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tenso
   auto dq_accum = torch::empty({a.B, a.T, a.H, a.D}, f32);
   a.delta = delta.data_ptr<float>();
   a.dq_accum = dq_accum.data_ptr<float>();
-  if (g_attn_mode == 1)
+  if (g_attn_mode & 1)
     check_rc(itb_flash_attn_bwd_tc(&a, status_word(q.get_device()).data_ptr<int>(), cur_stream()),
              "flash_attn_bwd_tc");
   else

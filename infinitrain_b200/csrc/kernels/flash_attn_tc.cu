@@ -1,7 +1,7 @@
-// Flash attention backward on the 5th-generation tensor cores (tcgen05, accumulators in TMEM,
-// operands staged by TMA), causal or full, grouped-query heads, head size 64 or 128.
+// Flash attention forward and backward on the 5th-generation tensor cores (tcgen05, accumulators
+// in TMEM, operands staged by TMA), causal or full, grouped-query heads, head size 64 or 128.
 //
-// One CTA owns 128 keys of one KV head and walks over the 128-row query tiles (and the query heads
+// Backward: one CTA owns 128 keys of one KV head and walks over the 128-row query tiles (and the query heads
 // of the group) that attend to them.  Per tile, with n = key row, m = query row, d = head column:
 //
 //   S^T[n,m]  = K[n,:] . Q[m,:]            tcgen05.mma  K (K-major)  x Q (K-major)   -> TMEM cols 0..127
@@ -25,6 +25,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <float.h>
 #include <math.h>
 #include <stdint.h>
 
@@ -382,6 +383,302 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------------------ forward
+// One CTA owns 128 query rows of one head and walks over the 128-key tiles up to the diagonal:
+//   S[m,n] = Q[m,:] . K[n,:]     tcgen05.mma  Q (K-major) x K (K-major)          -> TMEM cols 0..127
+//   online softmax: two threads per query row (64 keys each), row maximum exchanged through shared
+//   memory, P written as bf16 in the swizzled operand layout
+//   O_j[m,d] = P[m,n] V[n,d]     tcgen05.mma  P (K-major) x V (MN-major)         -> TMEM cols 128..
+//   o = o * exp2(m_old - m_new) + O_j   in registers (each thread keeps half of the head columns)
+template <int D>
+struct FwdCfg {
+  static constexpr int kAtoms = D / 64;
+  static constexpr int kTile = kAtoms * kAtom;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = kTile;
+  static constexpr int kOffV = 2 * kTile;
+  static constexpr int kOffP = 3 * kTile;                 // [2 n-chunks][128 m][64 n]
+  static constexpr int kOffStat = kOffP + 2 * kAtom;      // row maxima [2 buffers][2 halves][128], sums [2][128]
+  static constexpr int kOffBar = kOffStat + 6 * 128 * 4;
+  static constexpr int kSmem = kOffBar + 12 * 8 + 16;
+  static constexpr int kTmemCols = 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                    const __grid_constant__ CUtensorMap tv, const ItbAttnArgs a, int* err) {
+  using Cfg = FwdCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  float* s_max = reinterpret_cast<float*>(smem + Cfg::kOffStat);   // [2][2][128]
+  float* s_sum = s_max + 4 * 128;                                   // [2][128]
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
+  uint64_t* k_full = q_full + 1;
+  uint64_t* k_empty = k_full + 1;
+  uint64_t* v_full = k_empty + 1;
+  uint64_t* v_empty = v_full + 1;
+  uint64_t* s_full = v_empty + 1;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* o_full = p_full + 1;
+  uint64_t* o_drained = o_full + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_drained + 1);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heavier (later) query tiles first, so that the tail of the grid is made of short CTAs
+  const int mb = a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (a.H / a.KV);
+  const int m0 = mb * 128;
+  int n_blocks = (a.T + 127) / 128;
+  if (a.causal) n_blocks = min(n_blocks, mb + 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, kSoftmaxThreads);
+    mbar_init(o_full, 1);
+    mbar_init(o_drained, kSoftmaxThreads / 32);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tm_S = tmem_base, tm_O = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tq);
+      tma_prefetch_desc(&tk);
+      tma_prefetch_desc(&tv);
+      mbar_expect_tx(q_full, Cfg::kTile);
+#pragma unroll
+      for (int at = 0; at < Cfg::kAtoms; ++at)
+        tma_load_3d(smem + Cfg::kOffQ + at * kAtom, &tq, q_full, h * D + at * 64, m0, b);
+      for (int j = 0; j < n_blocks; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(k_empty, ph ^ 1) || *abort_flag) {
+          atomicCAS(err, 0, 211);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(k_full, Cfg::kTile);
+#pragma unroll
+        for (int at = 0; at < Cfg::kAtoms; ++at)
+          tma_load_3d(smem + Cfg::kOffK + at * kAtom, &tk, k_full, hk * D + at * 64, j * 128, b);
+        if (!mbar_wait(v_empty, ph ^ 1) || *abort_flag) {
+          atomicCAS(err, 0, 212);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(v_full, Cfg::kTile);
+#pragma unroll
+        for (int at = 0; at < Cfg::kAtoms; ++at)
+          tma_load_3d(smem + Cfg::kOffV + at * kAtom, &tv, v_full, hk * D + at * 64, j * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t id_s = make_idesc_bf16_f32(128, 128, false, false);
+    constexpr uint32_t id_o = make_idesc_bf16_f32(128, D, false, true);
+    const uint32_t aQ = smem_u32(smem + Cfg::kOffQ), aK = smem_u32(smem + Cfg::kOffK);
+    const uint32_t aV = smem_u32(smem + Cfg::kOffV), aP = smem_u32(smem + Cfg::kOffP);
+    auto issue_scores = [&](int j) {
+      if (!mbar_wait(k_full, j & 1) || *abort_flag) return false;
+      tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kAtom + (kk & 3) * 32;
+          umma_f16_ss(tm_S, make_smem_desc_sw128(aQ + off, 16, 1024), make_smem_desc_sw128(aK + off, 16, 1024), id_s,
+                      kk > 0);
+        }
+        umma_commit(k_empty);
+        umma_commit(s_full);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = mbar_wait(q_full, 0);
+    if (ok && n_blocks > 0) ok = issue_scores(0);
+    if (!ok && lane == 0) atomicCAS(err, 0, 213);
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      ok = mbar_wait(p_full, j & 1) && !*abort_flag;
+      if (ok && j > 0) ok = mbar_wait(o_drained, (j - 1) & 1) && !*abort_flag;
+      if (ok) ok = mbar_wait(v_full, j & 1) && !*abort_flag;
+      if (!ok) {
+        if (lane == 0) atomicCAS(err, 0, 214);
+        break;
+      }
+      tc_fence_after_sync();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {       // contraction over the 128 keys of the tile
+          const uint32_t koff = (kk >> 2) * kAtom + (kk & 3) * 32;
+          umma_f16_ss(tm_O, make_smem_desc_sw128(aP + koff, 16, 1024), make_smem_desc_sw128(aV + kk * 2048, kAtom, 1024),
+                      id_o, kk > 0);
+        }
+        umma_commit(v_empty);
+        umma_commit(o_full);
+      }
+      __syncwarp();
+      if (j + 1 < n_blocks && !issue_scores(j + 1)) {
+        if (lane == 0) atomicCAS(err, 0, 213);
+        ok = false;
+      }
+    }
+    if (!ok) *abort_flag = 1;
+  } else {
+    const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = qd * 32 + lane;                 // query row of the tile
+    const uint32_t lane_addr = static_cast<uint32_t>(qd * 32) << 16;
+    const float sl2 = a.scale * kLog2e;
+    constexpr int kOC = D / 2;                      // head columns this thread accumulates
+    float o[kOC];
+#pragma unroll
+    for (int i = 0; i < kOC; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;           // running maximum (scaled, log2 domain) and sum
+    uint8_t* rowP = smem + Cfg::kOffP + half * kAtom + row * 128;
+    bool ok = true;
+    for (int j = 0; j < n_blocks; ++j) {
+      float sv[64];
+      float mx = -INFINITY;
+      if (ok) {
+        ok = mbar_wait(s_full, j & 1) && !*abort_flag;
+        if (!ok) {
+          atomicCAS(err, 0, 215);
+          *abort_flag = 1;
+        }
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        const bool diag = a.causal && j == mb;
+        const bool tail = (j + 1) * 128 > a.T;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tm_S + lane_addr + half * 64 + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int n = half * 64 + c * 32 + i;
+            float v = __uint_as_float(r[i]) * sl2;
+            if ((diag && n > row) || (tail && j * 128 + n >= a.T)) v = -INFINITY;
+            sv[c * 32 + i] = v;
+            mx = fmaxf(mx, v);
+          }
+        }
+      }
+      s_max[((j & 1) * 2 + half) * 128 + row] = mx;
+      softmax_warps_sync();
+      if (ok) {
+        const float other = s_max[((j & 1) * 2 + (half ^ 1)) * 128 + row];
+        const float m_new = fmaxf(m_run, fmaxf(mx, other));
+        // a row with no visible key so far keeps -inf: use 0 as the base so that exp2 yields 0, not NaN
+        const float base = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = ex2(m_run - base);
+        float sum = 0.f;
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+          float pv[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            pv[e] = ex2(sv[c8 * 8 + e] - base);
+            sum += pv[e];
+          }
+          *reinterpret_cast<uint4*>(rowP + ((c8 ^ (row & 7)) << 4)) = pack8(pv);
+        }
+        l_run = l_run * corr + sum;
+        m_run = m_new;
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
+        ok = mbar_wait(o_full, j & 1) && !*abort_flag;
+        if (!ok) {
+          atomicCAS(err, 0, 216);
+          *abort_flag = 1;
+        }
+        if (ok) {
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < kOC / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tm_O + lane_addr + half * kOC + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr + __uint_as_float(r[i]);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(o_drained);
+        }
+      }
+    }
+    // the two halves of a row add their sums
+    s_sum[half * 128 + row] = l_run;
+    softmax_warps_sync();
+    const int qrow = m0 + row;
+    if (ok && qrow < a.T) {
+      const float l = l_run + s_sum[(half ^ 1) * 128 + row];
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.o) + b * a.o_batch_stride +
+                          static_cast<long long>(qrow) * a.o_row_stride + h * D + half * kOC;
+#pragma unroll
+      for (int i = 0; i < kOC; i += 8) {
+        float t[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) t[e] = o[i + e] * inv;
+        *reinterpret_cast<uint4*>(op + i) = pack8(t);
+      }
+      if (half == 0)
+        a.lse[(static_cast<long long>(b) * a.H + h) * a.T + qrow] =
+            l > 0.f ? m_run * 0.6931471805599453f + logf(l) : -FLT_MAX;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int D>
+static int fwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
+  using Cfg = FwdCfg<D>;
+  constexpr int smem = Cfg::kSmem + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  CUtensorMap tq, tk, tv;
+  int rc = make_tmap_bf16_3d(&tq, a->q, static_cast<uint64_t>(a->H) * D, a->T, a->B, a->q_row_stride,
+                             a->q_batch_stride, 64, 128);
+  if (!rc) rc = make_tmap_bf16_3d(&tk, a->k, static_cast<uint64_t>(a->KV) * D, a->T, a->B, a->k_row_stride,
+                                  a->k_batch_stride, 64, 128);
+  if (!rc) rc = make_tmap_bf16_3d(&tv, a->v, static_cast<uint64_t>(a->KV) * D, a->T, a->B, a->v_row_stride,
+                                  a->v_batch_stride, 64, 128);
+  if (rc) return rc;
+  dim3 grid((a->T + 127) / 128, a->H, a->B);
+  flash_fwd_tc_kernel<D><<<grid, kThreads, smem, s>>>(tq, tk, tv, *a, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
 __global__ void attn_delta_tc_kernel(const ItbAttnArgs a, int D) {
   // delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per (b,t,h)
   const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
@@ -472,5 +769,19 @@ extern "C" int itb_flash_attn_bwd_tc(const ItbAttnArgs* a, int* err, cudaStream_
     return -2;
   if (a->D == 64) return itb::fatc::bwd_launch<64>(a, err, s);
   if (a->D == 128) return itb::fatc::bwd_launch<128>(a, err, s);
+  return -4;
+}
+
+extern "C" int itb_flash_attn_fwd_tc(const ItbAttnArgs* a, int* err, cudaStream_t s) {
+  if (a->B <= 0 || a->T <= 0) return 0;
+  if (a->H % a->KV) return -3;
+  if ((a->q_row_stride | a->k_row_stride | a->v_row_stride | a->o_row_stride | a->q_batch_stride |
+       a->k_batch_stride | a->v_batch_stride | a->o_batch_stride) & 7)
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(a->q) | reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
+       reinterpret_cast<uintptr_t>(a->o)) & 15)
+    return -2;
+  if (a->D == 64) return itb::fatc::fwd_launch<64>(a, err, s);
+  if (a->D == 128) return itb::fatc::fwd_launch<128>(a, err, s);
   return -4;
 }

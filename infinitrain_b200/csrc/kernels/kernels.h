@@ -157,6 +157,7 @@ int itb_flash_attn_bwd(const ItbAttnArgs* args, cudaStream_t stream);
 // Same contract on the tcgen05 tensor cores (128 x 128 tiles, accumulators in TMEM, TMA operands).
 // `err` is a device status word (zero before the launch) that receives a code when a wait gives up.
 int itb_flash_attn_bwd_tc(const ItbAttnArgs* args, int* err, cudaStream_t stream);
+int itb_flash_attn_fwd_tc(const ItbAttnArgs* args, int* err, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -268,11 +268,12 @@ def _attn_ref(q, k, v, causal):
     return torch.einsum("bhts,bshd->bthd", p, vf)
 
 
-@pytest.mark.parametrize("attn_mode", [1, 0], ids=["tcgen05_bwd", "mma_sync_bwd"])
+@pytest.mark.parametrize("attn_mode", [3, 0], ids=["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("B,T,H,KV,D", [(2, 128, 4, 4, 64), (1, 200, 4, 2, 64), (2, 96, 8, 2, 128),
                                          (1, 1024, 2, 2, 64), (2, 384, 8, 2, 128)])
 def test_flash_attention(C, B, T, H, KV, D, attn_mode):
     torch.manual_seed(11)
+    default_mode = C.get_attn_mode()
     C.set_attn_mode(attn_mode)
     qkv = torch.randn(B, T, (H + 2 * KV) * D, device="cuda").bfloat16()
     q = qkv[..., : H * D].view(B, T, H, D)
@@ -289,7 +290,7 @@ def test_flash_attention(C, B, T, H, KV, D, attn_mode):
     dk = dqkv[..., H * D : (H + KV) * D].view(B, T, KV, D)
     dv = dqkv[..., (H + KV) * D :].view(B, T, KV, D)
     C.flash_attn_bwd(dout, q, k, v, o, lse, dq, dk, dv, 1.0 / math.sqrt(D), True)
-    C.set_attn_mode(1)
+    C.set_attn_mode(default_mode)
     assert C.kernel_status() == 0
     assert _rel(dv, vr.grad) < 3e-2
     assert _rel(dk, kr.grad) < 3e-2
