@@ -279,8 +279,10 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       }
       if (ok) {
         tc_fence_after_sync();
-        const bool diag = a.causal && mb == nb;
         const bool key_ok = n0 + row < a.T;
+        // the mask matters on the diagonal tile and for the keys beyond the sequence only
+        const bool diag = a.causal && mb == nb;
+        const bool need_mask = diag || (n0 + 128 > a.T);
         const float* lse = s_lse + sb * 128;
         const float* dl = s_delta + sb * 128;
 #pragma unroll 1
@@ -298,8 +300,8 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int j = j4 + e, m = cg * 32 + j;
-              float p = ex2(__uint_as_float(rs[j]) * sl2 - lv[e]);
-              if (!key_ok || (diag && row > m)) p = 0.f;
+              float p = ex2(fmaf(__uint_as_float(rs[j]), sl2, -lv[e]));
+              if (need_mask && (!key_ok || (diag && row > m))) p = 0.f;
               pv[j] = p;
               dv[j] = p * (__uint_as_float(rp[j]) - dd[e]);
             }
@@ -386,10 +388,12 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 // ------------------------------------------------------------------------------------ forward
 // One CTA owns 128 query rows of one head and walks over the 128-key tiles up to the diagonal:
 //   S[m,n] = Q[m,:] . K[n,:]     tcgen05.mma  Q (K-major) x K (K-major)          -> TMEM cols 0..127
-//   online softmax: two threads per query row (64 keys each), row maximum exchanged through shared
-//   memory, P written as bf16 in the swizzled operand layout
+//   online softmax: one thread per query row reads its row of S from TMEM twice (maximum, then
+//   exponentials), so nothing crosses threads; P is written as bf16 in the swizzled operand layout
 //   O_j[m,d] = P[m,n] V[n,d]     tcgen05.mma  P (K-major) x V (MN-major)         -> TMEM cols 128..
-//   o = o * exp2(m_old - m_new) + O_j   in registers (each thread keeps half of the head columns)
+//   o = o * exp2(m_old - m_new) + O_j   in registers
+// 192 threads (TMA warp, MMA warp, 4 softmax warps) and 80 KB of shared memory at head size 64, so
+// two CTAs share an SM and one's tensor-core and TMA latencies hide behind the other's softmax.
 template <int D>
 struct FwdCfg {
   static constexpr int kAtoms = D / 64;
@@ -398,22 +402,20 @@ struct FwdCfg {
   static constexpr int kOffK = kTile;
   static constexpr int kOffV = 2 * kTile;
   static constexpr int kOffP = 3 * kTile;                 // [2 n-chunks][128 m][64 n]
-  static constexpr int kOffStat = kOffP + 2 * kAtom;      // row maxima [2 buffers][2 halves][128], sums [2][128]
-  static constexpr int kOffBar = kOffStat + 6 * 128 * 4;
+  static constexpr int kOffBar = kOffP + 2 * kAtom;
   static constexpr int kSmem = kOffBar + 12 * 8 + 16;
   static constexpr int kTmemCols = 256;
 };
+constexpr int kFwdThreads = 192;
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kFwdThreads, D == 64 ? 2 : 1)
 flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                     const __grid_constant__ CUtensorMap tv, const ItbAttnArgs a, int* err) {
   using Cfg = FwdCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  float* s_max = reinterpret_cast<float*>(smem + Cfg::kOffStat);   // [2][2][128]
-  float* s_sum = s_max + 4 * 128;                                   // [2][128]
   uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
   uint64_t* k_full = q_full + 1;
   uint64_t* k_empty = k_full + 1;
@@ -442,9 +444,9 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
-    mbar_init(p_full, kSoftmaxThreads);
+    mbar_init(p_full, 128);
     mbar_init(o_full, 1);
-    mbar_init(o_drained, kSoftmaxThreads / 32);
+    mbar_init(o_drained, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -541,110 +543,103 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     if (!ok) *abort_flag = 1;
   } else {
     const int qd = warp & 3;
-    const int half = (warp - 2) >> 2;
     const int row = qd * 32 + lane;                 // query row of the tile
     const uint32_t lane_addr = static_cast<uint32_t>(qd * 32) << 16;
     const float sl2 = a.scale * kLog2e;
-    constexpr int kOC = D / 2;                      // head columns this thread accumulates
-    float o[kOC];
+    float o[D];
 #pragma unroll
-    for (int i = 0; i < kOC; ++i) o[i] = 0.f;
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;           // running maximum (scaled, log2 domain) and sum
-    uint8_t* rowP = smem + Cfg::kOffP + half * kAtom + row * 128;
+    uint8_t* rowP = smem + Cfg::kOffP + row * 128;
     bool ok = true;
-    for (int j = 0; j < n_blocks; ++j) {
-      float sv[64];
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      ok = mbar_wait(s_full, j & 1) && !*abort_flag;
+      if (!ok) {
+        atomicCAS(err, 0, 215);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      // only the diagonal tile and a ragged last tile need the mask
+      const bool masked = (a.causal && j == mb) || ((j + 1) * 128 > a.T);
+      const int n_lim = masked ? min(a.causal && j == mb ? row + 1 : 128, a.T - j * 128) : 128;   // keys [0, n_lim) visible
       float mx = -INFINITY;
-      if (ok) {
-        ok = mbar_wait(s_full, j & 1) && !*abort_flag;
-        if (!ok) {
-          atomicCAS(err, 0, 215);
-          *abort_flag = 1;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tm_S + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        if (!masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < n_lim) mx = fmaxf(mx, __uint_as_float(r[i]));
         }
       }
-      if (ok) {
-        tc_fence_after_sync();
-        const bool diag = a.causal && j == mb;
-        const bool tail = (j + 1) * 128 > a.T;
+      mx *= sl2;      // sl2 > 0: scaling commutes with the maximum
+      const float m_new = fmaxf(m_run, mx);
+      // a row with no visible key so far keeps -inf: use 0 as the base so that exp2 yields 0, not NaN
+      const float base = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = ex2(m_run - base);
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tm_S + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        float pv[32];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tm_S + lane_addr + half * 64 + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int n = half * 64 + c * 32 + i;
-            float v = __uint_as_float(r[i]) * sl2;
-            if ((diag && n > row) || (tail && j * 128 + n >= a.T)) v = -INFINITY;
-            sv[c * 32 + i] = v;
-            mx = fmaxf(mx, v);
-          }
+        for (int i = 0; i < 32; ++i) {
+          float p = ex2(fmaf(__uint_as_float(r[i]), sl2, -base));
+          if (masked && c * 32 + i >= n_lim) p = 0.f;
+          pv[i] = p;
+          sum += p;
         }
+        uint8_t* dst = rowP + (c >> 1) * kAtom;
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8)
+          *reinterpret_cast<uint4*>(dst + (((((c & 1) << 2) + c8) ^ (row & 7)) << 4)) = pack8(&pv[c8 * 8]);
       }
-      s_max[((j & 1) * 2 + half) * 128 + row] = mx;
-      softmax_warps_sync();
-      if (ok) {
-        const float other = s_max[((j & 1) * 2 + (half ^ 1)) * 128 + row];
-        const float m_new = fmaxf(m_run, fmaxf(mx, other));
-        // a row with no visible key so far keeps -inf: use 0 as the base so that exp2 yields 0, not NaN
-        const float base = m_new == -INFINITY ? 0.f : m_new;
-        const float corr = ex2(m_run - base);
-        float sum = 0.f;
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          float pv[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            pv[e] = ex2(sv[c8 * 8 + e] - base);
-            sum += pv[e];
-          }
-          *reinterpret_cast<uint4*>(rowP + ((c8 ^ (row & 7)) << 4)) = pack8(pv);
-        }
-        l_run = l_run * corr + sum;
-        m_run = m_new;
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        mbar_arrive(p_full);
-        ok = mbar_wait(o_full, j & 1) && !*abort_flag;
-        if (!ok) {
-          atomicCAS(err, 0, 216);
-          *abort_flag = 1;
-        }
-        if (ok) {
-          tc_fence_after_sync();
-#pragma unroll
-          for (int c = 0; c < kOC / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(tm_O + lane_addr + half * kOC + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr + __uint_as_float(r[i]);
-          }
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(o_drained);
-        }
+      l_run = l_run * corr + sum;
+      m_run = m_new;
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+      ok = mbar_wait(o_full, j & 1) && !*abort_flag;
+      if (!ok) {
+        atomicCAS(err, 0, 216);
+        *abort_flag = 1;
+        break;
       }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tm_O + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(r[i]));
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_drained);
     }
-    // the two halves of a row add their sums
-    s_sum[half * 128 + row] = l_run;
-    softmax_warps_sync();
     const int qrow = m0 + row;
     if (ok && qrow < a.T) {
-      const float l = l_run + s_sum[(half ^ 1) * 128 + row];
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* op = static_cast<__nv_bfloat16*>(a.o) + b * a.o_batch_stride +
-                          static_cast<long long>(qrow) * a.o_row_stride + h * D + half * kOC;
+                          static_cast<long long>(qrow) * a.o_row_stride + h * D;
 #pragma unroll
-      for (int i = 0; i < kOC; i += 8) {
+      for (int i = 0; i < D; i += 8) {
         float t[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) t[e] = o[i + e] * inv;
         *reinterpret_cast<uint4*>(op + i) = pack8(t);
       }
-      if (half == 0)
-        a.lse[(static_cast<long long>(b) * a.H + h) * a.T + qrow] =
-            l > 0.f ? m_run * 0.6931471805599453f + logf(l) : -FLT_MAX;
+      a.lse[(static_cast<long long>(b) * a.H + h) * a.T + qrow] =
+          l_run > 0.f ? m_run * 0.6931471805599453f + logf(l_run) : -FLT_MAX;
     }
   }
 
@@ -675,7 +670,7 @@ static int fwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
                                   a->v_batch_stride, 64, 128);
   if (rc) return rc;
   dim3 grid((a->T + 127) / 128, a->H, a->B);
-  flash_fwd_tc_kernel<D><<<grid, kThreads, smem, s>>>(tq, tk, tv, *a, err);
+  flash_fwd_tc_kernel<D><<<grid, kFwdThreads, smem, s>>>(tq, tk, tv, *a, err);
   return static_cast<int>(cudaGetLastError());
 }
 
