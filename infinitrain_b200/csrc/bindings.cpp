@@ -54,7 +54,7 @@ void set_gemm_mode(int64_t mode) { g_gemm_mode = static_cast<int>(mode); }
 int64_t get_gemm_mode() { return g_gemm_mode; }
 // bit 0: attention backward on tcgen05, bit 1: attention forward on tcgen05 (flash_attn_tc.cu);
 // a cleared bit selects the mma.sync kernel of flash_attn.cu for that pass.
-int g_attn_mode = 1;
+int g_attn_mode = 3;
 void set_attn_mode(int64_t mode) { g_attn_mode = static_cast<int>(mode); }
 int64_t get_attn_mode() { return g_attn_mode; }
 

@@ -105,6 +105,14 @@ __device__ __forceinline__ void tma_reduce_add_2d(const void* desc, const void* 
                : "l"(desc), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// 3-D flavour of the add-reduction.
+__device__ __forceinline__ void tma_reduce_add_3d(const void* desc, const void* smem_src, int32_t x,
+                                                  int32_t y, int32_t z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               :
+               : "l"(desc), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

@@ -37,6 +37,9 @@ namespace itb {
 int make_tmap_bf16_3d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t d1, uint64_t d2,
                       uint64_t ld1, uint64_t ld2, uint32_t box_inner, uint32_t box_d1);
 
+int make_tmap_f32_3d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t d1, uint64_t d2,
+                     uint64_t ld1, uint64_t ld2, uint32_t box_d1);
+
 namespace fatc {
 
 constexpr int kThreads = 320;     // TMA warp, MMA warp, 8 softmax / read-out warps
@@ -79,7 +82,7 @@ template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                     const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
-                    const ItbAttnArgs a, int* err) {
+                    const __grid_constant__ CUtensorMap tdq, const ItbAttnArgs a, int* err) {
   using Cfg = BwdCfg<D>;
   constexpr int S = Cfg::kQStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -169,28 +172,33 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     constexpr uint32_t id_q = make_idesc_bf16_f32(128, D, true, true);
     const uint32_t aK = smem_u32(smem + Cfg::kOffK), aV = smem_u32(smem + Cfg::kOffV);
     const uint32_t aP = smem_u32(smem + Cfg::kOffP), adS = smem_u32(smem + Cfg::kOffdS);
+    // Shared-memory descriptors are built once; a k-step only adds its byte offset (>> 4) to them.
+    const uint64_t dK_k = make_smem_desc_sw128(aK, 16, 1024), dV_k = make_smem_desc_sw128(aV, 16, 1024);
+    const uint64_t dP_k = make_smem_desc_sw128(aP, 16, 1024), ddS_k = make_smem_desc_sw128(adS, 16, 1024);
+    const uint64_t ddS_m = make_smem_desc_sw128(adS, kAtom, 1024), dK_m = make_smem_desc_sw128(aK, kAtom, 1024);
+    const uint32_t aQ0 = smem_u32(smem + Cfg::kOffQ), adO0 = smem_u32(smem + Cfg::kOffdO);
+    const uint64_t dQ_k0 = make_smem_desc_sw128(aQ0, 16, 1024), ddO_k0 = make_smem_desc_sw128(adO0, 16, 1024);
+    const uint64_t dQ_m0 = make_smem_desc_sw128(aQ0, kAtom, 1024), ddO_m0 = make_smem_desc_sw128(adO0, kAtom, 1024);
+    constexpr uint64_t kStageStep = (S > 1 ? Cfg::kTile : 0) >> 4;
     bool ok = mbar_wait(kv_full, 0);
     if (!ok && lane == 0) atomicCAS(err, 0, 202);
     auto issue_scores = [&](int it) {     // S^T and dP^T of tile `it`
       const int st = it % S;
-      const uint32_t aQ = smem_u32(smem + Cfg::kOffQ + st * Cfg::kTile);
-      const uint32_t adO = smem_u32(smem + Cfg::kOffdO + st * Cfg::kTile);
       if (!mbar_wait(&q_full[st], (it / S) & 1) || *abort_flag) return false;
       // with aliasing, dQ of the previous tile sits over S^T until the softmax warps have read it out
       if (kAlias && it > 0 && (!mbar_wait(dq_drained, (it - 1) & 1) || *abort_flag)) return false;
       tc_fence_after_sync();
       if (lane == 0) {
+        const uint64_t dQ_k = dQ_k0 + st * kStageStep, ddO_k = ddO_k0 + st * kStageStep;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kAtom + (kk & 3) * 32;
-          umma_f16_ss(tm_S, make_smem_desc_sw128(aK + off, 16, 1024), make_smem_desc_sw128(aQ + off, 16, 1024), id_s,
-                      kk > 0);
+          const uint64_t off = ((kk >> 2) * kAtom + (kk & 3) * 32) >> 4;
+          umma_f16_ss(tm_S, dK_k + off, dQ_k + off, id_s, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kAtom + (kk & 3) * 32;
-          umma_f16_ss(tm_dP, make_smem_desc_sw128(aV + off, 16, 1024), make_smem_desc_sw128(adO + off, 16, 1024), id_s,
-                      kk > 0);
+          const uint64_t off = ((kk >> 2) * kAtom + (kk & 3) * 32) >> 4;
+          umma_f16_ss(tm_dP, dV_k + off, ddO_k + off, id_s, kk > 0);
         }
         umma_commit(s_full);
       }
@@ -203,8 +211,6 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     }
     for (int it = 0; it < iters && ok; ++it) {
       const int st = it % S;
-      const uint32_t aQ = smem_u32(smem + Cfg::kOffQ + st * Cfg::kTile);
-      const uint32_t adO = smem_u32(smem + Cfg::kOffdO + st * Cfg::kTile);
       ok = mbar_wait(p_full, it & 1) && !*abort_flag;
       // its own dQ columns are rewritten below: the previous tile's dQ must have been read out
       if (ok && !kAlias && it > 0) ok = mbar_wait(dq_drained, (it - 1) & 1) && !*abort_flag;
@@ -214,20 +220,18 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       }
       tc_fence_after_sync();
       if (lane == 0) {
+        const uint64_t dQ_m = dQ_m0 + st * kStageStep, ddO_m = ddO_m0 + st * kStageStep;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {       // contraction over the 128 query rows of the tile
-          const uint32_t koff = (kk >> 2) * kAtom + (kk & 3) * 32;   // K-major operand: P^T / dS^T
-          const uint32_t moff = kk * 2048;                            // MN-major operand: 16 rows down
-          umma_f16_ss(tm_dV, make_smem_desc_sw128(aP + koff, 16, 1024), make_smem_desc_sw128(adO + moff, kAtom, 1024),
-                      id_kv, (it > 0 || kk > 0));
-          umma_f16_ss(tm_dK, make_smem_desc_sw128(adS + koff, 16, 1024), make_smem_desc_sw128(aQ + moff, kAtom, 1024),
-                      id_kv, (it > 0 || kk > 0));
+          const uint64_t koff = ((kk >> 2) * kAtom + (kk & 3) * 32) >> 4;   // K-major operand: P^T / dS^T
+          const uint64_t moff = (kk * 2048) >> 4;                            // MN-major operand: 16 rows down
+          umma_f16_ss(tm_dV, dP_k + koff, ddO_m + moff, id_kv, (it > 0 || kk > 0));
+          umma_f16_ss(tm_dK, ddS_k + koff, dQ_m + moff, id_kv, (it > 0 || kk > 0));
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {       // contraction over the 128 keys
-          const uint32_t moff = kk * 2048;
-          umma_f16_ss(tm_dQ, make_smem_desc_sw128(adS + moff, kAtom, 1024), make_smem_desc_sw128(aK + moff, kAtom, 1024),
-                      id_q, kk > 0);
+          const uint64_t moff = (kk * 2048) >> 4;
+          umma_f16_ss(tm_dQ, ddS_m + moff, dK_m + moff, id_q, kk > 0);
         }
         umma_commit(&q_empty[st]);
         umma_commit(dq_full);
@@ -325,28 +329,37 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         }
       }
       if (ok) {
+        // dQ of the tile: TMEM -> fp32 staging over the spent P^T / dS^T buffers (32 columns per
+        // 16 KB block, 128-byte swizzle) -> one bulk add-reduction per block into the fp32 dQ buffer
         tc_fence_after_sync();
-        const int qrow = mb * 128 + row;
-        float* dqg = a.dq_accum + ((static_cast<long long>(b) * a.T + qrow) * a.H + h) * D;
 #pragma unroll 1
         for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
           uint32_t r[32];
           tmem_ld_32x32(tm_dQ + lane_addr + c * 32, r);
           tmem_ld_wait();
-          if (qrow < a.T) {
+          uint8_t* dst = smem + Cfg::kOffP + c * kAtom + row * 128;
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dqg + c * 32 + j),
-                           "f"(__uint_as_float(r[j]) * a.scale), "f"(__uint_as_float(r[j + 1]) * a.scale),
-                           "f"(__uint_as_float(r[j + 2]) * a.scale), "f"(__uint_as_float(r[j + 3]) * a.scale)
-                           : "memory");
-          }
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(dst + ((j ^ (row & 7)) << 4)) =
+                make_float4(__uint_as_float(r[4 * j]) * a.scale, __uint_as_float(r[4 * j + 1]) * a.scale,
+                            __uint_as_float(r[4 * j + 2]) * a.scale, __uint_as_float(r[4 * j + 3]) * a.scale);
         }
+        fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(dq_drained);
       }
+      softmax_warps_sync();     // every row of the staging blocks is written
+      if (ok && tid == 0) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c)
+          tma_reduce_add_3d(&tdq, smem + Cfg::kOffP + c * kAtom, h * D + c * 32, mb * 128, b);
+        tma_store_commit();
+        // the staging blocks are P^T / dS^T again after the barrier at the top of the next tile
+        tma_store_wait_read<0>();
+      }
     }
+    if (tid == 0) tma_store_wait<0>();
     if (ok) {
       // dK (scaled) and dV of this CTA's 128 keys; the last dq_full covered the MMAs that wrote them
       const int krow = n0 + row;
@@ -675,27 +688,32 @@ static int fwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
 }
 
 __global__ void attn_delta_tc_kernel(const ItbAttnArgs a, int D) {
-  // delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per (b,t,h)
-  const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  // delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; D / 8 threads per (b,t,h), 16 bytes each
+  const int tpr = D >> 3;                                        // threads per row: 8 or 16
+  const long long gid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long w = gid / tpr;
+  const int part = static_cast<int>(gid % tpr);
   const long long total = static_cast<long long>(a.B) * a.T * a.H;
-  if (w >= total) return;
-  const int h = static_cast<int>(w % a.H);
-  const long long bt = w / a.H;
-  const int t = static_cast<int>(bt % a.T), b = static_cast<int>(bt / a.T);
-  const __nv_bfloat16* o = static_cast<const __nv_bfloat16*>(a.o) + b * a.o_batch_stride +
-                           static_cast<long long>(t) * a.o_row_stride + h * D;
-  const __nv_bfloat16* d = static_cast<const __nv_bfloat16*>(a.dout) + b * a.o_batch_stride +
-                           static_cast<long long>(t) * a.o_row_stride + h * D;
   float acc = 0.f;
-  for (int i = lane * 2; i < D; i += 64) {
-    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(o + i);
-    const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(d + i);
-    acc += __bfloat162float(x.x) * __bfloat162float(y.x) + __bfloat162float(x.y) * __bfloat162float(y.y);
-  }
+  int h = 0, t = 0, b = 0;
+  if (w < total) {
+    h = static_cast<int>(w % a.H);
+    const long long bt = w / a.H;
+    t = static_cast<int>(bt % a.T);
+    b = static_cast<int>(bt / a.T);
+    const long long off = b * a.o_batch_stride + static_cast<long long>(t) * a.o_row_stride + h * D + part * 8;
+    const uint4 x = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.o) + off);
+    const uint4 y = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.dout) + off);
+    const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+    const __nv_bfloat162* yb = reinterpret_cast<const __nv_bfloat162*>(&y);
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) a.delta[(static_cast<long long>(b) * a.H + h) * a.T + t] = acc;
+    for (int e = 0; e < 4; ++e) {
+      const float2 xf = __bfloat1622float2(xb[e]), yf = __bfloat1622float2(yb[e]);
+      acc += xf.x * yf.x + xf.y * yf.y;
+    }
+  }
+  for (int s = tpr >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (w < total && part == 0) a.delta[(static_cast<long long>(b) * a.H + h) * a.T + t] = acc;
 }
 
 __global__ void attn_dq_convert_tc_kernel(const ItbAttnArgs a, int D) {
@@ -728,8 +746,10 @@ static int bwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  CUtensorMap tq, tk, tv, tdo;
-  int rc = make_tmap_bf16_3d(&tq, a->q, static_cast<uint64_t>(a->H) * D, a->T, a->B, a->q_row_stride,
+  CUtensorMap tq, tk, tv, tdo, tdq;
+  int rc = make_tmap_f32_3d(&tdq, a->dq_accum, static_cast<uint64_t>(a->H) * D, a->T, a->B,
+                            static_cast<uint64_t>(a->H) * D, static_cast<uint64_t>(a->T) * a->H * D, 128);
+  if (!rc) rc = make_tmap_bf16_3d(&tq, a->q, static_cast<uint64_t>(a->H) * D, a->T, a->B, a->q_row_stride,
                              a->q_batch_stride, 64, 128);
   if (!rc) rc = make_tmap_bf16_3d(&tk, a->k, static_cast<uint64_t>(a->KV) * D, a->T, a->B, a->k_row_stride,
                                   a->k_batch_stride, 64, 128);
@@ -741,9 +761,9 @@ static int bwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
   const long long nrow = static_cast<long long>(a->B) * a->T * a->H;
   cudaError_t e = cudaMemsetAsync(a->dq_accum, 0, nrow * D * sizeof(float), s);
   if (e != cudaSuccess) return static_cast<int>(e);
-  attn_delta_tc_kernel<<<static_cast<int>((nrow * 32 + 255) / 256), 256, 0, s>>>(*a, D);
+  attn_delta_tc_kernel<<<static_cast<int>((nrow * (D / 8) + 255) / 256), 256, 0, s>>>(*a, D);
   dim3 grid((a->T + 127) / 128, a->KV, a->B);
-  flash_bwd_tc_kernel<D><<<grid, kThreads, smem, s>>>(tq, tk, tv, tdo, *a, err);
+  flash_bwd_tc_kernel<D><<<grid, kThreads, smem, s>>>(tq, tk, tv, tdo, tdq, *a, err);
   const long long nvec = nrow * (D / 4);
   attn_dq_convert_tc_kernel<<<static_cast<int>((nvec + 255) / 256), 256, 0, s>>>(*a, D);
   return static_cast<int>(cudaGetLastError());

@@ -312,6 +312,21 @@ int make_tmap_bf16_3d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// 3-D fp32 tensor map [d2][d1][inner], boxes of 32 columns (128 bytes) x box_d1 x 1, 128-byte swizzle.
+int make_tmap_f32_3d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t d1, uint64_t d2,
+                     uint64_t ld1, uint64_t ld2, uint32_t box_d1) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {inner, d1, d2};
+  cuuint64_t strides[2] = {ld1 * 4, ld2 * 4};
+  cuuint32_t box[3] = {32, box_d1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 // fp32 matrix, box of 32 columns (128 bytes) x box_outer rows, 128-byte swizzle.
 int make_tmap_f32_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
                      uint32_t box_outer) {
