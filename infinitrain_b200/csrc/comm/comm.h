@@ -41,6 +41,10 @@ int itb_nvl_rs_adamw_bcast(const ItbPeerPtrs* grads, const void* mc_grads, const
                            int world, int ch0, int epoch, const ItbAdamHyper* hyper, int* err,
                            int* epoch_ctr, const float* dev_hyper, cudaStream_t stream);
 
+// One thread polls `*flag` until it is >= target or `limit` polls have passed; a time-out writes
+// `code` into `*err` and the kernel returns (the bounded wait of the flag protocols, on its own).
+int itb_wait_flag(const int* flag, int target, unsigned limit, int code, int* err, cudaStream_t stream);
+
 // ---- tensor-parallel GEMMs fused with all-gather / reduce-scatter (tp_gemm.cu)
 // Activations are [batch * T, cols] with row = b * T + t; under sequence parallelism rank s holds
 // t in [s * Tl, (s + 1) * Tl), Tl = T / world (a multiple of 256).  All pointer tables are

@@ -173,6 +173,14 @@ void tp_gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, int
   check(itb_tp_gemm(&g, &t, at::cuda::getCurrentCUDAStream().stream()), "tp_gemm");
 }
 
+void wait_flag(const at::Tensor& flag, int64_t target, int64_t limit, int64_t code, at::Tensor& err) {
+  TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt && err.is_cuda() && err.scalar_type() == at::kInt,
+              "wait_flag: int32 CUDA tensors required");
+  check(itb_wait_flag(flag.data_ptr<int>(), static_cast<int>(target), static_cast<unsigned>(limit),
+                      static_cast<int>(code), err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream()),
+        "wait_flag");
+}
+
 void tp_wait(int64_t arrive_ptr, const at::Tensor& total, int64_t world, at::Tensor& err) {
   check(itb_tp_wait(reinterpret_cast<const int*>(arrive_ptr), total.data_ptr<int>(), static_cast<int>(world),
                     err.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream()),
@@ -192,5 +200,6 @@ void bind_comm(pybind11::module_& m) {
   m.attr("TP_SCATTER") = static_cast<int>(kItbTpScatter);
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_wait", &tp_wait);
+  m.def("wait_flag", &wait_flag);
   m.def("tp_gemm_ctas", [](int64_t M, int64_t N) { return itb_tp_gemm_ctas(static_cast<int>(M), static_cast<int>(N)); });
 }

@@ -210,6 +210,28 @@ rs_adamw_bcast_kernel(ItbPeerPtrs grads, const float* mc_grads, ItbPeerPtrs para
 
 using namespace itb;
 
+// The bounded wait of the flag protocols on its own: one thread polls `flag` until it has reached
+// `target` or `limit` polls have passed; on a time-out it records `code` in the status word and
+// returns.  Lets the host-visible error path be exercised on a single GPU with a flag that nothing
+// sets, without any peer and without hanging anything.
+__global__ void wait_flag_kernel(const int* flag, int target, unsigned limit, int code, int* err) {
+  bool ok = false;
+  for (unsigned i = 0; i < limit; ++i) {
+    if (ld_acquire_sys(flag) - target >= 0) {
+      ok = true;
+      break;
+    }
+    if (i > 32) __nanosleep(100);
+  }
+  if (!ok) atomicCAS(err, 0, code);
+}
+
+extern "C" int itb_wait_flag(const int* flag, int target, unsigned limit, int code, int* err,
+                             cudaStream_t stream) {
+  wait_flag_kernel<<<1, 1, 0, stream>>>(flag, target, limit, code, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int itb_comm_blocks(long long n_elements_per_rank) {
   long long b = (n_elements_per_rank / 4 + kCommThreads - 1) / kCommThreads;
   if (b < 1) b = 1;

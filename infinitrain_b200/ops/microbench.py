@@ -1,0 +1,133 @@
+"""Micro-benchmarks of the hot sm_100a kernels on the shapes of the headline models.
+
+    python -m infinitrain_b200.ops.microbench gemm        # tcgen05 GEMM vs torch.matmul (cuBLAS), GPT-2 shapes
+    python -m infinitrain_b200.ops.microbench attention   # tcgen05 vs mma.sync flash attention, forward + backward
+    python -m infinitrain_b200.ops.microbench profile     # one launch of each, for a profiler capture
+
+Every number is CUDA-event time on the launching stream after warm-up, with a buffer larger than L2
+written between timed launches.  One JSON line per case.
+"""
+from __future__ import annotations
+
+import json
+import math
+import sys
+
+import torch
+
+from .. import _ext
+
+
+def _timer():
+    flush = torch.empty(64 << 20, device="cuda", dtype=torch.float32)   # 256 MB > 126 MB of L2
+
+    def timeit(fn, n=10, warm=3):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+
+    return timeit
+
+
+def _attn_tensors(B, T, H, KV, D):
+    qkv = torch.randn(B, T, (H + 2 * KV) * D, device="cuda").bfloat16()
+    q = qkv[..., : H * D].view(B, T, H, D)
+    k = qkv[..., H * D: (H + KV) * D].view(B, T, KV, D)
+    v = qkv[..., (H + KV) * D:].view(B, T, KV, D)
+    dqkv = torch.empty_like(qkv)
+    dq = dqkv[..., : H * D].view(B, T, H, D)
+    dk = dqkv[..., H * D: (H + KV) * D].view(B, T, KV, D)
+    dv = dqkv[..., (H + KV) * D:].view(B, T, KV, D)
+    return q, k, v, dq, dk, dv
+
+
+def bench_gemm(C):
+    timeit = _timer()
+    tokens = 16 * 1024
+    shapes = []
+    for n, k in ((2304, 768), (768, 768), (3072, 768), (768, 3072), (50304, 768)):
+        shapes += [("fwd", tokens, n, k), ("dgrad", tokens, k, n), ("wgrad", n, k, tokens)]
+    for kind, M, N, K in shapes:
+        if kind == "fwd":
+            a = torch.randn(M, K, device="cuda").bfloat16()
+            b = torch.randn(N, K, device="cuda").bfloat16()
+            c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            ours = timeit(lambda: C.gemm(a, False, b, False, M, N, K, c, None, None, None, None, 0, 0))
+            lib = timeit(lambda: torch.matmul(a, b.t(), out=c))
+        elif kind == "dgrad":
+            a = torch.randn(M, K, device="cuda").bfloat16()
+            b = torch.randn(K, N, device="cuda").bfloat16()
+            c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            ours = timeit(lambda: C.gemm(a, False, b, True, M, N, K, c, None, None, None, None, 0, 0))
+            lib = timeit(lambda: torch.matmul(a, b, out=c))
+        else:
+            a = torch.randn(K, M, device="cuda").bfloat16()
+            b = torch.randn(K, N, device="cuda").bfloat16()
+            c = torch.zeros(M, N, device="cuda")
+            cb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            ours = timeit(lambda: C.gemm(a, True, b, True, M, N, K, c, None, None, None, None,
+                                         C.GEMM_OUT_F32 | C.GEMM_ATOMIC, 0))
+            lib = timeit(lambda: torch.matmul(a.t(), b, out=cb))
+        fl = 2.0 * M * N * K
+        print(json.dumps({"case": "gemm", "kind": kind, "M": M, "N": N, "K": K, "ours_ms": ours, "cublas_ms": lib,
+                          "ours_tflops": fl / ours / 1e9, "cublas_tflops": fl / lib / 1e9}))
+
+
+def bench_attention(C):
+    timeit = _timer()
+    default = C.get_attn_mode()
+    for B, T, H, KV, D in ((16, 1024, 12, 12, 64), (1, 2048, 32, 8, 128), (4, 2048, 32, 8, 128)):
+        q, k, v, dq, dk, dv = _attn_tensors(B, T, H, KV, D)
+        sc = 1.0 / math.sqrt(D)
+        o, lse = C.flash_attn_fwd(q, k, v, sc, True)
+        do = torch.randn_like(o)
+        fl = 4.0 * B * H * T * T * D / 2
+        res = {"case": "attention", "B": B, "T": T, "H": H, "KV": KV, "D": D}
+        for mode, name in ((0, "mma_sync"), (3, "tcgen05")):
+            C.set_attn_mode(mode)
+            t = timeit(lambda: C.flash_attn_fwd(q, k, v, sc, True))
+            res[f"fwd_{name}_ms"], res[f"fwd_{name}_tflops"] = t, fl / t / 1e9
+            t = timeit(lambda: C.flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, sc, True))
+            res[f"bwd_{name}_ms"], res[f"bwd_{name}_tflops"] = t, 2.5 * fl / t / 1e9
+        C.set_attn_mode(default)
+        res["status"] = C.kernel_status()
+        print(json.dumps(res))
+
+
+def profile_case(C):
+    """GEMM forward (twice) and weight gradient on 16384 x 2304 x 768, attention forward and backward on
+    16 x 1024 x 12 heads x 64: the launches a profiler capture of the top kernels needs, and no more."""
+    M, N, K = 16384, 2304, 768
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        C.gemm(a, False, b, False, M, N, K, c, None, None, None, None, 0, 0)
+    dw = torch.zeros(N, K, device="cuda")
+    C.gemm(c, True, a, True, N, K, M, dw, None, None, None, None, C.GEMM_OUT_F32 | C.GEMM_ATOMIC, 0)
+    q, k, v, dq, dk, dv = _attn_tensors(16, 1024, 12, 12, 64)
+    o, lse = C.flash_attn_fwd(q, k, v, 0.125, True)
+    C.flash_attn_bwd(torch.randn_like(o), q, k, v, o, lse, dq, dk, dv, 0.125, True)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": "profile", "status": C.kernel_status()}))
+
+
+def main(argv):
+    C = _ext.load(required=True)
+    torch.manual_seed(0)
+    case = argv[1] if len(argv) > 1 else "gemm"
+    {"gemm": bench_gemm, "attention": bench_attention, "profile": profile_case}[case](C)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv))

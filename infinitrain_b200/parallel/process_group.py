@@ -240,6 +240,20 @@ class ProcessGroup:
         if not self._trivial():
             dist.barrier(group=self.pg)
 
+    def abort(self) -> bool:
+        """Tears the communicator down without waiting for outstanding collectives (``ncclCommAbort``
+        for NCCL; backends without an abort return False).  Used by the failure watchdog."""
+        if self._trivial():
+            return False
+        fn = getattr(dist.distributed_c10d, "_abort_process_group", None)
+        if fn is None or self.backend != "nccl":
+            return False
+        try:
+            fn(self.pg)
+            return True
+        except Exception:  # noqa: BLE001
+            return False
+
     # ------------------------------------------------------------------ legacy data-parallel helpers
     def ReduceAddCoalesced(self, tensors: Sequence[torch.Tensor], dst_group_rank: int = 0):
         """Sum every tensor of the list onto ``dst`` (reference: process_group.cc:292-330)."""

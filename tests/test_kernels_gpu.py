@@ -295,3 +295,23 @@ def test_flash_attention(C, B, T, H, KV, D, attn_mode):
     assert _rel(dv, vr.grad) < 3e-2
     assert _rel(dk, kr.grad) < 3e-2
     assert _rel(dq, qr.grad) < 3e-2
+
+
+def test_bounded_wait_gives_up_with_a_status_code(C):
+    """A wait on a flag that nothing sets runs out of polls, records its code and returns; the
+    context stays usable.  A flag that is already set passes with status 0."""
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    C.wait_flag(flag, 1, 1 << 12, 77, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 77
+    from infinitrain_b200.utils.fault_tolerance import KernelTimeout, check_kernel_status
+
+    with pytest.raises(KernelTimeout):
+        check_kernel_status(lambda: int(err.item()), "flag wait")
+    err.zero_()
+    flag.fill_(5)
+    C.wait_flag(flag, 3, 1 << 12, 77, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert torch.ones(8, device="cuda").sum().item() == 8.0
