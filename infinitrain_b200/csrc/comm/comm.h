@@ -41,6 +41,16 @@ int itb_nvl_rs_adamw_bcast(const ItbPeerPtrs* grads, const void* mc_grads, const
                            int world, int ch0, int epoch, const ItbAdamHyper* hyper, int* err,
                            int* epoch_ctr, const float* dev_hyper, cudaStream_t stream);
 
+// Vocab-parallel cross-entropy: merges every rank's per-row (log-sum-exp of its vocabulary shard,
+// target logit if owned) into the global log-sum-exp and the row loss inside one kernel that
+// exchanges the pairs through `bufs` (symmetric, float2 [world][rows_cap] per rank) and meets the
+// other ranks at flag barriers.  row_loss is the local pass's lse_local - target logit (owner rows).
+// Uses channels ch0 .. ch0 + kItbMaxCommBlocks - 1; epochs come from epoch_ctr (device memory).
+int itb_nvl_ce_merge(const ItbPeerPtrs* bufs, const ItbPeerPtrs* flags, const float* lse_local,
+                     const float* row_loss, const long long* t_local, int vocab_valid, float* lse_out,
+                     float* loss_out, int rows, int rows_cap, int rank, int world, int ch0, int* err,
+                     int* epoch_ctr, cudaStream_t stream);
+
 // One thread polls `*flag` until it is >= target or `limit` polls have passed; a time-out writes
 // `code` into `*err` and the kernel returns (the bounded wait of the flag protocols, on its own).
 int itb_wait_flag(const int* flag, int target, unsigned limit, int code, int* err, cudaStream_t stream);

@@ -173,6 +173,27 @@ void tp_gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, int
   check(itb_tp_gemm(&g, &t, at::cuda::getCurrentCUDAStream().stream()), "tp_gemm");
 }
 
+void nvl_ce_merge(const std::vector<int64_t>& bufs, const std::vector<int64_t>& flags, const at::Tensor& lse_local,
+                  const at::Tensor& row_loss, const at::Tensor& t_local, int64_t vocab_valid, at::Tensor& lse_out,
+                  at::Tensor& loss_out, int64_t rows_cap, int64_t rank, int64_t world, int64_t ch0, at::Tensor& err,
+                  at::Tensor& epoch_ctr) {
+  TORCH_CHECK(lse_local.scalar_type() == at::kFloat && row_loss.scalar_type() == at::kFloat &&
+                  t_local.scalar_type() == at::kLong && lse_out.scalar_type() == at::kFloat &&
+                  loss_out.scalar_type() == at::kFloat && lse_local.is_contiguous() && row_loss.is_contiguous() &&
+                  t_local.is_contiguous() && lse_out.is_contiguous() && loss_out.is_contiguous(),
+              "nvl_ce_merge: contiguous fp32 statistics and int64 targets required");
+  const int64_t rows = lse_local.numel();
+  TORCH_CHECK(row_loss.numel() == rows && t_local.numel() == rows && lse_out.numel() == rows && loss_out.numel() == rows,
+              "nvl_ce_merge: one entry per row");
+  ItbPeerPtrs b = to_ptrs(bufs), f = to_ptrs(flags);
+  check(itb_nvl_ce_merge(&b, &f, lse_local.data_ptr<float>(), row_loss.data_ptr<float>(), reinterpret_cast<const long long*>(t_local.data_ptr<int64_t>()),
+                         static_cast<int>(vocab_valid), lse_out.data_ptr<float>(), loss_out.data_ptr<float>(),
+                         static_cast<int>(rows), static_cast<int>(rows_cap), static_cast<int>(rank),
+                         static_cast<int>(world), static_cast<int>(ch0), err.data_ptr<int>(), epoch_ctr.data_ptr<int>(),
+                         at::cuda::getCurrentCUDAStream().stream()),
+        "ce_merge");
+}
+
 void wait_flag(const at::Tensor& flag, int64_t target, int64_t limit, int64_t code, at::Tensor& err) {
   TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt && err.is_cuda() && err.scalar_type() == at::kInt,
               "wait_flag: int32 CUDA tensors required");
@@ -201,5 +222,6 @@ void bind_comm(pybind11::module_& m) {
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_wait", &tp_wait);
   m.def("wait_flag", &wait_flag);
+  m.def("nvl_ce_merge", &nvl_ce_merge);
   m.def("tp_gemm_ctas", [](int64_t M, int64_t N) { return itb_tp_gemm_ctas(static_cast<int>(M), static_cast<int>(N)); });
 }

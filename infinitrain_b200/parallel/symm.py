@@ -446,6 +446,42 @@ class _LinearReduceScatterFn(torch.autograd.Function):
         return dx, dw, db, dres
 
 
+class VocabCEMerge:
+    """Cross-rank merge of the vocab-parallel cross-entropy statistics in one NVLink kernel."""
+
+    _by_ctx: Dict[int, "VocabCEMerge"] = {}
+
+    @classmethod
+    def get(cls, device: torch.device) -> Optional["VocabCEMerge"]:
+        tp = _tp_context(device)
+        if tp is None:
+            return None
+        if id(tp) not in cls._by_ctx:
+            cls._by_ctx[id(tp)] = cls(tp.nvl)
+        return cls._by_ctx[id(tp)]
+
+    def __init__(self, nvl: NvlinkContext):
+        self.nvl = nvl
+        self.rows_cap = 0
+        self.buf = None
+        self.ch0 = nvl.reserve_channels(nvl.C.MAX_COMM_BLOCKS)
+
+    def __call__(self, lse_local, row_loss, t_local, vocab_valid):
+        nvl = self.nvl
+        rows = lse_local.numel()
+        if rows > self.rows_cap:
+            self.rows_cap = max(rows, 4096)
+            self.buf = nvl.alloc(2 * nvl.world * self.rows_cap, torch.float32)     # float2 [world][rows_cap]
+            self.ptrs, _ = nvl.ptrs(self.buf)
+        lse = torch.empty_like(lse_local)
+        loss = torch.empty_like(lse_local)
+        nvl.C.nvl_ce_merge(self.ptrs, nvl.flag_ptrs, lse_local.contiguous(), row_loss.contiguous(),
+                           t_local.contiguous(), vocab_valid, lse, loss, self.rows_cap, nvl.rank, nvl.world, self.ch0,
+                           nvl.err, nvl.epoch_ctr)
+        ops._counters["launches"] += 1
+        return lse, loss
+
+
 def allgather_linear(x, weight, bias, gelu=False):
     if _TP_CTX is None:
         raise RuntimeError("fused tensor-parallel kernels are not initialised")

@@ -334,6 +334,16 @@ class _VocabParallelCEFn(torch.autograd.Function):
             own = (t_local >= 0) & (t_local < vocab_valid_local)
             picked = lv.gather(1, t_local.clamp(0, max(vocab_valid_local - 1, 0)).unsqueeze(1)).squeeze(1)
             row_loss = torch.where(own, lse_local - picked, torch.zeros_like(lse_local))
+        if l2.is_cuda:
+            from . import symm
+
+            merge = symm.VocabCEMerge.get(l2.device)
+            if merge is not None:
+                # one kernel exchanges the per-row pairs over NVLink and merges them
+                lse, loss_rows = merge(lse_local, row_loss, t_local, vocab_valid_local)
+                ctx.save_for_backward(l2, t_local, lse)
+                ctx.meta = (logits.shape, vocab_valid_local, rows)
+                return loss_rows.view(target.shape)
         own = (t_local >= 0) & (t_local < vocab_valid_local)
         # target logit (0 where another rank owns it)
         tgt_logit = torch.where(own, lse_local - row_loss, torch.zeros_like(lse_local))

@@ -218,8 +218,58 @@ def tp_fused():
         print(f"TP FUSED OK worst_rel={t.item():.2e}")
 
 
+def vocab_ce():
+    """Vocab-parallel cross-entropy: the NVLink merge kernel against the all-gather formulation and
+    against the loss over the gathered full-vocabulary logits."""
+    import torch.distributed as dist
+
+    from infinitrain_b200.parallel import global_env as genv
+    from infinitrain_b200.parallel import symm
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory
+    from infinitrain_b200.parallel.tensor_parallel import VocabParallelCrossEntropyLoss
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    genv.InitAllEnv(world_size=world, rank=rank, tensor_parallel_size=world, sequence_parallel_enabled=True)
+    ProcessGroupFactory.Instance().Init(device=dev, timeout_s=120)
+    B, T, V_local = 2, 600, 1000
+    V_orig = V_local * world - 37            # the last shard is partly padding
+    loss_fn = VocabParallelCrossEntropyLoss(V_orig)
+    outs = {}
+    for fused in ("0", "1"):
+        os.environ["ITB_FUSED_TP"] = fused
+        symm.reset_fused_tp()
+        res = []
+        for it in range(3):
+            torch.manual_seed(77 + it)                      # same targets on every rank
+            target = torch.randint(0, V_orig, (B, T), device=dev)
+            torch.manual_seed(1000 * it + rank)
+            logits = (torch.randn(B, T, V_local, device=dev) * 2).bfloat16().requires_grad_(True)
+            keep = logits.detach().clone()      # the backward pass writes the gradient over the logits
+            loss = loss_fn(logits, target)
+            loss.backward()
+            res.append((loss.detach().float().clone(), logits.grad.float().clone(), keep, target))
+        torch.cuda.synchronize()
+        outs[fused] = res
+        if fused == "1":
+            assert symm._TP_CTX is not None and symm._TP_CTX.nvl.status() == 0
+    for (l0, g0, lg, tg), (l1, g1, _, _) in zip(outs["0"], outs["1"]):
+        assert abs(l0.item() - l1.item()) < 1e-4 * max(1.0, abs(l0.item())), ("nccl vs fused", l0.item(), l1.item())
+        assert ((g0 - g1).norm() / (g0.norm() + 1e-9)).item() < 1e-3, "gradients differ"
+        # full-vocabulary reference from the gathered shards
+        full = [torch.empty_like(lg) for _ in range(world)]
+        dist.all_gather(full, lg.contiguous())
+        ref = torch.nn.functional.cross_entropy(torch.cat(full, -1)[..., :V_orig].float().view(B * T, -1), tg.view(-1))
+        assert abs(ref.item() - l1.item()) < 2e-3 * max(1.0, abs(ref.item())), ("full vocab vs fused", ref.item(), l1.item())
+    if rank == 0:
+        print("VOCAB CE OK")
+
+
 if __name__ == "__main__":
-    if sys.argv[1] == "collectives":
+    if sys.argv[1] == "vocab_ce":
+        vocab_ce()
+    elif sys.argv[1] == "collectives":
         collectives()
     elif sys.argv[1] == "tp_fused":
         tp_fused()

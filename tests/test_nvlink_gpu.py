@@ -55,3 +55,10 @@ def test_fused_tensor_parallel_linears_match_nccl_8_ranks():
     os.environ["ITB_NVLS"] = "1"
     out = _torchrun("mgpu_worker.py", 8, "tp_fused")
     assert "TP FUSED OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_vocab_parallel_cross_entropy_merge_kernel():
+    os.environ["ITB_NVLS"] = "1"
+    out = _torchrun("mgpu_worker.py", 2, "vocab_ce")
+    assert "VOCAB CE OK" in out
