@@ -128,3 +128,43 @@ def test_checkpoint_resume_continues_identically(tmp_path):
     bad = TransformerConfig.GPT2(n_layer=3, n_embd=32, n_head=2, n_kv_head=2, vocab_size=64, original_vocab_size=64, block_size=16)
     with pytest.raises((ValueError, KeyError)):
         ResumeFromCheckpoint(os.path.join(root, "checkpoint_step_000006"), TransformerModel(bad), None, bad, False)
+
+
+def test_zero_optimizer_state_resharding():
+    """State saved by 4 data-parallel ranks, resumed on 2 and on 3: every parameter's moments end up
+    at the offsets the new flat layout gives them."""
+    import torch
+
+    from infinitrain_b200.checkpoint.reshard import gather_full_optimizer_state, reshard_zero_optimizer_state
+    from infinitrain_b200.parallel.ddp.param_and_grad_buffer import plan_flat_layout
+
+    torch.manual_seed(0)
+    numels = [130, 4096, 77, 250_000, 1_200_000, 64, 900_000, 31]
+    truth = [{"adam.m": torch.randn(n), "adam.v": torch.rand(n)} for n in numels]
+
+    def shards_for(dp):
+        lay = plan_flat_layout(numels, dp, shard=True)
+        states = [dict() for _ in range(dp)]
+        for key in ("adam.m", "adam.v"):
+            flat = torch.zeros(lay.numel)
+            for (s, e, _), t in zip(lay.param_ranges, truth):
+                flat[s:e] = t[key]
+            for b, (bs, be) in enumerate(lay.bucket_ranges):
+                n = (be - bs) // dp
+                for r in range(dp):
+                    states[r][f"{key}.{b}"] = flat[bs + r * n: bs + (r + 1) * n].clone()
+        for r in range(dp):
+            states[r]["adam.t"] = torch.tensor(7)
+        return states
+
+    old = shards_for(4)
+    for new_dp in (2, 3, 1, 8):
+        want = shards_for(new_dp)
+        for r in range(new_dp):
+            got = reshard_zero_optimizer_state(old, numels, new_dp, r)
+            assert set(got) == set(want[r])
+            for k in want[r]:
+                assert torch.equal(got[k], want[r][k]), (new_dp, r, k)
+    full = gather_full_optimizer_state(old, numels)
+    for f, t in zip(full, truth):
+        assert torch.equal(f["adam.m"], t["adam.m"]) and torch.equal(f["adam.v"], t["adam.v"])

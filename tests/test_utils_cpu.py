@@ -89,3 +89,44 @@ def test_step_line_matches_reference_parsers():
     m1 = re.search(r"step\s+(\d+)/\d+\s+\|\s+train loss\s+([\d.]+)", line)
     m2 = re.search(r"step\s+(\d+)/\d+\s+\|.*?\|\s+(\d+)\s+tok/s", line)
     assert m1 and float(m1.group(2)) == 4.123456 and m2 and int(m2.group(2)) == 524288
+
+
+def test_compare_logs_tool(tmp_path):
+    import importlib.util
+    import os
+
+    from infinitrain_b200.utils.logging import format_step_line
+
+    spec = importlib.util.spec_from_file_location(
+        "compare_logs", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "common",
+                                     "compare_logs.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    a, b, c = tmp_path / "run_bfloat16.log", tmp_path / "b" / "run_bfloat16.log", tmp_path / "c.log"
+    (tmp_path / "b").mkdir()
+    lines = [format_step_line(s, 3, 10.0 - s, 1e-4, 20.0, 50000.0, 100, 200, 1, 1, 0, 1) for s in (1, 2, 3)]
+    a.write_text("\n".join(lines))
+    b.write_text("\n".join(ln.replace("8.000000", "8.004000") for ln in lines))          # inside 1e-2
+    c.write_text("\n".join(ln.replace("8.000000", "8.400000").replace("50000 tok/s", "30000 tok/s") for ln in lines))
+    assert mod.main([str(a), str(b)]) == 0
+    assert mod.main([str(a), str(c)]) == 1
+    assert len(mod.compare(a, c, 1e-2, 0.2)) == 2     # one loss mismatch, throughput out of band
+
+
+def test_no_source_file_names_a_cluster_multicast_tma_load():
+    """TMA / bulk loads with cluster multicast are not used anywhere (they must never read another
+    GPU's memory, and multi-GPU runs are refused while any source names one)."""
+    import os
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pat = re.compile(r"cp\.async\.bulk[.\w:]*\.multicast::cluster")
+    hits = []
+    for base, _, files in os.walk(root):
+        if any(part in base for part in (".git", "gpurun_out", "baseline", "_work", "csrc/build")):
+            continue
+        for f in files:
+            if f.endswith((".cu", ".cuh", ".h", ".cpp", ".cc", ".py")) and f != "test_utils_cpu.py":
+                if pat.search(open(os.path.join(base, f), errors="replace").read()):
+                    hits.append(os.path.join(base, f))
+    assert not hits, hits
