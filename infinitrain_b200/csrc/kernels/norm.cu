@@ -196,7 +196,6 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
     TDX* dxr = dx + static_cast<long long>(row) * C;
     const float mean = kRms ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
-    float gc[kMaxVec][8], xh[kMaxVec][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
@@ -210,8 +209,6 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
         for (int e = 0; e < 8; ++e) {
           float xhat = (xv[e] - mean) * rstd;
           float gg = d[e] * g[e];
-          xh[i][e] = xhat;
-          gc[i][e] = gg;
           s1 += gg;
           s2 += gg * xhat;
           acc_g[i][e] += d[e] * xhat;
@@ -237,13 +234,21 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
     s1 = warp_sum(s1) / C;
     s2 = warp_sum(s2) / C;
     if (kRms) s1 = 0.f;
+    // Second pass re-reads the row (it is in L1 / L2 from the first pass) instead of holding it in
+    // registers: the kernel is bound by loads in flight, so occupancy matters more than the re-read.
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
       int vi = lane + i * 32;
       if (vi < nvec) {
-        float o[8];
+        float d[8], xv[8], g[8], o[8];
+        load8<TDY>(dyr + vi * 8, d);
+        load8<TX>(xr + vi * 8, xv);
+        load8<float>(gamma + vi * 8, g);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = rstd * (gc[i][e] - s1 - xh[i][e] * s2);
+        for (int e = 0; e < 8; ++e) {
+          float xhat = (xv[e] - mean) * rstd;
+          o[e] = rstd * (d[e] * g[e] - s1 - xhat * s2);
+        }
         store8<TDX>(dxr + vi * 8, o);
       }
     }
@@ -342,7 +347,11 @@ static int norm_bwd_dispatch(const void* dy, int dyd, const void* x, int xd, con
   if (smem > 48 * 1024) return -5;
 #define LAUNCH(TDY, TX, TDX)                                                                     \
   do {                                                                                           \
-    if (C <= 1024)                                                                               \
+    if (C <= 768)                                                                                \
+      norm_bwd_kernel<TDY, TX, TDX, kRms, 3><<<grid, kNormThreads, smem, s>>>(                   \
+          static_cast<const TDY*>(dy), static_cast<const TX*>(x), gamma, mean, rstd,             \
+          static_cast<TDX*>(dx), partial, rows, C);                                              \
+    else if (C <= 1024)                                                                          \
       norm_bwd_kernel<TDY, TX, TDX, kRms, 4><<<grid, kNormThreads, smem, s>>>(                   \
           static_cast<const TDY*>(dy), static_cast<const TX*>(x), gamma, mean, rstd,             \
           static_cast<TDX*>(dx), partial, rows, C);                                              \

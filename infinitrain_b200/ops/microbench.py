@@ -3,6 +3,8 @@
     python -m infinitrain_b200.ops.microbench gemm        # tcgen05 GEMM vs torch.matmul (cuBLAS), GPT-2 shapes
     python -m infinitrain_b200.ops.microbench attention   # tcgen05 vs mma.sync flash attention, forward + backward
     python -m infinitrain_b200.ops.microbench profile     # one launch of each, for a profiler capture
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m infinitrain_b200.ops.microbench tp             # fused vs NCCL tensor-parallel linear pair
 
 Every number is CUDA-event time on the launching stream after warm-up, with a buffer larger than L2
 written between timed launches.  One JSON line per case.
@@ -121,11 +123,79 @@ def profile_case(C):
     print(json.dumps({"case": "profile", "status": C.kernel_status()}))
 
 
+def bench_tp(C):
+    """Column-parallel + row-parallel linear pair (forward + backward) under sequence parallelism on
+    every rank of the job: fused all-gather+GEMM / GEMM+reduce-scatter launches against the NCCL
+    formulation of the same layers.  Shapes from the environment: TPB_B, TPB_T, TPB_H, TPB_F."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..autocast import AutocastGuard
+    from ..datatype import DataType
+    from ..device import DeviceType
+    from ..parallel import global_env as genv
+    from ..parallel import symm
+    from ..parallel.process_group import ProcessGroupFactory
+    from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    genv.InitAllEnv(world_size=world, rank=rank, tensor_parallel_size=world, sequence_parallel_enabled=True)
+    ProcessGroupFactory.Instance().Init(device=dev, timeout_s=120)
+    B, T = int(os.environ.get("TPB_B", 1)), int(os.environ.get("TPB_T", 2048))
+    H, F = int(os.environ.get("TPB_H", 4096)), int(os.environ.get("TPB_F", 28672))
+    Tl = T // world
+    col = ColumnParallelLinear(H, F, bias=False, gather_output=False, input_is_parallel=False,
+                               sequence_parallel=True, device=dev)
+    row = RowParallelLinear(F, H, bias=False, input_is_parallel=True, sequence_parallel=True, device=dev)
+    for p in list(col.Parameters()) + list(row.Parameters()):
+        p.data.normal_(0, 0.02)
+        p.main_grad = torch.zeros_like(p)
+    x = (torch.randn(B, Tl, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    res = (torch.randn(B, Tl, H, device=dev) * 0.5).bfloat16()
+    gy = torch.randn(B, Tl, H, device=dev).bfloat16() * 0.1
+    out = {"case": "tp", "B": B, "T": T, "H": H, "F": F, "world": world}
+
+    def step():
+        with AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16):
+            y = row(col(x), residual=res)
+        y.backward(gy)
+
+    for fused in ("0", "1"):
+        os.environ["ITB_FUSED_TP"] = fused
+        symm.reset_fused_tp()
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = 20
+        e0.record()
+        for _ in range(n):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["fused_ms" if fused == "1" else "nccl_ms"] = t.item()
+    if symm._TP_CTX is not None:
+        out["status"] = symm._TP_CTX.nvl.status()
+    flops = 3 * 2.0 * B * T * H * (F // world) * 2
+    out["fused_tflops_per_gpu"] = flops / out["fused_ms"] / 1e9
+    out["nccl_tflops_per_gpu"] = flops / out["nccl_ms"] / 1e9
+    if rank == 0:
+        print(json.dumps(out))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main(argv):
     C = _ext.load(required=True)
     torch.manual_seed(0)
     case = argv[1] if len(argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "attention": bench_attention, "profile": profile_case}[case](C)
+    {"gemm": bench_gemm, "attention": bench_attention, "profile": profile_case, "tp": bench_tp}[case](C)
     return 0
 
 
