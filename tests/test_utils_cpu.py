@@ -120,7 +120,8 @@ def test_no_source_file_names_a_cluster_multicast_tma_load():
     import re
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    pat = re.compile(r"cp\.async\.bulk[.\w:]*\.multicast::cluster")
+    # the qualifier is spelled in two pieces so that this file does not contain it itself
+    pat = re.compile(r"cp\.async\.bulk[.\w:]*\.multi" + "cast::cluster")
     hits = []
     for base, _, files in os.walk(root):
         if any(part in base for part in (".git", "gpurun_out", "baseline", "_work", "csrc/build")):
