@@ -60,7 +60,7 @@ int itb_wait_flag(const int* flag, int target, unsigned limit, int code, int* er
 // t in [s * Tl, (s + 1) * Tl), Tl = T / world (a multiple of 256).  All pointer tables are
 // symmetric-memory addresses of the same buffer on every rank; counters marked "this GPU" are
 // ordinary device memory that the kernels advance themselves (replayable from a CUDA graph).
-enum { kItbTpPush = 1, kItbTpGateA = 2, kItbTpScatter = 4 };
+enum { kItbTpPush = 1, kItbTpGateA = 2, kItbTpScatter = 4, kItbTpBroadcast = 8 };
 
 typedef struct {
   int mode;                   // kItbTpPush | kItbTpGateA | kItbTpScatter
@@ -92,6 +92,14 @@ typedef struct {
   const float* rs_bias;       // optional, added once after the sum
   const void* rs_residual;    // optional bf16 [batch * Tl, N]
   long long rs_ld_res;
+  // kItbTpBroadcast (together with kItbTpScatter): the summed rows are written to every rank's full
+  // [batch * T, N] bf16 buffer instead of rs_out -- a GEMM + all-reduce.  A consumer waits for
+  // `*ar_total` arrivals of every rank on ar_arrive (itb_tp_wait) before it reads the buffer.
+  ItbPeerPtrs ar_out;
+  void* ar_mc;
+  ItbPeerPtrs ar_arrive;      // int32[world] on each rank
+  int* ar_total;              // this GPU
+  int ar_lag;
 } ItbTpArgs;
 
 // `gemm` is an ItbGemmArgs (kernels/kernels.h); bf16 output only.  With kItbTpScatter the GEMM's own

@@ -151,19 +151,28 @@ void tp_gemm(const at::Tensor& a, bool a_mn, const at::Tensor& b, bool b_mn, int
     t.rs_arrive = dict_ptrs(tp, "rs_arrive");
     t.rs_total = dict_tensor_ptr<int>(tp, "rs_total");
     t.rs_lag = dict_int(tp, "rs_lag", 1 << 24);
-    at::Tensor out = tp["rs_out"].cast<at::Tensor>();
-    TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(0) == static_cast<int64_t>(t.batch) * t.Tl &&
-                    out.size(1) == N &&
-                    (out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat),
-                "tp_gemm: rs_out must be [batch * Tl, N] bf16 or fp32");
-    t.rs_out = out.data_ptr();
-    t.rs_ld_out = out.stride(0);
-    t.rs_out_f32 = out.scalar_type() == at::kFloat;
+    const int64_t rows_local = static_cast<int64_t>(t.batch) * t.Tl;
+    if (t.mode & kItbTpBroadcast) {
+      t.ar_out = dict_ptrs(tp, "ar_out");
+      t.ar_mc = reinterpret_cast<void*>(tp.contains("ar_mc") ? tp["ar_mc"].cast<int64_t>() : 0);
+      t.ar_arrive = dict_ptrs(tp, "ar_arrive");
+      t.ar_total = dict_tensor_ptr<int>(tp, "ar_total");
+      t.ar_lag = dict_int(tp, "ar_lag", 1 << 24);
+      TORCH_CHECK(t.ar_total, "tp_gemm: ar_total is required");
+    } else {
+      at::Tensor out = tp["rs_out"].cast<at::Tensor>();
+      TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(0) == rows_local && out.size(1) == N &&
+                      (out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat),
+                  "tp_gemm: rs_out must be [batch * Tl, N] bf16 or fp32");
+      t.rs_out = out.data_ptr();
+      t.rs_ld_out = out.stride(0);
+      t.rs_out_f32 = out.scalar_type() == at::kFloat;
+    }
     t.rs_bias = dict_tensor_ptr<const float>(tp, "rs_bias");
     if (tp.contains("rs_residual") && !tp["rs_residual"].is_none()) {
       at::Tensor res = tp["rs_residual"].cast<at::Tensor>();
       TORCH_CHECK(res.scalar_type() == at::kBFloat16 && res.dim() == 2 && res.stride(1) == 1 &&
-                      res.size(0) == out.size(0) && res.size(1) == N,
+                      res.size(0) == rows_local && res.size(1) == N,
                   "tp_gemm: rs_residual must be bf16 [batch * Tl, N]");
       t.rs_residual = res.data_ptr();
       t.rs_ld_res = res.stride(0);
@@ -219,6 +228,7 @@ void bind_comm(pybind11::module_& m) {
   m.attr("TP_PUSH") = static_cast<int>(kItbTpPush);
   m.attr("TP_GATE_A") = static_cast<int>(kItbTpGateA);
   m.attr("TP_SCATTER") = static_cast<int>(kItbTpScatter);
+  m.attr("TP_BROADCAST") = static_cast<int>(kItbTpBroadcast);
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_wait", &tp_wait);
   m.def("wait_flag", &wait_flag);

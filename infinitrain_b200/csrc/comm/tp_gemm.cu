@@ -10,6 +10,8 @@
 //     rows stored straight into the owner rank's slab for this source, the owner's rows last; when
 //     a rank has run out of tiles it waits for the slabs of every source and sums them in fp32
 //     with bias and residual;
+//   * GEMM + all-reduce (tensor parallelism without sequence parallelism): the scattering GEMM whose
+//     closing phase writes the summed rows to every rank (`multimem.st` or peer stores);
 //   * the same push in front of a scattering GEMM, for the backward pass of a column-parallel
 //     linear: dX = reduce-scatter(dY W) while X is re-gathered for the weight gradient that follows
 //     (itb_tp_wait holds that GEMM back until the shards have arrived).
@@ -145,7 +147,13 @@ extern "C" int itb_tp_gemm(const void* gemm, const ItbTpArgs* t, cudaStream_t st
     d.push_arrive[r] = static_cast<int*>(t->push_arrive.p[r]);
     d.slab[r] = static_cast<__nv_bfloat16*>(t->slab.p[r]);
     d.rs_arrive[r] = static_cast<int*>(t->rs_arrive.p[r]);
+    d.ar_out[r] = static_cast<__nv_bfloat16*>(t->ar_out.p[r]);
+    d.ar_arrive[r] = static_cast<int*>(t->ar_arrive.p[r]);
   }
+  d.ar_mc = static_cast<uint4*>(t->ar_mc);
+  d.ar_total = t->ar_total;
+  d.ar_lag = t->ar_lag;
+  if ((t->mode & kTpBroadcast) && (!scatter || !d.ar_total || !d.ar_out[0])) return -10;
   d.launch_ctr = t->launch_ctr;
   d.cta_done = t->cta_done;
   d.err = a->err;
@@ -165,7 +173,7 @@ extern "C" int itb_tp_gemm(const void* gemm, const ItbTpArgs* t, cudaStream_t st
   d.rs_bias = t->rs_bias;
   d.rs_residual = static_cast<const __nv_bfloat16*>(t->rs_residual);
   d.rs_ld_res = t->rs_ld_res;
-  if (scatter && ((reinterpret_cast<uintptr_t>(d.rs_out) & 15) || (d.rs_ld_out % 8) ||
+  if (scatter && !(t->mode & kTpBroadcast) && ((reinterpret_cast<uintptr_t>(d.rs_out) & 15) || (d.rs_ld_out % 8) ||
                   (d.rs_residual && ((reinterpret_cast<uintptr_t>(d.rs_residual) & 15) || (d.rs_ld_res % 8)))))
     return -9;
 

@@ -35,7 +35,7 @@ constexpr uint32_t kTmemCols = 512;                            // two 256-column
 // ---- tensor-parallel hooks -------------------------------------------------------------------
 // Rows of the full activation are (b, t) pairs, row = b * T + t; under sequence parallelism rank s
 // holds t in [s * Tl, (s + 1) * Tl) of every b as local row b * Tl + (t - s * Tl).
-enum { kTpPush = 1, kTpGateA = 2, kTpScatter = 4 };
+enum { kTpPush = 1, kTpGateA = 2, kTpScatter = 4, kTpBroadcast = 8 };
 constexpr int kTpMaxRanks = 8;
 constexpr unsigned kTpSpinLimit = 1u << 23;     // polls with a short sleep: seconds of skew
 
@@ -73,6 +73,13 @@ struct TpDev {
   const float* rs_bias;
   const __nv_bfloat16* rs_residual;
   long long rs_ld_res;
+  // broadcast (with scatter): the summed rows go to every rank's full [batch * T, N] bf16 buffer
+  // instead of rs_out, which turns the reduce-scatter into an all-reduce
+  __nv_bfloat16* ar_out[kTpMaxRanks];
+  uint4* ar_mc;             // multicast address of that buffer, or null
+  int* ar_arrive[kTpMaxRanks];     // counters [world] on each rank: CTAs of rank s that have delivered
+  int* ar_total;            // this GPU: arrivals per source that the launches so far add up to
+  int ar_lag;
 };
 
 __device__ __forceinline__ void tp_st_release_sys(int* p, int v) {
@@ -320,6 +327,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         int lag = 1 << 24;
         if (tp.mode & kTpPush) lag = min(lag, tp.push_lag);
         if (tp.mode & kTpScatter) lag = min(lag, tp.rs_lag);
+        if (tp.mode & kTpBroadcast) lag = min(lag, tp.ar_lag);
         bool ok = true;
         if (lane < tp.world) ok = tp_wait_ge(tp.started[tp.rank] + lane, tp_launch - lag + 2);
         tp_ok = __all_sync(0xffffffffu, ok);
@@ -558,7 +566,21 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[e] += __bfloat162float(b[e]);
           }
-          if (tp.rs_out_f32) {
+          if (tp.mode & kTpBroadcast) {
+            // local row -> row of the full activation; every rank receives the 16 bytes
+            const long long bb = row / tp.Tl, tt = row - bb * tp.Tl;
+            const long long idx = (bb * tp.T + tp.rank * tp.Tl + tt) * nv + c8;     // in 16-byte units
+            const uint4 u = pack8_bf16(acc);
+            if (tp.ar_mc) {
+              asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(tp.ar_mc + idx),
+                           "f"(__uint_as_float(u.x)), "f"(__uint_as_float(u.y)), "f"(__uint_as_float(u.z)),
+                           "f"(__uint_as_float(u.w))
+                           : "memory");
+            } else {
+              for (int d = 0; d < tp.world; ++d)
+                reinterpret_cast<uint4*>(tp.ar_out[(tp.rank + d) % tp.world])[idx] = u;
+            }
+          } else if (tp.rs_out_f32) {
             float* o = static_cast<float*>(tp.rs_out) + row * tp.rs_ld_out + c8 * 8;
             *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
             *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
@@ -568,6 +590,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           }
         }
       }
+    }
+    if (tp.mode & kTpBroadcast) {
+      // this CTA's share of the summed rows has left: count it on every rank
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x < tp.world) tp_red_release_sys(tp.ar_arrive[threadIdx.x] + tp.rank, 1);
     }
     // the last CTA to get here advances this GPU's counters for the next launch
     __threadfence();
@@ -579,6 +607,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         *tp.launch_ctr = tp_launch + 1;
         if (tp.mode & kTpPush) *tp.push_total += static_cast<int>(gridDim.x) * 4;
         if (tp.mode & kTpScatter) *tp.rs_total += (tp.batch * tp.Tl / 256) * p.tiles_n * 8;
+        if (tp.mode & kTpBroadcast) *tp.ar_total += static_cast<int>(gridDim.x);
         __threadfence();
       }
     }

@@ -254,10 +254,10 @@ class TpFusedContext:
         return (self.launch_index - b.last_use) if b.last_use is not None else (1 << 24)
 
     def launch(self, a, a_mn, b, b_mn, M, N, K, c, c2, bias, aux, flags, *, batch, T, push=None, push_src=None,
-               gate=None, gate_includes=1, slab=None, rs_out=None, rs_bias=None, rs_residual=None):
+               gate=None, gate_includes=1, slab=None, rs_out=None, rs_bias=None, rs_residual=None, bcast=None):
         C = self.C
         mode = (C.TP_PUSH if push is not None else 0) | (C.TP_GATE_A if gate is not None else 0) | \
-               (C.TP_SCATTER if slab is not None else 0)
+               (C.TP_SCATTER if slab is not None else 0) | (C.TP_BROADCAST if bcast is not None else 0)
         tp = {"mode": mode, "rank": self.rank, "world": self.world, "T": T, "Tl": T // self.world, "batch": batch,
               "started": self.flag_ptrs, "launch_ctr": self.launch_ctr, "cta_done": self.cta_done}
         if push is not None:
@@ -268,9 +268,12 @@ class TpFusedContext:
         if slab is not None:
             tp.update(slab=slab.ptrs, rs_arrive=slab.arrive_ptrs, rs_total=slab.total, rs_lag=self._lag(slab),
                       rs_out=rs_out, rs_bias=rs_bias, rs_residual=rs_residual)
+        if bcast is not None:
+            tp.update(ar_out=bcast.ptrs, ar_mc=bcast.mc, ar_arrive=bcast.arrive_ptrs, ar_total=bcast.total,
+                      ar_lag=self._lag(bcast))
         C.tp_gemm(a, a_mn, b, b_mn, M, N, K, c, c2, bias, aux, flags, tp, self.nvl.err)
         ops._counters["launches"] += 1
-        for bf in (push, gate, slab):
+        for bf in (push, gate, slab, bcast):
             if bf is not None:
                 bf.last_use = self.launch_index
         if push is not None:
@@ -480,6 +483,126 @@ class VocabCEMerge:
                            nvl.err, nvl.epoch_ctr)
         ops._counters["launches"] += 1
         return lse, loss
+
+
+class _LinearAllReduceFn(torch.autograd.Function):
+    """y[B, T, N] = all_reduce(x[B, T, K/tp] W^T) + bias (+ residual) for tensor parallelism without
+    sequence parallelism: the GEMM's partial rows go to their owner rank, which sums them and writes
+    the result to every rank -- one launch.  Backward needs no communication."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        tp = _TP_CTX
+        B, T, K = x.shape
+        N = weight.shape[0]
+        M = B * T
+        x2 = ops._as_bf16_2d(x)
+        w = ops.weight_lp(weight)
+        slab = tp.buf("slab", M * N)
+        full = tp.buf("allreduce", M * N)
+        tp.launch(x2, False, w, False, M, N, K, None, None, None, None, 0, batch=B, T=T, slab=slab, rs_bias=bias,
+                  bcast=full)
+        tp.wait_arrivals(full)
+        # leave the workspace at once: the next launch of the group writes into it again
+        y = full.t.view(M, N)
+        y = y.clone() if residual is None else y + residual.reshape(M, N).to(torch.bfloat16)
+        ctx.save_for_backward(x2, weight)
+        ctx.dims = (B, T, M, N, K)
+        ctx.has_bias, ctx.has_res, ctx.x_dtype = bias is not None, residual is not None, x.dtype
+        ctx.res_dtype = residual.dtype if residual is not None else None
+        return y.view(B, T, N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _TP_CTX.C
+        x2, weight = ctx.saved_tensors
+        B, T, M, N, K = ctx.dims
+        dy2 = ops._as_bf16_2d(dy)
+        dx = dw = db = dres = None
+        if ctx.needs_input_grad[0]:
+            dx2 = torch.empty((M, K), device=dy.device, dtype=torch.bfloat16)
+            C.gemm(dy2, False, ops.weight_lp(weight), True, M, K, N, dx2, None, None, None, None, 0, 0)
+            ops._counters["launches"] += 1
+            dx = dx2.view(B, T, K)
+            if ctx.x_dtype != torch.bfloat16:
+                dx = dx.to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = ops._wgrad(C, dy2, x2, weight, N, K, M)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = ops._bias_grad(C, dy2, N)
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = dy if dy.dtype == ctx.res_dtype else dy.to(ctx.res_dtype)
+        return dx, dw, db, dres
+
+
+class _CopyLinearFn(torch.autograd.Function):
+    """Column-parallel linear on an input every rank holds in full (no sequence parallelism):
+    y = x W^T + b needs no communication forward; backward computes dX = all_reduce(dY W) as one
+    GEMM + all-reduce launch."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, gelu):
+        C = _TP_CTX.C
+        B, T, K = x.shape
+        N = weight.shape[0]
+        M = B * T
+        x2 = ops._as_bf16_2d(x)
+        w = ops.weight_lp(weight)
+        ld = ops._pad_cols(N)
+        out = torch.empty((M, ld), device=x.device, dtype=torch.bfloat16)
+        flags = C.GEMM_BIAS if bias is not None else 0
+        pre = None
+        if gelu:
+            pre = torch.empty((M, ld), device=x.device, dtype=torch.bfloat16)
+            C.gemm(x2, False, w, False, M, N, K, pre, out, bias, None, None, flags | C.GEMM_GELU_DUAL, 0)
+        else:
+            C.gemm(x2, False, w, False, M, N, K, out, None, bias, None, None, flags, 0)
+        ops._counters["launches"] += 1
+        ctx.save_for_backward(x2, weight, pre)
+        ctx.dims = (B, T, M, N, K, ld)
+        ctx.has_bias, ctx.gelu, ctx.x_dtype = bias is not None, gelu, x.dtype
+        y = out[:, :N] if ld != N else out
+        return y.view(B, T, N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        tp = _TP_CTX
+        C = tp.C
+        x2, weight, pre = ctx.saved_tensors
+        B, T, M, N, K, ld = ctx.dims
+        dy2 = ops._as_bf16_2d(dy)
+        if ctx.gelu:
+            dyc = dy2 if dy2.is_contiguous() else dy2.contiguous()
+            prec = pre[:, :N] if ld != N else pre
+            dy2 = C.gelu_bwd(dyc, prec if prec.is_contiguous() else prec.contiguous())
+            ops._counters["launches"] += 1
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            slab = tp.buf("slab", M * K)
+            full = tp.buf("allreduce", M * K)
+            tp.launch(dy2, False, ops.weight_lp(weight), True, M, K, N, None, None, None, None, 0, batch=B, T=T,
+                      slab=slab, bcast=full)
+            tp.wait_arrivals(full)
+            dx = full.t.view(B, T, K).clone()
+            if ctx.x_dtype != torch.bfloat16:
+                dx = dx.to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = ops._wgrad(C, dy2, x2, weight, N, K, M)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = ops._bias_grad(C, dy2, N)
+        return dx, dw, db, None
+
+
+def linear_all_reduce(x, weight, bias, residual):
+    if _TP_CTX is None:
+        raise RuntimeError("fused tensor-parallel kernels are not initialised")
+    return _LinearAllReduceFn.apply(x, weight, bias, residual)
+
+
+def copy_linear(x, weight, bias, gelu=False):
+    if _TP_CTX is None:
+        raise RuntimeError("fused tensor-parallel kernels are not initialised")
+    return _CopyLinearFn.apply(x, weight, bias, gelu)
 
 
 def allgather_linear(x, weight, bias, gelu=False):

@@ -211,6 +211,10 @@ class ColumnParallelLinear(Module):
         add_bias = self.bias if (self.has_bias and not self.skip_bias_add) else None
         if self.sequence_parallel and symm.fused_tp_enabled(x):
             y = symm.allgather_linear(x, self.weight, add_bias, gelu=gelu)
+        elif (not self.sequence_parallel and not self.input_is_parallel and _tp() is not None
+              and symm.fused_tp_enabled(x, seq_sharded=False)):
+            # replicated input: no communication forward, the gradient all-reduce is fused into dgrad
+            y = symm.copy_linear(x, self.weight, add_bias, gelu=gelu)
         else:
             if self.sequence_parallel:
                 x = GatherFromSPRegionFunc(x)
@@ -262,6 +266,8 @@ class RowParallelLinear(Module):
             y = ops.linear(x, self.weight, add_bias, residual=residual)
         elif self.sequence_parallel and symm.fused_tp_enabled(x, seq_sharded=False):
             y = symm.linear_reduce_scatter(x, self.weight, add_bias, residual)
+        elif not self.sequence_parallel and symm.fused_tp_enabled(x, seq_sharded=False):
+            y = symm.linear_all_reduce(x, self.weight, add_bias, residual)
         else:
             y = ops.linear(x, self.weight, None)
             y = ReduceScatterToSPRegionFunc(y) if self.sequence_parallel else ReduceFromTPRegionFunc(y)

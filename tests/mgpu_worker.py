@@ -218,6 +218,69 @@ def tp_fused():
         print(f"TP FUSED OK worst_rel={t.item():.2e}")
 
 
+def tp_fused_nosp():
+    """Tensor parallelism without sequence parallelism: the GEMM + all-reduce launches (row-parallel
+    forward, column-parallel backward) against the NCCL formulation."""
+    import torch.distributed as dist
+
+    from infinitrain_b200.autocast import AutocastGuard
+    from infinitrain_b200.datatype import DataType
+    from infinitrain_b200.device import DeviceType
+    from infinitrain_b200.parallel import global_env as genv
+    from infinitrain_b200.parallel import symm
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory
+    from infinitrain_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    genv.InitAllEnv(world_size=world, rank=rank, tensor_parallel_size=world, sequence_parallel_enabled=False)
+    ProcessGroupFactory.Instance().Init(device=dev, timeout_s=120)
+    B, T, H, F = 2, 256 * world, 512, 1024 * world
+    col = ColumnParallelLinear(H, F, bias=True, gather_output=False, input_is_parallel=False, device=dev)
+    row = RowParallelLinear(F, H, bias=True, input_is_parallel=True, device=dev)
+    torch.manual_seed(100 + rank)
+    params = list(col.Parameters()) + list(row.Parameters())
+    for prm in params:
+        prm.data.normal_(0, 0.05)
+    dist.broadcast(row.bias.data, 0)           # a replicated parameter
+    results = {}
+    for fused in ("0", "1"):
+        os.environ["ITB_FUSED_TP"] = fused
+        symm.reset_fused_tp()
+        outs = []
+        for it in range(3):
+            torch.manual_seed(1000 + it)       # activations are replicated: same on every rank
+            x = (torch.randn(B, T, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
+            res = (torch.randn(B, T, H, device=dev) * 0.5).bfloat16().requires_grad_(True)
+            gy = (torch.randn(B, T, H, device=dev) * 0.1).bfloat16()
+            for prm in params:
+                prm.grad = None
+            with AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16):
+                y = row(col(x, gelu=(it % 2 == 1)), residual=res)
+            assert y.shape == (B, T, H)
+            y.backward(gy)
+            outs.append([y.detach().float(), x.grad.float(), res.grad.float()] + [p.grad.float().clone() for p in params])
+        torch.cuda.synchronize()
+        results[fused] = outs
+        if fused == "1":
+            assert symm._TP_CTX is not None and symm._TP_CTX.nvl.status() == 0
+            assert symm._TP_CTX.launch_index == 6, symm._TP_CTX.launch_index
+    worst = 0.0
+    names = ["y", "dx", "dres", "col.dw", "col.db", "row.dw", "row.db"]
+    for it, (a_it, b_it) in enumerate(zip(results["0"], results["1"])):
+        for name, a, b in zip(names, a_it, b_it):
+            rel = ((a - b).norm() / (a.norm() + 1e-6)).item()
+            if rel > 2e-2:
+                print(f"[rank {rank}] iteration {it} {name}: rel {rel:.3e}", flush=True)
+            worst = max(worst, rel)
+    t = torch.tensor([worst], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    assert t.item() < 2e-2, t.item()
+    if rank == 0:
+        print(f"TP NOSP OK worst_rel={t.item():.2e}")
+
+
 def vocab_ce():
     """Vocab-parallel cross-entropy: the NVLink merge kernel against the all-gather formulation and
     against the loss over the gathered full-vocabulary logits."""
@@ -269,6 +332,8 @@ def vocab_ce():
 if __name__ == "__main__":
     if sys.argv[1] == "vocab_ce":
         vocab_ce()
+    elif sys.argv[1] == "tp_fused_nosp":
+        tp_fused_nosp()
     elif sys.argv[1] == "collectives":
         collectives()
     elif sys.argv[1] == "tp_fused":

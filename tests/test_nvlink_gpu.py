@@ -62,3 +62,11 @@ def test_vocab_parallel_cross_entropy_merge_kernel():
     os.environ["ITB_NVLS"] = "1"
     out = _torchrun("mgpu_worker.py", 2, "vocab_ce")
     assert "VOCAB CE OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fused_gemm_all_reduce_matches_nccl(nvls):
+    os.environ["ITB_NVLS"] = nvls
+    out = _torchrun("mgpu_worker.py", 2, "tp_fused_nosp")
+    assert "TP NOSP OK" in out
