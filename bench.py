@@ -25,12 +25,107 @@ import time
 BASELINE_TOKENS_PER_S = None  # the reference publishes no throughput number
 
 
+REF_STEP = None   # compiled lazily: the reference's own step line
+
+
 def reference_arm(args):
+    """Runs the UNMODIFIED reference (built by ``baseline/build_reference.py`` into ``baseline/_ref``)
+    through its stock ``example/gpt2`` trainer on the same shapes and prints the same JSON line.  The
+    reference is one process with one thread per GPU, so under torchrun only rank 0 launches it; its
+    step time is its own host clock around each step (which ends with the loss read-back), its
+    optimizer is the SGD that its example hard-codes."""
+    import re
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = os.path.join(here, "baseline", "_ref", "bin", "gpt2")
+    if args.model != "gpt2" or args.tp != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "only the GPT-2 124M data-parallel configuration is wired "
+                          "to the reference's stock trainer"}))
+        return 0
+    if not os.path.exists(exe) and os.path.isdir("/root/reference/infini_train"):
+        try:     # one-off offline build (nvcc, no GPU needed); see baseline/build_reference.py
+            subprocess.run([sys.executable, os.path.join(here, "baseline", "build_reference.py")], capture_output=True,
+                           text=True, timeout=1800)
+        except Exception:  # noqa: BLE001
+            pass
+    if not os.path.exists(exe):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/bin/gpt2 is not built: pip cannot install "
+                          "/root/reference (no setup.py / pyproject.toml); build it with python baseline/build_reference.py"}))
+        return 0
+    import numpy as np
+
+    n, B, T = args.gpus, args.batch or 16, args.seq or 1024
+    iters = args.warmup + args.steps
+    tok_path = f"/tmp/itb_ref_tokens_{os.getpid()}.bin"
+    n_tok = B * T * n * (iters + 2) + 1
+    rng = np.random.default_rng(1234)
+    header = np.zeros(256, dtype=np.int32)                 # llm.c token file: 1024-byte header, uint16 ids
+    header[0], header[1], header[2] = 20240520, 1, n_tok
+    with open(tok_path, "wb") as f:
+        f.write(header.tobytes())
+        f.write(rng.integers(0, 50257, size=n_tok, dtype=np.uint16).tobytes())
+    # "d12" is the stock trainer's from-scratch GPT-2 124M shape (12 layers, 12 heads, 768 wide); its
+    # "gpt2" name is only defined together with an llm.c weight file
+    cmd = [exe, "--input_bin", tok_path, "--model", "d12", "--batch_size", str(B), "--sequence_length", str(T),
+           "--total_batch_size", str(B * T * n), "--num_iteration", str(iters), "--dtype", "bfloat16",
+           "--nthread_per_process", str(n), "--learning_rate", "1e-4", "--freq_generate_txt", "1000000",
+           "--overfit_single_batch=false"]
+    if n > 1:
+        cmd += ["--zero_stage", str(args.zero)]
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "LOCAL_WORLD_SIZE", "GROUP_RANK"):
+        env.pop(k, None)
+    sampler = ClockSampler(0)
+    sampler.start()
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env,
+                           cwd=os.path.join(here, "baseline", "_ref"))
+    except subprocess.TimeoutExpired:
+        sampler.stop()
+        print(json.dumps({"impl": "reference", "unavailable": "the reference trainer did not finish within 1500 s"}))
+        return 0
+    finally:
+        try:
+            os.remove(tok_path)
+        except OSError:
+            pass
+    clocks = sampler.stop()
+    pat = re.compile(r"step\s+(\d+)/\d+\s+\|\s+train loss\s+([-0-9.eE+naif]+).*?\(\s*([0-9.]+)\s*ms\s*\|\s*([0-9.]+)\s*tok/s")
+    steps = {}
+    for line in (r.stdout + "\n" + r.stderr).splitlines():
+        m = pat.search(line)
+        if m:
+            steps[int(m.group(1))] = (float(m.group(2)), float(m.group(3)))
+    timed = [steps[i][1] for i in range(args.warmup + 1, iters + 1) if i in steps]
+    if r.returncode != 0 or len(timed) != args.steps:
+        tail = (r.stderr or r.stdout).strip().splitlines()[-1:] or [""]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference trainer exited with code {r.returncode} "
+                          f"after {len(steps)} of {iters} steps: {tail[0][:200]}"}))
+        return 0
+    ms = sum(timed)
+    value = B * T * n * args.steps / (ms / 1e3)
     print(json.dumps({
         "impl": "reference",
-        "unavailable": "pip install of /root/reference failed: the directory is not installable (neither setup.py "
-                       "nor pyproject.toml; it is a CMake C++ project whose glog/gflags/eigen submodules are empty)",
-    }))
+        "metric": "tokens/sec GPT-2 124M training (bf16 autocast, AdamW, DDP + ZeRO-2 for N>1), max over ranks",
+        "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic uniform token ids (llm.c token file), random-init weights",
+        "config": {"model": "GPT-2 124M (reference example/gpt2, --model d12: 12L, 12H, 768, vocab 50257, ctx 1024)", "global_batch": B * n,
+                   "micro_batch_per_gpu": B, "seq_len": T,
+                   "parallelism": "single" if n == 1 else f"dp{n}+zero{args.zero} (threads of one process)",
+                   "optimizer": "SGD lr 1e-4 (hard-coded in the reference's example/gpt2/main.cc)",
+                   "timing": "the reference's own host clock around each step; a step ends with the loss read-back",
+                   "l2": "inputs larger than L2"},
+        "clocks": clocks,
+        "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms / args.steps,
+                "h2d_bytes_per_step": 2 * B * T * 8, "d2h_bytes_per_step": 4,
+                "note": "the reference's loop copies each batch from host memory and reads the loss back every step, so "
+                        "its only timing is end to end"},
+        "gpu_launches": None, "final_loss": steps[iters][0],
+    }), flush=True)
     return 0
 
 
