@@ -10,7 +10,8 @@ Rank 0 prints ONE JSON line.  ``value`` is device-timed (CUDA events around the 
 ranks, inputs resident on the device); ``e2e`` repeats the measurement through the public training
 API with, every step, the host->device copy of that step's tokens from pinned memory and a
 device->host read of the loss.  Data are synthetic uniform token ids; weights are random-init.
-``--impl reference`` reports why the reference arm is unavailable on this machine.
+``--impl reference`` runs the unmodified reference's stock GPT-2 trainer (built by
+``baseline/build_reference.py``) on the same shapes and prints the same line.
 """
 from __future__ import annotations
 
@@ -76,7 +77,10 @@ def reference_arm(args):
     if n > 1:
         cmd += ["--zero_stage", str(args.zero)]
     env = dict(os.environ)
-    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "LOCAL_WORLD_SIZE", "GROUP_RANK"):
+    # the launcher's rendezvous variables mean nothing to the reference, and its OMP_NUM_THREADS=1 would
+    # throttle the reference's host-side loops
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "LOCAL_WORLD_SIZE", "GROUP_RANK",
+              "OMP_NUM_THREADS"):
         env.pop(k, None)
     sampler = ClockSampler(0)
     sampler.start()
