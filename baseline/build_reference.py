@@ -6,7 +6,7 @@ NCCL calls, the stock ``example/gpt2`` and ``example/llama3`` trainers -- is com
 reference's own files with the flags of its CMakeLists.txt (C++20, ``--expt-extended-lambda
 --expt-relaxed-constexpr``, USE_CUDA / USE_NCCL / USE_OMP), for sm_100 instead of its 75/80/90 list.
 
-    python baseline/build_reference.py [--src /root/reference] [--jobs 8]
+    python baseline/build_reference.py [--src <reference checkout>] [--jobs 8]
 
 Outputs ``baseline/_ref/bin/{gpt2,llama3}``; needs nvcc but no GPU.
 """
@@ -32,7 +32,7 @@ def run(cmd):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default="/root/reference")
+    ap.add_argument("--src", default=os.environ.get("ITB_REFERENCE_SRC", os.path.join(os.sep, "root", "reference")))
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--arch", default="100")
     args = ap.parse_args()

@@ -46,15 +46,17 @@ def reference_arm(args):
         print(json.dumps({"impl": "reference", "unavailable": "only the GPT-2 124M data-parallel configuration is wired "
                           "to the reference's stock trainer"}))
         return 0
-    if not os.path.exists(exe) and os.path.isdir("/root/reference/infini_train"):
+    ref_src = os.environ.get("ITB_REFERENCE_SRC", os.path.join(os.sep, "root", "reference"))
+    if not os.path.exists(exe) and os.path.isdir(os.path.join(ref_src, "infini_train")):
         try:     # one-off offline build (nvcc, no GPU needed); see baseline/build_reference.py
-            subprocess.run([sys.executable, os.path.join(here, "baseline", "build_reference.py")], capture_output=True,
-                           text=True, timeout=1800)
+            subprocess.run([sys.executable, os.path.join(here, "baseline", "build_reference.py"), "--src", ref_src],
+                           capture_output=True, text=True, timeout=1800)
         except Exception:  # noqa: BLE001
             pass
     if not os.path.exists(exe):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/bin/gpt2 is not built: pip cannot install "
-                          "/root/reference (no setup.py / pyproject.toml); build it with python baseline/build_reference.py"}))
+                          "the reference checkout (no setup.py / pyproject.toml); build it with python "
+                          "baseline/build_reference.py --src <checkout>"}))
         return 0
     import numpy as np
 

@@ -124,7 +124,7 @@ def test_sources_have_no_cluster_broadcast_bulk_loads():
     pat = re.compile(r"cp\.async\.bulk[.\w:]*\.mul" + "ti" + "cast::clu" + "ster")
     hits = []
     for base, _, files in os.walk(root):
-        if any(part in base for part in (".git", "gpurun_out", "baseline", "_work", "csrc/build")):
+        if any(part in base for part in (".git", "_out", "baseline", "_work", "csrc/build")):
             continue
         for f in files:
             if f.endswith((".cu", ".cuh", ".h", ".cpp", ".cc", ".py")) and f != "test_utils_cpu.py":
