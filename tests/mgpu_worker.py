@@ -281,6 +281,63 @@ def tp_fused_nosp():
         print(f"TP NOSP OK worst_rel={t.item():.2e}")
 
 
+def tp_model():
+    """A small LLaMA-3-shaped model under TP + SP trained for a few steps: the loss trajectory with the
+    fused all-gather+GEMM / GEMM+reduce-scatter / CE-merge kernels against the NCCL formulation of the
+    same model from the same weights."""
+    import torch.distributed as dist
+
+    from infinitrain_b200.autocast import AutocastGuard
+    from infinitrain_b200.datatype import DataType
+    from infinitrain_b200.device import DeviceType
+    from infinitrain_b200.models import LLaMA3
+    from infinitrain_b200.nn import init
+    from infinitrain_b200.optim import Adam
+    from infinitrain_b200.parallel import global_env as genv
+    from infinitrain_b200.parallel import symm
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory
+    from infinitrain_b200.parallel.tensor_parallel import AllReduceSequenceParallelGrads, VocabParallelCrossEntropyLoss
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    genv.InitAllEnv(world_size=world, rank=rank, tensor_parallel_size=world, sequence_parallel_enabled=True)
+    ProcessGroupFactory.Instance().Init(device=dev, timeout_s=120)
+    B, T, V, steps = 2, 256 * world, 2048, 4
+    g = torch.Generator().manual_seed(5)
+    x = torch.randint(0, V, (B, T), generator=g).to(dev)
+    y = torch.randint(0, V, (B, T), generator=g).to(dev)
+    curves = {}
+    for fused in ("0", "1"):
+        os.environ["ITB_FUSED_TP"] = fused
+        symm.reset_fused_tp()
+        torch.manual_seed(0)
+        init.manual_seed(42 + rank)
+        model = LLaMA3("llama3-1b", n_layer=2, n_embd=512, n_head=8, n_kv_head=4, vocab_size=V, original_vocab_size=V,
+                       block_size=T).to(dev)
+        loss_fn = VocabParallelCrossEntropyLoss(V)
+        opt = Adam(model.Parameters(), 1e-3)
+        out = []
+        for _ in range(steps):
+            opt.ZeroGrad()
+            with AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16):
+                loss = loss_fn(model(x), y)
+            loss.backward()
+            AllReduceSequenceParallelGrads(model)
+            opt.Step()
+            out.append(loss.detach().float().clone())
+        torch.cuda.synchronize()
+        curves[fused] = torch.stack(out)
+        if fused == "1":
+            assert symm._TP_CTX is not None and symm._TP_CTX.nvl.status() == 0
+            assert symm._TP_CTX.launch_index > 0
+    a, b = curves["0"], curves["1"]
+    assert a[-1] < a[0] and b[-1] < b[0], (a.tolist(), b.tolist())
+    assert (a - b).abs().max().item() < 5e-2, (a.tolist(), b.tolist())
+    if rank == 0:
+        print(f"TP MODEL OK nccl={[round(v, 4) for v in a.tolist()]} fused={[round(v, 4) for v in b.tolist()]}")
+
+
 def vocab_ce():
     """Vocab-parallel cross-entropy: the NVLink merge kernel against the all-gather formulation and
     against the loss over the gathered full-vocabulary logits."""
@@ -334,6 +391,8 @@ if __name__ == "__main__":
         vocab_ce()
     elif sys.argv[1] == "tp_fused_nosp":
         tp_fused_nosp()
+    elif sys.argv[1] == "tp_model":
+        tp_model()
     elif sys.argv[1] == "collectives":
         collectives()
     elif sys.argv[1] == "tp_fused":

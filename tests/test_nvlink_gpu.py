@@ -70,3 +70,10 @@ def test_fused_gemm_all_reduce_matches_nccl(nvls):
     os.environ["ITB_NVLS"] = nvls
     out = _torchrun("mgpu_worker.py", 2, "tp_fused_nosp")
     assert "TP NOSP OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tp_sp_model_training_fused_matches_nccl():
+    os.environ["ITB_NVLS"] = "1"
+    out = _torchrun("mgpu_worker.py", 2, "tp_model")
+    assert "TP MODEL OK" in out
