@@ -267,7 +267,19 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Driver-API calls need a context bound to the calling thread.  A thread that has only been handed
+// work (an autograd worker whose first CUDA operation is one of these GEMMs, on device 0 where no
+// cudaSetDevice was needed) has none yet; one runtime call binds the primary context.
+static void ensure_context_on_this_thread() {
+  thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 static EncodeTiledFn get_encode_fn() {
+  ensure_context_on_this_thread();
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {

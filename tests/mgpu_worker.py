@@ -338,6 +338,56 @@ def tp_model():
         print(f"TP MODEL OK nccl={[round(v, 4) for v in a.tolist()]} fused={[round(v, 4) for v in b.tolist()]}")
 
 
+def pp_gpu():
+    """Two pipeline stages on two GPUs, bf16 autocast, virtual stages: the interleaved 1F1B and the
+    GPipe order of the same micro-batches give the same loss trajectory, and it decreases."""
+    import hashlib
+    import re
+
+    from infinitrain_b200.datatype import DataType
+    from infinitrain_b200.nn import CrossEntropyLoss
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+    from infinitrain_b200.optim import SGD
+    from infinitrain_b200.parallel import global_env as genv
+    from infinitrain_b200.parallel.pp.pipeline_parallel import PipelineParallel
+    from infinitrain_b200.parallel.process_group import ProcessGroupFactory
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    vpp = 2
+    genv.InitAllEnv(world_size=world, rank=rank, pipeline_parallel_size=world, virtual_pipeline_parallel=vpp)
+    ProcessGroupFactory.Instance().Init(device=dev, timeout_s=120)
+    cfg = TransformerConfig.LLaMA3(n_layer=4, n_embd=256, n_head=4, n_kv_head=2, vocab_size=512, original_vocab_size=512,
+                                   block_size=128, multiple_of=64)
+    B, T, n_mb, steps = 8, 128, 4, 3
+    g = torch.Generator().manual_seed(1)
+    x = torch.randint(0, 512, (B, T), generator=g).to(dev)
+    y = torch.randint(0, 512, (B, T), generator=g).to(dev)
+    curves = {}
+    for schedule in ("1f1b", "gpipe"):
+        model = TransformerModel(cfg).to(dev)
+        offs = [l for (s0, e0) in sorted(model.stage_info.layer_ranges_per_chunk) for l in range(s0, e0)]
+        with torch.no_grad():
+            for name, p in model.StateDict().items():
+                m = re.match(r"transformer\.h\.(\d+)\.(.*)", name)
+                gname = f"transformer.h.{offs[int(m.group(1))]}.{m.group(2)}" if m else name
+                gen = torch.Generator().manual_seed(int(hashlib.md5(gname.encode()).hexdigest()[:8], 16))
+                p.copy_((torch.randn(p.shape, generator=gen) * 0.05 + (1.0 if p.dim() == 1 else 0.0)).to(dev))
+        pp = PipelineParallel(model, world, n_mb, [B // n_mb, T, cfg.n_embd], rank, dev, vpp, schedule=schedule)
+        opt = SGD(pp.Parameters(), 0.05)
+        out = []
+        for _ in range(steps):
+            out.append(float(pp.TrainStep([x], [y], opt, CrossEntropyLoss(), DataType.kBFLOAT16)))
+        torch.cuda.synchronize()
+        curves[schedule] = out
+    if rank == world - 1:
+        a, b = curves["1f1b"], curves["gpipe"]
+        assert all(v == v for v in a) and a[-1] < a[0], a
+        assert max(abs(u - v) for u, v in zip(a, b)) < 2e-2, (a, b)
+        print(f"PP GPU OK 1f1b={[round(v, 4) for v in a]} gpipe={[round(v, 4) for v in b]}")
+
+
 def vocab_ce():
     """Vocab-parallel cross-entropy: the NVLink merge kernel against the all-gather formulation and
     against the loss over the gathered full-vocabulary logits."""
@@ -393,6 +443,8 @@ if __name__ == "__main__":
         tp_fused_nosp()
     elif sys.argv[1] == "tp_model":
         tp_model()
+    elif sys.argv[1] == "pp_gpu":
+        pp_gpu()
     elif sys.argv[1] == "collectives":
         collectives()
     elif sys.argv[1] == "tp_fused":

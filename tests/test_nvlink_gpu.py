@@ -77,3 +77,9 @@ def test_tp_sp_model_training_fused_matches_nccl():
     os.environ["ITB_NVLS"] = "1"
     out = _torchrun("mgpu_worker.py", 2, "tp_model")
     assert "TP MODEL OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_pipeline_parallel_on_gpus():
+    out = _torchrun("mgpu_worker.py", 2, "pp_gpu")
+    assert "PP GPU OK" in out
