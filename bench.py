@@ -201,6 +201,8 @@ def main():
     ap.add_argument("--model", default="gpt2", help="gpt2 | llama3-1b | llama3-3b | llama3-8b")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (sequence parallelism on when > 1)")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the model's own)")
+    ap.add_argument("--kernel-table", default="", help="after the measurement, trace 2 more steps with torch.profiler "
+                    "on rank 0 and write the per-kernel device-time table to this file (analysis aid, not a metric)")
     ap.add_argument("--residual", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--graph", type=int, default=None,
                     help="capture the whole training step in a CUDA graph (default: 1 without tensor parallelism)")
@@ -351,6 +353,22 @@ def main():
     e2e_ms = e2.elapsed_time(e3)
     clocks = sampler.stop() if rank == 0 else None
 
+    if args.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+
+        barrier()
+        if rank == 0:
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for i in range(2):
+                    train_step(dev_x[i % n_host], dev_y[i % n_host])
+                torch.cuda.synchronize()
+            with open(args.kernel_table, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=70))
+        else:
+            for i in range(2):
+                train_step(dev_x[i % n_host], dev_y[i % n_host])
+            torch.cuda.synchronize()
+        barrier()
     if world > 1:
         t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
