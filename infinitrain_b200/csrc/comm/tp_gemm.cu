@@ -40,11 +40,10 @@ static int launch_tp(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
                      const CUtensorMap& te, const GemmDev& p, const TpDev& tp, int pairs, cudaStream_t stream) {
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, true>;
   constexpr int smem = kSmemTotal + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   kern<<<2 * pairs, kThreads, smem, stream>>>(ta, tb, tc, tc2, te, p, tp);
   return static_cast<int>(cudaGetLastError());

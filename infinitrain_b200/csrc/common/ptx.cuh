@@ -12,6 +12,19 @@
 
 namespace itb {
 
+// Kernel attributes (the dynamic shared-memory limit) are per device: remember per device, not per
+// process, whether a launcher has set them.  Returns true on the first call for the current device.
+struct PerDeviceOnce {
+  bool seen[64] = {};
+  bool first() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return true;
+    if (seen[d]) return false;
+    seen[d] = true;
+    return true;
+  }
+};
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -13,6 +13,7 @@
 #include <float.h>
 #include <stdint.h>
 
+#include "../common/ptx.cuh"
 #include "kernels.h"
 
 namespace itb {
@@ -502,12 +503,11 @@ flash_bwd_kernel(const ItbAttnArgs a) {
 template <int D>
 static int attn_fwd_launch(const ItbAttnArgs* a, cudaStream_t s) {
   constexpr int smem = 5 * 64 * D * 2;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   dim3 grid((a->T + kBlkM - 1) / kBlkM, a->H, a->B);
   flash_fwd_kernel<D><<<grid, kAttnThreads, smem, s>>>(*a);
@@ -517,12 +517,11 @@ static int attn_fwd_launch(const ItbAttnArgs* a, cudaStream_t s) {
 template <int D>
 static int attn_bwd_launch(const ItbAttnArgs* a, cudaStream_t s) {
   constexpr int smem = 6 * 64 * D * 2 + 64 * 64 * 2 + 4 * 64 * 4;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(flash_bwd_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   const long long nrow = static_cast<long long>(a->B) * a->T * a->H;
   cudaError_t e = cudaMemsetAsync(a->dq_accum, 0, nrow * D * sizeof(float), s);

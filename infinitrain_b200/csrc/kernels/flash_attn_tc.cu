@@ -668,11 +668,10 @@ template <int D>
 static int fwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
   using Cfg = FwdCfg<D>;
   constexpr int smem = Cfg::kSmem + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(flash_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   CUtensorMap tq, tk, tv;
   int rc = make_tmap_bf16_3d(&tq, a->q, static_cast<uint64_t>(a->H) * D, a->T, a->B, a->q_row_stride,
@@ -740,11 +739,10 @@ template <int D>
 static int bwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
   using Cfg = BwdCfg<D>;
   constexpr int smem = Cfg::kSmem + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(flash_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   CUtensorMap tq, tk, tv, tdo, tdq;
   int rc = make_tmap_f32_3d(&tdq, a->dq_accum, static_cast<uint64_t>(a->H) * D, a->T, a->B,

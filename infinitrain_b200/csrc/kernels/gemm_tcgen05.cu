@@ -370,11 +370,10 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDev& p
                   cudaStream_t stream) {
   auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
   constexpr int smem = SmemLayout<BN>::kTotal + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
   }
   kern<<<grid, kGemmThreads, smem, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
