@@ -68,6 +68,9 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     a("--n_head", type=int, default=0)
     a("--n_kv_head", type=int, default=0)
     a("--vocab_size", type=int, default=0)
+    a("--heartbeat_timeout", type=float, default=0.0,
+      help="seconds without a peer's step heartbeat before the run stops with exit code 75 (0 = off); "
+           "ITB_FAULT=<rank>:<step>:<raise|exit|stall|mute> injects a host-side fault")
     return p
 
 
@@ -103,6 +106,21 @@ def main(family: str, argv=None) -> int:
     dev = torch.device("cuda", genv.GetLocalProcRank()) if use_cuda else torch.device("cpu")
     device = Device.from_torch(dev)
     ProcessGroupFactory.Instance().Init(device=dev)
+    heartbeat = injector = None
+    if args.heartbeat_timeout > 0 and world > 1:
+        import datetime
+
+        import torch.distributed as dist
+
+        from infinitrain_b200.utils.fault_tolerance import FaultInjector, Heartbeat
+
+        # the heartbeats travel over their own TCP store (CPU side channel), next to the rendezvous port
+        hb_port = int(os.environ.get("MASTER_PORT", "29500")) + 7
+        store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), hb_port, world, is_master=(rank == 0),
+                              timeout=datetime.timedelta(seconds=60))
+        heartbeat = Heartbeat(store, rank, world, timeout_s=args.heartbeat_timeout,
+                              poll_s=min(0.5, args.heartbeat_timeout / 4)).start()
+        injector = FaultInjector(rank, heartbeat=heartbeat)
     pc = PrecisionCheckConfig.Parse(args.precision_check)
     PrecisionCheckEnv.Instance().Init(pc, rank)
     if rank == 0:
@@ -198,6 +216,20 @@ def main(family: str, argv=None) -> int:
     last_rank = world - 1
 
     for step in range(start_step, args.num_iteration):
+        if heartbeat is not None:
+            from infinitrain_b200.utils.fault_tolerance import RankFailure
+
+            try:
+                injector.maybe_fire(step)        # a faulty rank leaves here, with nothing of its own in flight
+                heartbeat.step(step)
+                heartbeat.wait_peers(step)       # every peer is alive before this step's first collective
+            except RankFailure as e:
+                LOG("ERROR", f"peer failure detected at step {step + 1}: {e}; stopping before the next collective "
+                             f"(resume from the last checkpoint)")
+                heartbeat.stop()
+                sys.stdout.flush()
+                sys.stderr.flush()
+                os._exit(75)
         PrecisionChecker.ResetCounters()
         impl.ResetMemPoolHighWatermarks(device)
         profiler.SetTag(f"Step_{step}")

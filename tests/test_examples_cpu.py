@@ -60,3 +60,26 @@ def test_llama3_two_ranks_via_launcher(flags):
                 "--overfit_single_batch", "--learning_rate", "1e-3", *flags], timeout=900)
     l = _losses(out)
     assert len(l) == 2 and l[1] < l[0] + 1e-3, out[-1500:]
+
+
+def test_trainer_stops_when_a_peer_is_lost():
+    """Two data-parallel CPU ranks; rank 1 stops making progress between steps (host-side injected
+    stall, far longer than the heartbeat limit).  Rank 0's heartbeat check notices before the next
+    collective and stops with exit code 75 instead of waiting inside it."""
+    import time
+
+    port = 29950
+    cmd = [_launcher(), "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable,
+           "examples/llama3/main.py", "--device", "cpu", "--n_layer", "2", "--n_embd", "64", "--n_head", "4",
+           "--n_kv_head", "2", "--vocab_size", "512", "--batch_size", "2", "--sequence_length", "32",
+           "--total_batch_size", "128", "--num_iteration", "6", "--model", "llama3-1b", "--overfit_single_batch",
+           "--learning_rate", "1e-3", "--heartbeat_timeout", "3"]
+    e = dict(os.environ)
+    e.update(OMP_NUM_THREADS="1", ITB_FAULT="1:2:stall:120")
+    t0 = time.time()
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=e, cwd=ROOT)
+    out = r.stdout + r.stderr
+    assert time.time() - t0 < 200
+    assert r.returncode != 0
+    assert "peer failure detected at step 3" in out, out[-2000:]
+    assert len(_losses(out)) == 2          # two steps completed before the fault
