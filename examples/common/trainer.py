@@ -68,6 +68,9 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     a("--n_head", type=int, default=0)
     a("--n_kv_head", type=int, default=0)
     a("--vocab_size", type=int, default=0)
+    a("--elastic_resume", action="store_true",
+      help="allow --load to resume a pure data-parallel checkpoint on a different number of ranks "
+           "(ZeRO optimizer state is re-sharded)")
     a("--heartbeat_timeout", type=float, default=0.0,
       help="seconds without a peer's step heartbeat before the run stops with exit code 75 (0 = off); "
            "ITB_FAULT=<rank>:<step>:<raise|exit|stall|mute> injects a host-side fault")
@@ -203,7 +206,8 @@ def main(family: str, argv=None) -> int:
     start_step = 0
     it = iter(loader)
     if args.load:
-        res = ResumeFromCheckpoint(args.load, model, optimizer, cfg, load_optimizer_state=args.save_optimizer_state)
+        res = ResumeFromCheckpoint(args.load, model, optimizer, cfg, load_optimizer_state=args.save_optimizer_state,
+                                   allow_dp_resize=args.elastic_resume)
         start_step = res.global_step
         for _ in range(res.consumed_batches):
             next(it)

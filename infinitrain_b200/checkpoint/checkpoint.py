@@ -127,6 +127,35 @@ def SaveCheckpoint(checkpoint_root_dir: str, global_step: int, model, optimizer,
     return step_dir
 
 
+def _resume_on_other_dp_size(resume_root: str, old_ranks, model, optimizer, load_optimizer_state: bool):
+    """Pure data parallelism saved by ``len(old_ranks)`` ranks, resumed by a different number: the
+    weights are replicated (any rank's file will do); ZeRO optimizer state is re-sharded from all the
+    old ranks' files (:mod:`reshard`), replicated optimizer state is taken from rank 0."""
+    from .reshard import reshard_zero_optimizer_state
+
+    first = os.path.join(resume_root, old_ranks[0])
+    model.LoadStateDict(Checkpoint.LoadStateDict(os.path.join(first, "model.ckpt")))
+    if load_optimizer_state and optimizer is not None and optimizer.StateDict():
+        paths = [os.path.join(resume_root, r, "optimizer.ckpt") for r in old_ranks]
+        missing = [p for p in paths if not os.path.exists(p)]
+        if missing:
+            raise FileNotFoundError(f"Optimizer checkpoint not found at: {missing[0]}")
+        buffers = getattr(optimizer, "buffers", None)
+        if buffers:
+            if len(buffers) != 1:
+                raise ValueError("re-sharding optimizer state supports one flat buffer per rank")
+            buf = buffers[0]
+            old_states = [Checkpoint.LoadStateDict(p) for p in paths]
+            new_state = reshard_zero_optimizer_state(
+                old_states, [p.numel() for p in buf.params], buf.dp_size, buf.dp_rank,
+                bucket_size_in_elements=buf.config.bucket_size_in_elements,
+                pad_for_busbw=buf.config.pad_buckets_for_high_nccl_busbw)
+            optimizer.LoadStateDict(new_state)
+        else:
+            optimizer.LoadStateDict(Checkpoint.LoadStateDict(paths[0]))
+    return Checkpoint.LoadTrainerState(os.path.join(first, "trainer_state.json"))
+
+
 @dataclass
 class ResumeFromCheckpointResult:
     global_step: int = 0
@@ -142,6 +171,17 @@ def ResumeFromCheckpoint(resume_root: str, model, optimizer, model_config, load_
     rank = genv.MyRank() if rank is None else rank
     d = resume_root
     rd = os.path.join(resume_root, f"rank_{rank:06d}")
+    old_ranks = sorted(x for x in os.listdir(resume_root) if x.startswith("rank_")) if os.path.isdir(resume_root) else []
+    if (allow_dp_resize and old_ranks and genv.GetTensorParallelSize() == 1 and genv.GetPipelineParallelSize() == 1
+            and len(old_ranks) != genv.GetWorldSize()):
+        st = _resume_on_other_dp_size(resume_root, old_ranks, model, optimizer, load_optimizer_state)
+        for k in ("n_layer", "n_head", "n_kv_head", "n_embd", "vocab_size"):
+            if getattr(st, k) != getattr(model_config, k):
+                raise ValueError(f"{k} mismatch: ckpt={getattr(st, k)}, config={getattr(model_config, k)}")
+        # a rank consumes 1/dp of the batches: keep the position in the token stream
+        res.global_step, res.last_lr = st.global_step, st.last_lr
+        res.consumed_batches = max(st.consumed_batches, 0) * len(old_ranks) // max(genv.GetWorldSize(), 1)
+        return res
     if genv.GetWorldSize() > 1 and os.path.isdir(rd):
         d = rd
     st = Checkpoint.Load(d, model, optimizer, load_optimizer_state)
