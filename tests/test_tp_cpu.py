@@ -73,3 +73,62 @@ def test_tp2_training_matches_unpartitioned(tmp_path, family, sp):
         opt.Step()
         ref.append(loss.item())
     run_ranks(_tp_train_worker, 2, args=(family, path, ref), tp=2, sp=sp)
+
+
+def test_fused_tp_launch_bookkeeping_without_a_gpu():
+    """The host side of the fused tensor-parallel launches: workspace reuse distances ("lag"), which
+    hooks a launch enables, and the reuse of a gathered activation -- with the kernel call replaced by
+    a recorder."""
+    import torch
+
+    from infinitrain_b200.parallel import symm
+
+    class FakeC:
+        TP_PUSH, TP_GATE_A, TP_SCATTER, TP_BROADCAST = 1, 2, 4, 8
+
+        def __init__(self):
+            self.calls = []
+
+        def tp_gemm(self, a, a_mn, b, b_mn, M, N, K, c, c2, bias, aux, flags, tp, err):
+            self.calls.append(dict(tp))
+
+    class FakeNvl:
+        rank, world, device = 1, 4, torch.device("cpu")
+        err = torch.zeros(1, dtype=torch.int32)
+
+    class FakeBuf:
+        def __init__(self, n):
+            self.t = torch.zeros(n)
+            self.ptrs, self.mc = [10, 20, 30, 40], 99
+            self.arrive_ptrs, self.my_arrive = [1, 2, 3, 4], 2
+            self.total = torch.zeros(1, dtype=torch.int32)
+            self.last_use, self.content = None, None
+
+        holds = symm._SymBuf.holds
+
+    tp = object.__new__(symm.TpFusedContext)
+    tp.nvl, tp.C, tp.rank, tp.world = FakeNvl(), FakeC(), 1, 4
+    tp.flag_ptrs = [100, 200, 300, 400]
+    tp.launch_ctr = torch.zeros(1, dtype=torch.int32)
+    tp.cta_done = torch.zeros(1, dtype=torch.int32)
+    tp.launch_index, tp._bufs = 0, {}
+    gather, slab = FakeBuf(16), FakeBuf(16)
+    x = torch.zeros(4, 4)
+    a = b = torch.zeros(2, 2)
+    never = 1 << 24
+    tp.launch(a, False, b, False, 8, 8, 8, None, None, None, None, 0, batch=1, T=8, push=gather, push_src=x, gate=gather)
+    tp.launch(a, False, b, False, 8, 8, 8, None, None, None, None, 0, batch=1, T=8, slab=slab, rs_out=x)
+    tp.launch(a, False, b, False, 8, 8, 8, None, None, None, None, 0, batch=1, T=8, push=gather, push_src=x, gate=gather)
+    tp.launch(a, False, b, False, 8, 8, 8, None, None, None, None, 0, batch=1, T=8, slab=slab, rs_out=x, bcast=gather)
+    c = tp.C.calls
+    assert [d["mode"] for d in c] == [1 | 2, 4, 1 | 2, 4 | 8]
+    assert c[0]["push_lag"] == never and c[2]["push_lag"] == 2          # reused two launches later
+    assert c[1]["rs_lag"] == never and c[3]["rs_lag"] == 2
+    assert c[3]["ar_lag"] == 1 and c[3]["ar_out"] == gather.ptrs and c[3]["ar_mc"] == 99
+    assert c[0]["Tl"] == 2 and c[0]["rank"] == 1 and c[0]["world"] == 4 and c[0]["started"] == tp.flag_ptrs
+    assert tp.launch_index == 4 and gather.last_use == 3 and slab.last_use == 3
+    # the gathered copy is reused only for the very tensor that was pushed, unmodified
+    assert gather.holds(x)
+    assert not gather.holds(torch.zeros(4, 4))
+    x.add_(1)
+    assert not gather.holds(x)
