@@ -14,6 +14,7 @@
 #include <thread>
 
 #include "runtime.h"
+#include "token_io.h"
 
 namespace {
 
@@ -115,131 +116,37 @@ std::vector<std::pair<std::string, at::Tensor>> load_state_dict(const std::strin
 }
 
 // ------------------------------------------------------------------ llm.c token file + batcher
-// File: 1024-byte header (int32 magic 20240520 -> uint16 tokens, 20240801 -> uint32 tokens; int32
-// version; int32 num_tokens), then the tokens.  Sample i is x = tok[i*T, i*T+T), y = x shifted by 1.
-class TokenFile {
- public:
-  explicit TokenFile(const std::string& path) {
-    fd_ = ::open(path.c_str(), O_RDONLY);
-    TORCH_CHECK(fd_ >= 0, "cannot open token file: ", path);
-    struct stat st;
-    TORCH_CHECK(fstat(fd_, &st) == 0, "fstat failed: ", path);
-    size_ = static_cast<size_t>(st.st_size);
-    TORCH_CHECK(size_ >= 1024, "token file too small: ", path);
-    base_ = static_cast<const uint8_t*>(mmap(nullptr, size_, PROT_READ, MAP_PRIVATE, fd_, 0));
-    TORCH_CHECK(base_ != MAP_FAILED, "mmap failed: ", path);
-    const int32_t* h = reinterpret_cast<const int32_t*>(base_);
-    magic_ = h[0];
-    version_ = h[1];
-    num_tokens_ = h[2];
-    if (magic_ == 20240520) bytes_per_token_ = 2;
-    else if (magic_ == 20240801) bytes_per_token_ = 4;
-    else TORCH_CHECK(false, "unknown token file magic ", magic_);
-    TORCH_CHECK(1024 + static_cast<size_t>(num_tokens_) * bytes_per_token_ <= size_, "token file truncated: ", path);
-  }
-  ~TokenFile() {
-    if (base_ && base_ != MAP_FAILED) munmap(const_cast<uint8_t*>(base_), size_);
-    if (fd_ >= 0) ::close(fd_);
-  }
-  int64_t num_tokens() const { return num_tokens_; }
-  int64_t magic() const { return magic_; }
-  int64_t version() const { return version_; }
-  inline int64_t token(int64_t i) const {
-    const uint8_t* p = base_ + 1024 + i * bytes_per_token_;
-    if (bytes_per_token_ == 2) { uint16_t v; std::memcpy(&v, p, 2); return v; }
-    uint32_t v; std::memcpy(&v, p, 4); return v;
-  }
-  // x[b, t] = tok[(first + b) * T + t], y shifted by one token.
-  void fill(int64_t first_sample, int64_t B, int64_t T, int64_t* x, int64_t* y) const {
-    for (int64_t b = 0; b < B; ++b) {
-      const int64_t s = (first_sample + b) * T;
-      for (int64_t t = 0; t < T; ++t) {
-        x[b * T + t] = token(s + t);
-        y[b * T + t] = token(s + t + 1);
-      }
-    }
-  }
+using itb::TokenFile;
 
- private:
-  int fd_ = -1;
-  size_t size_ = 0;
-  const uint8_t* base_ = nullptr;
-  int32_t magic_ = 0, version_ = 0, num_tokens_ = 0;
-  int bytes_per_token_ = 2;
-};
-
-// Assembles batches on a background thread into a ring of (pinned when CUDA is present) host
-// buffers; `next()` hands out the oldest ready batch.  Batch k of this loader covers samples
-// [(start_batch + k * stride) * B, ... + B): rank r of dp ranks uses start_batch = r, stride = dp.
+// The prefetching ring of token_io.h over (pinned when asked) host tensors.
 class TokenBatcher {
  public:
   TokenBatcher(std::shared_ptr<TokenFile> file, int64_t B, int64_t T, int64_t start_batch, int64_t stride,
-               int64_t depth, bool pin)
-      : file_(std::move(file)), B_(B), T_(T), start_(start_batch), stride_(stride), depth_(depth) {
-    TORCH_CHECK(B > 0 && T > 0 && stride > 0 && depth >= 3, "TokenBatcher: bad arguments (depth >= 3)");
-    num_samples_ = file_->num_tokens() / T - 1;   // the last sample needs one token of look-ahead
-    TORCH_CHECK(num_samples_ >= B, "token file holds fewer samples than one batch");
-    num_batches_ = num_samples_ / B;
+               int64_t depth, bool pin) {
+    TORCH_CHECK(depth >= 3, "TokenBatcher: bad arguments (depth >= 3)");
     auto opts = torch::dtype(torch::kInt64).pinned_memory(pin);
-    for (int64_t i = 0; i < depth_; ++i) {
+    std::vector<int64_t*> xp, yp;
+    for (int64_t i = 0; i < depth; ++i) {
       xs_.push_back(torch::empty({B, T}, opts));
       ys_.push_back(torch::empty({B, T}, opts));
+      xp.push_back(xs_.back().data_ptr<int64_t>());
+      yp.push_back(ys_.back().data_ptr<int64_t>());
     }
-    worker_ = std::thread([this] { this->run(); });
+    ring_ = std::make_unique<itb::BatchRing>(std::move(file), B, T, start_batch, stride, std::move(xp), std::move(yp));
   }
-  ~TokenBatcher() {
-    {
-      std::lock_guard<std::mutex> g(mu_);
-      stop_ = true;
-    }
-    cv_.notify_all();
-    if (worker_.joinable()) worker_.join();
-  }
-  int64_t num_batches() const { return num_batches_; }
+  int64_t num_batches() const { return ring_->num_batches(); }
   // Returns (x, y) host tensors that stay valid until two further calls of next().
   std::pair<at::Tensor, at::Tensor> next() {
-    std::unique_lock<std::mutex> lk(mu_);
-    cv_.wait(lk, [this] { return produced_ > consumed_ || stop_; });
-    const int64_t slot = consumed_ % depth_;
-    ++consumed_;
-    lk.unlock();
-    cv_.notify_all();
+    const int64_t slot = ring_->next_slot();
     return {xs_[slot], ys_[slot]};
   }
   void skip(int64_t n) {
-    for (int64_t i = 0; i < n; ++i) next();
+    for (int64_t i = 0; i < n; ++i) ring_->next_slot();
   }
 
  private:
-  void run() {
-    int64_t k = 0;
-    for (;;) {
-      {
-        std::unique_lock<std::mutex> lk(mu_);
-        // the two batches handed out last may still be read by the consumer: never refill them
-        cv_.wait(lk, [this] { return stop_ || produced_ - consumed_ < depth_ - 2; });
-        if (stop_) return;
-      }
-      const int64_t batch = (start_ + k * stride_) % num_batches_;
-      const int64_t slot = produced_ % depth_;
-      file_->fill(batch * B_, B_, T_, xs_[slot].data_ptr<int64_t>(), ys_[slot].data_ptr<int64_t>());
-      ++k;
-      {
-        std::lock_guard<std::mutex> g(mu_);
-        ++produced_;
-      }
-      cv_.notify_all();
-    }
-  }
-  std::shared_ptr<TokenFile> file_;
-  int64_t B_, T_, start_, stride_, depth_;
-  int64_t num_samples_ = 0, num_batches_ = 0;
-  std::vector<at::Tensor> xs_, ys_;
-  std::thread worker_;
-  std::mutex mu_;
-  std::condition_variable cv_;
-  int64_t produced_ = 0, consumed_ = 0;
-  bool stop_ = false;
+  std::vector<at::Tensor> xs_, ys_;          // declared before the ring: its worker writes into them
+  std::unique_ptr<itb::BatchRing> ring_;
 };
 
 }  // namespace
