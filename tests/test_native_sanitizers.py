@@ -27,3 +27,24 @@ def test_runtime_under_sanitizers(tmp_path, sanitizer):
     assert r.returncode == 0, r.stdout + r.stderr[-3000:]
     assert "runtime checks ok" in r.stdout
     assert "Sanitizer" not in r.stderr and "runtime error" not in r.stderr, r.stderr[-3000:]
+
+
+@pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
+def test_tp_protocol_model_and_its_negative_control(tmp_path):
+    """Host-threads model of the fused tensor-parallel launches' flag protocol: with the rule the
+    kernels use no reader ever sees a newer epoch in a workspace slot (also race-free under
+    ThreadSanitizer); waiting for one launch less is caught."""
+    src = os.path.join(ROOT, "tests", "native", "tp_protocol_model.cc")
+    good, bad = tmp_path / "model_tsan", tmp_path / "model_relaxed"
+    b = subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", src, "-o", str(good), "-pthread"],
+                       capture_output=True, text=True)
+    if b.returncode != 0 and "sanitize" in b.stderr and "cannot find" in b.stderr:
+        pytest.skip("sanitizer runtime not installed")
+    assert b.returncode == 0, b.stderr[-2000:]
+    r = subprocess.run([str(good)], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, TSAN_OPTIONS="halt_on_error=1"))
+    assert r.returncode == 0 and "protocol model ok" in r.stdout, r.stdout + r.stderr[-2000:]
+    assert "ThreadSanitizer" not in r.stderr
+    subprocess.run(["g++", "-std=c++17", "-O1", "-DITB_MODEL_SLACK=1", src, "-o", str(bad), "-pthread"], check=True)
+    r = subprocess.run([str(bad)], capture_output=True, text=True, timeout=300)
+    assert r.returncode != 0 and "protocol violations" in r.stderr
