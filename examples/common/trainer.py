@@ -68,6 +68,7 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     a("--n_head", type=int, default=0)
     a("--n_kv_head", type=int, default=0)
     a("--vocab_size", type=int, default=0)
+    a("--metrics_jsonl", default="", help="append one JSON record per step to this file (last rank)")
     a("--elastic_resume", action="store_true",
       help="allow --load to resume a pure data-parallel checkpoint on a different number of ranks "
            "(ZeRO optimizer state is re-sharded)")
@@ -219,6 +220,7 @@ def main(family: str, argv=None) -> int:
     cached = None
     last_rank = world - 1
 
+    metrics = None
     for step in range(start_step, args.num_iteration):
         if heartbeat is not None:
             from infinitrain_b200.utils.fault_tolerance import RankFailure
@@ -288,8 +290,16 @@ def main(family: str, argv=None) -> int:
             used, reserved = impl.GetMemPoolPeakMB(device)
             LOG("ERROR", format_step_line(step + 1, args.num_iteration, lossf, args.learning_rate, dur_ms, tps, used,
                                           reserved, dp, tp, sp, pp))
+            dev_ms = ev0.elapsed_time(ev1) if use_cuda else None
             if use_cuda:
-                LOG("INFO", f"step {step + 1} device-timed {ev0.elapsed_time(ev1):.2f} ms")
+                LOG("INFO", f"step {step + 1} device-timed {dev_ms:.2f} ms")
+            if args.metrics_jsonl:
+                if metrics is None:
+                    from infinitrain_b200.utils.logging import MetricsSink
+
+                    metrics = MetricsSink(args.metrics_jsonl)
+                metrics.write(step=step + 1, loss=lossf, lr=args.learning_rate, host_ms=dur_ms, device_ms=dev_ms,
+                              tokens_per_s=tps, peak_used_mb=used, peak_reserved_mb=reserved, dp=dp, tp=tp, sp=sp, pp=pp)
         if tokenizer is not None and args.freq_generate_txt and (step + 1) % args.freq_generate_txt == 0 and pp == 1:
             tokenizer.GenerateText(model, B, T, args.text_length, dev)
         if args.save and args.save_interval and (step + 1) % args.save_interval == 0:

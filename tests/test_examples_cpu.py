@@ -31,9 +31,14 @@ def test_gpt2_single_process_cpu(tmp_path):
     out = _run([sys.executable, "examples/gpt2/main.py", "--device", "cpu", "--n_layer", "2", "--n_embd", "64", "--n_head", "4", "--vocab_size", "512",
                 "--batch_size", "2",
                 "--sequence_length", "32", "--total_batch_size", "128", "--num_iteration", "3", "--optimizer", "adam",
-                "--learning_rate", "1e-3", "--overfit_single_batch", "--save", str(tmp_path), "--save_interval", "3"])
+                "--learning_rate", "1e-3", "--overfit_single_batch", "--save", str(tmp_path), "--save_interval", "3",
+                "--metrics_jsonl", str(tmp_path / "metrics.jsonl")])
     l = _losses(out)
     assert len(l) == 3 and l[-1] < l[0]
+    import json
+
+    recs = [json.loads(line) for line in open(tmp_path / "metrics.jsonl")]
+    assert [r["step"] for r in recs] == [1, 2, 3] and abs(recs[2]["loss"] - l[2]) < 1e-5 and recs[0]["tokens_per_s"] > 0
     assert os.path.exists(os.path.join(tmp_path, "checkpoint_step_000003", "model.ckpt"))
 
 
