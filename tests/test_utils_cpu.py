@@ -131,3 +131,24 @@ def test_sources_have_no_cluster_broadcast_bulk_loads():
                 if pat.search(open(os.path.join(base, f), errors="replace").read()):
                     hits.append(os.path.join(base, f))
     assert not hits, hits
+
+
+def test_compare_precision_tool(tmp_path):
+    import importlib.util
+    import os
+
+    import numpy as np
+
+    spec = importlib.util.spec_from_file_location(
+        "compare_precision", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples",
+                                          "common", "compare_precision.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    for run, delta in (("a", 0.0), ("b", 1e-7), ("c", 1e-2)):
+        d = tmp_path / run / "rank_0" / "step0"
+        d.mkdir(parents=True)
+        np.save(d / "h.0.attn_0.npy", np.linspace(0, 1, 64, dtype=np.float32).reshape(8, 8) + delta)
+        np.save(d / "h.0.mlp_0.npy", np.ones((4, 4), dtype=np.float32))
+    (tmp_path / "c" / "rank_0" / "step0" / "h.0.mlp_0.npy").unlink()
+    assert mod.main([str(tmp_path / "a"), str(tmp_path / "b")]) == 0
+    assert mod.main([str(tmp_path / "a"), str(tmp_path / "c")]) == 1
