@@ -113,3 +113,15 @@ def test_elastic_resume_on_fewer_ranks(tmp_path):
                         "--total_batch_size", "128", "--num_iteration", "4", "--load", ckpt], capture_output=True,
                        text=True, timeout=900, cwd=ROOT, env={**os.environ, "OMP_NUM_THREADS": "1"})
     assert r.returncode != 0
+
+
+def test_run_matrix_and_compare(tmp_path):
+    """The configuration-matrix runner writes one log per run; comparing a matrix against itself
+    passes (same seeds, deterministic CPU math)."""
+    a, b = tmp_path / "a", tmp_path / "b"
+    # timings of such tiny CPU runs are noise: only the losses are held to their tolerance here
+    for out, extra in ((a, []), (b, ["--compare", str(a), "--tps-band", "100"])):
+        _run([sys.executable, "examples/common/run_matrix.py", "examples/common/matrix_smoke.json", "--out", str(out),
+              "--only", "1,1_bfloat16,zero1", "--port", "29760", *extra], timeout=900)
+    assert sorted(os.listdir(a)) == ["gpt2_1.log", "gpt2_1_bfloat16.log", "llama3_zero1.log"]
+    assert len(_losses(open(a / "llama3_zero1.log").read())) == 3
