@@ -20,6 +20,18 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 sys.path.insert(0, ROOT)
 
 
+def epochs(loader):
+    """The loader's batches, epoch after epoch: a run longer than its token file starts the file over
+    (the reference's loop is undefined past the end of its data)."""
+    while True:
+        n = 0
+        for batch in loader:
+            n += 1
+            yield batch
+        if n == 0:
+            raise ValueError("the token file holds less than one batch for this rank")
+
+
 def build_parser(family: str) -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(description=f"{family} training (infinitrain_b200)")
     a = p.add_argument
@@ -205,7 +217,7 @@ def main(family: str, argv=None) -> int:
 
     # ---- resume
     start_step = 0
-    it = iter(loader)
+    it = epochs(loader)
     if args.load:
         res = ResumeFromCheckpoint(args.load, model, optimizer, cfg, load_optimizer_state=args.save_optimizer_state,
                                    allow_dp_resize=args.elastic_resume)
