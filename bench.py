@@ -29,54 +29,134 @@ BASELINE_TOKENS_PER_S = None  # the reference publishes no throughput number
 REF_STEP = None   # compiled lazily: the reference's own step line
 
 
+def _write_llama3_weight_file(path, cfg):
+    """Random-init llm.c LLaMA-3 weight file of ``cfg``'s shape, streamed (an 8B file is 32 GB of
+    fp32): matrices repeat one 64 Mi block of N(0, 0.02) values, norm weights are ones."""
+    import struct
+
+    import numpy as np
+
+    from infinitrain_b200.models import llmc
+
+    header = bytearray(1024)
+    struct.pack_into("<8i", header, 0, llmc.kLlama3Magic, llmc.kLlama3Fp32Version, cfg.block_size, cfg.vocab_size,
+                     cfg.n_layer, cfg.n_head, cfg.n_kv_head, cfg.n_embd)
+    struct.pack_into("<f", header, 32, float(cfg.ffn_dim_multiplier or 0.0))
+    struct.pack_into("<i", header, 36, cfg.multiple_of)
+    struct.pack_into("<f", header, 40, float(cfg.norm_eps))
+    struct.pack_into("<f", header, 44, float(cfg.rope_theta))
+    struct.pack_into("<4i", header, 48, int(cfg.use_scaled_rope), cfg.max_gen_batch_size, 3, 1)
+    block = (np.random.default_rng(42).standard_normal(64 << 20, dtype=np.float32) * 0.02).tobytes()
+    with open(path, "wb") as f:
+        f.write(bytes(header))
+        for kind, shape in llmc._llama3_layout(cfg):
+            left = 4 * int(np.prod(shape))
+            if kind.startswith("ln_"):
+                f.write(np.ones(left // 4, dtype=np.float32).tobytes())
+                continue
+            while left > 0:
+                f.write(block[:left])
+                left -= min(left, len(block))
+
+
 def reference_arm(args):
     """Runs the UNMODIFIED reference (built by ``baseline/build_reference.py`` into ``baseline/_ref``)
-    through its stock ``example/gpt2`` trainer on the same shapes and prints the same JSON line.  The
-    reference is one process with one thread per GPU, so under torchrun only rank 0 launches it; its
-    step time is its own host clock around each step (which ends with the loss read-back), its
-    optimizer is the SGD that its example hard-codes."""
+    through its stock ``example/gpt2`` or ``example/llama3`` trainer on the same shapes and prints the
+    same JSON line.  The reference is one process with one thread per GPU, so under torchrun only rank
+    0 launches it; its step time is its own host clock around each step (which ends with the loss
+    read-back); its optimizers are the ones its examples hard-code (SGD for GPT-2, Adam for LLaMA-3).
+    The stock LLaMA-3 trainer only builds the 1B shape from scratch, so other shapes reach it as a
+    random-init llm.c weight file."""
     import re
+    import shutil
 
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     here = os.path.dirname(os.path.abspath(__file__))
-    exe = os.path.join(here, "baseline", "_ref", "bin", "gpt2")
-    if args.model != "gpt2" or args.tp != 1:
-        print(json.dumps({"impl": "reference", "unavailable": "only the GPT-2 124M data-parallel configuration is wired "
-                          "to the reference's stock trainer"}))
+    llama = args.model.startswith("llama3")
+    on_cpu = os.environ.get("ITB_REFERENCE_DEVICE", "cuda") == "cpu"       # plumbing checks without a GPU
+    exe = os.path.join(here, "baseline", "_ref", "bin", ("llama3" if llama else "gpt2") + ("_cpu" if on_cpu else ""))
+    if (not llama and (args.model != "gpt2" or args.tp != 1)) or (llama and args.gpus % max(args.tp, 1)):
+        print(json.dumps({"impl": "reference", "unavailable": "this model / parallelism is not wired to the reference's "
+                          "stock trainers"}))
         return 0
     ref_src = os.environ.get("ITB_REFERENCE_SRC", os.path.join(os.sep, "root", "reference"))
     if not os.path.exists(exe) and os.path.isdir(os.path.join(ref_src, "infini_train")):
         try:     # one-off offline build (nvcc, no GPU needed); see baseline/build_reference.py
-            subprocess.run([sys.executable, os.path.join(here, "baseline", "build_reference.py"), "--src", ref_src],
-                           capture_output=True, text=True, timeout=1800)
+            subprocess.run([sys.executable, os.path.join(here, "baseline", "build_reference.py"), "--src", ref_src]
+                           + (["--cpu-only"] if on_cpu else []), capture_output=True, text=True, timeout=1800)
         except Exception:  # noqa: BLE001
             pass
     if not os.path.exists(exe):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/bin/gpt2 is not built: pip cannot install "
-                          "the reference checkout (no setup.py / pyproject.toml); build it with python "
-                          "baseline/build_reference.py --src <checkout>"}))
+        print(json.dumps({"impl": "reference", "unavailable": f"baseline/_ref/bin/{os.path.basename(exe)} is not built: "
+                          "pip cannot install the reference checkout (no setup.py / pyproject.toml); build it with "
+                          "python baseline/build_reference.py --src <checkout>"}))
         return 0
+    if not on_cpu:
+        import ctypes
+
+        try:
+            ctypes.CDLL("libcuda.so.1")
+        except OSError:
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA driver on this machine (libcuda.so.1 does not "
+                              "load); the reference's CUDA build needs a GPU"}))
+            return 0
     import numpy as np
 
-    n, B, T = args.gpus, args.batch or 16, args.seq or 1024
+    n = args.gpus
+    B, T = args.batch or (1 if llama else 16), args.seq or (2048 if llama else 1024)
+    dp = n // max(args.tp, 1)
     iters = args.warmup + args.steps
+    scratch = []
     tok_path = f"/tmp/itb_ref_tokens_{os.getpid()}.bin"
-    n_tok = B * T * n * (iters + 2) + 1
+    scratch.append(tok_path)
+    n_tok = B * T * dp * (iters + 2) + 1
     rng = np.random.default_rng(1234)
-    header = np.zeros(256, dtype=np.int32)                 # llm.c token file: 1024-byte header, uint16 ids
-    header[0], header[1], header[2] = 20240520, 1, n_tok
+    header = np.zeros(256, dtype=np.int32)                 # llm.c token file: 1024-byte header, uint16 / uint32 ids
+    header[0], header[1], header[2] = (20240801, 7, n_tok) if llama else (20240520, 1, n_tok)
     with open(tok_path, "wb") as f:
         f.write(header.tobytes())
-        f.write(rng.integers(0, 50257, size=n_tok, dtype=np.uint16).tobytes())
-    # "d12" is the stock trainer's from-scratch GPT-2 124M shape (12 layers, 12 heads, 768 wide); its
-    # "gpt2" name is only defined together with an llm.c weight file
-    cmd = [exe, "--input_bin", tok_path, "--model", "d12", "--batch_size", str(B), "--sequence_length", str(T),
-           "--total_batch_size", str(B * T * n), "--num_iteration", str(iters), "--dtype", "bfloat16",
-           "--nthread_per_process", str(n), "--learning_rate", "1e-4", "--freq_generate_txt", "1000000",
-           "--overfit_single_batch=false"]
-    if n > 1:
+        if llama:
+            f.write(rng.integers(0, 128256, size=n_tok, dtype=np.uint32).tobytes())
+        else:
+            f.write(rng.integers(0, 50257, size=n_tok, dtype=np.uint16).tobytes())
+    dtype = "float32" if on_cpu else "bfloat16"
+    cmd = [exe, "--input_bin", tok_path, "--batch_size", str(B), "--sequence_length", str(T),
+           "--total_batch_size", str(B * T * dp), "--num_iteration", str(iters), "--dtype", dtype,
+           "--learning_rate", "1e-4", "--freq_generate_txt", "1000000", "--overfit_single_batch=false"]
+    cmd += ["--device", "cpu"] if on_cpu else ["--nthread_per_process", str(n)]
+    if llama:
+        from infinitrain_b200.models import llama3_config
+
+        mcfg = llama3_config(args.model, **({"n_layer": args.layers} if args.layers else {}))
+        nbytes = 1024 + 4 * sum(int(np.prod(sh)) for _, sh in __import__("infinitrain_b200.models.llmc", fromlist=["x"])
+                                ._llama3_layout(mcfg))
+        root = next((d for d in ("/dev/shm", "/tmp") if os.path.isdir(d) and shutil.disk_usage(d).free > nbytes + (4 << 30)),
+                    None)
+        if root is None:
+            print(json.dumps({"impl": "reference", "unavailable": f"no scratch space for the {nbytes >> 30} GiB llm.c weight "
+                              "file the reference's stock LLaMA-3 trainer needs for this shape"}))
+            return 0
+        w_path = os.path.join(root, f"itb_ref_llama3_{os.getpid()}.bin")
+        scratch.append(w_path)
+        _write_llama3_weight_file(w_path, mcfg)
+        cmd += ["--model", "llama3", "--llmc_filepath", w_path]
+        if args.tp > 1:
+            cmd += ["--tensor_parallel", str(args.tp), "--sequence_parallel"]
+        model_desc = (f"LLaMA-3 {args.model} shape through the reference's example/llama3 and a random-init llm.c file "
+                      f"({mcfg.n_layer}L, {mcfg.n_embd} wide, {mcfg.n_head}q/{mcfg.n_kv_head}kv heads, vocab {mcfg.vocab_size})")
+        opt_desc = "Adam lr 1e-4 (hard-coded in the reference's example/llama3/main.cc)"
+        metric = (f"tokens/sec {args.model} training (bf16 autocast, AdamW, "
+                  + (f"tp{args.tp}+sp" if args.tp > 1 else "single") + "), max over ranks")
+    else:
+        # "d12" is the stock trainer's from-scratch GPT-2 124M shape (12 layers, 12 heads, 768 wide); its
+        # "gpt2" name is only defined together with an llm.c weight file
+        cmd += ["--model", "d12"]
+        model_desc = "GPT-2 124M (reference example/gpt2, --model d12: 12L, 12H, 768, vocab 50257, ctx 1024)"
+        opt_desc = "SGD lr 1e-4 (hard-coded in the reference's example/gpt2/main.cc)"
+        metric = "tokens/sec GPT-2 124M training (bf16 autocast, AdamW, DDP + ZeRO-2 for N>1), max over ranks"
+    if dp > 1:
         cmd += ["--zero_stage", str(args.zero)]
     env = dict(os.environ)
     # the launcher's rendezvous variables mean nothing to the reference, and its OMP_NUM_THREADS=1 would
@@ -94,10 +174,11 @@ def reference_arm(args):
         print(json.dumps({"impl": "reference", "unavailable": "the reference trainer did not finish within 1500 s"}))
         return 0
     finally:
-        try:
-            os.remove(tok_path)
-        except OSError:
-            pass
+        for path in scratch:
+            try:
+                os.remove(path)
+            except OSError:
+                pass
     clocks = sampler.stop()
     pat = re.compile(r"step\s+(\d+)/\d+\s+\|\s+train loss\s+([-0-9.eE+naif]+).*?\(\s*([0-9.]+)\s*ms\s*\|\s*([0-9.]+)\s*tok/s")
     steps = {}
@@ -112,17 +193,16 @@ def reference_arm(args):
                           f"after {len(steps)} of {iters} steps: {tail[0][:200]}"}))
         return 0
     ms = sum(timed)
-    value = B * T * n * args.steps / (ms / 1e3)
+    value = B * T * dp * args.steps / (ms / 1e3)
+    par = "single" if n == 1 else (f"dp{dp}+zero{args.zero}" if args.tp <= 1 else f"tp{args.tp}+sp" + (f" x dp{dp}" if dp > 1 else ""))
     print(json.dumps({
-        "impl": "reference",
-        "metric": "tokens/sec GPT-2 124M training (bf16 autocast, AdamW, DDP + ZeRO-2 for N>1), max over ranks",
+        "impl": "reference", "metric": metric,
         "value": value, "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic uniform token ids (llm.c token file), random-init weights",
-        "config": {"model": "GPT-2 124M (reference example/gpt2, --model d12: 12L, 12H, 768, vocab 50257, ctx 1024)", "global_batch": B * n,
-                   "micro_batch_per_gpu": B, "seq_len": T,
-                   "parallelism": "single" if n == 1 else f"dp{n}+zero{args.zero} (threads of one process)",
-                   "optimizer": "SGD lr 1e-4 (hard-coded in the reference's example/gpt2/main.cc)",
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak" if args.tp <= 1 else "strong",
+        "vs_baseline": None, "dtype": "fp32 (CPU plumbing check)" if on_cpu else "bf16",
+        "data": "synthetic uniform token ids (llm.c token file), random-init weights",
+        "config": {"model": model_desc, "global_batch": B * dp, "micro_batch_per_gpu": B, "seq_len": T,
+                   "parallelism": par + (" (threads of one process)" if n > 1 else ""), "optimizer": opt_desc,
                    "timing": "the reference's own host clock around each step; a step ends with the loss read-back",
                    "l2": "inputs larger than L2"},
         "clocks": clocks,
@@ -383,7 +463,9 @@ def main():
                        if not llama else
                        f"tokens/sec {args.model} training (bf16 autocast, AdamW, {parallelism}), max over ranks"),
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+            # data parallelism fixes the work per GPU; one tensor-parallel group splits a fixed batch
+            "scaling": "weak" if tp <= 1 else "strong",
             "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "config": {"model": ("GPT-2 124M (12L, 12H, 768, vocab 50257, ctx 1024, tied embeddings)" if not llama else

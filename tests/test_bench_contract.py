@@ -22,7 +22,9 @@ def test_reference_arm_prints_one_json_line_and_exits_zero():
     assert ("unavailable" in rec and isinstance(rec["unavailable"], str)) or rec["value"] > 0
 
 
-def test_reference_arm_only_wires_the_headline_configuration():
+def test_llama_reference_arm_reports_itself_unavailable_without_a_gpu():
+    """The LLaMA-3 arm (a streamed random-init llm.c weight file fed to the reference's stock trainer)
+    writes nothing on a machine whose CUDA driver is absent."""
     r = subprocess.run([sys.executable, "bench.py", "--impl", "reference", "--model", "llama3-8b", "--tp", "8"],
                        capture_output=True, text=True, timeout=600, cwd=ROOT)
     rec = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][0])
