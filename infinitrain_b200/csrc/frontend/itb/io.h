@@ -1,0 +1,196 @@
+// File IO of the C++ frontend: llm.c weight files (reference: example/gpt2/checkpoint_loader.cc,
+// example/llama3/checkpoint_loader.cc), llm.c token files behind a prefetching loader
+// (example/common/tiny_shakespeare_dataset.cc, src/dataloader.cc), checkpoints
+// (src/checkpoint/checkpoint.cc).
+#pragma once
+#include <cstring>
+#include <filesystem>
+#include <fstream>
+#include <regex>
+#include <sstream>
+
+#include "../../runtime/state_dict_io.h"
+#include "../../runtime/token_io.h"
+#include "transformer.h"
+
+namespace itb {
+namespace io {
+
+// ------------------------------------------------------------------ llm.c weight files
+inline Tensor read_f32(std::ifstream& f, std::vector<int64_t> shape) {
+  Tensor t = torch::empty(shape, torch::kFloat32);
+  f.read(static_cast<char*>(t.data_ptr()), static_cast<std::streamsize>(t.numel() * 4));
+  TORCH_CHECK(f.good(), "llm.c weight file is truncated");
+  return t;
+}
+inline void assign(std::map<std::string, Tensor>& sd, const std::string& key, const Tensor& value) {
+  auto it = sd.find(key);
+  TORCH_CHECK(it != sd.end(), "model has no parameter '", key, "'");
+  TORCH_CHECK(it->second.sizes() == value.sizes(), "shape mismatch for '", key, "'");
+  torch::NoGradGuard g;
+  it->second.copy_(value);
+}
+
+// GPT-2: 256 int32 header {magic 20240326, version 3 (fp32), block_size, vocab, layers, heads, width,
+// padded vocab}, then the tensors kind by kind, each kind stacked over the layers.
+inline std::shared_ptr<nn::TransformerModel> LoadGPT2FromLLMC(const std::string& path) {
+  std::ifstream f(path, std::ios::binary);
+  TORCH_CHECK(f.is_open(), "File not found: ", path);
+  int32_t h[256];
+  f.read(reinterpret_cast<char*>(h), sizeof(h));
+  TORCH_CHECK(f.good() && h[0] == 20240326, "not an llm.c GPT-2 weight file: ", path);
+  TORCH_CHECK(h[1] == 3, "only fp32 llm.c GPT-2 files (version 3) are supported");
+  auto cfg = nn::TransformerConfig::GPT2();
+  cfg.block_size = h[2], cfg.vocab_size = cfg.original_vocab_size = h[3];
+  cfg.n_layer = h[4], cfg.n_head = cfg.n_kv_head = h[5], cfg.n_embd = h[6];
+  const int64_t Vp = h[7], L = cfg.n_layer, C = cfg.n_embd, F = cfg.ffn_hidden();
+  auto model = std::make_shared<nn::TransformerModel>(cfg);
+  auto sd = model->StateDict();
+  assign(sd, "lm_head.weight", read_f32(f, {Vp, C}).slice(0, 0, cfg.vocab_size));   // tied with transformer.wte.weight
+  assign(sd, "transformer.wpe.weight", read_f32(f, {cfg.block_size, C}));
+  const std::vector<std::pair<std::string, std::vector<int64_t>>> kinds = {
+      {"ln_1.weight", {C}},         {"ln_1.bias", {C}},        {"attn.c_attn.weight", {3 * C, C}}, {"attn.c_attn.bias", {3 * C}},
+      {"attn.c_proj.weight", {C, C}}, {"attn.c_proj.bias", {C}}, {"ln_2.weight", {C}},               {"ln_2.bias", {C}},
+      {"mlp.c_fc.weight", {F, C}},  {"mlp.c_fc.bias", {F}},    {"mlp.c_proj.weight", {C, F}},      {"mlp.c_proj.bias", {C}}};
+  for (const auto& [kind, shape] : kinds)
+    for (int64_t i = 0; i < L; ++i) assign(sd, "transformer.h." + std::to_string(i) + "." + kind, read_f32(f, shape));
+  assign(sd, "transformer.ln_f.weight", read_f32(f, {C}));
+  assign(sd, "transformer.ln_f.bias", read_f32(f, {C}));
+  return model;
+}
+
+// LLaMA-3: 1024-byte header {magic 20240803, version 3, block_size, vocab, layers, heads, kv heads, width,
+// ffn_dim_multiplier, multiple_of, norm_eps, rope_theta, use_scaled_rope, max_gen_batch, versions}.
+inline std::shared_ptr<nn::TransformerModel> LoadLLaMA3FromLLMC(const std::string& path) {
+  std::ifstream f(path, std::ios::binary);
+  TORCH_CHECK(f.is_open(), "File not found: ", path);
+  char raw[1024];
+  f.read(raw, sizeof(raw));
+  int32_t h[16];
+  std::memcpy(h, raw, sizeof(h));
+  TORCH_CHECK(f.good() && h[0] == 20240803, "not an llm.c LLaMA-3 weight file: ", path);
+  TORCH_CHECK(h[1] == 3, "only fp32 llm.c LLaMA-3 files (version 3) are supported");
+  float fl[4];
+  std::memcpy(fl, raw + 32, 4);
+  std::memcpy(fl + 1, raw + 40, 8);
+  auto cfg = nn::TransformerConfig::LLaMA3();
+  cfg.block_size = h[2], cfg.vocab_size = cfg.original_vocab_size = h[3];
+  cfg.n_layer = h[4], cfg.n_head = h[5], cfg.n_kv_head = h[6], cfg.n_embd = h[7];
+  cfg.ffn_dim_multiplier = static_cast<double>(fl[0]);
+  cfg.multiple_of = h[9];
+  cfg.norm_eps = fl[1], cfg.rope_theta = fl[2];
+  cfg.use_scaled_rope = h[12] != 0, cfg.max_gen_batch_size = h[13];
+  const int64_t L = cfg.n_layer, C = cfg.n_embd, V = cfg.vocab_size, F = cfg.ffn_hidden();
+  const int64_t Q = (cfg.n_head + 2 * cfg.n_kv_head) * cfg.head_dim();
+  auto model = std::make_shared<nn::TransformerModel>(cfg);
+  auto sd = model->StateDict();
+  assign(sd, "transformer.wte.weight", read_f32(f, {V, C}));
+  const std::vector<std::pair<std::string, std::vector<int64_t>>> kinds = {
+      {"ln_1.weight", {C}},       {"attn.c_attn.weight", {Q, C}}, {"attn.c_proj.weight", {C, C}}, {"ln_2.weight", {C}},
+      {"mlp.c_fc.weight", {F, C}}, {"mlp.c_fc2.weight", {F, C}},   {"mlp.c_proj.weight", {C, F}}};
+  for (const auto& [kind, shape] : kinds)
+    for (int64_t i = 0; i < L; ++i) assign(sd, "transformer.h." + std::to_string(i) + "." + kind, read_f32(f, shape));
+  assign(sd, "transformer.ln_f.weight", read_f32(f, {C}));
+  assign(sd, "lm_head.weight", read_f32(f, {V, C}));
+  return model;
+}
+
+// ------------------------------------------------------------------ token files
+// Sequential batches (x, y = x shifted by one token) of an llm.c token file; this data-parallel rank
+// reads batches rank, rank + world, ...  A background thread keeps `depth` batches assembled ahead.
+class TokenLoader {
+ public:
+  TokenLoader(const std::string& path, int64_t batch_size, int64_t sequence_length, int64_t ddp_rank = 0,
+              int64_t ddp_world = 1, int64_t depth = 4)
+      : file_(std::make_shared<TokenFile>(path)), B_(batch_size), T_(sequence_length) {
+    for (int64_t i = 0; i < depth; ++i) {
+      xs_.push_back(torch::empty({B_, T_}, torch::kInt64));
+      ys_.push_back(torch::empty({B_, T_}, torch::kInt64));
+    }
+    std::vector<int64_t*> xp, yp;
+    for (auto& t : xs_) xp.push_back(t.data_ptr<int64_t>());
+    for (auto& t : ys_) yp.push_back(t.data_ptr<int64_t>());
+    ring_ = std::make_unique<BatchRing>(file_, B_, T_, ddp_rank, ddp_world, xp, yp);
+  }
+  int64_t num_batches() const { return ring_->num_batches(); }
+  // The next batch; after the last batch of the file the loader starts over.  The returned tensors
+  // alias a ring slot that stays valid until two further calls.
+  void next(Tensor* x, Tensor* y) {
+    int64_t slot = ring_->next_slot();
+    *x = xs_[slot];
+    *y = ys_[slot];
+  }
+
+ private:
+  std::shared_ptr<TokenFile> file_;
+  int64_t B_, T_;
+  std::vector<Tensor> xs_, ys_;
+  std::unique_ptr<BatchRing> ring_;
+};
+
+// ------------------------------------------------------------------ checkpoints
+struct TrainerState {
+  int64_t global_step = 0, consumed_batches = 0;
+  double last_lr = 0.0;
+  int64_t n_layer = 0, n_head = 0, n_kv_head = 0, n_embd = 0, vocab_size = 0;
+  int64_t ddp_size = 1, tp_size = 1, sp_size = 1, pp_size = 1;
+};
+inline void SaveStateDict(const std::string& path, const std::map<std::string, Tensor>& sd) {
+  std::vector<std::string> names;
+  std::vector<Tensor> tensors;
+  for (const auto& [k, v] : sd) {
+    names.push_back(k);
+    tensors.push_back(v);
+  }
+  save_state_dict(path, names, tensors);
+}
+inline std::map<std::string, Tensor> LoadStateDict(const std::string& path) {
+  std::map<std::string, Tensor> out;
+  for (auto& [k, v] : load_state_dict(path)) out[k] = v;
+  return out;
+}
+inline void SaveTrainerState(const std::string& path, const TrainerState& s) {
+  std::ofstream f(path);
+  f << "{\n  \"n_layer\": " << s.n_layer << ",\n  \"n_head\": " << s.n_head << ",\n  \"n_kv_head\": " << s.n_kv_head
+    << ",\n  \"n_embd\": " << s.n_embd << ",\n  \"vocab_size\": " << s.vocab_size << ",\n  \"global_step\": " << s.global_step
+    << ",\n  \"consumed_batches\": " << s.consumed_batches << ",\n  \"last_lr\": " << s.last_lr << ",\n  \"ddp_size\": "
+    << s.ddp_size << ",\n  \"tp_size\": " << s.tp_size << ",\n  \"sp_size\": " << s.sp_size << ",\n  \"pp_size\": " << s.pp_size
+    << "\n}\n";
+}
+// Tolerant field scan (the reference's writer leaves out a comma after vocab_size).
+inline TrainerState LoadTrainerState(const std::string& path) {
+  std::ifstream f(path);
+  TORCH_CHECK(f.is_open(), "Failed to open ", path);
+  std::stringstream ss;
+  ss << f.rdbuf();
+  const std::string text = ss.str();
+  auto num = [&](const char* key, double dflt) {
+    std::smatch m;
+    std::regex re(std::string("\"") + key + "\"\\s*:\\s*(-?[0-9.eE+-]+)");
+    return std::regex_search(text, m, re) ? std::stod(m[1].str()) : dflt;
+  };
+  TrainerState s;
+  s.global_step = static_cast<int64_t>(num("global_step", 0)), s.consumed_batches = static_cast<int64_t>(num("consumed_batches", 0));
+  s.last_lr = num("last_lr", 0);
+  s.n_layer = static_cast<int64_t>(num("n_layer", 0)), s.n_head = static_cast<int64_t>(num("n_head", 0));
+  s.n_kv_head = static_cast<int64_t>(num("n_kv_head", 0)), s.n_embd = static_cast<int64_t>(num("n_embd", 0));
+  s.vocab_size = static_cast<int64_t>(num("vocab_size", 0));
+  s.ddp_size = static_cast<int64_t>(num("ddp_size", 1)), s.tp_size = static_cast<int64_t>(num("tp_size", 1));
+  s.sp_size = static_cast<int64_t>(num("sp_size", 1)), s.pp_size = static_cast<int64_t>(num("pp_size", 1));
+  return s;
+}
+// <root>/checkpoint_step_%06d/{model.ckpt, optimizer.ckpt, trainer_state.json}
+inline std::string SaveCheckpoint(const std::string& root, const TrainerState& state, const Module& model,
+                                  const std::map<std::string, Tensor>& optimizer_state) {
+  char name[64];
+  std::snprintf(name, sizeof(name), "checkpoint_step_%06lld", static_cast<long long>(state.global_step));
+  auto dir = std::filesystem::path(root) / name;
+  std::filesystem::create_directories(dir);
+  SaveStateDict((dir / "model.ckpt").string(), model.StateDict());
+  if (!optimizer_state.empty()) SaveStateDict((dir / "optimizer.ckpt").string(), optimizer_state);
+  SaveTrainerState((dir / "trainer_state.json").string(), state);
+  return dir.string();
+}
+
+}  // namespace io
+}  // namespace itb

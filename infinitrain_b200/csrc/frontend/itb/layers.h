@@ -1,0 +1,168 @@
+// Basic layers of the C++ frontend (reference: infini_train/src/nn/modules/{linear,sparse,
+// normalization,activations,loss,container}.cc): same constructor shapes, parameter names
+// ("weight", "bias") and initialisation rules.
+#pragma once
+#include <cmath>
+#include <random>
+
+#include "ops.h"
+
+namespace itb {
+namespace nn {
+
+// Host-side random initialisation from one global generator, seed 42 (reference:
+// src/nn/init.cc:22,35): values are drawn on the CPU and land on the parameter's device later.
+inline std::mt19937& global_rng() {
+  static std::mt19937 g(42);
+  return g;
+}
+inline void ManualSeed(uint32_t seed) { global_rng().seed(seed); }
+namespace init {
+inline void Uniform(Tensor t, float lo, float hi) {
+  torch::NoGradGuard g;
+  auto host = torch::empty(t.sizes(), torch::kFloat32);
+  std::uniform_real_distribution<float> d(lo, hi);
+  float* p = host.data_ptr<float>();
+  for (int64_t i = 0; i < host.numel(); ++i) p[i] = d(global_rng());
+  t.copy_(host);
+}
+inline void Normal(Tensor t, float mean, float std) {
+  torch::NoGradGuard g;
+  auto host = torch::empty(t.sizes(), torch::kFloat32);
+  std::normal_distribution<float> d(mean, std);
+  float* p = host.data_ptr<float>();
+  for (int64_t i = 0; i < host.numel(); ++i) p[i] = d(global_rng());
+  t.copy_(host);
+}
+// Kaiming-uniform with a = sqrt(5): bound = 1 / sqrt(fan_in).
+inline void KaimingUniform(Tensor t) {
+  float fan_in = static_cast<float>(t.size(1));
+  float bound = 1.0f / std::sqrt(fan_in);
+  Uniform(t, -bound, bound);
+}
+}  // namespace init
+
+class Linear : public Module {
+ public:
+  static constexpr const char* kType = "Linear";
+  Linear(int64_t in_features, int64_t out_features, bool bias = true) : Module(kType) {
+    weight = register_parameter("weight", torch::empty({out_features, in_features}));
+    init::KaimingUniform(weight);
+    if (bias) {
+      this->bias = register_parameter("bias", torch::empty({out_features}));
+      float bound = 1.0f / std::sqrt(static_cast<float>(in_features));
+      init::Uniform(this->bias, -bound, bound);
+    }
+  }
+  TensorList Forward(const TensorList& in) override { return {ops::linear(in[0], weight, opt(bias))}; }
+  Tensor forward(const Tensor& x, const c10::optional<Tensor>& residual = c10::nullopt, bool gelu = false) {
+    return ops::linear(x, weight, opt(bias), residual, gelu);
+  }
+  static c10::optional<Tensor> opt(const Tensor& t) { return t.defined() ? c10::optional<Tensor>(t) : c10::nullopt; }
+  Tensor weight, bias;
+};
+
+class Embedding : public Module {
+ public:
+  static constexpr const char* kType = "Embedding";
+  Embedding(int64_t num_embeddings, int64_t embedding_dim) : Module(kType) {
+    weight = register_parameter("weight", torch::empty({num_embeddings, embedding_dim}));
+    init::Normal(weight, 0.0f, 1.0f);
+  }
+  TensorList Forward(const TensorList& in) override { return {ops::embedding(in[0], weight)}; }
+  // Lets a model share this table with its output projection.
+  void tie(const Tensor& shared) {
+    alias_parameter("weight", shared);
+    weight = shared;
+  }
+  Tensor weight;
+};
+
+class LayerNorm : public Module {
+ public:
+  static constexpr const char* kType = "LayerNorm";
+  explicit LayerNorm(int64_t dim, double eps = 1e-5) : Module(kType), eps(eps) {
+    weight = register_parameter("weight", torch::ones({dim}));
+    bias = register_parameter("bias", torch::zeros({dim}));
+  }
+  TensorList Forward(const TensorList& in) override { return {ops::layernorm(in[0], weight, bias, eps)}; }
+  Tensor weight, bias;
+  double eps;
+};
+
+class RMSNorm : public Module {
+ public:
+  static constexpr const char* kType = "RMSNorm";
+  explicit RMSNorm(int64_t dim, double eps = 1e-6) : Module(kType), eps(eps) {
+    weight = register_parameter("weight", torch::ones({dim}));
+  }
+  TensorList Forward(const TensorList& in) override { return {ops::rmsnorm(in[0], weight, eps)}; }
+  Tensor weight;
+  double eps;
+};
+
+class Sigmoid : public Module {
+ public:
+  Sigmoid() : Module("Sigmoid") {}
+  TensorList Forward(const TensorList& in) override { return {torch::sigmoid(in[0])}; }
+};
+class NewGELU : public Module {
+ public:
+  NewGELU() : Module("NewGELU") {}
+  TensorList Forward(const TensorList& in) override { return {ops::gelu(in[0])}; }
+};
+// in[0] * silu(in[1])
+class SwiGLU : public Module {
+ public:
+  SwiGLU() : Module("SwiGLU") {}
+  TensorList Forward(const TensorList& in) override { return {ops::swiglu(in[0], in[1])}; }
+};
+class CrossEntropyLoss : public Module {
+ public:
+  CrossEntropyLoss() : Module("CrossEntropyLoss") {}
+  TensorList Forward(const TensorList& in) override { return {ops::cross_entropy(in[0], in[1])}; }
+};
+
+// Children named "0", "1", ...; Forward chains them.
+class Sequential : public Module {
+ public:
+  explicit Sequential(std::vector<std::shared_ptr<Module>> layers) : Module("Sequential") {
+    for (size_t i = 0; i < layers.size(); ++i) items_.push_back(register_module(std::to_string(i), layers[i]));
+  }
+  TensorList Forward(const TensorList& in) override {
+    TensorList x = in;
+    for (auto& m : items_) x = (*m)(x);
+    return x;
+  }
+  size_t size() const { return items_.size(); }
+  std::shared_ptr<Module> at(size_t i) const { return items_.at(i); }
+
+ private:
+  std::vector<std::shared_ptr<Module>> items_;
+};
+
+class ModuleList : public Module {
+ public:
+  ModuleList() : Module("ModuleList") {}
+  explicit ModuleList(std::vector<std::shared_ptr<Module>> layers) : Module("ModuleList") {
+    for (auto& l : layers) push_back(l);
+  }
+  void push_back(std::shared_ptr<Module> m) { items_.push_back(register_module(std::to_string(items_.size()), std::move(m))); }
+  size_t size() const { return items_.size(); }
+  std::shared_ptr<Module> at(size_t i) const { return items_.at(i); }
+  auto begin() const { return items_.begin(); }
+  auto end() const { return items_.end(); }
+
+ private:
+  std::vector<std::shared_ptr<Module>> items_;
+};
+
+class ModuleDict : public Module {
+ public:
+  ModuleDict() : Module("ModuleDict") {}
+  void insert(const std::string& name, std::shared_ptr<Module> m) { register_module(name, std::move(m)); }
+  std::shared_ptr<Module> at(const std::string& name) const { return mutable_module(name); }
+};
+
+}  // namespace nn
+}  // namespace itb
