@@ -1,0 +1,110 @@
+"""The C++ frontend (infinitrain_b200/csrc/frontend/itb) on CPU: its API checks, and its trainer
+against the Python trainer and the unmodified reference on the same weight and token files."""
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref", "bin", "gpt2_cpu")
+ENV = {**os.environ, "OMP_NUM_THREADS": "2"}
+
+
+def _losses(text):
+    return [float(m.group(1)) for m in re.finditer(r"step\s+\d+/\d+\s+\|\s+train loss\s+([\d.]+)", text)]
+
+
+def _run(cmd, cwd):
+    r = subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=900, cwd=cwd, env=ENV)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    return _losses(r.stdout + r.stderr)
+
+
+@pytest.fixture(scope="module")
+def trainer():
+    sys.path.insert(0, os.path.join(ROOT, "examples", "cpp"))
+    import build as cpp_build
+
+    return str(cpp_build.build(cuda=False))
+
+
+@pytest.fixture(scope="module")
+def files(tmp_path_factory):
+    from infinitrain_b200.data import write_token_file
+    from infinitrain_b200.models import llmc
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+    from infinitrain_b200.parallel import global_env as genv
+
+    d = tmp_path_factory.mktemp("cppfe")
+    genv.InitAllEnv(world_size=1, rank=0)
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, 256, (4 * 64 * 20 + 1,), generator=g).tolist()
+    write_token_file(str(d / "tokens16.bin"), toks)
+    write_token_file(str(d / "tokens32.bin"), toks, llama3=True)
+    torch.manual_seed(42)
+    gcfg = TransformerConfig.GPT2(n_layer=2, n_embd=96, n_head=12, n_kv_head=12, vocab_size=256, original_vocab_size=256,
+                                  block_size=64)
+    lcfg = TransformerConfig.LLaMA3(n_layer=2, n_embd=64, n_head=4, n_kv_head=2, vocab_size=256, original_vocab_size=256,
+                                    block_size=64, multiple_of=16, ffn_dim_multiplier=1.5)
+    for cfg, name, write in ((gcfg, "gpt2.bin", llmc.write_gpt2_llmc), (lcfg, "llama3.bin", llmc.write_llama3_llmc)):
+        m = TransformerModel(cfg)
+        with torch.no_grad():
+            for p in m.parameters():
+                if p.dim() > 1:
+                    p.normal_(0, 0.1)
+        write(str(d / name), cfg, llmc.full_state_dict(m))
+    return d
+
+
+def test_api_checks(tmp_path):
+    from torch.utils import cpp_extension as ce
+
+    exe = tmp_path / "frontend_api"
+    lib = ce.library_paths()[0]
+    cmd = ["g++", "-std=c++17", "-O1", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           *[f"-I{p}" for p in ce.include_paths()], f"-I{os.path.join(ROOT, 'infinitrain_b200', 'csrc', 'frontend')}",
+           os.path.join(ROOT, "tests", "native", "frontend_api.cc"), "-o", str(exe), f"-L{lib}", f"-Wl,-rpath,{lib}",
+           "-ltorch", "-ltorch_cpu", "-lc10", "-lpthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run([str(exe), str(tmp_path)], capture_output=True, text=True, timeout=300, env=ENV)
+    assert r.returncode == 0 and r.stdout.startswith("ok "), r.stdout + r.stderr
+
+
+def test_gpt2_trajectory_matches_python_trainer_and_reference(trainer, files):
+    common = ["--device", "cpu", "--llmc_filepath", "gpt2.bin", "--input_bin", "tokens16.bin", "--batch_size", "4",
+              "--sequence_length", "64", "--total_batch_size", "256", "--num_iteration", "8", "--dtype", "float32",
+              "--learning_rate", "0.05"]
+    cpp = _run([trainer, "--family", "gpt2", *common, "--optimizer", "sgd"], files)
+    py = _run([sys.executable, os.path.join(ROOT, "examples", "gpt2", "main.py"), *common, "--optimizer", "sgd"], files)
+    assert len(cpp) == 8 and max(abs(a - b) for a, b in zip(cpp, py)) <= 2e-6, list(zip(cpp, py))
+    if os.path.exists(REF):
+        ref = _run([REF, *common, "--overfit_single_batch=false"], files)
+        assert max(abs(a - b) for a, b in zip(cpp, ref)) <= 1e-5, list(zip(cpp, ref))
+
+
+def test_llama3_adam_with_accumulation_matches_python_trainer(trainer, files):
+    common = ["--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin", "--batch_size", "4",
+              "--sequence_length", "64", "--total_batch_size", "512", "--num_iteration", "6", "--dtype", "float32",
+              "--learning_rate", "1e-3", "--optimizer", "adam"]
+    cpp = _run([trainer, "--family", "llama3", *common], files)
+    py = _run([sys.executable, os.path.join(ROOT, "examples", "llama3", "main.py"), *common], files)
+    assert len(cpp) == 6 and max(abs(a - b) for a, b in zip(cpp, py)) <= 2e-6, list(zip(cpp, py))
+    assert cpp[-1] < cpp[0]                               # and the loss goes down
+
+
+def test_checkpoint_written_by_cpp_resumes_in_cpp_and_in_python(trainer, files):
+    common = ["--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin", "--batch_size", "4",
+              "--sequence_length", "64", "--total_batch_size", "256", "--num_iteration", "8", "--dtype", "float32",
+              "--learning_rate", "1e-3", "--optimizer", "adam"]
+    full = _run([trainer, "--family", "llama3", *common, "--save", "ck", "--save_interval", "4"], files)
+    ck = os.path.join("ck", "checkpoint_step_000004")
+    assert sorted(os.listdir(files / ck)) == ["model.ckpt", "optimizer.ckpt", "trainer_state.json"]
+    again = _run([trainer, "--family", "llama3", *common, "--load", ck], files)
+    assert len(again) == 4 and max(abs(a - b) for a, b in zip(full[4:], again)) <= 1e-6
+    py = _run([sys.executable, os.path.join(ROOT, "examples", "llama3", "main.py"), *common, "--load", ck,
+               "--save_optimizer_state"], files)
+    assert len(py) == 4 and max(abs(a - b) for a, b in zip(full[4:], py)) <= 2e-6, list(zip(full[4:], py))
