@@ -4,6 +4,8 @@
 //   itb_train --family gpt2 --llmc_filepath model.bin --input_bin tokens.bin --batch_size 4
 //             --sequence_length 64 --total_batch_size 256 --num_iteration 10 --learning_rate 1e-4
 //             --device cpu|cuda --dtype float32|bfloat16 --optimizer sgd|adam|adamw
+//             [--lora_rank 8 --lora_alpha 16 --lora_target_modules c_attn,c_proj --lora_load_path F --lora_save_path F]
+//             [--save DIR --save_interval N] [--load DIR/checkpoint_step_000004]
 #include <chrono>
 #include <cstdio>
 #include <iostream>
@@ -98,9 +100,22 @@ int main(int argc, char** argv) {
                (long long)cfg.n_layer, (long long)cfg.n_embd, (long long)cfg.n_head, (long long)cfg.n_kv_head,
                (long long)cfg.vocab_size, model->Parameters().size());
 
+  const int64_t lora_rank = fl.geti("lora_rank", 0);
+  if (lora_rank > 0) {
+    namespace lora = itb::nn::lora;
+    lora::LoRAConfig lc;
+    lc.rank = lora_rank, lc.alpha = fl.getd("lora_alpha", 16.0);
+    lc.target_modules = lora::ParseLoRATargetModules(fl.get("lora_target_modules", "c_attn,c_proj"));
+    lora::GetLoRAModel(model, lc);
+    model->To(device);
+    if (!fl.get("lora_load_path", "").empty()) lora::LoadLoRAWeights(model, fl.get("lora_load_path", ""));
+    std::fprintf(stderr, "[I] %s\n", lora::PrintLoRASummary(model).c_str());
+  }
+  itb::TensorList trainable = itb::nn::lora::TrainableParameters(model);
+
   std::unique_ptr<itb::optim::Optimizer> optimizer;
-  if (opt_name == "sgd") optimizer = std::make_unique<itb::optim::SGD>(model->Parameters(), lr);
-  else optimizer = std::make_unique<itb::optim::Adam>(model->Parameters(), lr, 0.9, 0.999, 1e-8,
+  if (opt_name == "sgd") optimizer = std::make_unique<itb::optim::SGD>(trainable, lr);
+  else optimizer = std::make_unique<itb::optim::Adam>(trainable, lr, 0.9, 0.999, 1e-8,
                                                       opt_name == "adamw" ? fl.getd("weight_decay", 0.1) : 0.0);
 
   itb::io::TokenLoader loader(fl.get("input_bin", ""), B, T);
@@ -148,5 +163,6 @@ int main(int argc, char** argv) {
       itb::io::SaveCheckpoint(fl.get("save", ""), st, *model, optimizer->StateDict());
     }
   }
+  if (lora_rank > 0 && !fl.get("lora_save_path", "").empty()) itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", ""));
   return 0;
 }

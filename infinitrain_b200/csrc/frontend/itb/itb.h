@@ -10,6 +10,7 @@
 #pragma once
 #include "io.h"
 #include "layers.h"
+#include "lora.h"
 #include "module.h"
 #include "ops.h"
 #include "optim.h"

@@ -54,12 +54,26 @@ class Linear : public Module {
       init::Uniform(this->bias, -bound, bound);
     }
   }
-  TensorList Forward(const TensorList& in) override { return {ops::linear(in[0], weight, opt(bias))}; }
-  Tensor forward(const Tensor& x, const c10::optional<Tensor>& residual = c10::nullopt, bool gelu = false) {
+  TensorList Forward(const TensorList& in) override { return {forward(in[0])}; }
+  // y = x W^T + b, optionally through tanh-GELU or plus a residual (fused into the GEMM epilogue on a B200)
+  virtual Tensor forward(const Tensor& x, const c10::optional<Tensor>& residual = c10::nullopt, bool gelu = false) {
     return ops::linear(x, weight, opt(bias), residual, gelu);
   }
   static c10::optional<Tensor> opt(const Tensor& t) { return t.defined() ? c10::optional<Tensor>(t) : c10::nullopt; }
+  int64_t in_features() const { return weight.size(1); }
+  int64_t out_features() const { return weight.size(0); }
   Tensor weight, bias;
+
+ protected:
+  // Adopts another Linear's tensors (a wrapper around an existing layer shares its storage).
+  Linear(const Linear& base, const char* type) : Module(type) {
+    alias_parameter("weight", base.weight);
+    weight = base.weight;
+    if (base.bias.defined()) {
+      alias_parameter("bias", base.bias);
+      bias = base.bias;
+    }
+  }
 };
 
 class Embedding : public Module {

@@ -1,0 +1,245 @@
+// LoRA for the C++ frontend (reference: infini_train/src/nn/lora/{lora_config,lora_linear,lora_utils}.cc):
+// y = base(x) + (alpha / r) (x A^T) B^T with A [r, in] Kaiming-uniform and B [out, r] zeros, base frozen;
+// injection by dotted-suffix targets, merge / unmerge, merge-and-unload, adapter files (magic
+// 0x4C4F5241, version 1, fp32) that the reference and the Python layer read and write too.
+#pragma once
+#include <fstream>
+#include <set>
+#include <sstream>
+
+#include "transformer.h"
+
+namespace itb {
+namespace nn {
+namespace lora {
+
+struct LoRAConfig {
+  int64_t rank = 8;
+  double alpha = 16.0;
+  double dropout = 0.0;   // accepted, unused (as in the reference)
+  std::set<std::string> target_modules = {"c_attn", "c_proj"};
+  double Scaling() const { return alpha / static_cast<double>(rank); }
+  // A module matches when its dotted path equals a target or ends with ".target"
+  // ("attn.c_proj" does not match "mlp.c_proj").
+  bool ShouldApplyLoRA(const std::string& path) const {
+    for (const auto& t : target_modules) {
+      if (path == t) return true;
+      if (path.size() > t.size() && path.compare(path.size() - t.size() - 1, t.size() + 1, "." + t) == 0) return true;
+    }
+    return false;
+  }
+};
+// "c_attn, attn.c_proj ,," -> {"c_attn", "attn.c_proj"}
+inline std::set<std::string> ParseLoRATargetModules(const std::string& spec) {
+  std::set<std::string> out;
+  std::stringstream ss(spec);
+  std::string item;
+  while (std::getline(ss, item, ',')) {
+    size_t a = item.find_first_not_of(" \t"), b = item.find_last_not_of(" \t");
+    if (a != std::string::npos) out.insert(item.substr(a, b - a + 1));
+  }
+  return out;
+}
+
+class LoRALinear : public Linear {
+ public:
+  LoRALinear(const std::shared_ptr<Linear>& base, const LoRAConfig& config) : Linear(*base, "LoRALinear"), config(config) {
+    auto opt = weight.options().requires_grad(false);
+    lora_A = register_parameter("lora_A", torch::empty({config.rank, in_features()}, opt));
+    init::KaimingUniform(lora_A);
+    lora_B = register_parameter("lora_B", torch::zeros({out_features(), config.rank}, opt));
+    weight.set_requires_grad(false);
+    if (bias.defined()) bias.set_requires_grad(false);
+  }
+  Tensor forward(const Tensor& x, const c10::optional<Tensor>& residual = c10::nullopt, bool gelu = false) override {
+    TORCH_CHECK(!(merged_ && (lora_A.requires_grad() || lora_B.requires_grad())),
+                "Forward() on merged LoRA with requires_grad=true. Call UnmergeWeights() before training.");
+    if (merged_) return ops::linear(x, weight, opt(bias), residual, gelu);
+    // the low-rank branch joins before the activation, so a fused GELU epilogue cannot be used here
+    Tensor y = ops::linear(x, weight, opt(bias));
+    Tensor low = ops::linear(ops::linear(x, lora_A), lora_B);
+    y = y + low.to(y.scalar_type()) * config.Scaling();
+    if (gelu) y = ops::gelu(y);
+    if (residual.has_value()) y = y + *residual;
+    return y;
+  }
+  Tensor Delta() const {
+    return torch::matmul(lora_B.detach().to(torch::kFloat32), lora_A.detach().to(torch::kFloat32)) * config.Scaling();
+  }
+  void MergeWeights() {
+    if (merged_) return;
+    torch::NoGradGuard g;
+    weight.add_(Delta().to(weight.scalar_type()));
+    merged_ = true;
+    lora_A.set_requires_grad(false);
+    lora_B.set_requires_grad(false);
+  }
+  void UnmergeWeights() {
+    if (!merged_) return;
+    torch::NoGradGuard g;
+    weight.sub_(Delta().to(weight.scalar_type()));
+    merged_ = false;
+    lora_A.set_requires_grad(true);
+    lora_B.set_requires_grad(true);
+  }
+  bool IsMerged() const { return merged_; }
+  LoRAConfig config;
+  Tensor lora_A, lora_B;
+
+ private:
+  bool merged_ = false;
+};
+
+// A plain Linear that owns copies of the wrapper's tensors' storage (used by MergeAndUnload).
+class UnwrappedLinear : public Linear {
+ public:
+  explicit UnwrappedLinear(const Linear& merged) : Linear(merged, Linear::kType) {}
+};
+
+inline void visit(const std::shared_ptr<Module>& m, const std::string& path,
+                  const std::function<void(const std::shared_ptr<Module>& parent, const std::string& name,
+                                           const std::string& child_path, const std::shared_ptr<Module>& child)>& fn) {
+  for (const auto& name : m->child_names()) {
+    auto child = m->mutable_module(name);
+    std::string child_path = path.empty() ? name : path + "." + name;
+    fn(m, name, child_path, child);
+    visit(m->mutable_module(name), child_path, fn);
+  }
+}
+
+inline void FreezeBaseModel(const std::shared_ptr<Module>& model) {
+  for (auto& [name, p] : model->NamedParameters()) {
+    bool is_lora = name.size() >= 6 && (name.compare(name.size() - 6, 6, "lora_A") == 0 || name.compare(name.size() - 6, 6, "lora_B") == 0);
+    Tensor t = p;
+    t.set_requires_grad(is_lora);
+  }
+}
+inline void UnfreezeModel(const std::shared_ptr<Module>& model) { model->set_requires_grad(true); }
+
+// Wraps every Linear whose path matches a target; everything else is frozen.
+inline std::shared_ptr<Module> InjectLoRALayers(const std::shared_ptr<Module>& model, const LoRAConfig& config) {
+  visit(model, "", [&](const std::shared_ptr<Module>& parent, const std::string& name, const std::string& path,
+                       const std::shared_ptr<Module>& child) {
+    if (child->type() != Linear::kType || !config.ShouldApplyLoRA(path)) return;
+    parent->replace_module(name, std::make_shared<LoRALinear>(std::static_pointer_cast<Linear>(child), config));
+  });
+  return model;
+}
+inline std::shared_ptr<Module> GetLoRAModel(const std::shared_ptr<Module>& model, const LoRAConfig& config) {
+  InjectLoRALayers(model, config);
+  FreezeBaseModel(model);
+  return model;
+}
+inline std::vector<std::shared_ptr<LoRALinear>> LoRAModules(const std::shared_ptr<Module>& model) {
+  std::vector<std::shared_ptr<LoRALinear>> out;
+  for (auto& [path, m] : model->NamedModules())
+    if (m->type() == "LoRALinear") out.push_back(std::static_pointer_cast<LoRALinear>(m));
+  return out;
+}
+inline TensorList GetLoRAParameters(const std::shared_ptr<Module>& model) {
+  TensorList out;
+  for (auto& m : LoRAModules(model)) {
+    out.push_back(m->lora_A);
+    out.push_back(m->lora_B);
+  }
+  return out;
+}
+inline TensorList TrainableParameters(const std::shared_ptr<Module>& model) {
+  TensorList out;
+  for (auto& p : model->Parameters())
+    if (p.requires_grad()) out.push_back(p);
+  return out;
+}
+inline void MergeLoRAWeights(const std::shared_ptr<Module>& model) {
+  for (auto& m : LoRAModules(model)) m->MergeWeights();
+}
+inline void UnmergeLoRAWeights(const std::shared_ptr<Module>& model) {
+  for (auto& m : LoRAModules(model)) m->UnmergeWeights();
+}
+// Folds every adapter into its base weight, puts plain Linears back and makes all parameters trainable.
+inline std::shared_ptr<Module> MergeAndUnload(const std::shared_ptr<Module>& model) {
+  visit(model, "", [&](const std::shared_ptr<Module>& parent, const std::string& name, const std::string&,
+                       const std::shared_ptr<Module>& child) {
+    if (child->type() != "LoRALinear") return;
+    auto l = std::static_pointer_cast<LoRALinear>(child);
+    l->MergeWeights();
+    parent->replace_module(name, std::make_shared<UnwrappedLinear>(*l));
+  });
+  UnfreezeModel(model);
+  return model;
+}
+inline int64_t CountTrainableParameters(const std::shared_ptr<Module>& model) {
+  int64_t n = 0;
+  for (auto& p : model->Parameters())
+    if (p.requires_grad()) n += p.numel();
+  return n;
+}
+inline int64_t CountTotalParameters(const std::shared_ptr<Module>& model) {
+  int64_t n = 0;
+  for (auto& p : model->Parameters()) n += p.numel();
+  return n;
+}
+inline std::map<std::string, Tensor> LoRAStateDict(const std::shared_ptr<Module>& model) {
+  std::map<std::string, Tensor> out;
+  for (auto& [k, v] : model->StateDict()) {
+    if (k.size() >= 6 && (k.compare(k.size() - 6, 6, "lora_A") == 0 || k.compare(k.size() - 6, 6, "lora_B") == 0)) out[k] = v;
+  }
+  return out;
+}
+
+constexpr uint32_t kLoRAMagic = 0x4C4F5241;
+inline void SaveLoRAWeights(const std::shared_ptr<Module>& model, const std::string& path) {
+  auto sd = LoRAStateDict(model);
+  std::ofstream f(path, std::ios::binary);
+  TORCH_CHECK(f.is_open(), "Failed to open ", path);
+  uint32_t head[3] = {kLoRAMagic, 1, static_cast<uint32_t>(sd.size())};
+  f.write(reinterpret_cast<const char*>(head), sizeof(head));
+  for (auto& [name, t] : sd) {
+    uint32_t len = static_cast<uint32_t>(name.size()), ndim = static_cast<uint32_t>(t.dim());
+    f.write(reinterpret_cast<const char*>(&len), 4);
+    f.write(name.data(), len);
+    f.write(reinterpret_cast<const char*>(&ndim), 4);
+    for (int64_t d : t.sizes()) f.write(reinterpret_cast<const char*>(&d), 8);
+    Tensor host = t.detach().to(torch::kCPU, torch::kFloat32).contiguous();
+    f.write(static_cast<const char*>(host.data_ptr()), host.numel() * 4);
+  }
+}
+inline void LoadLoRAWeights(const std::shared_ptr<Module>& model, const std::string& path) {
+  std::ifstream f(path, std::ios::binary);
+  TORCH_CHECK(f.is_open(), "Failed to open ", path);
+  uint32_t head[3];
+  f.read(reinterpret_cast<char*>(head), sizeof(head));
+  TORCH_CHECK(f.good() && head[0] == kLoRAMagic, "Invalid LoRA file format");
+  TORCH_CHECK(head[1] == 1, "Unsupported LoRA file version: ", head[1]);
+  auto own = model->StateDict();
+  torch::NoGradGuard g;
+  for (uint32_t i = 0; i < head[2]; ++i) {
+    uint32_t len = 0, ndim = 0;
+    f.read(reinterpret_cast<char*>(&len), 4);
+    std::string name(len, '\0');
+    f.read(name.data(), len);
+    f.read(reinterpret_cast<char*>(&ndim), 4);
+    std::vector<int64_t> dims(ndim);
+    for (auto& d : dims) f.read(reinterpret_cast<char*>(&d), 8);
+    Tensor t = torch::empty(dims, torch::kFloat32);
+    f.read(static_cast<char*>(t.data_ptr()), t.numel() * 4);
+    TORCH_CHECK(f.good(), "LoRA file is truncated: ", path);
+    auto it = own.find(name);
+    if (it == own.end()) {
+      std::fprintf(stderr, "[W] LoRA parameter not found in model: %s\n", name.c_str());
+      continue;
+    }
+    it->second.copy_(t);
+  }
+}
+inline std::string PrintLoRASummary(const std::shared_ptr<Module>& model) {
+  int64_t trainable = CountTrainableParameters(model), total = CountTotalParameters(model);
+  std::ostringstream os;
+  os << "LoRA: " << LoRAModules(model).size() << " adapted layers, trainable " << trainable << " / " << total << " ("
+     << 100.0 * static_cast<double>(trainable) / static_cast<double>(total) << " %)";
+  return os.str();
+}
+
+}  // namespace lora
+}  // namespace nn
+}  // namespace itb

@@ -76,6 +76,12 @@ class Module : public std::enable_shared_from_this<Module> {
     return out;
   }
   std::shared_ptr<Module> mutable_module(const std::string& name) const { return modules_.at(name); }
+  // Swaps a direct child for another module under the same name (LoRA injection, merge-and-unload).
+  void replace_module(const std::string& name, std::shared_ptr<Module> m) {
+    TORCH_CHECK(modules_.count(name), "replace_module: no child named '", name, "'");
+    modules_[name] = std::move(m);
+  }
+  const std::vector<std::string>& child_names() const { return module_order_; }
   bool has_module(const std::string& name) const { return modules_.count(name) != 0; }
   Tensor& parameter(const std::string& name) { return parameters_.at(name); }
   const Tensor& parameter(const std::string& name) const { return parameters_.at(name); }

@@ -63,40 +63,41 @@ class CausalSelfAttention : public Module {
     TORCH_CHECK(c.n_embd % c.n_head == 0, "n_embd must be divisible by n_head");
     TORCH_CHECK(c.n_head % c.n_kv_head == 0, "n_head must be divisible by n_kv_head");
     int64_t D = c.head_dim();
-    c_attn = register_module("c_attn", std::make_shared<Linear>(c.n_embd, (c.n_head + 2 * c.n_kv_head) * D, c.add_bias_linear));
-    c_proj = register_module("c_proj", std::make_shared<Linear>(c.n_embd, c.n_embd, c.add_bias_linear));
+    register_module("c_attn", std::make_shared<Linear>(c.n_embd, (c.n_head + 2 * c.n_kv_head) * D, c.add_bias_linear));
+    register_module("c_proj", std::make_shared<Linear>(c.n_embd, c.n_embd, c.add_bias_linear));
   }
+  // children are looked up by name on every call, so a wrapper put in their place (LoRA) takes over
+  std::shared_ptr<Linear> linear(const char* name) const { return std::static_pointer_cast<Linear>(mutable_module(name)); }
   // in: x, [freqs_cis]; residual is added in the projection's epilogue
   Tensor forward(const Tensor& x, const c10::optional<Tensor>& freqs, const c10::optional<Tensor>& residual) {
-    Tensor qkv = c_attn->forward(x);
+    Tensor qkv = linear("c_attn")->forward(x);
     auto rope = config.attention_type == AttentionType::kRoPE ? freqs : c10::nullopt;
     Tensor y = ops::attention_packed(qkv, config.n_head, config.n_kv_head, config.head_dim(), rope, 0, true);
-    return c_proj->forward(y, residual);
+    return linear("c_proj")->forward(y, residual);
   }
   TensorList Forward(const TensorList& in) override {
     return {forward(in[0], in.size() > 1 ? c10::optional<Tensor>(in[1]) : c10::nullopt, c10::nullopt)};
   }
   TransformerConfig config;
-  std::shared_ptr<Linear> c_attn, c_proj;
 };
 
 class MLP : public Module {
  public:
   explicit MLP(const TransformerConfig& c) : Module("MLP"), config(c) {
     int64_t hidden = c.ffn_hidden();
-    c_fc = register_module("c_fc", std::make_shared<Linear>(c.n_embd, hidden, c.add_bias_linear));
+    register_module("c_fc", std::make_shared<Linear>(c.n_embd, hidden, c.add_bias_linear));
     if (c.activation_type == MLPType::kSwiGLU)
-      c_fc2 = register_module("c_fc2", std::make_shared<Linear>(c.n_embd, hidden, c.add_bias_linear));
-    c_proj = register_module("c_proj", std::make_shared<Linear>(hidden, c.n_embd, c.add_bias_linear));
+      register_module("c_fc2", std::make_shared<Linear>(c.n_embd, hidden, c.add_bias_linear));
+    register_module("c_proj", std::make_shared<Linear>(hidden, c.n_embd, c.add_bias_linear));
   }
+  std::shared_ptr<Linear> linear(const char* name) const { return std::static_pointer_cast<Linear>(mutable_module(name)); }
   Tensor forward(const Tensor& x, const c10::optional<Tensor>& residual) {
     if (config.activation_type == MLPType::kSwiGLU)
-      return c_proj->forward(ops::swiglu(c_fc->forward(x), c_fc2->forward(x)), residual);
-    return c_proj->forward(c_fc->forward(x, c10::nullopt, /*gelu=*/true), residual);
+      return linear("c_proj")->forward(ops::swiglu(linear("c_fc")->forward(x), linear("c_fc2")->forward(x)), residual);
+    return linear("c_proj")->forward(linear("c_fc")->forward(x, c10::nullopt, /*gelu=*/true), residual);
   }
   TensorList Forward(const TensorList& in) override { return {forward(in[0], c10::nullopt)}; }
   TransformerConfig config;
-  std::shared_ptr<Linear> c_fc, c_fc2, c_proj;
 };
 
 // Pre-norm residual block: x + attn(ln_1(x)), then x + mlp(ln_2(x)).
@@ -136,8 +137,8 @@ class TransformerModel : public Module {
     ln_f = MakeNorm(c);
     body->insert("ln_f", ln_f);
     register_module("transformer", body);
-    lm_head = register_module("lm_head", std::make_shared<Linear>(c.n_embd, c.vocab_size, c.add_bias_lm_head));
-    if (c.tie_weights) wte->tie(lm_head->weight);   // one tensor serves the lookup and the projection
+    register_module("lm_head", std::make_shared<Linear>(c.n_embd, c.vocab_size, c.add_bias_lm_head));
+    if (c.tie_weights) wte->tie(lm_head()->weight);   // one tensor serves the lookup and the projection
   }
   // idx [B, T] int64 -> logits [B, T, vocab]
   Tensor forward(const Tensor& idx) {
@@ -151,7 +152,7 @@ class TransformerModel : public Module {
       freqs = freqs_cis_.slice(0, 0, T);
     }
     for (auto& layer : *h) x = std::static_pointer_cast<TransformerLayer>(layer)->forward(x, freqs);
-    return lm_head->forward((*ln_f)(x));
+    return lm_head()->forward((*ln_f)(x));
   }
   TensorList Forward(const TensorList& in) override { return {forward(in[0])}; }
 
@@ -159,7 +160,7 @@ class TransformerModel : public Module {
   std::shared_ptr<Embedding> wte, wpe;
   std::shared_ptr<ModuleList> h;
   std::shared_ptr<Module> ln_f;
-  std::shared_ptr<Linear> lm_head;
+  std::shared_ptr<Linear> lm_head() const { return std::static_pointer_cast<Linear>(mutable_module("lm_head")); }
 
  private:
   Tensor freqs_cis_;

@@ -79,7 +79,7 @@ int main(int argc, char** argv) {
   auto sd2 = other->StateDict();
   sd2["transformer.h.0.attn.bias"] = torch::zeros({1});                          // a buffer only the reference writes
   gpt->LoadStateDict(sd2);
-  EXPECT(torch::equal(gpt->lm_head->weight, other->lm_head->weight));
+  EXPECT(torch::equal(gpt->lm_head()->weight, other->lm_head()->weight));
   sd2.erase("transformer.ln_f.bias");
   bool threw = false;
   try {
@@ -123,7 +123,7 @@ int main(int argc, char** argv) {
   auto st2 = io::LoadTrainerState(dir + "/trainer_state.json");
   EXPECT(st2.global_step == 7 && st2.consumed_batches == 14 && st2.n_layer == 2 && st2.n_embd == 32);
   auto loaded = io::LoadStateDict(dir + "/model.ckpt");
-  EXPECT(loaded.size() == gpt->StateDict().size() && torch::equal(loaded.at("lm_head.weight"), gpt->lm_head->weight));
+  EXPECT(loaded.size() == gpt->StateDict().size() && torch::equal(loaded.at("lm_head.weight"), gpt->lm_head()->weight));
 
   // bf16 autocast emulation changes Linear only
   {
@@ -133,6 +133,52 @@ int main(int argc, char** argv) {
     AutocastGuard guard(torch::kBFloat16);
     Tensor low = l(x);
     EXPECT(!torch::equal(full, low) && torch::allclose(full, low, 5e-2, 5e-2));
+  }
+  // LoRA: target matching, shapes, frozen base, merge == unmerged forward, merge-and-unload
+  {
+    namespace lora = nn::lora;
+    lora::LoRAConfig lc;
+    lc.rank = 4, lc.alpha = 8.0;
+    EXPECT(lc.Scaling() == 2.0);
+    lc.target_modules = lora::ParseLoRATargetModules(" c_attn , attn.c_proj ,, ");
+    EXPECT(lc.target_modules == (std::set<std::string>{"c_attn", "attn.c_proj"}));
+    EXPECT(lc.ShouldApplyLoRA("transformer.h.0.attn.c_proj") && !lc.ShouldApplyLoRA("transformer.h.0.mlp.c_proj"));
+    EXPECT(lc.ShouldApplyLoRA("c_attn") && !lc.ShouldApplyLoRA("xc_attn"));
+    std::shared_ptr<Module> m = std::make_shared<nn::TransformerModel>(tiny_gpt());
+    int64_t total_before = lora::CountTotalParameters(m);
+    lora::GetLoRAModel(m, lc);
+    auto mods = lora::LoRAModules(m);
+    EXPECT(mods.size() == 4);                                                       // c_attn and attn.c_proj of 2 layers
+    EXPECT(mods[0]->lora_A.size(0) == 4 && mods[0]->lora_A.size(1) == 32 && mods[0]->lora_B.size(1) == 4);
+    EXPECT(!mods[0]->weight.requires_grad() && mods[0]->lora_A.requires_grad());
+    EXPECT(lora::CountTrainableParameters(m) == lora::CountTotalParameters(m) - total_before);
+    EXPECT(m->StateDict().count("transformer.h.0.attn.c_attn.lora_A") == 1);
+    {
+      torch::NoGradGuard g;
+      for (auto& p : lora::GetLoRAParameters(m)) p.normal_(0, 0.3);
+    }
+    auto tm = std::static_pointer_cast<nn::TransformerModel>(m);
+    Tensor before = tm->forward(idx).detach();
+    lora::MergeLoRAWeights(m);
+    EXPECT(mods[0]->IsMerged() && !mods[0]->lora_A.requires_grad());
+    EXPECT(torch::allclose(tm->forward(idx).detach(), before, 1e-4, 1e-4));
+    lora::UnmergeLoRAWeights(m);
+    EXPECT(!mods[0]->IsMerged() && mods[0]->lora_A.requires_grad());
+    EXPECT(torch::allclose(tm->forward(idx).detach(), before, 1e-4, 1e-4));
+    lora::SaveLoRAWeights(m, tmp + "/adapter.bin");
+    std::shared_ptr<Module> m2 = std::make_shared<nn::TransformerModel>(tiny_gpt());
+    m2->LoadStateDict([&] {
+      auto sd0 = m->StateDict();
+      for (auto it = sd0.begin(); it != sd0.end();) it = it->first.find("lora_") != std::string::npos ? sd0.erase(it) : std::next(it);
+      return sd0;
+    }());
+    lora::GetLoRAModel(m2, lc);
+    lora::LoadLoRAWeights(m2, tmp + "/adapter.bin");
+    EXPECT(torch::allclose(std::static_pointer_cast<nn::TransformerModel>(m2)->forward(idx).detach(), before, 1e-5, 1e-5));
+    lora::MergeAndUnload(m);
+    EXPECT(lora::LoRAModules(m).empty() && lora::LoRAStateDict(m).empty());
+    EXPECT(lora::CountTrainableParameters(m) == total_before);
+    EXPECT(torch::allclose(tm->forward(idx).detach(), before, 1e-4, 1e-4));
   }
   std::printf("ok %d\n", g_checks);
   return 0;

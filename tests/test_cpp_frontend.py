@@ -108,3 +108,37 @@ def test_checkpoint_written_by_cpp_resumes_in_cpp_and_in_python(trainer, files):
     py = _run([sys.executable, os.path.join(ROOT, "examples", "llama3", "main.py"), *common, "--load", ck,
                "--save_optimizer_state"], files)
     assert len(py) == 4 and max(abs(a - b) for a, b in zip(full[4:], py)) <= 2e-6, list(zip(full[4:], py))
+
+
+def test_lora_training_matches_python_trainer_and_reference(trainer, files):
+    """All three trainers load one adapter file, train the adapters on the frozen base along the same
+    trajectory and write adapter files with the same tensors."""
+    from infinitrain_b200.models import llmc
+    from infinitrain_b200.nn import lora
+
+    lcfg = lora.LoRAConfig(rank=4, alpha=8.0, target_modules=lora.ParseLoRATargetModules("c_attn,c_proj"))
+
+    def adapters(path=None):
+        m = lora.GetLoRAModel(llmc.GPT2FromLLMC(str(files / "gpt2.bin")), lcfg)
+        if path:
+            lora.LoadLoRAWeights(m, str(files / path))
+        return m
+
+    m = adapters()
+    torch.manual_seed(7)
+    with torch.no_grad():
+        for p in lora.GetLoRAParameters(m):
+            p.normal_(0, 0.3)
+    lora.SaveLoRAWeights(m, str(files / "adapter.bin"))
+    common = ["--device", "cpu", "--llmc_filepath", "gpt2.bin", "--input_bin", "tokens16.bin", "--batch_size", "4",
+              "--sequence_length", "64", "--total_batch_size", "256", "--num_iteration", "5", "--dtype", "float32",
+              "--learning_rate", "0.05", "--lora_rank", "4", "--lora_alpha", "8", "--lora_load_path", "adapter.bin"]
+    cpp = _run([trainer, "--family", "gpt2", *common, "--optimizer", "sgd", "--lora_save_path", "cpp_adapter.bin"], files)
+    py = _run([sys.executable, os.path.join(ROOT, "examples", "gpt2", "main.py"), *common, "--optimizer", "sgd",
+               "--lora_save_path", "py_adapter.bin"], files)
+    assert len(cpp) == 5 and max(abs(a - b) for a, b in zip(cpp, py)) <= 1e-5, list(zip(cpp, py))
+    a, b = ({k: v.detach() for k, v in lora.LoRAStateDict(adapters(p)).items()} for p in ("cpp_adapter.bin", "py_adapter.bin"))
+    assert max(float((a[k] - b[k]).abs().max()) for k in a) < 1e-5
+    if os.path.exists(REF):
+        ref = _run([REF, *common, "--overfit_single_batch=false"], files)
+        assert max(abs(x - y) for x, y in zip(cpp, ref)) <= 1e-5, list(zip(cpp, ref))
