@@ -33,6 +33,16 @@ def PrecomputeFreqsCis(head_dim: int, end: int, theta: float = 10000.0, use_scal
     return ref.precompute_freqs_cis(head_dim, end, theta, device)
 
 
+def _aligned() -> bool:
+    """True while the precision checker records module outputs: every module then computes exactly
+    what the reference's module of the same name computes (no residual add inside the projections,
+    GELU as its own module, token and position tables looked up separately), so that the two
+    frameworks' per-module logs and dumps line up.  Off, the fused formulations run."""
+    from ...utils.precision_checker import PrecisionCheckEnv, PrecisionCheckLevel
+
+    return PrecisionCheckEnv.Instance().config.level != PrecisionCheckLevel.OFF
+
+
 def _make_norm(config: TransformerConfig):
     if config.norm_type == NormType.kLayerNorm:
         n = LayerNorm(config.n_embd)
@@ -120,7 +130,13 @@ class MLP(Module):
         if self.config.activation_type == MLPType.kSwiGLU:
             x1 = self.c_fc(x)
             x2 = self.c_fc2(x)
+            if _aligned():
+                y = self.c_proj(x1 * self.silu(x2))
+                return y if residual is None else y + residual
             return self.c_proj(ops.swiglu(x1, x2), residual=residual)
+        if _aligned():
+            y = self.c_proj(self.gelu(self.c_fc(x)))
+            return y if residual is None else y + residual
         if self._plain() and x.is_cuda:
             return ops.mlp_gelu(x, self.c_fc.weight, self.c_fc.bias, self.c_proj.weight, self.c_proj.bias, residual)
         h = self.c_fc(x, gelu=True) if type(self.c_fc) is ColumnParallelLinear else ops.gelu(self.c_fc(x))
@@ -128,7 +144,7 @@ class MLP(Module):
 
 
 class TransformerLayer(Module):
-    kType = "TransformerLayer"
+    kType = "Layer"                      # the reference's type name (transformer.h:12)
 
     def __init__(self, config: TransformerConfig):
         super().__init__(self.kType)
@@ -138,6 +154,9 @@ class TransformerLayer(Module):
         self.mlp = MLP(config)
 
     def Forward(self, x, freqs_cis=None, start_pos: int = 0):
+        if _aligned():
+            x1 = x + self.attn(self.ln_1(x), freqs_cis, start_pos)
+            return x1 + self.mlp(self.ln_2(x1))
         x1 = self.attn(self.ln_1(x), freqs_cis, start_pos, residual=x)
         return self.mlp(self.ln_2(x1), residual=x1)
 
@@ -160,7 +179,9 @@ class TransformerFirstStage(Module):
         if T > self.config.block_size:
             raise ValueError(f"Cannot forward sequence of length {T}, block size is only {self.config.block_size}")
         has_pos = self.config.attention_type == AttentionType.kStandard
-        if _tp() is None:
+        if _tp() is None and has_pos and _aligned():
+            x = self.wte(idx) + self.wpe(torch.arange(T, device=idx.device))
+        elif _tp() is None:
             x = self.wte(idx, self.wpe.weight if has_pos else None, 0)
         else:
             x = self.wte(idx)
@@ -217,7 +238,7 @@ class TransformerLastStage(Module):
 class TransformerModel(Module):
     """GPT-2 or LLaMA-3 depending on ``config``; holds only the layers of this pipeline stage."""
 
-    kType = "TransformerModel"
+    kType = "Transformer"                # the reference's type name (transformer.h:71)
     kTransformerModelName = "transformer"
 
     def __init__(self, config: TransformerConfig, pp_rank: Optional[int] = None):

@@ -63,15 +63,17 @@ class PrecisionCheckContext:
     """Where in the step the checker is (micro-batch index, layer); part of every record key."""
 
     gas_step = 0
-    layer = ""
+    layer = 0
+    layer_name = ""
 
     @classmethod
-    def Set(cls, gas_step: int = 0, layer: str = ""):
-        cls.gas_step, cls.layer = gas_step, layer
+    def Set(cls, gas_step: int = 0, layer: int = 0, layer_name: str = ""):
+        cls.gas_step, cls.layer, cls.layer_name = gas_step, layer, layer_name
 
     @classmethod
     def Key(cls) -> str:
-        return f"[GAS-{cls.gas_step}]" + (f"[{cls.layer}]" if cls.layer else "")
+        """``[GAS-g] [L-l] name`` (reference: src/utils/precision_check_context.cc:22-29)."""
+        return f"[GAS-{cls.gas_step}] [L-{cls.layer}]" + (f" {cls.layer_name}" if cls.layer_name else "")
 
 
 class PrecisionCheckEnv:
@@ -132,15 +134,27 @@ def ComputeMD5(t: torch.Tensor, tolerance: float = 0.0) -> str:
     return hashlib.md5(a.tobytes()).hexdigest()
 
 
+def _g(v: float) -> str:
+    """A float the way a C++ stream prints it by default (six significant digits)."""
+    return f"{v:.6g}"
+
+
+def _dtype_name(t: torch.Tensor) -> str:
+    return str(t.dtype).replace("torch.", "")
+
+
 def Summarize(t: torch.Tensor) -> str:
-    f = t.detach().float()
-    flat = f.reshape(-1)
-    first = ", ".join(f"{v:.6g}" for v in flat[:6].cpu().tolist())
-    nan, inf = int(torch.isnan(flat).sum()), int(torch.isinf(flat).sum())
+    """``dtype=float32 shape=(4,64,96) min=.. max=.. mean=.. [v0, .., v5, ...] [NaN:0 Inf:0]``: the
+    body of the reference's ``simple`` line (src/utils/precision_checker.cc:352-371)."""
+    flat = t.detach().float().reshape(-1)
+    shape = "(" + ",".join(str(d) for d in t.shape) + ")"
+    head = f"dtype={_dtype_name(t)} shape={shape} "
     if flat.numel() == 0:
-        return "empty"
-    return (f"shape={tuple(t.shape)} dtype={str(t.dtype).replace('torch.', '')} min={flat.min().item():.6g} "
-            f"max={flat.max().item():.6g} mean={flat.mean().item():.6g} first6=[{first}] nan={nan} inf={inf}")
+        return head + "min=0 max=0 mean=0 [] [NaN:0 Inf:0]"
+    nan, inf = int(torch.isnan(flat).sum()), int(torch.isinf(flat).sum())
+    first = ", ".join(_g(v) for v in flat[:6].cpu().tolist()) + (", ..." if flat.numel() > 6 else "")
+    return (head + f"min={_g(flat.min().item())} max={_g(flat.max().item())} mean={_g(flat.double().mean().item())} "
+            f"[{first}] [NaN:{nan} Inf:{inf}]")
 
 
 class PrecisionChecker:
@@ -149,44 +163,57 @@ class PrecisionChecker:
 
     @classmethod
     def BuildNameMap(cls, model, prefix: str = "") -> None:
+        """Module -> dotted path, as the reference builds it (src/utils/precision_checker.cc:397-418):
+        the root and the pipeline-internal ``__pp*`` subtrees are skipped, so layers carry their
+        state-dict paths (``transformer.h.0.attn.c_attn``) and the stage wrappers their type names."""
         cls._name_map = {}
-        named = model.NamedModules() if hasattr(model, "NamedModules") else list(model.named_modules())
+        named = (model.NamedModules(remove_duplicate=False) if hasattr(model, "NamedModules")
+                 else list(model.named_modules(remove_duplicate=False)))
         for name, mod in named:
-            cls._name_map.setdefault(id(mod), name or prefix or type(mod).__name__)
+            if not name or name.startswith("__pp"):
+                continue
+            cls._name_map.setdefault(id(mod), (prefix + "." if prefix else "") + name)
 
     @classmethod
     def ResetCounters(cls):
         PrecisionCheckEnv.Instance().ResetCounters()
 
     @classmethod
-    def _record(cls, kind: str, name: str, idx: int, t: torch.Tensor):
+    def _record(cls, stage: str, name: str, i: int, t: torch.Tensor):
+        """One line ``<context> <name>[_<n>]_<forward|backward> tensor[<i>]: ...`` and, when asked, one
+        ``rank_<r>/<name>[_<n>]_<stage>.npy``; ``n`` counts the records of this (name, stage) since the
+        last ``ResetCounters`` (reference: src/utils/precision_checker.cc:281-371)."""
         env = PrecisionCheckEnv.Instance()
         cfg = env.config
         if cfg.level == PrecisionCheckLevel.OFF or not isinstance(t, torch.Tensor) or not t.is_floating_point():
             return
-        key = f"{PrecisionCheckContext.Key()}[{kind}] {name} #{idx}"
-        n = env.GetAndIncrementCounter(key)
-        body = ComputeMD5(t, cfg.md5_tolerance) if cfg.format == "md5" else Summarize(t)
+        short = "forward" if "Forward" in stage else "backward"
+        n = env.GetAndIncrementCounter(f"{name}_{short}")
+        log_name = name + (f"_{n}" if n > 0 else "") + "_" + short
+        if cfg.format == "md5":
+            shape = "(" + ",".join(str(d) for d in t.shape) + ")"
+            body = f"dtype={_dtype_name(t)} shape={shape} md5={ComputeMD5(t, cfg.md5_tolerance)}"
+        else:
+            body = Summarize(t)
         with open(os.path.join(env.timestamped_path, f"precision_check_rank_{env.rank}.log"), "a") as f:
-            f.write(f"{key} ({n}): {body}\n")
+            f.write(f"{PrecisionCheckContext.Key()} {log_name} tensor[{i}]: {body}\n")
         if cfg.save_tensors:
-            safe = key.replace("/", "_").replace(" ", "_").replace("[", "").replace("]", "_").replace("#", "")
             d = os.path.join(env.timestamped_path, f"rank_{env.rank}")
             os.makedirs(d, exist_ok=True)
-            np.save(os.path.join(d, f"{safe}_{n}.npy"), t.detach().float().cpu().numpy())
+            np.save(os.path.join(d, f"{log_name}.npy"), t.detach().float().cpu().numpy())
 
     @classmethod
     def ModuleForwardHook(cls, module, inputs, outputs):
-        name = cls._name_map.get(id(module), type(module).__name__)
+        name = cls._name_map.get(id(module), getattr(module, "kType", None) or type(module).__name__)
         outs = outputs if isinstance(outputs, (tuple, list)) else (outputs,)
         for i, o in enumerate(outs):
             cls._record("Forward Output", name, i, o)
 
     @classmethod
     def ModuleBackwardHook(cls, module, grad_outputs, grad_inputs):
-        name = cls._name_map.get(id(module), type(module).__name__)
+        name = cls._name_map.get(id(module), getattr(module, "kType", None) or type(module).__name__)
         for i, g in enumerate(grad_outputs or ()):
-            cls._record("Backward GradOutput", name, i, g)
+            cls._record("GradOutputs", name, i, g)
 
     @classmethod
     def InstallFunctionHooks(cls):
@@ -201,7 +228,7 @@ class PrecisionChecker:
 
             def wrapped(*a, _orig=orig, _n=fname, **k):
                 out = _orig(*a, **k)
-                cls._record("Function Output", _n, 0, out)
+                cls._record("Forward Output", _n, 0, out)
                 return out
 
             setattr(ops, fname, wrapped)

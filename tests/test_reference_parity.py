@@ -132,3 +132,32 @@ def test_resume_from_a_checkpoint_written_by_the_reference(world):
     b = _run([*OURS, *args, "--optimizer", "sgd", "--load", str(ck)], d)
     _close(a[4:], b, 4)
     shutil.rmtree(d / "ref_ckpt")
+
+
+def test_per_module_dumps_line_up_with_the_reference(world):
+    """With the precision checker on, both trainers log one record per module call under the same
+    names and dump the same .npy files; every forward output and every backward gradient agrees
+    within the reference's own comparison rule (allclose, atol 1e-5, rtol 1e-3)."""
+    import glob
+    import importlib.util
+
+    d, common = world
+    args = [*common, "--total_batch_size", "512", "--num_iteration", "2"]
+    _run([BIN, *args, "--overfit_single_batch=false", "--precision_check",
+          "level=1,format=simple,path=pc_ref,save_tensors=true"], d)
+    _run([*OURS, *args, "--optimizer", "sgd", "--precision_check", "level=1,format=simple,path=pc_ours,save_tensors=true"], d)
+    (ref_dir,), (our_dir,) = glob.glob(str(d / "pc_ref" / "*")), glob.glob(str(d / "pc_ours" / "*"))
+
+    def names(run):
+        return [ln.split()[2] for ln in open(os.path.join(run, "precision_check_rank_0.log"))]
+
+    a, b = names(ref_dir), names(our_dir)
+    assert len(a) == len(b) > 200
+    assert sorted(a) == sorted(b)                        # same records; only the two embedding tables' backward order differs
+    assert [n for n in a if n.endswith("_forward")] == [n for n in b if n.endswith("_forward")]
+    assert sorted(os.listdir(os.path.join(ref_dir, "rank_0"))) == sorted(os.listdir(os.path.join(our_dir, "rank_0")))
+    spec = importlib.util.spec_from_file_location("compare_precision",
+                                                  os.path.join(ROOT, "examples", "common", "compare_precision.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.main([ref_dir, our_dir]) == 0
