@@ -215,20 +215,33 @@ class PrecisionChecker:
         for i, g in enumerate(grad_outputs or ()):
             cls._record("GradOutputs", name, i, g)
 
+    # fused op -> record name, after the reference's ``<kType>Function`` names where an op of that
+    # type exists there (src/autograd/*.cc); the fused ops have no finer-grained records
+    _FUNCTION_NAMES = {"linear": "LinearFunction", "mlp_gelu": "MlpGeluFunction", "layernorm": "LayerNormFunction",
+                       "rmsnorm": "RMSNormFunction", "gelu": "GeluFunction", "swiglu": "SwiGLUFunction",
+                       "attention_packed": "AttentionFunction", "embedding": "EmbeddingFunction",
+                       "cross_entropy": "CrossEntropyFunction"}
+
     @classmethod
     def InstallFunctionHooks(cls):
+        """FUNCTION level: every fused op of ``ops.functional`` records its tensor inputs and its output
+        under ``<Name>Function_forward`` and the gradient that reaches its output under
+        ``<Name>Function_backward`` (reference: RegisterForFunction, src/utils/precision_checker.cc:420-446)."""
         from ..ops import functional as ops
 
-        for fname in ("linear", "mlp_gelu", "layernorm", "rmsnorm", "gelu", "swiglu", "attention_packed", "embedding",
-                      "cross_entropy"):
+        for fname, rec in cls._FUNCTION_NAMES.items():
             if fname in cls._orig_fns:
                 continue
             orig = getattr(ops, fname)
             cls._orig_fns[fname] = orig
 
-            def wrapped(*a, _orig=orig, _n=fname, **k):
+            def wrapped(*a, _orig=orig, _n=rec, **k):
+                for i, t in enumerate(x for x in a if isinstance(x, torch.Tensor)):
+                    cls._record("Forward Input", _n, i, t)
                 out = _orig(*a, **k)
                 cls._record("Forward Output", _n, 0, out)
+                if isinstance(out, torch.Tensor) and out.requires_grad:
+                    out.register_hook(lambda g, _n=_n: cls._record("Backward Input", _n, 0, g))
                 return out
 
             setattr(ops, fname, wrapped)

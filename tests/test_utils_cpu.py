@@ -57,7 +57,7 @@ def test_precision_checker_simple_md5_npy(tmp_path):
         log = open(os.path.join(env.GetOutputPath(), "precision_check_rank_0.log")).read()
         # the reference's line: <context> <name>[_<n>]_<forward|backward> tensor[<i>]: dtype= shape= md5=
         assert re.search(r"^\[GAS-0\] \[L-0\] 0_forward tensor\[0\]: dtype=float32 shape=\(2,4\) md5=[0-9a-f]{32}$", log, re.M)
-        assert "linear_forward tensor[0]" in log and "0_backward tensor[0]" in log and "Sequential_forward" in log
+        assert "LinearFunction_forward tensor[0]" in log and "LinearFunction_backward tensor[0]" in log and "LinearFunction_3_forward" in log and "0_backward tensor[0]" in log and "Sequential_forward" in log
         files = os.listdir(os.path.join(env.GetOutputPath(), "rank_0"))
         assert "0_forward.npy" in files and "1_backward.npy" in files
     finally:
