@@ -186,17 +186,28 @@ def GetPipelineParallelProcessGroupName(rank: int) -> str: return f"PP{GetGroupI
 
 
 def ProcessGroupOverview(skip_trivial_axes: bool = True) -> str:
-    """Readable dump of every DP / TP / PP group (for logs and topology checks)."""
+    """Dump of every DP / TP / PP group, in the reference's text (src/nn/parallel/global.cc:196-257):
+    groups in group-id order with the coordinates that are fixed inside them."""
     L = _g().layout
-    lines = [f"Global: world={_g().world_size} DP={L.sizes[Axis.DP]} TP={L.sizes[Axis.TP]} PP={L.sizes[Axis.PP]} "
-             f"SP={'on' if _g().sequence_parallel_enabled else 'off'} vPP={_g().virtual_pipeline_parallel_size}"]
-    for ax in Axis:
+    out = ["", "=== Parallel Communication Groups ===",
+           f"world_size = {_g().world_size}, config: {{DP={L.sizes[Axis.DP]}, TP={L.sizes[Axis.TP]}, "
+           f"PP={L.sizes[Axis.PP]}}}, order: {{" + " -> ".join(ax.name for ax in L.order) + "}"]
+    axes = list(Axis)
+    for k, ax in enumerate(axes):
         if skip_trivial_axes and L.sizes[ax] <= 1:
+            out.append(f"[{ax.name}] size={L.sizes[ax]}, unenabled")
             continue
-        groups = {}
-        for r in range(_g().world_size):
-            groups.setdefault(L.GroupId(ax, *L.CoordOf(r)), L.GroupRanks(ax, *L.CoordOf(r)))
-        lines.append(f"[{ax.name}] size={L.sizes[ax]}, num_groups={len(groups)}")
-        for gid in sorted(groups):
-            lines.append(f"  - {ax.name} {gid}: [{', '.join(str(x) for x in sorted(groups[gid]))}]")
-    return "\n".join(lines)
+        groups = []
+        for dp in range(1 if ax == Axis.DP else L.sizes[Axis.DP]):
+            for tp in range(1 if ax == Axis.TP else L.sizes[Axis.TP]):
+                for pp in range(1 if ax == Axis.PP else L.sizes[Axis.PP]):
+                    groups.append((L.GroupId(ax, dp, tp, pp), (dp, tp, pp)))
+        groups.sort(key=lambda g: g[0])
+        out.append(f"[{ax.name}] size={L.sizes[ax]}, num_groups={L.NumGroups(ax)}")
+        for gid, (dp, tp, pp) in groups:
+            ranks = ", ".join(str(r) for r in sorted(L.GroupRanks(ax, dp, tp, pp)))
+            c = ["-" if ax == a2 else str(v) for a2, v in zip((Axis.DP, Axis.TP, Axis.PP), (dp, tp, pp))]
+            out.append(f"  - {ax.name} {gid} (dp={c[0]}, tp={c[1]}, pp={c[2]}): [{ranks}]")
+        if k + 1 < len(axes):
+            out.append("")
+    return "\n".join(out) + "\n\n"

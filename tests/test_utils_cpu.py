@@ -154,3 +154,18 @@ def test_compare_precision_tool(tmp_path):
     (tmp_path / "c" / "rank_0" / "step0" / "h.0.mlp_0.npy").unlink()
     assert mod.main([str(tmp_path / "a"), str(tmp_path / "b")]) == 0
     assert mod.main([str(tmp_path / "a"), str(tmp_path / "c")]) == 1
+
+
+def test_process_group_overview_is_the_reference_text():
+    from infinitrain_b200.parallel import global_env as g
+
+    g.InitAllEnv(world_size=1, rank=0)
+    # the text the reference's stock trainer prints for one rank (src/nn/parallel/global.cc:196-257)
+    assert g.ProcessGroupOverview() == ("\n=== Parallel Communication Groups ===\n"
+                                        "world_size = 1, config: {DP=1, TP=1, PP=1}, order: {TP -> DP -> PP}\n"
+                                        "[DP] size=1, unenabled\n[TP] size=1, unenabled\n[PP] size=1, unenabled\n\n")
+    g.InitAllEnv(world_size=8, rank=0, tensor_parallel_size=2, pipeline_parallel_size=2)
+    text = g.ProcessGroupOverview()
+    assert "[DP] size=2, num_groups=4\n  - DP 0 (dp=-, tp=0, pp=0): [0, 2]\n  - DP 1 (dp=-, tp=0, pp=1): [4, 6]" in text
+    assert "  - PP 3 (dp=1, tp=1, pp=-): [3, 7]\n\n" in text
+    g.InitAllEnv(world_size=1, rank=0)
