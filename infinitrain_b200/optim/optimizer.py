@@ -208,9 +208,34 @@ class Adam(Optimizer):
         out["adam.t"] = torch.tensor(self.t, dtype=torch.int64)
         return out
 
-    def LoadStateDict(self, state_dict):
+    def NamedStateDict(self, model) -> "OrderedDict[str, torch.Tensor]":
+        """The same state keyed by parameter NAME (``adam.m.transformer.h.0.attn.c_attn.weight``): it
+        survives a change of parameter order or a frozen subset; ``LoadStateDict`` takes either form."""
+        names = self._param_names(model)
+        out = OrderedDict()
         for i, (m, v) in enumerate(zip(self.m, self.v)):
-            for key, dst in ((f"adam.m.{i}", m), (f"adam.v.{i}", v)):
+            out[f"adam.m.{names[i]}"] = m
+            out[f"adam.v.{names[i]}"] = v
+        out["adam.t"] = torch.tensor(self.t, dtype=torch.int64)
+        return out
+
+    def _param_names(self, model):
+        by_id = {}
+        named = model.NamedParameters() if hasattr(model, "NamedParameters") else model.named_parameters()
+        for name, p in named:
+            by_id.setdefault(id(p), name)
+        missing = [i for i, p in enumerate(self.params) if id(p) not in by_id]
+        if missing:
+            raise KeyError(f"optimizer parameter {missing[0]} is not a parameter of the model")
+        return [by_id[id(p)] for p in self.params]
+
+    def LoadStateDict(self, state_dict, model=None):
+        names = self._param_names(model) if model is not None else None
+        for i, (m, v) in enumerate(zip(self.m, self.v)):
+            for kind, dst in (("m", m), ("v", v)):
+                key = f"adam.{kind}.{i}"
+                if key not in state_dict and names is not None:
+                    key = f"adam.{kind}.{names[i]}"
                 if key not in state_dict:
                     raise KeyError(f"Missing optimizer state: {key}")
                 with torch.no_grad():

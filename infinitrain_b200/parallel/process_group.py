@@ -14,6 +14,8 @@ and either returns a ``Work`` (``async_op=True``) or makes the compute stream wa
 """
 from __future__ import annotations
 
+import os
+
 import enum
 import time
 from datetime import timedelta
@@ -306,7 +308,12 @@ class ProcessGroupFactory:
     def Reset(cls):
         cls._instance = None
 
-    def Init(self, backend: Optional[str] = None, timeout_s: float = 600.0, device: Optional[torch.device] = None):
+    def Init(self, backend: Optional[str] = None, timeout_s: float = 600.0, device: Optional[torch.device] = None,
+             rendezvous_file: Optional[str] = None):
+        """Creates the job's groups.  Rendezvous is a TCP store (``MASTER_ADDR`` / ``MASTER_PORT``) or,
+        when ``rendezvous_file`` / ``ITB_RDZV_FILE`` names a path on a filesystem all ranks share, a
+        file there (the reference's only scheme: src/core/ccl/ccl_utils.cc:14-53); the file must not
+        exist before the job starts."""
         if self.initialized:
             return self
         world = genv.GetWorldSize()
@@ -317,6 +324,9 @@ class ProcessGroupFactory:
             kwargs = {}
             if backend == "nccl" and device is not None:
                 kwargs["device_id"] = device
+            rendezvous_file = rendezvous_file or os.environ.get("ITB_RDZV_FILE")
+            if rendezvous_file:
+                kwargs["init_method"] = "file://" + os.path.abspath(rendezvous_file)
             dist.init_process_group(backend=backend, rank=rank, world_size=world,
                                     timeout=timedelta(seconds=timeout_s), **kwargs)
         if world <= 1 or not dist.is_initialized():

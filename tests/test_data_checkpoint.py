@@ -168,3 +168,29 @@ def test_zero_optimizer_state_resharding():
     full = gather_full_optimizer_state(old, numels)
     for f, t in zip(full, truth):
         assert torch.equal(f["adam.m"], t["adam.m"]) and torch.equal(f["adam.v"], t["adam.v"])
+
+
+def test_optimizer_state_by_parameter_name():
+    """Adam state keyed by parameter name loads into an optimizer whose parameters come in another
+    order; the positional keys of the reference keep working."""
+    from infinitrain_b200 import nn
+    from infinitrain_b200.optim import Adam
+
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(4, 3), nn.Linear(3, 2))
+    opt = Adam(m.Parameters(), 1e-2)
+    for _ in range(2):
+        opt.ZeroGrad()
+        m(torch.randn(5, 4)).sum().backward()
+        opt.Step()
+    named = opt.NamedStateDict(m)
+    assert "adam.m.0.weight" in named and "adam.v.1.bias" in named and int(named["adam.t"]) == 2
+    other = Adam(list(reversed(m.Parameters())), 1e-2)
+    other.LoadStateDict(named, model=m)
+    for p, mm in zip(other.params, other.m):
+        i = [id(q) for q in opt.params].index(id(p))
+        assert torch.equal(mm, opt.m[i])
+    assert other.t == 2
+    again = Adam(m.Parameters(), 1e-2)
+    again.LoadStateDict(opt.StateDict())                      # positional form
+    assert torch.equal(again.v[3], opt.v[3])

@@ -141,3 +141,17 @@ def test_corrupted_checkpoint_is_rejected(tmp_path):
     corrupt_file(path, 0, 4)               # the magic number
     with pytest.raises(Exception):
         Checkpoint.LoadStateDict(path)
+
+
+def test_file_rendezvous(tmp_path):
+    """Ranks with no MASTER_ADDR meet through a file on a shared filesystem (the reference's scheme)."""
+    import subprocess
+    import sys
+
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "rdzv_worker.py")
+    path = str(tmp_path / "rendezvous.bin")
+    procs = [subprocess.Popen([sys.executable, worker, str(r), "2", path], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              text=True) for r in range(2)]
+    outs = [p.communicate(timeout=180)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+    assert "rank 0 ok" in outs[0] and "rank 1 ok" in outs[1]
