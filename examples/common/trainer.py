@@ -50,7 +50,9 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     a("--weight_decay", type=float, default=0.0)
     a("--optimizer", default="sgd" if family == "gpt2" else "adam", choices=["sgd", "adam", "adamw"])
     a("--zero_stage", type=int, default=0)
-    a("--val_loss_every", type=int, default=0)
+    a("--val_loss_every", type=int, default=0,
+      help="every N steps (and after the last one) log the mean loss over --val_max_batches batches of --input_val_bin")
+    a("--val_max_batches", type=int, default=20)
     a("--sample_every", type=int, default=0)
     a("--overfit_single_batch", action="store_true")
     a("--device", default="cuda" if torch.cuda.is_available() else "cpu")
@@ -214,6 +216,9 @@ def main(family: str, argv=None) -> int:
     train_ds = TinyShakespeareDataset(data_path, T)
     loader = DistributedDataLoader(train_ds, loader_batch, dp_rank, dp)
     tokenizer = Tokenizer(args.tokenizer_bin) if args.tokenizer_bin else None
+    val_loader = None
+    if args.input_val_bin and args.val_loss_every > 0:
+        val_loader = DistributedDataLoader(TinyShakespeareDataset(args.input_val_bin, T), B, dp_rank, dp)
 
     # ---- resume
     start_step = 0
@@ -312,6 +317,23 @@ def main(family: str, argv=None) -> int:
                     metrics = MetricsSink(args.metrics_jsonl)
                 metrics.write(step=step + 1, loss=lossf, lr=args.learning_rate, host_ms=dur_ms, device_ms=dev_ms,
                               tokens_per_s=tps, peak_used_mb=used, peak_reserved_mb=reserved, dp=dp, tp=tp, sp=sp, pp=pp)
+        if (val_loader is not None and pp == 1
+                and ((step + 1) % args.val_loss_every == 0 or step + 1 == args.num_iteration)):
+            # validation loss (a TODO in the reference's loop, example/gpt2/main.cc:401-404): no gradients, the
+            # first batches of this rank's share of the file, averaged over the data-parallel group
+            with torch.no_grad():
+                total, n = torch.zeros((), device=dev), 0
+                for vx, vy in val_loader:
+                    with AutocastGuard(dtype=dtype, enabled=to_torch_dtype(dtype) != torch.float32):
+                        total += loss_fn(model(vx.to(dev)), vy.to(dev)).float()
+                    n += 1
+                    if n >= args.val_max_batches:
+                        break
+                total /= max(n, 1)
+                if dp > 1:
+                    ProcessGroupFactory.Instance().dp_group().AllReduce(total, ReduceOpType.kAvg)
+            if rank == last_rank:
+                LOG("ERROR", f"step {step + 1:4d}/{args.num_iteration} | val loss {total.item():.6f} ({n} batches)")
         if tokenizer is not None and args.freq_generate_txt and (step + 1) % args.freq_generate_txt == 0 and pp == 1:
             tokenizer.GenerateText(model, B, T, args.text_length, dev)
         if args.save and args.save_interval and (step + 1) % args.save_interval == 0:

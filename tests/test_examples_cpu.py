@@ -125,3 +125,20 @@ def test_run_matrix_and_compare(tmp_path):
               "--only", "1,1_bfloat16,zero1", "--port", "29760", *extra], timeout=900)
     assert sorted(os.listdir(a)) == ["gpt2_1.log", "gpt2_1_bfloat16.log", "llama3_zero1.log"]
     assert len(_losses(open(a / "llama3_zero1.log").read())) == 3
+
+
+def test_validation_loss_is_logged(tmp_path):
+    import torch
+
+    from infinitrain_b200.data import write_token_file
+
+    g = torch.Generator().manual_seed(3)
+    val = str(tmp_path / "val.bin")
+    write_token_file(val, torch.randint(0, 512, (2 * 32 * 6 + 1,), generator=g).tolist())
+    out = _run([sys.executable, "examples/gpt2/main.py", "--device", "cpu", "--n_layer", "2", "--n_embd", "64", "--n_head", "4",
+                "--vocab_size", "512", "--batch_size", "2", "--sequence_length", "32", "--total_batch_size", "64",
+                "--num_iteration", "5", "--optimizer", "adam", "--learning_rate", "1e-3", "--input_val_bin", val,
+                "--val_loss_every", "2", "--val_max_batches", "4"])
+    vals = [(int(m.group(1)), float(m.group(2))) for m in re.finditer(r"step\s+(\d+)/5 \| val loss ([\d.]+) \(4 batches\)", out)]
+    assert [s for s, _ in vals] == [2, 4, 5] and all(5.0 < v < 8.0 for _, v in vals)
+    assert len(_losses(out)) == 5                     # the train-loss parser does not pick the validation lines up
