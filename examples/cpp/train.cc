@@ -132,6 +132,9 @@ int main(int argc, char** argv) {
     consumed = st.consumed_batches;
   }
   const int64_t save_interval = fl.geti("save_interval", 0);
+  std::unique_ptr<itb::data::Tokenizer> tokenizer;
+  if (!fl.get("tokenizer_bin", "").empty()) tokenizer = std::make_unique<itb::data::Tokenizer>(fl.get("tokenizer_bin", ""));
+  const int64_t freq_generate = fl.geti("freq_generate_txt", 10), text_length = fl.geti("text_length", 64);
 
   for (int64_t step = start_step; step < iters; ++step) {
     auto t0 = std::chrono::steady_clock::now();
@@ -155,6 +158,14 @@ int main(int argc, char** argv) {
     std::fprintf(stderr, "[E] step %4lld/%lld | train loss %.6f | lr %.2e | (%.2f ms | %.0f tok/s | peak used: %5.0f MB | "
                          "peak reserved: %5.0f MB, DP=1, TP=1, SP=1, PP=1)\n",
                  (long long)(step + 1), (long long)iters, lossf, lr, ms, total / (ms / 1e3), 0.0, 0.0);
+    if (tokenizer && freq_generate > 0 && (step + 1) % freq_generate == 0) {
+      std::vector<int64_t> ids;
+      std::string text = tokenizer->GenerateText([&](const itb::Tensor& ids_in) { return model->forward(ids_in); }, B, T,
+                                                 text_length, device, &ids);
+      std::printf("%s\n[generated ids]", text.c_str());
+      for (int64_t id : ids) std::printf(" %lld", (long long)id);
+      std::printf("\n");
+    }
     if (save_interval > 0 && (step + 1) % save_interval == 0 && !fl.get("save", "").empty()) {
       itb::io::TrainerState st;
       st.global_step = step + 1, st.consumed_batches = consumed, st.last_lr = lr;

@@ -14,4 +14,5 @@
 #include "module.h"
 #include "ops.h"
 #include "optim.h"
+#include "tokenizer.h"
 #include "transformer.h"

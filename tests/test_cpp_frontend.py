@@ -142,3 +142,34 @@ def test_lora_training_matches_python_trainer_and_reference(trainer, files):
     if os.path.exists(REF):
         ref = _run([REF, *common, "--overfit_single_batch=false"], files)
         assert max(abs(x - y) for x, y in zip(cpp, ref)) <= 1e-5, list(zip(cpp, ref))
+
+
+def test_text_generation_matches_python_sampler(trainer, tmp_path):
+    """Same weights, same tokenizer file, same xorshift* stream: the C++ trainer and the Python
+    Tokenizer.GenerateText sample the same continuation of the reference's prompt."""
+    from infinitrain_b200.data import Tokenizer, write_token_file
+    from infinitrain_b200.data.tokenizer import write_tokenizer_file
+    from infinitrain_b200.models import llmc
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+    from infinitrain_b200.parallel import global_env as genv
+
+    genv.InitAllEnv(world_size=1, rank=0)
+    V = 4096                                                 # the prompt's GPT-2 token ids go up to 3616
+    cfg = TransformerConfig.GPT2(n_layer=1, n_embd=48, n_head=12, n_kv_head=12, vocab_size=V, original_vocab_size=V,
+                                 block_size=32)
+    torch.manual_seed(5)
+    m = TransformerModel(cfg)
+    with torch.no_grad():
+        for p in m.parameters():
+            p.normal_(0, 0.3)
+    llmc.write_gpt2_llmc(str(tmp_path / "m.bin"), cfg, llmc.full_state_dict(m))
+    write_tokenizer_file(str(tmp_path / "tok.bin"), [f"<{i}>".encode() for i in range(V)], eot=V - 1)
+    write_token_file(str(tmp_path / "t.bin"), torch.randint(0, V, (2 * 32 * 4 + 1,)).tolist())
+    want = Tokenizer(str(tmp_path / "tok.bin")).GenerateText(m, 2, 32, 16, torch.device("cpu"), print_fn=None)
+    r = subprocess.run([trainer, "--family", "gpt2", "--device", "cpu", "--llmc_filepath", "m.bin", "--input_bin", "t.bin",
+                        "--tokenizer_bin", "tok.bin", "--batch_size", "2", "--sequence_length", "32", "--total_batch_size",
+                        "64", "--num_iteration", "1", "--learning_rate", "0", "--freq_generate_txt", "1", "--text_length", "16"],
+                       capture_output=True, text=True, timeout=300, cwd=tmp_path, env=ENV)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [ln for ln in r.stdout.splitlines() if ln.startswith("The meaning of life is")]
+    assert got == [want] and want.count("<") == 11, (got, want)
