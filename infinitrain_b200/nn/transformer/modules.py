@@ -38,9 +38,15 @@ def _aligned() -> bool:
     what the reference's module of the same name computes (no residual add inside the projections,
     GELU as its own module, token and position tables looked up separately), so that the two
     frameworks' per-module logs and dumps line up.  Off, the fused formulations run."""
-    from ...utils.precision_checker import PrecisionCheckEnv, PrecisionCheckLevel
+    global _CHECK_ENV
+    if _CHECK_ENV is None:
+        from ...utils.precision_checker import PrecisionCheckEnv
 
-    return PrecisionCheckEnv.Instance().config.level != PrecisionCheckLevel.OFF
+        _CHECK_ENV = PrecisionCheckEnv.Instance()
+    return int(_CHECK_ENV.config.level) != 0
+
+
+_CHECK_ENV = None
 
 
 def _make_norm(config: TransformerConfig):
