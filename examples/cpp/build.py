@@ -42,6 +42,10 @@ def build(cuda: bool = False, out: str | None = None) -> Path:
         nvdirs = sorted(str(d) for d in nv.glob("*/lib")) if nv.is_dir() else []
         for d in nvdirs:
             cmd += [f"-L{d}", f"-Wl,-rpath,{d}"]
+        if (nv / "nccl" / "include").is_dir():         # the NCCL that libtorch_cuda itself loads
+            cmd += [f"-I{nv / 'nccl' / 'include'}", "-l:libnccl.so.2"]
+        else:
+            cmd += ["-lnccl"]
         cmd += ["-Wl,--allow-shlib-undefined"]
         cmd += ["-DITB_WITH_CUDA", f"-I{os.environ.get('CUDA_HOME', '/usr/local/cuda')}/include", "-Wl,--no-as-needed",
                 "-ltorch_cuda", "-lc10_cuda", f"-L{os.environ.get('CUDA_HOME', '/usr/local/cuda')}/lib64", "-lcudart",

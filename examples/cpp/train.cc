@@ -1,5 +1,6 @@
 // GPT-2 / LLaMA-3 training loop on the C++ frontend, with the flag names and the per-step log line of
-// the reference's example/gpt2/main.cc and example/llama3/main.cc (single process, one device).
+// the reference's example/gpt2/main.cc and example/llama3/main.cc: one process per device, data
+// parallel over the ranks that infini_run / torchrun start (RANK, WORLD_SIZE, MASTER_ADDR, MASTER_PORT).
 //
 //   itb_train --family gpt2 --llmc_filepath model.bin --input_bin tokens.bin --batch_size 4
 //             --sequence_length 64 --total_batch_size 256 --num_iteration 10 --learning_rate 1e-4
@@ -80,9 +81,12 @@ int main(int argc, char** argv) {
   const double lr = fl.getd("learning_rate", family == "gpt2" ? 1e-4 : 1e-5);
   const std::string opt_name = fl.get("optimizer", family == "gpt2" ? "sgd" : "adam");
   const bool bf16 = fl.get("dtype", "float32") == "bfloat16";
-  TORCH_CHECK(total % (B * T) == 0, "total_batch_size must be a multiple of batch_size * sequence_length");
-  const int64_t grad_accum = total / (B * T);
-  torch::Device device(fl.get("device", "cpu") == "cuda" ? torch::kCUDA : torch::kCPU);
+  const int64_t world_env = itb::dist::Env::FromEnvironment().world;
+  TORCH_CHECK(total % (B * T * world_env) == 0, "total_batch_size must be a multiple of batch_size * sequence_length * ranks");
+  const int64_t grad_accum = total / (B * T * world_env);
+  const itb::dist::Env env = itb::dist::Env::FromEnvironment();    // one process per device (infini_run / torchrun)
+  torch::Device device = fl.get("device", "cpu") == "cuda" ? torch::Device(torch::kCUDA, env.local_rank) : torch::Device(torch::kCPU);
+  const int64_t dp = env.world;
   itb::nn::ManualSeed(static_cast<uint32_t>(fl.geti("seed", 42)));
 
   std::shared_ptr<itb::nn::TransformerModel> model;
@@ -111,6 +115,12 @@ int main(int argc, char** argv) {
     if (!fl.get("lora_load_path", "").empty()) lora::LoadLoRAWeights(model, fl.get("lora_load_path", ""));
     std::fprintf(stderr, "[I] %s\n", lora::PrintLoRASummary(model).c_str());
   }
+  std::shared_ptr<itb::dist::Comm> comm;
+  std::unique_ptr<itb::dist::DistributedDataParallel> ddp;
+  if (dp > 1) {
+    comm = itb::dist::MakeComm(env, device);
+    ddp = std::make_unique<itb::dist::DistributedDataParallel>(model, comm);   // parameters become rank 0's
+  }
   itb::TensorList trainable = itb::nn::lora::TrainableParameters(model);
 
   std::unique_ptr<itb::optim::Optimizer> optimizer;
@@ -118,7 +128,7 @@ int main(int argc, char** argv) {
   else optimizer = std::make_unique<itb::optim::Adam>(trainable, lr, 0.9, 0.999, 1e-8,
                                                       opt_name == "adamw" ? fl.getd("weight_decay", 0.1) : 0.0);
 
-  itb::io::TokenLoader loader(fl.get("input_bin", ""), B, T);
+  itb::io::TokenLoader loader(fl.get("input_bin", ""), B, T, env.rank, dp);
   int64_t start_step = 0, consumed = 0;
   if (!fl.get("load", "").empty()) {
     const std::string dir = fl.get("load", "");
@@ -153,12 +163,19 @@ int main(int argc, char** argv) {
       lossf += loss.item<float>();
       loss.backward();
     }
+    if (ddp) {
+      ddp->SyncGradients();
+      itb::Tensor l = torch::full({1}, lossf, torch::dtype(torch::kFloat32).device(device));
+      comm->AllReduceSum(l);
+      lossf = l.item<float>() / static_cast<double>(dp);
+    }
     optimizer->Step();
     double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
-    std::fprintf(stderr, "[E] step %4lld/%lld | train loss %.6f | lr %.2e | (%.2f ms | %.0f tok/s | peak used: %5.0f MB | "
-                         "peak reserved: %5.0f MB, DP=1, TP=1, SP=1, PP=1)\n",
-                 (long long)(step + 1), (long long)iters, lossf, lr, ms, total / (ms / 1e3), 0.0, 0.0);
-    if (tokenizer && freq_generate > 0 && (step + 1) % freq_generate == 0) {
+    if (env.rank == dp - 1)   // the last rank logs, as in the reference
+      std::fprintf(stderr, "[E] step %4lld/%lld | train loss %.6f | lr %.2e | (%.2f ms | %.0f tok/s | peak used: %5.0f MB | "
+                           "peak reserved: %5.0f MB, DP=%lld, TP=1, SP=1, PP=1)\n",
+                   (long long)(step + 1), (long long)iters, lossf, lr, ms, total / (ms / 1e3), 0.0, 0.0, (long long)dp);
+    if (tokenizer && freq_generate > 0 && (step + 1) % freq_generate == 0 && env.rank == 0) {
       std::vector<int64_t> ids;
       std::string text = tokenizer->GenerateText([&](const itb::Tensor& ids_in) { return model->forward(ids_in); }, B, T,
                                                  text_length, device, &ids);
@@ -166,14 +183,15 @@ int main(int argc, char** argv) {
       for (int64_t id : ids) std::printf(" %lld", (long long)id);
       std::printf("\n");
     }
-    if (save_interval > 0 && (step + 1) % save_interval == 0 && !fl.get("save", "").empty()) {
+    if (save_interval > 0 && (step + 1) % save_interval == 0 && !fl.get("save", "").empty() && env.rank == 0) {
       itb::io::TrainerState st;
       st.global_step = step + 1, st.consumed_batches = consumed, st.last_lr = lr;
       st.n_layer = cfg.n_layer, st.n_head = cfg.n_head, st.n_kv_head = cfg.n_kv_head, st.n_embd = cfg.n_embd;
-      st.vocab_size = cfg.vocab_size;
+      st.vocab_size = cfg.vocab_size, st.ddp_size = dp;
       itb::io::SaveCheckpoint(fl.get("save", ""), st, *model, optimizer->StateDict());
     }
   }
-  if (lora_rank > 0 && !fl.get("lora_save_path", "").empty()) itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", ""));
+  if (comm) comm->Barrier();
+  if (lora_rank > 0 && !fl.get("lora_save_path", "").empty() && env.rank == 0) itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", ""));
   return 0;
 }

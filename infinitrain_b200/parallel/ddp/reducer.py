@@ -174,8 +174,9 @@ class Reducer:
 
     def RebindGradViews(self):
         """After ``ZeroGrad(set_to_none=True)`` the ``.grad`` views are gone: point them at the bucket
-        again and clear the stale bucket memory (a fresh step starts from zero); while gradients
-        are being accumulated over micro-batches the views are still bound and nothing is done."""
+        again and clear the stale bucket memory (a fresh step starts from zero); gradients that
+        micro-batches under ``no_sync`` accumulated in tensors of their own are carried into the
+        bucket; views that are still bound are left alone."""
         if not self.config.gradient_as_bucket_view or self.flat_buffer is not None:
             return
         for bucket in self.buckets:
@@ -186,6 +187,10 @@ class Reducer:
             bucket.contents.zero_()
             for p, off in zip(ps, bucket.offsets):
                 view = bucket.contents[off:off + p.numel()].view(p.shape)
+                if p.grad is not None:
+                    # gradients of earlier micro-batches, accumulated outside the bucket while the
+                    # synchronisation was off (no_sync): they move into the bucket, they are not dropped
+                    view.copy_(p.grad)
                 p.grad = view
                 p.main_grad = view
 

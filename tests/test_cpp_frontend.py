@@ -173,3 +173,22 @@ def test_text_generation_matches_python_sampler(trainer, tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     got = [ln for ln in r.stdout.splitlines() if ln.startswith("The meaning of life is")]
     assert got == [want] and want.count("<") == 11, (got, want)
+
+
+def test_two_rank_data_parallel_matches_python_ddp(trainer, files):
+    """Two CPU ranks started by the C++ launcher: the C++ trainer (gradient buckets averaged through its
+    store transport) and the Python trainer (gloo DDP) follow the same loss trajectory."""
+    from infinitrain_b200 import _ext
+
+    launcher = _ext.launcher_path()
+    if not launcher.exists():
+        _ext.build_launcher()
+    common = ["--device", "cpu", "--llmc_filepath", "gpt2.bin", "--input_bin", "tokens16.bin", "--batch_size", "2",
+              "--sequence_length", "64", "--total_batch_size", "512", "--num_iteration", "5", "--dtype", "float32",
+              "--learning_rate", "0.05", "--optimizer", "sgd"]
+    cpp = _run([launcher, "--nproc_per_node=2", "--rdzv_endpoint=127.0.0.1:29741", "--", trainer, "--family", "gpt2", *common],
+               files)
+    py = _run([launcher, "--nproc_per_node=2", "--rdzv_endpoint=127.0.0.1:29742", "--", sys.executable,
+               os.path.join(ROOT, "examples", "gpt2", "main.py"), *common], files)
+    assert len(cpp) == 5 and len(py) == 5, (cpp, py)
+    assert max(abs(a - b) for a, b in zip(cpp, py)) <= 1e-5, list(zip(cpp, py))

@@ -142,3 +142,24 @@ def test_validation_loss_is_logged(tmp_path):
     vals = [(int(m.group(1)), float(m.group(2))) for m in re.finditer(r"step\s+(\d+)/5 \| val loss ([\d.]+) \(4 batches\)", out)]
     assert [s for s, _ in vals] == [2, 4, 5] and all(5.0 < v < 8.0 for _, v in vals)
     assert len(_losses(out)) == 5                     # the train-loss parser does not pick the validation lines up
+
+
+def test_ddp_with_gradient_accumulation_equals_one_rank(tmp_path):
+    """Two data-parallel ranks with two micro-batches each see the same four batches per step as one
+    rank with four micro-batches: the loss trajectories must coincide (gradients of the micro-batches
+    that ran under no_sync are part of the bucket that gets averaged)."""
+    import torch
+
+    from infinitrain_b200.data import write_token_file
+
+    g = torch.Generator().manual_seed(4)
+    data = str(tmp_path / "train.bin")
+    write_token_file(data, torch.randint(0, 512, (2 * 32 * 24 + 1,), generator=g).tolist())
+    common = ["examples/gpt2/main.py", "--device", "cpu", "--n_layer", "2", "--n_embd", "64", "--n_head", "4",
+              "--vocab_size", "512", "--batch_size", "2", "--sequence_length", "32", "--total_batch_size", "256",
+              "--num_iteration", "4", "--optimizer", "sgd", "--learning_rate", "0.5", "--input_bin", data, "--seed", "7"]
+    one = _losses(_run([sys.executable, *common]))
+    two = _losses(_run([_launcher(), "--nproc_per_node=2", "--rdzv_endpoint=127.0.0.1:29927", "--", sys.executable, *common]))
+    assert len(one) == 4 and len(two) == 4
+    assert max(abs(a - b) for a, b in zip(one, two)) <= 2e-5, list(zip(one, two))
+    assert abs(one[0] - one[-1]) > 1e-3
