@@ -58,6 +58,12 @@ class DistributedDataParallel(Module):
         if not params:
             return
         if self.config.zero_stage >= 1:
+            # ZeRO consumes gradients during backward (reduce-scatter into shards; with the fused kernels
+            # also the optimizer step): the tensor-parallel sum of sequence-parallel-replicated parameters'
+            # gradients has to happen before that, inside backward
+            from ..tensor_parallel import InstallSequenceParallelGradHooks
+
+            InstallSequenceParallelGradHooks(params)
             self._build_param_and_grad_buffers(params)
         elif self.config.gradient_bucketing_enabled:
             self._build_reducer(params)

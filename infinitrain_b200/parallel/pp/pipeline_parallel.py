@@ -156,6 +156,12 @@ class PipelineSchedule:
             tgs = list(target.chunk(self.n, dim=0))
         optimizer.ZeroGrad()
         loss = self.StepMicroBatches(mbs, tgs, loss_fn, dtype)
+        # under sequence parallelism the replicated parameters of this stage (norm weights, position
+        # table, row-parallel biases) hold the gradient of their sequence slice only
+        from ..tensor_parallel import AllReduceSequenceParallelGrads
+
+        for chunk in self.stage.mutable_chunks():
+            AllReduceSequenceParallelGrads(chunk)
         optimizer.Step()
         return loss
 

@@ -456,6 +456,32 @@ class VocabParallelCrossEntropyLoss(Module):
         return per_tok.reshape(-1).mean()
 
 
+def InstallSequenceParallelGradHooks(params) -> int:
+    """Sums the gradient of every sequence-parallel-replicated parameter over the tensor-parallel
+    group INSIDE backward (a tensor hook, before the gradient is accumulated).  Needed wherever
+    the gradient is consumed before backward returns -- ZeRO reduce-scatters into shards and the fused
+    reduce-scatter + AdamW kernels run as soon as a bucket is complete -- so that a sum after
+    backward (``AllReduceSequenceParallelGrads``) would come too late; parameters hooked here are
+    skipped by that function.  Returns the number of parameters hooked."""
+    grp = _tp()
+    if grp is None or not genv.GetSequenceParallelEnabled():
+        return 0
+    n = 0
+    for p in params:
+        if not getattr(p, "_itb_sp_replicated", False) or getattr(p, "_itb_sp_hooked", False) or not p.requires_grad:
+            continue
+
+        def hook(g, _grp=grp):
+            out = g.detach().clone(memory_format=torch.contiguous_format)
+            _grp.AllReduce(out, ReduceOpType.kSum)
+            return out
+
+        p.register_hook(hook)
+        p._itb_sp_hooked = True
+        n += 1
+    return n
+
+
 def AllReduceSequenceParallelGrads(model: torch.nn.Module) -> int:
     """Sums, over the tensor-parallel group, the gradients of parameters that are replicated across
     TP ranks but see only a slice of the sequence under sequence parallelism (norm weights, position
@@ -471,7 +497,7 @@ def AllReduceSequenceParallelGrads(model: torch.nn.Module) -> int:
         return 0
     grads = []
     for p in model.parameters():
-        if getattr(p, "_itb_sp_replicated", False):
+        if getattr(p, "_itb_sp_replicated", False) and not getattr(p, "_itb_sp_hooked", False):
             g = p.grad if p.grad is not None else getattr(p, "main_grad", None)
             if g is not None:
                 grads.append(g)

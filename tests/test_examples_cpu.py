@@ -163,3 +163,51 @@ def test_ddp_with_gradient_accumulation_equals_one_rank(tmp_path):
     assert len(one) == 4 and len(two) == 4
     assert max(abs(a - b) for a, b in zip(one, two)) <= 2e-5, list(zip(one, two))
     assert abs(one[0] - one[-1]) > 1e-3
+
+
+@pytest.fixture(scope="module")
+def llama_files(tmp_path_factory):
+    import torch
+
+    from infinitrain_b200.data import write_token_file
+    from infinitrain_b200.models import llmc
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+    from infinitrain_b200.parallel import global_env as genv
+
+    d = tmp_path_factory.mktemp("hybrid")
+    genv.InitAllEnv(world_size=1, rank=0)
+    cfg = TransformerConfig.LLaMA3(n_layer=4, n_embd=64, n_head=4, n_kv_head=2, vocab_size=256, original_vocab_size=256,
+                                   block_size=64, multiple_of=16, ffn_dim_multiplier=1.5)
+    torch.manual_seed(42)
+    m = TransformerModel(cfg)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() > 1:
+                p.normal_(0, 0.1)
+    llmc.write_llama3_llmc(str(d / "l4.bin"), cfg, llmc.full_state_dict(m))
+    g = torch.Generator().manual_seed(1)
+    write_token_file(str(d / "tok.bin"), torch.randint(0, 256, (4 * 64 * 30 + 1,), generator=g).tolist(), llama3=True)
+    common = ["examples/llama3/main.py", "--device", "cpu", "--llmc_filepath", str(d / "l4.bin"), "--input_bin", str(d / "tok.bin"),
+              "--batch_size", "2", "--sequence_length", "64", "--total_batch_size", "512", "--num_iteration", "3",
+              "--dtype", "float32", "--learning_rate", "0.05", "--optimizer", "sgd"]
+    return common, _losses(_run([sys.executable, *common]))
+
+
+@pytest.mark.parametrize("ranks,flags", [
+    (4, ["--tensor_parallel", "2", "--sequence_parallel", "--zero_stage", "2"]),
+    (4, ["--tensor_parallel", "2", "--sequence_parallel", "--pipeline_parallel", "2"]),
+    (8, ["--tensor_parallel", "2", "--sequence_parallel", "--pipeline_parallel", "2", "--virtual_pipeline_parallel", "2",
+         "--zero_stage", "2"]),
+])
+def test_hybrid_parallel_runs_follow_the_one_rank_trajectory(llama_files, ranks, flags):
+    """DP x TP+SP x PP (x vPP, ZeRO) on CPU ranks against ONE rank on the same weights and the same
+    global batch: the same losses step by step.  Catches gradients that a parallel mode loses or
+    counts twice (sequence-parallel-replicated parameters under ZeRO-2 or inside a pipeline stage)."""
+    common, one = llama_files
+    port = 29940 + ranks + len(flags)
+    out = _run([_launcher(), f"--nproc_per_node={ranks}", f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable, *common,
+                *flags], timeout=900)
+    got = _losses(out)
+    assert len(one) == 3 and len(got) == 3
+    assert max(abs(a - b) for a, b in zip(one, got)) <= 2e-5, list(zip(one, got))
+    assert abs(one[0] - one[1]) > 1e-2
