@@ -3,4 +3,4 @@ from .lora_layers import LoRAColumnParallelLinear, LoRALinear, LoRARowParallelLi
 from .lora_utils import (CountTotalParameters, CountTrainableParameters, FreezeBaseModel, GetBaseParameters,
                          GetLoRAModel, GetLoRAParameters, InjectLoRALayers, LoadLoRAStateDict, LoadLoRAWeights,
                          LoRAStateDict, MergeAndUnload, MergeLoRAWeights, PrintLoRASummary, ReplaceModuleByPath,
-                         SaveLoRAWeights, UnfreezeModel, UnmergeLoRAWeights)
+                         SaveLoRAWeights, ShardedLoRAPath, UnfreezeModel, UnmergeLoRAWeights)

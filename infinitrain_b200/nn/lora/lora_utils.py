@@ -196,6 +196,20 @@ def LoadLoRAStateDict(model: Module, state_dict: Dict[str, torch.Tensor]) -> Non
             warnings.warn(f"LoRA parameter not found in model: {k}")
 
 
+def ShardedLoRAPath(filepath: str) -> str:
+    """The adapter file of THIS rank.  With tensor or pipeline parallelism a rank holds a shard of
+    the adapters (its slice of the sharded factors, the layers of its stage under their local
+    names), so every (tp, pp) coordinate has a file of its own, ``<path>.tp<i>.pp<j>``; data-parallel
+    replicas share it.  Without model parallelism the path is returned unchanged.  (In the reference
+    every rank writes the one path it was given: example/gpt2/main.cc:531-534.)"""
+    from ...parallel import global_env as genv
+
+    tp, pp = genv.GetTensorParallelSize(), genv.GetPipelineParallelSize()
+    if tp <= 1 and pp <= 1:
+        return filepath
+    return f"{filepath}.tp{genv.GetTensorParallelRank()}.pp{genv.GetPipelineParallelRank()}"
+
+
 def SaveLoRAWeights(model: Module, filepath: str) -> None:
     sd = LoRAStateDict(model)
     with open(filepath, "wb") as f:

@@ -211,3 +211,26 @@ def test_hybrid_parallel_runs_follow_the_one_rank_trajectory(llama_files, ranks,
     assert len(one) == 3 and len(got) == 3
     assert max(abs(a - b) for a, b in zip(one, got)) <= 2e-5, list(zip(one, got))
     assert abs(one[0] - one[1]) > 1e-2
+
+
+def test_lora_adapters_are_saved_and_loaded_per_model_parallel_coordinate(llama_files, tmp_path):
+    """Under tensor parallelism every TP rank writes its shard of the adapters to a file of its own;
+    a later run that loads them continues where the first stopped."""
+    common, _ = llama_files
+    lora_flags = ["--lora_rank", "4", "--lora_alpha", "8", "--lora_target_modules", "c_attn,c_proj,c_fc,c_fc2",
+                  "--tensor_parallel", "2", "--sequence_parallel", "--overfit_single_batch"]
+    base = [a for a in common]
+    path = str(tmp_path / "adapter.bin")
+
+    def run(port, iters, extra):
+        args = list(base)
+        args[args.index("--num_iteration") + 1] = str(iters)
+        return _losses(_run([_launcher(), "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable,
+                             *args, *lora_flags, *extra]))
+
+    first = run(29961, 2, ["--lora_save_path", path])
+    assert sorted(os.listdir(tmp_path)) == ["adapter.bin.tp0.pp0", "adapter.bin.tp1.pp0"]
+    whole = run(29962, 3, [])
+    cont = run(29963, 1, ["--lora_load_path", path])
+    assert first == whole[:2]
+    assert abs(cont[0] - whole[2]) <= 2e-6 and abs(whole[2] - whole[0]) > 1e-4, (cont, whole)
