@@ -171,7 +171,7 @@ def main(family: str, argv=None) -> int:
                                target_modules=lora.ParseLoRATargetModules(args.lora_target_modules))
         model = lora.GetLoRAModel(model, lcfg)
         if args.lora_load_path:
-            lora.LoadLoRAWeights(model, lora.ShardedLoRAPath(args.lora_load_path))
+            lora.LoadFullLoRAWeights(model, args.lora_load_path)    # whole-model file, sharded on load
         if rank == 0:
             lora.PrintLoRASummary(model, lambda s: LOG("INFO", s))
     trainable = [p for p in model.parameters() if p.requires_grad]
@@ -339,9 +339,9 @@ def main(family: str, argv=None) -> int:
         if args.save and args.save_interval and (step + 1) % args.save_interval == 0:
             SaveCheckpoint(args.save, step + 1, model, optimizer, cfg, consumed, args.learning_rate,
                            args.save_optimizer_state, args.max_checkpoint_keep)
-    if args.lora_rank > 0 and args.lora_save_path and dp_rank == 0:
-        # one file per (tp, pp) coordinate: each holds that rank's shard of the adapters
-        lora.SaveLoRAWeights(model, lora.ShardedLoRAPath(args.lora_save_path))
+    if args.lora_rank > 0 and args.lora_save_path:
+        # one whole-model file gathered from every tensor- and pipeline-parallel rank (a collective)
+        lora.SaveFullLoRAWeights(model, args.lora_save_path)
     if args.profile:
         profiler.Report(f"{family}.report.rank{rank}")
         profiler.PrintRecords(f"{family}.records.log.rank{rank}")

@@ -1,6 +1,7 @@
 from .lora_config import LoRAConfig, ParseLoRATargetModules
 from .lora_layers import LoRAColumnParallelLinear, LoRALinear, LoRARowParallelLinear
 from .lora_utils import (CountTotalParameters, CountTrainableParameters, FreezeBaseModel, GetBaseParameters,
-                         GetLoRAModel, GetLoRAParameters, InjectLoRALayers, LoadLoRAStateDict, LoadLoRAWeights,
+                         GatherFullLoRAStateDict, GetLoRAModel, GetLoRAParameters, InjectLoRALayers, LoadFullLoRAWeights,
+                         LoadLoRAStateDict, LoadLoRAWeights,
                          LoRAStateDict, MergeAndUnload, MergeLoRAWeights, PrintLoRASummary, ReplaceModuleByPath,
-                         SaveLoRAWeights, ShardedLoRAPath, UnfreezeModel, UnmergeLoRAWeights)
+                         SaveFullLoRAWeights, SaveLoRAWeights, ScatterFullLoRAStateDict, UnfreezeModel, UnmergeLoRAWeights)

@@ -127,10 +127,10 @@ class LoRAColumnParallelLinear(_LoRAMixin, ColumnParallelLinear):
         self.weight, self.bias = base_module.weight, base_module.bias
         self._setup_lora(config, (config.rank, self.in_features), (self.output_size_per_partition, config.rank),
                          self.weight.device)
-        # A sees the full input on every rank: its gradient is identical across the TP group unless
-        # the input is sequence-sharded upstream, in which case it is summed like other replicated
-        # parameters.
-        self.lora_A._itb_sp_replicated = True
+        # A is replicated but every rank back-propagates through its own shard of B: each holds one
+        # term of A's gradient, with or without sequence parallelism; the terms are summed over the
+        # tensor-parallel group before the optimizer step.
+        self.lora_A._itb_tp_partial_grad = True
 
     def Forward(self, x, gelu: bool = False):
         self._check_forward_allowed()
@@ -166,7 +166,9 @@ class LoRARowParallelLinear(_LoRAMixin, RowParallelLinear):
         self.weight, self.bias = base_module.weight, base_module.bias
         self._setup_lora(config, (config.rank, self.input_size_per_partition), (self.out_features, config.rank),
                          self.weight.device)
-        self.lora_B._itb_sp_replicated = True
+        # B is replicated but multiplies this rank's partial product x_r A_r^T: its gradient is one term
+        # of a sum over the tensor-parallel group
+        self.lora_B._itb_tp_partial_grad = True
 
     def Forward(self, x, residual=None):
         self._check_forward_allowed()

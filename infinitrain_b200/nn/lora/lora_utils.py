@@ -196,22 +196,127 @@ def LoadLoRAStateDict(model: Module, state_dict: Dict[str, torch.Tensor]) -> Non
             warnings.warn(f"LoRA parameter not found in model: {k}")
 
 
-def ShardedLoRAPath(filepath: str) -> str:
-    """The adapter file of THIS rank.  With tensor or pipeline parallelism a rank holds a shard of
-    the adapters (its slice of the sharded factors, the layers of its stage under their local
-    names), so every (tp, pp) coordinate has a file of its own, ``<path>.tp<i>.pp<j>``; data-parallel
-    replicas share it.  Without model parallelism the path is returned unchanged.  (In the reference
-    every rank writes the one path it was given: example/gpt2/main.cc:531-534.)"""
+# --------------------------------------------------------------------------- topology-independent adapters
+def _global_layer_indices(model) -> List[int]:
+    """Global index of every layer this rank holds, in the order of its local ``transformer.h.<i>`` names."""
+    info = getattr(model, "stage_info", None)
+    if info is None:
+        return []
+    out: List[int] = []
+    for s, e in sorted(info.layer_ranges_per_chunk):
+        out += list(range(s, e))
+    return out
+
+
+def _rename_layer(name: str, mapping: Dict[int, int]) -> str:
+    parts = name.split(".")
+    if len(parts) > 2 and parts[0] == "transformer" and parts[1] == "h" and parts[2].isdigit():
+        parts[2] = str(mapping[int(parts[2])])
+    return ".".join(parts)
+
+
+def _qkv_split(model, name: str):
+    """(q_rows, kv_rows) of the full fused projection when ``name`` is an attention ``c_attn``, else None."""
+    cfg = getattr(model, "config", None)
+    if cfg is None or not name.endswith("attn.c_attn.lora_B"):
+        return None
+    d = cfg.head_dim()
+    return cfg.n_head * d, cfg.n_kv_head * d
+
+
+def _modules_by_state_dict_path(model) -> Dict[str, Module]:
+    """path -> module with the paths state-dict keys use (``transformer.h.0.attn.c_attn``)."""
+    if hasattr(model, "NamedModules"):
+        return {n: m for n, m in model.NamedModules(remove_duplicate=False)}
+    return dict(model.named_modules(remove_duplicate=False))
+
+
+def GatherFullLoRAStateDict(model: Module) -> "OrderedDict[str, torch.Tensor]":
+    """The adapters of the WHOLE model under global names, assembled from every tensor- and
+    pipeline-parallel rank (a collective over all ranks of the job; every rank gets the result).
+    Column-parallel B factors are concatenated along the output rows (a fused QKV projection back into
+    its Q | K | V order), row-parallel A factors along the input columns, replicated factors are taken
+    from tensor-parallel rank 0, and a stage's local layer numbers become global ones."""
+    import torch.distributed as dist
+
     from ...parallel import global_env as genv
 
-    tp, pp = genv.GetTensorParallelSize(), genv.GetPipelineParallelSize()
-    if tp <= 1 and pp <= 1:
-        return filepath
-    return f"{filepath}.tp{genv.GetTensorParallelRank()}.pp{genv.GetPipelineParallelRank()}"
+    tp, tp_rank = genv.GetTensorParallelSize(), genv.GetTensorParallelRank()
+    local_to_global = dict(enumerate(_global_layer_indices(model)))
+    mine = {}
+    mods = _modules_by_state_dict_path(model)
+    for name, t in LoRAStateDict(model).items():
+        owner = mods.get(name.rsplit(".", 1)[0])
+        kind = "rep"
+        if isinstance(owner, LoRAColumnParallelLinear) and name.endswith("lora_B") and tp > 1:
+            kind = "rows"
+        elif isinstance(owner, LoRARowParallelLinear) and name.endswith("lora_A") and tp > 1:
+            kind = "cols"
+        mine[_rename_layer(name, local_to_global) if local_to_global else name] = (kind, tp_rank, t.detach().float().cpu())
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        everyone = [None] * dist.get_world_size()
+        dist.all_gather_object(everyone, mine if genv.GetDataParallelRank() == 0 else {})
+    else:
+        everyone = [mine]
+    pieces: Dict[str, Dict[int, torch.Tensor]] = {}
+    kinds: Dict[str, str] = {}
+    for d in everyone:
+        for name, (kind, r, t) in d.items():
+            pieces.setdefault(name, {})[r] = t
+            kinds[name] = kind
+    out = OrderedDict()
+    for name in sorted(pieces):
+        shards = [pieces[name][r] for r in sorted(pieces[name])]
+        if kinds[name] == "rep":
+            out[name] = shards[0]
+        elif kinds[name] == "cols":
+            out[name] = torch.cat(shards, dim=1)
+        else:
+            split = _qkv_split(model, name)
+            if split is None:
+                out[name] = torch.cat(shards, dim=0)
+            else:
+                q, kv = split[0] // len(shards), split[1] // len(shards)
+                out[name] = torch.cat([s[:q] for s in shards] + [s[q:q + kv] for s in shards] + [s[q + kv:] for s in shards], 0)
+    return out
 
 
-def SaveLoRAWeights(model: Module, filepath: str) -> None:
-    sd = LoRAStateDict(model)
+def ScatterFullLoRAStateDict(model: Module, full: Dict[str, torch.Tensor]) -> int:
+    """Loads this rank's part of a whole-model adapter dict (global names, unsharded factors): the
+    inverse of :func:`GatherFullLoRAStateDict`.  Returns the number of tensors loaded."""
+    from ...parallel import global_env as genv
+
+    tp, tp_rank = genv.GetTensorParallelSize(), genv.GetTensorParallelRank()
+    local_to_global = dict(enumerate(_global_layer_indices(model)))
+    mods = _modules_by_state_dict_path(model)
+    n = 0
+    for name, dst in LoRAStateDict(model).items():
+        gname = _rename_layer(name, local_to_global) if local_to_global else name
+        if gname not in full:
+            raise KeyError(f"adapter file has no tensor '{gname}'")
+        src = full[gname].float()
+        owner = mods.get(name.rsplit(".", 1)[0])
+        if tp > 1 and isinstance(owner, LoRAColumnParallelLinear) and name.endswith("lora_B"):
+            split = _qkv_split(model, name)
+            if split is None:
+                k = src.shape[0] // tp
+                src = src[tp_rank * k:(tp_rank + 1) * k]
+            else:
+                qr, kvr = split
+                q, k_, v = src[:qr], src[qr:qr + kvr], src[qr + kvr:]
+                src = torch.cat([t[tp_rank * (t.shape[0] // tp):(tp_rank + 1) * (t.shape[0] // tp)] for t in (q, k_, v)], 0)
+        elif tp > 1 and isinstance(owner, LoRARowParallelLinear) and name.endswith("lora_A"):
+            k = src.shape[1] // tp
+            src = src[:, tp_rank * k:(tp_rank + 1) * k]
+        if tuple(src.shape) != tuple(dst.shape):
+            raise ValueError(f"adapter tensor '{gname}' has shape {tuple(src.shape)}, this rank needs {tuple(dst.shape)}")
+        with torch.no_grad():
+            dst.copy_(src.to(dst.device, dst.dtype))
+        n += 1
+    return n
+
+
+def _write_lora_file(sd: Dict[str, torch.Tensor], filepath: str) -> None:
     with open(filepath, "wb") as f:
         f.write(struct.pack("<III", kLoRAMagic, 1, len(sd)))
         for name, t in sd.items():
@@ -224,7 +329,7 @@ def SaveLoRAWeights(model: Module, filepath: str) -> None:
             f.write(t.detach().float().cpu().contiguous().numpy().tobytes())
 
 
-def LoadLoRAWeights(model: Module, filepath: str) -> None:
+def _read_lora_file(filepath: str) -> Dict[str, torch.Tensor]:
     with open(filepath, "rb") as f:
         magic, version, count = struct.unpack("<III", f.read(12))
         if magic != kLoRAMagic:
@@ -238,9 +343,36 @@ def LoadLoRAWeights(model: Module, filepath: str) -> None:
             (ndim,) = struct.unpack("<I", f.read(4))
             dims = [struct.unpack("<q", f.read(8))[0] for _ in range(ndim)]
             n = int(np.prod(dims)) if dims else 1
-            data = np.frombuffer(f.read(4 * n), dtype="<f4").reshape(dims).copy()
-            sd[name] = torch.from_numpy(data)
-    LoadLoRAStateDict(model, sd)
+            sd[name] = torch.from_numpy(np.frombuffer(f.read(4 * n), dtype="<f4").reshape(dims).copy())
+    return sd
+
+
+def SaveFullLoRAWeights(model: Module, filepath: str) -> None:
+    """One adapter file for the whole model, whatever the parallel layout it was trained in (collective
+    over all ranks; global rank 0 writes).  The file is an ordinary adapter file: a single-rank run,
+    the C++ frontend and the reference read it."""
+    import torch.distributed as dist
+
+    full = GatherFullLoRAStateDict(model)
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        _write_lora_file(full, filepath)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def LoadFullLoRAWeights(model: Module, filepath: str) -> None:
+    """Loads a whole-model adapter file into this rank's shard of the model (any parallel layout)."""
+    ScatterFullLoRAStateDict(model, _read_lora_file(filepath))
+
+
+def SaveLoRAWeights(model: Module, filepath: str) -> None:
+    """This rank's adapter tensors under their local names (the reference's file: magic 0x4C4F5241,
+    version 1, fp32; src/nn/lora/lora_utils.cc:309-358)."""
+    _write_lora_file(LoRAStateDict(model), filepath)
+
+
+def LoadLoRAWeights(model: Module, filepath: str) -> None:
+    LoadLoRAStateDict(model, _read_lora_file(filepath))
 
 
 def CountTrainableParameters(model: Module) -> int:

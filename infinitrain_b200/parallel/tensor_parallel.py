@@ -456,6 +456,15 @@ class VocabParallelCrossEntropyLoss(Module):
         return per_tok.reshape(-1).mean()
 
 
+def _needs_tp_grad_sum(p) -> bool:
+    """Replicated parameters whose gradient is, on each tensor-parallel rank, one term of a sum: those
+    that see a slice of the sequence under sequence parallelism (``_itb_sp_replicated``), and those that
+    sit next to a sharded factor whatever the sequence layout (``_itb_tp_partial_grad``: the replicated
+    LoRA factors of column- and row-parallel layers)."""
+    return (getattr(p, "_itb_tp_partial_grad", False)
+            or (getattr(p, "_itb_sp_replicated", False) and genv.GetSequenceParallelEnabled()))
+
+
 def InstallSequenceParallelGradHooks(params) -> int:
     """Sums the gradient of every sequence-parallel-replicated parameter over the tensor-parallel
     group INSIDE backward (a tensor hook, before the gradient is accumulated).  Needed wherever
@@ -464,11 +473,11 @@ def InstallSequenceParallelGradHooks(params) -> int:
     backward (``AllReduceSequenceParallelGrads``) would come too late; parameters hooked here are
     skipped by that function.  Returns the number of parameters hooked."""
     grp = _tp()
-    if grp is None or not genv.GetSequenceParallelEnabled():
+    if grp is None:
         return 0
     n = 0
     for p in params:
-        if not getattr(p, "_itb_sp_replicated", False) or getattr(p, "_itb_sp_hooked", False) or not p.requires_grad:
+        if not _needs_tp_grad_sum(p) or getattr(p, "_itb_sp_hooked", False) or not p.requires_grad:
             continue
 
         def hook(g, _grp=grp):
@@ -493,11 +502,11 @@ def AllReduceSequenceParallelGrads(model: torch.nn.Module) -> int:
     gradient and nothing is done.
     """
     grp = _tp()
-    if grp is None or not genv.GetSequenceParallelEnabled():
+    if grp is None:
         return 0
     grads = []
     for p in model.parameters():
-        if getattr(p, "_itb_sp_replicated", False) and not getattr(p, "_itb_sp_hooked", False):
+        if _needs_tp_grad_sum(p) and not getattr(p, "_itb_sp_hooked", False):
             g = p.grad if p.grad is not None else getattr(p, "main_grad", None)
             if g is not None:
                 grads.append(g)

@@ -213,24 +213,32 @@ def test_hybrid_parallel_runs_follow_the_one_rank_trajectory(llama_files, ranks,
     assert abs(one[0] - one[1]) > 1e-2
 
 
-def test_lora_adapters_are_saved_and_loaded_per_model_parallel_coordinate(llama_files, tmp_path):
-    """Under tensor parallelism every TP rank writes its shard of the adapters to a file of its own;
-    a later run that loads them continues where the first stopped."""
+@pytest.mark.parametrize("ranks,flags", [
+    (2, ["--tensor_parallel", "2"]),
+    (8, ["--tensor_parallel", "2", "--sequence_parallel", "--pipeline_parallel", "2", "--virtual_pipeline_parallel", "2",
+         "--zero_stage", "2"]),
+])
+def test_lora_in_any_layout_follows_the_one_rank_run_and_writes_the_same_adapter(llama_files, tmp_path, ranks, flags):
+    """One whole-model adapter file goes into a one-rank run and into a model-parallel run: the same
+    losses, and the adapter gathered from the parallel ranks equals the one-rank result (sharded LoRA
+    factors re-assembled, the replicated ones' partial gradients summed over the tensor-parallel group,
+    a stage's local layer numbers made global)."""
+    import torch
+
+    from infinitrain_b200.nn.lora.lora_utils import _read_lora_file
+
     common, _ = llama_files
-    lora_flags = ["--lora_rank", "4", "--lora_alpha", "8", "--lora_target_modules", "c_attn,c_proj,c_fc,c_fc2",
-                  "--tensor_parallel", "2", "--sequence_parallel", "--overfit_single_batch"]
-    base = [a for a in common]
-    path = str(tmp_path / "adapter.bin")
-
-    def run(port, iters, extra):
-        args = list(base)
-        args[args.index("--num_iteration") + 1] = str(iters)
-        return _losses(_run([_launcher(), "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable,
-                             *args, *lora_flags, *extra]))
-
-    first = run(29961, 2, ["--lora_save_path", path])
-    assert sorted(os.listdir(tmp_path)) == ["adapter.bin.tp0.pp0", "adapter.bin.tp1.pp0"]
-    whole = run(29962, 3, [])
-    cont = run(29963, 1, ["--lora_load_path", path])
-    assert first == whole[:2]
-    assert abs(cont[0] - whole[2]) <= 2e-6 and abs(whole[2] - whole[0]) > 1e-4, (cont, whole)
+    lora_flags = ["--lora_rank", "4", "--lora_alpha", "8", "--lora_target_modules", "c_attn,c_proj,c_fc,c_fc2"]
+    start, one_out, par_out = (str(tmp_path / n) for n in ("start.bin", "one.bin", "par.bin"))
+    two_steps = list(common)
+    two_steps[two_steps.index("--num_iteration") + 1] = "2"
+    _run([sys.executable, *two_steps, *lora_flags, "--lora_save_path", start])      # B leaves zero after a step
+    one = _losses(_run([sys.executable, *common, *lora_flags, "--lora_load_path", start, "--lora_save_path", one_out]))
+    par = _losses(_run([_launcher(), f"--nproc_per_node={ranks}", f"--rdzv_endpoint=127.0.0.1:{29970 + ranks}", "--",
+                        sys.executable, *common, *lora_flags, *flags, "--lora_load_path", start, "--lora_save_path", par_out],
+                       timeout=900))
+    assert len(one) == 3 and max(abs(a - b) for a, b in zip(one, par)) <= 2e-6, list(zip(one, par))
+    a, b, c = _read_lora_file(one_out), _read_lora_file(par_out), _read_lora_file(start)
+    assert sorted(a) == sorted(b) and len(a) == 4 * 5 * 2
+    assert max(float((a[k] - b[k]).abs().max()) for k in a) < 1e-6
+    assert max(float((a[k] - c[k]).abs().max()) for k in a) > 1e-4        # and training moved them
