@@ -74,6 +74,9 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     a("--lora_target_modules", default="c_attn,c_proj")
     a("--lora_save_path", default="")
     a("--lora_load_path", default="")
+    a("--lora_merge_check", action="store_true",
+      help="after training, fold the adapters into the base weights, compare the loss of one batch before and "
+           "after, and unfold them again (not with pipeline parallelism)")
     a("--fused_nvlink", type=int, default=1)
     a("--profile", action="store_true")
     a("--seed", type=int, default=42)
@@ -339,6 +342,23 @@ def main(family: str, argv=None) -> int:
         if args.save and args.save_interval and (step + 1) % args.save_interval == 0:
             SaveCheckpoint(args.save, step + 1, model, optimizer, cfg, consumed, args.learning_rate,
                            args.save_optimizer_state, args.max_checkpoint_keep)
+    if args.lora_rank > 0 and args.lora_merge_check and pp == 1 and cached is not None:
+        # merged and unmerged adapters must give the same function (reference: tests/lora/test_lora.cc:108-147)
+        def _eval_loss():
+            with torch.no_grad(), AutocastGuard(dtype=dtype, enabled=to_torch_dtype(dtype) != torch.float32):
+                return float(loss_fn(model(cached[0].to(dev)), cached[1].to(dev)).float())
+
+        before = _eval_loss()
+        lora.MergeLoRAWeights(model)
+        merged = _eval_loss()
+        lora.UnmergeLoRAWeights(model)
+        after = _eval_loss()
+        ok = abs(before - merged) <= 1e-3 * max(1.0, abs(before)) and abs(before - after) <= 1e-3 * max(1.0, abs(before))
+        if rank == last_rank:
+            LOG("ERROR", f"lora merge check: loss {before:.6f} unmerged, {merged:.6f} merged, {after:.6f} unmerged again: "
+                         f"{'ok' if ok else 'MISMATCH'}")
+        if not ok:
+            return 3
     if args.lora_rank > 0 and args.lora_save_path:
         # one whole-model file gathered from every tensor- and pipeline-parallel rank (a collective)
         lora.SaveFullLoRAWeights(model, args.lora_save_path)

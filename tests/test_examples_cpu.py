@@ -234,9 +234,12 @@ def test_lora_in_any_layout_follows_the_one_rank_run_and_writes_the_same_adapter
     two_steps[two_steps.index("--num_iteration") + 1] = "2"
     _run([sys.executable, *two_steps, *lora_flags, "--lora_save_path", start])      # B leaves zero after a step
     one = _losses(_run([sys.executable, *common, *lora_flags, "--lora_load_path", start, "--lora_save_path", one_out]))
-    par = _losses(_run([_launcher(), f"--nproc_per_node={ranks}", f"--rdzv_endpoint=127.0.0.1:{29970 + ranks}", "--",
-                        sys.executable, *common, *lora_flags, *flags, "--lora_load_path", start, "--lora_save_path", par_out],
-                       timeout=900))
+    out = _run([_launcher(), f"--nproc_per_node={ranks}", f"--rdzv_endpoint=127.0.0.1:{29970 + ranks}", "--",
+                sys.executable, *common, *lora_flags, *flags, "--lora_load_path", start, "--lora_save_path", par_out,
+                "--lora_merge_check"], timeout=900)
+    par = _losses(out)
+    if "--pipeline_parallel" not in flags:           # merged == unmerged == unmerged again, on sharded factors too
+        assert re.search(r"lora merge check: .* ok", out) and "MISMATCH" not in out
     assert len(one) == 3 and max(abs(a - b) for a, b in zip(one, par)) <= 2e-6, list(zip(one, par))
     a, b, c = _read_lora_file(one_out), _read_lora_file(par_out), _read_lora_file(start)
     assert sorted(a) == sorted(b) and len(a) == 4 * 5 * 2
