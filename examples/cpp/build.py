@@ -3,6 +3,7 @@ against libtorch (the one inside the installed torch package).
 
     python examples/cpp/build.py            # CPU / libtorch-composite build
     python examples/cpp/build.py --cuda     # + the sm_100a kernels: -DITB_WITH_CUDA, links infinitrain_b200/_C.so
+    python examples/cpp/build.py --cuda --src examples/cpp/check_fused.cc --out infinitrain_b200/bin/itb_check_fused
 """
 from __future__ import annotations
 
@@ -15,13 +16,13 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parents[2]
 
 
-def build(cuda: bool = False, out: str | None = None) -> Path:
+def build(cuda: bool = False, out: str | None = None, src: str | None = None) -> Path:
     import torch
     from torch.utils import cpp_extension as ce
 
     dst = Path(out) if out else ROOT / "infinitrain_b200" / "bin" / ("itb_train_cuda" if cuda else "itb_train")
     dst.parent.mkdir(parents=True, exist_ok=True)
-    srcs = [ROOT / "examples" / "cpp" / "train.cc"]
+    srcs = [Path(src).resolve() if src else ROOT / "examples" / "cpp" / "train.cc"]
     hdrs = sorted((ROOT / "infinitrain_b200" / "csrc" / "frontend" / "itb").glob("*.h"))
     if dst.exists() and all(dst.stat().st_mtime > p.stat().st_mtime for p in srcs + hdrs):
         return dst
@@ -62,6 +63,7 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--cuda", action="store_true")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--src", default=None, help="another program on the frontend (default: examples/cpp/train.cc)")
     a = ap.parse_args()
-    print(build(a.cuda, a.out))
+    print(build(a.cuda, a.out, a.src))
     sys.exit(0)
