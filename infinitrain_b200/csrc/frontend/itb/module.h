@@ -118,6 +118,16 @@ class Module : public std::enable_shared_from_this<Module> {
     for (auto& [id, h] : pre_hooks_) h(this, inputs);
     TensorList outputs = Forward(inputs);
     for (auto& [id, h] : post_hooks_) h(this, inputs, outputs);
+    if (!backward_hooks_.empty()) {
+      // the gradient that reaches output i during backward is shown to the hooks registered now
+      for (size_t i = 0; i < outputs.size(); ++i) {
+        if (!outputs[i].defined() || !outputs[i].requires_grad()) continue;
+        auto hooks = backward_hooks_;
+        outputs[i].register_hook([this, hooks, i](const Tensor& grad) {
+          for (auto& [id, h] : hooks) h(this, i, grad);
+        });
+      }
+    }
     return outputs;
   }
   Tensor operator()(const Tensor& x) { return (*this)(TensorList{x})[0]; }
@@ -154,6 +164,15 @@ class Module : public std::enable_shared_from_this<Module> {
     int id = next_hook_++;
     post_hooks_[id] = std::move(hook);
     return std::make_shared<HookHandle>([this, id] { post_hooks_.erase(id); });
+  }
+
+  // hook(module, output index, gradient w.r.t. that output), called during backward (the reference's
+  // RegisterBackwardPostHook records the same tensors as "GradOutputs")
+  using BackwardHook = std::function<void(Module*, size_t, const Tensor&)>;
+  std::shared_ptr<HookHandle> RegisterBackwardPostHook(BackwardHook hook) {
+    int id = next_hook_++;
+    backward_hooks_[id] = std::move(hook);
+    return std::make_shared<HookHandle>([this, id] { backward_hooks_.erase(id); });
   }
 
   void set_requires_grad(bool on) {
@@ -205,6 +224,7 @@ class Module : public std::enable_shared_from_this<Module> {
   std::vector<std::string> param_order_, module_order_;   // registration order
   std::map<int, PreHook> pre_hooks_;
   std::map<int, PostHook> post_hooks_;
+  std::map<int, std::function<void(Module*, size_t, const Tensor&)>> backward_hooks_;
   int next_hook_ = 0;
 };
 

@@ -73,6 +73,14 @@ int main(int argc, char** argv) {
   h1->Remove();
   lin(torch::randn({3, 16}));
   EXPECT(pre == 1 && post == 2);
+  int bwd = 0;
+  auto h3 = lin.RegisterBackwardPostHook([&](Module*, size_t i, const Tensor& g) {
+    if (i == 0 && g.sizes() == torch::IntArrayRef({3, 8})) ++bwd;
+  });
+  lin(torch::randn({3, 16})).sum().backward();
+  h3->Remove();
+  lin(torch::randn({3, 16})).sum().backward();
+  EXPECT(bwd == 1);
 
   // strict loading; extra keys ignored; dtype conversion keeps tensor identity
   auto other = std::make_shared<nn::TransformerModel>(tiny_gpt());
