@@ -161,3 +161,22 @@ def test_per_module_dumps_line_up_with_the_reference(world):
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     assert mod.main([ref_dir, our_dir]) == 0
+
+
+def test_reference_regression_script_accepts_our_log(world, tmp_path):
+    """The reference's own scripts/compare_loss.py, given a log directory written by its trainer and
+    one written by ours (same file names, same step-line format), finds no loss mismatch."""
+    script = os.path.join(SRC, "scripts", "compare_loss.py")
+    if not os.path.exists(script):
+        pytest.skip("no reference checkout with scripts/compare_loss.py")
+    d, common = world
+    args = [*common, "--total_batch_size", "256", "--num_iteration", "6"]
+    for name, cmd in (("ref", [BIN, *args, "--overfit_single_batch=false"]), ("ours", [*OURS, *args, "--optimizer", "sgd"])):
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=d)
+        assert r.returncode == 0, r.stderr[-2000:]
+        (tmp_path / name).mkdir()
+        (tmp_path / name / "gpt2_1.log").write_text(r.stdout + r.stderr)
+    r = subprocess.run([sys.executable, script, str(tmp_path / "ref"), str(tmp_path / "ours")], capture_output=True,
+                       text=True, timeout=120, cwd=os.path.dirname(script))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "gpt2_1" in r.stdout or "1/1" in r.stdout or "passed" in r.stdout.lower(), r.stdout
