@@ -161,6 +161,12 @@ def test_per_module_dumps_line_up_with_the_reference(world):
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     assert mod.main([ref_dir, our_dir]) == 0
+    theirs = os.path.join(SRC, "scripts", "precision_check", "precision_compare.py")
+    if os.path.exists(theirs):          # and the reference's own comparison tool says the same
+        r = subprocess.run([sys.executable, theirs, "--dir1", ref_dir, "--dir2", our_dir], capture_output=True, text=True,
+                           timeout=300)
+        assert r.returncode == 0 and " 0 failed, 0 errors" in r.stdout, r.stdout[-1500:]
+        assert "Missing: 0 in dir1 only, 0 in dir2 only" in r.stdout
 
 
 def test_reference_regression_script_accepts_our_log(world, tmp_path):
