@@ -104,6 +104,12 @@ int main(int argc, char** argv) {
                (long long)cfg.n_layer, (long long)cfg.n_embd, (long long)cfg.n_head, (long long)cfg.n_kv_head,
                (long long)cfg.vocab_size, model->Parameters().size());
 
+  auto loss_module = std::make_shared<itb::nn::CrossEntropyLoss>();
+  if (!fl.get("precision_check", "").empty()) {   // "level=1,format=simple,path=DIR,save_tensors=true"
+    itb::utils::PrecisionChecker::Instance().Init(fl.get("precision_check", ""), env.rank);
+    itb::utils::PrecisionChecker::Instance().Attach(model);
+    itb::utils::PrecisionChecker::Instance().Attach(loss_module);
+  }
   const int64_t lora_rank = fl.geti("lora_rank", 0);
   if (lora_rank > 0) {
     namespace lora = itb::nn::lora;
@@ -148,6 +154,7 @@ int main(int argc, char** argv) {
 
   for (int64_t step = start_step; step < iters; ++step) {
     auto t0 = std::chrono::steady_clock::now();
+    itb::utils::PrecisionChecker::Instance().ResetCounters();
     optimizer->ZeroGrad();
     double lossf = 0.0;
     for (int64_t micro = 0; micro < grad_accum; ++micro) {
@@ -158,7 +165,8 @@ int main(int argc, char** argv) {
       itb::Tensor loss;
       {
         itb::AutocastGuard autocast(bf16 ? torch::kBFloat16 : torch::kFloat32);
-        loss = itb::ops::cross_entropy(model->forward(x), y) / static_cast<double>(grad_accum);
+        itb::Tensor logits = (*model)(itb::TensorList{x})[0];   // through the call operator: hooks see the model's output
+        loss = (*loss_module)(itb::TensorList{logits, y})[0] / static_cast<double>(grad_accum);
       }
       lossf += loss.item<float>();
       loss.backward();

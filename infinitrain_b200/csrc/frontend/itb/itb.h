@@ -15,5 +15,6 @@
 #include "module.h"
 #include "ops.h"
 #include "optim.h"
+#include "precision.h"
 #include "tokenizer.h"
 #include "transformer.h"

@@ -125,11 +125,15 @@ class NewGELU : public Module {
   NewGELU() : Module("NewGELU") {}
   TensorList Forward(const TensorList& in) override { return {ops::gelu(in[0])}; }
 };
-// in[0] * silu(in[1])
+// One input: x * sigmoid(x), the reference's module of this name (src/nn/modules/activations.cc:21-23);
+// two inputs: the gated product in[0] * silu(in[1]) in one fused op.
 class SwiGLU : public Module {
  public:
   SwiGLU() : Module("SwiGLU") {}
-  TensorList Forward(const TensorList& in) override { return {ops::swiglu(in[0], in[1])}; }
+  TensorList Forward(const TensorList& in) override {
+    if (in.size() == 1) return {in[0] * torch::sigmoid(in[0])};
+    return {ops::swiglu(in[0], in[1])};
+  }
 };
 class CrossEntropyLoss : public Module {
  public:

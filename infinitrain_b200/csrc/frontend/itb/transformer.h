@@ -5,6 +5,7 @@
 // so weight files, checkpoints and LoRA targets carry over.
 #pragma once
 #include "layers.h"
+#include "precision.h"
 
 namespace itb {
 namespace nn {
@@ -70,6 +71,12 @@ class CausalSelfAttention : public Module {
   std::shared_ptr<Linear> linear(const char* name) const { return std::static_pointer_cast<Linear>(mutable_module(name)); }
   // in: x, [freqs_cis]; residual is added in the projection's epilogue
   Tensor forward(const Tensor& x, const c10::optional<Tensor>& freqs, const c10::optional<Tensor>& residual) {
+    if (utils::aligned_mode()) {   // through the children's call operators, so that their hooks see the tensors
+      Tensor qkv = (*mutable_module("c_attn"))(x);
+      auto rope = config.attention_type == AttentionType::kRoPE ? freqs : c10::nullopt;
+      Tensor y = (*mutable_module("c_proj"))(ops::attention_packed(qkv, config.n_head, config.n_kv_head, config.head_dim(), rope, 0, true));
+      return residual.has_value() ? y + *residual : y;
+    }
     Tensor qkv = linear("c_attn")->forward(x);
     auto rope = config.attention_type == AttentionType::kRoPE ? freqs : c10::nullopt;
     Tensor y = ops::attention_packed(qkv, config.n_head, config.n_kv_head, config.head_dim(), rope, 0, true);
@@ -89,9 +96,21 @@ class MLP : public Module {
     if (c.activation_type == MLPType::kSwiGLU)
       register_module("c_fc2", std::make_shared<Linear>(c.n_embd, hidden, c.add_bias_linear));
     register_module("c_proj", std::make_shared<Linear>(hidden, c.n_embd, c.add_bias_linear));
+    // activation modules under the reference's names; the fused path does not go through them
+    if (c.activation_type == MLPType::kSwiGLU) register_module("silu", std::make_shared<SwiGLU>());
+    else register_module("gelu", std::make_shared<NewGELU>());
   }
   std::shared_ptr<Linear> linear(const char* name) const { return std::static_pointer_cast<Linear>(mutable_module(name)); }
   Tensor forward(const Tensor& x, const c10::optional<Tensor>& residual) {
+    if (utils::aligned_mode()) {
+      Tensor h;
+      if (config.activation_type == MLPType::kSwiGLU)
+        h = (*mutable_module("c_fc"))(x) * (*mutable_module("silu"))((*mutable_module("c_fc2"))(x));
+      else
+        h = (*mutable_module("gelu"))((*mutable_module("c_fc"))(x));
+      Tensor y = (*mutable_module("c_proj"))(h);
+      return residual.has_value() ? y + *residual : y;
+    }
     if (config.activation_type == MLPType::kSwiGLU)
       return linear("c_proj")->forward(ops::swiglu(linear("c_fc")->forward(x), linear("c_fc2")->forward(x)), residual);
     return linear("c_proj")->forward(linear("c_fc")->forward(x, c10::nullopt, /*gelu=*/true), residual);
@@ -103,13 +122,19 @@ class MLP : public Module {
 // Pre-norm residual block: x + attn(ln_1(x)), then x + mlp(ln_2(x)).
 class TransformerLayer : public Module {
  public:
-  explicit TransformerLayer(const TransformerConfig& c) : Module("TransformerLayer") {
+  explicit TransformerLayer(const TransformerConfig& c) : Module("Layer") {   // the reference's type name
     ln_1 = register_module("ln_1", MakeNorm(c));
     attn = register_module("attn", std::make_shared<CausalSelfAttention>(c));
     ln_2 = register_module("ln_2", MakeNorm(c));
     mlp = register_module("mlp", std::make_shared<MLP>(c));
   }
   Tensor forward(const Tensor& x, const c10::optional<Tensor>& freqs) {
+    if (utils::aligned_mode()) {
+      TensorList a_in = {(*ln_1)(x)};
+      if (freqs.has_value()) a_in.push_back(*freqs);
+      Tensor h = x + (*attn)(a_in)[0];
+      return h + (*mlp)(TensorList{(*ln_2)(h)})[0];
+    }
     Tensor h = attn->forward((*ln_1)(x), freqs, x);
     return mlp->forward((*ln_2)(h), h);
   }
@@ -123,7 +148,7 @@ class TransformerLayer : public Module {
 
 class TransformerModel : public Module {
  public:
-  explicit TransformerModel(const TransformerConfig& c) : Module("TransformerModel"), config(c) {
+  explicit TransformerModel(const TransformerConfig& c) : Module("Transformer"), config(c) {   // the reference's type name
     auto body = std::make_shared<ModuleDict>();
     wte = std::make_shared<Embedding>(c.vocab_size, c.n_embd);
     body->insert("wte", wte);
@@ -144,12 +169,27 @@ class TransformerModel : public Module {
   Tensor forward(const Tensor& idx) {
     int64_t T = idx.size(1);
     TORCH_CHECK(T <= config.block_size, "sequence longer than block_size");
-    Tensor x = ops::embedding(idx, wte->weight, wpe ? c10::optional<Tensor>(wpe->weight) : c10::nullopt, 0);
+    const bool aligned = utils::aligned_mode();
+    Tensor x;
+    if (aligned) {
+      x = (*wte)(idx);
+      if (wpe) x = x + (*wpe)(torch::arange(T, torch::TensorOptions().dtype(torch::kInt64).device(idx.device())));
+    } else {
+      x = ops::embedding(idx, wte->weight, wpe ? c10::optional<Tensor>(wpe->weight) : c10::nullopt, 0);
+    }
     c10::optional<Tensor> freqs;
     if (config.attention_type == AttentionType::kRoPE) {
       if (!freqs_cis_.defined() || freqs_cis_.device() != x.device())
         freqs_cis_ = ops::precompute_freqs_cis(config.head_dim(), 2 * config.block_size, config.rope_theta, x.device());
       freqs = freqs_cis_.slice(0, 0, T);
+    }
+    if (aligned) {
+      for (auto& layer : *h) {
+        TensorList in = {x};
+        if (freqs.has_value()) in.push_back(*freqs);
+        x = (*layer)(in)[0];
+      }
+      return (*mutable_module("lm_head"))((*ln_f)(x));
     }
     for (auto& layer : *h) x = std::static_pointer_cast<TransformerLayer>(layer)->forward(x, freqs);
     return lm_head()->forward((*ln_f)(x));

@@ -17,6 +17,14 @@ def _losses(text):
     return [float(m.group(1)) for m in re.finditer(r"step\s+\d+/\d+\s+\|\s+train loss\s+([\d.]+)", text)]
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
 def _run(cmd, cwd):
     r = subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=900, cwd=cwd, env=ENV)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
@@ -25,9 +33,11 @@ def _run(cmd, cwd):
 
 @pytest.fixture(scope="module")
 def trainer():
-    sys.path.insert(0, os.path.join(ROOT, "examples", "cpp"))
-    import build as cpp_build
+    import importlib.util
 
+    spec = importlib.util.spec_from_file_location("itb_cpp_build", os.path.join(ROOT, "examples", "cpp", "build.py"))
+    cpp_build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cpp_build)
     return str(cpp_build.build(cuda=False))
 
 
@@ -186,9 +196,41 @@ def test_two_rank_data_parallel_matches_python_ddp(trainer, files):
     common = ["--device", "cpu", "--llmc_filepath", "gpt2.bin", "--input_bin", "tokens16.bin", "--batch_size", "2",
               "--sequence_length", "64", "--total_batch_size", "512", "--num_iteration", "5", "--dtype", "float32",
               "--learning_rate", "0.05", "--optimizer", "sgd"]
-    cpp = _run([launcher, "--nproc_per_node=2", "--rdzv_endpoint=127.0.0.1:29741", "--", trainer, "--family", "gpt2", *common],
+    cpp = _run([launcher, "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", trainer, "--family", "gpt2", *common],
                files)
-    py = _run([launcher, "--nproc_per_node=2", "--rdzv_endpoint=127.0.0.1:29742", "--", sys.executable,
+    py = _run([launcher, "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", sys.executable,
                os.path.join(ROOT, "examples", "gpt2", "main.py"), *common], files)
     assert len(cpp) == 5 and len(py) == 5, (cpp, py)
     assert max(abs(a - b) for a, b in zip(cpp, py)) <= 1e-5, list(zip(cpp, py))
+
+
+def test_per_module_records_line_up_with_the_reference(trainer, files):
+    """With --precision_check the C++ trainer writes the reference's record lines and dump files for
+    every module it has (the reference adds its three pipeline-stage wrappers); all tensors both sides
+    dump agree within allclose(atol 1e-5, rtol 1e-3)."""
+    import glob
+
+    import numpy as np
+
+    if not os.path.exists(REF):
+        pytest.skip("the reference's CPU build is not there")
+    common = ["--device", "cpu", "--llmc_filepath", "gpt2.bin", "--input_bin", "tokens16.bin", "--batch_size", "4",
+              "--sequence_length", "64", "--total_batch_size", "512", "--num_iteration", "2", "--dtype", "float32",
+              "--learning_rate", "0.05"]
+    _run([REF, *common, "--overfit_single_batch=false", "--precision_check", "level=1,format=simple,path=pc_ref,save_tensors=true"],
+         files)
+    _run([trainer, "--family", "gpt2", *common, "--optimizer", "sgd", "--precision_check",
+          "level=1,format=simple,path=pc_cpp,save_tensors=true"], files)
+    (ref_dir,), (cpp_dir,) = glob.glob(str(files / "pc_ref" / "*")), glob.glob(str(files / "pc_cpp" / "*"))
+    ref_files = set(os.listdir(os.path.join(ref_dir, "rank_0")))
+    cpp_files = set(os.listdir(os.path.join(cpp_dir, "rank_0")))
+    assert cpp_files <= ref_files and len(cpp_files) >= 100
+    assert all(f.startswith(("TransformerFirstStage", "TransformerChunk", "TransformerLastStage")) for f in ref_files - cpp_files)
+    for f in sorted(cpp_files):
+        a, b = np.load(os.path.join(ref_dir, "rank_0", f)), np.load(os.path.join(cpp_dir, "rank_0", f))
+        assert a.shape == b.shape and np.allclose(a, b, atol=1e-5, rtol=1e-3), f
+    ref_names = {ln.split()[2] for ln in open(os.path.join(ref_dir, "precision_check_rank_0.log"))}
+    cpp_lines = open(os.path.join(cpp_dir, "precision_check_rank_0.log")).read().splitlines()
+    assert {ln.split()[2] for ln in cpp_lines} <= ref_names
+    assert re.match(r"\[GAS-0\] \[L-0\] transformer\.wte_forward tensor\[0\]: dtype=float32 shape=\(4,64,96\) min=\S+ max=\S+ "
+                    r"mean=\S+ \[.*, \.\.\.\] \[NaN:0 Inf:0\]$", cpp_lines[0])
