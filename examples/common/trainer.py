@@ -154,6 +154,8 @@ def main(family: str, argv=None) -> int:
     if args.total_batch_size % tokens_per_fwdbwd:
         raise SystemExit(f"total_batch_size must be a multiple of batch*seq*dp = {tokens_per_fwdbwd}")
     grad_accum = args.total_batch_size // tokens_per_fwdbwd
+    if args.sequence_parallel and tp > 1 and T % tp:
+        raise SystemExit(f"sequence_length ({T}) must be divisible by the tensor-parallel size ({tp}) under sequence parallelism")
     dtype = parse_dtype(args.dtype)
     torch.manual_seed(args.seed)
 

@@ -252,6 +252,9 @@ class TransformerModel(Module):
         self.config = config
         pp = genv.GetPipelineParallelSize()
         pp_rank = genv.GetPipelineParallelRank() if pp_rank is None else pp_rank
+        vpp = genv.GetVirtualPipelineParallelSize()
+        if config.n_layer < pp * vpp:
+            raise ValueError(f"the model has {config.n_layer} layers: too few for {pp} pipeline stages x {vpp} chunks each")
         self.stage_info: StageInfo = GetStageInfo(config.n_layer, pp, pp_rank, genv.GetVirtualPipelineParallelSize())
         tp = genv.GetTensorParallelSize()
         if config.vocab_size % tp:
