@@ -184,7 +184,14 @@ def ResumeFromCheckpoint(resume_root: str, model, optimizer, model_config, load_
         return res
     if genv.GetWorldSize() > 1 and os.path.isdir(rd):
         d = rd
-    st = Checkpoint.Load(d, model, optimizer, load_optimizer_state)
+    # model shape and topology are checked BEFORE any tensor is loaded (reference: checkpoint_manager.cc:45-63);
+    # a checkpoint of several ranks keeps its files in rank directories
+    state_file = os.path.join(d, "trainer_state.json")
+    if not os.path.exists(state_file) and old_ranks:
+        state_file = os.path.join(resume_root, old_ranks[0], "trainer_state.json")
+    if not os.path.exists(state_file):
+        raise FileNotFoundError(f"no trainer_state.json under {resume_root}")
+    st = Checkpoint.LoadTrainerState(state_file)
     for k in ("n_layer", "n_head", "n_kv_head", "n_embd", "vocab_size"):
         if getattr(st, k) != getattr(model_config, k):
             raise ValueError(f"{k} mismatch: ckpt={getattr(st, k)}, config={getattr(model_config, k)}")
@@ -193,5 +200,6 @@ def ResumeFromCheckpoint(resume_root: str, model, optimizer, model_config, load_
     for k, cur in topo.items():
         if getattr(st, k) != cur and not (k == "ddp_size" and allow_dp_resize and not load_optimizer_state):
             raise ValueError(f"{k.upper()} mismatch: checkpoint has {getattr(st, k)}, but current run has {cur}")
+    st = Checkpoint.Load(d, model, optimizer, load_optimizer_state)
     res.global_step, res.consumed_batches, res.last_lr = st.global_step, max(st.consumed_batches, 0), st.last_lr
     return res

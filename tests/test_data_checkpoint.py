@@ -194,3 +194,22 @@ def test_optimizer_state_by_parameter_name():
     again = Adam(m.Parameters(), 1e-2)
     again.LoadStateDict(opt.StateDict())                      # positional form
     assert torch.equal(again.v[3], opt.v[3])
+
+
+def test_resume_reports_a_topology_mismatch_before_loading(tmp_path):
+    """A checkpoint of a 2-way tensor-parallel run, resumed in a run without tensor parallelism, is
+    refused by its recorded topology, not by a shape error half way through the weights."""
+    from infinitrain_b200.checkpoint.checkpoint import Checkpoint, ResumeFromCheckpoint, TrainerState
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+    from infinitrain_b200.parallel import global_env as genv
+
+    genv.InitAllEnv(world_size=1, rank=0)
+    cfg = TransformerConfig.GPT2(n_layer=1, n_embd=32, n_head=4, n_kv_head=4, vocab_size=64, original_vocab_size=64, block_size=16)
+    m = TransformerModel(cfg)
+    for r in (0, 1):
+        d = tmp_path / "ck" / f"rank_{r:06d}"
+        d.mkdir(parents=True)
+        Checkpoint.SaveTrainerState(str(d / "trainer_state.json"),
+                                    TrainerState(2, 2, 1e-4, 1, 4, 4, 32, 64, ddp_size=1, tp_size=2, sp_size=1, pp_size=1))
+    with pytest.raises(ValueError, match="TP_SIZE mismatch: checkpoint has 2, but current run has 1"):
+        ResumeFromCheckpoint(str(tmp_path / "ck"), m, None, cfg)
