@@ -104,3 +104,83 @@ def SwiGLU(a, b):
 
 def CrossEntropy(logits, target):
     return ops.cross_entropy(logits, target)
+
+
+# --------------------------------------------------------------------------- the rest of the reference's op catalogue
+# (infini_train/include/autograd/{elementwise,transform,gather,scatter,outer,matmul}.h): thin names over
+# PyTorch ops with the reference's conventions.
+def Neg(x):
+    return torch.neg(x)
+
+
+def Exp(x):
+    return torch.exp(x)
+
+
+def Log(x):
+    return torch.log(x)
+
+
+def Matmul(a, b):
+    return torch.matmul(a, b)
+
+
+def Outer(a, b):
+    return torch.outer(a, b)
+
+
+def Transpose(x, dim0: int, dim1: int):
+    return x.transpose(dim0, dim1).contiguous()          # the reference materialises the copy
+
+
+def _as_input_dtype(mask, x):
+    return mask.to(x.dtype)
+
+
+def Equals(a, b):
+    """Comparisons give 0 / 1 in the INPUT dtype, not bool (reference: src/kernels/cpu/elementwise.cc)."""
+    return _as_input_dtype(a == b, a)
+
+
+def Lt(a, b):
+    return _as_input_dtype(a < b, a)
+
+
+def Le(a, b):
+    return _as_input_dtype(a <= b, a)
+
+
+def Gt(a, b):
+    return _as_input_dtype(a > b, a)
+
+
+def Ge(a, b):
+    return _as_input_dtype(a >= b, a)
+
+
+def And(a, b):
+    return _as_input_dtype((a != 0) & (b != 0), a)
+
+
+def Or(a, b):
+    return _as_input_dtype((a != 0) | (b != 0), a)
+
+
+def Mask(x, mask, value: float):
+    """masked_fill with a mask that may cover only the trailing (or leading) dimensions of ``x``."""
+    m = mask.to(torch.bool)
+    if m.dim() < x.dim() and tuple(x.shape[:m.dim()]) == tuple(m.shape) and tuple(x.shape[-m.dim():]) != tuple(m.shape):
+        m = m.reshape(*m.shape, *([1] * (x.dim() - m.dim())))          # lead-aligned
+    return x.masked_fill(m, value)
+
+
+def Gather(x, dim: int, index):
+    return torch.gather(x, dim, index)
+
+
+def Scatter(values, indices, out_dims: Sequence[int]):
+    """Top-k scatter (reference: src/kernels/cpu/scatter.cc:13-47): ``values`` and ``indices`` are
+    ``[..., k]``; row r of the zero-filled output ``[..., n]`` gets ``values[r, j]`` at column
+    ``indices[r, j]``.  The gradient gathers the same positions back."""
+    out = torch.zeros(tuple(out_dims), dtype=values.dtype, device=values.device)
+    return out.scatter(-1, indices, values)

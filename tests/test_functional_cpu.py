@@ -157,3 +157,28 @@ def test_autograd_engine_contracts():
     assert torch.equal(b.grad, a)
     with torch.no_grad():
         assert not (b * 2).requires_grad
+
+
+def test_remaining_catalogue_ops():
+    a, b = torch.tensor([1.0, 2.0, 0.0]), torch.tensor([1.0, 3.0, 5.0])
+    for f, want in ((fn.Equals, [1, 0, 0]), (fn.Lt, [0, 1, 1]), (fn.Le, [1, 1, 1]), (fn.Gt, [0, 0, 0]), (fn.Ge, [1, 0, 0]),
+                    (fn.And, [1, 1, 0]), (fn.Or, [1, 1, 1])):
+        out = f(a, b)
+        assert out.dtype == torch.float32 and out.tolist() == [float(v) for v in want]        # 0 / 1 in the input dtype
+    assert fn.Equals(a.bfloat16(), 1.0).dtype == torch.bfloat16
+    x = torch.randn(2, 3, 4)
+    assert torch.equal(fn.Neg(x), -x) and torch.allclose(fn.Log(fn.Exp(x)), x, atol=1e-6)
+    assert fn.Transpose(x, 0, 2).shape == (4, 3, 2) and fn.Transpose(x, 0, 2).is_contiguous()
+    assert fn.Matmul(x, x.transpose(1, 2)).shape == (2, 3, 3) and fn.Outer(a, b).shape == (3, 3)
+    tail = torch.tensor([[False, True, False, False]] * 3)
+    assert fn.Mask(x, tail, -1.0)[1, 2, 1] == -1.0 and fn.Mask(x, tail, -1.0)[1, 2, 0] == x[1, 2, 0]
+    lead = torch.tensor([[True, False, False], [False, False, True]])
+    assert bool((fn.Mask(x, lead, 9.0)[0, 0] == 9.0).all()) and fn.Mask(x, lead, 9.0)[0, 1, 0] == x[0, 1, 0]
+    assert torch.equal(fn.Gather(x, 2, torch.zeros(2, 3, 1, dtype=torch.long)), x[..., :1])
+    vals = torch.tensor([[0.7, 0.3], [0.6, 0.4]], requires_grad=True)
+    idx = torch.tensor([[2, 0], [1, 3]])
+    out = fn.Scatter(vals, idx, (2, 4))
+    assert out.tolist() == [[0.3, 0.0, 0.7, 0.0], [0.0, 0.6, 0.0, 0.4]] or torch.allclose(
+        out, torch.tensor([[0.3, 0.0, 0.7, 0.0], [0.0, 0.6, 0.0, 0.4]]))
+    (out * torch.arange(8.0).view(2, 4)).sum().backward()
+    assert torch.allclose(vals.grad, torch.tensor([[2.0, 0.0], [5.0, 7.0]]))                  # gathered back
