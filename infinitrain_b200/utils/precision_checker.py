@@ -130,7 +130,10 @@ class PrecisionCheckEnv:
 def ComputeMD5(t: torch.Tensor, tolerance: float = 0.0) -> str:
     a = t.detach().float().cpu().contiguous().numpy()
     if tolerance > 0:
-        a = (np.round(a / tolerance) * tolerance).astype(np.float32)
+        # the reference's quantisation, bit for bit (src/utils/precision_checker.cc:249-260): double
+        # arithmetic, round half away from zero, back to fp32
+        x = a.astype(np.float64) * (1.0 / tolerance)
+        a = (np.sign(x) * np.floor(np.abs(x) + 0.5) * tolerance).astype(np.float32)
     return hashlib.md5(a.tobytes()).hexdigest()
 
 

@@ -64,6 +64,8 @@ def test_precision_checker_simple_md5_npy(tmp_path):
         env.Shutdown()
     a = torch.tensor([1.0, 2.0])
     assert ComputeMD5(a, 1e-2) == ComputeMD5(a + 1e-4, 1e-2) and ComputeMD5(a) != ComputeMD5(a + 1e-4)
+    # the reference quantises with std::round (half away from zero), in double
+    assert ComputeMD5(torch.tensor([0.5, -0.5, 2.5]), 1.0) == ComputeMD5(torch.tensor([1.0, -1.0, 3.0]), 1.0)
 
 
 def test_profiler_report_and_trace(tmp_path):
