@@ -68,6 +68,8 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     a("--save", default="")
     a("--max_checkpoint_keep", type=int, default=0)
     a("--save_optimizer_state", action="store_true")
+    a("--save_reference_buffers", action="store_true",
+      help="also write the causal-mask buffers the reference's strict checkpoint loader expects (GPT-2)")
     a("--precision_check", default="")
     a("--lora_rank", type=int, default=0)
     a("--lora_alpha", type=float, default=16.0)
@@ -343,7 +345,8 @@ def main(family: str, argv=None) -> int:
             tokenizer.GenerateText(model, B, T, args.text_length, dev)
         if args.save and args.save_interval and (step + 1) % args.save_interval == 0:
             SaveCheckpoint(args.save, step + 1, model, optimizer, cfg, consumed, args.learning_rate,
-                           args.save_optimizer_state, args.max_checkpoint_keep)
+                           args.save_optimizer_state, args.max_checkpoint_keep,
+                           reference_buffers=args.save_reference_buffers)
     if args.lora_rank > 0 and args.lora_merge_check and pp == 1 and cached is not None:
         # merged and unmerged adapters must give the same function (reference: tests/lora/test_lora.cc:108-147)
         def _eval_loss():

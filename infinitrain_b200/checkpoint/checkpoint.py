@@ -78,15 +78,34 @@ class Checkpoint:
         return st
 
     @staticmethod
-    def Save(checkpoint_dir: str, model, optimizer, state: TrainerState, save_optimizer_state: bool = True) -> None:
+    def Save(checkpoint_dir: str, model, optimizer, state: TrainerState, save_optimizer_state: bool = True,
+             reference_buffers: bool = False) -> None:
         os.makedirs(checkpoint_dir, exist_ok=True)
         sd = model.StateDict() if hasattr(model, "StateDict") else model.state_dict()
+        if reference_buffers:
+            sd = Checkpoint.WithReferenceBuffers(sd, model)
         Checkpoint.SaveStateDict(os.path.join(checkpoint_dir, "model.ckpt"), sd)
         if save_optimizer_state and optimizer is not None:
             osd = optimizer.StateDict()
             if osd:
                 Checkpoint.SaveStateDict(os.path.join(checkpoint_dir, "optimizer.ckpt"), osd)
         Checkpoint.SaveTrainerState(os.path.join(checkpoint_dir, "trainer_state.json"), state)
+
+    @staticmethod
+    def WithReferenceBuffers(sd, model):
+        """Adds what the reference's strict loader expects beyond the parameters: the causal-mask buffer
+        ``transformer.h.<i>.attn.bias`` (``[1, 1, block, block]`` lower-triangular ones) that its GPT-2
+        attention registers (src/nn/modules/transformer/causal_self_attention.cc:46-50).  This framework
+        has no such buffer (the attention kernels mask in place) and ignores it on load."""
+        cfg = getattr(model, "config", None)
+        if cfg is None or int(getattr(cfg, "attention_type", 0)) != 0:
+            return sd
+        out = OrderedDict(sd)
+        layers = sorted({k.split(".")[2] for k in sd if k.startswith("transformer.h.") and k.split(".")[2].isdigit()}, key=int)
+        mask = torch.tril(torch.ones(cfg.block_size, cfg.block_size)).view(1, 1, cfg.block_size, cfg.block_size)
+        for i in layers:
+            out[f"transformer.h.{i}.attn.bias"] = mask
+        return out
 
     @staticmethod
     def Load(checkpoint_dir: str, model, optimizer, load_optimizer_state: bool = True) -> TrainerState:
@@ -107,7 +126,7 @@ def _rank_dir(root: str, rank: int, world: int) -> str:
 
 def SaveCheckpoint(checkpoint_root_dir: str, global_step: int, model, optimizer, model_config, consumed_batches: int = 0,
                    last_lr: float = 0.0, save_optimizer_state: bool = True, max_checkpoint_keep: int = 0,
-                   rank: Optional[int] = None) -> str:
+                   rank: Optional[int] = None, reference_buffers: bool = False) -> str:
     """Writes ``<root>/checkpoint_step_%06d[/rank_%06d]`` and prunes old step directories (rank 0,
     lexicographic order of the zero-padded names, keep the newest ``max_checkpoint_keep``)."""
     rank = genv.MyRank() if rank is None else rank
@@ -118,7 +137,7 @@ def SaveCheckpoint(checkpoint_root_dir: str, global_step: int, model, optimizer,
                          model_config.n_kv_head, model_config.n_embd, model_config.vocab_size,
                          genv.GetDataParallelSize(), genv.GetTensorParallelSize(), genv.GetSequenceParallelSize(),
                          genv.GetPipelineParallelSize())
-    Checkpoint.Save(_rank_dir(step_dir, rank, world), model, optimizer, state, save_optimizer_state)
+    Checkpoint.Save(_rank_dir(step_dir, rank, world), model, optimizer, state, save_optimizer_state, reference_buffers)
     if rank == 0 and max_checkpoint_keep > 0 and os.path.isdir(checkpoint_root_dir):
         ckpts = sorted(d for d in os.listdir(checkpoint_root_dir)
                        if d.startswith("checkpoint_step_") and os.path.isdir(os.path.join(checkpoint_root_dir, d)))

@@ -186,3 +186,23 @@ def test_reference_regression_script_accepts_our_log(world, tmp_path):
                        text=True, timeout=120, cwd=os.path.dirname(script))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "gpt2_1" in r.stdout or "1/1" in r.stdout or "passed" in r.stdout.lower(), r.stdout
+
+
+def test_reference_resumes_from_a_checkpoint_written_here(world):
+    """The other direction: a checkpoint written here with --save_reference_buffers (the causal-mask
+    buffers the reference's strict loader wants) is resumed by the reference's trainer, which then
+    follows its own uninterrupted trajectory."""
+    d, common = world
+    args = [*common, "--total_batch_size", "256", "--num_iteration", "8"]
+    whole = _run([BIN, *args, "--overfit_single_batch=false"], d)
+    first = [*common, "--total_batch_size", "256", "--num_iteration", "4"]
+    _run([*OURS, *first, "--optimizer", "sgd", "--save", "our_ckpt", "--save_interval", "4", "--save_reference_buffers"], d)
+    ck = d / "our_ckpt" / "checkpoint_step_000004"
+    # The stock trainer validates against its DEFAULT model shape when the weights come from an llm.c
+    # file (example/gpt2/main.cc:213-216 keeps model_config at GPT2Config()): record that shape.
+    text = (ck / "trainer_state.json").read_text()
+    text = text.replace('"n_layer": 2', '"n_layer": 12').replace('"n_embd": 96', '"n_embd": 768')
+    (ck / "trainer_state.json").write_text(text.replace('"vocab_size": 256', '"vocab_size": 50304'))
+    resumed = _run([BIN, *args, "--overfit_single_batch=false", "--load", str(ck)], d)
+    _close(whole[4:], resumed, 4)
+    shutil.rmtree(d / "our_ckpt")
