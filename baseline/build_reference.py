@@ -35,7 +35,10 @@ def run(cmd):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default=os.environ.get("ITB_REFERENCE_SRC", os.path.join(os.sep, "root", "reference")))
+    ap.add_argument("--src", default=os.environ.get("ITB_REFERENCE_SRC")
+                    or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"),
+                    help="the reference checkout (default: ITB_REFERENCE_SRC, else a directory named 'reference' "
+                         "beside this repository)")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)
     ap.add_argument("--arch", default="100")
     ap.add_argument("--cpu-only", action="store_true")

@@ -81,6 +81,11 @@ def build_parser(family: str) -> argparse.ArgumentParser:
            "after, and unfold them again (not with pipeline parallelism)")
     a("--fused_nvlink", type=int, default=1)
     a("--profile", action="store_true")
+    a("--untie_weights", action="store_true",
+      help="GPT-2: keep wte and lm_head as two parameters (both start from the file's wte).  The reference's CUDA "
+           "build trains them untied -- its Module::To re-creates the parameters -- so GPU parity runs need this")
+    a("--residual_dtype", default="bfloat16", choices=["bfloat16", "float32"],
+      help="dtype of the residual stream under bf16 autocast (float32 = the reference's arithmetic)")
     a("--seed", type=int, default=42)
     a("--n_layer", type=int, default=0, help="override the layer count (smoke tests)")
     a("--n_embd", type=int, default=0, help="override the hidden size (smoke tests)")
@@ -101,7 +106,7 @@ def main(family: str, argv=None) -> int:
     args = build_parser(family).parse_args(argv)
     from infinitrain_b200.autocast import AutocastGuard
     from infinitrain_b200.checkpoint import ResumeFromCheckpoint, SaveCheckpoint
-    from infinitrain_b200.data import DistributedDataLoader, TinyShakespeareDataset, Tokenizer, write_token_file
+    from infinitrain_b200.data import DeviceFeeder, DistributedDataLoader, TinyShakespeareDataset, Tokenizer, write_token_file
     from infinitrain_b200.datatype import DataType, parse_dtype, to_torch_dtype
     from infinitrain_b200.device import Device, DeviceGuardImpl
     from infinitrain_b200.models import gpt2_config, llama3_config, llmc
@@ -162,10 +167,14 @@ def main(family: str, argv=None) -> int:
     torch.manual_seed(args.seed)
 
     # ---- model
+    over_common = {"residual_dtype": torch.float32 if args.residual_dtype == "float32" else torch.bfloat16}
+    if args.untie_weights:
+        over_common["tie_weights"] = False
     if args.llmc_filepath:
-        model = (llmc.GPT2FromLLMC if family == "gpt2" else llmc.LLaMA3FromLLMC)(args.llmc_filepath)
+        model = (llmc.GPT2FromLLMC if family == "gpt2" else llmc.LLaMA3FromLLMC)(args.llmc_filepath, **over_common)
     else:
         over = {k: getattr(args, k) for k in ("n_layer", "n_embd", "n_head", "n_kv_head") if getattr(args, k)}
+        over.update(over_common)
         if args.vocab_size:
             over.update(vocab_size=args.vocab_size, original_vocab_size=args.vocab_size)
         cfg = gpt2_config(args.model, **over) if family == "gpt2" else llama3_config(args.model, **over)
@@ -229,13 +238,14 @@ def main(family: str, argv=None) -> int:
 
     # ---- resume
     start_step = 0
-    it = epochs(loader)
+    # batches reach the device through the feeder: asynchronous copies out of the loader's pinned ring,
+    # ordered against the ring's slot reuse (several micro-batches may be in flight before a host sync)
+    it = DeviceFeeder(epochs(loader), dev)
     if args.load:
         res = ResumeFromCheckpoint(args.load, model, optimizer, cfg, load_optimizer_state=args.save_optimizer_state,
                                    allow_dp_resize=args.elastic_resume)
         start_step = res.global_step
-        for _ in range(res.consumed_batches):
-            next(it)
+        it.skip(res.consumed_batches)
     consumed = start_step * (1 if pp > 1 else grad_accum)
     profiler = Profiler.Instance()
     if args.profile:
@@ -274,8 +284,7 @@ def main(family: str, argv=None) -> int:
                 cached = (x, y)
                 consumed += 1
             x, y = cached
-            lossf = pipeline.TrainStep([x.to(dev, non_blocking=True)], [y.to(dev, non_blocking=True)], optimizer,
-                                       loss_fn, dtype)
+            lossf = pipeline.TrainStep([x], [y], optimizer, loss_fn, dtype)
         else:
             optimizer.ZeroGrad()
             loss_acc = torch.zeros((), device=dev)
@@ -285,7 +294,6 @@ def main(family: str, argv=None) -> int:
                     cached = (x, y)
                     consumed += 1
                 x, y = cached
-                x, y = x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)
                 last = micro == grad_accum - 1
                 ctxs = [c.no_sync() for c in ddp_chunks] if (not last and ddp_chunks) else []
                 for c in ctxs:
@@ -308,6 +316,20 @@ def main(family: str, argv=None) -> int:
         if use_cuda:
             ev1.record()
             torch.cuda.synchronize()
+            # the step's one sync point: a bounded device-side wait that gave up (a fused NVLink
+            # collective that lost a peer) has skipped its reduction -- stop like the heartbeat path does
+            from infinitrain_b200.utils.fault_tolerance import KernelTimeout, check_device_status
+
+            try:
+                check_device_status(sync=True)
+            except KernelTimeout as e:
+                LOG("ERROR", f"step {step + 1}: {e}; stopping (resume from the last checkpoint)")
+                if heartbeat is not None:
+                    heartbeat.request_abort(str(e))
+                    heartbeat.stop()
+                sys.stdout.flush()
+                sys.stderr.flush()
+                os._exit(75)
         dur_ms = (time.perf_counter() - t0) * 1e3
         tps = args.total_batch_size / (dur_ms / 1e3)
         if rank == last_rank:
@@ -351,7 +373,7 @@ def main(family: str, argv=None) -> int:
         # merged and unmerged adapters must give the same function (reference: tests/lora/test_lora.cc:108-147)
         def _eval_loss():
             with torch.no_grad(), AutocastGuard(dtype=dtype, enabled=to_torch_dtype(dtype) != torch.float32):
-                return float(loss_fn(model(cached[0].to(dev)), cached[1].to(dev)).float())
+                return float(loss_fn(model(cached[0]), cached[1]).float())
 
         before = _eval_loss()
         lora.MergeLoRAWeights(model)

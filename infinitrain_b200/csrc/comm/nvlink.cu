@@ -118,6 +118,8 @@ __global__ void __launch_bounds__(kCommThreads)
 allreduce_scale_kernel(ItbPeerPtrs bufs, float* mc, ItbPeerPtrs flags, long long off, long long n,
                        int rank, int world, int ch0, int epoch, float scale, int* err,
                        int* __restrict__ epoch_ctr) {
+  // an earlier launch gave up on a peer: the flags are no longer in step, do not wait again
+  if (*static_cast<volatile int*>(err) != 0) return;
   const int ch = ch0 + blockIdx.x;
   // Device-side epoch (one counter per channel, private to this GPU): lets a captured CUDA graph
   // replay the launch; every rank's counter advances in lockstep because every rank replays the
@@ -150,6 +152,7 @@ rs_adamw_bcast_kernel(ItbPeerPtrs grads, const float* mc_grads, ItbPeerPtrs para
                       float* __restrict__ v, ItbPeerPtrs flags, long long off, long long n, int rank,
                       int world, int ch0, int epoch, ItbAdamHyper h, int* err,
                       int* __restrict__ epoch_ctr, const float* __restrict__ dev_hyper) {
+  if (*static_cast<volatile int*>(err) != 0) return;
   const int ch = ch0 + blockIdx.x;
   if (epoch_ctr) epoch = epoch_ctr[ch] + 1;
   if (dev_hyper) {   // [lr, 1/bc1, 1/bc2] refreshed by the host before every graph replay
@@ -220,6 +223,7 @@ ce_merge_kernel(ItbPeerPtrs bufs, ItbPeerPtrs flags, const float* __restrict__ l
                 const float* __restrict__ row_loss, const long long* __restrict__ t_local, int vocab_valid,
                 float* __restrict__ lse_out, float* __restrict__ loss_out, int rows, int rows_cap, int rank,
                 int world, int ch0, int* err, int* __restrict__ epoch_ctr) {
+  if (*static_cast<volatile int*>(err) != 0) return;
   const int ch = ch0 + blockIdx.x;
   const int epoch = epoch_ctr[ch] + 1;
   const int chunk = (rows + gridDim.x - 1) / gridDim.x;

@@ -16,7 +16,10 @@
 //   * The scratch array is part of the loaded library image: every GPU that loads the library holds
 //     its 4 MiB until the process exits.
 //   * The first call on each device looks up the device address of the array (cudaGetSymbolAddress)
-//     with that device current.  Make that first call outside any CUDA stream capture.
+//     with that device current.  Make that first call outside any CUDA stream capture, and from one
+//     thread per device: the cached address is written without a lock (concurrent first calls on one
+//     device would each look up and store the same value, which is harmless but not synchronised).
+//   * x must be 16-byte aligned, ld >= N, and rows at most 65535 * 128; otherwise -3 is returned.
 //   * No cudaMalloc / cudaFree / allocating library routine is called, here or in the kernels.
 //   * All calls on a device share the one array.  The first stage overwrites every partial sum it
 //     later reads, so nothing needs clearing between calls, but two calls that can run at the same

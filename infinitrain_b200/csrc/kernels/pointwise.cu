@@ -480,8 +480,9 @@ extern "C" int itb_colsum_partial_rows(int rows) {
 extern "C" int itb_colsum(const void* x, int dtype, long long ld, float* out, float* partial,
                           int rows, int N, int accumulate, cudaStream_t s) {
   if (rows <= 0 || N <= 0) return 0;
-  if (N % 8 || ld % 8) return -3;
+  if (N % 8 || ld % 8 || ld < N || (reinterpret_cast<uintptr_t>(x) & 15)) return -3;
   const int nparts = itb_colsum_partial_rows(rows);
+  if (nparts > 65535) return -3;      // grid.y limit
   dim3 grid((N + 255) / 256, nparts);
   if (dtype == kItbBF16)
     colsum_stage1_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
@@ -525,9 +526,11 @@ int colsum_static_scratch(float** out_ptr) {
 extern "C" int itb_colsum_static(const void* x, int dtype, long long ld, float* out, int rows, int N,
                                  int accumulate, cudaStream_t s) {
   if (rows <= 0 || N <= 0) return 0;
-  if (N % 8 || ld % 8) return -3;
+  // 16-byte vector loads of x: aligned base, row stride and width in multiples of 8 elements
+  if (N % 8 || ld % 8 || ld < N || (reinterpret_cast<uintptr_t>(x) & 15)) return -3;
   if (dtype != kItbBF16 && dtype != kItbF32) return -4;
   const int nparts = itb_colsum_partial_rows(rows);
+  if (nparts > 65535) return -3;      // grid.y limit (more than 8.3 M rows)
   if (static_cast<long long>(nparts) * N > kItbColsumStaticMaxPartials) return kItbErrScratchTooSmall;
   float* partial = nullptr;
   if (int rc = colsum_static_scratch(&partial)) return rc;

@@ -3,6 +3,7 @@
 // { uint32 name_len, name, int8 dtype code, uint32 ndim, int64 dims[ndim], uint64 bytes, raw data }
 // (the reference's format: infini_train/src/checkpoint/checkpoint.cc:112-140).
 #pragma once
+#include <algorithm>
 #include <torch/torch.h>
 
 #include <cstdio>
@@ -74,6 +75,9 @@ inline void save_state_dict(const std::string& path, const std::vector<std::stri
 inline std::vector<std::pair<std::string, at::Tensor>> load_state_dict(const std::string& path) {
   std::ifstream ifs(path, std::ios::binary);
   TORCH_CHECK(ifs.is_open(), "Failed to open checkpoint file: ", path);
+  ifs.seekg(0, std::ios::end);
+  const uint64_t file_size = static_cast<uint64_t>(ifs.tellg());
+  ifs.seekg(0, std::ios::beg);
   uint32_t magic = 0, version = 0, count = 0;
   ifs.read(reinterpret_cast<char*>(&magic), 4);
   ifs.read(reinterpret_cast<char*>(&version), 4);
@@ -96,9 +100,21 @@ inline std::vector<std::pair<std::string, at::Tensor>> load_state_dict(const std
     for (auto& d : dims) ifs.read(reinterpret_cast<char*>(&d), 8);
     uint64_t bytes = 0;
     ifs.read(reinterpret_cast<char*>(&bytes), 8);
-    at::Tensor t = torch::empty(dims, torch::dtype(dtype_from_code(code)));
-    TORCH_CHECK(bytes == static_cast<uint64_t>(t.numel()) * t.element_size(),
-                "Tensor bytes mismatch for key: ", name);
+    TORCH_CHECK(ifs.good(), "Truncated checkpoint: ", path);
+    // validate the record against itself and against the file BEFORE allocating: a corrupt dims or
+    // bytes field must give a clear error, not a huge allocation
+    const auto dtype = dtype_from_code(code);
+    uint64_t numel = 1;
+    for (int64_t d : dims) {
+      TORCH_CHECK(d >= 0, "Corrupt checkpoint (negative dimension) for key: ", name);
+      TORCH_CHECK(d == 0 || numel <= (uint64_t{1} << 56) / static_cast<uint64_t>(d),
+                  "Corrupt checkpoint (dimensions overflow) for key: ", name);
+      numel *= static_cast<uint64_t>(d);
+    }
+    TORCH_CHECK(bytes == numel * c10::elementSize(dtype), "Tensor bytes mismatch for key: ", name);
+    TORCH_CHECK(bytes <= file_size - std::min<uint64_t>(file_size, static_cast<uint64_t>(ifs.tellg())),
+                "Truncated checkpoint: ", path);
+    at::Tensor t = torch::empty(dims, torch::dtype(dtype));
     ifs.read(static_cast<char*>(t.data_ptr()), static_cast<std::streamsize>(bytes));
     TORCH_CHECK(ifs.good() || (ifs.eof() && i + 1 == count && ifs.gcount() == (std::streamsize)bytes),
                 "Truncated checkpoint: ", path);

@@ -130,3 +130,47 @@ class DistributedDataLoader(DataLoader):
             return
         for b in range(self.ddp_rank, self._num_batches(), self.ddp_world_size):
             yield self.batch(b)
+
+
+class DeviceFeeder:
+    """Moves the batches of a loader to the device with asynchronous copies, and keeps the copies
+    ordered against the loader's buffer reuse.
+
+    The prefetching loader hands out views of pinned ring slots that stay valid only until two
+    further batches have been fetched (the worker thread then refills the slot).  A training loop that
+    fetches several micro-batches ahead of the GPU (gradient accumulation with no host sync in
+    between) could therefore have a slot refilled while its host-to-device copy has not run yet.
+    ``next()`` records an event after each pair of copies and, before fetching a batch whose arrival
+    frees a slot, waits on the host for the copy that read that slot.  Loaders without a ring
+    (fresh tensors per batch) pay one cheap event per batch.
+    """
+
+    kSlotsInFlight = 2      # a slot handed out by call n may be refilled once call n + 2 has begun
+
+    def __init__(self, batches, device: torch.device):
+        self._it = iter(batches)
+        self.device = device
+        self._pending: List = []          # events of the copies whose source slot may still be live
+
+    def next(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        cuda = self.device.type == "cuda"
+        if cuda and len(self._pending) >= self.kSlotsInFlight:
+            self._pending.pop(0).synchronize()
+        x, y = next(self._it)
+        if not cuda:
+            return x.to(self.device), y.to(self.device)
+        dx, dy = x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pending.append(ev)
+        return dx, dy
+
+    def skip(self, n: int) -> None:
+        """Drops ``n`` batches (resume: fast-forward past what a checkpoint had consumed)."""
+        for _ in range(n):
+            next(self._it)
+
+    __next__ = next
+
+    def __iter__(self):
+        return self

@@ -1,6 +1,7 @@
 """Micro-benchmarks of the hot sm_100a kernels on the shapes of the headline models.
 
     python -m infinitrain_b200.ops.microbench gemm        # tcgen05 GEMM vs torch.matmul (cuBLAS), GPT-2 shapes
+    python -m infinitrain_b200.ops.microbench gemm_llama_tp8   # the same for LLaMA-3 8B's per-rank shapes under TP8
     python -m infinitrain_b200.ops.microbench attention   # tcgen05 vs mma.sync flash attention, forward + backward
     python -m infinitrain_b200.ops.microbench profile     # one launch of each, for a profiler capture
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
@@ -52,11 +53,12 @@ def _attn_tensors(B, T, H, KV, D):
     return q, k, v, dq, dk, dv
 
 
-def bench_gemm(C):
+def bench_gemm(C, tokens=16 * 1024, layers=((2304, 768), (768, 768), (3072, 768), (768, 3072), (50304, 768))):
+    """Forward, input-gradient and weight-gradient GEMM of each linear layer ``(out, in)`` on ``tokens``
+    rows.  Defaults: GPT-2 124M at 16 x 1024 tokens."""
     timeit = _timer()
-    tokens = 16 * 1024
     shapes = []
-    for n, k in ((2304, 768), (768, 768), (3072, 768), (768, 3072), (50304, 768)):
+    for n, k in layers:
         shapes += [("fwd", tokens, n, k), ("dgrad", tokens, k, n), ("wgrad", n, k, tokens)]
     for kind, M, N, K in shapes:
         if kind == "fwd":
@@ -82,6 +84,12 @@ def bench_gemm(C):
         fl = 2.0 * M * N * K
         print(json.dumps({"case": "gemm", "kind": kind, "M": M, "N": N, "K": K, "ours_ms": ours, "cublas_ms": lib,
                           "ours_tflops": fl / ours / 1e9, "cublas_tflops": fl / lib / 1e9}))
+
+
+def bench_gemm_llama_tp8(C):
+    """The per-rank GEMMs of LLaMA-3 8B under 8-way tensor parallelism at 1 x 2048 tokens (the skinny
+    shapes behind the fused all-gather+GEMM / GEMM+reduce-scatter kernels), without the collectives."""
+    bench_gemm(C, tokens=2048, layers=((768, 4096), (4096, 512), (1792, 4096), (4096, 1792), (16032, 4096)))
 
 
 def bench_attention(C):
@@ -195,7 +203,8 @@ def main(argv):
     C = _ext.load(required=True)
     torch.manual_seed(0)
     case = argv[1] if len(argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "attention": bench_attention, "profile": profile_case, "tp": bench_tp}[case](C)
+    {"gemm": bench_gemm, "gemm_llama_tp8": bench_gemm_llama_tp8, "attention": bench_attention, "profile": profile_case,
+     "tp": bench_tp}[case](C)
     return 0
 
 

@@ -56,22 +56,40 @@ class DataParallel(Module):
             devices = [torch.device("cuda", i) for i in range(n)] or [torch.device("cpu")]
         self.devices = list(devices)
         self.output_device = self.devices[0]
+        self._replicas: Optional[List[torch.nn.Module]] = None
+
+    def _replica_shells(self, module: torch.nn.Module) -> List[torch.nn.Module]:
+        """One module object per device.  The replicas' own parameter tensors are never used: every
+        forward runs them on the freshly broadcast copies of the source module's parameters (the
+        reference replicates the module each forward, data_parallel.cc:61-100).  Separate objects are
+        needed because the replicas run in threads, and substituting parameters into ONE module from
+        several threads at once would leave it holding a replica's tensors."""
+        if self._replicas is None:
+            import copy
+
+            self._replicas = [module] + [copy.deepcopy(module).to(d) for d in self.devices[1:]]
+        return self._replicas
 
     def Forward(self, *inputs):
         module = self._modules[self.kModuleName]
         if len(self.devices) == 1:
             return module(*[x.to(self.devices[0]) for x in inputs])
         scattered = [PF.Scatter(x, self.devices, self.dim) for x in inputs]
-        params = list(module.parameters())
+        names = [n for n, _ in module.named_parameters()]
+        params = [p for _, p in module.named_parameters()]
         copies = _Broadcast.apply(self.devices, *params)
+        buffers = list(module.named_buffers())
+        replicas = self._replica_shells(module)
         outputs: List[Optional[torch.Tensor]] = [None] * len(self.devices)
         errors: List[Optional[BaseException]] = [None] * len(self.devices)
 
         def run(i, dev):
             try:
-                rep_params = copies[i * len(params):(i + 1) * len(params)]
-                names = [n for n, _ in module.named_parameters()]
-                out = torch.func.functional_call(module, dict(zip(names, rep_params)), tuple(s[i] for s in scattered))
+                if scattered and scattered[0][i:i + 1] == []:
+                    return            # fewer chunks than devices (batch smaller than the device count)
+                state = dict(zip(names, copies[i * len(params):(i + 1) * len(params)]))
+                state.update({n: b.to(dev) for n, b in buffers})
+                out = torch.func.functional_call(replicas[i], state, tuple(s[i] for s in scattered))
                 outputs[i] = out
             except BaseException as e:  # noqa: BLE001
                 errors[i] = e
@@ -84,4 +102,4 @@ class DataParallel(Module):
         for e in errors:
             if e is not None:
                 raise e
-        return PF.Gather(outputs, self.output_device, self.dim)
+        return PF.Gather([o for o in outputs if o is not None], self.output_device, self.dim)

@@ -100,6 +100,8 @@ class DistributedDataParallel(Module):
                     return work if work is not None else pg.AllReduce(contents, ReduceOpType.kAvg, async_op=True)
         indices = ComputeBucketAssignmentBySize(params, limits)
         self.reducer = Reducer(params, indices, self.pg, self.config, allreduce_fn=allreduce_fn, flat_buffer=flat)
+        if allreduce_fn is not None:
+            self.reducer.status_ctx = self.nvlink_ctx
         self.reducer.AttachHooksToParameters()
 
     # ------------------------------------------------------------------ mode: ZeRO-1/2

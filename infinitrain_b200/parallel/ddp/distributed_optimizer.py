@@ -61,11 +61,14 @@ class DistributedOptimizer(Optimizer):
         from .. import symm
 
         base = self.base_optimizer
+        self._nvlink_ctxs = []
         if not isinstance(base, Adam) or not all(getattr(ch, "nvlink_ctx", None) is not None for ch in chunks):
             return False
         k = 0
         for ch in chunks:
             ctx = ch.nvlink_ctx
+            if ctx not in self._nvlink_ctxs:
+                self._nvlink_ctxs.append(ctx)
             for g in ch.bucket_groups:
                 steps = []
                 for bucket in g.buckets:
@@ -75,10 +78,20 @@ class DistributedOptimizer(Optimizer):
                 g.fused_hyper_fn = self._fused_hyper
         return True
 
-    def _fused_hyper(self):
+    def _fused_hyper(self, group: Optional[ParamAndGradBucketGroup] = None, bucket=None):
+        """Arguments of one fused bucket launch.  The kernel sums the ranks' gradients, so the scale it
+        applies afterwards carries the data-parallel average (``average_in_collective``, the
+        reference's ``kAvg``: ddp/param_and_grad_buffer.cc:286-292) and the bucket's own
+        ``gradient_scaling_factor``, as the NCCL formulation does."""
         b = self.base_optimizer
         t = b.t + 1   # the step these launches belong to (Step() increments t afterwards)
-        return (b.learning_rate, b.beta1, b.beta2, b.eps, b.weight_decay, 1.0 - b.beta1 ** t, 1.0 - b.beta2 ** t, 1.0,
+        scale = 1.0
+        if group is not None:
+            if group.config.average_in_collective:
+                scale /= max(group.pg_size, 1)
+            if bucket is not None:
+                scale *= bucket.gradient_scaling_factor
+        return (b.learning_rate, b.beta1, b.beta2, b.eps, b.weight_decay, 1.0 - b.beta1 ** t, 1.0 - b.beta2 ** t, scale,
                 b._dev_hyper())
 
     def ZeroGrad(self, set_to_none: bool = True) -> None:
@@ -115,6 +128,13 @@ class DistributedOptimizer(Optimizer):
         self.FinishGradSync()
         if self.fused:
             # Every bucket was reduced, updated and broadcast by its fused kernel during backward.
+            # A kernel that gave up on a peer skipped its reduction: look at the status word as of the
+            # previous step (pinned mirror, no host sync) and queue this step's copy.
+            capturing = torch.cuda.is_current_stream_capturing()
+            for ctx in self._nvlink_ctxs:
+                if not capturing:
+                    ctx.check(sync=False, what="fused ZeRO step")
+                ctx.poll_status()
             self.base_optimizer.t += 1
             self.base_optimizer._prepared = False
             for buf in self.buffers:

@@ -289,9 +289,8 @@ class ParamAndGradBucketGroup:
         op = ReduceOpType.kAvg if self.config.average_in_collective else ReduceOpType.kSum
         async_op = self.config.overlap_grad_reduce
         if self.fused_steps is not None and self.fused_hyper_fn is not None:
-            hyper = self.fused_hyper_fn()
-            for step in self.fused_steps:
-                self.grad_reduce_works.append(step(*hyper))
+            for step, bucket in zip(self.fused_steps, self.buckets):
+                self.grad_reduce_works.append(step(*self.fused_hyper_fn(self, bucket)))
             self.fused_updated = True
             self.grad_reduce_dispatched = True
             self.params_with_grad.clear()

@@ -86,6 +86,7 @@ class Reducer:
         self.pg = pg
         self.config = config or DistributedDataParallelConfig()
         self.allreduce_fn = allreduce_fn   # optional override: the fused NVLink kernel
+        self.status_ctx = None             # the NvlinkContext whose status word that kernel writes
         self.buckets: List[_Bucket] = []
         self.locator: Dict[int, tuple] = {}
         self.next_bucket = 0
@@ -239,6 +240,12 @@ class Reducer:
                         p.grad.copy_(bucket.contents[bucket.offsets[j]:bucket.offsets[j] + p.numel()].view(p.shape))
         if not self.has_rebuilt:
             self.need_rebuild = True
+        if self.status_ctx is not None:
+            # a fused all-reduce that gave up on a peer left its bucket unreduced: the word as of the
+            # previous backward is checked here without a host sync, this backward's copy is queued
+            if not torch.cuda.is_current_stream_capturing():
+                self.status_ctx.check(sync=False, what="fused gradient all-reduce")
+            self.status_ctx.poll_status()
 
     def Flush(self):
         """Launches whatever has not been launched (parameters that received no gradient)."""

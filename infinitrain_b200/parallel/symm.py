@@ -69,6 +69,8 @@ class NvlinkContext:
         self.flags = self.alloc(kFlagChannels * self.C.MAX_RANKS, torch.int32, device)
         self.flag_ptrs, _ = self.ptrs(self.flags)
         self.err = torch.zeros(4, dtype=torch.int32, device=device)
+        # pinned host mirror of the status word, refreshed by poll_status() without a host sync
+        self.err_host = torch.zeros(4, dtype=torch.int32).pin_memory()
         self.stream = torch.cuda.Stream(device=device, priority=-1)
         self._next_channel = 0
         # Launch epochs live on the device (one counter per channel, advanced by the kernels), so a
@@ -115,7 +117,29 @@ class NvlinkContext:
         return ch
 
     def status(self) -> int:
+        """The status word, read with a synchronous copy (0 = every bounded wait so far was met)."""
         return int(self.err.cpu()[0].item())
+
+    def poll_status(self) -> None:
+        """Queues a copy of the status word into the pinned host mirror on the current stream: no
+        host synchronisation, and capturable in a CUDA graph (every replay refreshes the mirror)."""
+        self.err_host.copy_(self.err, non_blocking=True)
+
+    def check(self, sync: bool = False, what: str = "NVLink collective") -> None:
+        """Raises ``KernelTimeout`` when a fused collective gave up waiting for a peer.  With
+        ``sync=False`` it looks at the host mirror, i.e. at the state of the last completed
+        ``poll_status``; a kernel that timed out skipped its reduction, so training must not go on."""
+        code = self.status() if sync else int(self.err_host[0])
+        if code != 0:
+            from ..utils.fault_tolerance import KernelTimeout
+
+            raise KernelTimeout(f"{what} of group {self.pg.name}: a bounded device-side wait gave up "
+                                f"(code {code}); gradients / shards of this step are not reduced")
+
+    @classmethod
+    def check_all(cls, sync: bool = False) -> None:
+        for ctx in list(cls._by_group.values()):
+            ctx.check(sync)
 
     # ------------------------------------------------------------------ launch helper
     def launch(self, fn) -> StreamWork:
@@ -308,6 +332,33 @@ def reset_fused_tp():
     _TP_CTX, _TP_TRIED = None, False
 
 
+# Which formulation the tensor-parallel linears ran: calls served by the fused all-gather+GEMM /
+# GEMM+reduce-scatter kernels and calls that fell back to NCCL collectives around a plain GEMM.  A
+# benchmark quotes these so that a "fused" number cannot come from the fallback unnoticed.
+tp_path_counts: Dict[str, int] = {"fused": 0, "nccl": 0}
+_tp_path_logged: set = set()
+
+
+def note_tp_path(module, x: torch.Tensor, fused: bool) -> None:
+    """Counts the call and logs, once per layer and path, which formulation served it."""
+    tp_path_counts["fused" if fused else "nccl"] += 1
+    key = (id(module), fused)
+    if key in _tp_path_logged:
+        return
+    _tp_path_logged.add(key)
+    if os.environ.get("ITB_LOG_TP_PATH", "0") == "1" or (not fused and x.is_cuda):
+        from ..utils.logging import LOG
+
+        why = "" if fused else (" (the fused kernels need a bf16 CUDA activation [B, T, C] with C % 8 == 0 and "
+                                f"T / tp a multiple of {kTpRowTile}; got {tuple(x.shape)} {x.dtype})")
+        LOG("INFO", f"{type(module).__name__}({getattr(module, 'in_features', '?')} -> "
+                    f"{getattr(module, 'out_features', '?')}): "
+                    f"{'fused NVLink kernel' if fused else 'NCCL collective + GEMM'}{why}")
+
+
+kTpRowTile = 256     # rows of one output tile of the fused kernels: T / tp must be a multiple of it
+
+
 def fused_tp_enabled(x: torch.Tensor, seq_sharded: bool = True) -> bool:
     """True when the fused all-gather+GEMM / GEMM+reduce-scatter kernels can serve ``x``: a 3-D CUDA
     activation under bf16 whose per-rank sequence length is a multiple of 256."""
@@ -317,7 +368,7 @@ def fused_tp_enabled(x: torch.Tensor, seq_sharded: bool = True) -> bool:
     if tp is None:
         return False
     t_local = x.shape[1] if seq_sharded else x.shape[1] // tp.world
-    return t_local % 256 == 0 and (seq_sharded or x.shape[1] % tp.world == 0)
+    return t_local % kTpRowTile == 0 and (seq_sharded or x.shape[1] % tp.world == 0)
 
 
 class _AllGatherLinearFn(torch.autograd.Function):

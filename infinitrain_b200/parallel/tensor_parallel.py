@@ -210,12 +210,16 @@ class ColumnParallelLinear(Module):
 
         add_bias = self.bias if (self.has_bias and not self.skip_bias_add) else None
         if self.sequence_parallel and symm.fused_tp_enabled(x):
+            symm.note_tp_path(self, x, True)
             y = symm.allgather_linear(x, self.weight, add_bias, gelu=gelu)
         elif (not self.sequence_parallel and not self.input_is_parallel and _tp() is not None
               and symm.fused_tp_enabled(x, seq_sharded=False)):
             # replicated input: no communication forward, the gradient all-reduce is fused into dgrad
+            symm.note_tp_path(self, x, True)
             y = symm.copy_linear(x, self.weight, add_bias, gelu=gelu)
         else:
+            if _tp() is not None:
+                symm.note_tp_path(self, x, False)
             if self.sequence_parallel:
                 x = GatherFromSPRegionFunc(x)
             elif not self.input_is_parallel:
@@ -265,10 +269,13 @@ class RowParallelLinear(Module):
         if grp is None or not self.reduce_output:
             y = ops.linear(x, self.weight, add_bias, residual=residual)
         elif self.sequence_parallel and symm.fused_tp_enabled(x, seq_sharded=False):
+            symm.note_tp_path(self, x, True)
             y = symm.linear_reduce_scatter(x, self.weight, add_bias, residual)
         elif not self.sequence_parallel and symm.fused_tp_enabled(x, seq_sharded=False):
+            symm.note_tp_path(self, x, True)
             y = symm.linear_all_reduce(x, self.weight, add_bias, residual)
         else:
+            symm.note_tp_path(self, x, False)
             y = ops.linear(x, self.weight, None)
             y = ReduceScatterToSPRegionFunc(y) if self.sequence_parallel else ReduceFromTPRegionFunc(y)
             if add_bias is not None:

@@ -12,6 +12,7 @@ inputs are copied into static buffers before each replay.
 """
 from __future__ import annotations
 
+import sys
 from typing import Callable, Sequence
 
 import torch
@@ -43,6 +44,11 @@ class GraphedTrainStep:
         for dst, src in zip(self.static_inputs, inputs):
             if dst.data_ptr() != src.data_ptr():
                 dst.copy_(src, non_blocking=True)
+        # a fused NVLink collective of an earlier replay that gave up on a peer has left gradients
+        # unreduced: stop here (the captured step refreshes the pinned status mirrors itself)
+        symm = sys.modules.get("infinitrain_b200.parallel.symm")
+        if symm is not None:
+            symm.NvlinkContext.check_all(sync=False)
         self.graph.replay()
         ops._counters["launches"] += self.launches_per_replay
         return self.static_loss

@@ -214,6 +214,27 @@ def check_kernel_status(status_fn: Callable[[], int], what: str = "kernel") -> N
         raise KernelTimeout(f"{what}: a bounded device-side wait gave up (code {code})")
 
 
+def check_device_status(sync: bool = True) -> None:
+    """One call for a training loop's per-step sync point: raises ``KernelTimeout`` when a bounded
+    wait of the single-GPU kernels or of any fused NVLink collective of this process has given up.
+    ``sync=True`` reads the words with synchronous copies (use it where the loop has just
+    synchronised anyway, e.g. after reading the loss); ``sync=False`` only looks at the pinned host
+    mirrors that ``NvlinkContext.poll_status`` refreshes.  Does nothing on CPU ranks."""
+    import sys
+
+    symm = sys.modules.get("infinitrain_b200.parallel.symm")
+    if symm is not None:
+        symm.NvlinkContext.check_all(sync)
+    if sync:
+        from .. import _ext
+
+        C = _ext.load(required=False)
+        import torch
+
+        if C is not None and torch.cuda.is_available() and torch.cuda.is_initialized():
+            check_kernel_status(C.kernel_status, "single-GPU kernel")
+
+
 # --------------------------------------------------------------------------- fault injection (host only)
 class FaultInjector:
     """``ITB_FAULT="<rank>:<step>:<kind>[:<arg>]"`` with kind one of
@@ -237,6 +258,18 @@ class FaultInjector:
             self.arg = parts[3] if len(parts) > 3 else ""
         self.fired = False
 
+    @staticmethod
+    def exit_allowed() -> bool:
+        """A process may be killed by the injector when it has no CUDA context, or when neither NCCL
+        nor this framework's kernels use NVLS multicast (``NCCL_NVLS_ENABLE=0`` and ``ITB_NVLS=0``)."""
+        import sys
+
+        torch = sys.modules.get("torch")
+        on_cuda = torch is not None and torch.cuda.is_available() and torch.cuda.is_initialized()
+        if not on_cuda:
+            return True
+        return os.environ.get("ITB_NVLS", "1") == "0" and os.environ.get("NCCL_NVLS_ENABLE", "") == "0"
+
     def maybe_fire(self, step: int) -> None:
         if self.fired or self.kind == "" or self.rank != self.target_rank or step != self.step:
             return
@@ -244,6 +277,11 @@ class FaultInjector:
         if self.kind == "raise":
             raise RuntimeError(f"injected fault on rank {self.rank} at step {step}")
         if self.kind == "exit":
+            if not self.exit_allowed():
+                raise RuntimeError(
+                    "ITB_FAULT ...:exit refused: this process holds CUDA memory that may be bound to an NVLink "
+                    "multicast object, and a rank that dies like that faults its peers' GPUs; rerun on CPU ranks, or "
+                    "with ITB_NVLS=0 and NCCL_NVLS_ENABLE=0")
             os._exit(int(self.arg or 17))
         if self.kind == "stall":
             time.sleep(float(self.arg or 1.0))

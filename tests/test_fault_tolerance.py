@@ -143,6 +143,94 @@ def test_corrupted_checkpoint_is_rejected(tmp_path):
         Checkpoint.LoadStateDict(path)
 
 
+def test_corrupt_record_fields_give_clear_errors_before_any_allocation(tmp_path):
+    """A damaged dimension or byte-count field must be refused by the record's own consistency checks
+    (not by an attempt to allocate what the field says), and a file cut short must say so."""
+    import struct
+
+    from infinitrain_b200.checkpoint.checkpoint import Checkpoint
+
+    path = str(tmp_path / "model.ckpt")
+    Checkpoint.SaveStateDict(path, {"w": torch.arange(12, dtype=torch.float32).view(3, 4)})
+    good = open(path, "rb").read()
+    # header 12 B, then: name_len u32 @12, "w" @16, dtype @17, ndim u32 @18, dims i64 @22 and @30, bytes u64 @38, data @46
+    assert struct.unpack_from("<q", good, 22)[0] == 3 and struct.unpack_from("<Q", good, 38)[0] == 48
+
+    def damaged(offset, fmt, value):
+        b = bytearray(good)
+        struct.pack_into(fmt, b, offset, value)
+        with open(path, "wb") as f:
+            f.write(bytes(b))
+
+    damaged(22, "<q", 1 << 40)                     # a dimension that would ask for terabytes
+    with pytest.raises(Exception, match="bytes mismatch|overflow"):
+        Checkpoint.LoadStateDict(path)
+    damaged(22, "<q", -3)
+    with pytest.raises(Exception, match="negative dimension"):
+        Checkpoint.LoadStateDict(path)
+    damaged(38, "<Q", 1 << 50)                     # byte count that disagrees with the dimensions
+    with pytest.raises(Exception, match="bytes mismatch"):
+        Checkpoint.LoadStateDict(path)
+    with open(path, "wb") as f:                    # consistent record, data cut short
+        f.write(good[:-16])
+    with pytest.raises(Exception, match="Truncated"):
+        Checkpoint.LoadStateDict(path)
+    with open(path, "wb") as f:
+        f.write(good)
+    assert torch.equal(Checkpoint.LoadStateDict(path)["w"], torch.arange(12, dtype=torch.float32).view(3, 4))
+
+
+def test_a_timed_out_fused_collective_stops_training_on_the_host():
+    """The status word of an NVLink context is read at the step's sync point (synchronously) and at the
+    fused optimizer step / graph replay (pinned mirror, no sync); a non-zero word raises ``KernelTimeout``.
+    The context here is a stand-in: no GPU, no peer, nothing waits."""
+    from infinitrain_b200.parallel import symm
+    from infinitrain_b200.utils.fault_tolerance import check_device_status
+
+    class _PG:
+        name = "DP0"
+
+    ctx = symm.NvlinkContext.__new__(symm.NvlinkContext)
+    ctx.pg = _PG()
+    ctx.err = torch.zeros(4, dtype=torch.int32)
+    ctx.err_host = torch.zeros(4, dtype=torch.int32)
+    symm.NvlinkContext._by_group["test:cpu"] = ctx
+    try:
+        check_device_status(sync=True)             # all clear
+        ctx.check()
+        ctx.err[0] = 203                           # what rs_adamw_bcast_kernel records when a peer never arrives
+        ctx.check()                                # the mirror has not been refreshed yet
+        with pytest.raises(KernelTimeout, match="203"):
+            check_device_status(sync=True)
+        ctx.poll_status()
+        with pytest.raises(KernelTimeout, match="not reduced"):
+            ctx.check(sync=False)
+        with pytest.raises(KernelTimeout):
+            check_device_status(sync=False)
+    finally:
+        del symm.NvlinkContext._by_group["test:cpu"]
+
+
+def test_injector_refuses_to_kill_a_cuda_rank_with_multicast_on(monkeypatch):
+    """``exit`` faults are for CPU ranks, or for GPU runs with NVLS off in NCCL and in this framework:
+    a rank that dies while its memory is bound to an NVLink multicast object faults its peers."""
+    import infinitrain_b200.utils.fault_tolerance as ft
+
+    assert ft.FaultInjector.exit_allowed()         # this process has no CUDA context
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "is_initialized", lambda: True)
+    monkeypatch.delenv("ITB_NVLS", raising=False)
+    monkeypatch.delenv("NCCL_NVLS_ENABLE", raising=False)
+    assert not ft.FaultInjector.exit_allowed()
+    inj = ft.FaultInjector(0, "0:2:exit:17")
+    with pytest.raises(RuntimeError, match="refused"):
+        inj.maybe_fire(2)
+    monkeypatch.setenv("ITB_NVLS", "0")
+    assert not ft.FaultInjector.exit_allowed()     # NCCL's own multicast is still on
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    assert ft.FaultInjector.exit_allowed()
+
+
 def test_file_rendezvous(tmp_path):
     """Ranks with no MASTER_ADDR meet through a file on a shared filesystem (the reference's scheme)."""
     import subprocess

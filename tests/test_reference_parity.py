@@ -16,7 +16,8 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BIN = os.path.join(ROOT, "baseline", "_ref", "bin", "gpt2_cpu")
-SRC = os.environ.get("ITB_REFERENCE_SRC", os.path.join(os.sep, "root", "reference"))
+# the reference checkout: ITB_REFERENCE_SRC, else a directory named "reference" beside this repository
+SRC = os.environ.get("ITB_REFERENCE_SRC") or os.path.join(os.path.dirname(ROOT), "reference")
 OURS = [sys.executable, os.path.join(ROOT, "examples", "gpt2", "main.py")]
 
 

@@ -61,3 +61,7 @@ def test_static_scratch_rejects_oversized_requests():
     rc = fn(x.data_ptr(), 0, 8192, out.data_ptr(), 128 * 200, 8192, 0, stream)
     assert rc == -100
     assert fn(x.data_ptr(), 0, 12, out.data_ptr(), 8, 12, 0, stream) == -3      # N not a multiple of 8
+    # more than 65535 row blocks (the grid's y limit) passes the scratch check with N = 8: rejected, not launched
+    assert fn(x.data_ptr(), 0, 8, out.data_ptr(), 65536 * 128, 8, 0, stream) == -3
+    assert fn(x.data_ptr(), 0, 8, out.data_ptr(), 8, 16, 0, stream) == -3       # row stride shorter than a row
+    assert fn(x.data_ptr() + 4, 0, 8, out.data_ptr(), 8, 8, 0, stream) == -3    # x not 16-byte aligned
