@@ -450,6 +450,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("GEMM_RESIDUAL") = static_cast<int>(kGemmResidual);
   m.attr("GEMM_GELU_DUAL") = static_cast<int>(kGemmGeluDual);
   m.attr("GEMM_DGELU") = static_cast<int>(kGemmDGelu);
+  m.attr("GEMM_PROBE_NO_LOAD") = static_cast<int>(kGemmProbeNoLoad);
+  m.attr("GEMM_PROBE_NO_MMA") = static_cast<int>(kGemmProbeNoMma);
   m.def("kernel_status", &kernel_status);
   m.def("kernel_status_reset", &kernel_status_reset);
   m.def("gemm", &gemm);

@@ -288,4 +288,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t mbar_cluster_addr) {
                : "memory");
 }
 
+// One commit that arrives on the mbarrier at the same shared-memory offset in every CTA of `cta_mask`
+// (the pair: 0b11).  Signals only: no data moves, this is not a load.
+__device__ __forceinline__ void umma_commit_pair_mc(uint32_t mbar_addr, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          mbar_addr),
+      "h"(cta_mask)
+      : "memory");
+}
+
 }  // namespace itb

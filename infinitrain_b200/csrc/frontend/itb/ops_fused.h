@@ -101,8 +101,11 @@ inline void gemm(const Tensor& a, bool a_mn, const Tensor& b, bool b_mn, int64_t
 
 // ------------------------------------------------------------------ linear
 struct LinearFn : public torch::autograd::Function<LinearFn> {
-  static Tensor forward(AutogradContext* ctx, const Tensor& x, const Tensor& weight, const Tensor& bias,
-                        const Tensor& residual, bool gelu) {
+  // Optional tensor inputs are std::optional arguments: an undefined Tensor passed to apply() would be
+  // recorded as a variable input, and the engine rejects a variable without a device.
+  static Tensor forward(AutogradContext* ctx, const Tensor& x, const Tensor& weight, const c10::optional<Tensor>& bias_o,
+                        const c10::optional<Tensor>& residual_o, bool gelu) {
+    const Tensor bias = bias_o.value_or(Tensor()), residual = residual_o.value_or(Tensor());
     int64_t K = x.size(-1), N = weight.size(0);
     Tensor x2 = as_bf16_2d(x);
     int64_t M = x2.size(0), ld = pad64(N);
@@ -180,7 +183,7 @@ struct LinearFn : public torch::autograd::Function<LinearFn> {
 };
 inline Tensor linear(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& b, const c10::optional<Tensor>& r,
                      bool gelu) {
-  return LinearFn::apply(x, w, b.value_or(Tensor()), r.value_or(Tensor()), gelu);
+  return LinearFn::apply(x, w, b, r, gelu);
 }
 
 // ------------------------------------------------------------------ normalisation
@@ -189,7 +192,9 @@ inline torch::Dtype norm_out_dtype(const Tensor& x) {
              ? torch::kBFloat16 : torch::kFloat32;
 }
 struct LayerNormFn : public torch::autograd::Function<LayerNormFn> {
-  static Tensor forward(AutogradContext* ctx, const Tensor& x, const Tensor& gamma, const Tensor& beta, double eps) {
+  static Tensor forward(AutogradContext* ctx, const Tensor& x, const Tensor& gamma, const c10::optional<Tensor>& beta_o,
+                        double eps) {
+    const Tensor beta = beta_o.value_or(Tensor());
     Tensor xc = contig(x);
     int64_t C = xc.size(-1), rows = xc.numel() / C;
     Tensor y = torch::empty(xc.sizes(), xc.options().dtype(norm_out_dtype(x)).requires_grad(false));
@@ -218,7 +223,7 @@ struct LayerNormFn : public torch::autograd::Function<LayerNormFn> {
   }
 };
 inline Tensor layernorm(const Tensor& x, const Tensor& g, const c10::optional<Tensor>& b, double eps) {
-  return LayerNormFn::apply(x, g, b.value_or(Tensor()), eps);
+  return LayerNormFn::apply(x, g, b, eps);
 }
 struct RMSNormFn : public torch::autograd::Function<RMSNormFn> {
   static Tensor forward(AutogradContext* ctx, const Tensor& x, const Tensor& gamma, double eps) {
@@ -313,8 +318,9 @@ struct AttentionFn : public torch::autograd::Function<AttentionFn> {
     a->scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(D)));
     a->causal = causal;
   }
-  static Tensor forward(AutogradContext* ctx, const Tensor& qkv_in, int64_t H, int64_t KV, int64_t D, const Tensor& freqs,
-                        int64_t pos0, bool causal) {
+  static Tensor forward(AutogradContext* ctx, const Tensor& qkv_in, int64_t H, int64_t KV, int64_t D,
+                        const c10::optional<Tensor>& freqs_o, int64_t pos0, bool causal) {
+    const Tensor freqs = freqs_o.value_or(Tensor());
     Tensor qkv = qkv_in.scalar_type() == torch::kBFloat16 ? qkv_in : qkv_in.to(torch::kBFloat16);
     int64_t B = qkv.size(0), T = qkv.size(1);
     if (!qkv.is_contiguous()) qkv = qkv.contiguous();
@@ -359,12 +365,14 @@ struct AttentionFn : public torch::autograd::Function<AttentionFn> {
 };
 inline Tensor attention_packed(const Tensor& qkv, int64_t H, int64_t KV, int64_t D, const c10::optional<Tensor>& freqs,
                                int64_t pos0, bool causal) {
-  return AttentionFn::apply(qkv, H, KV, D, freqs.value_or(Tensor()), pos0, causal);
+  return AttentionFn::apply(qkv, H, KV, D, freqs, pos0, causal);
 }
 
 // ------------------------------------------------------------------ embedding
 struct EmbeddingFn : public torch::autograd::Function<EmbeddingFn> {
-  static Tensor forward(AutogradContext* ctx, const Tensor& idx_in, const Tensor& wte, const Tensor& wpe, int64_t pos0) {
+  static Tensor forward(AutogradContext* ctx, const Tensor& idx_in, const Tensor& wte, const c10::optional<Tensor>& wpe_o,
+                        int64_t pos0) {
+    const Tensor wpe = wpe_o.value_or(Tensor());
     Tensor idx = contig(idx_in);
     int64_t B = idx.size(0), T = idx.size(1), C = wte.size(1);
     bool lp = autocast_state().enabled && autocast_state().dtype == torch::kBFloat16;
@@ -391,7 +399,7 @@ struct EmbeddingFn : public torch::autograd::Function<EmbeddingFn> {
   }
 };
 inline Tensor embedding(const Tensor& idx, const Tensor& wte, const c10::optional<Tensor>& wpe, int64_t pos0) {
-  return EmbeddingFn::apply(idx, wte, wpe.value_or(Tensor()), pos0);
+  return EmbeddingFn::apply(idx, wte, wpe, pos0);
 }
 
 // ------------------------------------------------------------------ cross entropy

@@ -20,13 +20,17 @@ constexpr int BMC = 128;        // rows of A per CTA (pair: 256)
 constexpr int BNC = 128;        // columns of B per CTA (pair: 256)
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int kStages = 5;
+#ifndef ITB_PAIR_STAGES
+#define ITB_PAIR_STAGES 5
+#endif
+constexpr int kStages = ITB_PAIR_STAGES;
+constexpr int kSlotsPerWarp = kStages >= 6 ? 2 : 4;
 constexpr int kThreads = 192;
 constexpr int kABytes = BMC * BK * 2;
 constexpr int kBBytes = BNC * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;                 // 32 KB
 constexpr int kSlotBytes = 32 * 128;                           // 32 rows x 64 bf16, 128-byte swizzle
-constexpr int kWarpStaging = 4 * kSlotBytes;                   // two sets of (C, C2 / operand) slots
+constexpr int kWarpStaging = kSlotsPerWarp * kSlotBytes;       // two sets of (C, C2 / operand) slots
 constexpr int kStagingOffset = kStages * kStageBytes;
 constexpr int kBarOffset = kStagingOffset + 4 * kWarpStaging;
 constexpr int kSmemTotal = kBarOffset + (2 * kStages + 4 + 4) * 8 + 16;
@@ -192,6 +196,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t phase = 0;
       bool ok = true;
       [[maybe_unused]] uint32_t gate_seen = 0;
+      // (probe without loads: nothing holds the leader back for the peer's sake, so the peer's producer
+      // could miss a barrier phase; it has no part in that run)
+      if ((p.flags & kGemmProbeNoLoad) && !leader) ok = false;
       for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
         int tm, tn, kb0, kb1;
         decode_tile(t, tm, tn, kb0, kb1);
@@ -225,6 +232,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           uint8_t* sb = sa + kABytes;
           // every load of the pair completes on the LEADER's barrier
           const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
+          if (p.flags & kGemmProbeNoLoad) {
+            if (leader) mbar_arrive(&full_bar[stage]);
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * kStageBytes);
           if constexpr (!A_MN) {
             tma_load_2d_pair(sa, &tma_a, bar, kb * BK, row0);
@@ -249,11 +264,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (leader) {
+    // ONE thread runs the whole loop: wait for a stage, issue its four MMAs, release it with one
+    // commit that arrives on both CTAs' barriers.  No tcgen05 fence inside the k-loop (the operands
+    // arrive through the async proxy and the barrier wait orders them); the fence after a thread
+    // synchronisation is only needed where the epilogue warps hand an accumulator back.
+    if (leader && lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16_f32(256, BN, A_MN, B_MN);
+      const bool probe_no_mma = p.flags & kGemmProbeNoMma;
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t acc_phase[2] = {0, 0};
+      uint32_t acc_phase0 = 0, acc_phase1 = 0;
       int local = 0;
       bool ok = true;
       for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++local) {
@@ -261,47 +281,39 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         decode_tile(t, tm, tn, kb0, kb1);
         const int acc = local & 1;
         if (kb1 <= kb0) continue;
-        if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1) || *abort_flag) {
-          if (lane == 0) atomicCAS(p.err, 0, 112);
+        const uint32_t ap = acc ? acc_phase1 : acc_phase0;
+        if (!mbar_wait(&tmem_empty[acc], ap ^ 1) || *abort_flag) {
+          atomicCAS(p.err, 0, 112);
           *abort_flag = 1;
-          ok = false;
           break;
         }
-        acc_phase[acc] ^= 1;
+        if (acc) acc_phase1 ^= 1; else acc_phase0 ^= 1;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase) || *abort_flag) {
-            if (lane == 0) atomicCAS(p.err, 0, 113);
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            atomicCAS(p.err, 0, 113);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          tc_fence_after_sync();
-          if (lane == 0) {
-            const uint32_t sa = smem_u32(smem + stage * kStageBytes);
-            const uint32_t sb = sa + kABytes;
-            const uint64_t adesc0 = A_MN ? make_smem_desc_sw128(sa, 64 * BK * 2, 1024)
-                                         : make_smem_desc_sw128(sa, 16, 1024);
-            const uint64_t bdesc0 = B_MN ? make_smem_desc_sw128(sb, 64 * BK * 2, 1024)
-                                         : make_smem_desc_sw128(sb, 16, 1024);
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+          const uint64_t adesc0 = A_MN ? make_smem_desc_sw128(sa, 64 * BK * 2, 1024)
+                                       : make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc0 = B_MN ? make_smem_desc_sw128(sb, 64 * BK * 2, 1024)
+                                       : make_smem_desc_sw128(sb, 16, 1024);
+          if (!probe_no_mma) {
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               const uint64_t adesc = adesc0 + (A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
               const uint64_t bdesc = bdesc0 + (B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
               umma_f16_ss_pair(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
             }
-            // free this stage in both CTAs
-            const uint32_t eb = smem_u32(&empty_bar[stage]);
-            umma_commit_pair(eb);
-            umma_commit_pair(mapa_u32(eb, 1));
-            if (kb == kb1 - 1) {
-              const uint32_t fb = smem_u32(&tmem_full[acc]);
-              umma_commit_pair(fb);
-              umma_commit_pair(mapa_u32(fb, 1));
-            }
           }
-          __syncwarp();
+          // free this stage in both CTAs
+          umma_commit_pair_mc(smem_u32(&empty_bar[stage]), 3);
+          if (kb == kb1 - 1) umma_commit_pair_mc(smem_u32(&tmem_full[acc]), 3);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -419,7 +431,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         for (int c = 0; c < BN && ok; c += 64, ++group) {
           const int col0 = tn * BN + c;
           if (col0 >= p.N) break;
-          uint8_t* s0 = wstage + (group & 1) * (2 * kSlotBytes);
+          uint8_t* s0 = wstage + (group & 1) * ((kSlotsPerWarp / 2) * kSlotBytes);
           uint8_t* s1 = s0 + kSlotBytes;
           // the slots of this set were last read by the store group issued two groups ago
           if (lane == 0) tma_store_wait_read<1>();

@@ -157,53 +157,52 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = make_idesc_bf16_f32(BM, BN, A_MN, B_MN);
+    // One thread runs the loop: wait for a stage, issue its MMAs, release it with a commit.  The
+    // operands arrive through the async proxy, so the k-loop needs no tcgen05 fence; the fence after a
+    // thread synchronisation belongs where the epilogue warps hand an accumulator back.
     int stage = 0;
     uint32_t phase = 0;
-    uint32_t acc_phase[2] = {0, 0};
+    uint32_t acc_phase0 = 0, acc_phase1 = 0;
     int local = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+    for (int t = blockIdx.x; t < total_tiles && ok && lane == 0; t += gridDim.x, ++local) {
       int tm, tn, kb0, kb1;
       decode_tile(t, tm, tn, kb0, kb1);
       const int acc = local & 1;
       if (kb1 <= kb0) continue;  // empty K-split: mirrors the epilogue's skip
       // Wait until the epilogue has drained this accumulator (first use passes immediately).
-      if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1) || *abort_flag) {
-        if (lane == 0) atomicCAS(p.err, 0, 102);
+      const uint32_t ap = acc ? acc_phase1 : acc_phase0;
+      if (!mbar_wait(&tmem_empty[acc], ap ^ 1) || *abort_flag) {
+        atomicCAS(p.err, 0, 102);
         *abort_flag = 1;
-        ok = false;
         break;
       }
-      acc_phase[acc] ^= 1;
+      if (acc) acc_phase1 ^= 1; else acc_phase0 ^= 1;
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + acc * BN;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(&full_bar[stage], phase) || *abort_flag) {
-          if (lane == 0) atomicCAS(p.err, 0, 103);
+        if (!mbar_wait(&full_bar[stage], phase)) {
+          atomicCAS(p.err, 0, 103);
           *abort_flag = 1;
           ok = false;
           break;
         }
-        tc_fence_after_sync();
-        if (lane == 0) {
-          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
-          const uint32_t sb = sa + L::kABytes;
-          const uint64_t adesc0 = A_MN ? make_smem_desc_sw128(sa, 64 * BK * 2, 1024)
-                                       : make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc0 = B_MN ? make_smem_desc_sw128(sb, 64 * BK * 2, 1024)
-                                       : make_smem_desc_sw128(sb, 16, 1024);
+        const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+        const uint32_t sb = sa + L::kABytes;
+        const uint64_t adesc0 = A_MN ? make_smem_desc_sw128(sa, 64 * BK * 2, 1024)
+                                     : make_smem_desc_sw128(sa, 16, 1024);
+        const uint64_t bdesc0 = B_MN ? make_smem_desc_sw128(sb, 64 * BK * 2, 1024)
+                                     : make_smem_desc_sw128(sb, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            // K-major: 16 elements = 32 bytes along the swizzled row.
-            // MN-major: 16 k-rows = 2 groups of 8 rows x 128 bytes = 2048 bytes.
-            const uint64_t adesc = adesc0 + (A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
-            const uint64_t bdesc = bdesc0 + (B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
-            umma_f16_ss(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-          }
-          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
-          if (kb == kb1 - 1) umma_commit(&tmem_full[acc]);
+        for (int k = 0; k < BK / 16; ++k) {
+          // K-major: 16 elements = 32 bytes along the swizzled row.
+          // MN-major: 16 k-rows = 2 groups of 8 rows x 128 bytes = 2048 bytes.
+          const uint64_t adesc = adesc0 + (A_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+          const uint64_t bdesc = bdesc0 + (B_MN ? (k * 2048) >> 4 : (k * 32) >> 4);
+          umma_f16_ss(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
         }
-        __syncwarp();
+        umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+        if (kb == kb1 - 1) umma_commit(&tmem_full[acc]);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1;

@@ -21,6 +21,11 @@ enum {
   kGemmResidual = 16,  // + residual[m,n] (same dtype as C)
   kGemmGeluDual = 32,  // C = h (bf16), C2 = gelu_tanh(h) (bf16)
   kGemmDGelu = 64,     // C = (A*B) * gelu_tanh'(aux[m,n])
+  // Timing probes of the CTA-pair pipeline (results are meaningless): the same launch with the
+  // operand loads left out (the MMA warp finds every stage "full" at once: issue rate + shared-memory
+  // reads of the tensor core alone) or with the MMAs left out (TMA fill rate of the ring alone).
+  kGemmProbeNoLoad = 1 << 20,
+  kGemmProbeNoMma = 1 << 21,
 };
 
 typedef struct {

@@ -92,6 +92,30 @@ def bench_gemm_llama_tp8(C):
     bench_gemm(C, tokens=2048, layers=((768, 4096), (4096, 512), (1792, 4096), (4096, 1792), (16032, 4096)))
 
 
+def bench_gemm_probe(C):
+    """Where the CTA-pair GEMM's main loop spends its time: the full kernel against the same launch
+    without operand loads (tensor-core issue + shared-memory reads alone) and without MMAs (TMA fill
+    of the ring alone).  The probe launches compute nothing meaningful; only their times are read."""
+    timeit = _timer()
+    for M, N, K in ((8192, 8192, 8192), (16384, 2304, 768), (2048, 16032, 4096)):
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        res = {"case": "gemm_probe", "M": M, "N": N, "K": K}
+        probes = (("full", 0), ("no_load", C.GEMM_PROBE_NO_LOAD), ("no_mma", C.GEMM_PROBE_NO_MMA),
+                  ("neither", C.GEMM_PROBE_NO_LOAD | C.GEMM_PROBE_NO_MMA))
+        for name, fl in probes:
+            t = timeit(lambda: C.gemm(a, False, b, False, M, N, K, c, None, None, None, None, fl, 0))
+            res[name + "_us"] = t * 1e3
+        res["cublas_us"] = timeit(lambda: torch.matmul(a, b.t(), out=c)) * 1e3
+        # per k-block of 64 and CTA pair, in SM cycles at the nominal 1.965 GHz
+        kblocks = ((M + 255) // 256) * ((N + 255) // 256) * (K // 64) / 74.0
+        for name, _ in probes:
+            res[name + "_cycles_per_kblock"] = res[name + "_us"] * 1965.0 / kblocks
+        res["status"] = C.kernel_status()
+        print(json.dumps(res))
+
+
 def bench_attention(C):
     timeit = _timer()
     default = C.get_attn_mode()
@@ -203,7 +227,7 @@ def main(argv):
     C = _ext.load(required=True)
     torch.manual_seed(0)
     case = argv[1] if len(argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "gemm_llama_tp8": bench_gemm_llama_tp8, "attention": bench_attention, "profile": profile_case,
+    {"gemm": bench_gemm, "gemm_llama_tp8": bench_gemm_llama_tp8, "gemm_probe": bench_gemm_probe, "attention": bench_attention, "profile": profile_case,
      "tp": bench_tp}[case](C)
     return 0
 

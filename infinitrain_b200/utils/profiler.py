@@ -1,13 +1,26 @@
 """Profiler: per-kernel host / device time and peak memory, per-tag reports, NVTX ranges and a
 Chrome-trace export.
 
-Reference: infini_train/src/profiler.cc:41-313 (compile-time PROFILE_MODE; every kernel call is
-bracketed by stream synchronisation, device time from events, mem-pool peak; per-rank report and
-record files).  Here profiling is a runtime switch: ``Profiler.Instance().Enable()`` wraps the
-fused ops of :mod:`ops.functional` (and collectives recorded through ``RecordRange``); records carry
-the current tag (``SetTag("Step_9")``); ``Report`` prints the reference's table (count, host µs,
-device µs, averages, peak MB) sortable by seven keys; ``ExportChromeTrace`` writes a timeline
-the reference cannot produce.
+Reference: infini_train/src/profiler.cc:41-313 and include/dispatcher.h:22-43 (compile-time
+PROFILE_MODE; every dispatched kernel, forward and backward, is bracketed by stream synchronisation,
+device time from events, mem-pool peak; per-rank report and record files; collectives are not seen).
+Here profiling is a runtime switch.  ``Profiler.Instance().Enable()`` brackets
+
+* every launch entry point of the native extension (``gemm``, ``flash_attn_fwd / _bwd``,
+  ``layernorm_fwd / _bwd``, ``adamw``, ..., and the fused NVLink kernels ``tp_gemm``,
+  ``nvl_allreduce_scale``, ``nvl_rs_adamw_bcast``, ``nvl_ce_merge``), whoever calls it -- the forward
+  wrappers, the ``autograd.Function.backward``s (records made while autograd runs a backward pass are
+  named ``<entry>[bwd]``), the optimizers, the reducer;
+* every collective of ``ProcessGroup`` (``AllReduce``, ``AllGather``, ``ReduceScatter``, ``Send``,
+  ``Recv``, ``BroadCast``, ``Barrier``), named ``pg.<Collective>(<group>)``;
+
+each with a host time, a device time (events on the stream the launch goes to, so kernels on the
+communication side stream are timed there) and an NVTX range.  ``Enable(level="op")`` records the
+ten fused forward ops as units instead (their inner launches are then nested and not listed).
+Records carry the current tag (``SetTag("Step_9")``); ``Report`` prints the reference's table (count,
+host us, device us, averages, peak MB) sortable by seven keys; ``ExportChromeTrace`` writes a timeline
+the reference cannot produce.  Like the reference's profile build, an enabled profiler serialises
+the step: its numbers are shares, not a benchmark.
 """
 from __future__ import annotations
 
@@ -42,7 +55,8 @@ class Profiler:
         self.records: List[ProfileRecord] = []
         self.tag = "Untagged"
         self.depth = 0
-        self._orig = {}
+        self.level = "kernel"
+        self._orig = []
         self._t0 = time.perf_counter()
 
     @classmethod
@@ -89,29 +103,67 @@ class Profiler:
                                               (t0 - self._t0) * 1e6))
             self.depth -= 1
 
-    def Enable(self):
+    # entry points of the native extension that launch kernels (everything else in the module is a
+    # query or a mode switch)
+    kNativeLaunchers = ("gemm", "layernorm_fwd", "layernorm_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "gelu_fwd", "gelu_bwd",
+                        "swiglu_fwd", "swiglu_bwd", "rope_inplace", "embedding_fwd", "embedding_bwd", "ce_fwd", "ce_bwd",
+                        "adamw", "adam_advance", "sgd", "cast_into", "colsum", "flash_attn_fwd", "flash_attn_bwd",
+                        "nvl_allreduce_scale", "nvl_rs_adamw_bcast", "nvl_ce_merge", "tp_gemm", "tp_wait")
+    kCollectives = ("AllReduce", "AllGather", "ReduceScatter", "Send", "Recv", "BroadCast", "Barrier")
+    kForwardOps = ("linear", "mlp_gelu", "layernorm", "rmsnorm", "gelu", "swiglu", "swiglu_packed", "attention_packed",
+                   "embedding", "cross_entropy")
+
+    @staticmethod
+    def _in_backward() -> bool:
+        try:
+            return torch._C._current_graph_task_id() != -1
+        except Exception:  # noqa: BLE001
+            return False
+
+    def _wrap(self, owner, attr: str, label):
+        orig = getattr(owner, attr)
+        self._orig.append((owner, attr, orig))
+
+        def wrapped(*a, _orig=orig, **k):
+            name = label(a) if callable(label) else label
+            if self._in_backward():
+                name += "[bwd]"
+            with self.RecordRange(name):
+                return _orig(*a, **k)
+
+        setattr(owner, attr, wrapped)
+
+    def Enable(self, level: str = "kernel"):
+        """``level="kernel"`` (default): every native launch and every collective is a record.
+        ``level="op"``: the fused forward ops are the records (what they launch inside is nested)."""
+        from .. import _ext
         from ..ops import functional as ops
+        from ..parallel.process_group import ProcessGroup
 
         if self.enabled:
             return
+        if level not in ("kernel", "op"):
+            raise ValueError("profiler level must be 'kernel' or 'op'")
         self.enabled = True
-        for fname in ("linear", "mlp_gelu", "layernorm", "rmsnorm", "gelu", "swiglu", "swiglu_packed",
-                      "attention_packed", "embedding", "cross_entropy"):
-            orig = getattr(ops, fname)
-            self._orig[fname] = orig
-
-            def wrapped(*a, _orig=orig, _n=fname, **k):
-                with self.RecordRange(_n):
-                    return _orig(*a, **k)
-
-            setattr(ops, fname, wrapped)
+        self.level = level
+        self._orig = []
+        if level == "op":
+            for fname in self.kForwardOps:
+                self._wrap(ops, fname, fname)
+        C = _ext.load(required=False)
+        if C is not None:
+            for fname in self.kNativeLaunchers:
+                if hasattr(C, fname):
+                    self._wrap(C, fname, fname)
+        for cname in self.kCollectives:
+            if hasattr(ProcessGroup, cname):
+                self._wrap(ProcessGroup, cname,
+                           lambda a, _c=cname: f"pg.{_c}({getattr(a[0], 'name', '?')})" if a else f"pg.{_c}")
 
     def Disable(self):
-        from ..ops import functional as ops
-
-        for fname, orig in self._orig.items():
-            setattr(ops, fname, orig)
-        self._orig = {}
+        for owner, attr, orig in reversed(self._orig):
+            setattr(owner, attr, orig)
+        self._orig = []
         self.enabled = False
 
     def Reset(self):

@@ -70,7 +70,7 @@ def world(tmp_path_factory):
     write_token_file(str(d / "tokens.bin"), ids.tolist())
     common = ["--llmc_filepath", "model.bin", "--input_bin", "tokens.bin", "--batch_size", str(B), "--sequence_length",
               str(T), "--total_batch_size", str(B * T), "--num_iteration", str(kSteps), "--dtype", "bfloat16",
-              "--learning_rate", "0.02"]
+              "--learning_rate", "0.003"]
     env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "OMP_NUM_THREADS")}
     ref, log = _run([BIN, *common, "--model", "gpt2", "--device", "cuda", "--nthread_per_process", "1",
                      "--overfit_single_batch=false", "--freq_generate_txt", "1000000"], d, env)

@@ -68,10 +68,66 @@ def test_precision_checker_simple_md5_npy(tmp_path):
     assert ComputeMD5(torch.tensor([0.5, -0.5, 2.5]), 1.0) == ComputeMD5(torch.tensor([1.0, -1.0, 3.0]), 1.0)
 
 
+def test_profiler_records_backward_launches_and_collectives(tmp_path):
+    """Kernel level: every native launch entry point is bracketed wherever it is called from (records
+    made while autograd runs a backward pass carry ``[bwd]``), and so is every ProcessGroup collective."""
+    from infinitrain_b200 import _ext
+    from infinitrain_b200.parallel.process_group import ProcessGroup
+
+    C = _ext.load(required=False)
+    if C is None:
+        pytest.skip("native extension not available")
+    p = Profiler.Instance()
+    p.Reset()
+    calls = []
+    saved = {n: getattr(C, n) for n in ("gemm", "layernorm_bwd")}
+    saved_pg = ProcessGroup.AllReduce
+    try:
+        # stand-ins for the launchers (no GPU here): the profiler must wrap whatever the module exposes
+        C.gemm = lambda *a, **k: calls.append("gemm")
+        C.layernorm_bwd = lambda *a, **k: calls.append("layernorm_bwd")
+        ProcessGroup.AllReduce = lambda self, t, *a, **k: calls.append("allreduce")
+        p.Enable()
+        p.SetTag("Step_3")
+
+        class Fn(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, x):
+                C.gemm(x)
+                return x * 2
+
+            @staticmethod
+            def backward(ctx, g):
+                C.gemm(g)
+                C.layernorm_bwd(g)
+                return g * 2
+
+        x = torch.ones(3, requires_grad=True)
+        Fn.apply(x).sum().backward()
+
+        class FakeGroup(ProcessGroup):
+            def __init__(self):
+                self.name = "DP0"
+
+        FakeGroup().AllReduce(torch.ones(2))
+    finally:
+        p.Disable()
+        assert C.gemm is not saved["gemm"]           # Disable restored the stand-ins, not the originals
+        for n, f in saved.items():
+            setattr(C, n, f)
+        ProcessGroup.AllReduce = saved_pg
+    assert calls == ["gemm", "gemm", "layernorm_bwd", "allreduce"]
+    names = [r.name for r in p.records]
+    assert names == ["gemm", "gemm[bwd]", "layernorm_bwd[bwd]", "pg.AllReduce(DP0)"], names
+    rep = p.Report(None, "Count")
+    assert "gemm[bwd]" in rep and "pg.AllReduce(DP0)" in rep and "Tag: Step_3" in rep
+    p.Reset()
+
+
 def test_profiler_report_and_trace(tmp_path):
     p = Profiler.Instance()
     p.Reset()
-    p.Enable()
+    p.Enable(level="op")
     try:
         p.SetTag("Step_0")
         nn.Linear(8, 8)(torch.randn(2, 8))
