@@ -140,23 +140,43 @@ std::vector<at::Tensor> layernorm_fwd(const at::Tensor& x, const at::Tensor& gam
            "layernorm_fwd");
   return {y, mean, rstd};
 }
+// dres (optional): gradient of the residual stream past the norm, added to dx in the same pass;
+// dgamma_out / dbeta_out / dres_sum_out (optional fp32 [C]): gradients are ACCUMULATED into these
+// tensors (views of a flat gradient buffer) instead of being returned; want_dres_sum without an
+// output tensor returns the column sums of dres as a fresh tensor.
 std::vector<at::Tensor> layernorm_bwd(const at::Tensor& dy, const at::Tensor& x,
                                       const at::Tensor& gamma, const at::Tensor& mean,
-                                      const at::Tensor& rstd, bool has_beta) {
+                                      const at::Tensor& rstd, bool has_beta,
+                                      const c10::optional<at::Tensor>& dres,
+                                      const c10::optional<at::Tensor>& dgamma_out,
+                                      const c10::optional<at::Tensor>& dbeta_out,
+                                      const c10::optional<at::Tensor>& dres_sum_out, bool want_dres_sum) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous() && dy.is_contiguous(), "layernorm_bwd: contiguous tensors required");
   const int C = x.size(-1);
   const int rows = x.numel() / C;
   auto dx = torch::empty_like(x);
-  auto dgamma = torch::empty({C}, x.options().dtype(at::kFloat));
-  auto dbeta = torch::empty({C}, x.options().dtype(at::kFloat));
-  auto partial = torch::empty({itb_norm_partial_rows(rows), 2 * C}, x.options().dtype(at::kFloat));
-  check_rc(itb_layernorm_bwd(dy.data_ptr(), dt(dy), x.data_ptr(), dt(x), gamma.data_ptr<float>(),
-                             mean.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr(), dt(dx),
-                             dgamma.data_ptr<float>(), dbeta.data_ptr<float>(),
-                             partial.data_ptr<float>(), rows, C, 0, cur_stream()),
+  if (dres) TORCH_CHECK(dres->is_contiguous() && dres->scalar_type() == dx.scalar_type() && dres->numel() == x.numel(),
+                        "layernorm_bwd: dres must match dx");
+  int acc = 0;
+  auto f32 = x.options().dtype(at::kFloat);
+  at::Tensor dgamma = dgamma_out ? *dgamma_out : torch::empty({C}, f32);
+  at::Tensor dbeta = dbeta_out ? *dbeta_out : torch::empty({C}, f32);
+  at::Tensor dsum;
+  if (dres && (dres_sum_out || want_dres_sum)) dsum = dres_sum_out ? *dres_sum_out : torch::empty({C}, f32);
+  if (dgamma_out) acc |= 1;
+  if (dbeta_out) acc |= 2;
+  if (dres_sum_out) acc |= 4;
+  for (const at::Tensor* t : {&dgamma, &dbeta})
+    TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == C, "layernorm_bwd: fp32 [C] outputs");
+  auto partial = torch::empty({itb_norm_partial_rows(rows), 3 * C}, f32);
+  check_rc(itb_layernorm_bwd_res(dy.data_ptr(), dt(dy), x.data_ptr(), dt(x), gamma.data_ptr<float>(),
+                                 mean.data_ptr<float>(), rstd.data_ptr<float>(), dres ? dres->data_ptr() : nullptr,
+                                 dx.data_ptr(), dt(dx), dgamma.data_ptr<float>(), dbeta.data_ptr<float>(),
+                                 dsum.defined() ? dsum.data_ptr<float>() : nullptr, partial.data_ptr<float>(), rows, C,
+                                 acc, cur_stream()),
            "layernorm_bwd");
-  return {dx, dgamma, dbeta};
+  return {dx, dgamma, dbeta, dsum};
 }
 std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& gamma, double eps,
                                     at::ScalarType out_dtype) {
@@ -172,19 +192,30 @@ std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& gamma
   return {y, rstd};
 }
 std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x,
-                                    const at::Tensor& gamma, const at::Tensor& rstd) {
+                                    const at::Tensor& gamma, const at::Tensor& rstd,
+                                    const c10::optional<at::Tensor>& dres,
+                                    const c10::optional<at::Tensor>& dgamma_out,
+                                    const c10::optional<at::Tensor>& dres_sum_out, bool want_dres_sum) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous() && dy.is_contiguous(), "rmsnorm_bwd: contiguous tensors required");
   const int C = x.size(-1);
   const int rows = x.numel() / C;
   auto dx = torch::empty_like(x);
-  auto dgamma = torch::empty({C}, x.options().dtype(at::kFloat));
-  auto partial = torch::empty({itb_norm_partial_rows(rows), 2 * C}, x.options().dtype(at::kFloat));
-  check_rc(itb_rmsnorm_bwd(dy.data_ptr(), dt(dy), x.data_ptr(), dt(x), gamma.data_ptr<float>(),
-                           rstd.data_ptr<float>(), dx.data_ptr(), dt(dx), dgamma.data_ptr<float>(),
-                           partial.data_ptr<float>(), rows, C, 0, cur_stream()),
+  if (dres) TORCH_CHECK(dres->is_contiguous() && dres->scalar_type() == dx.scalar_type() && dres->numel() == x.numel(),
+                        "rmsnorm_bwd: dres must match dx");
+  auto f32 = x.options().dtype(at::kFloat);
+  at::Tensor dgamma = dgamma_out ? *dgamma_out : torch::empty({C}, f32);
+  TORCH_CHECK(dgamma.scalar_type() == at::kFloat && dgamma.is_contiguous() && dgamma.numel() == C, "rmsnorm_bwd: fp32 [C] output");
+  at::Tensor dsum;
+  if (dres && (dres_sum_out || want_dres_sum)) dsum = dres_sum_out ? *dres_sum_out : torch::empty({C}, f32);
+  const int acc = (dgamma_out ? 1 : 0) | (dres_sum_out ? 4 : 0);
+  auto partial = torch::empty({itb_norm_partial_rows(rows), 3 * C}, f32);
+  check_rc(itb_rmsnorm_bwd_res(dy.data_ptr(), dt(dy), x.data_ptr(), dt(x), gamma.data_ptr<float>(),
+                               rstd.data_ptr<float>(), dres ? dres->data_ptr() : nullptr, dx.data_ptr(), dt(dx),
+                               dgamma.data_ptr<float>(), dsum.defined() ? dsum.data_ptr<float>() : nullptr,
+                               partial.data_ptr<float>(), rows, C, acc, cur_stream()),
            "rmsnorm_bwd");
-  return {dx, dgamma};
+  return {dx, dgamma, dsum};
 }
 
 // ------------------------------------------------------------------ activations
@@ -346,14 +377,17 @@ void cast_into(const at::Tensor& src, at::Tensor& dst) {
   check_rc(itb_cast(src.data_ptr(), dt(src), dst.data_ptr(), dt(dst), src.numel(), cur_stream()),
            "cast");
 }
-at::Tensor colsum(const at::Tensor& x) {
+// Column sums of a [rows, N] matrix; with `into` (fp32 [N]) the sums are ADDED to that tensor (a view
+// of a flat gradient buffer) and it is returned.
+at::Tensor colsum(const at::Tensor& x, const c10::optional<at::Tensor>& into) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "colsum: 2-D row-major input");
   const int rows = x.size(0), N = x.size(1);
-  auto out = torch::empty({N}, x.options().dtype(at::kFloat));
+  at::Tensor out = into ? *into : torch::empty({N}, x.options().dtype(at::kFloat));
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == N, "colsum: fp32 [N] output");
   auto partial = torch::empty({itb_colsum_partial_rows(rows), N}, x.options().dtype(at::kFloat));
   check_rc(itb_colsum(x.data_ptr(), dt(x), x.stride(0), out.data_ptr<float>(),
-                      partial.data_ptr<float>(), rows, N, 0, cur_stream()),
+                      partial.data_ptr<float>(), rows, N, into ? 1 : 0, cur_stream()),
            "colsum");
   return out;
 }
@@ -460,9 +494,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("get_attn_mode", &get_attn_mode);
   m.def("get_gemm_mode", &get_gemm_mode);
   m.def("layernorm_fwd", &layernorm_fwd);
-  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("layernorm_bwd", &layernorm_bwd, pybind11::arg("dy"), pybind11::arg("x"), pybind11::arg("gamma"),
+        pybind11::arg("mean"), pybind11::arg("rstd"), pybind11::arg("has_beta"), pybind11::arg("dres") = pybind11::none(),
+        pybind11::arg("dgamma_out") = pybind11::none(), pybind11::arg("dbeta_out") = pybind11::none(),
+        pybind11::arg("dres_sum_out") = pybind11::none(), pybind11::arg("want_dres_sum") = false);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, pybind11::arg("dy"), pybind11::arg("x"), pybind11::arg("gamma"), pybind11::arg("rstd"),
+        pybind11::arg("dres") = pybind11::none(), pybind11::arg("dgamma_out") = pybind11::none(),
+        pybind11::arg("dres_sum_out") = pybind11::none(), pybind11::arg("want_dres_sum") = false);
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);
@@ -479,7 +518,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adam_advance", &adam_advance);
   m.def("sgd", &sgd);
   m.def("cast_into", &cast_into);
-  m.def("colsum", &colsum);
+  m.def("colsum", &colsum, pybind11::arg("x"), pybind11::arg("into") = pybind11::none());
   m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("flash_attn_bwd", &flash_attn_bwd);
   bind_comm(m);

@@ -214,7 +214,7 @@ struct LayerNormFn : public torch::autograd::Function<LayerNormFn> {
     int64_t C = x.size(-1), rows = x.numel() / C;
     Tensor dx = torch::empty_like(x);
     Tensor dg = torch::empty({C}, gamma.options().requires_grad(false)), db = torch::empty_like(dg);
-    Tensor partial = torch::empty({itb_norm_partial_rows(static_cast<int>(rows)), 2 * C}, dg.options());
+    Tensor partial = torch::empty({itb_norm_partial_rows(static_cast<int>(rows)), 3 * C}, dg.options());
     check(itb_layernorm_bwd(dy.data_ptr(), code(dy), x.data_ptr(), code(x), gamma.data_ptr<float>(), mean.data_ptr<float>(),
                             rstd.data_ptr<float>(), dx.data_ptr(), code(dx), dg.data_ptr<float>(), db.data_ptr<float>(),
                             partial.data_ptr<float>(), static_cast<int>(rows), static_cast<int>(C), 0, stream()),
@@ -243,7 +243,7 @@ struct RMSNormFn : public torch::autograd::Function<RMSNormFn> {
     if (dy.scalar_type() == torch::kFloat32 && x.scalar_type() == torch::kBFloat16) dy = dy.to(torch::kBFloat16);
     int64_t C = x.size(-1), rows = x.numel() / C;
     Tensor dx = torch::empty_like(x), dg = torch::empty({C}, gamma.options().requires_grad(false));
-    Tensor partial = torch::empty({itb_norm_partial_rows(static_cast<int>(rows)), 2 * C}, dg.options());
+    Tensor partial = torch::empty({itb_norm_partial_rows(static_cast<int>(rows)), 3 * C}, dg.options());
     check(itb_rmsnorm_bwd(dy.data_ptr(), code(dy), x.data_ptr(), code(x), gamma.data_ptr<float>(), rstd.data_ptr<float>(),
                           dx.data_ptr(), code(dx), dg.data_ptr<float>(), partial.data_ptr<float>(), static_cast<int>(rows),
                           static_cast<int>(C), 0, stream()), "rmsnorm_bwd");

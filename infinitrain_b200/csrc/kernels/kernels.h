@@ -59,18 +59,30 @@ int itb_layernorm_fwd(const void* x, int x_dtype, const float* gamma, const floa
                       int y_dtype, float* mean, float* rstd, int rows, int C, float eps,
                       cudaStream_t stream);
 // dx = LN'(dy); dgamma/dbeta are reduced in two stages through `partial` (fp32,
-// [itb_norm_partial_rows(rows), 2*C]) and ADDED to dgamma/dbeta when accumulate != 0.
+// [itb_norm_partial_rows(rows), 3*C]) and ADDED to dgamma/dbeta when accumulate != 0.
 int itb_norm_partial_rows(int rows);
 int itb_layernorm_bwd(const void* dy, int dy_dtype, const void* x, int x_dtype, const float* gamma,
                       const float* mean, const float* rstd, void* dx, int dx_dtype, float* dgamma,
                       float* dbeta, float* partial, int rows, int C, int accumulate,
                       cudaStream_t stream);
+// The norm on a residual stream: dx = LN'(dy) + dres, where dres (dtype of dx) is the gradient that
+// reaches the stream past the norm; when dres_sum is not null, dres_sum[c] (+)= sum over rows of
+// dres (the bias gradient of the projection that wrote into the stream).  `accumulate` is a bit mask:
+// bit 0 dgamma, bit 1 dbeta, bit 2 dres_sum are added to instead of overwritten.
+int itb_layernorm_bwd_res(const void* dy, int dy_dtype, const void* x, int x_dtype, const float* gamma,
+                          const float* mean, const float* rstd, const void* dres, void* dx, int dx_dtype,
+                          float* dgamma, float* dbeta, float* dres_sum, float* partial, int rows, int C,
+                          int accumulate, cudaStream_t stream);
 // y = x * rsqrt(mean(x^2) + eps) * gamma
 int itb_rmsnorm_fwd(const void* x, int x_dtype, const float* gamma, void* y, int y_dtype,
                     float* rstd, int rows, int C, float eps, cudaStream_t stream);
 int itb_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int x_dtype, const float* gamma,
                     const float* rstd, void* dx, int dx_dtype, float* dgamma, float* partial,
                     int rows, int C, int accumulate, cudaStream_t stream);
+int itb_rmsnorm_bwd_res(const void* dy, int dy_dtype, const void* x, int x_dtype, const float* gamma,
+                        const float* rstd, const void* dres, void* dx, int dx_dtype, float* dgamma,
+                        float* dres_sum, float* partial, int rows, int C, int accumulate,
+                        cudaStream_t stream);
 
 // ------------------------------------------------------------------ activations
 // tanh-GELU and SiLU-gated product on bf16 or fp32 tensors of n elements.

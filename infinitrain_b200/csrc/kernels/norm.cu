@@ -166,147 +166,246 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ gamma,
   }
 }
 
+// Eight consecutive elements as they come out of one or two 16-byte loads, kept packed in registers
+// (a bf16 chunk costs 4 registers instead of 8) and unpacked where they are used.
+template <typename T>
+struct Raw8;
+template <>
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = *reinterpret_cast<const float4*>(p);
+    b = *reinterpret_cast<const float4*>(p + 4);
+  }
+  __device__ __forceinline__ void unpack(float (&v)[8]) const {
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+template <>
+struct Raw8<__nv_bfloat16> {
+  uint4 u;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void unpack(float (&v)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+};
+
 // Backward.  With xhat = (x - mean) * rstd and g = dy * gamma:
 //   LayerNorm: dx = rstd * (g - mean_C(g) - xhat * mean_C(g * xhat))
 //   RMSNorm:   dx = rstd * (g - xhat * mean_C(g * xhat))                    (mean = 0)
-// dgamma += dy * xhat, dbeta += dy, accumulated per block in shared memory (fp32 atomics on shared
-// memory only), then written as one partial row per block.
-template <typename TDY, typename TX, typename TDX, bool kRms, int kMaxVec>
-__global__ void __launch_bounds__(kNormThreads)
+// One pass over the row: dy and x stay (packed) in registers between the statistics and the output.
+// kRes: the norm sits on a residual stream, out = dx + dres where dres is the gradient that reaches
+// the stream past the norm (the skip connection); its column sums come out as a third partial row
+// (they are the bias gradient of the projection that wrote into the stream).
+//
+// kWide = false: one warp per row (rows up to 1024 wide), kChunks chunks of 8 per lane.
+// kWide = true:  the whole block works on one row at a time (rows up to kChunks * 1024 wide); the two
+//                row statistics cross the warps through a double-buffered shared-memory slot, one
+//                __syncthreads per row.
+// dgamma += dy * xhat, dbeta += dy and the dres sums live in per-lane registers over all rows a block
+// handles and leave as ONE partial row of 3 C per block, without atomics: in the warp-per-row layout
+// the warps add their registers to a shared-memory row in turns; in the wide layout every thread owns
+// its columns.
+template <typename TDY, typename TX, typename TDX, bool kRms, int kChunks, bool kRes, bool kWide>
+__global__ void __launch_bounds__(kNormThreads, kWide ? 4 : 3)
 norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
                 const float* __restrict__ gamma, const float* __restrict__ mean_in,
-                const float* __restrict__ rstd_in, TDX* __restrict__ dx,
-                float* __restrict__ partial, int rows, int C) {
-  extern __shared__ float sh[];  // [2*C]: dgamma | dbeta (dbeta unused for RMSNorm)
+                const float* __restrict__ rstd_in, const TDX* __restrict__ dres,
+                TDX* __restrict__ dx, float* __restrict__ partial, int rows, int C) {
+  extern __shared__ float sh[];  // warp-per-row: [3*C] combine row; wide: [2][kNormWarps][2] statistics
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = C / 8;
-  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sh[i] = 0.f;
-  __syncthreads();
-  // Per-lane register accumulators for the first kMaxVec chunks: summed over this warp's rows,
-  // flushed to shared memory once at the end.
-  float acc_g[kMaxVec][8], acc_b[kMaxVec][8];
+  // chunk i of this thread covers elements [8 * vi(i), 8 * vi(i) + 8) of a row
+  auto vi_of = [&](int i) { return kWide ? static_cast<int>(threadIdx.x) + i * kNormThreads : lane + i * 32; };
+  float gam[kChunks][8];
+  float acc_g[kChunks][8], acc_b[kRms ? 1 : kChunks][8], acc_r[kRes ? kChunks : 1][8];
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i)
+  for (int i = 0; i < kChunks; ++i) {
+    const int vi = vi_of(i);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc_g[i][e] = acc_b[i][e] = 0.f;
-
-  for (int row = blockIdx.x * kNormWarps + warp; row < rows; row += gridDim.x * kNormWarps) {
+    for (int e = 0; e < 8; ++e) {
+      gam[i][e] = vi < nvec ? gamma[vi * 8 + e] : 0.f;
+      acc_g[i][e] = 0.f;
+      if (!kRms) acc_b[i][e] = 0.f;
+      if (kRes) acc_r[i][e] = 0.f;
+    }
+  }
+  const int row_step = kWide ? static_cast<int>(gridDim.x) : static_cast<int>(gridDim.x) * kNormWarps;
+  int parity = 0;
+  for (int row = kWide ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) * kNormWarps + warp;
+       row < rows; row += row_step) {
     const TDY* dyr = dy + static_cast<long long>(row) * C;
     const TX* xr = x + static_cast<long long>(row) * C;
+    const TDX* rr = kRes ? dres + static_cast<long long>(row) * C : nullptr;
     TDX* dxr = dx + static_cast<long long>(row) * C;
+    // every load of the row is issued before anything waits on one
+    Raw8<TDY> rd[kChunks];
+    Raw8<TX> rx[kChunks];
+    Raw8<TDX> rres[kRes ? kChunks : 1];
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+      const int vi = vi_of(i);
+      if (vi < nvec) {
+        rd[i].load(dyr + vi * 8);
+        rx[i].load(xr + vi * 8);
+        if (kRes) rres[i].load(rr + vi * 8);
+      }
+    }
     const float mean = kRms ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      int vi = lane + i * 32;
-      if (vi < nvec) {
-        float d[8], xv[8], g[8];
-        load8<TDY>(dyr + vi * 8, d);
-        load8<TX>(xr + vi * 8, xv);
-        load8<float>(gamma + vi * 8, g);
+    for (int i = 0; i < kChunks; ++i) {
+      if (vi_of(i) < nvec) {
+        float d[8], xv[8];
+        rd[i].unpack(d);
+        rx[i].unpack(xv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          float xhat = (xv[e] - mean) * rstd;
-          float gg = d[e] * g[e];
+          const float xhat = (xv[e] - mean) * rstd;
+          const float gg = d[e] * gam[i][e];
           s1 += gg;
           s2 += gg * xhat;
           acc_g[i][e] += d[e] * xhat;
-          acc_b[i][e] += d[e];
+          if (!kRms) acc_b[i][e] += d[e];
         }
       }
     }
-    for (int vi = lane + kMaxVec * 32; vi < nvec; vi += 32) {
-      float d[8], xv[8], g[8];
-      load8<TDY>(dyr + vi * 8, d);
-      load8<TX>(xr + vi * 8, xv);
-      load8<float>(gamma + vi * 8, g);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        float xhat = (xv[e] - mean) * rstd;
-        float gg = d[e] * g[e];
-        s1 += gg;
-        s2 += gg * xhat;
-        atomicAdd(&sh[vi * 8 + e], d[e] * xhat);
-        if (!kRms) atomicAdd(&sh[C + vi * 8 + e], d[e]);
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (kWide) {
+      float* slot = sh + parity * (2 * kNormWarps);
+      if (lane == 0) {
+        slot[2 * warp] = s1;
+        slot[2 * warp + 1] = s2;
       }
-    }
-    s1 = warp_sum(s1) / C;
-    s2 = warp_sum(s2) / C;
-    if (kRms) s1 = 0.f;
-    // Second pass re-reads the row (it is in L1 / L2 from the first pass) instead of holding it in
-    // registers: the kernel is bound by loads in flight, so occupancy matters more than the re-read.
+      __syncthreads();
+      s1 = s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      int vi = lane + i * 32;
+      for (int w = 0; w < kNormWarps; ++w) {
+        s1 += slot[2 * w];
+        s2 += slot[2 * w + 1];
+      }
+      parity ^= 1;
+    }
+    s1 = kRms ? 0.f : s1 / C;
+    s2 /= C;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i) {
+      const int vi = vi_of(i);
       if (vi < nvec) {
-        float d[8], xv[8], g[8], o[8];
-        load8<TDY>(dyr + vi * 8, d);
-        load8<TX>(xr + vi * 8, xv);
-        load8<float>(gamma + vi * 8, g);
+        float d[8], xv[8], o[8];
+        rd[i].unpack(d);
+        rx[i].unpack(xv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          float xhat = (xv[e] - mean) * rstd;
-          o[e] = rstd * (d[e] * g[e] - s1 - xhat * s2);
+          const float xhat = (xv[e] - mean) * rstd;
+          o[e] = rstd * (d[e] * gam[i][e] - s1 - xhat * s2);
+        }
+        if (kRes) {
+          float r[8];
+          rres[i].unpack(r);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            o[e] += r[e];
+            acc_r[i][e] += r[e];
+          }
         }
         store8<TDX>(dxr + vi * 8, o);
       }
     }
-    for (int vi = lane + kMaxVec * 32; vi < nvec; vi += 32) {
-      float d[8], xv[8], g[8], o[8];
-      load8<TDY>(dyr + vi * 8, d);
-      load8<TX>(xr + vi * 8, xv);
-      load8<float>(gamma + vi * 8, g);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        float xhat = (xv[e] - mean) * rstd;
-        o[e] = rstd * (d[e] * g[e] - s1 - xhat * s2);
-      }
-      store8<TDX>(dxr + vi * 8, o);
-    }
   }
+  float* prow = partial + static_cast<long long>(blockIdx.x) * 3 * C;
+  if (kWide) {
+    // every thread owns its columns: straight to the block's partial row
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    int vi = lane + i * 32;
-    if (vi < nvec) {
+    for (int i = 0; i < kChunks; ++i) {
+      const int vi = vi_of(i);
+      if (vi < nvec) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        atomicAdd(&sh[vi * 8 + e], acc_g[i][e]);
-        if (!kRms) atomicAdd(&sh[C + vi * 8 + e], acc_b[i][e]);
+        for (int e = 0; e < 8; ++e) {
+          prow[vi * 8 + e] = acc_g[i][e];
+          prow[C + vi * 8 + e] = kRms ? 0.f : acc_b[i][e];
+          prow[2 * C + vi * 8 + e] = kRes ? acc_r[i][e] : 0.f;
+        }
       }
     }
+    return;
   }
-  __syncthreads();
-  float* prow = partial + static_cast<long long>(blockIdx.x) * 2 * C;
-  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) prow[i] = sh[i];
+  // warp-per-row: the warps add their registers to the shared row one after the other
+  for (int w = 0; w < kNormWarps; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i) {
+        const int vi = vi_of(i);
+        if (vi < nvec) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int c = vi * 8 + e;
+            sh[c] = (w ? sh[c] : 0.f) + acc_g[i][e];
+            sh[C + c] = kRms ? 0.f : (w ? sh[C + c] : 0.f) + acc_b[i][e];
+            sh[2 * C + c] = kRes ? (w ? sh[2 * C + c] : 0.f) + acc_r[i][e] : 0.f;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < 3 * C; i += blockDim.x) prow[i] = sh[i];
 }
 
-// out[c] (+)= sum_r partial[r, c]: a block of 32 columns x 8 row lanes; the row lanes are combined
-// in shared memory.
-__global__ void __launch_bounds__(256)
+// out[c] (+)= sum_r partial[r, c] for the three column groups of a partial row (dgamma | dbeta | dres
+// sums): a block of 32 columns x 32 row lanes; the row lanes are combined in shared memory.  A null
+// output skips its group; `accumulate` bit k adds to output k instead of overwriting it.
+constexpr int kReduceLanes = 32;   // row lanes of partial_reduce_kernel (block = 32 columns x 32 lanes)
+__global__ void __launch_bounds__(32 * kReduceLanes)
 partial_reduce_kernel(const float* __restrict__ partial, int prow_stride, int nrows,
-                      float* __restrict__ out_a, float* __restrict__ out_b, int C, int accumulate) {
-  __shared__ float sh[8][33];
+                      float* __restrict__ out_a, float* __restrict__ out_b, float* __restrict__ out_c, int C,
+                      int accumulate) {
+  __shared__ float sh[kReduceLanes][33];
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
-  float s = 0.f;
-  if (c < 2 * C)
-    for (int r = ry; r < nrows; r += 8) s += partial[static_cast<long long>(r) * prow_stride + c];
-  sh[ry][cx] = s;
+  const int which = c < C ? 0 : (c < 2 * C ? 1 : 2);
+  float* out = which == 0 ? out_a : (which == 1 ? out_b : out_c);
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < 3 * C && out) {
+    const float* p = partial + c;
+    int r = ry;
+    // four independent loads in flight per thread
+    for (; r + 3 * kReduceLanes < nrows; r += 4 * kReduceLanes) {
+      s0 += p[static_cast<long long>(r) * prow_stride];
+      s1 += p[static_cast<long long>(r + kReduceLanes) * prow_stride];
+      s2 += p[static_cast<long long>(r + 2 * kReduceLanes) * prow_stride];
+      s3 += p[static_cast<long long>(r + 3 * kReduceLanes) * prow_stride];
+    }
+    for (; r < nrows; r += kReduceLanes) s0 += p[static_cast<long long>(r) * prow_stride];
+  }
+  sh[ry][cx] = (s0 + s1) + (s2 + s3);
   __syncthreads();
-  if (ry != 0 || c >= 2 * C) return;
+  if (ry != 0 || c >= 3 * C || !out) return;
   float t = 0.f;
 #pragma unroll
-  for (int r = 0; r < 8; ++r) t += sh[r][cx];
-  float* out = c < C ? out_a : out_b;
-  if (!out) return;
-  const int oc = c < C ? c : c - C;
-  out[oc] = accumulate ? out[oc] + t : t;
+  for (int r = 0; r < kReduceLanes; ++r) t += sh[r][cx];
+  const int oc = c - which * C;
+  out[oc] = ((accumulate >> which) & 1) ? out[oc] + t : t;
 }
 
-static int norm_grid(int rows) {
-  int blocks = (rows + kNormWarps - 1) / kNormWarps;
-  return blocks < kMaxPartialRows ? blocks : kMaxPartialRows;
+// Upper bound of the backward grid for `rows` rows in either layout: what callers size `partial` with.
+static int norm_grid(int rows) { return rows < kMaxPartialRows ? (rows < 1 ? 1 : rows) : kMaxPartialRows; }
+static int norm_bwd_grid(int rows, bool wide, int blocks_per_sm) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int want = wide ? rows : (rows + kNormWarps - 1) / kNormWarps;
+  int cap = sms * blocks_per_sm;
+  if (cap > kMaxPartialRows) cap = kMaxPartialRows;
+  return want < cap ? want : cap;
 }
 
 template <bool kRms>
@@ -337,28 +436,30 @@ static int norm_fwd_dispatch(const void* x, int xd, const float* gamma, const fl
 
 template <bool kRms>
 static int norm_bwd_dispatch(const void* dy, int dyd, const void* x, int xd, const float* gamma,
-                             const float* mean, const float* rstd, void* dx, int dxd,
-                             float* dgamma, float* dbeta, float* partial, int rows, int C,
+                             const float* mean, const float* rstd, const void* dres, void* dx, int dxd,
+                             float* dgamma, float* dbeta, float* dres_sum, float* partial, int rows, int C,
                              int accumulate, cudaStream_t s) {
-  if (C % 8) return -3;
+  if (C % 8 || C > 6144) return -3;
   if (rows < 1) return 0;
-  const int grid = norm_grid(rows);
-  const int smem = 2 * C * sizeof(float);
-  if (smem > 48 * 1024) return -5;
-#define LAUNCH(TDY, TX, TDX)                                                                     \
-  do {                                                                                           \
-    if (C <= 768)                                                                                \
-      norm_bwd_kernel<TDY, TX, TDX, kRms, 3><<<grid, kNormThreads, smem, s>>>(                   \
-          static_cast<const TDY*>(dy), static_cast<const TX*>(x), gamma, mean, rstd,             \
-          static_cast<TDX*>(dx), partial, rows, C);                                              \
-    else if (C <= 1024)                                                                          \
-      norm_bwd_kernel<TDY, TX, TDX, kRms, 4><<<grid, kNormThreads, smem, s>>>(                   \
-          static_cast<const TDY*>(dy), static_cast<const TX*>(x), gamma, mean, rstd,             \
-          static_cast<TDX*>(dx), partial, rows, C);                                              \
-    else                                                                                         \
-      norm_bwd_kernel<TDY, TX, TDX, kRms, 8><<<grid, kNormThreads, smem, s>>>(                   \
-          static_cast<const TDY*>(dy), static_cast<const TX*>(x), gamma, mean, rstd,             \
-          static_cast<TDX*>(dx), partial, rows, C);                                              \
+  const bool wide = C > 1024;
+  const int grid = norm_bwd_grid(rows, wide, wide ? 4 : 3);
+  const int smem = wide ? 2 * kNormWarps * 2 * static_cast<int>(sizeof(float)) : 3 * C * static_cast<int>(sizeof(float));
+#define LAUNCH_K(TDY, TX, TDX, CH, RES, WIDE)                                                     \
+  norm_bwd_kernel<TDY, TX, TDX, kRms, CH, RES, WIDE><<<grid, kNormThreads, smem, s>>>(            \
+      static_cast<const TDY*>(dy), static_cast<const TX*>(x), gamma, mean, rstd,                  \
+      static_cast<const TDX*>(dres), static_cast<TDX*>(dx), partial, rows, C)
+#define LAUNCH_R(TDY, TX, TDX, RES)                                  \
+  do {                                                               \
+    if (C <= 768) LAUNCH_K(TDY, TX, TDX, 3, RES, false);             \
+    else if (C <= 1024) LAUNCH_K(TDY, TX, TDX, 4, RES, false);       \
+    else if (C <= 2048) LAUNCH_K(TDY, TX, TDX, 2, RES, true);        \
+    else if (C <= 4096) LAUNCH_K(TDY, TX, TDX, 4, RES, true);        \
+    else LAUNCH_K(TDY, TX, TDX, 6, RES, true);                       \
+  } while (0)
+#define LAUNCH(TDY, TX, TDX)                  \
+  do {                                        \
+    if (dres) LAUNCH_R(TDY, TX, TDX, true);   \
+    else LAUNCH_R(TDY, TX, TDX, false);       \
   } while (0)
   if (dyd == kItbBF16 && xd == kItbBF16 && dxd == kItbBF16)
     LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
@@ -370,10 +471,12 @@ static int norm_bwd_dispatch(const void* dy, int dyd, const void* x, int xd, con
     LAUNCH(float, __nv_bfloat16, __nv_bfloat16);
   else return -4;
 #undef LAUNCH
+#undef LAUNCH_R
+#undef LAUNCH_K
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  partial_reduce_kernel<<<(2 * C + 31) / 32, 256, 0, s>>>(partial, 2 * C, grid, dgamma, dbeta, C,
-                                                           accumulate);
+  partial_reduce_kernel<<<(3 * C + 31) / 32, 32 * kReduceLanes, 0, s>>>(partial, 3 * C, grid, dgamma, dbeta,
+                                                           dres ? dres_sum : nullptr, C, accumulate);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -391,8 +494,20 @@ extern "C" int itb_layernorm_bwd(const void* dy, int dy_dtype, const void* x, in
                                  const float* gamma, const float* mean, const float* rstd, void* dx,
                                  int dx_dtype, float* dgamma, float* dbeta, float* partial,
                                  int rows, int C, int accumulate, cudaStream_t stream) {
-  return itb::norm_bwd_dispatch<false>(dy, dy_dtype, x, x_dtype, gamma, mean, rstd, dx, dx_dtype,
-                                       dgamma, dbeta, partial, rows, C, accumulate, stream);
+  return itb::norm_bwd_dispatch<false>(dy, dy_dtype, x, x_dtype, gamma, mean, rstd, nullptr, dx, dx_dtype,
+                                       dgamma, dbeta, nullptr, partial, rows, C, accumulate ? 3 : 0, stream);
+}
+// The same with the residual stream's gradient folded in: dx = norm backward + dres, and (when
+// dres_sum is not null) dres_sum[c] (+)= sum over rows of dres.  `accumulate` is a bit mask: bit 0
+// dgamma, bit 1 dbeta, bit 2 dres_sum are added to instead of overwritten.  partial: [rows of
+// itb_norm_partial_rows(rows), 3 C] fp32.
+extern "C" int itb_layernorm_bwd_res(const void* dy, int dy_dtype, const void* x, int x_dtype,
+                                     const float* gamma, const float* mean, const float* rstd,
+                                     const void* dres, void* dx, int dx_dtype, float* dgamma, float* dbeta,
+                                     float* dres_sum, float* partial, int rows, int C, int accumulate,
+                                     cudaStream_t stream) {
+  return itb::norm_bwd_dispatch<false>(dy, dy_dtype, x, x_dtype, gamma, mean, rstd, dres, dx, dx_dtype,
+                                       dgamma, dbeta, dres_sum, partial, rows, C, accumulate, stream);
 }
 extern "C" int itb_rmsnorm_fwd(const void* x, int x_dtype, const float* gamma, void* y, int y_dtype,
                                float* rstd, int rows, int C, float eps, cudaStream_t stream) {
@@ -403,6 +518,13 @@ extern "C" int itb_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int 
                                const float* gamma, const float* rstd, void* dx, int dx_dtype,
                                float* dgamma, float* partial, int rows, int C, int accumulate,
                                cudaStream_t stream) {
-  return itb::norm_bwd_dispatch<true>(dy, dy_dtype, x, x_dtype, gamma, nullptr, rstd, dx, dx_dtype,
-                                      dgamma, nullptr, partial, rows, C, accumulate, stream);
+  return itb::norm_bwd_dispatch<true>(dy, dy_dtype, x, x_dtype, gamma, nullptr, rstd, nullptr, dx, dx_dtype,
+                                      dgamma, nullptr, nullptr, partial, rows, C, accumulate ? 1 : 0, stream);
+}
+extern "C" int itb_rmsnorm_bwd_res(const void* dy, int dy_dtype, const void* x, int x_dtype,
+                                   const float* gamma, const float* rstd, const void* dres, void* dx,
+                                   int dx_dtype, float* dgamma, float* dres_sum, float* partial, int rows,
+                                   int C, int accumulate, cudaStream_t stream) {
+  return itb::norm_bwd_dispatch<true>(dy, dy_dtype, x, x_dtype, gamma, nullptr, rstd, dres, dx, dx_dtype,
+                                      dgamma, nullptr, dres_sum, partial, rows, C, accumulate, stream);
 }

@@ -67,7 +67,11 @@ class LayerNorm(Module):
         self.weight = torch.nn.Parameter(torch.ones(self.normalized_shape, device=device))
         self.bias = torch.nn.Parameter(torch.zeros(self.normalized_shape, device=device))
 
-    def Forward(self, x):
+    def Forward(self, x, skip: bool = False):
+        """``skip=True`` returns ``(y, x)``: hand the second output to the ``residual`` argument of the
+        projection that closes the residual branch (see :func:`ops.functional.layernorm_skip`)."""
+        if skip:
+            return ops.layernorm_skip(x, self.weight, self.bias, self.eps)
         return ops.layernorm(x, self.weight, self.bias, self.eps)
 
 
@@ -79,7 +83,9 @@ class RMSNorm(Module):
         self.eps = eps
         self.weight = torch.nn.Parameter(torch.ones(dim, device=device))
 
-    def Forward(self, x):
+    def Forward(self, x, skip: bool = False):
+        if skip:
+            return ops.rmsnorm_skip(x, self.weight, self.eps)
         return ops.rmsnorm(x, self.weight, self.eps)
 
 

@@ -163,8 +163,12 @@ class TransformerLayer(Module):
         if _aligned():
             x1 = x + self.attn(self.ln_1(x), freqs_cis, start_pos)
             return x1 + self.mlp(self.ln_2(x1))
-        x1 = self.attn(self.ln_1(x), freqs_cis, start_pos, residual=x)
-        return self.mlp(self.ln_2(x1), residual=x1)
+        # the residual connection starts at the norm (its second output), so that backward adds the
+        # skip's gradient inside the norm's backward kernel
+        y, xs = self.ln_1(x, skip=True)
+        x1 = self.attn(y, freqs_cis, start_pos, residual=xs)
+        y, x1s = self.ln_2(x1, skip=True)
+        return self.mlp(y, residual=x1s)
 
 
 class TransformerFirstStage(Module):

@@ -136,6 +136,8 @@ class _LinearFn(torch.autograd.Function):
             C.gemm(x2, False, w, False, M, N, K, out, None, bias, res2, None, flags, 0)
         _counters["launches"] += 1
         ctx.save_for_backward(x2, weight, pre if gelu else None)
+        ctx.bias_param = bias            # the Parameter itself: its gradient may go straight to a flat buffer
+        ctx.bias_elsewhere = claim_bias_grad(residual, bias)
         ctx.has_bias = bias is not None
         ctx.has_res = residual is not None
         ctx.gelu = gelu
@@ -177,8 +179,8 @@ class _LinearFn(torch.autograd.Function):
                 dx = dx.to(ctx.x_dtype)
         if ctx.needs_input_grad[1]:
             dw = _wgrad(C, dy2, x2, weight, N, K, M)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = _bias_grad(C, dy2, N)
+        if ctx.has_bias and ctx.needs_input_grad[2] and not ctx.bias_elsewhere:
+            db = _bias_grad(C, dy2, N, ctx.bias_param)
         return dx, dw, db, d_res, None
 
 
@@ -204,9 +206,37 @@ def _wgrad(C, dy2, x2, weight, N, K, M):
     return dw if weight.dtype == torch.float32 else dw.to(weight.dtype)
 
 
-def _bias_grad(C, dy2, N):
-    if N % 8 == 0:
+def _main_grad_of(p: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """The fp32 slot of ``p`` in a flat gradient buffer that a kernel may accumulate into directly, or
+    None (no flat buffer, or a parameter shared by several ops whose ready hook must fire once)."""
+    if p is None or getattr(p, "_itb_shared", False):
+        return None
+    if getattr(p, "_itb_sp_hooked", False) or getattr(p, "_backward_hooks", None):
+        return None      # a tensor hook must see this gradient (e.g. the sum over the tensor-parallel group)
+    main = getattr(p, "main_grad", None)
+    if main is None and getattr(p, "_itb_main_grad_fn", None) is not None:
+        main = p._itb_main_grad_fn()
+    if main is None or main.dtype != torch.float32 or not main.is_contiguous():
+        return None
+    return main
+
+
+def _grad_written(p: torch.Tensor) -> None:
+    """A kernel has added ``p``'s gradient to its flat-buffer slot: tell the reducer / ZeRO group."""
+    for hook in getattr(p, "_itb_grad_ready_hooks", ()):
+        hook(p)
+
+
+def _bias_grad(C, dy2, N, bias=None):
+    """Column sums of dY.  With a flat gradient buffer behind ``bias`` they are added straight into
+    its slot (no gradient tensor, no separate accumulation launch) and None is returned."""
+    if N % 8 == 0 and dy2.data_ptr() % 16 == 0:
         _counters["launches"] += 2
+        main = _main_grad_of(bias)
+        if main is not None:
+            C.colsum(dy2, main)
+            _grad_written(bias)
+            return None
         return C.colsum(dy2)
     return dy2.float().sum(0)
 
@@ -253,6 +283,8 @@ class _MlpGeluFn(torch.autograd.Function):
         C.gemm(g, False, wpr, False, M, Cd, F, out, None, b_proj, res2, None, flags, 0)
         _counters["launches"] += 2
         ctx.save_for_backward(x2, h, g, w_fc, w_proj)
+        ctx.bias_params = (b_fc, b_proj)
+        ctx.bias_elsewhere = claim_bias_grad(residual, b_proj)
         ctx.meta = (M, Cd, F, x.shape, x.dtype, b_fc is not None, b_proj is not None,
                     residual.dtype if residual is not None else None)
         return out.view(x.shape)
@@ -271,7 +303,10 @@ class _MlpGeluFn(torch.autograd.Function):
         C.gemm(dy2, False, weight_lp(w_proj), True, M, F, Cd, dh, None, None, None, h, C.GEMM_DGELU, 0)
         _counters["launches"] += 1
         dw_proj = _wgrad(C, dy2, g, w_proj, Cd, F, M) if ctx.needs_input_grad[3] else None
-        db_proj = _bias_grad(C, dy2, Cd) if has_bpr and ctx.needs_input_grad[4] else None
+        b_fc, b_proj = ctx.bias_params
+        db_proj = None
+        if has_bpr and ctx.needs_input_grad[4] and not ctx.bias_elsewhere:
+            db_proj = _bias_grad(C, dy2, Cd, b_proj)
         dx = None
         if ctx.needs_input_grad[0]:
             dx2 = torch.empty((M, Cd), device=dy.device, dtype=torch.bfloat16)
@@ -281,7 +316,7 @@ class _MlpGeluFn(torch.autograd.Function):
             if x_dtype != torch.bfloat16:
                 dx = dx.to(x_dtype)
         dw_fc = _wgrad(C, dh, x2, w_fc, F, Cd, M) if ctx.needs_input_grad[1] else None
-        db_fc = _bias_grad(C, dh, F) if has_bfc and ctx.needs_input_grad[2] else None
+        db_fc = _bias_grad(C, dh, F, b_fc) if has_bfc and ctx.needs_input_grad[2] else None
         return dx, dw_fc, db_fc, dw_proj, db_proj, d_res
 
 
@@ -293,49 +328,117 @@ def mlp_gelu(x, w_fc, b_fc, w_proj, b_proj, residual=None):
 
 
 # --------------------------------------------------------------------------- normalisation
+class _SkipHolder:
+    """Travels on the skip tensor of a residual norm to the projection that adds it back in: that
+    projection's bias gradient is the column sum of the skip's gradient, which the norm's backward
+    kernel reads anyway."""
+
+    __slots__ = ("bias",)
+
+    def __init__(self):
+        self.bias = None
+
+
+def claim_bias_grad(residual, bias) -> bool:
+    """Called by a linear whose epilogue adds ``residual``: True when the norm that produced
+    ``residual`` as its skip output will compute ``bias``'s gradient (straight into the flat
+    gradient buffer) in its own backward pass, so the linear must not."""
+    holder = getattr(residual, "_itb_skip_holder", None)
+    if holder is None or bias is None or holder.bias is not None or _main_grad_of(bias) is None:
+        return False
+    holder.bias = bias
+    return True
+
+
+def _norm_param_grads(params, outs):
+    """Gradient tensors for autograd, or None for parameters whose gradient the kernel has already
+    added to their flat-buffer slot."""
+    res = []
+    for p, slot, g in zip(params, outs[0], outs[1]):
+        if p is None:
+            res.append(None)
+        elif slot is not None:
+            _grad_written(p)
+            res.append(None)
+        else:
+            res.append(g)
+    return res
+
+
 class _LayerNormFn(torch.autograd.Function):
+    """LayerNorm; with ``skip=True`` also returns the input as a second output, so that the residual
+    connection around the normalised branch starts HERE: backward then receives the branch's
+    gradient and the skip's gradient together and one kernel computes norm'(dy) + dskip (and the
+    column sums of dskip for the bias of the projection that adds the skip back in)."""
+
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps, out_dtype):
+    def forward(ctx, x, gamma, beta, eps, out_dtype, holder=None):
         C = _C()
         xc = x if x.is_contiguous() else x.contiguous()
         y, mean, rstd = C.layernorm_fwd(xc, gamma, beta, eps, out_dtype)
         _counters["launches"] += 1
-        ctx.save_for_backward(xc, gamma, mean, rstd)
-        ctx.has_beta = beta is not None
-        return y
+        ctx.save_for_backward(xc, mean, rstd)
+        ctx.params = (gamma, beta)
+        ctx.holder = holder
+        if holder is None:
+            return y
+        return y, xc.view_as(xc)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dskip=None):
         C = _C()
-        x, gamma, mean, rstd = ctx.saved_tensors
+        x, mean, rstd = ctx.saved_tensors
+        gamma, beta = ctx.params
         dyc = dy if dy.is_contiguous() else dy.contiguous()
         if dyc.dtype == torch.float32 and x.dtype == torch.bfloat16:
             dyc = dyc.to(torch.bfloat16)
-        dx, dg, db = C.layernorm_bwd(dyc, x, gamma, mean, rstd, ctx.has_beta)
+        if dskip is not None:
+            dskip = dskip if dskip.dtype == x.dtype else dskip.to(x.dtype)
+            dskip = dskip if dskip.is_contiguous() else dskip.contiguous()
+        bias = ctx.holder.bias if (ctx.holder is not None and dskip is not None) else None
+        slots = (_main_grad_of(gamma), _main_grad_of(beta), _main_grad_of(bias))
+        dx, dg, db, _ = C.layernorm_bwd(dyc, x, gamma, mean, rstd, beta is not None, dskip, slots[0],
+                                        slots[1] if beta is not None else None, slots[2], False)
         _counters["launches"] += 2
-        return dx, dg, (db if ctx.has_beta else None), None, None
+        if bias is not None:
+            _grad_written(bias)
+        dgamma, dbeta = _norm_param_grads((gamma, beta), (slots, (dg, db)))
+        return dx, dgamma, dbeta, None, None, None
 
 
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gamma, eps, out_dtype):
+    def forward(ctx, x, gamma, eps, out_dtype, holder=None):
         C = _C()
         xc = x if x.is_contiguous() else x.contiguous()
         y, rstd = C.rmsnorm_fwd(xc, gamma, eps, out_dtype)
         _counters["launches"] += 1
-        ctx.save_for_backward(xc, gamma, rstd)
-        return y
+        ctx.save_for_backward(xc, rstd)
+        ctx.params = (gamma,)
+        ctx.holder = holder
+        if holder is None:
+            return y
+        return y, xc.view_as(xc)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dskip=None):
         C = _C()
-        x, gamma, rstd = ctx.saved_tensors
+        x, rstd = ctx.saved_tensors
+        (gamma,) = ctx.params
         dyc = dy if dy.is_contiguous() else dy.contiguous()
         if dyc.dtype == torch.float32 and x.dtype == torch.bfloat16:
             dyc = dyc.to(torch.bfloat16)
-        dx, dg = C.rmsnorm_bwd(dyc, x, gamma, rstd)
+        if dskip is not None:
+            dskip = dskip if dskip.dtype == x.dtype else dskip.to(x.dtype)
+            dskip = dskip if dskip.is_contiguous() else dskip.contiguous()
+        bias = ctx.holder.bias if (ctx.holder is not None and dskip is not None) else None
+        slots = (_main_grad_of(gamma), _main_grad_of(bias))
+        dx, dg, _ = C.rmsnorm_bwd(dyc, x, gamma, rstd, dskip, slots[0], slots[1], False)
         _counters["launches"] += 2
-        return dx, dg, None, None
+        if bias is not None:
+            _grad_written(bias)
+        (dgamma,) = _norm_param_grads((gamma,), ((slots[0],), (dg,)))
+        return dx, dgamma, None, None, None
 
 
 def _norm_out_dtype(x):
@@ -344,20 +447,45 @@ def _norm_out_dtype(x):
     return torch.float32
 
 
-def layernorm(x, gamma, beta=None, eps=1e-5):
+def _norm_fused(x, gamma) -> bool:
     C_ = x.shape[-1]
-    if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and gamma.dtype == torch.float32 and C_ % 8 == 0 \
-            and C_ <= 6144 and _ext.available():
+    return (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and gamma.dtype == torch.float32 and C_ % 8 == 0
+            and C_ <= 6144 and _ext.available())
+
+
+def layernorm(x, gamma, beta=None, eps=1e-5):
+    if _norm_fused(x, gamma):
         return _LayerNormFn.apply(x, gamma, beta, eps, _norm_out_dtype(x))
     return ref.layernorm(x, gamma, beta, eps)
 
 
 def rmsnorm(x, gamma, eps=1e-6):
-    C_ = x.shape[-1]
-    if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and gamma.dtype == torch.float32 and C_ % 8 == 0 \
-            and C_ <= 6144 and _ext.available():
+    if _norm_fused(x, gamma):
         return _RMSNormFn.apply(x, gamma, eps, _norm_out_dtype(x))
     return ref.rmsnorm(x, gamma, eps)
+
+
+def layernorm_skip(x, gamma, beta=None, eps=1e-5):
+    """``(layernorm(x), x)``: the second output is the start of the residual connection around the
+    normalised branch.  Adding it back in through a fused linear's ``residual`` argument lets the
+    backward pass add the skip's gradient inside the norm's backward kernel (no separate add) and
+    take that linear's bias gradient from the same pass."""
+    if _norm_fused(x, gamma):
+        holder = _SkipHolder()
+        y, xs = _LayerNormFn.apply(x, gamma, beta, eps, _norm_out_dtype(x), holder)
+        xs._itb_skip_holder = holder
+        return y, xs
+    return ref.layernorm(x, gamma, beta, eps), x
+
+
+def rmsnorm_skip(x, gamma, eps=1e-6):
+    """``(rmsnorm(x), x)``; see :func:`layernorm_skip`."""
+    if _norm_fused(x, gamma):
+        holder = _SkipHolder()
+        y, xs = _RMSNormFn.apply(x, gamma, eps, _norm_out_dtype(x), holder)
+        xs._itb_skip_holder = holder
+        return y, xs
+    return ref.rmsnorm(x, gamma, eps), x
 
 
 # --------------------------------------------------------------------------- activations

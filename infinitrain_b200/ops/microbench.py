@@ -116,6 +116,34 @@ def bench_gemm_probe(C):
         print(json.dumps(res))
 
 
+def bench_norm(C):
+    """LayerNorm / RMSNorm forward and backward on the activations of the headline models, against the
+    bytes they have to move (bf16 x, dy in, y / dx out) at the measured copy bandwidth."""
+    timeit = _timer()
+    for rows, Cd, rms in ((16384, 768, False), (2048, 4096, True), (16384, 4096, True)):
+        x = torch.randn(rows, Cd, device="cuda").bfloat16()
+        g = torch.ones(Cd, device="cuda")
+        b = torch.zeros(Cd, device="cuda")
+        dy = torch.randn_like(x)
+        dres = torch.randn_like(x)
+        res = {"case": "norm", "rows": rows, "C": Cd, "rms": rms}
+        if rms:
+            y, rstd = C.rmsnorm_fwd(x, g, 1e-5, torch.bfloat16)
+            res["fwd_us"] = timeit(lambda: C.rmsnorm_fwd(x, g, 1e-5, torch.bfloat16)) * 1e3
+            res["bwd_us"] = timeit(lambda: C.rmsnorm_bwd(dy, x, g, rstd)) * 1e3
+            res["bwd_res_us"] = timeit(lambda: C.rmsnorm_bwd(dy, x, g, rstd, dres, None, None, True)) * 1e3
+        else:
+            y, mean, rstd = C.layernorm_fwd(x, g, b, 1e-5, torch.bfloat16)
+            res["fwd_us"] = timeit(lambda: C.layernorm_fwd(x, g, b, 1e-5, torch.bfloat16)) * 1e3
+            res["bwd_us"] = timeit(lambda: C.layernorm_bwd(dy, x, g, mean, rstd, True)) * 1e3
+            res["bwd_res_us"] = timeit(lambda: C.layernorm_bwd(dy, x, g, mean, rstd, True, dres, None, None, None, True)) * 1e3
+        nbytes = rows * Cd * 2
+        res["fwd_floor_us"] = 2 * nbytes / 6.5389e12 * 1e6
+        res["bwd_floor_us"] = 3 * nbytes / 6.5389e12 * 1e6
+        res["bwd_res_floor_us"] = 4 * nbytes / 6.5389e12 * 1e6
+        print(json.dumps(res))
+
+
 def bench_attention(C):
     timeit = _timer()
     default = C.get_attn_mode()
@@ -227,7 +255,7 @@ def main(argv):
     C = _ext.load(required=True)
     torch.manual_seed(0)
     case = argv[1] if len(argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "gemm_llama_tp8": bench_gemm_llama_tp8, "gemm_probe": bench_gemm_probe, "attention": bench_attention, "profile": profile_case,
+    {"gemm": bench_gemm, "gemm_llama_tp8": bench_gemm_llama_tp8, "gemm_probe": bench_gemm_probe, "norm": bench_norm, "attention": bench_attention, "profile": profile_case,
      "tp": bench_tp}[case](C)
     return 0
 

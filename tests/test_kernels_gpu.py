@@ -117,10 +117,20 @@ def test_layernorm(C, rows, Cdim, xdt):
     assert torch.allclose(mean, xr.mean(-1), atol=1e-4)
     dy = torch.randn(rows, Cdim, device="cuda").bfloat16()
     ref.backward(dy.float())
-    dx, dg, db = C.layernorm_bwd(dy, x, g, mean, rstd, True)
+    dx, dg, db, _ = C.layernorm_bwd(dy, x, g, mean, rstd, True)
     assert dx.dtype == x.dtype
     assert _rel(dx, xr.grad) < (1e-2 if xdt == torch.bfloat16 else 1e-4)
     assert _rel(dg, gr.grad) < 1e-3 and _rel(db, br.grad) < 1e-3
+    # on a residual stream: dx = norm'(dy) + dres, column sums of dres, gradients accumulated into given slots
+    dres = torch.randn(rows, Cdim, device="cuda").to(xdt)
+    slot_g, slot_b, slot_s = (torch.full((Cdim,), 0.5, device="cuda") for _ in range(3))
+    dx2, dg2, db2, ds2 = C.layernorm_bwd(dy, x, g, mean, rstd, True, dres, slot_g, slot_b, slot_s)
+    assert dg2.data_ptr() == slot_g.data_ptr() and ds2.data_ptr() == slot_s.data_ptr()
+    assert _rel(dx2.float(), xr.grad + dres.float()) < (1e-2 if xdt == torch.bfloat16 else 1e-4)
+    assert _rel(slot_g, gr.grad + 0.5) < 1e-3 and _rel(slot_b, br.grad + 0.5) < 1e-3
+    assert _rel(slot_s, dres.float().sum(0) + 0.5) < 1e-3
+    _, _, _, ds3 = C.layernorm_bwd(dy, x, g, mean, rstd, True, dres, None, None, None, True)
+    assert _rel(ds3, dres.float().sum(0)) < 1e-3
 
 
 @pytest.mark.parametrize("rows,Cdim", [(64, 768), (257, 2048), (48, 4096)])
@@ -136,9 +146,55 @@ def test_rmsnorm(C, rows, Cdim, xdt):
     assert _rel(y, ref) < 1e-2
     dy = torch.randn(rows, Cdim, device="cuda").bfloat16()
     ref.backward(dy.float())
-    dx, dg = C.rmsnorm_bwd(dy, x, g, rstd)
+    dx, dg, _ = C.rmsnorm_bwd(dy, x, g, rstd)
     assert _rel(dx, xr.grad) < (1e-2 if xdt == torch.bfloat16 else 1e-4)
     assert _rel(dg, gr.grad) < 1e-3
+    dres = torch.randn(rows, Cdim, device="cuda").to(xdt)
+    slot_g = torch.full((Cdim,), 0.25, device="cuda")
+    dx2, dg2, ds2 = C.rmsnorm_bwd(dy, x, g, rstd, dres, slot_g, None, True)
+    assert _rel(dx2.float(), xr.grad + dres.float()) < (1e-2 if xdt == torch.bfloat16 else 1e-4)
+    assert _rel(slot_g, gr.grad + 0.25) < 1e-3 and _rel(ds2, dres.float().sum(0)) < 1e-3
+
+
+def test_residual_norm_block_matches_plain_autograd(C):
+    """``(y, skip) = norm_skip(x)`` followed by a fused linear that adds ``skip`` back in: the backward
+    pass of the norm takes the skip's gradient (no separate add), the bias gradient of that linear comes
+    out of the same kernel, and parameter gradients land in their flat-buffer slots."""
+    from infinitrain_b200.autocast import AutocastGuard
+    from infinitrain_b200.datatype import DataType
+    from infinitrain_b200.device import DeviceType
+    from infinitrain_b200.ops import functional as ops
+
+    torch.manual_seed(11)
+    B, T, Cd = 2, 96, 256
+    x0 = (torch.randn(B, T, Cd, device="cuda") * 0.5).bfloat16()
+    gamma, beta = torch.randn(Cd, device="cuda") * 0.2 + 1, torch.randn(Cd, device="cuda") * 0.1
+    w, b = torch.randn(Cd, Cd, device="cuda") * 0.05, torch.randn(Cd, device="cuda") * 0.1
+    up = torch.randn(B, T, Cd, device="cuda").bfloat16()
+
+    def run(fused):
+        ps = [t.clone().requires_grad_(True) for t in (gamma, beta, w, b)]
+        if fused:
+            for p in ps:                  # flat-buffer slots, as DDP / the fused optimizer set them up
+                p.main_grad = torch.zeros_like(p)
+                p.grad = p.main_grad
+        x = x0.clone().requires_grad_(True)
+        with AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16):
+            if fused:
+                y, skip = ops.layernorm_skip(x, ps[0], ps[1])
+                out = ops.linear(y, ps[2], ps[3], residual=skip)
+            else:
+                out = ops.linear(ops.layernorm(x, ps[0], ps[1]), ps[2], ps[3]) + x
+        out.backward(up)
+        grads = [p.main_grad if fused else p.grad for p in ps]
+        return out, x.grad, grads
+
+    o1, dx1, g1 = run(True)
+    o0, dx0, g0 = run(False)
+    assert _rel(o1, o0) < 1e-2 and _rel(dx1, dx0) < 2e-2
+    for a, r in zip(g1, g0):
+        assert _rel(a, r) < 2e-2
+    assert C.kernel_status() == 0
 
 
 def test_gelu_swiglu(C):
