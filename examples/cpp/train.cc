@@ -1,12 +1,16 @@
 // GPT-2 / LLaMA-3 training loop on the C++ frontend, with the flag names and the per-step log line of
-// the reference's example/gpt2/main.cc and example/llama3/main.cc: one process per device, data
-// parallel over the ranks that infini_run / torchrun start (RANK, WORLD_SIZE, MASTER_ADDR, MASTER_PORT).
+// the reference's example/gpt2/main.cc and example/llama3/main.cc: one process per device, started by
+// infini_run / torchrun (RANK, WORLD_SIZE, MASTER_ADDR, MASTER_PORT).
 //
 //   itb_train --family gpt2 --llmc_filepath model.bin --input_bin tokens.bin --batch_size 4
 //             --sequence_length 64 --total_batch_size 256 --num_iteration 10 --learning_rate 1e-4
 //             --device cpu|cuda --dtype float32|bfloat16 --optimizer sgd|adam|adamw
 //             [--lora_rank 8 --lora_alpha 16 --lora_target_modules c_attn,c_proj --lora_load_path F --lora_save_path F]
 //             [--save DIR --save_interval N] [--load DIR/checkpoint_step_000004]
+//             [--tensor_parallel N --sequence_parallel --pipeline_parallel N --virtual_pipeline_parallel N
+//              --pipeline_schedule 1f1b|gpipe --zero_stage 0|1|2 --no_overlap_grad_reduce]
+// The ranks are laid out TP fastest, then DP, then PP; data parallelism takes what is left of the
+// world size.  CPU ranks talk through the job's TCP store, GPU ranks through NCCL.
 #include <chrono>
 #include <cstdio>
 #include <iostream>
@@ -73,7 +77,9 @@ itb::nn::TransformerConfig from_scratch_config(const std::string& family, const 
 
 }  // namespace
 
+
 int main(int argc, char** argv) {
+  namespace par = itb::parallel;
   Flags fl = parse(argc, argv);
   const std::string family = fl.get("family", "gpt2");
   const int64_t B = fl.geti("batch_size", 4), T = fl.geti("sequence_length", 64);
@@ -81,12 +87,23 @@ int main(int argc, char** argv) {
   const double lr = fl.getd("learning_rate", family == "gpt2" ? 1e-4 : 1e-5);
   const std::string opt_name = fl.get("optimizer", family == "gpt2" ? "sgd" : "adam");
   const bool bf16 = fl.get("dtype", "float32") == "bfloat16";
-  const int64_t world_env = itb::dist::Env::FromEnvironment().world;
-  TORCH_CHECK(total % (B * T * world_env) == 0, "total_batch_size must be a multiple of batch_size * sequence_length * ranks");
-  const int64_t grad_accum = total / (B * T * world_env);
-  const itb::dist::Env env = itb::dist::Env::FromEnvironment();    // one process per device (infini_run / torchrun)
+  const int zero_stage = static_cast<int>(fl.geti("zero_stage", 0));
+
+  // ---- topology: one process per device; TP fastest, then DP, then PP
+  par::GlobalEnv& env = par::env();
+  env.InitAllEnv(static_cast<int>(fl.geti("tensor_parallel", 1)), fl.getb("sequence_parallel", false),
+                 static_cast<int>(fl.geti("pipeline_parallel", 1)), static_cast<int>(fl.geti("virtual_pipeline_parallel", 1)));
+  const int64_t dp = env.dp(), tp = env.tp(), pp = env.pp();
+  TORCH_CHECK(total % (B * T * dp) == 0, "total_batch_size must be a multiple of batch_size * sequence_length * data-parallel ranks");
+  const int64_t grad_accum = total / (B * T * dp);
+  TORCH_CHECK(!env.sequence_parallel || T % tp == 0, "sequence_length must be divisible by the tensor-parallel size");
   torch::Device device = fl.get("device", "cpu") == "cuda" ? torch::Device(torch::kCUDA, env.local_rank) : torch::Device(torch::kCPU);
-  const int64_t dp = env.world;
+  if (env.world > 1) {
+    par::ProcessGroupFactory::Instance().Init(device);
+    if (env.rank == 0) std::fprintf(stderr, "%s", env.ProcessGroupOverview().c_str());
+  }
+  auto dp_group = par::dp_group();
+  auto pp_group = par::pp_group();
   itb::nn::ManualSeed(static_cast<uint32_t>(fl.geti("seed", 42)));
 
   std::shared_ptr<itb::nn::TransformerModel> model;
@@ -100,11 +117,13 @@ int main(int argc, char** argv) {
   }
   model->To(device);
   const auto& cfg = model->config;
-  std::fprintf(stderr, "[I] model: %lld layers, %lld wide, %lld/%lld heads, vocab %lld; %zu parameter tensors\n",
-               (long long)cfg.n_layer, (long long)cfg.n_embd, (long long)cfg.n_head, (long long)cfg.n_kv_head,
+  std::fprintf(stderr, "[I] rank %d: model: %lld layers (%zu here), %lld wide, %lld/%lld heads, vocab %lld; %zu parameter tensors\n", env.rank,
+               (long long)cfg.n_layer, model->h->size(), (long long)cfg.n_embd, (long long)cfg.n_head, (long long)cfg.n_kv_head,
                (long long)cfg.vocab_size, model->Parameters().size());
 
-  auto loss_module = std::make_shared<itb::nn::CrossEntropyLoss>();
+  std::shared_ptr<itb::Module> loss_module;
+  if (tp > 1) loss_module = std::make_shared<par::VocabParallelCrossEntropyLoss>(cfg.original_vocab_size);
+  else loss_module = std::make_shared<itb::nn::CrossEntropyLoss>();
   if (!fl.get("precision_check", "").empty()) {   // "level=1,format=simple,path=DIR,save_tensors=true"
     itb::utils::PrecisionChecker::Instance().Init(fl.get("precision_check", ""), env.rank);
     itb::utils::PrecisionChecker::Instance().Attach(model);
@@ -121,25 +140,55 @@ int main(int argc, char** argv) {
     if (!fl.get("lora_load_path", "").empty()) lora::LoadLoRAWeights(model, fl.get("lora_load_path", ""));
     std::fprintf(stderr, "[I] %s\n", lora::PrintLoRASummary(model).c_str());
   }
-  std::shared_ptr<itb::dist::Comm> comm;
-  std::unique_ptr<itb::dist::DistributedDataParallel> ddp;
+  // ---- data parallelism: the wrapper broadcasts rank 0's parameters and reduces gradients during backward
+  std::shared_ptr<par::DistributedDataParallel> ddp;
   if (dp > 1) {
-    comm = itb::dist::MakeComm(env, device);
-    ddp = std::make_unique<itb::dist::DistributedDataParallel>(model, comm);   // parameters become rank 0's
+    par::DistributedDataParallelConfig dc;
+    dc.zero_stage = zero_stage;
+    dc.overlap_grad_reduce = !fl.getb("no_overlap_grad_reduce", false);
+    ddp = std::make_shared<par::DistributedDataParallel>(model, dp_group, dc);
   }
   itb::TensorList trainable = itb::nn::lora::TrainableParameters(model);
 
+  auto make_base = [&](itb::TensorList params) -> std::unique_ptr<itb::optim::Optimizer> {
+    if (opt_name == "sgd") return std::make_unique<itb::optim::SGD>(std::move(params), lr);
+    return std::make_unique<itb::optim::Adam>(std::move(params), lr, 0.9, 0.999, 1e-8, opt_name == "adamw" ? fl.getd("weight_decay", 0.1) : 0.0);
+  };
   std::unique_ptr<itb::optim::Optimizer> optimizer;
-  if (opt_name == "sgd") optimizer = std::make_unique<itb::optim::SGD>(trainable, lr);
-  else optimizer = std::make_unique<itb::optim::Adam>(trainable, lr, 0.9, 0.999, 1e-8,
-                                                      opt_name == "adamw" ? fl.getd("weight_decay", 0.1) : 0.0);
+  if (ddp && zero_stage >= 1) optimizer = std::make_unique<par::DistributedOptimizer>(make_base, std::vector<par::DistributedDataParallel*>{ddp.get()});
+  else optimizer = make_base(trainable);
 
-  itb::io::TokenLoader loader(fl.get("input_bin", ""), B, T, env.rank, dp);
+  // ---- pipeline
+  std::unique_ptr<par::PipelineParallel> pipeline;
+  if (pp > 1) {
+    par::PipelineConfig pc;
+    pc.num_stages = static_cast<int>(pp), pc.stage = env.pp_rank, pc.vpp = env.vpp;
+    pc.num_micro_batches = static_cast<int>(grad_accum);
+    pc.schedule = fl.get("pipeline_schedule", "1f1b");
+    pc.boundary_shape = {B, T / env.sp(), cfg.n_embd};
+    pc.boundary_dtype = (bf16 && device.is_cuda()) ? torch::kBFloat16 : torch::kFloat32;
+    pc.device = device;
+    pipeline = std::make_unique<par::PipelineParallel>(
+        pc, [&](int64_t ci, const itb::Tensor& in) {
+          itb::AutocastGuard autocast(bf16 ? torch::kBFloat16 : torch::kFloat32);
+          return model->forward_chunk(ci, in, T);
+        }, pp_group);
+    if (env.rank == 0) std::fprintf(stderr, "[I] pipeline schedule (%s)\n%s", pc.schedule.c_str(), pipeline->ScheduleTable().c_str());
+  }
+
+  itb::io::TokenLoader loader(fl.get("input_bin", ""), B, T, env.dp_rank, dp);
   int64_t start_step = 0, consumed = 0;
+  const bool model_parallel = tp * pp > 1;
+  // which ranks hold state nobody else has: every model-parallel slice, and under ZeRO every shard of the optimizer state
+  const bool own_state = model_parallel || (dp > 1 && zero_stage >= 1);
   if (!fl.get("load", "").empty()) {
-    const std::string dir = fl.get("load", "");
+    std::string dir = fl.get("load", "");
+    if (std::filesystem::exists(dir + "/" + itb::io::RankDirName(env.rank))) dir += "/" + itb::io::RankDirName(env.rank);
     auto st = itb::io::LoadTrainerState(dir + "/trainer_state.json");
     TORCH_CHECK(st.n_layer == cfg.n_layer && st.n_embd == cfg.n_embd, "checkpoint and model shapes differ");
+    TORCH_CHECK(st.tp_size == tp && st.pp_size == pp && st.sp_size == env.sp() && (st.ddp_size == dp || !own_state),
+                "the checkpoint was written under another parallel layout (DP=", st.ddp_size, " TP=", st.tp_size, " SP=", st.sp_size,
+                " PP=", st.pp_size, ")");
     model->LoadStateDict(itb::io::LoadStateDict(dir + "/model.ckpt"));
     if (std::filesystem::exists(dir + "/optimizer.ckpt")) optimizer->LoadStateDict(itb::io::LoadStateDict(dir + "/optimizer.ckpt"));
     start_step = st.global_step;
@@ -151,39 +200,64 @@ int main(int argc, char** argv) {
   std::unique_ptr<itb::data::Tokenizer> tokenizer;
   if (!fl.get("tokenizer_bin", "").empty()) tokenizer = std::make_unique<itb::data::Tokenizer>(fl.get("tokenizer_bin", ""));
   const int64_t freq_generate = fl.geti("freq_generate_txt", 10), text_length = fl.geti("text_length", 64);
+  auto loss_of = [&](const itb::Tensor& logits, const itb::Tensor& y) {
+    itb::AutocastGuard autocast(bf16 ? torch::kBFloat16 : torch::kFloat32);
+    return (*loss_module)(itb::TensorList{logits, y})[0];
+  };
 
   for (int64_t step = start_step; step < iters; ++step) {
     auto t0 = std::chrono::steady_clock::now();
     itb::utils::PrecisionChecker::Instance().ResetCounters();
     optimizer->ZeroGrad();
+    if (ddp) ddp->ZeroGrad();
     double lossf = 0.0;
-    for (int64_t micro = 0; micro < grad_accum; ++micro) {
-      itb::Tensor x, y;
-      loader.next(&x, &y);
-      ++consumed;
-      x = x.to(device), y = y.to(device);
-      itb::Tensor loss;
-      {
-        itb::AutocastGuard autocast(bf16 ? torch::kBFloat16 : torch::kFloat32);
-        itb::Tensor logits = (*model)(itb::TensorList{x})[0];   // through the call operator: hooks see the model's output
-        loss = (*loss_module)(itb::TensorList{logits, y})[0] / static_cast<double>(grad_accum);
+    if (pipeline) {
+      std::vector<itb::Tensor> xs, ys;
+      for (int64_t micro = 0; micro < grad_accum; ++micro) {
+        itb::Tensor x, y;
+        loader.next(&x, &y);
+        ++consumed;
+        // the loader's tensors alias a ring slot that the next calls reuse: the schedule needs its own copies
+        xs.push_back(device.is_cpu() ? x.clone() : x.to(device)), ys.push_back(device.is_cpu() ? y.clone() : y.to(device));
       }
-      lossf += loss.item<float>();
-      loss.backward();
+      lossf = pipeline->StepMicroBatches(xs, ys, loss_of, [&](int64_t, bool last) {
+        if (ddp) ddp->set_sync(last);
+      });
+    } else {
+      for (int64_t micro = 0; micro < grad_accum; ++micro) {
+        itb::Tensor x, y;
+        loader.next(&x, &y);
+        ++consumed;
+        x = x.to(device), y = y.to(device);
+        if (ddp) ddp->set_sync(micro == grad_accum - 1);   // earlier micro-batches only accumulate
+        itb::Tensor loss;
+        {
+          itb::AutocastGuard autocast(bf16 ? torch::kBFloat16 : torch::kFloat32);
+          // through the call operator: hooks see the model's output
+          itb::Tensor logits = ddp ? (*ddp)(itb::TensorList{x})[0] : (*model)(itb::TensorList{x})[0];
+          loss = loss_of(logits, y) / static_cast<double>(grad_accum);
+        }
+        lossf += loss.item<float>();
+        loss.backward();
+      }
     }
-    if (ddp) {
-      ddp->SyncGradients();
-      itb::Tensor l = torch::full({1}, lossf, torch::dtype(torch::kFloat32).device(device));
-      comm->AllReduceSum(l);
-      lossf = l.item<float>() / static_cast<double>(dp);
-    }
+    if (ddp) ddp->FinishGradSync();
+    // under sequence parallelism the parameters that every tensor-parallel rank holds whole saw a
+    // slice of the sequence each: their gradients are partial sums
+    if (env.sequence_parallel) par::AllReduceSequenceParallelGrads(model->SequenceParallelReplicated());
     optimizer->Step();
+    if (dp_group) {
+      itb::Tensor l = torch::full({1}, lossf, torch::dtype(torch::kFloat32).device(device));
+      dp_group->AllReduce(l, par::ReduceOp::kAvg);
+      lossf = l.item<float>();
+    }
     double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
-    if (env.rank == dp - 1)   // the last rank logs, as in the reference
+    if (env.rank == env.world - 1)   // the last rank logs, as in the reference (it holds the last pipeline stage)
       std::fprintf(stderr, "[E] step %4lld/%lld | train loss %.6f | lr %.2e | (%.2f ms | %.0f tok/s | peak used: %5.0f MB | "
-                           "peak reserved: %5.0f MB, DP=%lld, TP=1, SP=1, PP=1)\n",
-                   (long long)(step + 1), (long long)iters, lossf, lr, ms, total / (ms / 1e3), 0.0, 0.0, (long long)dp);
-    if (tokenizer && freq_generate > 0 && (step + 1) % freq_generate == 0 && env.rank == 0) {
+                           "peak reserved: %5.0f MB, DP=%lld, TP=%lld, SP=%d, PP=%lld)\n",
+                   (long long)(step + 1), (long long)iters, lossf, lr, ms, total / (ms / 1e3), 0.0, 0.0, (long long)dp, (long long)tp,
+                   env.sp(), (long long)pp);
+    if (tokenizer && freq_generate > 0 && (step + 1) % freq_generate == 0 && env.rank == 0 && !model_parallel) {
       std::vector<int64_t> ids;
       std::string text = tokenizer->GenerateText([&](const itb::Tensor& ids_in) { return model->forward(ids_in); }, B, T,
                                                  text_length, device, &ids);
@@ -191,15 +265,19 @@ int main(int argc, char** argv) {
       for (int64_t id : ids) std::printf(" %lld", (long long)id);
       std::printf("\n");
     }
-    if (save_interval > 0 && (step + 1) % save_interval == 0 && !fl.get("save", "").empty() && env.rank == 0) {
+    // a rank saves what only it holds: its model-parallel slice, its shard of a ZeRO optimizer state
+    const bool saver = own_state ? (env.dp_rank == 0 || zero_stage >= 1) : env.rank == 0;
+    if (save_interval > 0 && (step + 1) % save_interval == 0 && !fl.get("save", "").empty() && saver) {
       itb::io::TrainerState st;
       st.global_step = step + 1, st.consumed_batches = consumed, st.last_lr = lr;
       st.n_layer = cfg.n_layer, st.n_head = cfg.n_head, st.n_kv_head = cfg.n_kv_head, st.n_embd = cfg.n_embd;
-      st.vocab_size = cfg.vocab_size, st.ddp_size = dp;
-      itb::io::SaveCheckpoint(fl.get("save", ""), st, *model, optimizer->StateDict());
+      st.vocab_size = cfg.vocab_size, st.ddp_size = dp, st.tp_size = tp, st.sp_size = env.sp(), st.pp_size = pp;
+      itb::io::SaveCheckpoint(fl.get("save", ""), st, *model, optimizer->StateDict(), own_state ? env.rank : -1);
     }
   }
-  if (comm) comm->Barrier();
+  if (auto world = par::ProcessGroupFactory::Instance().GetDefaultProcessGroup()) world->Barrier();
   if (lora_rank > 0 && !fl.get("lora_save_path", "").empty() && env.rank == 0) itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", ""));
+  ddp.reset();
+  par::ProcessGroupFactory::Instance().Shutdown();
   return 0;
 }

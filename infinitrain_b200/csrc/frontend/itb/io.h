@@ -31,8 +31,62 @@ inline void assign(std::map<std::string, Tensor>& sd, const std::string& key, co
   it->second.copy_(value);
 }
 
+// How one tensor of a weight file maps onto this rank's slice of a tensor- / pipeline-parallel model
+// (reference: the loaders of example/gpt2/net.cc:263-520 and example/llama3/net.cc:236-530 read every
+// tensor and keep the rows or columns of their rank).
+enum class Shard { kReplicated, kRows, kCols, kQKVRows };
+class ShardedAssigner {
+ public:
+  ShardedAssigner(std::ifstream& f, nn::TransformerModel& model) : f_(f), model_(model), sd_(model.StateDict()) {}
+  // Reads the next tensor of the file (full shape `shape`) into parameter `name`, given in the
+  // single-process naming with GLOBAL layer numbers; skips it when this rank does not hold it.
+  void next(const std::string& name, const std::vector<int64_t>& shape, Shard how, int64_t keep_rows = -1) {
+    const std::string local = LocalName(name);
+    int64_t numel = 1;
+    for (int64_t d : shape) numel *= d;
+    if (local.empty() || sd_.find(local) == sd_.end()) {
+      f_.seekg(static_cast<std::streamoff>(numel * 4), std::ios::cur);
+      TORCH_CHECK(f_.good(), "llm.c weight file is truncated");
+      return;
+    }
+    Tensor t = read_f32(f_, shape);
+    if (keep_rows >= 0) t = t.slice(0, 0, keep_rows);
+    assign(sd_, local, Slice(t, how));
+  }
+  // The same tensor into a second parameter (an untied copy of a tied weight).
+  void also(const std::string& name, const std::string& from) {
+    const std::string dst = LocalName(name), src = LocalName(from);
+    if (dst.empty() || src.empty() || sd_.find(dst) == sd_.end() || sd_.find(src) == sd_.end()) return;
+    if (sd_.at(dst).data_ptr() != sd_.at(src).data_ptr()) assign(sd_, dst, sd_.at(src));
+  }
+
+ private:
+  std::string LocalName(const std::string& name) const {
+    static const std::string kLayer = "transformer.h.";
+    if (name.rfind(kLayer, 0) != 0) return name;
+    const size_t dot = name.find('.', kLayer.size());
+    const int64_t local = model_.local_layer(std::stoll(name.substr(kLayer.size(), dot - kLayer.size())));
+    return local < 0 ? std::string() : kLayer + std::to_string(local) + name.substr(dot);
+  }
+  Tensor Slice(const Tensor& t, Shard how) const {
+    const auto& pe = parallel::env();
+    const int64_t tp = pe.tp(), r = pe.tp_rank;
+    if (tp == 1 || how == Shard::kReplicated) return t;
+    if (how == Shard::kRows) return t.chunk(tp, 0)[r];
+    if (how == Shard::kCols) return t.chunk(tp, 1)[r];
+    // fused QKV: the file stacks [q | k | v]; a rank holds [q_r | k_r | v_r]
+    const auto& c = model_.config;
+    const int64_t q = c.n_head * c.head_dim(), kv = c.n_kv_head * c.head_dim();
+    return torch::cat({t.slice(0, 0, q).chunk(tp, 0)[r], t.slice(0, q, q + kv).chunk(tp, 0)[r], t.slice(0, q + kv, q + 2 * kv).chunk(tp, 0)[r]}, 0);
+  }
+  std::ifstream& f_;
+  nn::TransformerModel& model_;
+  std::map<std::string, Tensor> sd_;
+};
+
 // GPT-2: 256 int32 header {magic 20240326, version 3 (fp32), block_size, vocab, layers, heads, width,
-// padded vocab}, then the tensors kind by kind, each kind stacked over the layers.
+// padded vocab}, then the tensors kind by kind, each kind stacked over the layers.  Under tensor
+// parallelism the vocabulary keeps the file's padding so that it divides among the ranks.
 inline std::shared_ptr<nn::TransformerModel> LoadGPT2FromLLMC(const std::string& path) {
   std::ifstream f(path, std::ios::binary);
   TORCH_CHECK(f.is_open(), "File not found: ", path);
@@ -41,21 +95,31 @@ inline std::shared_ptr<nn::TransformerModel> LoadGPT2FromLLMC(const std::string&
   TORCH_CHECK(f.good() && h[0] == 20240326, "not an llm.c GPT-2 weight file: ", path);
   TORCH_CHECK(h[1] == 3, "only fp32 llm.c GPT-2 files (version 3) are supported");
   auto cfg = nn::TransformerConfig::GPT2();
-  cfg.block_size = h[2], cfg.vocab_size = cfg.original_vocab_size = h[3];
+  const int64_t Vp = h[7];
+  cfg.block_size = h[2], cfg.original_vocab_size = h[3];
+  cfg.vocab_size = parallel::env().tp() > 1 ? Vp : h[3];
   cfg.n_layer = h[4], cfg.n_head = cfg.n_kv_head = h[5], cfg.n_embd = h[6];
-  const int64_t Vp = h[7], L = cfg.n_layer, C = cfg.n_embd, F = cfg.ffn_hidden();
+  const int64_t L = cfg.n_layer, C = cfg.n_embd, F = cfg.ffn_hidden();
   auto model = std::make_shared<nn::TransformerModel>(cfg);
-  auto sd = model->StateDict();
-  assign(sd, "lm_head.weight", read_f32(f, {Vp, C}).slice(0, 0, cfg.vocab_size));   // tied with transformer.wte.weight
-  assign(sd, "transformer.wpe.weight", read_f32(f, {cfg.block_size, C}));
-  const std::vector<std::pair<std::string, std::vector<int64_t>>> kinds = {
-      {"ln_1.weight", {C}},         {"ln_1.bias", {C}},        {"attn.c_attn.weight", {3 * C, C}}, {"attn.c_attn.bias", {3 * C}},
-      {"attn.c_proj.weight", {C, C}}, {"attn.c_proj.bias", {C}}, {"ln_2.weight", {C}},               {"ln_2.bias", {C}},
-      {"mlp.c_fc.weight", {F, C}},  {"mlp.c_fc.bias", {F}},    {"mlp.c_proj.weight", {C, F}},      {"mlp.c_proj.bias", {C}}};
-  for (const auto& [kind, shape] : kinds)
-    for (int64_t i = 0; i < L; ++i) assign(sd, "transformer.h." + std::to_string(i) + "." + kind, read_f32(f, shape));
-  assign(sd, "transformer.ln_f.weight", read_f32(f, {C}));
-  assign(sd, "transformer.ln_f.bias", read_f32(f, {C}));
+  ShardedAssigner put(f, *model);
+  if (model->stage.is_last_stage) {   // one tensor in the file: the projection, and (tied or copied) the lookup table
+    put.next("lm_head.weight", {Vp, C}, Shard::kRows, cfg.vocab_size);
+    put.also("transformer.wte.weight", "lm_head.weight");
+  } else {
+    put.next("transformer.wte.weight", {Vp, C}, Shard::kRows, cfg.vocab_size);
+  }
+  put.next("transformer.wpe.weight", {cfg.block_size, C}, Shard::kReplicated);
+  const std::vector<std::tuple<std::string, std::vector<int64_t>, Shard>> kinds = {
+      {"ln_1.weight", {C}, Shard::kReplicated},          {"ln_1.bias", {C}, Shard::kReplicated},
+      {"attn.c_attn.weight", {3 * C, C}, Shard::kQKVRows}, {"attn.c_attn.bias", {3 * C}, Shard::kQKVRows},
+      {"attn.c_proj.weight", {C, C}, Shard::kCols},      {"attn.c_proj.bias", {C}, Shard::kReplicated},
+      {"ln_2.weight", {C}, Shard::kReplicated},          {"ln_2.bias", {C}, Shard::kReplicated},
+      {"mlp.c_fc.weight", {F, C}, Shard::kRows},         {"mlp.c_fc.bias", {F}, Shard::kRows},
+      {"mlp.c_proj.weight", {C, F}, Shard::kCols},       {"mlp.c_proj.bias", {C}, Shard::kReplicated}};
+  for (const auto& [kind, shape, how] : kinds)
+    for (int64_t i = 0; i < L; ++i) put.next("transformer.h." + std::to_string(i) + "." + kind, shape, how);
+  put.next("transformer.ln_f.weight", {C}, Shard::kReplicated);
+  put.next("transformer.ln_f.bias", {C}, Shard::kReplicated);
   return model;
 }
 
@@ -83,15 +147,17 @@ inline std::shared_ptr<nn::TransformerModel> LoadLLaMA3FromLLMC(const std::strin
   const int64_t L = cfg.n_layer, C = cfg.n_embd, V = cfg.vocab_size, F = cfg.ffn_hidden();
   const int64_t Q = (cfg.n_head + 2 * cfg.n_kv_head) * cfg.head_dim();
   auto model = std::make_shared<nn::TransformerModel>(cfg);
-  auto sd = model->StateDict();
-  assign(sd, "transformer.wte.weight", read_f32(f, {V, C}));
-  const std::vector<std::pair<std::string, std::vector<int64_t>>> kinds = {
-      {"ln_1.weight", {C}},       {"attn.c_attn.weight", {Q, C}}, {"attn.c_proj.weight", {C, C}}, {"ln_2.weight", {C}},
-      {"mlp.c_fc.weight", {F, C}}, {"mlp.c_fc2.weight", {F, C}},   {"mlp.c_proj.weight", {C, F}}};
-  for (const auto& [kind, shape] : kinds)
-    for (int64_t i = 0; i < L; ++i) assign(sd, "transformer.h." + std::to_string(i) + "." + kind, read_f32(f, shape));
-  assign(sd, "transformer.ln_f.weight", read_f32(f, {C}));
-  assign(sd, "lm_head.weight", read_f32(f, {V, C}));
+  ShardedAssigner put(f, *model);
+  put.next("transformer.wte.weight", {V, C}, Shard::kRows);
+  const std::vector<std::tuple<std::string, std::vector<int64_t>, Shard>> kinds = {
+      {"ln_1.weight", {C}, Shard::kReplicated},    {"attn.c_attn.weight", {Q, C}, Shard::kQKVRows},
+      {"attn.c_proj.weight", {C, C}, Shard::kCols}, {"ln_2.weight", {C}, Shard::kReplicated},
+      {"mlp.c_fc.weight", {F, C}, Shard::kRows},   {"mlp.c_fc2.weight", {F, C}, Shard::kRows},
+      {"mlp.c_proj.weight", {C, F}, Shard::kCols}};
+  for (const auto& [kind, shape, how] : kinds)
+    for (int64_t i = 0; i < L; ++i) put.next("transformer.h." + std::to_string(i) + "." + kind, shape, how);
+  put.next("transformer.ln_f.weight", {C}, Shard::kReplicated);
+  put.next("lm_head.weight", {V, C}, Shard::kRows);
   return model;
 }
 
@@ -179,12 +245,20 @@ inline TrainerState LoadTrainerState(const std::string& path) {
   s.sp_size = static_cast<int64_t>(num("sp_size", 1)), s.pp_size = static_cast<int64_t>(num("pp_size", 1));
   return s;
 }
-// <root>/checkpoint_step_%06d/{model.ckpt, optimizer.ckpt, trainer_state.json}
+// <root>/checkpoint_step_%06d/{model.ckpt, optimizer.ckpt, trainer_state.json}; a rank of a parallel job
+// (global_rank >= 0) writes its slice under .../rank_%06d/ of the step directory, as the reference does
+// (src/checkpoint/checkpoint_manager.cc:33-39).
+inline std::string RankDirName(int global_rank) {
+  char name[32];
+  std::snprintf(name, sizeof(name), "rank_%06d", global_rank);
+  return name;
+}
 inline std::string SaveCheckpoint(const std::string& root, const TrainerState& state, const Module& model,
-                                  const std::map<std::string, Tensor>& optimizer_state) {
+                                  const std::map<std::string, Tensor>& optimizer_state, int global_rank = -1) {
   char name[64];
   std::snprintf(name, sizeof(name), "checkpoint_step_%06lld", static_cast<long long>(state.global_step));
   auto dir = std::filesystem::path(root) / name;
+  if (global_rank >= 0) dir /= RankDirName(global_rank);
   std::filesystem::create_directories(dir);
   SaveStateDict((dir / "model.ckpt").string(), model.StateDict());
   if (!optimizer_state.empty()) SaveStateDict((dir / "optimizer.ckpt").string(), optimizer_state);

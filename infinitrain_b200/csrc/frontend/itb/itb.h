@@ -8,6 +8,7 @@
 // Build: g++ -std=c++17 -I infinitrain_b200/csrc/frontend against libtorch (examples/cpp/build.py);
 // add -DITB_WITH_CUDA and link infinitrain_b200/_C.so for the sm_100a kernels.
 #pragma once
+#include "ddp.h"
 #include "distributed.h"
 #include "io.h"
 #include "layers.h"
@@ -15,6 +16,10 @@
 #include "module.h"
 #include "ops.h"
 #include "optim.h"
+#include "parallel_env.h"
+#include "pipeline.h"
 #include "precision.h"
+#include "process_group.h"
+#include "tensor_parallel.h"
 #include "tokenizer.h"
 #include "transformer.h"

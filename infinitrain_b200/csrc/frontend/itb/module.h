@@ -180,6 +180,8 @@ class Module : public std::enable_shared_from_this<Module> {
   }
 
  protected:
+  // A subclass that specialises an existing layer type (tensor-parallel linears) names itself.
+  void set_type(std::string type) { type_ = std::move(type); }
   Tensor& register_parameter(const std::string& name, Tensor t, bool requires_grad = true) {
     if (!parameters_.count(name)) param_order_.push_back(name);
     t.set_requires_grad(requires_grad);

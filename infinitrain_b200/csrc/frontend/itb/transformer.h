@@ -6,6 +6,7 @@
 #pragma once
 #include "layers.h"
 #include "precision.h"
+#include "tensor_parallel.h"
 
 namespace itb {
 namespace nn {
@@ -58,15 +59,31 @@ inline std::shared_ptr<Module> MakeNorm(const TransformerConfig& c) {
   return std::make_shared<RMSNorm>(c.n_embd, c.norm_eps);
 }
 
+// Every linear of the Transformer is a tensor-parallel layer that degrades to a plain Linear with one
+// tensor-parallel rank (reference: tensor_parallel.cc:31-34, causal_self_attention.cc:21-75).
+inline std::shared_ptr<Linear> MakeColumnLinear(int64_t in, int64_t out, bool bias) {
+  if (parallel::env().tp() == 1) return std::make_shared<Linear>(in, out, bias);
+  return std::make_shared<parallel::ColumnParallelLinear>(in, out, bias, /*gather_output=*/false, /*input_is_parallel=*/false,
+                                                          /*skip_bias_add=*/false, parallel::env().sequence_parallel);
+}
+inline std::shared_ptr<Linear> MakeRowLinear(int64_t in, int64_t out, bool bias) {
+  if (parallel::env().tp() == 1) return std::make_shared<Linear>(in, out, bias);
+  return std::make_shared<parallel::RowParallelLinear>(in, out, bias, /*reduce_output=*/true, /*input_is_parallel=*/true,
+                                                       /*skip_bias_add=*/false, parallel::env().sequence_parallel);
+}
+
 class CausalSelfAttention : public Module {
  public:
   explicit CausalSelfAttention(const TransformerConfig& c) : Module("CausalSelfAttention"), config(c) {
     TORCH_CHECK(c.n_embd % c.n_head == 0, "n_embd must be divisible by n_head");
     TORCH_CHECK(c.n_head % c.n_kv_head == 0, "n_head must be divisible by n_kv_head");
-    int64_t D = c.head_dim();
-    register_module("c_attn", std::make_shared<Linear>(c.n_embd, (c.n_head + 2 * c.n_kv_head) * D, c.add_bias_linear));
-    register_module("c_proj", std::make_shared<Linear>(c.n_embd, c.n_embd, c.add_bias_linear));
+    const int64_t D = c.head_dim(), tp = parallel::env().tp();
+    TORCH_CHECK(c.n_head % tp == 0 && c.n_kv_head % tp == 0, "head counts must be divisible by the tensor-parallel size");
+    local_heads = c.n_head / tp, local_kv_heads = c.n_kv_head / tp;
+    register_module("c_attn", MakeColumnLinear(c.n_embd, (c.n_head + 2 * c.n_kv_head) * D, c.add_bias_linear));
+    register_module("c_proj", MakeRowLinear(c.n_embd, c.n_embd, c.add_bias_linear));
   }
+  int64_t local_heads = 0, local_kv_heads = 0;   // heads of this tensor-parallel rank (the fused QKV rows are [q_r | k_r | v_r])
   // children are looked up by name on every call, so a wrapper put in their place (LoRA) takes over
   std::shared_ptr<Linear> linear(const char* name) const { return std::static_pointer_cast<Linear>(mutable_module(name)); }
   // in: x, [freqs_cis]; residual is added in the projection's epilogue
@@ -74,12 +91,12 @@ class CausalSelfAttention : public Module {
     if (utils::aligned_mode()) {   // through the children's call operators, so that their hooks see the tensors
       Tensor qkv = (*mutable_module("c_attn"))(x);
       auto rope = config.attention_type == AttentionType::kRoPE ? freqs : c10::nullopt;
-      Tensor y = (*mutable_module("c_proj"))(ops::attention_packed(qkv, config.n_head, config.n_kv_head, config.head_dim(), rope, 0, true));
+      Tensor y = (*mutable_module("c_proj"))(ops::attention_packed(qkv, local_heads, local_kv_heads, config.head_dim(), rope, 0, true));
       return residual.has_value() ? y + *residual : y;
     }
     Tensor qkv = linear("c_attn")->forward(x);
     auto rope = config.attention_type == AttentionType::kRoPE ? freqs : c10::nullopt;
-    Tensor y = ops::attention_packed(qkv, config.n_head, config.n_kv_head, config.head_dim(), rope, 0, true);
+    Tensor y = ops::attention_packed(qkv, local_heads, local_kv_heads, config.head_dim(), rope, 0, true);
     return linear("c_proj")->forward(y, residual);
   }
   TensorList Forward(const TensorList& in) override {
@@ -92,10 +109,9 @@ class MLP : public Module {
  public:
   explicit MLP(const TransformerConfig& c) : Module("MLP"), config(c) {
     int64_t hidden = c.ffn_hidden();
-    register_module("c_fc", std::make_shared<Linear>(c.n_embd, hidden, c.add_bias_linear));
-    if (c.activation_type == MLPType::kSwiGLU)
-      register_module("c_fc2", std::make_shared<Linear>(c.n_embd, hidden, c.add_bias_linear));
-    register_module("c_proj", std::make_shared<Linear>(hidden, c.n_embd, c.add_bias_linear));
+    register_module("c_fc", MakeColumnLinear(c.n_embd, hidden, c.add_bias_linear));
+    if (c.activation_type == MLPType::kSwiGLU) register_module("c_fc2", MakeColumnLinear(c.n_embd, hidden, c.add_bias_linear));
+    register_module("c_proj", MakeRowLinear(hidden, c.n_embd, c.add_bias_linear));
     // activation modules under the reference's names; the fused path does not go through them
     if (c.activation_type == MLPType::kSwiGLU) register_module("silu", std::make_shared<SwiGLU>());
     else register_module("gelu", std::make_shared<NewGELU>());
@@ -146,57 +162,133 @@ class TransformerLayer : public Module {
   std::shared_ptr<MLP> mlp;
 };
 
+// GPT-2 or LLaMA-3 depending on the config; with pipeline parallelism a rank holds only its stage:
+// the embeddings on the first stage, its chunks of consecutive layers (round robin over the stages,
+// reference pipeline_parallel.cc:42-77), the final norm and the head on the last stage.  State-dict
+// names are the reference's, with stage-local layer indices (transformer.h.<i>...).
 class TransformerModel : public Module {
  public:
   explicit TransformerModel(const TransformerConfig& c) : Module("Transformer"), config(c) {   // the reference's type name
+    const auto& pe = parallel::env();
+    TORCH_CHECK(c.vocab_size % pe.tp() == 0, "Vocab size should be divisible by TP world size");
+    stage = parallel::GetStageInfo(static_cast<int>(c.n_layer), pe.pp(), pe.pp_rank, pe.vpp);
     auto body = std::make_shared<ModuleDict>();
-    wte = std::make_shared<Embedding>(c.vocab_size, c.n_embd);
-    body->insert("wte", wte);
-    if (c.attention_type == AttentionType::kStandard) {
-      wpe = std::make_shared<Embedding>(c.block_size, c.n_embd);
-      body->insert("wpe", wpe);
+    if (stage.is_first_stage) {
+      if (pe.tp() > 1) wte = std::make_shared<parallel::VocabParallelEmbedding>(c.vocab_size, c.n_embd, pe.sequence_parallel);
+      else wte = std::make_shared<Embedding>(c.vocab_size, c.n_embd);
+      body->insert("wte", wte);
+      if (c.attention_type == AttentionType::kStandard) {
+        wpe = std::make_shared<Embedding>(c.block_size, c.n_embd);
+        body->insert("wpe", wpe);
+      }
     }
     h = std::make_shared<ModuleList>();
-    for (int64_t i = 0; i < c.n_layer; ++i) h->push_back(std::make_shared<TransformerLayer>(c));
-    body->insert("h", h);
-    ln_f = MakeNorm(c);
-    body->insert("ln_f", ln_f);
-    register_module("transformer", body);
-    register_module("lm_head", std::make_shared<Linear>(c.n_embd, c.vocab_size, c.add_bias_lm_head));
-    if (c.tie_weights) wte->tie(lm_head()->weight);   // one tensor serves the lookup and the projection
-  }
-  // idx [B, T] int64 -> logits [B, T, vocab]
-  Tensor forward(const Tensor& idx) {
-    int64_t T = idx.size(1);
-    TORCH_CHECK(T <= config.block_size, "sequence longer than block_size");
-    const bool aligned = utils::aligned_mode();
-    Tensor x;
-    if (aligned) {
-      x = (*wte)(idx);
-      if (wpe) x = x + (*wpe)(torch::arange(T, torch::TensorOptions().dtype(torch::kInt64).device(idx.device())));
-    } else {
-      x = ops::embedding(idx, wte->weight, wpe ? c10::optional<Tensor>(wpe->weight) : c10::nullopt, 0);
+    auto ranges = stage.layer_ranges_per_chunk;
+    std::sort(ranges.begin(), ranges.end());
+    for (const auto& r : ranges) {
+      chunk_begin.push_back(static_cast<int64_t>(h->size()));
+      for (int i = r.first; i < r.second; ++i) h->push_back(std::make_shared<TransformerLayer>(c));
     }
+    chunk_begin.push_back(static_cast<int64_t>(h->size()));
+    body->insert("h", h);
+    if (stage.is_last_stage) {
+      ln_f = MakeNorm(c);
+      body->insert("ln_f", ln_f);
+    }
+    register_module("transformer", body);
+    if (stage.is_last_stage) register_module("lm_head", MakeColumnLinear(c.n_embd, c.vocab_size, c.add_bias_lm_head));
+    // one tensor serves the lookup and the projection (only possible when one stage holds both)
+    if (c.tie_weights && pe.pp() == 1) wte->tie(lm_head()->weight);
+  }
+  int64_t num_chunks() const { return static_cast<int64_t>(chunk_begin.size()) - 1; }
+  // index into h of the layer numbered `global` in the whole model, -1 when another stage holds it
+  int64_t local_layer(int64_t global) const {
+    int64_t at = 0;
+    for (const auto& r : stage.layer_ranges_per_chunk) {
+      if (global >= r.first && global < r.second) return at + (global - r.first);
+      at += r.second - r.first;
+    }
+    return -1;
+  }
+
+  // ---- the three pieces a pipeline schedule strings together
+  // idx [B, T] int64 -> the residual stream [B, T (/ sp), C]
+  Tensor embed(const Tensor& idx) {
+    const int64_t T = idx.size(1);
+    TORCH_CHECK(T <= config.block_size, "sequence longer than block_size");
+    const auto& pe = parallel::env();
+    if (pe.tp() == 1) {
+      if (utils::aligned_mode()) {
+        Tensor x = (*wte)(idx);
+        if (wpe) x = x + (*wpe)(torch::arange(T, torch::TensorOptions().dtype(torch::kInt64).device(idx.device())));
+        return x;
+      }
+      return ops::embedding(idx, wte->weight, wpe ? c10::optional<Tensor>(wpe->weight) : c10::nullopt, 0);
+    }
+    Tensor x = std::static_pointer_cast<parallel::VocabParallelEmbedding>(wte)->lookup(idx);
+    if (wpe) {   // positions are added after the reduction; under sequence parallelism this rank holds a slice of T
+      const int64_t t_local = x.size(1), start = pe.sequence_parallel ? pe.tp_rank * t_local : 0;
+      x = x + wpe->weight.slice(0, start, start + t_local).to(x.scalar_type());
+    }
+    return x;
+  }
+  // the layers of local chunk `ci` (all layers when ci < 0); T_full is the sequence length before any sharding
+  Tensor run_layers(Tensor x, int64_t ci, int64_t T_full) {
     c10::optional<Tensor> freqs;
     if (config.attention_type == AttentionType::kRoPE) {
       if (!freqs_cis_.defined() || freqs_cis_.device() != x.device())
         freqs_cis_ = ops::precompute_freqs_cis(config.head_dim(), 2 * config.block_size, config.rope_theta, x.device());
-      freqs = freqs_cis_.slice(0, 0, T);
+      freqs = freqs_cis_.slice(0, 0, T_full);
     }
-    if (aligned) {
-      for (auto& layer : *h) {
+    const int64_t b = ci < 0 ? 0 : chunk_begin[ci], e = ci < 0 ? static_cast<int64_t>(h->size()) : chunk_begin[ci + 1];
+    const bool aligned = utils::aligned_mode();
+    for (int64_t i = b; i < e; ++i) {
+      auto layer = h->at(static_cast<size_t>(i));
+      if (aligned) {
         TensorList in = {x};
         if (freqs.has_value()) in.push_back(*freqs);
         x = (*layer)(in)[0];
+      } else {
+        x = std::static_pointer_cast<TransformerLayer>(layer)->forward(x, freqs);
       }
-      return (*mutable_module("lm_head"))((*ln_f)(x));
     }
-    for (auto& layer : *h) x = std::static_pointer_cast<TransformerLayer>(layer)->forward(x, freqs);
+    return x;
+  }
+  // final norm + output projection: logits [B, T, vocab / tp]
+  Tensor head(const Tensor& x) {
+    if (utils::aligned_mode()) return (*mutable_module("lm_head"))((*ln_f)(x));
     return lm_head()->forward((*ln_f)(x));
+  }
+  // One local chunk of a pipeline stage: `in` is the token ids for the first chunk of the first stage,
+  // the previous chunk's activation otherwise; the last chunk of the last stage returns logits.
+  Tensor forward_chunk(int64_t ci, const Tensor& in, int64_t T_full) {
+    Tensor x = (stage.is_first_stage && ci == 0) ? embed(in) : in;
+    x = run_layers(x, ci, T_full);
+    return (stage.is_last_stage && ci == num_chunks() - 1) ? head(x) : x;
+  }
+  // idx [B, T] int64 -> logits [B, T, vocab / tp] (whole model on this rank: pp == 1)
+  Tensor forward(const Tensor& idx) {
+    TORCH_CHECK(stage.is_first_stage && stage.is_last_stage, "forward() needs the whole model; use forward_chunk under pipeline parallelism");
+    return head(run_layers(embed(idx), -1, idx.size(1)));
   }
   TensorList Forward(const TensorList& in) override { return {forward(in[0])}; }
 
+  // Parameters that are replicated over the tensor-parallel group but see a slice of the sequence
+  // under sequence parallelism: their gradients are partial sums (norm weights, position table,
+  // row-parallel biases).
+  TensorList SequenceParallelReplicated() const {
+    TensorList out;
+    for (const auto& [name, p] : NamedParameters()) {
+      const bool norm = name.find("ln_") != std::string::npos;
+      const bool row_bias = name.size() > 11 && name.compare(name.size() - 11, 11, "c_proj.bias") == 0;
+      if (norm || row_bias || name.find("wpe.weight") != std::string::npos) out.push_back(p);
+    }
+    return out;
+  }
+
   TransformerConfig config;
+  parallel::StageInfo stage;
+  std::vector<int64_t> chunk_begin;     // first layer (index into h) of every local chunk, plus the end
   std::shared_ptr<Embedding> wte, wpe;
   std::shared_ptr<ModuleList> h;
   std::shared_ptr<Module> ln_f;

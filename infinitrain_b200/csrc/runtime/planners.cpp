@@ -1,4 +1,10 @@
-// Flat-buffer layout and pipeline schedule planners (pure host code).
+// Flat-buffer layout and pipeline schedule planners (pure host code).  Compiled as a translation unit
+// of the extension; a header-only user (the C++ frontend) defines ITB_PLANNERS_INLINE as `inline` and
+// includes this file.
+#pragma once
+#ifndef ITB_PLANNERS_INLINE
+#define ITB_PLANNERS_INLINE
+#endif
 #include <algorithm>
 #include <numeric>
 
@@ -6,9 +12,9 @@
 
 namespace itb {
 
-static int64_t pad_to(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+static inline int64_t pad_to(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
-FlatLayoutResult PlanFlatLayout(const std::vector<int64_t>& numels, int64_t dp_size, bool shard,
+ITB_PLANNERS_INLINE FlatLayoutResult PlanFlatLayout(const std::vector<int64_t>& numels, int64_t dp_size, bool shard,
                                 int64_t bucket_size, bool pad_for_busbw) {
   FlatLayoutResult r;
   const size_t n = numels.size();
@@ -50,11 +56,11 @@ FlatLayoutResult PlanFlatLayout(const std::vector<int64_t>& numels, int64_t dp_s
   return r;
 }
 
-static PipeTask make_task(int step, int mb, int g, int stages, int chunks, bool fwd) {
+static inline PipeTask make_task(int step, int mb, int g, int stages, int chunks, bool fwd) {
   return PipeTask{step, mb, g, g / stages, g % stages, fwd, g == 0, g == chunks - 1};
 }
 
-std::vector<PipeTask> GpipeSchedule(int n, int stages, int vpp) {
+ITB_PLANNERS_INLINE std::vector<PipeTask> GpipeSchedule(int n, int stages, int vpp) {
   std::vector<PipeTask> out;
   const int chunks = stages * vpp, total = n + chunks - 1;
   for (int step = 0; step < total; ++step)
@@ -73,7 +79,7 @@ std::vector<PipeTask> GpipeSchedule(int n, int stages, int vpp) {
   return out;
 }
 
-std::vector<PipeTask> Interleaved1F1BSchedule(int n, int stages, int vpp) {
+ITB_PLANNERS_INLINE std::vector<PipeTask> Interleaved1F1BSchedule(int n, int stages, int vpp) {
   std::vector<PipeTask> out;
   if (n <= 0 || stages <= 0 || vpp <= 0) return out;
   const int chunks = stages * vpp, warm = chunks - 1, total = 2 * warm + n;

@@ -1,0 +1,141 @@
+"""The C++ frontend's parallel stack (itb/parallel_env.h, process_group.h, tensor_parallel.h, ddp.h,
+pipeline.h) end to end: the C++ trainer started as several CPU ranks by the C++ launcher must follow the
+loss trajectory of one rank on the same weight and token files, whatever mix of tensor / sequence /
+pipeline / data parallelism and ZeRO stage splits the work (reference: the per-strategy runs of
+scripts/test_config.json, compared by scripts/compare_loss.py)."""
+import os
+import re
+import socket
+import subprocess
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ENV = {**os.environ, "OMP_NUM_THREADS": "1"}
+
+
+def _free_port() -> int:
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
+def _losses(text):
+    return [float(m.group(1)) for m in re.finditer(r"step\s+\d+/\d+\s+\|\s+train loss\s+([\d.]+)", text)]
+
+
+@pytest.fixture(scope="module")
+def binaries():
+    import importlib.util
+
+    from infinitrain_b200 import _ext
+
+    spec = importlib.util.spec_from_file_location("itb_cpp_build", os.path.join(ROOT, "examples", "cpp", "build.py"))
+    cpp_build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cpp_build)
+    launcher = _ext.launcher_path()
+    if not launcher.exists():
+        _ext.build_launcher()
+    return str(launcher), str(cpp_build.build(cuda=False))
+
+
+@pytest.fixture(scope="module")
+def files(tmp_path_factory):
+    from infinitrain_b200.data import write_token_file
+    from infinitrain_b200.models import llmc
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+    from infinitrain_b200.parallel import global_env as genv
+
+    d = tmp_path_factory.mktemp("cpppar")
+    genv.InitAllEnv(world_size=1, rank=0)
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, 256, (4 * 64 * 40 + 1,), generator=g).tolist()
+    write_token_file(str(d / "tokens16.bin"), toks)
+    write_token_file(str(d / "tokens32.bin"), toks, llama3=True)
+    torch.manual_seed(42)
+    gcfg = TransformerConfig.GPT2(n_layer=4, n_embd=96, n_head=12, n_kv_head=12, vocab_size=256, original_vocab_size=256,
+                                  block_size=64)
+    lcfg = TransformerConfig.LLaMA3(n_layer=4, n_embd=64, n_head=4, n_kv_head=2, vocab_size=256, original_vocab_size=256,
+                                    block_size=64, multiple_of=16, ffn_dim_multiplier=1.5)
+    for cfg, name, write in ((gcfg, "gpt2.bin", llmc.write_gpt2_llmc), (lcfg, "llama3.bin", llmc.write_llama3_llmc)):
+        m = TransformerModel(cfg)
+        with torch.no_grad():
+            for p in m.parameters():   # biases and norm weights away from 0 / 1, so that a lost gradient shows
+                p.normal_(0, 0.1) if p.dim() > 1 else p.add_(torch.randn_like(p) * 0.1)
+        write(str(d / name), cfg, llmc.full_state_dict(m))
+    return d
+
+
+def _train(binaries, files, family, ranks, *extra, iters=4):
+    launcher, trainer = binaries
+    tokens = "tokens16.bin" if family == "gpt2" else "tokens32.bin"
+    cmd = [trainer, "--family", family, "--device", "cpu", "--llmc_filepath", f"{family}.bin", "--input_bin", tokens,
+           "--batch_size", "2", "--sequence_length", "64", "--total_batch_size", "1024", "--num_iteration", str(iters),
+           "--dtype", "float32", *extra]
+    if ranks > 1:
+        cmd = [launcher, f"--nproc_per_node={ranks}", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", *cmd]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=files, env=ENV)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    losses = _losses(r.stdout + r.stderr)
+    assert len(losses) == iters, (r.stdout + r.stderr)[-3000:]
+    return losses, r.stdout + r.stderr
+
+
+LLAMA = ("--learning_rate", "0.01", "--optimizer", "adam")
+GPT2 = ("--learning_rate", "0.05", "--optimizer", "sgd")
+
+
+@pytest.fixture(scope="module")
+def single(binaries, files):
+    return {"llama3": _train(binaries, files, "llama3", 1, *LLAMA)[0], "gpt2": _train(binaries, files, "gpt2", 1, *GPT2)[0]}
+
+
+@pytest.mark.parametrize("family,ranks,flags", [
+    ("gpt2", 2, ("--tensor_parallel", "2")),
+    ("gpt2", 2, ("--tensor_parallel", "2", "--sequence_parallel")),
+    ("llama3", 2, ("--tensor_parallel", "2", "--sequence_parallel")),
+    ("llama3", 2, ("--pipeline_parallel", "2", "--pipeline_schedule", "gpipe")),
+    ("llama3", 2, ("--pipeline_parallel", "2", "--virtual_pipeline_parallel", "2")),
+    ("llama3", 2, ("--zero_stage", "1")),
+    ("llama3", 2, ("--zero_stage", "2", "--no_overlap_grad_reduce")),
+    ("llama3", 4, ("--pipeline_parallel", "2", "--zero_stage", "1")),
+    ("llama3", 8, ("--tensor_parallel", "2", "--sequence_parallel", "--pipeline_parallel", "2", "--virtual_pipeline_parallel", "2",
+                   "--zero_stage", "1")),
+], ids=lambda v: "_".join(s.strip("-") for s in v) if isinstance(v, tuple) else str(v))
+def test_parallel_run_follows_the_single_rank_trajectory(binaries, files, single, family, ranks, flags):
+    losses, log = _train(binaries, files, family, ranks, *(LLAMA if family == "llama3" else GPT2), *flags)
+    want = single[family]
+    assert max(abs(a - b) for a, b in zip(losses, want)) <= 2e-5, list(zip(losses, want))
+    tp = int(flags[flags.index("--tensor_parallel") + 1]) if "--tensor_parallel" in flags else 1
+    pp = int(flags[flags.index("--pipeline_parallel") + 1]) if "--pipeline_parallel" in flags else 1
+    assert f"DP={ranks // (tp * pp)}, TP={tp}, SP={tp if '--sequence_parallel' in flags else 1}, PP={pp}" in log
+
+
+def test_gpt2_pipeline_unties_the_embedding_like_the_reference_does(binaries, files, single):
+    """Two stages cannot share one tensor between the lookup and the output projection: the first loss is
+    the single-rank one (same weights), later ones drift by the missing tie only."""
+    losses, log = _train(binaries, files, "gpt2", 2, *GPT2, "--pipeline_parallel", "2")
+    assert abs(losses[0] - single["gpt2"][0]) <= 2e-6
+    assert max(abs(a - b) for a, b in zip(losses, single["gpt2"])) <= 5e-3
+    assert "pipeline schedule (1f1b)" in log and "F0.0" in log
+
+
+def test_model_parallel_checkpoint_resumes_per_rank(binaries, files, tmp_path):
+    """Every rank of a tensor-parallel job saves and reloads its own slice; the resumed run continues the
+    uninterrupted one."""
+    flags = (*LLAMA, "--tensor_parallel", "2")
+    full, _ = _train(binaries, files, "llama3", 2, *flags, iters=4)
+    _train(binaries, files, "llama3", 2, *flags, "--save", str(tmp_path), "--save_interval", "2", iters=2)
+    ckpt = tmp_path / "checkpoint_step_000002"
+    assert sorted(p.name for p in ckpt.iterdir()) == ["rank_000000", "rank_000001"]
+    assert (ckpt / "rank_000001" / "model.ckpt").exists() and (ckpt / "rank_000001" / "trainer_state.json").exists()
+    launcher, trainer = binaries
+    cmd = [launcher, "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", trainer, "--family", "llama3",
+           "--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin", "--batch_size", "2",
+           "--sequence_length", "64", "--total_batch_size", "1024", "--num_iteration", "4", "--dtype", "float32", *flags,
+           "--load", str(ckpt)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=files, env=ENV)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    resumed = _losses(r.stdout + r.stderr)
+    assert len(resumed) == 2 and max(abs(a - b) for a, b in zip(resumed, full[2:])) <= 2e-5, (resumed, full)
