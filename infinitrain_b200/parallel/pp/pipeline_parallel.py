@@ -5,12 +5,14 @@ Reference: infini_train/src/nn/parallel/pp/{pipeline_parallel,pipeline_stage,pip
 interleaved by default, GPipe selectable) and steps the optimizer; it returns the summed
 ``loss / n`` on the last stage and 0 elsewhere.
 
-Transfers are explicit: a forward task receives its input (if it is not the first chunk), runs the
-chunk and sends the output on asynchronously; a backward task receives the output gradient (or
-computes the loss), back-propagates through the chunk and sends the input gradient back.  Sends
-are asynchronous and kept alive until completion, receives block the stream (NCCL) or the host
-(gloo).  With data parallelism each chunk is a DistributedDataParallel module and gradient
-synchronisation is armed only for the last micro-batch.
+Transfers are organised by STEP of the task table, not by task: after the tasks of step b every stage
+runs one exchange that holds its sends of what step b produced and its receives of what the
+neighbours produced in step b, all in one batched point-to-point call.  Two neighbours that owe each
+other a tensor in the same step (an activation one way, a gradient the other: the steady state of
+1F1B) therefore cannot block one another, and an exchange of step b depends only on exchanges of
+earlier steps, whatever the transport buffers.  A tensor that arrives before its consumer's step
+waits in a dictionary.  With data parallelism each chunk is a DistributedDataParallel module and
+gradient synchronisation is armed only for the last micro-batch.
 """
 from __future__ import annotations
 
@@ -64,7 +66,7 @@ class PipelineSchedule:
         self.vpp = vpp_size if vpp_size is not None else genv.GetVirtualPipelineParallelSize()
         self.boundary_dtype = boundary_dtype
         self._printed = False
-        self._pending_sends = []
+        self._messages = None
 
     # ------------------------------------------------------------------ task list
     def tasks(self) -> List[Task]:
@@ -72,21 +74,50 @@ class PipelineSchedule:
         return gen(self.n, self.num_stages, self.vpp)
 
     # ------------------------------------------------------------------ transfers
-    def _recv(self, peer: int, dtype: torch.dtype) -> torch.Tensor:
-        buf = torch.empty(self.stage.recv_shape()[0], dtype=dtype, device=self.stage.device())
-        self.pg.Recv([buf], peer, async_op=False)
+    def messages(self, schedule: List[Task]):
+        """What every step produces for another chunk: step -> [(key, src stage, dst stage)] in task
+        order, with key = (is activation, micro-batch, consumer's global chunk)."""
+        S = self.num_stages
+        when = {(t.is_forward, t.microbatch_id, t.global_chunk_id): t.step for t in schedule}
+        out = {}
+        for t in schedule:
+            if t.is_forward and not t.is_last_chunk:
+                key = (True, t.microbatch_id, t.global_chunk_id + 1)
+            elif not t.is_forward and not t.is_first_chunk:
+                key = (False, t.microbatch_id, t.global_chunk_id - 1)
+            else:
+                continue
+            assert when[key] > t.step, "schedule consumes a tensor before the step after its production"
+            out.setdefault(t.step, []).append((key, t.stage_id, key[2] % S))
+        return out
+
+    def _exchange(self, msgs, outbox, inbox, in_flight, dtype):
+        me = self.stage.stage_index()
+        ops, received = [], []
+        for key, src, dst in msgs:
+            if src == me and dst == me:
+                inbox[key] = (outbox[key], None)
+            elif src == me:
+                ops.append((True, outbox[key], dst))
+            elif dst == me:
+                buf = torch.empty(self.stage.recv_shape()[0], dtype=dtype, device=self.stage.device())
+                ops.append((False, buf, src))
+                received.append((key, buf))
+        if not ops:
+            return
+        work = self.pg.BatchSendRecv(ops, async_op=True)
+        for key, buf in received:
+            inbox[key] = (buf, work)
+        sent = [t for is_send, t, _ in ops if is_send]
+        if sent:
+            in_flight.append((work, sent))   # the payloads live until the step's end
+
+    @staticmethod
+    def _take(inbox, key):
+        buf, work = inbox.pop(key)
+        if work is not None:
+            work.WaitNonBlocking()
         return buf
-
-    def _send(self, t: torch.Tensor, peer: int):
-        t = t.detach().contiguous()
-        w = self.pg.Send([t], peer, async_op=True)
-        self._pending_sends.append((w, t))   # keep the payload alive until the send has completed
-
-    def _drain_sends(self):
-        for w, _ in self._pending_sends:
-            if w is not None:
-                w.WaitNonBlocking()
-        self._pending_sends.clear()
 
     # ------------------------------------------------------------------ execution
     def StepMicroBatches(self, microbatch_inputs, microbatch_targets, loss_fn, dtype) -> float:
@@ -96,56 +127,64 @@ class PipelineSchedule:
         if not self._printed and sidx == 0 and genv.MyRank() == 0:
             self._printed = True
             self.schedule_table = PrintScheduleTable(schedule, self.n, S, self.vpp)
+        if self._messages is None:
+            self._messages = self.messages(schedule)
         dev = stage.device()
         tdtype = to_torch_dtype(dtype) if not isinstance(dtype, torch.dtype) else dtype
         use_autocast = tdtype != torch.float32
         bdtype = self.boundary_dtype or (tdtype if (use_autocast and torch.device(dev).type == "cuda") else torch.float32)
         saved = {}          # (local chunk, mb) -> (input tensor or None, output tensor)
+        inbox, in_flight = {}, []
         total_loss = torch.zeros((), device=dev)
         last_bwd = {}       # local chunk -> index of its last backward task (arms DDP sync)
         for i, t in enumerate(schedule):
             if t.stage_id == sidx and not t.is_forward:
                 last_bwd[t.local_chunk_idx] = i
+        steps = (max(t.step for t in schedule) + 1) if schedule else 0
+        by_step = {}
         for i, t in enumerate(schedule):
-            if t.stage_id != sidx:
-                continue
-            mb, lc = t.microbatch_id, t.local_chunk_idx
-            chunk = stage.chunks_[lc]
-            if t.is_forward:
-                if t.is_first_chunk:
-                    x_in, inputs = None, (microbatch_inputs[mb],)
-                else:
-                    peer = S - 1 if stage.IsFirstStage() else stage.prev_rank()
-                    x_in = self._recv(peer, bdtype).requires_grad_(True)
-                    inputs = (x_in,)
-                with AutocastGuard(dtype=tdtype, enabled=use_autocast):
-                    out = stage.ForwardOneChunk(inputs, lc)
-                saved[(lc, mb)] = (x_in, out)
-                if not t.is_last_chunk:
-                    peer = 0 if stage.IsLastStage() else stage.next_rank()
-                    self._send(out.to(bdtype), peer)
-            else:
-                x_in, out = saved.pop((lc, mb))
-                sync_ctx = nullcontext()
-                if hasattr(chunk, "no_sync"):
-                    if i != last_bwd[lc]:
-                        sync_ctx = chunk.no_sync()
-                    elif getattr(chunk, "reducer", None) is not None:
-                        chunk.reducer.PrepareForBackward()   # arm the bucket counters for this pass only
-                with sync_ctx:
-                    if t.is_last_chunk:
-                        with AutocastGuard(dtype=tdtype, enabled=use_autocast):
-                            loss = loss_fn(out, microbatch_targets[mb].to(out.device)) / self.n
-                        total_loss += loss.detach().float()
-                        loss.backward()
+            if t.stage_id == sidx:
+                by_step.setdefault(t.step, []).append((i, t))
+        for step in range(steps):
+            outbox = {}
+            for i, t in by_step.get(step, ()):
+                mb, lc = t.microbatch_id, t.local_chunk_idx
+                chunk = stage.chunks_[lc]
+                if t.is_forward:
+                    if t.is_first_chunk:
+                        x_in, inputs = None, (microbatch_inputs[mb],)
                     else:
-                        peer = 0 if stage.IsLastStage() else stage.next_rank()
-                        g = self._recv(peer, bdtype)
-                        out.backward(g.to(out.dtype))
-                if not t.is_first_chunk:
-                    peer = S - 1 if stage.IsFirstStage() else stage.prev_rank()
-                    self._send(x_in.grad.to(bdtype), peer)
-        self._drain_sends()
+                        x_in = self._take(inbox, (True, mb, t.global_chunk_id)).requires_grad_(True)
+                        inputs = (x_in,)
+                    with AutocastGuard(dtype=tdtype, enabled=use_autocast):
+                        out = stage.ForwardOneChunk(inputs, lc)
+                    saved[(lc, mb)] = (x_in, out)
+                    if not t.is_last_chunk:
+                        outbox[(True, mb, t.global_chunk_id + 1)] = out.detach().to(bdtype).contiguous()
+                else:
+                    x_in, out = saved.pop((lc, mb))
+                    sync_ctx = nullcontext()
+                    if hasattr(chunk, "no_sync"):
+                        if i != last_bwd[lc]:
+                            sync_ctx = chunk.no_sync()
+                        elif getattr(chunk, "reducer", None) is not None:
+                            chunk.reducer.PrepareForBackward()   # arm the bucket counters for this pass only
+                    with sync_ctx:
+                        if t.is_last_chunk:
+                            with AutocastGuard(dtype=tdtype, enabled=use_autocast):
+                                loss = loss_fn(out, microbatch_targets[mb].to(out.device)) / self.n
+                            total_loss += loss.detach().float()
+                            loss.backward()
+                        else:
+                            g = self._take(inbox, (False, mb, t.global_chunk_id))
+                            out.backward(g.to(out.dtype))
+                    if not t.is_first_chunk:
+                        outbox[(False, mb, t.global_chunk_id - 1)] = x_in.grad.to(bdtype).contiguous()
+            self._exchange(self._messages.get(step, ()), outbox, inbox, in_flight, bdtype)
+        for w, _ in in_flight:
+            if w is not None:
+                w.WaitNonBlocking()
+        assert not inbox and not saved, "pipeline step ended with undelivered tensors"
         return float(total_loss.item())
 
     def Step(self, input, target, optimizer, loss_fn, dtype) -> float:

@@ -220,6 +220,16 @@ class ProcessGroup:
         works = [dist.irecv(t, src=self.ranks[src_group_rank], group=self.pg) for t in tensors]
         return self._p2p(works, async_op)
 
+    def BatchSendRecv(self, ops: Sequence[tuple], async_op: bool = False):
+        """``ops`` is a list of (is_send, tensor, peer group rank).  All transfers progress together
+        (one NCCL group), so two ranks that each send to and receive from the other in one exchange
+        cannot block one another; transfers between one pair of ranks match in list order."""
+        if not ops:
+            return None
+        p2p = [dist.P2POp(dist.isend if is_send else dist.irecv, t, self.ranks[peer], group=self.pg)
+               for is_send, t, peer in ops]
+        return self._p2p(dist.batch_isend_irecv(p2p), async_op)
+
     def _p2p(self, works, async_op):
         class _Multi:
             def __init__(self, ws):
