@@ -48,3 +48,25 @@ def test_tp_protocol_model_and_its_negative_control(tmp_path):
     subprocess.run(["g++", "-std=c++17", "-O1", "-DITB_MODEL_SLACK=1", src, "-o", str(bad), "-pthread"], check=True)
     r = subprocess.run([str(bad)], capture_output=True, text=True, timeout=300)
     assert r.returncode != 0 and "protocol violations" in r.stderr
+
+
+@pytest.mark.skipif(shutil.which("cmake") is None, reason="needs cmake")
+def test_parallel_stack_under_thread_sanitizer(tmp_path):
+    """The C++ frontend's process groups, DDP reducer, ZeRO optimizer and pipeline executor, with the
+    ranks played by threads (tests/native/test_parallel.cc), built with -fsanitize=thread through the
+    CMake project's ITB_SANITIZE option: no data race may be reported."""
+    build = tmp_path / "tsan"
+    gen = ["-G", "Ninja"] if shutil.which("ninja") else []
+    cxx = ["-DCMAKE_CXX_COMPILER=/usr/bin/g++"] if os.path.exists("/usr/bin/g++") else []
+    cfg = subprocess.run(["cmake", "-S", ROOT, "-B", str(build), *gen, *cxx, "-DITB_WITH_CUDA=OFF", "-DITB_SANITIZE=thread"],
+                         capture_output=True, text=True, timeout=600)
+    assert cfg.returncode == 0, cfg.stdout[-3000:] + cfg.stderr[-3000:]
+    b = subprocess.run(["cmake", "--build", str(build), "--target", "test_parallel_cpu"], capture_output=True, text=True,
+                       timeout=3000)
+    if b.returncode != 0 and "cannot find" in (b.stdout + b.stderr) and "tsan" in (b.stdout + b.stderr):
+        pytest.skip("sanitizer runtime not installed")
+    assert b.returncode == 0, b.stdout[-4000:] + b.stderr[-3000:]
+    r = subprocess.run([str(build / "test_parallel_cpu"), "--device", "cpu"], capture_output=True, text=True, timeout=900)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and "0 failed" in out, out[-4000:]
+    assert "ThreadSanitizer" not in out, out[-6000:]
