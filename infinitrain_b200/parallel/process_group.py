@@ -52,8 +52,9 @@ class CclStatus(enum.IntEnum):
 class Work:
     """Handle of one asynchronous collective (reference: work.h:19-30, work.cc)."""
 
-    def __init__(self, handle=None, post=None, device: Optional[torch.device] = None):
+    def __init__(self, handle=None, post=None, device: Optional[torch.device] = None, group: Optional["ProcessGroup"] = None):
         self._handle = handle
+        self._group = group          # asked for the communicator's asynchronous error state
         self._post = post            # runs once after completion (e.g. the division of a gloo "avg")
         self._done = handle is None
         self._exception: Optional[BaseException] = None
@@ -115,6 +116,20 @@ class Work:
         return self._exception is None and self.IsCompleted()
 
     def CheckCclStatus(self) -> CclStatus:
+        """Error state of this operation and of its communicator (reference: work.cc:118-132 asks
+        ``ncclCommGetAsyncError``; here the NCCL backend's watchdog keeps that state and
+        ``get_error()`` reports it).  An error found this way is kept as the Work's exception."""
+        if self._exception is None and self._handle is not None and hasattr(self._handle, "exception"):
+            try:
+                e = self._handle.exception()
+                if e is not None:
+                    self._exception = e if isinstance(e, BaseException) else RuntimeError(f"collective failed: {e}")
+            except Exception as e:  # noqa: BLE001
+                self._exception = e
+        if self._exception is None and self._group is not None:
+            code = self._group.AsyncError()
+            if code != 0:
+                self._exception = RuntimeError(f"CCL async error on group {self._group.name}: code {code}")
         if self._exception is not None:
             return CclStatus.kError
         return CclStatus.kSuccess if self.IsCompleted() else CclStatus.kInProgress
@@ -150,8 +165,22 @@ class ProcessGroup:
     def _trivial(self) -> bool:
         return self.world_size <= 1 or self.pg is None
 
+    def AsyncError(self) -> int:
+        """0 = healthy.  For NCCL groups: the communicator's asynchronous error as the backend's
+        watchdog sees it (1 time-out, 2 communicator error, 3 error on a remote rank)."""
+        if self.pg is None:
+            return 0
+        try:
+            backend = self.pg._get_backend(torch.device("cuda")) if self.backend == "nccl" else None
+        except Exception:  # noqa: BLE001
+            backend = None
+        if backend is None or not hasattr(backend, "get_error"):
+            return 0
+        err = backend.get_error()
+        return int(getattr(err, "value", err))
+
     def _wrap(self, handle, async_op, post=None, device=None):
-        w = Work(handle, post, device)
+        w = Work(handle, post, device, self)
         if not async_op:
             w.WaitNonBlocking()
             return None
@@ -242,7 +271,7 @@ class ProcessGroup:
             def is_completed(self):
                 return all(w.is_completed() for w in self.ws)
 
-        w = Work(_Multi(works))
+        w = Work(_Multi(works), group=self)
         if not async_op:
             w.WaitNonBlocking()
             return None

@@ -243,3 +243,52 @@ def test_file_rendezvous(tmp_path):
     outs = [p.communicate(timeout=180)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
     assert "rank 0 ok" in outs[0] and "rank 1 ok" in outs[1]
+
+
+def test_work_reports_the_communicators_asynchronous_error():
+    """CheckCclStatus asks the operation and then its communicator (reference: work.cc:118-132 over
+    ncclCommGetAsyncError); the NCCL call is faked here: a backend whose get_error() turns to
+    COMM_ERROR after the collective was issued."""
+    from infinitrain_b200.parallel.process_group import CclStatus, ProcessGroup, Work
+
+    class FakeBackend:
+        code = 0
+
+        def get_error(self):
+            return self.code
+
+    class FakePg:
+        def __init__(self):
+            self.b = FakeBackend()
+
+        def _get_backend(self, device):
+            return self.b
+
+    class Group(ProcessGroup):
+        backend = "nccl"
+
+    class Handle:
+        done = False
+
+        def is_completed(self):
+            return self.done
+
+        def exception(self):
+            return None
+
+        def wait(self):
+            self.done = True
+
+    g = Group("DP0", [0, 1], FakePg())
+    assert g.AsyncError() == 0
+    w = Work(Handle(), group=g)
+    assert w.CheckCclStatus() == CclStatus.kInProgress and not w.IsSuccess()
+    g.pg.b.code = 2   # the watchdog saw the communicator fail
+    assert g.AsyncError() == 2
+    assert w.CheckCclStatus() == CclStatus.kError
+    assert "DP0" in str(w.exception()) and not w.IsSuccess()
+    # an operation whose own handle carries the error
+    h = Handle()
+    h.exception = lambda: RuntimeError("remote rank gone")
+    w2 = Work(h, group=Group("TP0", [0, 1], FakePg()))
+    assert w2.CheckCclStatus() == CclStatus.kError and "remote rank gone" in str(w2.exception())

@@ -86,3 +86,45 @@ def test_training_reduces_loss_with_fused_optimizer():
     # the bf16 shadow the GEMMs read is the rounded fp32 master
     w = model.lm_head.weight
     assert torch.equal(w._itb_shadow, w.detach().bfloat16())
+
+
+@pytest.mark.parametrize("family", ["gpt2", "llama3"])
+def test_same_seed_runs_are_bit_identical_where_the_algorithm_is(family):
+    """Two runs from the same seed on the same inputs.  The forward pass uses fixed reduction orders
+    throughout (GEMM tiles, attention, norms), so the logits must agree bit for bit.  Three reductions
+    are unordered fp32 sums and make what follows them reproducible only to rounding: the mean of the
+    row losses (atomics), the dQ accumulation of the attention backward over key tiles (bulk
+    add-reductions) and the token-table gradient (atomics on shared ids).  Loss and gradients are
+    therefore compared with a tight tolerance instead."""
+    from infinitrain_b200.autocast import AutocastGuard
+    from infinitrain_b200.datatype import DataType
+    from infinitrain_b200.device import DeviceType
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+
+    _setup()
+
+    def once():
+        torch.manual_seed(123)
+        if family == "gpt2":
+            cfg = TransformerConfig.GPT2(n_layer=2, n_embd=256, n_head=4, n_kv_head=4, vocab_size=1001,
+                                         original_vocab_size=1001, block_size=256)
+        else:
+            cfg = TransformerConfig.LLaMA3(n_layer=2, n_embd=256, n_head=4, n_kv_head=2, vocab_size=1000,
+                                           original_vocab_size=1000, block_size=256, multiple_of=64)
+        model = TransformerModel(cfg).cuda()
+        g = torch.Generator().manual_seed(5)
+        x = torch.randint(0, 1000, (4, 256), generator=g).cuda()
+        y = torch.randint(0, 1000, (4, 256), generator=g).cuda()
+        with torch.no_grad(), AutocastGuard(DeviceType.kCUDA, DataType.kBFLOAT16, enabled=True):
+            logits = model(x).detach().clone()
+        losses = _run(model, x, y, autocast=True, steps=1)
+        grads = {n: p.grad.detach().float().clone() for n, p in model.named_parameters()}
+        return logits, losses[0], grads
+
+    o1, l1, g1 = once()
+    o2, l2, g2 = once()
+    assert torch.equal(o1, o2)
+    assert abs(l1 - l2) <= 2e-6 * abs(l1), (l1, l2)
+    for n in g1:
+        rel = (g1[n] - g2[n]).norm() / (g1[n].norm() + 1e-20)
+        assert rel < 1e-4, (n, rel.item())
