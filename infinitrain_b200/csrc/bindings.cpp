@@ -463,6 +463,11 @@ void flash_attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tenso
   auto dq_accum = torch::empty({a.B, a.T, a.H, a.D}, f32);
   a.delta = delta.data_ptr<float>();
   a.dq_accum = dq_accum.data_ptr<float>();
+  at::Tensor dkv_accum;
+  if ((g_attn_mode & 1) && itb_flash_attn_bwd_parts(a.B, a.T, a.H, a.KV, a.causal) > 1) {
+    dkv_accum = torch::empty({2, a.B, a.T, a.KV, a.D}, f32);
+    a.dkv_accum = dkv_accum.data_ptr<float>();
+  }
   if (g_attn_mode & 1)
     check_rc(itb_flash_attn_bwd_tc(&a, status_word(q.get_device()).data_ptr<int>(), cur_stream()),
              "flash_attn_bwd_tc");

@@ -355,6 +355,11 @@ struct AttentionFn : public torch::autograd::Function<AttentionFn> {
     a.dout = dout.data_ptr();
     a.dq = dbase, a.dk = dbase + 2 * H * D, a.dv = dbase + 2 * (H + KV) * D;
     a.delta = delta.data_ptr<float>(), a.dq_accum = dq_accum.data_ptr<float>();
+    Tensor dkv_accum;   // few key tiles and KV heads: several CTAs share a key tile and sum dK / dV here
+    if (itb_flash_attn_bwd_parts(a.B, a.T, a.H, a.KV, a.causal) > 1) {
+      dkv_accum = torch::empty({2, B, T, KV, D}, lse.options());
+      a.dkv_accum = dkv_accum.data_ptr<float>();
+    }
     check(itb_flash_attn_bwd_tc(&a, status_word(qkv.device().index()).data_ptr<int>(), stream()), "flash_attn_bwd_tc");
     if (freqs.defined())
       check(itb_rope_inplace(dqkv.data_ptr(), kItbBF16, freqs.data_ptr<float>(), static_cast<int>(B), static_cast<int>(T),

@@ -101,13 +101,24 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // The (query head of the group, query tile) pairs that meet this CTA's 128 keys are dealt out to
+  // `nparts` CTAs in turn (a.bwd_parts > 1 when the plain grid would leave most SMs idle: few key
+  // tiles, one KV head per rank under tensor parallelism); each then adds its dK / dV into fp32
+  // accumulators instead of writing them.
+  const int nparts = a.bwd_parts > 1 ? a.bwd_parts : 1;
+  const int nb = blockIdx.x, hk = blockIdx.y / nparts, part = blockIdx.y % nparts, b = blockIdx.z;
   const int G = a.H / a.KV;
   const int n0 = nb * 128;
   const int n_qblocks = (a.T + 127) / 128;
   const int mb_first = a.causal ? nb : 0;
   const int per_head = n_qblocks - mb_first;
-  const int iters = per_head * G;
+  const int total_iters = per_head * G;
+  const int iters = total_iters > part ? (total_iters - part + nparts - 1) / nparts : 0;
+  auto tile_of = [&](int it, int& h, int& mb) {
+    const int g = part + it * nparts;
+    h = hk * G + g / per_head;
+    mb = mb_first + g % per_head;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -155,7 +166,8 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
           *abort_flag = 1;
           break;
         }
-        const int h = hk * G + it / per_head, mb = mb_first + it % per_head;
+        int h, mb;
+        tile_of(it, h, mb);
         mbar_expect_tx(&q_full[st], 2 * Cfg::kTile);
 #pragma unroll
         for (int at = 0; at < Cfg::kAtoms; ++at) {
@@ -257,7 +269,8 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     // lse * log2(e) (threads 0..127) or delta (threads 128..255) of query row tid & 127 of tile `it`;
     // rows beyond the sequence get probability 0 (lse = +inf) and delta 0
     auto load_stat = [&](int it) -> float {
-      const int h = hk * G + it / per_head, mb = mb_first + it % per_head;
+      int h, mb;
+      tile_of(it, h, mb);
       const int qrow = mb * 128 + (tid & 127);
       const long long so = (static_cast<long long>(b) * a.H + h) * a.T + qrow;
       if (tid < 128) return qrow < a.T ? __ldg(a.lse + so) * kLog2e : INFINITY;
@@ -265,7 +278,8 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     };
     float stat_next = iters > 0 ? load_stat(0) : 0.f;
     for (int it = 0; it < iters; ++it) {
-      const int h = hk * G + it / per_head, mb = mb_first + it % per_head;
+      int h, mb;
+      tile_of(it, h, mb);
       const int sb = it & 1;
       // this tile's statistics were fetched while the previous tile was being processed
       if (tid < 128)
@@ -360,7 +374,33 @@ flash_bwd_tc_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       }
     }
     if (tid == 0) tma_store_wait<0>();
-    if (ok) {
+    if (ok && iters > 0 && nparts > 1) {
+      // this CTA's share of dK (scaled) and dV: added to the fp32 accumulators [2][B, T, KV, D]
+      const int krow = n0 + row;
+      const long long plane = static_cast<long long>(a.B) * a.T * a.KV * D;
+      float* dka = a.dkv_accum + ((static_cast<long long>(b) * a.T + krow) * a.KV + hk) * D;
+      float* dva = dka + plane;
+#pragma unroll 1
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        uint32_t rk[32], rv[32];
+        tmem_ld_32x32(tm_dK + lane_addr + c * 32, rk);
+        tmem_ld_32x32(tm_dV + lane_addr + c * 32, rv);
+        tmem_ld_wait();
+        if (krow < a.T) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dka + c * 32 + j),
+                         "f"(__uint_as_float(rk[j]) * a.scale), "f"(__uint_as_float(rk[j + 1]) * a.scale),
+                         "f"(__uint_as_float(rk[j + 2]) * a.scale), "f"(__uint_as_float(rk[j + 3]) * a.scale)
+                         : "memory");
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dva + c * 32 + j),
+                         "f"(__uint_as_float(rv[j])), "f"(__uint_as_float(rv[j + 1])), "f"(__uint_as_float(rv[j + 2])),
+                         "f"(__uint_as_float(rv[j + 3]))
+                         : "memory");
+          }
+        }
+      }
+    } else if (ok && nparts == 1) {
       // dK (scaled) and dV of this CTA's 128 keys; the last dq_full covered the MMAs that wrote them
       const int krow = n0 + row;
       __nv_bfloat16* dkg = static_cast<__nv_bfloat16*>(a.dk) + b * a.k_batch_stride +
@@ -735,8 +775,35 @@ __global__ void attn_dq_convert_tc_kernel(const ItbAttnArgs a, int D) {
   *reinterpret_cast<uint2*>(dst) = u;
 }
 
+// dk, dv (bf16, strided) = the fp32 accumulators [2][B, T, KV, D]
+__global__ void attn_dkv_convert_tc_kernel(const ItbAttnArgs a, int D) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;  // 4 elements each
+  const int dv = D / 4;
+  const long long plane4 = static_cast<long long>(a.B) * a.T * a.KV * dv;
+  if (i >= 2 * plane4) return;
+  const bool is_v = i >= plane4;
+  long long r = is_v ? i - plane4 : i;
+  const int c = static_cast<int>(r % dv) * 4;
+  r /= dv;
+  const int h = static_cast<int>(r % a.KV);
+  r /= a.KV;
+  const int t = static_cast<int>(r % a.T), b = static_cast<int>(r / a.T);
+  const float4 v = *reinterpret_cast<const float4*>(a.dkv_accum + i * 4);
+  __nv_bfloat16* dst = is_v ? static_cast<__nv_bfloat16*>(a.dv) + b * a.v_batch_stride + static_cast<long long>(t) * a.v_row_stride
+                            : static_cast<__nv_bfloat16*>(a.dk) + b * a.k_batch_stride + static_cast<long long>(t) * a.k_row_stride;
+  dst += h * D + c;
+  uint2 u;
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  u.x = *reinterpret_cast<uint32_t*>(&lo);
+  u.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = u;
+}
+
 template <int D>
-static int bwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
+static int bwd_launch(const ItbAttnArgs* a_in, int* err, cudaStream_t s) {
+  ItbAttnArgs args = *a_in;
+  args.bwd_parts = args.dkv_accum ? itb_flash_attn_bwd_parts(args.B, args.T, args.H, args.KV, args.causal) : 1;
+  const ItbAttnArgs* a = &args;
   using Cfg = BwdCfg<D>;
   constexpr int smem = Cfg::kSmem + 1024;
   static PerDeviceOnce configured;
@@ -760,15 +827,34 @@ static int bwd_launch(const ItbAttnArgs* a, int* err, cudaStream_t s) {
   cudaError_t e = cudaMemsetAsync(a->dq_accum, 0, nrow * D * sizeof(float), s);
   if (e != cudaSuccess) return static_cast<int>(e);
   attn_delta_tc_kernel<<<static_cast<int>((nrow * (D / 8) + 255) / 256), 256, 0, s>>>(*a, D);
-  dim3 grid((a->T + 127) / 128, a->KV, a->B);
+  const int parts = a->bwd_parts > 1 ? a->bwd_parts : 1;
+  const long long kv_vecs = 2LL * a->B * a->T * a->KV * (D / 4);
+  if (parts > 1) {
+    e = cudaMemsetAsync(a->dkv_accum, 0, kv_vecs * 4 * sizeof(float), s);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  dim3 grid((a->T + 127) / 128, a->KV * parts, a->B);
   flash_bwd_tc_kernel<D><<<grid, kThreads, smem, s>>>(tq, tk, tv, tdo, tdq, *a, err);
   const long long nvec = nrow * (D / 4);
   attn_dq_convert_tc_kernel<<<static_cast<int>((nvec + 255) / 256), 256, 0, s>>>(*a, D);
+  if (parts > 1) attn_dkv_convert_tc_kernel<<<static_cast<int>((kv_vecs + 255) / 256), 256, 0, s>>>(*a, D);
   return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace fatc
 }  // namespace itb
+
+extern "C" int itb_flash_attn_bwd_parts(int B, int T, int H, int KV, int causal) {
+  (void)causal;
+  const long long ctas = static_cast<long long>((T + 127) / 128) * KV * B;
+  const int sms = 148;
+  if (ctas <= 0 || ctas * 2 > sms) return 1;                 // at least half a wave as it is
+  const int most = ((T + 127) / 128) * (H / KV);             // tiles of the busiest CTA
+  int parts = static_cast<int>(sms / ctas);
+  if (parts > most) parts = most;
+  if (parts > 16) parts = 16;
+  return parts < 1 ? 1 : parts;
+}
 
 extern "C" int itb_flash_attn_bwd_tc(const ItbAttnArgs* a, int* err, cudaStream_t s) {
   if (a->B <= 0 || a->T <= 0) return 0;

@@ -167,7 +167,15 @@ typedef struct {
   void *dq, *dk, *dv;     // same strides as q, k, v
   float* delta;           // scratch [B, H, T] fp32
   float* dq_accum;        // scratch [B, T, H, D] fp32 (zeroed by the call)
+  // tensor-core backward only, optional: scratch [2][B, T, KV, D] fp32 (zeroed by the call).  When it is
+  // there and the grid of one CTA per (key tile, KV head, batch) would fill less than half of the
+  // SMs, itb_flash_attn_bwd_parts() CTAs share each key tile and sum their dK / dV here.
+  float* dkv_accum;
+  int bwd_parts;          // set by the launcher
 } ItbAttnArgs;
+// How many CTAs the tensor-core backward puts on one (key tile, KV head, batch); 1 = the scratch
+// buffer `dkv_accum` is not needed.
+int itb_flash_attn_bwd_parts(int B, int T, int H, int KV, int causal);
 
 int itb_flash_attn_fwd(const ItbAttnArgs* args, cudaStream_t stream);
 int itb_flash_attn_bwd(const ItbAttnArgs* args, cudaStream_t stream);

@@ -147,7 +147,7 @@ def bench_norm(C):
 def bench_attention(C):
     timeit = _timer()
     default = C.get_attn_mode()
-    for B, T, H, KV, D in ((16, 1024, 12, 12, 64), (1, 2048, 32, 8, 128), (4, 2048, 32, 8, 128)):
+    for B, T, H, KV, D in ((16, 1024, 12, 12, 64), (1, 2048, 32, 8, 128), (4, 2048, 32, 8, 128), (1, 2048, 4, 1, 128)):
         q, k, v, dq, dk, dv = _attn_tensors(B, T, H, KV, D)
         sc = 1.0 / math.sqrt(D)
         o, lse = C.flash_attn_fwd(q, k, v, sc, True)

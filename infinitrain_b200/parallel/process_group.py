@@ -357,6 +357,8 @@ class ProcessGroupFactory:
             return self
         world = genv.GetWorldSize()
         rank = genv.MyRank()
+        if os.environ.get("ITB_PG_TIMEOUT_S"):   # rendezvous and collective time-out of this job, in seconds
+            timeout_s = float(os.environ["ITB_PG_TIMEOUT_S"])
         if world > 1 and not dist.is_initialized():
             if backend is None:
                 backend = "nccl" if (device is not None and device.type == "cuda") else "gloo"

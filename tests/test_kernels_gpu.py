@@ -326,7 +326,7 @@ def _attn_ref(q, k, v, causal):
 
 @pytest.mark.parametrize("attn_mode", [3, 0], ids=["tcgen05", "mma_sync"])
 @pytest.mark.parametrize("B,T,H,KV,D", [(2, 128, 4, 4, 64), (1, 200, 4, 2, 64), (2, 96, 8, 2, 128),
-                                         (1, 1024, 2, 2, 64), (2, 384, 8, 2, 128)])
+                                         (1, 1024, 2, 2, 64), (2, 384, 8, 2, 128), (1, 2048, 4, 1, 128)])
 def test_flash_attention(C, B, T, H, KV, D, attn_mode):
     torch.manual_seed(11)
     default_mode = C.get_attn_mode()
