@@ -397,7 +397,10 @@ def _run_secondary(args, rank, script=None, sp=subprocess):
     per_attempt = max(60, args.secondary_budget // len(attempts))
     reasons = []
     for k, (name, flags) in enumerate(attempts):
-        env = dict(os.environ)
+        # the children rendezvous among themselves: rank 0's child serves the store on a port of its
+        # own, so nothing may tell them that a launcher's agent already hosts one (torchrun does, through
+        # TORCHELASTIC_USE_AGENT_STORE: every rank would then connect as a client to a server that does not exist)
+        env = {k_: v for k_, v in os.environ.items() if not k_.startswith("TORCHELASTIC_")}
         env["MASTER_PORT"] = str(base_port + 13 + 7 * k)
         env["ITB_PG_TIMEOUT_S"] = str(max(60, per_attempt - 30))   # a rank that never joins ends the others' rendezvous in time
         cmd = [sys.executable, script or os.path.abspath(__file__), "--gpus", str(world), "--steps", str(args.steps), "--warmup",

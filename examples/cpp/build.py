@@ -23,7 +23,10 @@ def build(cuda: bool = False, out: str | None = None, src: str | None = None) ->
     dst = Path(out) if out else ROOT / "infinitrain_b200" / "bin" / ("itb_train_cuda" if cuda else "itb_train")
     dst.parent.mkdir(parents=True, exist_ok=True)
     srcs = [Path(src).resolve() if src else ROOT / "examples" / "cpp" / "train.cc"]
-    hdrs = sorted((ROOT / "infinitrain_b200" / "csrc" / "frontend" / "itb").glob("*.h"))
+    csrc = ROOT / "infinitrain_b200" / "csrc"
+    # every header the trainer sees: the frontend, the C launch interface of the kernels, the planners
+    hdrs = sorted((csrc / "frontend" / "itb").glob("*.h")) + sorted((csrc / "kernels").glob("*.h")) + \
+        sorted((csrc / "comm").glob("*.h")) + sorted((csrc / "runtime").glob("*.h")) + [csrc / "runtime" / "planners.cpp"]
     if dst.exists() and all(dst.stat().st_mtime > p.stat().st_mtime for p in srcs + hdrs):
         return dst
     inc = [f"-I{p}" for p in ce.include_paths(device_type="cuda" if cuda else "cpu")]

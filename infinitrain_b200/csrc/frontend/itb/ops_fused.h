@@ -40,18 +40,33 @@ inline Tensor& status_word(int device) {
 }
 inline int64_t kernel_status() { return status_word(at::cuda::current_device()).cpu()[0].item<int64_t>(); }
 
-// bf16 copy of an fp32 weight, cached per tensor and refreshed when the weight's version moved.
+// bf16 copy of an fp32 weight, cached per tensor and refreshed when the weight's version moved.  An
+// entry holds a weak reference to its tensor: the tensor's address cannot be handed to another tensor
+// while the entry exists (a new weight can never pick up a dead weight's copy), and entries of dead
+// tensors are dropped the next time the table grows.
 struct Shadow {
   Tensor bf16;
   int64_t version = -1;
+  c10::weak_intrusive_ptr<c10::TensorImpl> owner{c10::intrusive_ptr<c10::TensorImpl>()};
 };
 inline std::unordered_map<const void*, Shadow>& shadows() {
   static std::unordered_map<const void*, Shadow> m;
   return m;
 }
+inline Shadow& shadow_entry(const Tensor& w) {
+  auto& table = shadows();
+  auto it = table.find(w.unsafeGetTensorImpl());
+  if (it != table.end() && !it->second.owner.expired()) return it->second;
+  if (it == table.end() && table.size() % 64 == 63)
+    for (auto dead = table.begin(); dead != table.end();) dead = dead->second.owner.expired() ? table.erase(dead) : std::next(dead);
+  Shadow& s = table[w.unsafeGetTensorImpl()];
+  s = Shadow{};
+  s.owner = c10::weak_intrusive_ptr<c10::TensorImpl>(w.getIntrusivePtr());
+  return s;
+}
 inline Tensor weight_lp(const Tensor& w) {
   if (w.scalar_type() == torch::kBFloat16) return w.detach();
-  auto& s = shadows()[w.unsafeGetTensorImpl()];
+  auto& s = shadow_entry(w);
   int64_t ver = static_cast<int64_t>(w._version());
   if (s.bf16.defined() && s.version == ver && s.bf16.device() == w.device()) return s.bf16;
   if (!s.bf16.defined() || s.bf16.sizes() != w.sizes() || s.bf16.device() != w.device())
@@ -64,11 +79,11 @@ inline Tensor weight_lp(const Tensor& w) {
 // An optimizer that wrote the shadow itself stamps it with the weight's new version.
 inline void mark_shadow_fresh(const Tensor& w) {
   auto it = shadows().find(w.unsafeGetTensorImpl());
-  if (it != shadows().end()) it->second.version = static_cast<int64_t>(w._version());
+  if (it != shadows().end() && !it->second.owner.expired()) it->second.version = static_cast<int64_t>(w._version());
 }
 inline Tensor shadow_of(const Tensor& w) {
   weight_lp(w);
-  return shadows()[w.unsafeGetTensorImpl()].bf16;
+  return shadow_entry(w).bf16;
 }
 
 inline Tensor as_bf16_2d(const Tensor& x) {

@@ -104,6 +104,9 @@ def test_same_seed_runs_are_bit_identical_where_the_algorithm_is(family):
     _setup()
 
     def once():
+        from infinitrain_b200.nn import init
+
+        init.manual_seed(123)   # the framework's one initialisation stream
         torch.manual_seed(123)
         if family == "gpt2":
             cfg = TransformerConfig.GPT2(n_layer=2, n_embd=256, n_head=4, n_kv_head=4, vocab_size=1001,
