@@ -706,12 +706,26 @@ def main():
     yb = torch.empty((B, T), dtype=torch.int64, device=dev)
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    from infinitrain_b200.utils.cuda_graph import LaggedScalar
+
+    # every step: its tokens from pinned host memory (a graphed step copies them straight into its
+    # static input buffers) and its loss to the host; the loss of step i is looked at after step
+    # i + 1 has been queued, so the read-back does not drain the device
+    reader = LaggedScalar()
     e2.record()
     last = 0.0
     for i in range(args.steps):
-        xb.copy_(host_x[i % n_host], non_blocking=True)
-        yb.copy_(host_y[i % n_host], non_blocking=True)
-        last = float(train_step(xb, yb).item())
+        if args.graph:
+            loss_t = train_step(host_x[i % n_host], host_y[i % n_host])
+        else:
+            xb.copy_(host_x[i % n_host], non_blocking=True)
+            yb.copy_(host_y[i % n_host], non_blocking=True)
+            loss_t = train_step(xb, yb)
+        reader.push(loss_t)
+        if i >= 1:
+            last = reader.pop()
+    for last in reader.drain():
+        pass
     e3.record()
     barrier()
     e2e_ms = e2.elapsed_time(e3)

@@ -18,6 +18,16 @@ namespace itb {
 constexpr int kNormWarps = 4;           // rows per block in flight
 constexpr int kNormThreads = kNormWarps * 32;
 constexpr int kMaxPartialRows = 592;    // 4 blocks per SM on 148 SMs
+#ifndef ITB_NORM_FWD_BLOCKS_PER_SM
+#define ITB_NORM_FWD_BLOCKS_PER_SM 8
+#endif
+constexpr int kNormFwdBlocksPerSm = ITB_NORM_FWD_BLOCKS_PER_SM;
+// warp-per-row backward: two sets of packed row chunks (current and prefetched) beside the per-lane
+// parameter-gradient accumulators need more than 168 registers
+#ifndef ITB_NORM_BWD_BLOCKS_PER_SM
+#define ITB_NORM_BWD_BLOCKS_PER_SM 2
+#endif
+constexpr int kNormBwdBlocksPerSm = ITB_NORM_BWD_BLOCKS_PER_SM;
 
 template <typename T>
 __device__ __forceinline__ float to_f(T v);
@@ -74,9 +84,41 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const fl
   *reinterpret_cast<uint4*>(p) = u;
 }
 
-// Rows up to kMaxVec*256 elements wide stay in registers (kMaxVec chunks of 8 per lane); the part
-// of a wider row beyond that is re-read from global memory.  kMaxVec is a template parameter so
-// that narrow rows (GPT-2: 768) do not pay the register cost of wide ones.
+// Eight consecutive elements as they come out of one or two 16-byte loads, kept packed in registers
+// (a bf16 chunk costs 4 registers instead of 8) and unpacked where they are used.
+template <typename T>
+struct Raw8;
+template <>
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = *reinterpret_cast<const float4*>(p);
+    b = *reinterpret_cast<const float4*>(p + 4);
+  }
+  __device__ __forceinline__ void unpack(float (&v)[8]) const {
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+template <>
+struct Raw8<__nv_bfloat16> {
+  uint4 u;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void unpack(float (&v)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+};
+
+// Rows up to kMaxVec*256 elements wide stay (packed) in registers (kMaxVec chunks of 8 per lane); the
+// part of a wider row beyond that is re-read from global memory.  kMaxVec is a template parameter so
+// that narrow rows (GPT-2: 768) do not pay the register cost of wide ones.  The grid is one resident
+// wave; a warp walks its rows with the loads of the NEXT row issued before the current row's
+// arithmetic, so a row's memory latency hides behind its predecessor's reductions and stores.
 
 template <typename TX, typename TY, bool kRms, int kMaxVec>
 __global__ void __launch_bounds__(kNormThreads)
@@ -85,18 +127,30 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ gamma,
                 float* __restrict__ rstd_out, int rows, int C, float eps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = C / 8;
-  for (int row = blockIdx.x * kNormWarps + warp; row < rows; row += gridDim.x * kNormWarps) {
+  const int step = static_cast<int>(gridDim.x) * kNormWarps;
+  Raw8<TX> cur[kMaxVec], nxt[kMaxVec];
+  auto fetch = [&](int r, Raw8<TX> (&buf)[kMaxVec]) {
+    const TX* xr = x + static_cast<long long>(r) * C;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) buf[i].load(xr + vi * 8);
+    }
+  };
+  int row = blockIdx.x * kNormWarps + warp;
+  if (row < rows) fetch(row, cur);
+  for (; row < rows; row += step) {
+    if (row + step < rows) fetch(row + step, nxt);
     const TX* xr = x + static_cast<long long>(row) * C;
     TY* yr = y + static_cast<long long>(row) * C;
-    float cache[kMaxVec][8];
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
-      int vi = lane + i * 32;
-      if (vi < nvec) {
-        load8<TX>(xr + vi * 8, cache[i]);
+      if (lane + i * 32 < nvec) {
+        float v[8];
+        cur[i].unpack(v);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) sum += kRms ? cache[i][e] * cache[i][e] : cache[i][e];
+        for (int e = 0; e < 8; ++e) sum += kRms ? v[e] * v[e] : v[e];
       }
     }
     for (int vi = lane + kMaxVec * 32; vi < nvec; vi += 32) {
@@ -114,11 +168,12 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ gamma,
       float var = 0.f;
 #pragma unroll
       for (int i = 0; i < kMaxVec; ++i) {
-        int vi = lane + i * 32;
-        if (vi < nvec) {
+        if (lane + i * 32 < nvec) {
+          float v[8];
+          cur[i].unpack(v);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            float d = cache[i][e] - mean;
+            float d = v[e] - mean;
             var += d * d;
           }
         }
@@ -155,46 +210,22 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ gamma,
     };
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
-      int vi = lane + i * 32;
-      if (vi < nvec) emit(vi, cache[i]);
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float v[8];
+        cur[i].unpack(v);
+        emit(vi, v);
+      }
     }
     for (int vi = lane + kMaxVec * 32; vi < nvec; vi += 32) {
       float t[8];
       load8<TX>(xr + vi * 8, t);
       emit(vi, t);
     }
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) cur[i] = nxt[i];
   }
 }
-
-// Eight consecutive elements as they come out of one or two 16-byte loads, kept packed in registers
-// (a bf16 chunk costs 4 registers instead of 8) and unpacked where they are used.
-template <typename T>
-struct Raw8;
-template <>
-struct Raw8<float> {
-  float4 a, b;
-  __device__ __forceinline__ void load(const float* p) {
-    a = *reinterpret_cast<const float4*>(p);
-    b = *reinterpret_cast<const float4*>(p + 4);
-  }
-  __device__ __forceinline__ void unpack(float (&v)[8]) const {
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  }
-};
-template <>
-struct Raw8<__nv_bfloat16> {
-  uint4 u;
-  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
-  __device__ __forceinline__ void unpack(float (&v)[8]) const {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 f = __bfloat1622float2(h[i]);
-      v[2 * i] = f.x;
-      v[2 * i + 1] = f.y;
-    }
-  }
-};
 
 // Backward.  With xhat = (x - mean) * rstd and g = dy * gamma:
 //   LayerNorm: dx = rstd * (g - mean_C(g) - xhat * mean_C(g * xhat))
@@ -213,7 +244,7 @@ struct Raw8<__nv_bfloat16> {
 // the warps add their registers to a shared-memory row in turns; in the wide layout every thread owns
 // its columns.
 template <typename TDY, typename TX, typename TDX, bool kRms, int kChunks, bool kRes, bool kWide>
-__global__ void __launch_bounds__(kNormThreads, kWide ? 4 : 3)
+__global__ void __launch_bounds__(kNormThreads, kWide ? 4 : kNormBwdBlocksPerSm)
 norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
                 const float* __restrict__ gamma, const float* __restrict__ mean_in,
                 const float* __restrict__ rstd_in, const TDX* __restrict__ dres,
@@ -238,27 +269,49 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
   }
   const int row_step = kWide ? static_cast<int>(gridDim.x) : static_cast<int>(gridDim.x) * kNormWarps;
   int parity = 0;
-  for (int row = kWide ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) * kNormWarps + warp;
-       row < rows; row += row_step) {
-    const TDY* dyr = dy + static_cast<long long>(row) * C;
-    const TX* xr = x + static_cast<long long>(row) * C;
-    const TDX* rr = kRes ? dres + static_cast<long long>(row) * C : nullptr;
-    TDX* dxr = dx + static_cast<long long>(row) * C;
-    // every load of the row is issued before anything waits on one
-    Raw8<TDY> rd[kChunks];
-    Raw8<TX> rx[kChunks];
-    Raw8<TDX> rres[kRes ? kChunks : 1];
+  // The loads of the NEXT row are issued before the current row's arithmetic (kPrefetch: the
+  // warp-per-row layout, where the register budget allows a second set of packed chunks).
+  constexpr bool kPrefetch = !kWide;
+  Raw8<TDY> rd[kChunks], nd[kPrefetch ? kChunks : 1];
+  Raw8<TX> rx[kChunks], nx[kPrefetch ? kChunks : 1];
+  Raw8<TDX> rres[kRes ? kChunks : 1], nres[(kRes && kPrefetch) ? kChunks : 1];
+  auto fetch = [&](int r, Raw8<TDY>* bd, Raw8<TX>* bx, Raw8<TDX>* br) {
+    const TDY* dyr = dy + static_cast<long long>(r) * C;
+    const TX* xr = x + static_cast<long long>(r) * C;
+    const TDX* rr = kRes ? dres + static_cast<long long>(r) * C : nullptr;
 #pragma unroll
     for (int i = 0; i < kChunks; ++i) {
       const int vi = vi_of(i);
       if (vi < nvec) {
-        rd[i].load(dyr + vi * 8);
-        rx[i].load(xr + vi * 8);
-        if (kRes) rres[i].load(rr + vi * 8);
+        bd[i].load(dyr + vi * 8);
+        bx[i].load(xr + vi * 8);
+        if (kRes) br[i].load(rr + vi * 8);
       }
     }
-    const float mean = kRms ? 0.f : mean_in[row];
-    const float rstd = rstd_in[row];
+  };
+  int row = kWide ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) * kNormWarps + warp;
+  float mean_n = 0.f, rstd_n = 0.f;
+  if (kPrefetch && row < rows) {
+    fetch(row, rd, rx, rres);
+    mean_n = kRms ? 0.f : mean_in[row];
+    rstd_n = rstd_in[row];
+  }
+  for (; row < rows; row += row_step) {
+    TDX* dxr = dx + static_cast<long long>(row) * C;
+    float mean, rstd;
+    if (kPrefetch) {
+      mean = mean_n, rstd = rstd_n;
+      if (row + row_step < rows) {
+        fetch(row + row_step, nd, nx, nres);
+        mean_n = kRms ? 0.f : mean_in[row + row_step];
+        rstd_n = rstd_in[row + row_step];
+      }
+    } else {
+      // every load of the row is issued before anything waits on one
+      fetch(row, rd, rx, rres);
+      mean = kRms ? 0.f : mean_in[row];
+      rstd = rstd_in[row];
+    }
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < kChunks; ++i) {
@@ -318,6 +371,14 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
           }
         }
         store8<TDX>(dxr + vi * 8, o);
+      }
+    }
+    if (kPrefetch) {
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i) {
+        rd[i] = nd[i];
+        rx[i] = nx[i];
+        if (kRes) rres[i] = nres[i];
       }
     }
   }
@@ -413,17 +474,28 @@ static int norm_fwd_dispatch(const void* x, int xd, const float* gamma, const fl
                              int yd, float* mean, float* rstd, int rows, int C, float eps,
                              cudaStream_t s) {
   if (C % 8) return -3;
-  int grid = (rows + kNormWarps - 1) / kNormWarps;
-  if (grid > 148 * 16) grid = 148 * 16;
-  if (grid < 1) return 0;
-#define LAUNCH(TX, TY)                                                                           \
+  const int want = (rows + kNormWarps - 1) / kNormWarps;
+  if (want < 1) return 0;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // one wave of resident blocks: what the kernel's register use lets an SM hold, at most kNormFwdBlocksPerSm
+#define LAUNCH_V(TX, TY, V)                                                                      \
   do {                                                                                           \
-    if (C <= 1024)                                                                               \
-      norm_fwd_kernel<TX, TY, kRms, 4><<<grid, kNormThreads, 0, s>>>(                            \
-          static_cast<const TX*>(x), gamma, beta, static_cast<TY*>(y), mean, rstd, rows, C, eps); \
-    else                                                                                         \
-      norm_fwd_kernel<TX, TY, kRms, 8><<<grid, kNormThreads, 0, s>>>(                            \
-          static_cast<const TX*>(x), gamma, beta, static_cast<TY*>(y), mean, rstd, rows, C, eps); \
+    static int per_sm = 0;                                                                       \
+    if (per_sm == 0) {                                                                           \
+      int n = 0;                                                                                 \
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, norm_fwd_kernel<TX, TY, kRms, V>, kNormThreads, 0); \
+      per_sm = n < 1 ? 1 : (n > kNormFwdBlocksPerSm ? kNormFwdBlocksPerSm : n);                  \
+    }                                                                                            \
+    const int grid = want < sms * per_sm ? want : sms * per_sm;                                  \
+    norm_fwd_kernel<TX, TY, kRms, V><<<grid, kNormThreads, 0, s>>>(                              \
+        static_cast<const TX*>(x), gamma, beta, static_cast<TY*>(y), mean, rstd, rows, C, eps);  \
+  } while (0)
+#define LAUNCH(TX, TY)              \
+  do {                              \
+    if (C <= 1024) LAUNCH_V(TX, TY, 4); \
+    else LAUNCH_V(TX, TY, 8);       \
   } while (0)
   if (xd == kItbBF16 && yd == kItbBF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (xd == kItbF32 && yd == kItbBF16) LAUNCH(float, __nv_bfloat16);
@@ -431,6 +503,7 @@ static int norm_fwd_dispatch(const void* x, int xd, const float* gamma, const fl
   else if (xd == kItbBF16 && yd == kItbF32) LAUNCH(__nv_bfloat16, float);
   else return -4;
 #undef LAUNCH
+#undef LAUNCH_V
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -442,7 +515,7 @@ static int norm_bwd_dispatch(const void* dy, int dyd, const void* x, int xd, con
   if (C % 8 || C > 6144) return -3;
   if (rows < 1) return 0;
   const bool wide = C > 1024;
-  const int grid = norm_bwd_grid(rows, wide, wide ? 4 : 3);
+  const int grid = norm_bwd_grid(rows, wide, wide ? 4 : kNormBwdBlocksPerSm);
   const int smem = wide ? 2 * kNormWarps * 2 * static_cast<int>(sizeof(float)) : 3 * C * static_cast<int>(sizeof(float));
 #define LAUNCH_K(TDY, TX, TDX, CH, RES, WIDE)                                                     \
   norm_bwd_kernel<TDY, TX, TDX, kRms, CH, RES, WIDE><<<grid, kNormThreads, smem, s>>>(            \

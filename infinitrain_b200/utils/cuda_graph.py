@@ -52,3 +52,42 @@ class GraphedTrainStep:
         self.graph.replay()
         ops._counters["launches"] += self.launches_per_replay
         return self.static_loss
+
+
+class LaggedScalar:
+    """Per-step read-back of a device scalar (the loss) that does not drain the device.
+
+    ``float(loss)`` right after a step makes the host wait for the step and the device wait for the
+    host's next launch.  Here ``push`` enqueues an asynchronous copy of the scalar into pinned host
+    memory behind the step that produced it, and ``pop`` returns the OLDEST pushed value, waiting
+    only for that copy.  Called as ``push(step i); pop() -> value of step i - 1`` the host stays one
+    step ahead: step i is queued on the device before step i - 1's value is looked at, every step's
+    value is still read, in order, one step late.  ``drain`` returns what is left at the end.
+    """
+
+    def __init__(self, depth: int = 2):
+        self._slots = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(depth)]
+        self._events = [torch.cuda.Event() for _ in range(depth)]
+        self._pending = []
+        self._next = 0
+
+    def push(self, value: torch.Tensor) -> None:
+        if len(self._pending) == len(self._slots):
+            raise RuntimeError("LaggedScalar: pop() before pushing more values than its depth")
+        k = self._next
+        self._next = (k + 1) % len(self._slots)
+        v = value.detach()
+        self._slots[k].copy_(v if v.dtype == torch.float32 else v.float(), non_blocking=True)
+        self._events[k].record()
+        self._pending.append(k)
+
+    def pop(self) -> float:
+        k = self._pending.pop(0)
+        self._events[k].synchronize()
+        return float(self._slots[k])
+
+    def drain(self):
+        return [self.pop() for _ in range(len(self._pending))]
+
+    def __len__(self) -> int:
+        return len(self._pending)

@@ -131,3 +131,23 @@ def test_same_seed_runs_are_bit_identical_where_the_algorithm_is(family):
     for n in g1:
         rel = (g1[n] - g2[n]).norm() / (g1[n].norm() + 1e-20)
         assert rel < 1e-4, (n, rel.item())
+
+
+def test_lagged_scalar_returns_every_value_in_order_one_step_late():
+    from infinitrain_b200.utils.cuda_graph import LaggedScalar
+
+    reader = LaggedScalar()
+    seen = []
+    static = torch.zeros((), device="cuda")
+    for i in range(5):
+        static.fill_(float(i) + 0.5)         # the producer overwrites one static tensor, as a replayed graph does
+        reader.push(static)
+        if i >= 1:
+            seen.append(reader.pop())
+    seen += reader.drain()
+    assert seen == [0.5, 1.5, 2.5, 3.5, 4.5]
+    assert len(reader) == 0
+    reader.push(static)
+    reader.push(static.bfloat16())
+    with pytest.raises(RuntimeError):
+        reader.push(static)
