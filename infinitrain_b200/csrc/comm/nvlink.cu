@@ -28,6 +28,14 @@
 namespace itb {
 
 constexpr int kCommThreads = 512;
+#ifndef ITB_AR_UNROLL
+#define ITB_AR_UNROLL 8
+#endif
+#ifndef ITB_ZERO_UNROLL
+#define ITB_ZERO_UNROLL 2
+#endif
+constexpr int kArUnroll = ITB_AR_UNROLL;       // 16-byte reductions in flight per thread (all-reduce)
+constexpr int kZeroUnroll = ITB_ZERO_UNROLL;   // 32-byte chunks in flight per thread (ZeRO step)
 // ~2^24 polls with a short sleep: of the order of a few seconds of skew tolerated between ranks.
 constexpr unsigned kSpinLimit = 1u << 24;
 
@@ -131,12 +139,24 @@ allreduce_scale_kernel(ItbPeerPtrs bufs, float* mc, ItbPeerPtrs flags, long long
   const long long per = (nv + world - 1) / world;
   const long long v0 = min(nv, per * rank), v1 = min(nv, v0 + per);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  // A reduction through the switch (or a round of peer loads) takes microseconds to come back:
+  // every thread keeps kArUnroll of them in flight before it touches the first result.
   for (long long v = v0 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < v1;
-       v += stride) {
-    const long long i = off + v * 4;
-    float4 s = reduce4<kMC>(bufs, mc, i, world);
-    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
-    bcast4<kMC>(bufs, mc, i, world, s);
+       v += stride * kArUnroll) {
+    float4 s[kArUnroll];
+#pragma unroll
+    for (int u = 0; u < kArUnroll; ++u) {
+      const long long vu = v + u * stride;
+      if (vu < v1) s[u] = reduce4<kMC>(bufs, mc, off + vu * 4, world);
+    }
+#pragma unroll
+    for (int u = 0; u < kArUnroll; ++u) {
+      const long long vu = v + u * stride;
+      if (vu < v1) {
+        s[u].x *= scale; s[u].y *= scale; s[u].z *= scale; s[u].w *= scale;
+        bcast4<kMC>(bufs, mc, off + vu * 4, world, s[u]);
+      }
+    }
   }
   rank_barrier(flags, rank, world, ch, epoch + 1, err, 202);
   if (epoch_ctr && threadIdx.x == 0) epoch_ctr[ch] = epoch + 1;
@@ -166,43 +186,58 @@ rs_adamw_bcast_kernel(ItbPeerPtrs grads, const float* mc_grads, ItbPeerPtrs para
   const long long nv = shard / 8;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const float* my_params = static_cast<const float*>(params.p[rank]);
-  for (long long k = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; k < nv;
-       k += stride) {
-    const long long i = s0 + k * 8;   // index in the flat buffers
-    const long long j = k * 8;        // index in the shard-local state
-    float g[8], p[8], mm[8], vv[8];
-    *reinterpret_cast<float4*>(g) = reduce4<kMC>(grads, mc_grads, i, world);
-    *reinterpret_cast<float4*>(g + 4) = reduce4<kMC>(grads, mc_grads, i + 4, world);
-    *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(my_params + i);
-    *reinterpret_cast<float4*>(p + 4) = *reinterpret_cast<const float4*>(my_params + i + 4);
-    *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(m + j);
-    *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(m + j + 4);
-    *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(v + j);
-    *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(v + j + 4);
+  // kZeroUnroll chunks of 8 elements per thread and pass: the gradient reductions and the local
+  // loads of all of them are issued before the arithmetic of the first
+  for (long long k0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; k0 < nv;
+       k0 += stride * kZeroUnroll) {
+    float g[kZeroUnroll][8], p[kZeroUnroll][8], mm[kZeroUnroll][8], vv[kZeroUnroll][8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float ge = g[e] * h.grad_scale;
-      mm[e] = h.beta1 * mm[e] + (1.f - h.beta1) * ge;
-      vv[e] = h.beta2 * vv[e] + (1.f - h.beta2) * ge * ge;
-      const float mhat = mm[e] * h.inv_bc1, vhat = vv[e] * h.inv_bc2;
-      p[e] -= h.lr * (mhat / (sqrtf(vhat) + h.eps) + h.weight_decay * p[e]);
+    for (int u = 0; u < kZeroUnroll; ++u) {
+      const long long k = k0 + u * stride;
+      if (k < nv) {
+        const long long i = s0 + k * 8;   // index in the flat buffers
+        const long long j = k * 8;        // index in the shard-local state
+        *reinterpret_cast<float4*>(g[u]) = reduce4<kMC>(grads, mc_grads, i, world);
+        *reinterpret_cast<float4*>(g[u] + 4) = reduce4<kMC>(grads, mc_grads, i + 4, world);
+        *reinterpret_cast<float4*>(p[u]) = *reinterpret_cast<const float4*>(my_params + i);
+        *reinterpret_cast<float4*>(p[u] + 4) = *reinterpret_cast<const float4*>(my_params + i + 4);
+        *reinterpret_cast<float4*>(mm[u]) = *reinterpret_cast<const float4*>(m + j);
+        *reinterpret_cast<float4*>(mm[u] + 4) = *reinterpret_cast<const float4*>(m + j + 4);
+        *reinterpret_cast<float4*>(vv[u]) = *reinterpret_cast<const float4*>(v + j);
+        *reinterpret_cast<float4*>(vv[u] + 4) = *reinterpret_cast<const float4*>(v + j + 4);
+      }
     }
-    *reinterpret_cast<float4*>(m + j) = *reinterpret_cast<float4*>(mm);
-    *reinterpret_cast<float4*>(m + j + 4) = *reinterpret_cast<float4*>(mm + 4);
-    *reinterpret_cast<float4*>(v + j) = *reinterpret_cast<float4*>(vv);
-    *reinterpret_cast<float4*>(v + j + 4) = *reinterpret_cast<float4*>(vv + 4);
-    bcast4<kMC>(params, mc_params, i, world, *reinterpret_cast<float4*>(p));
-    bcast4<kMC>(params, mc_params, i + 4, world, *reinterpret_cast<float4*>(p + 4));
-    uint4 sh;
-    __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&sh);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) hb[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
-    if (kMC) {
-      mm_st_bf16x8(mc_shadows + i, sh);
-    } else {
+    for (int u = 0; u < kZeroUnroll; ++u) {
+      const long long k = k0 + u * stride;
+      if (k >= nv) continue;
+      const long long i = s0 + k * 8;
+      const long long j = k * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float ge = g[u][e] * h.grad_scale;
+        mm[u][e] = h.beta1 * mm[u][e] + (1.f - h.beta1) * ge;
+        vv[u][e] = h.beta2 * vv[u][e] + (1.f - h.beta2) * ge * ge;
+        const float mhat = mm[u][e] * h.inv_bc1, vhat = vv[u][e] * h.inv_bc2;
+        p[u][e] -= h.lr * (mhat / (sqrtf(vhat) + h.eps) + h.weight_decay * p[u][e]);
+      }
+      *reinterpret_cast<float4*>(m + j) = *reinterpret_cast<float4*>(mm[u]);
+      *reinterpret_cast<float4*>(m + j + 4) = *reinterpret_cast<float4*>(mm[u] + 4);
+      *reinterpret_cast<float4*>(v + j) = *reinterpret_cast<float4*>(vv[u]);
+      *reinterpret_cast<float4*>(v + j + 4) = *reinterpret_cast<float4*>(vv[u] + 4);
+      bcast4<kMC>(params, mc_params, i, world, *reinterpret_cast<float4*>(p[u]));
+      bcast4<kMC>(params, mc_params, i + 4, world, *reinterpret_cast<float4*>(p[u] + 4));
+      uint4 sh;
+      __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&sh);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) hb[e] = __floats2bfloat162_rn(p[u][2 * e], p[u][2 * e + 1]);
+      if (kMC) {
+        mm_st_bf16x8(mc_shadows + i, sh);
+      } else {
 #pragma unroll 1
-      for (int r = 0; r < world; ++r)
-        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(shadows.p[r]) + i) = sh;
+        for (int r = 0; r < world; ++r)
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(shadows.p[r]) + i) = sh;
+      }
     }
   }
   rank_barrier(flags, rank, world, ch, epoch + 1, err, 204);

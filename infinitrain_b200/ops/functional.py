@@ -221,8 +221,21 @@ def _main_grad_of(p: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return main
 
 
+def autograd_ready_hook(fn):
+    """Wraps a grad-ready callback for ``register_post_accumulate_grad_hook``: the call autograd makes
+    for a parameter whose gradient another op will write later in this backward pass (see
+    ``claim_bias_grad``) is dropped; that op reports the parameter through ``_itb_grad_ready_hooks``."""
+    def hook(p):
+        if getattr(p, "_itb_grad_elsewhere", False):
+            return None
+        return fn(p)
+    return hook
+
+
 def _grad_written(p: torch.Tensor) -> None:
     """A kernel has added ``p``'s gradient to its flat-buffer slot: tell the reducer / ZeRO group."""
+    if getattr(p, "_itb_grad_elsewhere", False):
+        p._itb_grad_elsewhere = False
     for hook in getattr(p, "_itb_grad_ready_hooks", ()):
         hook(p)
 
@@ -347,6 +360,10 @@ def claim_bias_grad(residual, bias) -> bool:
     if holder is None or bias is None or holder.bias is not None or _main_grad_of(bias) is None:
         return False
     holder.bias = bias
+    # Until that norm's backward has run, nothing may report this parameter's gradient as complete:
+    # autograd still visits its accumulator (with an undefined gradient, because the linear returns
+    # none) and fires the parameter's post-accumulate hook there, long before the norm writes the slot.
+    bias._itb_grad_elsewhere = True
     return True
 
 

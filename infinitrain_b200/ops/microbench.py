@@ -251,12 +251,98 @@ def bench_tp(C):
     dist.destroy_process_group()
 
 
+def bench_collectives(C):
+    """The data-parallel collectives as NVLink kernels against their NCCL formulation, on every rank
+    of the job, per bucket size (25 MB: a DDP bucket; 154 MB: GPT-2's tied embedding bucket):
+      * all-reduce(avg) of an fp32 gradient bucket  vs  ncclAllReduce;
+      * reduce-scatter + AdamW + broadcast of fp32 weights and bf16 shadows in ONE kernel  vs
+        ncclReduceScatter + the AdamW kernel on the shard + ncclAllGather of fp32 weights and of bf16 shadows.
+    CUDA events on the launching stream, max over ranks.  The roofline of each is the bytes one GPU has
+    to send (= receive) over NVLink divided by the measured peer-copy bandwidth (770 GB/s per direction)."""
+    import os
+    from types import SimpleNamespace
+
+    import torch.distributed as dist
+
+    from ..parallel import global_env as genv
+    from ..parallel import symm
+    from ..parallel.process_group import ProcessGroupFactory, dp_group
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    genv.InitAllEnv(world_size=world, rank=rank)
+    ProcessGroupFactory.Instance().Init(device=dev, timeout_s=120)
+    pg = dp_group()
+    ctx = symm.NvlinkContext.get(pg, dev)
+    link = 770e9
+
+    def timed(fn, n=20, warm=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    for mb in (25, 154):
+        n = mb * 1024 * 1024 // 4 // (world * 128) * (world * 128)
+        grads = ctx.alloc(n, torch.float32)
+        params = ctx.alloc(n, torch.float32)
+        shadow = ctx.alloc(n, torch.bfloat16)
+        grads.normal_()
+        params.normal_()
+        res = {"case": "collectives", "world": world, "bucket_mb": mb, "multimem": bool(ctx.ptrs(grads)[1])}
+        ar = symm.BucketAllReduce(ctx, grads)
+        res["allreduce_fused_ms"] = timed(lambda: ar(grads).WaitNonBlocking())
+        res["allreduce_nccl_ms"] = timed(lambda: dist.all_reduce(grads, op=dist.ReduceOp.AVG))
+        wire = 4.0 * n * (world - 1) / world          # bytes out of (and into) one GPU
+        res["allreduce_floor_ms"] = wire / link * 1e3
+        res["allreduce_fraction_of_link"] = res["allreduce_floor_ms"] / res["allreduce_fused_ms"]
+        # ZeRO step of the bucket
+        shard = n // world
+        m, v = torch.zeros(shard, device=dev), torch.zeros(shard, device=dev)
+        buffer = SimpleNamespace(grad_buffer=grads, param_buffer=params, shadow_buffer=shadow)
+        bucket = SimpleNamespace(offset=0, numel=n)
+        step = symm.FusedZeroBucketStep(ctx, buffer, bucket, m, v)
+        res["zero_fused_ms"] = timed(lambda: step(1e-4, 0.9, 0.999, 1e-8, 0.1, 0.1, 0.001, 1.0 / world).WaitNonBlocking())
+        gs = torch.empty(shard, device=dev)
+        m2, v2 = torch.zeros(shard, device=dev), torch.zeros(shard, device=dev)
+        my_p = params[rank * shard:(rank + 1) * shard]
+        my_s = shadow[rank * shard:(rank + 1) * shard]
+
+        def nccl_step():
+            dist.reduce_scatter_tensor(gs, grads, op=dist.ReduceOp.AVG)
+            C.adamw(my_p, gs, m2, v2, my_s, 1e-4, 0.9, 0.999, 1e-8, 0.1, 0.1, 0.001, 1.0, None)
+            dist.all_gather_into_tensor(params, my_p)
+            dist.all_gather_into_tensor(shadow, my_s)
+
+        res["zero_nccl_ms"] = timed(nccl_step)
+        # in: (W-1)/W of the gradients; out: this rank's shard of weights (4 B) and shadows (2 B), once
+        # each with multicast stores, W-1 times with peer stores; in again: everybody else's shards
+        wire_in = 4.0 * n * (world - 1) / world + 6.0 * shard * (world - 1)
+        res["zero_floor_ms"] = wire_in / link * 1e3
+        res["zero_fraction_of_link"] = res["zero_floor_ms"] / res["zero_fused_ms"]
+        res["status"] = ctx.status()
+        if rank == 0:
+            print(json.dumps(res), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main(argv):
     C = _ext.load(required=True)
     torch.manual_seed(0)
     case = argv[1] if len(argv) > 1 else "gemm"
     {"gemm": bench_gemm, "gemm_llama_tp8": bench_gemm_llama_tp8, "gemm_probe": bench_gemm_probe, "norm": bench_norm, "attention": bench_attention, "profile": profile_case,
-     "tp": bench_tp}[case](C)
+     "tp": bench_tp, "collectives": bench_collectives}[case](C)
     return 0
 
 

@@ -20,6 +20,7 @@ from typing import List, Optional
 import torch
 
 from ...nn.module import Module
+from ...ops.functional import autograd_ready_hook
 from .. import global_env as genv
 from ..process_group import ProcessGroup, ProcessGroupFactory, ReduceOpType
 from .config import DistributedDataParallelConfig
@@ -134,9 +135,9 @@ class DistributedDataParallel(Module):
             if buf.zero2_temp_grads:
                 g = self.param_to_group[id(p)]
                 p._itb_main_grad_fn = (lambda g=g, p=p: g.full_grad_view(p))
-                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._zero2_hook))
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(autograd_ready_hook(self._zero2_hook)))
             else:
-                self._hook_handles.append(p.register_post_accumulate_grad_hook(self._on_grad_ready))
+                self._hook_handles.append(p.register_post_accumulate_grad_hook(autograd_ready_hook(self._on_grad_ready)))
             p._itb_grad_ready_hooks = [self._on_grad_ready]
 
     def _zero2_hook(self, p):

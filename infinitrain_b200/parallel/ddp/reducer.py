@@ -18,6 +18,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 
+from ...ops.functional import autograd_ready_hook
 from ..process_group import ProcessGroup, ReduceOpType, Work
 from .config import DistributedDataParallelConfig
 
@@ -150,7 +151,7 @@ class Reducer:
         for p in self.params:
             if not p.requires_grad:
                 continue
-            self._hook_handles.append(p.register_post_accumulate_grad_hook(self._on_grad))
+            self._hook_handles.append(p.register_post_accumulate_grad_hook(autograd_ready_hook(self._on_grad)))
             p._itb_grad_ready_hooks = [self._on_grad]
 
     def _on_grad(self, p):

@@ -140,14 +140,17 @@ def ddp(mode):
     losses = run(ddp_mod, opt, x.chunk(world)[rank], y.chunk(world)[rank], ddp_mod)
     dist.all_reduce(losses, op=dist.ReduceOp.AVG)
     assert (losses - ref_losses).abs().max().item() < 2e-2, (losses, ref_losses)
-    worst = 0.0
+    worst, worst_at = 0.0, ""
     num = den = 0.0
-    for p, r, p0 in zip(ddp_mod.Parameters(), ref_params, init_params):
-        worst = max(worst, ((p - r).norm() / (r.norm() + 1e-9)).item())
+    names = [n for n, _ in ddp_mod.named_parameters()]
+    for k, (p, r, p0) in enumerate(zip(ddp_mod.Parameters(), ref_params, init_params)):
+        rel = ((p - r).norm() / (r.norm() + 1e-9)).item()
+        if rel > worst:
+            worst, worst_at = rel, f"{names[k] if k < len(names) else k} {tuple(p.shape)}"
         num += float(((p - p0) - (r - p0)).double().pow(2).sum())
         den += float((r - p0).double().pow(2).sum())
     update_err = (num / max(den, 1e-30)) ** 0.5
-    assert worst < 0.05, worst
+    assert worst < 0.05, (worst, worst_at)
     # the four steps' total update, against the single-GPU run's: bf16 noise is a few per cent, a wrong
     # gradient scale is of order one
     assert update_err < 0.2, update_err

@@ -182,3 +182,39 @@ def test_remaining_catalogue_ops():
         out, torch.tensor([[0.3, 0.0, 0.7, 0.0], [0.0, 0.6, 0.0, 0.4]]))
     (out * torch.arange(8.0).view(2, 4)).sum().backward()
     assert torch.allclose(vals.grad, torch.tensor([[2.0, 0.0], [5.0, 7.0]]))                  # gathered back
+
+
+def test_autograd_hook_of_a_gradient_written_elsewhere_is_dropped():
+    """A linear whose bias gradient is produced by the norm's backward returns no gradient for the bias;
+    autograd still fires the bias's post-accumulate hook (with an undefined gradient) at that point.
+    That call must not reach the reducer: the bucket would be reduced before the norm has written it."""
+    import torch
+
+    from infinitrain_b200.ops import functional as F
+
+    class _Lin(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x, b):
+            return x + b
+
+        @staticmethod
+        def backward(ctx, g):
+            return g, None          # the bias gradient comes from elsewhere
+
+    x = torch.randn(4, requires_grad=True)
+    b = torch.zeros(4, requires_grad=True)
+    b.main_grad = torch.zeros(4)
+    ready = []
+    b.register_post_accumulate_grad_hook(F.autograd_ready_hook(lambda p: ready.append("autograd")))
+    b._itb_grad_ready_hooks = [lambda p: ready.append("written")]
+    holder = F._SkipHolder()
+    res = torch.zeros(4)
+    res._itb_skip_holder = holder
+    assert F.claim_bias_grad(res, b) and holder.bias is b
+    _Lin.apply(x, b).sum().backward()
+    assert ready == []                      # autograd's call was dropped
+    F._grad_written(b)                      # the norm's backward reports the slot
+    assert ready == ["written"] and not b._itb_grad_elsewhere
+    # a parameter nobody claimed is reported by autograd as before
+    _Lin.apply(x, b).sum().backward()
+    assert ready == ["written", "autograd"]
