@@ -245,3 +245,28 @@ def test_lora_in_any_layout_follows_the_one_rank_run_and_writes_the_same_adapter
     assert sorted(a) == sorted(b) and len(a) == 4 * 5 * 2
     assert max(float((a[k] - b[k]).abs().max()) for k in a) < 1e-6
     assert max(float((a[k] - c[k]).abs().max()) for k in a) > 1e-4        # and training moved them
+
+
+def test_gpu_regression_matrix_expands_to_the_references_runs(tmp_path):
+    """examples/common/matrix_gpu.json is the reference's scripts/test_config.json (groups basic, zero,
+    lora) for both model families and both dtypes; --dry-run prints the command of every run, --profile
+    adds the second pass with the profiler on."""
+    import json
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = json.load(open(os.path.join(root, "examples", "common", "matrix_gpu.json")))
+    ids = {r["id"] for r in spec["runs"]}
+    for want in ("1", "2_bfloat16", "3", "4", "5_bfloat16", "6", "7", "8", "3_zero1", "3_zero2", "8_zero2", "lora_3", "lora_5"):
+        assert want in ids, want
+    eight = next(r for r in spec["runs"] if r["id"] == "8" and r["family"] == "llama3")
+    assert eight["nproc"] == 8 and eight["args"]["tensor_parallel"] == 2 and eight["args"]["virtual_pipeline_parallel"] == 2
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "common", "run_matrix.py"),
+                        os.path.join(root, "examples", "common", "matrix_gpu.json"), "--out", str(tmp_path), "--dry-run", "--profile"],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 2 * len(spec["runs"])
+    assert sum("--profile" in ln for ln in lines) == len(spec["runs"])
+    assert any("--nproc_per_node=8" in ln and "--pipeline_parallel 8" in ln for ln in lines)
