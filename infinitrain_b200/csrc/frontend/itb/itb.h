@@ -20,6 +20,8 @@
 #include "pipeline.h"
 #include "precision.h"
 #include "process_group.h"
+#include "runtime.h"
+#include "tensor_api.h"
 #include "tensor_parallel.h"
 #include "tokenizer.h"
 #include "transformer.h"

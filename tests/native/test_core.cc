@@ -1,0 +1,121 @@
+// The device runtime (itb/runtime.h: streams with priorities, events, raw memory from the tensors'
+// pool, copies, the device guard) and the reference-named tensor functions (itb/tensor_api.h), on the
+// CPU and, in the CUDA pass, on cuda:0.  Reference surface: infini_train/include/core/runtime/
+// device_guard.h:59-143 and include/tensor.h:62-223.
+#define ITB_TEST_WITH_TORCH
+#include "itb_test.h"
+
+#include <fstream>
+
+#include "itb/itb.h"
+
+using itb::Tensor;
+using itbtest::device;
+namespace core = itb::core;
+namespace ta = itb::tensor_api;
+
+ITB_TEST_P(Runtime, StreamsEventsAndOrdering) {
+  core::Runtime& rt = core::Runtime::For(device());
+  EXPECT(rt.Type() == device().type() && rt.DeviceCount() >= 1);
+  int low = 1, high = 1;
+  rt.GetStreamPriorityRange(&low, &high);
+  EXPECT(high <= low);
+  core::Stream cur = rt.GetStream(device());
+  core::Stream side = rt.CreateStreamWithPriority(device(), high);
+  EXPECT(side.priority() == high && side.device().type() == device().type());
+  core::Event a, b, untimed(core::EventFlag::kDisableTiming);
+  EXPECT(rt.EventQuery(&a) == core::RuntimeStatus::kError);   // never recorded
+  EXPECT_THROWS(rt.StreamWaitEvent(side, &a));
+  rt.EventRecord(&a, cur);
+  Tensor x = torch::ones({1 << 16}, torch::dtype(torch::kFloat32).device(device()));
+  for (int i = 0; i < 8; ++i) x = x * 1.0001f + 0.5f;
+  rt.EventRecord(&b, cur);
+  rt.StreamWaitEvent(side, &b);          // work queued on `side` from here on sees x
+  EXPECT(rt.EventSynchronize(&b) == core::RuntimeStatus::kSuccess);
+  EXPECT(rt.EventQuery(&a) == core::RuntimeStatus::kSuccess);
+  EXPECT(rt.EventElapsedTime(&a, &b) >= 0.0f);
+  rt.EventRecord(&untimed, cur);
+  EXPECT_THROWS(rt.EventElapsedTime(&a, &untimed));
+  rt.SynchronizeStream(side);
+  rt.SynchronizeDevice(device());
+}
+
+ITB_TEST_P(Runtime, RawMemoryAndCopies) {
+  core::Runtime& rt = core::Runtime::For(device());
+  const size_t n = 1 << 14;
+  std::vector<float> host(n), back(n, 0.f);
+  for (size_t i = 0; i < n; ++i) host[i] = static_cast<float>(i) * 0.25f;
+  rt.ResetMemPoolHighWatermarks(device());
+  void *p = nullptr, *q = nullptr;
+  rt.Malloc(&p, n * sizeof(float));
+  core::Stream s = rt.CreateStream(device());
+  rt.MallocAsync(&q, n * sizeof(float), s);
+  EXPECT(p && q && p != q && reinterpret_cast<uintptr_t>(p) % 64 == 0);
+  rt.Memcpy(p, host.data(), n * sizeof(float), core::MemcpyKind::kH2D);
+  core::Event copied;
+  rt.EventRecord(&copied, rt.GetStream(device()));
+  rt.StreamWaitEvent(s, &copied);
+  rt.MemcpyAsync(q, p, n * sizeof(float), core::MemcpyKind::kD2D, s);
+  rt.SynchronizeStream(s);
+  rt.Memcpy(back.data(), q, n * sizeof(float), core::MemcpyKind::kD2H);
+  EXPECT(back == host);
+  if (rt.is_cuda()) EXPECT(rt.GetMemPoolPeakMB(device()).second >= rt.GetMemPoolPeakMB(device()).first);
+  rt.FreeAsync(q, s);
+  rt.Free(p);
+  rt.Free(nullptr);
+}
+
+ITB_TEST_P(Runtime, DeviceGuardRestoresTheDevice) {
+  core::Runtime& rt = core::Runtime::For(device());
+  const torch::Device before = rt.GetDevice();
+  {
+    core::DeviceGuard g(device());
+    EXPECT(g.original_device() == before && g.current_device().type() == device().type());
+    if (rt.is_cuda() && rt.DeviceCount() > 1) {
+      g.SetDevice(torch::Device(torch::kCUDA, 1));
+      EXPECT(rt.GetDevice().index() == 1);
+    }
+  }
+  EXPECT(rt.GetDevice() == before);
+}
+
+ITB_TEST_P(TensorApi, ReferenceNamesComputeWhatTheirTorchFormsDo) {
+  torch::manual_seed(3);
+  Tensor a = torch::randn({4, 6}).to(device()), b = torch::randn({4, 6}).to(device());
+  EXPECT(ta::Dims(a) == (std::vector<int64_t>{4, 6}) && ta::NumElements(a) == 24 && ta::SizeInBytes(a) == 96);
+  EXPECT(torch::equal(ta::Add(ta::Mul(a, 2.0f), b), a * 2.0f + b));
+  EXPECT(torch::equal(ta::And(ta::Gt(a, 0.f), ta::Le(b, a)), (a > 0).logical_and(b <= a)));
+  EXPECT(torch::allclose(ta::Matmul(a, ta::Transpose(b, 0, 1)), a.matmul(b.t())));
+  EXPECT(torch::equal(ta::Max(a, 1, true), std::get<0>(a.max(1, true))));
+  EXPECT(ta::Split(a, 4, 1).size() == 2 && ta::Slice(a, 1, 0, 6, 2).size(1) == 3);
+  EXPECT(torch::equal(ta::MaskedFill(a, ta::Lt(a, 0.f), 0.f), a.clamp_min(0.f)));
+  EXPECT(torch::allclose(ta::Outer(ta::Flatten(a), ta::Flatten(b)).sum(), a.sum() * b.sum(), 1e-3, 1e-3));
+  Tensor w = ta::RequiresGrad(torch::ones({6}).to(device()));
+  ta::Backward(ta::Sum(ta::Mul(ta::Matmul(a, w), ta::Matmul(a, w)), 0));
+  EXPECT(torch::allclose(w.grad(), 2.0f * a.t().matmul(a.matmul(w.detach())), 1e-4, 1e-4));
+  ta::ZeroGrad(w);
+  EXPECT(!w.grad().defined());
+  Tensor f = ta::MakeTensor({3, 2}, torch::kFloat32, device());
+  ta::Fill(f, 1.5);
+  Tensor g = torch::zeros({3, 2}, torch::kFloat64);
+  ta::CopyFrom(g, f);                                   // across devices and dtypes
+  EXPECT(g.sum().item<double>() == 9.0);
+}
+
+ITB_TEST(TensorApi, SaveAsNpyWritesAVersionOneFile) {
+  Tensor t = torch::arange(6, torch::kFloat32).view({2, 3});
+  const std::string path = "itb_test_core.npy";
+  ta::SaveAsNpy(t, path);
+  std::ifstream in(path, std::ios::binary);
+  std::string bytes((std::istreambuf_iterator<char>(in)), std::istreambuf_iterator<char>());
+  EXPECT(bytes.size() > 64 && bytes.compare(1, 5, "NUMPY") == 0 && bytes[6] == 1);
+  EXPECT(bytes.find("'shape': (2,3)") != std::string::npos && bytes.find("'<f4'") != std::string::npos);
+  const size_t data = 10 + (static_cast<unsigned char>(bytes[8]) | (static_cast<unsigned char>(bytes[9]) << 8));
+  EXPECT(data % 64 == 0 && bytes.size() == data + 24);
+  float last;
+  std::memcpy(&last, bytes.data() + data + 20, 4);
+  EXPECT(last == 5.0f);
+  std::remove(path.c_str());
+}
+
+ITB_TEST_MAIN()
