@@ -87,6 +87,10 @@ class Runtime {
     if (device.is_cuda()) {
 #ifndef ITB_WITH_CUDA
       TORCH_CHECK(false, "this build has no CUDA runtime (compile with -DITB_WITH_CUDA)");
+#else
+      // the caching allocator and the stream pools exist only after libtorch's lazy CUDA initialisation
+      static const bool ready = (at::globalContext().lazyInitDevice(c10::DeviceType::CUDA), true);
+      (void)ready;
 #endif
       return cuda;
     }
@@ -124,7 +128,8 @@ class Runtime {
   }
   Stream CreateStream(torch::Device device) const { return CreateStreamWithPriority(device, 0); }
   // priority: 0 = default, negative = higher (as the CUDA runtime counts).  Streams come from c10's
-  // pools (32 per priority and device, handed out round robin), so "destroying" one is a no-op.
+  // pools (32 per priority and device, handed out round robin), so "destroying" one is a no-op; c10
+  // keeps fewer priority levels than the device offers and clamps the request to the highest it has.
   Stream CreateStreamWithPriority(torch::Device device, int priority) const {
 #ifdef ITB_WITH_CUDA
     if (is_cuda()) return Stream(device, c10::cuda::getStreamFromPool(priority, index_of(device)));

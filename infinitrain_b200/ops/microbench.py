@@ -333,6 +333,42 @@ def bench_collectives(C):
         res["status"] = ctx.status()
         if rank == 0:
             print(json.dumps(res), flush=True)
+    # vocab-parallel cross-entropy statistics of 2048 token rows: one kernel that exchanges (lse, target
+    # logit) pairs and merges them, against three all-reduces (max, sum of exponentials, target logit)
+    rows, shard = 2048, 16032
+    merge = symm.VocabCEMerge(ctx)
+    lse_l = torch.randn(rows, device=dev) + 10.0
+    # local target index: inside [0, shard) on the rank that owns the row's target, outside elsewhere
+    own = (torch.arange(rows, device=dev) % world) == rank
+    t_l = torch.where(own, torch.randint(0, shard, (rows,), device=dev), torch.full((rows,), -1, device=dev))
+    picked = torch.randn(rows, device=dev)
+    row_loss = torch.where(own, lse_l - picked, torch.zeros_like(lse_l))
+    res = {"case": "collectives", "world": world, "op": "vocab_ce_merge", "rows": rows}
+    res["fused_ms"] = timed(lambda: merge(lse_l, row_loss, t_l, shard))
+
+    def nccl_merge():   # the formulation the framework falls back to: one all-gather of (lse, target logit) pairs
+        tgt = torch.where(own, lse_l - row_loss, torch.zeros_like(lse_l))
+        stats = torch.stack([lse_l, tgt], dim=0).contiguous()
+        allst = torch.empty((world,) + tuple(stats.shape), device=dev)
+        dist.all_gather_into_tensor(allst.view(-1), stats.view(-1))
+        return torch.logsumexp(allst[:, 0], dim=0) - allst[:, 1].sum(0)
+
+    def nccl_three():   # the reference's three all-reduces: max, sum of exponentials, target logit
+        m = lse_l.clone()
+        dist.all_reduce(m, op=dist.ReduceOp.MAX)
+        se = torch.exp(lse_l - m)
+        dist.all_reduce(se)
+        tl = torch.where(own, lse_l - row_loss, torch.zeros_like(lse_l))
+        dist.all_reduce(tl)
+        return m + torch.log(se) - tl
+
+    res["nccl_allgather_ms"] = timed(nccl_merge)
+    res["nccl_three_allreduces_ms"] = timed(nccl_three)
+    # 8 bytes per row to every peer: latency-bound (two flag barriers), not bandwidth-bound
+    res["floor_ms"] = 8.0 * rows * (world - 1) / link * 1e3
+    res["status"] = ctx.status()
+    if rank == 0:
+        print(json.dumps(res), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

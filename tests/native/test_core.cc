@@ -22,7 +22,9 @@ ITB_TEST_P(Runtime, StreamsEventsAndOrdering) {
   EXPECT(high <= low);
   core::Stream cur = rt.GetStream(device());
   core::Stream side = rt.CreateStreamWithPriority(device(), high);
-  EXPECT(side.priority() == high && side.device().type() == device().type());
+  // the pools keep fewer levels than the device offers: a high-priority request gets the highest there is
+  EXPECT(side.priority() <= 0 && (high == 0 || side.priority() < 0) && side.priority() >= high);
+  EXPECT(side.device().type() == device().type());
   core::Event a, b, untimed(core::EventFlag::kDisableTiming);
   EXPECT(rt.EventQuery(&a) == core::RuntimeStatus::kError);   // never recorded
   EXPECT_THROWS(rt.StreamWaitEvent(side, &a));
