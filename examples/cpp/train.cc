@@ -9,6 +9,8 @@
 //             [--save DIR --save_interval N] [--load DIR/checkpoint_step_000004]
 //             [--tensor_parallel N --sequence_parallel --pipeline_parallel N --virtual_pipeline_parallel N
 //              --pipeline_schedule 1f1b|gpipe --zero_stage 0|1|2 --no_overlap_grad_reduce]
+//             [--profile]   per-op / per-collective records, written as <family>.report.rank<r> and
+//                           <family>.records.log.rank<r> into the working directory
 // The ranks are laid out TP fastest, then DP, then PP; data parallelism takes what is left of the
 // world size.  CPU ranks talk through the job's TCP store, GPU ranks through NCCL.
 #include <chrono>
@@ -205,8 +207,11 @@ int main(int argc, char** argv) {
     return (*loss_module)(itb::TensorList{logits, y})[0];
   };
 
+  const bool profile = fl.getb("profile", false);
+  if (profile) itb::utils::Profiler::Instance().Enable(env.rank);
   for (int64_t step = start_step; step < iters; ++step) {
     auto t0 = std::chrono::steady_clock::now();
+    if (profile) itb::utils::Profiler::Instance().SetTag("Step_" + std::to_string(step + 1));
     itb::utils::PrecisionChecker::Instance().ResetCounters();
     optimizer->ZeroGrad();
     if (ddp) ddp->ZeroGrad();
@@ -274,6 +279,12 @@ int main(int argc, char** argv) {
       st.vocab_size = cfg.vocab_size, st.ddp_size = dp, st.tp_size = tp, st.sp_size = env.sp(), st.pp_size = pp;
       itb::io::SaveCheckpoint(fl.get("save", ""), st, *model, optimizer->StateDict(), own_state ? env.rank : -1);
     }
+  }
+  if (profile) {
+    auto& prof = itb::utils::Profiler::Instance();
+    prof.Disable();
+    prof.Report(family + ".report.rank" + std::to_string(env.rank));
+    prof.PrintRecords(family + ".records.log.rank" + std::to_string(env.rank));
   }
   if (auto world = par::ProcessGroupFactory::Instance().GetDefaultProcessGroup()) world->Barrier();
   if (lora_rank > 0 && !fl.get("lora_save_path", "").empty() && env.rank == 0) itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", ""));

@@ -19,6 +19,7 @@
 #include "parallel_env.h"
 #include "pipeline.h"
 #include "precision.h"
+#include "profiler.h"
 #include "process_group.h"
 #include "runtime.h"
 #include "tensor_api.h"

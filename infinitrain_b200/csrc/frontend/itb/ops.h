@@ -11,6 +11,7 @@
 #include <cmath>
 
 #include "module.h"
+#include "profiler.h"
 
 namespace itb {
 
@@ -66,6 +67,7 @@ inline Tensor new_gelu(const Tensor& x) {
 // y = x W^T (+ bias) (+ gelu) (+ residual)
 inline Tensor linear(const Tensor& x, const Tensor& weight, const c10::optional<Tensor>& bias = c10::nullopt,
                      const c10::optional<Tensor>& residual = c10::nullopt, bool gelu = false) {
+  ITB_PROFILE("linear", x);
 #ifdef ITB_WITH_CUDA
   if (use_fused(x) && x.size(-1) % 8 == 0 && weight.is_cuda()) return fused::linear(x, weight, bias, residual, gelu);
 #endif
@@ -84,6 +86,7 @@ inline Tensor linear(const Tensor& x, const Tensor& weight, const c10::optional<
 }
 
 inline Tensor layernorm(const Tensor& x, const Tensor& gamma, const c10::optional<Tensor>& beta, double eps = 1e-5) {
+  ITB_PROFILE("layernorm", x);
 #ifdef ITB_WITH_CUDA
   if (x.is_cuda() && gamma.scalar_type() == torch::kFloat32 && x.size(-1) % 8 == 0 && x.size(-1) <= 6144)
     return fused::layernorm(x, gamma, beta, eps);
@@ -97,6 +100,7 @@ inline Tensor layernorm(const Tensor& x, const Tensor& gamma, const c10::optiona
 }
 
 inline Tensor rmsnorm(const Tensor& x, const Tensor& gamma, double eps = 1e-6) {
+  ITB_PROFILE("rmsnorm", x);
 #ifdef ITB_WITH_CUDA
   if (x.is_cuda() && gamma.scalar_type() == torch::kFloat32 && x.size(-1) % 8 == 0 && x.size(-1) <= 6144)
     return fused::rmsnorm(x, gamma, eps);
@@ -106,6 +110,7 @@ inline Tensor rmsnorm(const Tensor& x, const Tensor& gamma, double eps = 1e-6) {
 }
 
 inline Tensor gelu(const Tensor& x) {
+  ITB_PROFILE("gelu", x);
 #ifdef ITB_WITH_CUDA
   if (x.is_cuda() && (x.scalar_type() == torch::kFloat32 || x.scalar_type() == torch::kBFloat16))
     return fused::gelu(x);
@@ -114,6 +119,7 @@ inline Tensor gelu(const Tensor& x) {
 }
 
 inline Tensor swiglu(const Tensor& a, const Tensor& b) {
+  ITB_PROFILE("swiglu", a);
 #ifdef ITB_WITH_CUDA
   if (a.is_cuda() && a.size(-1) % 8 == 0 && (a.scalar_type() == torch::kFloat32 || a.scalar_type() == torch::kBFloat16))
     return fused::swiglu_packed(torch::cat({a, b}, -1));
@@ -132,6 +138,7 @@ inline Tensor precompute_freqs_cis(int64_t head_dim, int64_t end, double theta =
 
 // x [B, T, H, D] with interleaved (even, odd) pairs.
 inline Tensor apply_rope(const Tensor& x, const Tensor& freqs, int64_t pos0 = 0) {
+  ITB_PROFILE("apply_rope", x);
   auto B = x.size(0), T = x.size(1), H = x.size(2), D = x.size(3);
   auto xf = x.to(torch::kFloat32).reshape({B, T, H, D / 2, 2});
   auto f = freqs.slice(0, pos0, pos0 + T);
@@ -145,6 +152,7 @@ inline Tensor apply_rope(const Tensor& x, const Tensor& freqs, int64_t pos0 = 0)
 inline Tensor attention_packed(const Tensor& qkv, int64_t H, int64_t KV, int64_t D,
                                const c10::optional<Tensor>& freqs = c10::nullopt, int64_t pos0 = 0,
                                bool causal = true) {
+  ITB_PROFILE("attention_packed", qkv);
 #ifdef ITB_WITH_CUDA
   if (qkv.is_cuda() && (D == 64 || D == 128) && use_fused(qkv))
     return fused::attention_packed(qkv, H, KV, D, freqs, pos0, causal);
@@ -174,6 +182,7 @@ inline Tensor attention_packed(const Tensor& qkv, int64_t H, int64_t KV, int64_t
 // Token (+ position) embedding.
 inline Tensor embedding(const Tensor& idx, const Tensor& wte, const c10::optional<Tensor>& wpe = c10::nullopt,
                         int64_t pos0 = 0) {
+  ITB_PROFILE("embedding", idx);
 #ifdef ITB_WITH_CUDA
   if (wte.is_cuda() && wte.scalar_type() == torch::kFloat32 && wte.size(1) % 8 == 0 && idx.dim() == 2)
     return fused::embedding(idx, wte, wpe, pos0);
@@ -185,6 +194,7 @@ inline Tensor embedding(const Tensor& idx, const Tensor& wte, const c10::optiona
 
 // Mean cross-entropy over all rows, statistics in fp32.
 inline Tensor cross_entropy(const Tensor& logits, const Tensor& target) {
+  ITB_PROFILE("cross_entropy", logits);
 #ifdef ITB_WITH_CUDA
   if (logits.is_cuda() && (logits.scalar_type() == torch::kFloat32 || logits.scalar_type() == torch::kBFloat16))
     return fused::cross_entropy(logits, target);

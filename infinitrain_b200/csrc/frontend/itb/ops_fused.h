@@ -5,6 +5,7 @@
 // Mixed precision as in the Python layer: bf16 activations and bf16 weight shadows into the tcgen05
 // GEMM, fp32 accumulation, fp32 weight / bias / norm gradients, fp32 statistics.
 #pragma once
+#include "profiler.h"
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
@@ -154,6 +155,7 @@ struct LinearFn : public torch::autograd::Function<LinearFn> {
     return y.view(shape);
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    ITB_PROFILE("linear[bwd]", grads[0]);
     auto saved = ctx->get_saved_variables();
     Tensor x2 = saved[0], weight = saved[1], pre = saved[2];
     Tensor dy = grads[0];
@@ -222,6 +224,7 @@ struct LayerNormFn : public torch::autograd::Function<LayerNormFn> {
     return y;
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    ITB_PROFILE("layernorm[bwd]", grads[0]);
     auto s = ctx->get_saved_variables();
     Tensor x = s[0], gamma = s[1], mean = s[2], rstd = s[3];
     Tensor dy = contig(grads[0]);
@@ -252,6 +255,7 @@ struct RMSNormFn : public torch::autograd::Function<RMSNormFn> {
     return y;
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    ITB_PROFILE("rmsnorm[bwd]", grads[0]);
     auto s = ctx->get_saved_variables();
     Tensor x = s[0], gamma = s[1], rstd = s[2];
     Tensor dy = contig(grads[0]);
@@ -276,6 +280,7 @@ struct GeluFn : public torch::autograd::Function<GeluFn> {
     return y;
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    ITB_PROFILE("gelu[bwd]", grads[0]);
     Tensor x = ctx->get_saved_variables()[0];
     Tensor dy = contig(grads[0].to(x.scalar_type())), dx = torch::empty_like(x);
     check(itb_gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), code(x), x.numel(), stream()), "gelu_bwd");
@@ -302,6 +307,7 @@ struct SwiGLUFn : public torch::autograd::Function<SwiGLUFn> {
     return out.view(shape);
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    ITB_PROFILE("swiglu[bwd]", grads[0]);
     Tensor ab2 = ctx->get_saved_variables()[0];
     int64_t F = ab2.size(1) / 2, rows = ab2.size(0), eb = ab2.element_size();
     Tensor d2 = grads[0].reshape({-1, F}).to(ab2.scalar_type());
@@ -353,6 +359,7 @@ struct AttentionFn : public torch::autograd::Function<AttentionFn> {
     return o.view({B, T, H * D});
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    ITB_PROFILE("attention_packed[bwd]", grads[0]);
     auto s = ctx->get_saved_variables();
     Tensor qkv = s[0], o = s[1], lse = s[2], freqs = s[3];
     auto meta = ctx->saved_data["meta"].toIntVector();
@@ -406,6 +413,7 @@ struct EmbeddingFn : public torch::autograd::Function<EmbeddingFn> {
     return out;
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    ITB_PROFILE("embedding[bwd]", grads[0]);
     auto s = ctx->get_saved_variables();
     Tensor idx = s[0], wte = s[1], wpe = s[2];
     Tensor dout = contig(grads[0]);
@@ -441,6 +449,7 @@ struct CrossEntropyFn : public torch::autograd::Function<CrossEntropyFn> {
     return loss.reshape({});
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    ITB_PROFILE("cross_entropy[bwd]", grads[0]);
     auto s = ctx->get_saved_variables();
     Tensor l2 = s[0], t = s[1], lse = s[2];
     Tensor g = grads[0].reshape({1}).to(torch::kFloat32);

@@ -34,6 +34,7 @@ class SGD : public Optimizer {
  public:
   SGD(TensorList params, double lr) : Optimizer(std::move(params)), lr_(lr) {}
   void Step() override {
+    ITB_PROFILE("sgd.Step", params_.empty() ? Tensor() : params_[0]);
     torch::NoGradGuard g;
     for (auto& p : params_) {
       if (!p.grad().defined()) continue;
@@ -67,6 +68,7 @@ class Adam : public Optimizer {
     }
   }
   void Step() override {
+    ITB_PROFILE("adam.Step", params_.empty() ? Tensor() : params_[0]);
     torch::NoGradGuard g;
     ++t_;
     double bc1 = 1.0 - std::pow(b1_, t_), bc2 = 1.0 - std::pow(b2_, t_);

@@ -25,6 +25,7 @@
 
 #include "module.h"
 #include "parallel_env.h"
+#include "profiler.h"
 #ifdef ITB_WITH_CUDA
 #include <ATen/cuda/CUDAContext.h>
 #include <ATen/cuda/CUDAEvent.h>
@@ -128,6 +129,7 @@ class StoreProcessGroup : public ProcessGroup {
       : ProcessGroup(std::move(name), std::move(ranks), my_global_rank), store_(std::move(store)) {}
 
   std::shared_ptr<Work> AllReduce(Tensor& t, ReduceOp op, bool) override {
+    ITB_PROFILE("pg.AllReduce(" + name_ + ")", false);
     Check(t);
     const int64_t n = seq_++;
     Publish(Key("c", n, rank()), t);
@@ -139,6 +141,7 @@ class StoreProcessGroup : public ProcessGroup {
     return done();
   }
   std::shared_ptr<Work> AllGather(Tensor& out, const Tensor& in, bool) override {
+    ITB_PROFILE("pg.AllGather(" + name_ + ")", false);
     Check(out), Check(in);
     TORCH_CHECK(out.numel() == in.numel() * size(), "AllGather: output must hold one input per rank");
     const int64_t n = seq_++;
@@ -149,6 +152,7 @@ class StoreProcessGroup : public ProcessGroup {
     return done();
   }
   std::shared_ptr<Work> ReduceScatter(Tensor& out, const Tensor& in, ReduceOp op, bool) override {
+    ITB_PROFILE("pg.ReduceScatter(" + name_ + ")", false);
     Check(out), Check(in);
     TORCH_CHECK(in.numel() == out.numel() * size(), "ReduceScatter: input must hold one output per rank");
     const int64_t n = seq_++;
@@ -164,6 +168,7 @@ class StoreProcessGroup : public ProcessGroup {
     return done();
   }
   std::shared_ptr<Work> BroadCast(Tensor& t, int src, bool) override {
+    ITB_PROFILE("pg.BroadCast(" + name_ + ")", false);
     Check(t);
     const int64_t n = seq_++;
     const std::string key = Key("c", n, src), ack = key + "/ack";
@@ -368,6 +373,7 @@ class NcclProcessGroup : public ProcessGroup {
  private:
   template <class F>
   std::shared_ptr<Work> Run(bool async_op, const TensorList& touched, F&& enqueue) {
+    ITB_PROFILE("pg.nccl(" + name_ + ")", true);
     for (const Tensor& t : touched) TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "NcclProcessGroup: contiguous CUDA tensors");
     auto compute = at::cuda::getCurrentCUDAStream();
     at::cuda::CUDAEvent ready;

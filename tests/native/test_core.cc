@@ -6,6 +6,7 @@
 #include "itb_test.h"
 
 #include <fstream>
+#include <sstream>
 
 #include "itb/itb.h"
 
@@ -118,6 +119,39 @@ ITB_TEST(TensorApi, SaveAsNpyWritesAVersionOneFile) {
   std::memcpy(&last, bytes.data() + data + 20, 4);
   EXPECT(last == 5.0f);
   std::remove(path.c_str());
+}
+
+ITB_TEST_P(Profiler, RecordsOpsOncePerOuterRangeAndReportsPerTag) {
+  auto& prof = itb::utils::Profiler::Instance();
+  prof.Reset();
+  torch::manual_seed(1);
+  Tensor x = torch::randn({8, 16}).to(device()), w = torch::randn({32, 16}).to(device()).set_requires_grad(true);
+  itb::ops::linear(x, w);                      // disabled: nothing is recorded
+  EXPECT(prof.records().empty());
+  prof.Enable(3);
+  prof.SetTag("Step_1");
+  {
+    ITB_PROFILE("outer", x);
+    itb::ops::linear(x, w);                    // nested in "outer": part of it
+  }
+  Tensor y = itb::ops::linear(x, w);
+  itb::ops::layernorm(y, torch::ones({32}).to(device()), c10::nullopt);
+  prof.SetTag("Step_2");
+  itb::ops::linear(x, w).sum().backward();
+  prof.Disable();
+  std::vector<std::string> names;
+  for (const auto& r : prof.records()) names.push_back(r.tag + ":" + r.name);
+  EXPECT(names.size() >= 4 && names[0] == "Step_1:outer" && names[1] == "Step_1:linear" && names[2] == "Step_1:layernorm");
+  EXPECT(names[3] == "Step_2:linear");
+  for (const auto& r : prof.records()) EXPECT(r.rank == 3 && r.host_us >= 0 && r.device == (device().is_cuda() ? "cuda" : "cpu"));
+  if (device().is_cuda()) EXPECT(prof.records()[1].device_us > 0);
+  std::ostringstream rep, rec;
+  prof.Report(rep, itb::utils::Profiler::SortBy::Count);
+  prof.PrintRecords(rec);
+  EXPECT(rep.str().find("Tag: Step_1") != std::string::npos && rep.str().find("Tag: Step_2") != std::string::npos);
+  EXPECT(rep.str().find("Device Avg(us)") != std::string::npos && rec.str().find("Step_2\t3\tlinear") != std::string::npos);
+  prof.Reset();
+  EXPECT(prof.records().empty());
 }
 
 ITB_TEST_MAIN()

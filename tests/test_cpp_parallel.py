@@ -139,3 +139,29 @@ def test_model_parallel_checkpoint_resumes_per_rank(binaries, files, tmp_path):
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
     resumed = _losses(r.stdout + r.stderr)
     assert len(resumed) == 2 and max(abs(a - b) for a, b in zip(resumed, full[2:])) <= 2e-5, (resumed, full)
+
+
+def test_profile_flag_writes_per_rank_reports_with_ops_and_collectives(binaries, files, tmp_path):
+    """--profile: every rank writes <family>.report.rank<r> and <family>.records.log.rank<r>; the records
+    are tagged by step and hold the ops, the optimizer step and the process-group collectives."""
+    import shutil
+
+    work = tmp_path / "run"
+    work.mkdir()
+    for name in ("llama3.bin", "tokens32.bin"):
+        shutil.copy(files / name, work / name)
+    launcher, trainer = binaries
+    cmd = [launcher, "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", trainer, "--family", "llama3",
+           "--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin", "--batch_size", "2",
+           "--sequence_length", "64", "--total_batch_size", "256", "--num_iteration", "2", "--dtype", "float32", *LLAMA,
+           "--tensor_parallel", "2", "--profile"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=work, env=ENV)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    for rank in (0, 1):
+        report = (work / f"llama3.report.rank{rank}").read_text()
+        records = (work / f"llama3.records.log.rank{rank}").read_text()
+        assert "Tag: Step_1" in report and "Tag: Step_2" in report and "Device Avg(us)" in report
+        for name in ("linear", "rmsnorm", "attention_packed", "adam.Step", "pg.AllReduce(TP0)"):
+            assert name in report, (name, report[:2000])
+        first = records.splitlines()[0].split("\t")
+        assert first[0] == "Step_1" and first[1] == str(rank) and first[3] == "cpu"
