@@ -137,9 +137,13 @@ int main(int argc, char** argv) {
     lora::LoRAConfig lc;
     lc.rank = lora_rank, lc.alpha = fl.getd("lora_alpha", 16.0);
     lc.target_modules = lora::ParseLoRATargetModules(fl.get("lora_target_modules", "c_attn,c_proj"));
+    // the adapters' draws must not depend on how many numbers the (layout-dependent) construction of the
+    // base model took from the stream: every layout starts them from the same state
+    itb::nn::ManualSeed(static_cast<uint32_t>(fl.geti("seed", 42)) ^ 0x4C6F5241u);
     lora::GetLoRAModel(model, lc);
     model->To(device);
-    if (!fl.get("lora_load_path", "").empty()) lora::LoadLoRAWeights(model, fl.get("lora_load_path", ""));
+    if (!fl.get("lora_load_path", "").empty())
+      lora::LoadLoRAWeights(model, fl.get("lora_load_path", "") + (tp * pp > 1 ? ".rank" + std::to_string(env.rank) : ""));
     std::fprintf(stderr, "[I] %s\n", lora::PrintLoRASummary(model).c_str());
   }
   // ---- data parallelism: the wrapper broadcasts rank 0's parameters and reduces gradients during backward
@@ -250,6 +254,8 @@ int main(int argc, char** argv) {
     // under sequence parallelism the parameters that every tensor-parallel rank holds whole saw a
     // slice of the sequence each: their gradients are partial sums
     if (env.sequence_parallel) par::AllReduceSequenceParallelGrads(model->SequenceParallelReplicated());
+    // replicated adapter factors next to a split one hold this rank's part of their gradient
+    if (lora_rank > 0 && tp > 1) par::AllReduceSequenceParallelGrads(itb::nn::lora::PartialGradParameters(model), /*always=*/true);
     optimizer->Step();
     if (dp_group) {
       itb::Tensor l = torch::full({1}, lossf, torch::dtype(torch::kFloat32).device(device));
@@ -287,7 +293,9 @@ int main(int argc, char** argv) {
     prof.PrintRecords(family + ".records.log.rank" + std::to_string(env.rank));
   }
   if (auto world = par::ProcessGroupFactory::Instance().GetDefaultProcessGroup()) world->Barrier();
-  if (lora_rank > 0 && !fl.get("lora_save_path", "").empty() && env.rank == 0) itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", ""));
+  // adapters of a model-parallel run are this rank's slices: one file per rank
+  if (lora_rank > 0 && !fl.get("lora_save_path", "").empty() && env.dp_rank == 0 && (env.rank == 0 || model_parallel))
+    itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", "") + (model_parallel ? ".rank" + std::to_string(env.rank) : ""));
   ddp.reset();
   par::ProcessGroupFactory::Instance().Shutdown();
   return 0;

@@ -41,19 +41,41 @@ inline std::set<std::string> ParseLoRATargetModules(const std::string& spec) {
   return out;
 }
 
+// One wrapper for the three kinds of base layer.  Around a tensor-parallel base the low-rank factors
+// follow the base's split (reference: infini_train/src/nn/lora/lora_parallel_linear.cc):
+//   column-parallel base, W [out / tp, in]:  A [r, in] replicated, B [out / tp, r] split like W's rows;
+//   row-parallel base,    W [out, in / tp]:  A [r, in / tp] split like W's columns, B [out, r] replicated;
+//     the rank-r partial products x_local A^T are summed over the group (all-reduce, or reduce-scatter
+//     along the sequence) beside the base's partial outputs, B is applied after the sum.
+// A is drawn at its FULL shape on every rank from the shared initialisation stream and then cut, so a
+// tensor-parallel run starts from the adapters a one-rank run starts from.  The replicated factor sees
+// only this rank's part of the product in backward (A of a column base always, B of a row base under
+// sequence parallelism): PartialGradParameters() lists them for the sum over the group that has to
+// precede the optimizer step.
 class LoRALinear : public Linear {
  public:
+  enum class Kind { kPlain, kColumn, kRow };
   LoRALinear(const std::shared_ptr<Linear>& base, const LoRAConfig& config) : Linear(*base, "LoRALinear"), config(config) {
-    auto opt = weight.options().requires_grad(false);
-    lora_A = register_parameter("lora_A", torch::empty({config.rank, in_features()}, opt));
-    init::KaimingUniform(lora_A);
-    lora_B = register_parameter("lora_B", torch::zeros({out_features(), config.rank}, opt));
-    weight.set_requires_grad(false);
-    if (bias.defined()) bias.set_requires_grad(false);
+    Init(in_features(), /*a_cols_begin=*/0);
+  }
+  LoRALinear(const std::shared_ptr<parallel::ColumnParallelLinear>& base, const LoRAConfig& config)
+      : Linear(*base, "LoRAColumnParallelLinear"), config(config), kind_(Kind::kColumn), column_(base) {
+    Init(in_features(), 0);
+  }
+  LoRALinear(const std::shared_ptr<parallel::RowParallelLinear>& base, const LoRAConfig& config)
+      : Linear(*base, "LoRARowParallelLinear"), config(config), kind_(Kind::kRow), row_(base) {
+    const auto& pe = parallel::env();
+    Init(in_features() * pe.tp(), in_features() * pe.tp_rank);
+  }
+  Kind kind() const { return kind_; }
+  static bool IsLoRAType(const std::string& type) {
+    return type == "LoRALinear" || type == "LoRAColumnParallelLinear" || type == "LoRARowParallelLinear";
   }
   Tensor forward(const Tensor& x, const c10::optional<Tensor>& residual = c10::nullopt, bool gelu = false) override {
     TORCH_CHECK(!(merged_ && (lora_A.requires_grad() || lora_B.requires_grad())),
                 "Forward() on merged LoRA with requires_grad=true. Call UnmergeWeights() before training.");
+    if (kind_ == Kind::kColumn) return ForwardColumn(x, residual, gelu);
+    if (kind_ == Kind::kRow) return ForwardRow(x, residual, gelu);
     if (merged_) return ops::linear(x, weight, opt(bias), residual, gelu);
     // the low-rank branch joins before the activation, so a fused GELU epilogue cannot be used here
     Tensor y = ops::linear(x, weight, opt(bias));
@@ -63,6 +85,7 @@ class LoRALinear : public Linear {
     if (residual.has_value()) y = y + *residual;
     return y;
   }
+  // this rank's part of (alpha / r) B A, in the shape of this rank's base weight
   Tensor Delta() const {
     return torch::matmul(lora_B.detach().to(torch::kFloat32), lora_A.detach().to(torch::kFloat32)) * config.Scaling();
   }
@@ -83,11 +106,59 @@ class LoRALinear : public Linear {
     lora_B.set_requires_grad(true);
   }
   bool IsMerged() const { return merged_; }
+  // the factor whose gradient is a partial sum on every tensor-parallel rank (undefined when there is none)
+  Tensor PartialGradFactor() const {
+    if (kind_ == Kind::kColumn && parallel::env().tp() > 1) return lora_A;
+    if (kind_ == Kind::kRow && row_->sequence_parallel()) return lora_B;
+    return Tensor();
+  }
   LoRAConfig config;
   Tensor lora_A, lora_B;
 
  private:
+  void Init(int64_t in_global, int64_t a_cols_begin) {
+    auto o = weight.options().requires_grad(false);
+    Tensor full = torch::empty({config.rank, in_global}, o.device(torch::kCPU));
+    init::KaimingUniform(full);
+    lora_A = register_parameter("lora_A", full.slice(1, a_cols_begin, a_cols_begin + in_features()).contiguous().to(weight.device()));
+    lora_B = register_parameter("lora_B", torch::zeros({out_features(), config.rank}, o));
+    weight.set_requires_grad(false);
+    if (bias.defined()) bias.set_requires_grad(false);
+  }
+  Tensor ForwardColumn(const Tensor& x_in, const c10::optional<Tensor>& residual, bool gelu) {
+    Tensor x = x_in;
+    if (column_->sequence_parallel()) x = parallel::GatherFromSPRegion::apply(x);
+    else if (!column_->input_is_parallel() && parallel::TP()) x = parallel::CopyToTPRegion::apply(x);
+    auto b = column_->skip_bias_add() ? c10::nullopt : opt(bias);
+    Tensor y;
+    if (merged_) {
+      y = ops::linear(x, weight, b, c10::nullopt, gelu);
+    } else {
+      y = ops::linear(x, weight, b);
+      y = y + ops::linear(ops::linear(x, lora_A), lora_B).to(y.scalar_type()) * config.Scaling();
+      if (gelu) y = ops::gelu(y);
+    }
+    if (column_->gather_output()) y = parallel::GatherFromTPRegion::apply(y);
+    return residual.has_value() ? y + *residual : y;
+  }
+  Tensor ForwardRow(const Tensor& x_in, const c10::optional<Tensor>& residual, bool gelu) {
+    TORCH_CHECK(!gelu, "a row-parallel linear has no activation epilogue");
+    Tensor x = row_->input_is_parallel() ? x_in : parallel::ScatterToTPRegion::apply(x_in);
+    auto b = row_->skip_bias_add() ? c10::nullopt : opt(bias);
+    const bool reduce = parallel::TP() && row_->reduce_output();
+    auto sum = [&](const Tensor& t) {
+      if (!reduce) return t;
+      return row_->sequence_parallel() ? parallel::ReduceScatterToSPRegion::apply(t) : parallel::ReduceFromTPRegion::apply(t);
+    };
+    Tensor y = sum(ops::linear(x, weight));
+    if (!merged_) y = y + ops::linear(sum(ops::linear(x, lora_A)), lora_B).to(y.scalar_type()) * config.Scaling();
+    if (b.has_value()) y = y + b->to(y.scalar_type());
+    return residual.has_value() ? y + *residual : y;
+  }
   bool merged_ = false;
+  Kind kind_ = Kind::kPlain;
+  std::shared_ptr<parallel::ColumnParallelLinear> column_;
+  std::shared_ptr<parallel::RowParallelLinear> row_;
 };
 
 // A plain Linear that owns copies of the wrapper's tensors' storage (used by MergeAndUnload).
@@ -120,8 +191,13 @@ inline void UnfreezeModel(const std::shared_ptr<Module>& model) { model->set_req
 inline std::shared_ptr<Module> InjectLoRALayers(const std::shared_ptr<Module>& model, const LoRAConfig& config) {
   visit(model, "", [&](const std::shared_ptr<Module>& parent, const std::string& name, const std::string& path,
                        const std::shared_ptr<Module>& child) {
-    if (child->type() != Linear::kType || !config.ShouldApplyLoRA(path)) return;
-    parent->replace_module(name, std::make_shared<LoRALinear>(std::static_pointer_cast<Linear>(child), config));
+    if (!config.ShouldApplyLoRA(path)) return;
+    if (child->type() == Linear::kType)
+      parent->replace_module(name, std::make_shared<LoRALinear>(std::static_pointer_cast<Linear>(child), config));
+    else if (child->type() == "ColumnParallelLinear")
+      parent->replace_module(name, std::make_shared<LoRALinear>(std::static_pointer_cast<parallel::ColumnParallelLinear>(child), config));
+    else if (child->type() == "RowParallelLinear")
+      parent->replace_module(name, std::make_shared<LoRALinear>(std::static_pointer_cast<parallel::RowParallelLinear>(child), config));
   });
   return model;
 }
@@ -133,7 +209,7 @@ inline std::shared_ptr<Module> GetLoRAModel(const std::shared_ptr<Module>& model
 inline std::vector<std::shared_ptr<LoRALinear>> LoRAModules(const std::shared_ptr<Module>& model) {
   std::vector<std::shared_ptr<LoRALinear>> out;
   for (auto& [path, m] : model->NamedModules())
-    if (m->type() == "LoRALinear") out.push_back(std::static_pointer_cast<LoRALinear>(m));
+    if (LoRALinear::IsLoRAType(m->type())) out.push_back(std::static_pointer_cast<LoRALinear>(m));
   return out;
 }
 inline TensorList GetLoRAParameters(const std::shared_ptr<Module>& model) {
@@ -141,6 +217,15 @@ inline TensorList GetLoRAParameters(const std::shared_ptr<Module>& model) {
   for (auto& m : LoRAModules(model)) {
     out.push_back(m->lora_A);
     out.push_back(m->lora_B);
+  }
+  return out;
+}
+// Adapter factors whose gradients are partial sums on every tensor-parallel rank (see LoRALinear).
+inline TensorList PartialGradParameters(const std::shared_ptr<Module>& model) {
+  TensorList out;
+  for (auto& m : LoRAModules(model)) {
+    Tensor t = m->PartialGradFactor();
+    if (t.defined()) out.push_back(t);
   }
   return out;
 }
@@ -160,8 +245,10 @@ inline void UnmergeLoRAWeights(const std::shared_ptr<Module>& model) {
 inline std::shared_ptr<Module> MergeAndUnload(const std::shared_ptr<Module>& model) {
   visit(model, "", [&](const std::shared_ptr<Module>& parent, const std::string& name, const std::string&,
                        const std::shared_ptr<Module>& child) {
-    if (child->type() != "LoRALinear") return;
+    if (!LoRALinear::IsLoRAType(child->type())) return;
     auto l = std::static_pointer_cast<LoRALinear>(child);
+    TORCH_CHECK(l->kind() == LoRALinear::Kind::kPlain, "MergeAndUnload of a tensor-parallel adapter: merge with MergeLoRAWeights "
+                                                      "and keep the wrapper (it carries the base layer's collectives)");
     l->MergeWeights();
     parent->replace_module(name, std::make_shared<UnwrappedLinear>(*l));
   });

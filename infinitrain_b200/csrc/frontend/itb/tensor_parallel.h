@@ -152,6 +152,10 @@ class ColumnParallelLinear : public nn::Linear {
     return residual.has_value() ? y + *residual : y;
   }
   int64_t out_features_global() const { return out_features_global_; }
+  bool gather_output() const { return gather_output_; }
+  bool input_is_parallel() const { return input_is_parallel_; }
+  bool skip_bias_add() const { return skip_bias_add_; }
+  bool sequence_parallel() const { return sequence_parallel_; }
 
  private:
   static int64_t Shard(int64_t n) {
@@ -184,6 +188,10 @@ class RowParallelLinear : public nn::Linear {
     if (add_bias.has_value()) y = y + add_bias->to(y.scalar_type());
     return residual.has_value() ? y + *residual : y;
   }
+  bool reduce_output() const { return reduce_output_; }
+  bool input_is_parallel() const { return input_is_parallel_; }
+  bool skip_bias_add() const { return skip_bias_add_; }
+  bool sequence_parallel() const { return sequence_parallel_; }
 
  private:
   static int64_t Shard(int64_t n) {
@@ -298,9 +306,11 @@ class VocabParallelCrossEntropyLoss : public Module {
 // Sums, over the tensor-parallel group, the gradients of parameters that are replicated on its ranks
 // but see only a slice of the sequence under sequence parallelism (norm weights, position table,
 // row-parallel biases).  Call it after backward and before the optimizer step.
-inline int AllReduceSequenceParallelGrads(const TensorList& replicated) {
+// `always`: the listed gradients are partial with or without sequence parallelism (replicated adapter
+// factors next to a split one).
+inline int AllReduceSequenceParallelGrads(const TensorList& replicated, bool always = false) {
   auto grp = TP();
-  if (!grp || !env().sequence_parallel) return 0;
+  if (!grp || !(env().sequence_parallel || always)) return 0;
   TensorList grads;
   for (const Tensor& p : replicated)
     if (p.grad().defined()) grads.push_back(p.grad());

@@ -165,3 +165,21 @@ def test_profile_flag_writes_per_rank_reports_with_ops_and_collectives(binaries,
             assert name in report, (name, report[:2000])
         first = records.splitlines()[0].split("\t")
         assert first[0] == "Step_1" and first[1] == str(rank) and first[3] == "cpu"
+
+
+@pytest.mark.parametrize("flags", [("--tensor_parallel", "2"), ("--tensor_parallel", "2", "--sequence_parallel"),
+                                   ("--tensor_parallel", "2", "--sequence_parallel", "--zero_stage", "1")],
+                         ids=["tp2", "tp2_sp", "dp2_tp2_sp_zero1"])
+def test_lora_on_tensor_parallel_linears_follows_the_single_rank_adapters(binaries, files, flags):
+    """LoRA around column- and row-parallel linears (A or B split like the base weight, the replicated
+    factor's partial gradients summed over the group): same loss trajectory as LoRA on one rank, whose
+    adapters start from the same draws."""
+    lora = (*LLAMA, "--lora_rank", "4", "--lora_alpha", "8", "--lora_target_modules", "c_attn,c_proj,c_fc,c_fc2",
+            "--learning_rate", "0.02")
+    one, log1 = _train(binaries, files, "llama3", 1, *lora, iters=5)
+    ranks = 4 if "--zero_stage" in flags else 2
+    got, log = _train(binaries, files, "llama3", ranks, *lora, *flags, iters=5)
+    frozen, _ = _train(binaries, files, "llama3", 1, *lora[:-1], "0.0", iters=5)
+    assert max(abs(a - b) for a, b in zip(one, frozen)) > 1e-3, (one, frozen)   # the adapters do move the loss
+    assert max(abs(a - b) for a, b in zip(got, one)) <= 3e-5, list(zip(got, one))
+    assert "LoRA" in log
