@@ -8,6 +8,7 @@
 // Build: g++ -std=c++17 -I infinitrain_b200/csrc/frontend against libtorch (examples/cpp/build.py);
 // add -DITB_WITH_CUDA and link infinitrain_b200/_C.so for the sm_100a kernels.
 #pragma once
+#include "data.h"
 #include "ddp.h"
 #include "distributed.h"
 #include "io.h"

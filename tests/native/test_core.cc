@@ -154,4 +154,45 @@ ITB_TEST_P(Profiler, RecordsOpsOncePerOuterRangeAndReportsPerTag) {
   EXPECT(prof.records().empty());
 }
 
+ITB_TEST(Data, LoadersStackConsecutiveSamplesAndRanksStrideOverBatches) {
+  // 7 samples of (i, 10 i): batch size 2 gives three full batches, the ragged one is dropped
+  auto ds = std::make_shared<itb::data::TensorDataset>(torch::arange(7, torch::kFloat32).view({7, 1}), torch::arange(7, torch::kFloat32) * 10);
+  itb::data::DataLoader loader(ds, 2);
+  EXPECT(loader.num_batches() == 3);
+  std::vector<float> firsts;
+  for (auto it = loader.begin(); it != loader.end(); ++it) {
+    auto [x, y] = *it;
+    EXPECT(x.size(0) == 2 && x.size(1) == 1 && y.size(0) == 2);
+    EXPECT(y[1].item<float>() == 10 * x[1][0].item<float>());
+    firsts.push_back(x[0][0].item<float>());
+  }
+  EXPECT((firsts == std::vector<float>{0, 2, 4}));
+  itb::data::DistributedDataLoader r0(ds, 2, 0, 2), r1(ds, 2, 1, 2);
+  std::vector<size_t> b0, b1;
+  for (auto it = r0.begin(); it < r0.end(); it++) b0.push_back(it.BatchIndex());
+  for (auto it = r1.begin(); it < r1.end(); it++) b1.push_back(it.BatchIndex());
+  EXPECT((b0 == std::vector<size_t>{0, 2}) && (b1 == std::vector<size_t>{1}));
+  EXPECT_THROWS(*loader.end());
+  EXPECT_THROWS(itb::data::DistributedDataLoader(ds, 2, 2, 2));
+}
+
+ITB_TEST(Data, TokenFileSamplesShiftTheTargetByOneToken) {
+  const std::string path = "itb_test_tokens.bin";
+  {
+    std::ofstream f(path, std::ios::binary);
+    int32_t header[256] = {20240520, 1, 11};
+    f.write(reinterpret_cast<const char*>(header), sizeof(header));
+    for (uint16_t t = 0; t < 11; ++t) {
+      uint16_t v = static_cast<uint16_t>(100 + t);
+      f.write(reinterpret_cast<const char*>(&v), 2);
+    }
+  }
+  itb::data::TinyShakespeareDataset ds(path, 4);
+  EXPECT(ds.Size() == 2);                         // (11 - 1) / 4
+  auto [x, y] = ds[1];
+  EXPECT(x[0].item<int64_t>() == 104 && x[3].item<int64_t>() == 107 && y[0].item<int64_t>() == 105 && y[3].item<int64_t>() == 108);
+  EXPECT_THROWS(ds[2]);
+  std::remove(path.c_str());
+}
+
 ITB_TEST_MAIN()
