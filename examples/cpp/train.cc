@@ -6,7 +6,7 @@
 //             --sequence_length 64 --total_batch_size 256 --num_iteration 10 --learning_rate 1e-4
 //             --device cpu|cuda --dtype float32|bfloat16 --optimizer sgd|adam|adamw
 //             [--lora_rank 8 --lora_alpha 16 --lora_target_modules c_attn,c_proj --lora_load_path F --lora_save_path F]
-//             [--save DIR --save_interval N] [--load DIR/checkpoint_step_000004]
+//             [--save DIR --save_interval N --save_optimizer_state --max_checkpoint_keep K] [--load DIR/checkpoint_step_000004]
 //             [--tensor_parallel N --sequence_parallel --pipeline_parallel N --virtual_pipeline_parallel N
 //              --pipeline_schedule 1f1b|gpipe --zero_stage 0|1|2 --no_overlap_grad_reduce]
 //             [--profile]   per-op / per-collective records, written as <family>.report.rank<r> and
@@ -278,12 +278,19 @@ int main(int argc, char** argv) {
     }
     // a rank saves what only it holds: its model-parallel slice, its shard of a ZeRO optimizer state
     const bool saver = own_state ? (env.dp_rank == 0 || zero_stage >= 1) : env.rank == 0;
-    if (save_interval > 0 && (step + 1) % save_interval == 0 && !fl.get("save", "").empty() && saver) {
-      itb::io::TrainerState st;
-      st.global_step = step + 1, st.consumed_batches = consumed, st.last_lr = lr;
-      st.n_layer = cfg.n_layer, st.n_head = cfg.n_head, st.n_kv_head = cfg.n_kv_head, st.n_embd = cfg.n_embd;
-      st.vocab_size = cfg.vocab_size, st.ddp_size = dp, st.tp_size = tp, st.sp_size = env.sp(), st.pp_size = pp;
-      itb::io::SaveCheckpoint(fl.get("save", ""), st, *model, optimizer->StateDict(), own_state ? env.rank : -1);
+    if (save_interval > 0 && (step + 1) % save_interval == 0 && !fl.get("save", "").empty()) {
+      if (saver) {
+        itb::io::TrainerState st;
+        st.global_step = step + 1, st.consumed_batches = consumed, st.last_lr = lr;
+        st.n_layer = cfg.n_layer, st.n_head = cfg.n_head, st.n_kv_head = cfg.n_kv_head, st.n_embd = cfg.n_embd;
+        st.vocab_size = cfg.vocab_size, st.ddp_size = dp, st.tp_size = tp, st.sp_size = env.sp(), st.pp_size = pp;
+        const bool with_optimizer = fl.getb("save_optimizer_state", true);
+        itb::io::SaveCheckpoint(fl.get("save", ""), st, *model,
+                                with_optimizer ? optimizer->StateDict() : std::map<std::string, itb::Tensor>{}, own_state ? env.rank : -1);
+      }
+      // every rank's part of this step is on disk before the oldest step directory goes
+      if (auto world = par::ProcessGroupFactory::Instance().GetDefaultProcessGroup()) world->Barrier();
+      if (env.rank == 0) itb::io::PruneCheckpoints(fl.get("save", ""), fl.geti("max_checkpoint_keep", 0));
     }
   }
   if (profile) {

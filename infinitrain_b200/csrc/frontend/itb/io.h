@@ -3,6 +3,11 @@
 // (example/common/tiny_shakespeare_dataset.cc, src/dataloader.cc), checkpoints
 // (src/checkpoint/checkpoint.cc).
 #pragma once
+#include <dirent.h>
+#include <ftw.h>
+#include <sys/stat.h>
+
+#include <algorithm>
 #include <cstring>
 #include <filesystem>
 #include <fstream>
@@ -264,6 +269,33 @@ inline std::string SaveCheckpoint(const std::string& root, const TrainerState& s
   if (!optimizer_state.empty()) SaveStateDict((dir / "optimizer.ckpt").string(), optimizer_state);
   SaveTrainerState((dir / "trainer_state.json").string(), state);
   return dir.string();
+}
+
+// Keeps the `keep` newest <root>/checkpoint_step_* directories (zero-padded names sort by step) and removes
+// the rest (reference: src/checkpoint/checkpoint_manager.cc:103-118).  Returns how many were removed.
+// Directory listing and recursive removal go through POSIX calls: std::filesystem's iterators are not
+// ABI-stable across the libstdc++ the binary was compiled against and the one libtorch loads.
+inline int PruneCheckpoints(const std::string& root, int64_t keep) {
+  if (keep <= 0) return 0;
+  DIR* d = ::opendir(root.c_str());
+  if (!d) return 0;
+  std::vector<std::string> dirs;
+  while (dirent* e = ::readdir(d)) {
+    const std::string name = e->d_name;
+    if (name.rfind("checkpoint_step_", 0) != 0) continue;
+    struct stat st;
+    if (::stat((root + "/" + name).c_str(), &st) == 0 && S_ISDIR(st.st_mode)) dirs.push_back(root + "/" + name);
+  }
+  ::closedir(d);
+  std::sort(dirs.begin(), dirs.end());
+  int removed = 0;
+  while (static_cast<int64_t>(dirs.size()) > keep) {
+    ::nftw(dirs.front().c_str(), [](const char* path, const struct stat*, int, struct FTW*) { return ::remove(path); }, 16,
+           FTW_DEPTH | FTW_PHYS);
+    dirs.erase(dirs.begin());
+    ++removed;
+  }
+  return removed;
 }
 
 }  // namespace io

@@ -183,3 +183,13 @@ def test_lora_on_tensor_parallel_linears_follows_the_single_rank_adapters(binari
     assert max(abs(a - b) for a, b in zip(one, frozen)) > 1e-3, (one, frozen)   # the adapters do move the loss
     assert max(abs(a - b) for a, b in zip(got, one)) <= 3e-5, list(zip(got, one))
     assert "LoRA" in log
+
+
+def test_checkpoint_rotation_keeps_the_newest_steps(binaries, files, tmp_path):
+    """--max_checkpoint_keep 2 with a checkpoint every step: after three steps the directories of steps 2
+    and 3 are left; --save_optimizer_state=false leaves the optimizer state out.  Two data-parallel ranks:
+    only rank 0 writes, both take part in the barrier before the rotation."""
+    _train(binaries, files, "llama3", 2, *LLAMA, "--save", str(tmp_path), "--save_interval", "1", "--max_checkpoint_keep", "2",
+           "--save_optimizer_state=false", iters=3)
+    assert sorted(p.name for p in tmp_path.iterdir()) == ["checkpoint_step_000002", "checkpoint_step_000003"]
+    assert sorted(p.name for p in (tmp_path / "checkpoint_step_000003").iterdir()) == ["model.ckpt", "trainer_state.json"]
