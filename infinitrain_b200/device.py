@@ -105,8 +105,73 @@ class DeviceGuardImpl:
         return cls._side_streams[key]
 
     @staticmethod
+    def CreateStream(device: Device):
+        return torch.cuda.Stream(device=device.index) if device.IsCUDA() else None
+
+    @staticmethod
+    def CreateStreamWithPriority(device: Device, priority: int):
+        """``priority`` as the CUDA runtime counts: 0 = default, negative = higher."""
+        return torch.cuda.Stream(device=device.index, priority=priority) if device.IsCUDA() else None
+
+    @staticmethod
+    def GetStreamPriorityRange():
+        """(lowest, highest) priority a stream can be created with; the highest is the most negative."""
+        if not torch.cuda.is_available():
+            return 0, 0
+        low, high = torch.cuda.Stream.priority_range()
+        return low, high
+
+    @staticmethod
     def CreateEvent(timing: bool = False):
         return torch.cuda.Event(enable_timing=timing)
+
+    # Events: on a CPU device every call is a no-op that reports success (work has completed when the
+    # call that issued it returns), so code written against this interface also runs in CPU tests.
+    @staticmethod
+    def EventRecord(event, stream=None) -> None:
+        if event is not None:
+            event.record(stream) if stream is not None else event.record()
+
+    @staticmethod
+    def StreamWaitEvent(stream, event) -> None:
+        if stream is not None and event is not None:
+            stream.wait_event(event)
+
+    @staticmethod
+    def EventSynchronize(event) -> bool:
+        if event is not None:
+            event.synchronize()
+        return True
+
+    @staticmethod
+    def EventQuery(event) -> bool:
+        return True if event is None else bool(event.query())
+
+    @staticmethod
+    def EventElapsedTime(start, stop) -> float:
+        """Milliseconds between two recorded timing events (0 on a CPU device)."""
+        return 0.0 if start is None or stop is None else float(start.elapsed_time(stop))
+
+    @staticmethod
+    def SynchronizeStream(stream) -> None:
+        if stream is not None:
+            stream.synchronize()
+
+    @staticmethod
+    def Malloc(device: Device, nbytes: int, stream=None) -> int:
+        """A raw block out of the caching allocator the tensors use (so it shows in the same statistics);
+        returns its address.  With ``stream`` the block may be reused by later work of that stream as soon
+        as it is freed (the reference's MallocAsync)."""
+        if not device.IsCUDA():
+            raise RuntimeError("raw device memory exists on CUDA devices only")
+        return int(torch.cuda.caching_allocator_alloc(nbytes, device.index, stream))
+
+    MallocAsync = Malloc
+
+    @staticmethod
+    def Free(ptr: int) -> None:
+        if ptr:
+            torch.cuda.caching_allocator_delete(ptr)
 
     @staticmethod
     def SynchronizeDevice(device: Device) -> None:

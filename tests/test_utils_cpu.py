@@ -227,3 +227,28 @@ def test_process_group_overview_is_the_reference_text():
     assert "[DP] size=2, num_groups=4\n  - DP 0 (dp=-, tp=0, pp=0): [0, 2]\n  - DP 1 (dp=-, tp=0, pp=1): [4, 6]" in text
     assert "  - PP 3 (dp=1, tp=1, pp=-): [3, 7]\n\n" in text
     g.InitAllEnv(world_size=1, rank=0)
+
+
+def test_device_runtime_surface_is_callable_on_a_cpu_device():
+    """DeviceGuardImpl carries the reference's runtime calls (streams with priorities, events, raw
+    memory, pool statistics); on a CPU device they are no-ops that report completion."""
+    from infinitrain_b200.device import Device, DeviceGuardImpl, GetDeviceGuardImpl
+
+    impl = GetDeviceGuardImpl()
+    cpu = Device.CPU()
+    assert impl is DeviceGuardImpl
+    assert impl.GetStream(cpu) is None and impl.CreateStream(cpu) is None and impl.CreateStreamWithPriority(cpu, -1) is None
+    low, high = impl.GetStreamPriorityRange()
+    assert high <= low
+    impl.EventRecord(None)
+    impl.StreamWaitEvent(None, None)
+    assert impl.EventSynchronize(None) and impl.EventQuery(None) and impl.EventElapsedTime(None, None) == 0.0
+    impl.SynchronizeStream(None)
+    impl.SynchronizeDevice(cpu)
+    impl.ResetMemPoolHighWatermarks(cpu)
+    assert impl.GetMemPoolPeakMB(cpu) == (0.0, 0.0)
+    import pytest
+
+    with pytest.raises(RuntimeError):
+        impl.Malloc(cpu, 64)
+    impl.Free(0)
