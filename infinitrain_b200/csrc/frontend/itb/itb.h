@@ -9,6 +9,7 @@
 // add -DITB_WITH_CUDA and link infinitrain_b200/_C.so for the sm_100a kernels.
 #pragma once
 #include "data.h"
+#include "datatype.h"
 #include "ddp.h"
 #include "distributed.h"
 #include "io.h"

@@ -195,4 +195,26 @@ ITB_TEST(Data, TokenFileSamplesShiftTheTargetByOneToken) {
   std::remove(path.c_str());
 }
 
+ITB_TEST(DataTypes, SizesNamesPromotionAndTorchMapping) {
+  using itb::DataType;
+  const DataType all[] = {DataType::kBOOL, DataType::kUINT8, DataType::kINT8, DataType::kUINT16, DataType::kINT16, DataType::kUINT32,
+                          DataType::kINT32, DataType::kUINT64, DataType::kINT64, DataType::kBFLOAT16, DataType::kFLOAT16,
+                          DataType::kFLOAT32, DataType::kFLOAT64};
+  for (DataType t : all) {
+    EXPECT(itb::FromTorch(itb::ToTorch(t)) == t);
+    EXPECT(itb::DataTypeSize(t) == torch::elementSize(itb::ToTorch(t)));
+    EXPECT(itb::PromoteDataTypes(t, t) == t);
+  }
+  EXPECT(std::string(itb::DataTypeDesc(DataType::kBFLOAT16)) == "bfloat16");
+  EXPECT(itb::PromoteDataTypes(DataType::kFLOAT16, DataType::kBFLOAT16) == DataType::kFLOAT32);
+  EXPECT(itb::PromoteDataTypes(DataType::kINT64, DataType::kBFLOAT16) == DataType::kBFLOAT16);
+  EXPECT(itb::PromoteDataTypes(DataType::kINT32, DataType::kINT64) == DataType::kINT64);
+  EXPECT(itb::PromoteDataTypes(DataType::kFLOAT32, DataType::kFLOAT64) == DataType::kFLOAT64);
+  itb::Scalar a(2.75), b(true), c(int64_t(-3)), d(uint64_t(7));
+  EXPECT(a.To<int>() == 2 && b.To<double>() == 1.0 && c.To<float>() == -3.0f && d.kind() == itb::Scalar::Kind::kUInt64);
+  Tensor t = torch::zeros({2});
+  t.fill_(a.ToTorch());
+  EXPECT(t[1].item<float>() == 2.75f);
+}
+
 ITB_TEST_MAIN()
