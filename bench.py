@@ -310,6 +310,8 @@ def reference_arm(args):
             try:
                 out["secondary"] = _reference_measure(args, "llama3-8b", args.gpus, 1, 1, 0, args.zero, 1, 2048,
                                                       weights=weights, time_limit=left)
+            except Exception as e:  # noqa: BLE001  (the first measurement is printed whatever happens to the second)
+                out["secondary"] = {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}
             finally:
                 weights.remove()
     print(json.dumps(out), flush=True)
