@@ -825,7 +825,10 @@ def main():
 
     # ---- the second half of the headline metric, in fresh processes (this one lets go of the GPUs first)
     _destroy_process_group(torch, exit_on_timeout=False)
-    sec = _run_secondary(args, rank)
+    try:
+        sec = _run_secondary(args, rank)
+    except Exception as e:  # noqa: BLE001  (the first measurement is printed whatever happens to the second)
+        sec = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     if rank == 0:
         out["secondary"] = sec
         print(json.dumps(out), flush=True)
