@@ -130,6 +130,27 @@ struct GlobalEnv {
 
 inline GlobalEnv& env() { return GlobalEnv::Instance(); }
 
+// Who this worker is among the job's workers (reference: include/nn/parallel/rank.h).  The reference
+// counts processes on the node and threads inside a process (one thread per GPU); here a worker is a
+// process, so thread_rank is 0 and thread_size 1 unless a program sets them for threads of its own.
+class Rank {
+ public:
+  Rank(int process_rank, int thread_rank, int process_size, int thread_size)
+      : process_rank_(process_rank), thread_rank_(thread_rank), process_size_(process_size), thread_size_(thread_size) {}
+  static Rank Current() { return Rank(env().rank, 0, env().world, 1); }
+  int process_rank() const { return process_rank_; }
+  int thread_rank() const { return thread_rank_; }
+  int process_size() const { return process_size_; }
+  int thread_size() const { return thread_size_; }
+  int GlobalRank() const { return process_rank_ * thread_size_ + thread_rank_; }
+  bool IsParallel() const { return process_size_ * thread_size_ > 1; }
+  bool IsMainRank() const { return GlobalRank() == 0; }
+  bool IsLastRank() const { return GlobalRank() == process_size_ * thread_size_ - 1; }
+
+ private:
+  int process_rank_, thread_rank_, process_size_, thread_size_;
+};
+
 // Which layers a pipeline stage holds (reference: pipeline_parallel.cc:42-77).  The model is cut into
 // pp * vpp chunks of consecutive layers; the first (layers % chunks) chunks get one layer more; stage s
 // owns the chunks local * pp + s, local = 0 .. vpp - 1 (round robin, so that consecutive chunks sit on

@@ -107,6 +107,12 @@ ITB_TEST(Layout3D, TensorParallelRanksAreAdjacentThenDataThenPipeline) {
   EXPECT(e.ProcessGroupOverview().find("TP3 (dp=1, tp=-, pp=1): [6, 7]") != std::string::npos);
 }
 
+ITB_TEST(Layout3D, RankCountsProcessesAndThreads) {
+  par::Rank r(2, 1, 4, 2);                       // process 2 of 4, thread 1 of 2
+  EXPECT(r.GlobalRank() == 5 && r.IsParallel() && !r.IsMainRank() && !r.IsLastRank());
+  EXPECT(par::Rank(3, 1, 4, 2).IsLastRank() && par::Rank(0, 0, 1, 1).IsMainRank() && !par::Rank(0, 0, 1, 1).IsParallel());
+}
+
 ITB_TEST(StagePartition, RoundRobinChunksAndRemainderToTheFirstChunks) {
   auto s0 = par::GetStageInfo(10, 2, 0, 2), s1 = par::GetStageInfo(10, 2, 1, 2);   // 4 chunks: 3 3 2 2
   EXPECT((s0.layer_ranges_per_chunk == std::vector<std::pair<int, int>>{{0, 3}, {6, 8}}));
