@@ -193,3 +193,35 @@ def test_checkpoint_rotation_keeps_the_newest_steps(binaries, files, tmp_path):
            "--save_optimizer_state=false", iters=3)
     assert sorted(p.name for p in tmp_path.iterdir()) == ["checkpoint_step_000002", "checkpoint_step_000003"]
     assert sorted(p.name for p in (tmp_path / "checkpoint_step_000003").iterdir()) == ["model.ckpt", "trainer_state.json"]
+
+
+def test_gpt2_padded_vocabulary_under_tensor_parallelism(binaries, tmp_path):
+    """An llm.c GPT-2 file whose vocabulary (250) is padded to 256 rows: one rank uses the 250 real rows,
+    two tensor-parallel ranks split the 256 padded rows and must keep the padding out of the softmax."""
+    from infinitrain_b200.data import write_token_file
+    from infinitrain_b200.models import llmc
+    from infinitrain_b200.nn.transformer import TransformerConfig, TransformerModel
+    from infinitrain_b200.parallel import global_env as genv
+
+    genv.InitAllEnv(world_size=1, rank=0)
+    g = torch.Generator().manual_seed(3)
+    write_token_file(str(tmp_path / "tokens16.bin"), torch.randint(0, 250, (2 * 64 * 40 + 1,), generator=g).tolist())
+    torch.manual_seed(7)
+    cfg = TransformerConfig.GPT2(n_layer=2, n_embd=96, n_head=12, n_kv_head=12, vocab_size=250, original_vocab_size=250, block_size=64)
+    m = TransformerModel(cfg)
+    with torch.no_grad():
+        for p in m.parameters():
+            p.normal_(0, 0.1) if p.dim() > 1 else p.add_(torch.randn_like(p) * 0.1)
+    llmc.write_gpt2_llmc(str(tmp_path / "gpt2.bin"), cfg, llmc.full_state_dict(m), padded_vocab_size=256)
+    one, _ = _train(binaries, tmp_path, "gpt2", 1, *GPT2)
+    two, _ = _train(binaries, tmp_path, "gpt2", 2, *GPT2, "--tensor_parallel", "2", "--sequence_parallel")
+    assert max(abs(a - b) for a, b in zip(one, two)) <= 2e-5, list(zip(one, two))
+
+
+def test_gpt2_tensor_and_sequence_parallel_inside_pipeline_stages(binaries, files):
+    """GPT-2 (learned positions, biases, LayerNorm) on TP2+SP x PP2 against PP2 alone: both run the untied
+    two-stage model, so the trajectories must agree; the position table and the row-parallel biases are
+    the parameters whose sequence-parallel gradient sum this exercises."""
+    pp, _ = _train(binaries, files, "gpt2", 2, *GPT2, "--pipeline_parallel", "2")
+    both, _ = _train(binaries, files, "gpt2", 4, *GPT2, "--pipeline_parallel", "2", "--tensor_parallel", "2", "--sequence_parallel")
+    assert max(abs(a - b) for a, b in zip(pp, both)) <= 2e-5, list(zip(pp, both))
