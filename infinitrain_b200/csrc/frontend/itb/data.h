@@ -10,7 +10,10 @@
 // background thread; these classes are for programs written against the reference's iteration
 // protocol and for datasets that are not token files.
 #pragma once
+#include <cstdint>
+#include <fstream>
 #include <memory>
+#include <string>
 #include <utility>
 
 #include "../../runtime/token_io.h"
@@ -66,6 +69,54 @@ class TensorDataset : public Dataset {
 
  private:
   Tensor x_, y_;
+};
+
+// An IDX file of unsigned bytes (the MNIST distribution format): big-endian magic 0x0000 08 <ndim>, then one
+// big-endian uint32 per dimension, then the bytes (reference: example/mnist/dataset.cc:45-80).
+inline Tensor ReadIdxFile(const std::string& path) {
+  std::ifstream f(path, std::ios::binary);
+  TORCH_CHECK(f.good(), "cannot open IDX file ", path);
+  unsigned char head[4];
+  f.read(reinterpret_cast<char*>(head), 4);
+  TORCH_CHECK(f.gcount() == 4 && head[0] == 0 && head[1] == 0, "not an IDX file: ", path);
+  TORCH_CHECK(head[2] == 0x08, "IDX file ", path, " does not hold unsigned bytes (type code ", int(head[2]), ")");
+  const int ndim = head[3];
+  TORCH_CHECK(ndim >= 1 && ndim <= 8, "IDX file ", path, " has ", ndim, " dimensions");
+  std::vector<int64_t> dims;
+  int64_t count = 1;
+  for (int i = 0; i < ndim; ++i) {
+    unsigned char b[4];
+    f.read(reinterpret_cast<char*>(b), 4);
+    TORCH_CHECK(f.gcount() == 4, "IDX file ", path, " ends inside its header");
+    dims.push_back((int64_t(b[0]) << 24) | (int64_t(b[1]) << 16) | (int64_t(b[2]) << 8) | int64_t(b[3]));
+    count *= dims.back();
+  }
+  Tensor out = torch::empty(dims, torch::kUInt8);
+  f.read(reinterpret_cast<char*>(out.data_ptr<uint8_t>()), count);
+  TORCH_CHECK(f.gcount() == count, "IDX file ", path, " holds ", f.gcount(), " of the ", count, " bytes its header announces");
+  return out;
+}
+
+// MNIST out of `<dir>/{train,t10k}-images-idx3-ubyte` and `-labels-idx1-ubyte`: sample i is the image as
+// fp32 [28, 28] scaled to [0, 1] and its label as one uint8 (reference: example/mnist/dataset.cc:82-125).
+class MNISTDataset : public Dataset {
+ public:
+  MNISTDataset(const std::string& dir, bool train) {
+    const std::string prefix = dir + "/" + (train ? "train" : "t10k");
+    Tensor images = ReadIdxFile(prefix + "-images-idx3-ubyte");
+    labels_ = ReadIdxFile(prefix + "-labels-idx1-ubyte");
+    TORCH_CHECK(images.dim() == 3 && labels_.dim() == 1 && images.size(0) == labels_.size(0),
+                "MNIST files under ", dir, " disagree: images ", images.sizes(), ", labels ", labels_.sizes());
+    images_ = images.to(torch::kFloat32) / 255.0f;
+  }
+  std::pair<Tensor, Tensor> operator[](size_t idx) const override {
+    TORCH_CHECK(idx < Size(), "sample ", idx, " of ", Size());
+    return {images_[static_cast<int64_t>(idx)], labels_[static_cast<int64_t>(idx)]};
+  }
+  size_t Size() const override { return static_cast<size_t>(labels_.size(0)); }
+
+ private:
+  Tensor images_, labels_;
 };
 
 class DataLoaderIterator {

@@ -9,9 +9,11 @@
 // add -DITB_WITH_CUDA and link infinitrain_b200/_C.so for the sm_100a kernels.
 #pragma once
 #include "data.h"
+#include "data_parallel.h"
 #include "datatype.h"
 #include "ddp.h"
 #include "distributed.h"
+#include "functional.h"
 #include "io.h"
 #include "layers.h"
 #include "lora.h"

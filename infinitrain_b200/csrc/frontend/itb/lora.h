@@ -178,6 +178,28 @@ inline void visit(const std::shared_ptr<Module>& m, const std::string& path,
   }
 }
 
+// Puts `replacement` where the module at the dotted `path` sits (reference: lora_utils.cc ReplaceModuleByPath).
+inline void ReplaceModuleByPath(const std::shared_ptr<Module>& model, const std::string& path, std::shared_ptr<Module> replacement) {
+  TORCH_CHECK(!path.empty(), "ReplaceModuleByPath: the path names a child, the root cannot be replaced");
+  std::shared_ptr<Module> parent = model;
+  size_t begin = 0;
+  while (true) {
+    size_t dot = path.find('.', begin);
+    std::string name = path.substr(begin, dot == std::string::npos ? std::string::npos : dot - begin);
+    TORCH_CHECK(parent->has_module(name), "ReplaceModuleByPath: no module '", name, "' on the way to '", path, "'");
+    if (dot == std::string::npos) {
+      parent->replace_module(name, std::move(replacement));
+      return;
+    }
+    parent = parent->mutable_module(name);
+    begin = dot + 1;
+  }
+}
+
+inline bool IsLoRAParameterName(const std::string& name) {
+  return name.size() >= 6 && (name.compare(name.size() - 6, 6, "lora_A") == 0 || name.compare(name.size() - 6, 6, "lora_B") == 0);
+}
+
 inline void FreezeBaseModel(const std::shared_ptr<Module>& model) {
   for (auto& [name, p] : model->NamedParameters()) {
     bool is_lora = name.size() >= 6 && (name.compare(name.size() - 6, 6, "lora_A") == 0 || name.compare(name.size() - 6, 6, "lora_B") == 0);
@@ -218,6 +240,14 @@ inline TensorList GetLoRAParameters(const std::shared_ptr<Module>& model) {
     out.push_back(m->lora_A);
     out.push_back(m->lora_B);
   }
+  return out;
+}
+// Every parameter that is not an adapter factor, each tensor once.
+inline TensorList GetBaseParameters(const std::shared_ptr<Module>& model) {
+  TensorList out;
+  std::unordered_set<const void*> seen;
+  for (auto& [name, p] : model->NamedParameters())
+    if (!IsLoRAParameterName(name) && seen.insert(p.unsafeGetTensorImpl()).second) out.push_back(p);
   return out;
 }
 // Adapter factors whose gradients are partial sums on every tensor-parallel rank (see LoRALinear).
@@ -272,6 +302,23 @@ inline std::map<std::string, Tensor> LoRAStateDict(const std::shared_ptr<Module>
     if (k.size() >= 6 && (k.compare(k.size() - 6, 6, "lora_A") == 0 || k.compare(k.size() - 6, 6, "lora_B") == 0)) out[k] = v;
   }
   return out;
+}
+
+// Copies the adapter tensors of `state_dict` into the model; names the model lacks are reported and skipped,
+// a shape mismatch is an error (reference: lora_utils.cc LoadLoRAStateDict).
+inline void LoadLoRAStateDict(const std::shared_ptr<Module>& model, const std::map<std::string, Tensor>& state_dict) {
+  auto own = LoRAStateDict(model);
+  torch::NoGradGuard g;
+  for (auto& [name, t] : state_dict) {
+    auto it = own.find(name);
+    if (it == own.end()) {
+      std::fprintf(stderr, "[W] LoRA parameter not found in model: %s\n", name.c_str());
+      continue;
+    }
+    TORCH_CHECK(it->second.sizes() == t.sizes(), "LoRA parameter ", name, ": the model holds ", it->second.sizes(), ", the state dict ",
+                t.sizes());
+    it->second.copy_(t);
+  }
 }
 
 constexpr uint32_t kLoRAMagic = 0x4C4F5241;

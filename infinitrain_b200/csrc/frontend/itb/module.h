@@ -10,6 +10,7 @@
 #include <functional>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <unordered_set>
 #include <utility>
@@ -31,6 +32,73 @@ class HookHandle {
 
  private:
   std::function<void()> remove_;
+};
+
+class Module;
+
+// Process-wide module hooks: they run for every module's call, around the module's own hooks
+// (reference: include/utils/global_module_hook_registry.h:19-52 and src/nn/modules/module.cc:198-266;
+// the precision checker and the profiler hang their per-module work here).  Registration and the calls
+// take a snapshot under a mutex, so ranks that run as threads of one process may register and call
+// concurrently.
+class GlobalModuleHookRegistry {
+ public:
+  using ModuleForwardPreHook = std::function<void(Module*, const TensorList&)>;
+  using ModuleForwardHook = std::function<void(Module*, const TensorList&, const TensorList&)>;
+  // hook(module, gradients w.r.t. the outputs, gradients w.r.t. the inputs); the second list holds the
+  // entries that exist when the hook runs (libtorch shows a module's backward one output at a time)
+  using ModuleFullBackwardHook = std::function<void(Module*, const TensorList&, const TensorList&)>;
+
+  static GlobalModuleHookRegistry& Instance() {
+    static GlobalModuleHookRegistry r;
+    return r;
+  }
+  std::shared_ptr<HookHandle> RegisterModuleForwardPreHook(ModuleForwardPreHook h) { return add(&pre_, std::move(h)); }
+  std::shared_ptr<HookHandle> RegisterModuleForwardHook(ModuleForwardHook h) { return add(&post_, std::move(h)); }
+  std::shared_ptr<HookHandle> RegisterModuleFullBackwardHook(ModuleFullBackwardHook h) { return add(&bwd_, std::move(h)); }
+
+  void CallModuleForwardPreHooks(Module* m, const TensorList& in) {
+    for (auto& h : snapshot(pre_)) h(m, in);
+  }
+  void CallModuleForwardHooks(Module* m, const TensorList& in, const TensorList& out) {
+    for (auto& h : snapshot(post_)) h(m, in, out);
+  }
+  void CallModuleFullBackwardHooks(Module* m, const TensorList& grad_outputs, const TensorList& grad_inputs) {
+    for (auto& h : snapshot(bwd_)) h(m, grad_outputs, grad_inputs);
+  }
+  bool HasModuleBackwardHooks() const {
+    std::lock_guard<std::mutex> lock(mu_);
+    return !bwd_.empty();
+  }
+  bool empty() const {
+    std::lock_guard<std::mutex> lock(mu_);
+    return pre_.empty() && post_.empty() && bwd_.empty();
+  }
+
+ private:
+  template <class H>
+  std::shared_ptr<HookHandle> add(std::map<int, H>* where, H h) {
+    std::lock_guard<std::mutex> lock(mu_);
+    int id = next_++;
+    (*where)[id] = std::move(h);
+    return std::make_shared<HookHandle>([this, where, id] {
+      std::lock_guard<std::mutex> l(mu_);
+      where->erase(id);
+    });
+  }
+  template <class H>
+  std::vector<H> snapshot(const std::map<int, H>& from) const {
+    std::lock_guard<std::mutex> lock(mu_);
+    std::vector<H> out;
+    out.reserve(from.size());
+    for (auto& [id, h] : from) out.push_back(h);
+    return out;
+  }
+  mutable std::mutex mu_;
+  std::map<int, ModuleForwardPreHook> pre_;
+  std::map<int, ModuleForwardHook> post_;
+  std::map<int, ModuleFullBackwardHook> bwd_;
+  int next_ = 0;
 };
 
 class Module : public std::enable_shared_from_this<Module> {
@@ -114,17 +182,33 @@ class Module : public std::enable_shared_from_this<Module> {
   virtual TensorList Forward(const TensorList& inputs) {
     TORCH_CHECK(false, "Forward is not implemented for module type ", type_);
   }
+  // Order of a call (the reference's, module.cc:198-266): global pre-hooks, the module's pre-hooks,
+  // Forward, the module's post-hooks, global post-hooks; backward hooks are attached to the outputs.
   TensorList operator()(const TensorList& inputs) {
+    auto& global = GlobalModuleHookRegistry::Instance();
+    const bool any_global = !global.empty();
+    if (any_global) global.CallModuleForwardPreHooks(this, inputs);
     for (auto& [id, h] : pre_hooks_) h(this, inputs);
     TensorList outputs = Forward(inputs);
     for (auto& [id, h] : post_hooks_) h(this, inputs, outputs);
-    if (!backward_hooks_.empty()) {
-      // the gradient that reaches output i during backward is shown to the hooks registered now
+    if (any_global) global.CallModuleForwardHooks(this, inputs, outputs);
+    const bool global_bwd = any_global && global.HasModuleBackwardHooks();
+    if (!backward_hooks_.empty() || !backward_pre_hooks_.empty() || global_bwd) {
+      // the gradient that reaches output i during backward is shown to the hooks registered now:
+      // pre-hooks first, then the module's backward hooks, then the process-wide ones
       for (size_t i = 0; i < outputs.size(); ++i) {
         if (!outputs[i].defined() || !outputs[i].requires_grad()) continue;
+        auto pre = backward_pre_hooks_;
         auto hooks = backward_hooks_;
-        outputs[i].register_hook([this, hooks, i](const Tensor& grad) {
+        const size_t n_out = outputs.size();
+        outputs[i].register_hook([this, pre, hooks, i, n_out, global_bwd](const Tensor& grad) {
+          for (auto& [id, h] : pre) h(this, i, grad);
           for (auto& [id, h] : hooks) h(this, i, grad);
+          if (global_bwd) {
+            TensorList grad_outputs(n_out);
+            grad_outputs[i] = grad;
+            GlobalModuleHookRegistry::Instance().CallModuleFullBackwardHooks(this, grad_outputs, {});
+          }
         });
       }
     }
@@ -173,6 +257,14 @@ class Module : public std::enable_shared_from_this<Module> {
     int id = next_hook_++;
     backward_hooks_[id] = std::move(hook);
     return std::make_shared<HookHandle>([this, id] { backward_hooks_.erase(id); });
+  }
+
+  // Runs before the module's backward hooks, on the same gradient (reference:
+  // Module::RegisterBackwardPreHook, module.cc:321-324).
+  std::shared_ptr<HookHandle> RegisterBackwardPreHook(BackwardHook hook) {
+    int id = next_hook_++;
+    backward_pre_hooks_[id] = std::move(hook);
+    return std::make_shared<HookHandle>([this, id] { backward_pre_hooks_.erase(id); });
   }
 
   void set_requires_grad(bool on) {
@@ -226,7 +318,7 @@ class Module : public std::enable_shared_from_this<Module> {
   std::vector<std::string> param_order_, module_order_;   // registration order
   std::map<int, PreHook> pre_hooks_;
   std::map<int, PostHook> post_hooks_;
-  std::map<int, std::function<void(Module*, size_t, const Tensor&)>> backward_hooks_;
+  std::map<int, std::function<void(Module*, size_t, const Tensor&)>> backward_hooks_, backward_pre_hooks_;
   int next_hook_ = 0;
 };
 

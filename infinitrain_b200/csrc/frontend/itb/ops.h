@@ -193,8 +193,11 @@ inline Tensor embedding(const Tensor& idx, const Tensor& wte, const c10::optiona
 }
 
 // Mean cross-entropy over all rows, statistics in fp32.
-inline Tensor cross_entropy(const Tensor& logits, const Tensor& target) {
+// Mean over rows of -log softmax(logits)[target]; targets are class indices as int64 or as uint8 (the
+// reference's loss takes both, src/kernels/cpu/cross_entropy.cc).
+inline Tensor cross_entropy(const Tensor& logits, const Tensor& target_in) {
   ITB_PROFILE("cross_entropy", logits);
+  const Tensor target = target_in.scalar_type() == torch::kLong ? target_in : target_in.to(torch::kLong);
 #ifdef ITB_WITH_CUDA
   if (logits.is_cuda() && (logits.scalar_type() == torch::kFloat32 || logits.scalar_type() == torch::kBFloat16))
     return fused::cross_entropy(logits, target);

@@ -15,11 +15,14 @@
 #pragma once
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <stdexcept>
 #include <string>
 #include <vector>
+
+#include <unistd.h>
 
 namespace itbtest {
 
@@ -35,6 +38,16 @@ struct Failure : std::exception {
   explicit Failure(std::string m) : msg(std::move(m)) {}
   const char* what() const noexcept override { return msg.c_str(); }
 };
+
+// A fresh directory under $TMPDIR (or /tmp) for the files of one case; it is left for the system to clean.
+inline std::string temp_dir(const std::string& tag) {
+  const char* base = std::getenv("TMPDIR");
+  std::string pattern = std::string(base && *base ? base : "/tmp") + "/itb_" + tag + "_XXXXXX";
+  std::vector<char> buf(pattern.begin(), pattern.end());
+  buf.push_back('\0');
+  if (!mkdtemp(buf.data())) throw std::runtime_error("cannot create a temporary directory from " + pattern);
+  return std::string(buf.data());
+}
 
 struct Case {
   std::string suite, name;

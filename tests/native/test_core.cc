@@ -217,4 +217,209 @@ ITB_TEST(DataTypes, SizesNamesPromotionAndTorchMapping) {
   EXPECT(t[1].item<float>() == 2.75f);
 }
 
+// ---- process-wide module hooks, backward pre-hooks
+ITB_TEST(Hooks, GlobalRegistryRunsAroundTheModulesOwnHooksAndHandlesRemoveThem) {
+  using namespace itb::nn;
+  auto net = std::make_shared<Sequential>(std::vector<std::shared_ptr<itb::Module>>{
+      std::make_shared<Linear>(4, 3), std::make_shared<Sigmoid>(), std::make_shared<Linear>(3, 2)});
+  std::vector<std::string> order;
+  auto& reg = itb::GlobalModuleHookRegistry::Instance();
+  auto h1 = reg.RegisterModuleForwardPreHook([&](itb::Module* m, const itb::TensorList&) { order.push_back("gpre:" + m->type()); });
+  auto h2 = reg.RegisterModuleForwardHook(
+      [&](itb::Module* m, const itb::TensorList&, const itb::TensorList& out) { order.push_back("gpost:" + m->type() + ":" + std::to_string(out.size())); });
+  int backward_calls = 0;
+  auto h3 = reg.RegisterModuleFullBackwardHook([&](itb::Module*, const itb::TensorList& grad_outputs, const itb::TensorList&) {
+    EXPECT(grad_outputs.size() == 1 && grad_outputs[0].defined());
+    ++backward_calls;
+  });
+  auto local_pre = net->RegisterForwardPreHook([&](itb::Module*, const itb::TensorList&) { order.push_back("pre"); });
+  auto local_post = net->RegisterForwardPostHook([&](itb::Module*, const itb::TensorList&, const itb::TensorList&) { order.push_back("post"); });
+  std::vector<std::string> bwd_order;
+  auto bpre = net->RegisterBackwardPreHook([&](itb::Module*, size_t, const Tensor&) { bwd_order.push_back("bpre"); });
+  auto bpost = net->RegisterBackwardPostHook([&](itb::Module*, size_t, const Tensor&) { bwd_order.push_back("bpost"); });
+  EXPECT(reg.HasModuleBackwardHooks());
+
+  Tensor x = torch::randn({5, 4});
+  Tensor y = (*net)(x);
+  // the Sequential itself, then its three children; the module's own hooks sit inside the global ones
+  EXPECT(order.size() == 2 + 2 + 3 * 2);
+  EXPECT(order[0] == "gpre:Sequential" && order[1] == "pre");
+  EXPECT(order[2] == "gpre:Linear" && order[3] == "gpost:Linear:1");
+  EXPECT(order[order.size() - 2] == "post" && order.back() == "gpost:Sequential:1");
+  y.sum().backward();
+  EXPECT(backward_calls == 4);               // every module whose output needed a gradient
+  EXPECT(bwd_order.size() == 2 && bwd_order[0] == "bpre" && bwd_order[1] == "bpost");
+
+  h1->Remove(), h2->Remove(), h3->Remove();
+  EXPECT(reg.empty() && !reg.HasModuleBackwardHooks());
+  order.clear();
+  backward_calls = 0;
+  (*net)(x).sum().backward();
+  EXPECT(order.size() == 2 && order[0] == "pre" && order[1] == "post" && backward_calls == 0);
+}
+
+// ---- nn::function
+ITB_TEST_P(Functional, ReferenceNamesAndTheReferencesResultTypes) {
+  namespace F = itb::nn::function;
+  auto opt = torch::dtype(torch::kFloat32).device(device());
+  Tensor a = torch::arange(12, opt).reshape({3, 4}) - 5.0f;
+  EXPECT(torch::equal(F::Tril(a), a.tril()) && torch::equal(F::Triu(a, 1), a.triu(1)));
+  EXPECT(F::Ones({2, 3}).sum().item<float>() == 6.0f);
+  EXPECT(torch::allclose(F::Pow(2.0f, a), torch::pow(2.0, a)) && torch::allclose(F::Pow(a, 2.0f), a * a));
+  EXPECT(torch::allclose(F::Softmax(a, -1).sum(-1), torch::ones({3}, opt)));
+  EXPECT(torch::equal(F::Slice(a, {1, 0}, {3, 4}, {1, 2}), a.slice(0, 1, 3).slice(1, 0, 4, 2)));
+  EXPECT_THROWS(F::Slice(a, {0}, {1}, {1}));
+  EXPECT(F::Stack({a, a}, 0).sizes() == torch::IntArrayRef({2, 3, 4}) && F::Concat({a, a}, 1).sizes() == torch::IntArrayRef({3, 8}));
+  EXPECT(torch::equal(F::Max(a, 1), std::get<0>(a.max(1))) && torch::equal(F::Mean(a, 0, true), a.mean(0, true)));
+  // comparisons: 0 / 1 in the input's dtype, also for a half-precision input
+  Tensor lt = F::Lt(a, 0.0f);
+  EXPECT(lt.scalar_type() == torch::kFloat32 && lt.sum().item<float>() == 5.0f);
+  Tensor h = a.to(torch::kBFloat16);
+  EXPECT(F::Ge(h, h).scalar_type() == torch::kBFloat16 && F::Equals(h, h).to(torch::kFloat32).sum().item<float>() == 12.0f);
+  EXPECT(torch::equal(F::And(F::Gt(a, -2.0f), F::Le(a, 2.0f)), ((a > -2) & (a <= 2)).to(torch::kFloat32)));
+  EXPECT(torch::equal(F::Or(F::Lt(a, -4.0f), F::Gt(a, 5.0f)), ((a < -4) | (a > 5)).to(torch::kFloat32)));
+  // masks aligned to the trailing or to the leading dimensions
+  Tensor t3 = torch::ones({2, 3, 4}, opt);
+  Tensor tail = torch::zeros({3, 4}, opt);
+  tail[0][0] = 1;
+  EXPECT(F::Mask(t3, tail, -1.0f).sum().item<float>() == 24.0f - 2 * 2.0f);
+  Tensor lead = torch::zeros({2}, opt);
+  lead[1] = 1;
+  EXPECT(F::Mask(t3, lead, 0.0f).sum().item<float>() == 12.0f);
+  EXPECT_THROWS(F::Mask(t3, torch::zeros({5}, opt), 0.0f));
+  // top-k scatter
+  Tensor vals = torch::tensor({{1.0f, 2.0f}, {3.0f, 4.0f}}, opt);
+  Tensor idx = torch::tensor({{0, 3}, {2, 1}}, torch::dtype(torch::kLong).device(device()));
+  Tensor sc = F::Scatter(vals, idx, {2, 4});
+  EXPECT(torch::equal(sc, torch::tensor({{1.0f, 0.0f, 0.0f, 2.0f}, {0.0f, 4.0f, 3.0f, 0.0f}}, opt)));
+  EXPECT(torch::equal(F::Gather(sc, 1, idx), vals));
+}
+
+// ---- single-process DataParallel and its helpers
+namespace {
+std::shared_ptr<itb::Module> TinyNet() {
+  using namespace itb::nn;
+  return std::make_shared<Sequential>(std::vector<std::shared_ptr<itb::Module>>{
+      std::make_shared<Linear>(6, 5), std::make_shared<Sigmoid>(), std::make_shared<Linear>(5, 3)});
+}
+}  // namespace
+
+ITB_TEST(DataParallel, ScatterGatherAndBroadcastHelpers) {
+  namespace pf = itb::parallel::function;
+  std::vector<torch::Device> cpus(3, torch::Device(torch::kCPU));
+  Tensor x = torch::arange(14, torch::kFloat32).reshape({7, 2}).set_requires_grad(true);
+  auto parts = pf::Scatter({x}, cpus, 0);
+  EXPECT(parts.size() == 3 && parts[0][0].size(0) == 3 && parts[2][0].size(0) == 1);
+  auto two = pf::Scatter({torch::zeros({2, 2})}, cpus, 0);
+  EXPECT(two.size() == 2);                                   // fewer chunks than devices
+  Tensor back = pf::Gather(parts, cpus[0], 0)[0];
+  EXPECT(torch::equal(back, x));
+  (back * 2).sum().backward();
+  EXPECT(torch::equal(x.grad(), torch::full({7, 2}, 2.0f)));  // the split and the join are differentiable
+  auto copies = pf::BroadcastCoalescedReshape({x, back}, cpus);
+  EXPECT(copies.size() == 3 && copies[1].size() == 2 && torch::equal(copies[2][0], x));
+  EXPECT(copies[1][0].data_ptr() != x.data_ptr() && !copies[1][0].requires_grad());
+  auto net = TinyNet();
+  auto reps = pf::Replicate(net, TinyNet, cpus);
+  EXPECT(reps.size() == 3 && reps[0] == net && reps[1] != net);
+  auto a = net->StateDict(), b = reps[2]->StateDict();
+  for (auto& [k, v] : a) EXPECT(torch::equal(v, b.at(k)) && v.data_ptr() != b.at(k).data_ptr());
+}
+
+ITB_TEST(DataParallel, ReplicasGiveTheOneModuleGradientsAndFollowItsUpdates) {
+  itb::nn::ManualSeed(7);
+  auto single = TinyNet();
+  auto wrapped_inner = TinyNet();
+  wrapped_inner->LoadStateDict(single->StateDict());
+  std::vector<torch::Device> cpus(3, torch::Device(torch::kCPU));
+  auto dp = std::make_shared<itb::parallel::DataParallel>(wrapped_inner, TinyNet, cpus);
+  EXPECT(dp->Parameters().size() == single->Parameters().size());   // the replicas are not parameters of the wrapper
+  itb::optim::SGD opt_single(single->Parameters(), 0.1), opt_dp(dp->Parameters(), 0.1);
+  Tensor x = torch::randn({8, 6}), y = torch::randint(0, 3, {8});
+  for (int step = 0; step < 3; ++step) {
+    opt_single.ZeroGrad(), opt_dp.ZeroGrad();
+    Tensor l1 = itb::ops::cross_entropy((*single)(x), y);
+    Tensor l2 = itb::ops::cross_entropy((*dp)(x), y);
+    EXPECT(std::fabs(l1.item<float>() - l2.item<float>()) < 1e-6f);
+    l1.backward(), l2.backward();
+    auto g1 = single->Parameters(), g2 = dp->Parameters();
+    for (size_t i = 0; i < g1.size(); ++i) EXPECT(torch::allclose(g1[i].grad(), g2[i].grad(), 1e-5, 1e-6));
+    opt_single.Step(), opt_dp.Step();
+  }
+  EXPECT(dp->replica_forwards() == 9);
+  // a batch of one runs on the source module alone; without grad mode nothing is recorded
+  EXPECT((*dp)(x.slice(0, 0, 1)).sizes() == torch::IntArrayRef({1, 3}) && dp->replica_forwards() == 9);
+  {
+    torch::NoGradGuard g;
+    EXPECT(!(*dp)(x).requires_grad());
+  }
+  // an error inside one replica's thread comes back to the caller
+  EXPECT_THROWS((*dp)(torch::randn({8, 5})));
+}
+
+// ---- LoRA utilities by path and by state dict
+ITB_TEST(LoRA, ReplaceByPathBaseParametersAndStateDictLoading) {
+  namespace lora = itb::nn::lora;
+  auto net = TinyNet();
+  lora::LoRAConfig cfg;
+  cfg.rank = 2, cfg.alpha = 4.0f;
+  cfg.target_modules = lora::ParseLoRATargetModules("0");
+  lora::GetLoRAModel(net, cfg);
+  EXPECT(lora::LoRAModules(net).size() == 1);
+  EXPECT(lora::GetLoRAParameters(net).size() == 2 && lora::GetBaseParameters(net).size() == 4);
+  for (auto& p : lora::GetBaseParameters(net)) EXPECT(!p.requires_grad());
+  auto sd = lora::LoRAStateDict(net);
+  std::map<std::string, Tensor> incoming;
+  for (auto& [k, v] : sd) incoming[k] = torch::full_like(v, 0.5f);
+  incoming["nowhere.lora_A"] = torch::zeros({1});
+  lora::LoadLoRAStateDict(net, incoming);                      // the unknown name is reported, not fatal
+  for (auto& [k, v] : lora::LoRAStateDict(net)) EXPECT(v.mean().item<float>() == 0.5f);
+  incoming.begin()->second = torch::zeros({1, 1});
+  EXPECT_THROWS(lora::LoadLoRAStateDict(net, incoming));
+  auto fresh = std::make_shared<itb::nn::Linear>(6, 5);
+  lora::ReplaceModuleByPath(net, "0", fresh);
+  EXPECT(lora::LoRAModules(net).empty() && net->mutable_module("0") == fresh);
+  EXPECT_THROWS(lora::ReplaceModuleByPath(net, "7.weight", fresh));
+  EXPECT_THROWS(lora::ReplaceModuleByPath(net, "", fresh));
+}
+
+// ---- IDX files
+ITB_TEST(Data, IdxFilesAndTheMnistDataset) {
+  const std::string dir = itbtest::temp_dir("mnist");
+  auto be32 = [](std::ofstream& f, uint32_t v) {
+    unsigned char b[4] = {static_cast<unsigned char>(v >> 24), static_cast<unsigned char>(v >> 16), static_cast<unsigned char>(v >> 8),
+                          static_cast<unsigned char>(v)};
+    f.write(reinterpret_cast<const char*>(b), 4);
+  };
+  const int n = 5;
+  for (const char* prefix : {"train", "t10k"}) {
+    std::ofstream img(dir + "/" + prefix + "-images-idx3-ubyte", std::ios::binary), lab(dir + "/" + prefix + "-labels-idx1-ubyte", std::ios::binary);
+    be32(img, 0x00000803), be32(img, n), be32(img, 28), be32(img, 28);
+    be32(lab, 0x00000801), be32(lab, n);
+    for (int i = 0; i < n; ++i) {
+      std::vector<unsigned char> px(28 * 28, static_cast<unsigned char>(51 * i));
+      img.write(reinterpret_cast<const char*>(px.data()), px.size());
+      unsigned char l = static_cast<unsigned char>(i * 2);
+      lab.write(reinterpret_cast<const char*>(&l), 1);
+    }
+  }
+  itb::data::MNISTDataset ds(dir, true);
+  EXPECT(ds.Size() == 5);
+  auto [x, y] = ds[3];
+  EXPECT(x.sizes() == torch::IntArrayRef({28, 28}) && x.scalar_type() == torch::kFloat32 && y.scalar_type() == torch::kUInt8);
+  EXPECT(std::fabs(x[0][0].item<float>() - 153.0f / 255.0f) < 1e-6f && y.item<uint8_t>() == 6);
+  itb::data::DataLoader loader(std::make_shared<itb::data::MNISTDataset>(dir, false), 2);
+  auto [bx, by] = *loader.begin();
+  EXPECT(bx.sizes() == torch::IntArrayRef({2, 28, 28}) && by.sizes() == torch::IntArrayRef({2}));
+  // uint8 class indices go straight into the loss
+  Tensor loss = itb::ops::cross_entropy(torch::zeros({2, 10}), by);
+  EXPECT(std::fabs(loss.item<float>() - std::log(10.0f)) < 1e-5f);
+  // a file that is not IDX, and one shorter than its header says
+  { std::ofstream bad(dir + "/bad", std::ios::binary); bad << "nope, not idx"; }
+  EXPECT_THROWS(itb::data::ReadIdxFile(dir + "/bad"));
+  { std::ofstream cut(dir + "/short", std::ios::binary); be32(cut, 0x00000801); be32(cut, 100); cut << "abc"; }
+  EXPECT_THROWS(itb::data::ReadIdxFile(dir + "/short"));
+  EXPECT_THROWS(itb::data::ReadIdxFile(dir + "/absent"));
+}
+
 ITB_TEST_MAIN()

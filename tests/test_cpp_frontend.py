@@ -234,3 +234,50 @@ def test_per_module_records_line_up_with_the_reference(trainer, files):
     assert {ln.split()[2] for ln in cpp_lines} <= ref_names
     assert re.match(r"\[GAS-0\] \[L-0\] transformer\.wte_forward tensor\[0\]: dtype=float32 shape=\(4,64,96\) min=\S+ max=\S+ "
                     r"mean=\S+ \[.*, \.\.\.\] \[NaN:0 Inf:0\]$", cpp_lines[0])
+
+
+def _write_idx(path, array):
+    import struct
+
+    with open(path, "wb") as f:
+        f.write(struct.pack(">HBB", 0, 0x08, array.ndim) + struct.pack(">" + "I" * array.ndim, *array.shape))
+        f.write(array.tobytes())
+
+
+def test_mnist_trainer_learns_and_data_parallel_replicas_change_nothing(tmp_path):
+    """examples/cpp/mnist.cc on IDX files: the loss falls, the test set is classified, and running the
+    network through the single-process DataParallel module (three replicas in threads) prints the same
+    numbers as the one module."""
+    import importlib.util
+
+    import numpy as np
+
+    spec = importlib.util.spec_from_file_location("itb_cpp_build", os.path.join(ROOT, "examples", "cpp", "build.py"))
+    cpp_build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cpp_build)
+    exe = cpp_build.build(src=os.path.join(ROOT, "examples", "cpp", "mnist.cc"), out=str(tmp_path / "itb_mnist"))
+    g = np.random.default_rng(0)
+    centers = g.uniform(0, 255, (10, 784))
+    for prefix, n in (("train", 640), ("t10k", 128)):
+        labels = g.integers(0, 10, n).astype(np.uint8)
+        images = np.clip(centers[labels] + g.normal(0, 30, (n, 784)), 0, 255).astype(np.uint8).reshape(n, 28, 28)
+        _write_idx(tmp_path / f"{prefix}-images-idx3-ubyte", images)
+        _write_idx(tmp_path / f"{prefix}-labels-idx1-ubyte", labels)
+
+    def run(*extra):
+        r = subprocess.run([str(exe), "--dataset", str(tmp_path), "--bs", "64", "--num_epoch", "3", "--lr", "0.5", *extra],
+                           capture_output=True, text=True, timeout=600, env=ENV)
+        assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+        text = r.stdout + r.stderr
+        epochs = [float(m.group(1)) for m in re.finditer(r"train loss ([\d.]+)", text)]
+        final = re.search(r"Total: (\d+), Correct: (\d+), Accuracy: ([\d.]+), AverageLoss: ([\d.]+)", text)
+        assert len(epochs) == 3 and final, text[-2000:]
+        return epochs, [float(x) for x in final.groups()], [l for l in text.splitlines() if "loss" in l.lower() and "ms" not in l]
+
+    epochs, final, lines = run()
+    assert epochs[2] < 0.5 * epochs[0]
+    assert final[0] == 128 and final[2] > 0.9
+    epochs_dp, final_dp, lines_dp = run("--data_parallel", "3")
+    assert lines_dp == lines and final_dp == final
+    r = subprocess.run([str(exe), "--dataset", str(tmp_path / "absent")], capture_output=True, text=True, timeout=60, env=ENV)
+    assert r.returncode != 0 and "cannot open IDX file" in r.stdout + r.stderr
