@@ -16,6 +16,7 @@
 //     its contribution, everybody combines them in group-rank order: slow, deterministic, and enough
 //     to run every parallel strategy of the framework on a machine without GPUs).
 #pragma once
+#include <torch/csrc/distributed/c10d/FileStore.hpp>
 #include <torch/csrc/distributed/c10d/TCPStore.hpp>
 
 #include <chrono>
@@ -125,7 +126,7 @@ inline Tensor Combine(const Tensor& acc, const Tensor& next, ReduceOp op) {
 // ------------------------------------------------------------------ CPU ranks through the TCP store
 class StoreProcessGroup : public ProcessGroup {
  public:
-  StoreProcessGroup(std::string name, std::vector<int> ranks, int my_global_rank, c10::intrusive_ptr<c10d::TCPStore> store)
+  StoreProcessGroup(std::string name, std::vector<int> ranks, int my_global_rank, c10::intrusive_ptr<c10d::Store> store)
       : ProcessGroup(std::move(name), std::move(ranks), my_global_rank), store_(std::move(store)) {}
 
   std::shared_ptr<Work> AllReduce(Tensor& t, ReduceOp op, bool) override {
@@ -245,7 +246,7 @@ class StoreProcessGroup : public ProcessGroup {
       mine_.erase(mine_.begin());
     }
   }
-  c10::intrusive_ptr<c10d::TCPStore> store_;
+  c10::intrusive_ptr<c10d::Store> store_;
   int64_t seq_ = 0, barrier_seq_ = 0;
   std::map<int, int64_t> send_seq_, recv_seq_;
   std::vector<std::string> mine_;
@@ -285,7 +286,7 @@ class CudaWork : public Work {
 
 class NcclProcessGroup : public ProcessGroup {
  public:
-  NcclProcessGroup(std::string name, std::vector<int> ranks, int my_global_rank, c10::intrusive_ptr<c10d::TCPStore> store)
+  NcclProcessGroup(std::string name, std::vector<int> ranks, int my_global_rank, c10::intrusive_ptr<c10d::Store> store)
       : ProcessGroup(std::move(name), std::move(ranks), my_global_rank),
         stream_(c10::cuda::getStreamFromPool(/*isHighPriority=*/true)) {
     ncclUniqueId id;
@@ -417,7 +418,7 @@ class NcclProcessGroup : public ProcessGroup {
 #endif  // ITB_WITH_CUDA
 
 // ------------------------------------------------------------------ factory
-// One TCP store per job (rank 0 serves it), one process group per name.  Init() creates the
+// One store per job (a TCP store that rank 0 serves, or a shared file), one process group per name.  Init() creates the
 // "default" group over every rank; DP / TP / PP groups of this rank come from the layout.
 class ProcessGroupFactory {
  public:
@@ -429,14 +430,23 @@ class ProcessGroupFactory {
     if (store_) return;
     GlobalEnv& e = env();
     device_ = device;
-    c10d::TCPStoreOptions o;
-    const char* port = std::getenv("MASTER_PORT");
-    const char* addr = std::getenv("MASTER_ADDR");
-    o.port = static_cast<uint16_t>(port && *port ? std::atoi(port) : 29500);
-    o.isServer = e.rank == 0;
-    o.numWorkers = e.world;
-    o.timeout = std::chrono::milliseconds(1000LL * timeout_s);
-    store_ = c10::make_intrusive<c10d::TCPStore>(addr && *addr ? addr : "127.0.0.1", o);
+    // Rendezvous: a file every rank can reach (ITB_RDZV_FILE, for jobs whose nodes share a file system and
+    // have no address to agree on; the reference exchanges its communicator ids through files in the same
+    // way, src/core/ccl/ccl_utils.cc:14-53), else the TCP store served by rank 0 at MASTER_ADDR:MASTER_PORT.
+    const char* file = std::getenv("ITB_RDZV_FILE");
+    if (file && *file) {
+      store_ = c10::make_intrusive<c10d::FileStore>(file, e.world);
+      store_->setTimeout(std::chrono::milliseconds(1000LL * timeout_s));
+    } else {
+      c10d::TCPStoreOptions o;
+      const char* port = std::getenv("MASTER_PORT");
+      const char* addr = std::getenv("MASTER_ADDR");
+      o.port = static_cast<uint16_t>(port && *port ? std::atoi(port) : 29500);
+      o.isServer = e.rank == 0;
+      o.numWorkers = e.world;
+      o.timeout = std::chrono::milliseconds(1000LL * timeout_s);
+      store_ = c10::make_intrusive<c10d::TCPStore>(addr && *addr ? addr : "127.0.0.1", o);
+    }
 #ifdef ITB_WITH_CUDA
     if (device.is_cuda()) c10::cuda::set_device(device.has_index() ? device.index() : static_cast<c10::DeviceIndex>(e.local_rank));
 #endif
@@ -445,7 +455,7 @@ class ProcessGroupFactory {
     GetOrCreate("default", all);
   }
   bool initialized() const { return static_cast<bool>(store_); }
-  c10::intrusive_ptr<c10d::TCPStore> store() const { return store_; }
+  c10::intrusive_ptr<c10d::Store> store() const { return store_; }
 
   std::shared_ptr<ProcessGroup> GetOrCreate(const std::string& name, const std::vector<int>& ranks) {
     auto it = groups_.find(name);
@@ -495,7 +505,7 @@ class ProcessGroupFactory {
   }
 
  private:
-  c10::intrusive_ptr<c10d::TCPStore> store_;
+  c10::intrusive_ptr<c10d::Store> store_;
   std::map<std::string, std::shared_ptr<ProcessGroup>> groups_;
   torch::Device device_ = torch::Device(torch::kCPU);
 };

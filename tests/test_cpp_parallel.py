@@ -225,3 +225,17 @@ def test_gpt2_tensor_and_sequence_parallel_inside_pipeline_stages(binaries, file
     pp, _ = _train(binaries, files, "gpt2", 2, *GPT2, "--pipeline_parallel", "2")
     both, _ = _train(binaries, files, "gpt2", 4, *GPT2, "--pipeline_parallel", "2", "--tensor_parallel", "2", "--sequence_parallel")
     assert max(abs(a - b) for a, b in zip(pp, both)) <= 2e-5, list(zip(pp, both))
+
+
+def test_ranks_meet_through_a_shared_file_instead_of_a_tcp_store(binaries, files, single, tmp_path):
+    """ITB_RDZV_FILE: the job's store is a file every rank can reach (the reference's ranks exchange their
+    communicator ids through files too); the endpoint the launcher exports is never contacted."""
+    launcher, trainer = binaries
+    cmd = [launcher, "--nproc_per_node=2", "--rdzv_endpoint=127.0.0.1:1", "--", trainer, "--family", "llama3", "--device", "cpu",
+           "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin", "--batch_size", "2", "--sequence_length", "64",
+           "--total_batch_size", "1024", "--num_iteration", "4", "--dtype", "float32", *LLAMA, "--tensor_parallel", "2"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=files,
+                       env={**ENV, "ITB_RDZV_FILE": str(tmp_path / "rendezvous")})
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    losses = _losses(r.stdout + r.stderr)
+    assert len(losses) == 4 and max(abs(a - b) for a, b in zip(losses, single["llama3"])) <= 2e-5
