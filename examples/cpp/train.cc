@@ -9,6 +9,7 @@
 //             [--save DIR --save_interval N --save_optimizer_state --max_checkpoint_keep K] [--load DIR/checkpoint_step_000004]
 //             [--tensor_parallel N --sequence_parallel --pipeline_parallel N --virtual_pipeline_parallel N
 //              --pipeline_schedule 1f1b|gpipe --zero_stage 0|1|2 --no_overlap_grad_reduce]
+//             [--overfit_single_batch] [--input_val_bin F --val_loss_every N --val_max_batches M] [--sample_every N]
 //             [--profile]   per-op / per-collective records, written as <family>.report.rank<r> and
 //                           <family>.records.log.rank<r> into the working directory
 // The ranks are laid out TP fastest, then DP, then PP; data parallelism takes what is left of the
@@ -206,6 +207,28 @@ int main(int argc, char** argv) {
   std::unique_ptr<itb::data::Tokenizer> tokenizer;
   if (!fl.get("tokenizer_bin", "").empty()) tokenizer = std::make_unique<itb::data::Tokenizer>(fl.get("tokenizer_bin", ""));
   const int64_t freq_generate = fl.geti("freq_generate_txt", 10), text_length = fl.geti("text_length", 64);
+  // --sample_every N: the llm.c name for the same sampling period (a placeholder in the reference's loop)
+  const int64_t sample_every = fl.geti("sample_every", 0);
+  // --overfit_single_batch: every micro-batch of every step is the first batch of the file
+  const bool overfit = fl.getb("overfit_single_batch", false);
+  itb::Tensor first_x, first_y;
+  auto next_batch = [&](itb::Tensor* x, itb::Tensor* y) {
+    if (overfit && first_x.defined()) {
+      *x = first_x, *y = first_y;
+      return;
+    }
+    loader.next(x, y);
+    ++consumed;
+    if (overfit) first_x = x->clone(), first_y = y->clone(), *x = first_x, *y = first_y;
+  };
+  // --input_val_bin F --val_loss_every N: every N steps and after the last one, the mean loss over the first
+  // --val_max_batches batches of this rank's share of F, averaged over the data-parallel group (a
+  // placeholder in the reference's loop, example/gpt2/main.cc:401-404); not under pipeline parallelism
+  const int64_t val_every = fl.geti("val_loss_every", 0), val_max_batches = fl.geti("val_max_batches", 20);
+  std::unique_ptr<itb::data::DistributedDataLoader> val_loader;
+  if (!fl.get("input_val_bin", "").empty() && val_every > 0 && pp == 1)
+    val_loader = std::make_unique<itb::data::DistributedDataLoader>(
+        std::make_shared<itb::data::TinyShakespeareDataset>(fl.get("input_val_bin", ""), T), B, env.dp_rank, dp);
   auto loss_of = [&](const itb::Tensor& logits, const itb::Tensor& y) {
     itb::AutocastGuard autocast(bf16 ? torch::kBFloat16 : torch::kFloat32);
     return (*loss_module)(itb::TensorList{logits, y})[0];
@@ -224,8 +247,7 @@ int main(int argc, char** argv) {
       std::vector<itb::Tensor> xs, ys;
       for (int64_t micro = 0; micro < grad_accum; ++micro) {
         itb::Tensor x, y;
-        loader.next(&x, &y);
-        ++consumed;
+        next_batch(&x, &y);
         // the loader's tensors alias a ring slot that the next calls reuse: the schedule needs its own copies
         xs.push_back(device.is_cpu() ? x.clone() : x.to(device)), ys.push_back(device.is_cpu() ? y.clone() : y.to(device));
       }
@@ -235,8 +257,7 @@ int main(int argc, char** argv) {
     } else {
       for (int64_t micro = 0; micro < grad_accum; ++micro) {
         itb::Tensor x, y;
-        loader.next(&x, &y);
-        ++consumed;
+        next_batch(&x, &y);
         x = x.to(device), y = y.to(device);
         if (ddp) ddp->set_sync(micro == grad_accum - 1);   // earlier micro-batches only accumulate
         itb::Tensor loss;
@@ -263,12 +284,33 @@ int main(int argc, char** argv) {
       lossf = l.item<float>();
     }
     double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    // high-water marks of the tensors' memory pool since the previous step (0 on the CPU, which has no pool)
+    auto [peak_used_mb, peak_reserved_mb] = itb::core::Runtime::For(device).GetMemPoolPeakMB(device);
+    itb::core::Runtime::For(device).ResetMemPoolHighWatermarks(device);
     if (env.rank == env.world - 1)   // the last rank logs, as in the reference (it holds the last pipeline stage)
       std::fprintf(stderr, "[E] step %4lld/%lld | train loss %.6f | lr %.2e | (%.2f ms | %.0f tok/s | peak used: %5.0f MB | "
                            "peak reserved: %5.0f MB, DP=%lld, TP=%lld, SP=%d, PP=%lld)\n",
-                   (long long)(step + 1), (long long)iters, lossf, lr, ms, total / (ms / 1e3), 0.0, 0.0, (long long)dp, (long long)tp,
+                   (long long)(step + 1), (long long)iters, lossf, lr, ms, total / (ms / 1e3), static_cast<double>(peak_used_mb), static_cast<double>(peak_reserved_mb), (long long)dp, (long long)tp,
                    env.sp(), (long long)pp);
-    if (tokenizer && freq_generate > 0 && (step + 1) % freq_generate == 0 && env.rank == 0 && !model_parallel) {
+    if (val_loader && ((step + 1) % val_every == 0 || step + 1 == iters)) {
+      torch::NoGradGuard no_grad;
+      double sum = 0.0;
+      int64_t n = 0;
+      for (auto it = val_loader->begin(); it != val_loader->end() && n < val_max_batches; ++it, ++n) {
+        auto [vx, vy] = *it;
+        itb::AutocastGuard autocast(bf16 ? torch::kBFloat16 : torch::kFloat32);
+        sum += loss_of(model->forward(vx.to(device)), vy.to(device)).item<float>();
+      }
+      itb::Tensor v = torch::tensor({sum, static_cast<double>(n)}, torch::dtype(torch::kFloat32).device(device));
+      if (dp_group) dp_group->AllReduce(v, par::ReduceOp::kSum);
+      v = v.cpu();
+      if (env.rank == env.world - 1 && v[1].item<float>() > 0)
+        std::fprintf(stderr, "[E] step %4lld/%lld | val loss %.6f (%lld batches)\n", (long long)(step + 1), (long long)iters,
+                     v[0].item<float>() / v[1].item<float>(), (long long)n);
+    }
+    const bool sample_now = (freq_generate > 0 && (step + 1) % freq_generate == 0) ||
+                            (sample_every > 0 && ((step + 1) % sample_every == 0 || step + 1 == iters));
+    if (tokenizer && sample_now && env.rank == 0 && !model_parallel) {
       std::vector<int64_t> ids;
       std::string text = tokenizer->GenerateText([&](const itb::Tensor& ids_in) { return model->forward(ids_in); }, B, T,
                                                  text_length, device, &ids);

@@ -236,6 +236,30 @@ def test_per_module_records_line_up_with_the_reference(trainer, files):
                     r"mean=\S+ \[.*, \.\.\.\] \[NaN:0 Inf:0\]$", cpp_lines[0])
 
 
+def test_validation_loss_and_single_batch_overfit_match_python_trainer(trainer, files):
+    """--input_val_bin / --val_loss_every / --val_max_batches and --overfit_single_batch: the C++ and the
+    Python trainer log the same validation losses and the same single-batch trajectory."""
+    common = ["--device", "cpu", "--llmc_filepath", "gpt2.bin", "--input_bin", "tokens16.bin", "--batch_size", "4",
+              "--sequence_length", "64", "--total_batch_size", "512", "--num_iteration", "5", "--dtype", "float32",
+              "--learning_rate", "0.05", "--optimizer", "sgd", "--input_val_bin", "tokens16.bin", "--val_loss_every", "2",
+              "--val_max_batches", "3", "--overfit_single_batch"]
+
+    def run(cmd):
+        r = subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=900, cwd=files, env=ENV)
+        assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+        text = r.stdout + r.stderr
+        val = [(int(m.group(1)), float(m.group(2)), int(m.group(3)))
+               for m in re.finditer(r"step\s+(\d+)/\d+ \| val loss ([\d.]+) \((\d+) batches\)", text)]
+        return _losses(text), val
+
+    cpp, cpp_val = run([trainer, "--family", "gpt2", *common])
+    py, py_val = run([sys.executable, os.path.join(ROOT, "examples", "gpt2", "main.py"), *common])
+    assert len(cpp) == 5 and max(abs(a - b) for a, b in zip(cpp, py)) <= 2e-6, list(zip(cpp, py))
+    assert all(b < a for a, b in zip(cpp, cpp[1:]))              # one batch, seen ten times: the loss only falls
+    assert [v[0] for v in cpp_val] == [2, 4, 5] and all(v[2] == 3 for v in cpp_val)
+    assert len(py_val) == 3 and max(abs(a[1] - b[1]) for a, b in zip(cpp_val, py_val)) <= 2e-6, (cpp_val, py_val)
+
+
 def _write_idx(path, array):
     import struct
 
