@@ -10,8 +10,9 @@
 //             [--tensor_parallel N --sequence_parallel --pipeline_parallel N --virtual_pipeline_parallel N
 //              --pipeline_schedule 1f1b|gpipe --zero_stage 0|1|2 --no_overlap_grad_reduce]
 //             [--overfit_single_batch] [--input_val_bin F --val_loss_every N --val_max_batches M] [--sample_every N]
-//             [--profile]   per-op / per-collective records, written as <family>.report.rank<r> and
-//                           <family>.records.log.rank<r> into the working directory
+//             [--profile]   per-op / per-collective records, written as <family>.report.rank<r>,
+//                           <family>.records.log.rank<r> and <family>.trace.rank<r>.json (Chrome trace) into
+//                           the working directory
 // The ranks are laid out TP fastest, then DP, then PP; data parallelism takes what is left of the
 // world size.  CPU ranks talk through the job's TCP store, GPU ranks through NCCL.
 #include <chrono>
@@ -340,6 +341,7 @@ int main(int argc, char** argv) {
     prof.Disable();
     prof.Report(family + ".report.rank" + std::to_string(env.rank));
     prof.PrintRecords(family + ".records.log.rank" + std::to_string(env.rank));
+    prof.ExportChromeTrace(family + ".trace.rank" + std::to_string(env.rank) + ".json");
   }
   if (auto world = par::ProcessGroupFactory::Instance().GetDefaultProcessGroup()) world->Barrier();
   // adapters of a model-parallel run are this rank's slices: one file per rank

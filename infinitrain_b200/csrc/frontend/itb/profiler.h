@@ -8,7 +8,8 @@
 // PrintRecords, SetTag, Reset).  There the profiler is a build mode (PROFILE_MODE); here it is a
 // run-time switch, off by default: a disabled range costs one load and one branch.  Like the
 // reference's, an enabled profiler serialises the device around every record: its numbers are shares
-// of a step, not a benchmark.
+// of a step, not a benchmark.  Beyond the reference: every record is also an NVTX range (CUDA build; a
+// no-op unless a tool is attached) and the records export as a Chrome trace (chrome://tracing, Perfetto).
 #pragma once
 #include <torch/torch.h>
 
@@ -27,6 +28,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <ATen/cuda/CUDAEvent.h>
 #include <c10/cuda/CUDACachingAllocator.h>
+#include <nvtx3/nvToolsExt.h>   // header-only: loads the tool's injection library when one is attached
 #endif
 
 namespace itb {
@@ -67,6 +69,7 @@ class Profiler {
     if (s.depth++ > 0) return;
     s.name = name, s.cuda = cuda;
 #ifdef ITB_WITH_CUDA
+    nvtxRangePushA(name.c_str());
     if (cuda) {
       at::cuda::getCurrentCUDAStream().synchronize();
       s.begin = std::make_unique<at::cuda::CUDAEvent>(cudaEventDefault);
@@ -92,6 +95,7 @@ class Profiler {
       const auto st = c10::cuda::CUDACachingAllocator::getDeviceStats(c10::cuda::current_device());
       r.max_device_mem_usage_mb = static_cast<int64_t>(st.reserved_bytes[0].peak >> 20);
     }
+    nvtxRangePop();
 #endif
     std::lock_guard<std::mutex> g(mu_);
     records_.push_back(std::move(r));
@@ -164,6 +168,35 @@ class Profiler {
     std::ofstream f(path);
     TORCH_CHECK(f.is_open(), "cannot write ", path);
     PrintRecords(f);
+  }
+  // Complete ("X") events, one per record, in the Trace Event format: pid = rank, tid 0 = host spans (start
+  // and host duration), tid 1 = device spans (same start, device duration), args carry the tag and the peak.
+  void ExportChromeTrace(std::ostream& os) const {
+    auto esc = [](const std::string& in) {
+      std::string out;
+      for (char c : in) {
+        if (c == '"' || c == '\\') out.push_back('\\');
+        out.push_back(c);
+      }
+      return out;
+    };
+    os << std::fixed << std::setprecision(3) << "{\"displayTimeUnit\": \"ms\", \"traceEvents\": [";
+    bool first = true;
+    for (const auto& r : records_) {
+      for (int lane = 0; lane < (r.device == "cuda" ? 2 : 1); ++lane) {
+        os << (first ? "\n" : ",\n") << "{\"name\": \"" << esc(r.name) << "\", \"cat\": \"" << (lane ? "device" : "host")
+           << "\", \"ph\": \"X\", \"pid\": " << r.rank << ", \"tid\": " << lane << ", \"ts\": " << r.start_us << ", \"dur\": "
+           << (lane ? r.device_us : r.host_us) << ", \"args\": {\"tag\": \"" << esc(r.tag) << "\", \"peak_mb\": "
+           << r.max_device_mem_usage_mb << "}}";
+        first = false;
+      }
+    }
+    os << "\n]}\n";
+  }
+  void ExportChromeTrace(const std::string& path) const {
+    std::ofstream f(path);
+    TORCH_CHECK(f.is_open(), "cannot write ", path);
+    ExportChromeTrace(f);
   }
 
  private:

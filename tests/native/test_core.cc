@@ -5,6 +5,7 @@
 #define ITB_TEST_WITH_TORCH
 #include "itb_test.h"
 
+#include <algorithm>
 #include <fstream>
 #include <sstream>
 
@@ -150,6 +151,16 @@ ITB_TEST_P(Profiler, RecordsOpsOncePerOuterRangeAndReportsPerTag) {
   prof.PrintRecords(rec);
   EXPECT(rep.str().find("Tag: Step_1") != std::string::npos && rep.str().find("Tag: Step_2") != std::string::npos);
   EXPECT(rep.str().find("Device Avg(us)") != std::string::npos && rec.str().find("Step_2\t3\tlinear") != std::string::npos);
+  // Chrome trace: one host span per record (and one device span on cuda), rank as the process id
+  std::ostringstream trace;
+  prof.ExportChromeTrace(trace);
+  const std::string tj = trace.str();
+  size_t spans = 0;
+  for (size_t at = tj.find("\"ph\": \"X\""); at != std::string::npos; at = tj.find("\"ph\": \"X\"", at + 1)) ++spans;
+  EXPECT(spans == prof.records().size() * (device().is_cuda() ? 2 : 1));
+  EXPECT(tj.find("\"traceEvents\": [") != std::string::npos && tj.find("\"name\": \"outer\"") != std::string::npos);
+  EXPECT(tj.find("\"pid\": 3") != std::string::npos && tj.find("\"tag\": \"Step_2\"") != std::string::npos);
+  EXPECT(tj.rfind("]}") != std::string::npos && std::count(tj.begin(), tj.end(), '{') == std::count(tj.begin(), tj.end(), '}'));
   prof.Reset();
   EXPECT(prof.records().empty());
 }

@@ -142,8 +142,9 @@ def test_model_parallel_checkpoint_resumes_per_rank(binaries, files, tmp_path):
 
 
 def test_profile_flag_writes_per_rank_reports_with_ops_and_collectives(binaries, files, tmp_path):
-    """--profile: every rank writes <family>.report.rank<r> and <family>.records.log.rank<r>; the records
-    are tagged by step and hold the ops, the optimizer step and the process-group collectives."""
+    """--profile: every rank writes <family>.report.rank<r>, <family>.records.log.rank<r> and a Chrome
+    trace; the records are tagged by step and hold the ops, the optimizer step and the process-group
+    collectives."""
     import shutil
 
     work = tmp_path / "run"
@@ -165,6 +166,13 @@ def test_profile_flag_writes_per_rank_reports_with_ops_and_collectives(binaries,
             assert name in report, (name, report[:2000])
         first = records.splitlines()[0].split("\t")
         assert first[0] == "Step_1" and first[1] == str(rank) and first[3] == "cpu"
+        # the same records as a Chrome trace: one complete event per record, the rank as the process id
+        import json
+
+        trace = json.loads((work / f"llama3.trace.rank{rank}.json").read_text())
+        events = trace["traceEvents"]
+        assert len(events) == len(records.splitlines()) and all(e["ph"] == "X" and e["pid"] == rank for e in events)
+        assert {"linear", "pg.AllReduce(TP0)"} <= {e["name"] for e in events} and events[-1]["args"]["tag"] == "Step_2"
 
 
 @pytest.mark.parametrize("flags", [("--tensor_parallel", "2"), ("--tensor_parallel", "2", "--sequence_parallel"),
