@@ -10,6 +10,10 @@
 //             [--tensor_parallel N --sequence_parallel --pipeline_parallel N --virtual_pipeline_parallel N
 //              --pipeline_schedule 1f1b|gpipe --zero_stage 0|1|2 --no_overlap_grad_reduce]
 //             [--overfit_single_batch] [--input_val_bin F --val_loss_every N --val_max_batches M] [--sample_every N]
+//             [--heartbeat_timeout S]   step heartbeats through the job's store and a watchdog thread: when a peer is
+//                           silent for S seconds, or asks for an abort, the process groups are aborted and the rank
+//                           ends with exit code 3 instead of waiting inside a collective (0 = off, the default);
+//                           ITB_FAULT="<rank>:<step>:raise|exit|stall|mute[:arg]" injects a host-side fault
 //             [--profile]   per-op / per-collective records, written as <family>.report.rank<r>,
 //                           <family>.records.log.rank<r> and <family>.trace.rank<r>.json (Chrome trace) into
 //                           the working directory
@@ -20,6 +24,7 @@
 #include <iostream>
 #include <map>
 #include <string>
+#include <thread>
 
 #include "itb/itb.h"
 
@@ -237,7 +242,32 @@ int main(int argc, char** argv) {
 
   const bool profile = fl.getb("profile", false);
   if (profile) itb::utils::Profiler::Instance().Enable(env.rank);
+  // failure detection: heartbeats and a watchdog over the job's store; faults are injected between steps
+  const double heartbeat_timeout = fl.getd("heartbeat_timeout", 0.0);
+  std::unique_ptr<itb::utils::Heartbeat> heartbeat;
+  if (heartbeat_timeout > 0 && env.world > 1) {
+    auto& factory = par::ProcessGroupFactory::Instance();
+    factory.SetAbortable(true);
+    heartbeat = std::make_unique<itb::utils::Heartbeat>(factory.store(), env.rank, env.world, heartbeat_timeout,
+                                                        std::min(0.5, heartbeat_timeout / 4), [&factory] { return factory.AllGroups(); });
+    heartbeat->Start();
+  }
+  itb::utils::FaultInjector injector(env.rank, nullptr, heartbeat.get(), device.is_cuda());
+  auto rank_failed = [&](const std::string& why) {
+    std::fprintf(stderr, "[E] rank %d stops: %s\n", env.rank, why.c_str());
+    std::fflush(stderr);
+    std::_Exit(3);   // peers are gone: no ordered shutdown, no collective in a destructor
+  };
   for (int64_t step = start_step; step < iters; ++step) {
+    injector.MaybeFire(step + 1);
+    if (heartbeat) {
+      try {
+        heartbeat->Step(step + 1);
+      } catch (const itb::utils::RankFailure& e) {
+        rank_failed(e.what());
+      }
+    }
+    try {
     auto t0 = std::chrono::steady_clock::now();
     if (profile) itb::utils::Profiler::Instance().SetTag("Step_" + std::to_string(step + 1));
     itb::utils::PrecisionChecker::Instance().ResetCounters();
@@ -335,7 +365,16 @@ int main(int argc, char** argv) {
       if (auto world = par::ProcessGroupFactory::Instance().GetDefaultProcessGroup()) world->Barrier();
       if (env.rank == 0) itb::io::PruneCheckpoints(fl.get("save", ""), fl.geti("max_checkpoint_keep", 0));
     }
+    } catch (const c10::Error& e) {
+      // a collective that the watchdog aborted comes back as an error: report the failure it saw
+      // (an error of the store itself can arrive before the watchdog's next look: give it two polls)
+      for (int i = 0; heartbeat && !heartbeat->failure() && i < 100; ++i)
+        std::this_thread::sleep_for(std::chrono::duration<double>(std::min(0.5, heartbeat_timeout / 4) / 50));
+      if (heartbeat && heartbeat->failure()) rank_failed(heartbeat->failure()->str());
+      throw;
+    }
   }
+  if (heartbeat) heartbeat->Stop();
   if (profile) {
     auto& prof = itb::utils::Profiler::Instance();
     prof.Disable();

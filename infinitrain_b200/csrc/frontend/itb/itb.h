@@ -13,6 +13,7 @@
 #include "datatype.h"
 #include "ddp.h"
 #include "distributed.h"
+#include "fault_tolerance.h"
 #include "functional.h"
 #include "io.h"
 #include "layers.h"

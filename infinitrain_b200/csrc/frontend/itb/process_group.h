@@ -19,9 +19,11 @@
 #include <torch/csrc/distributed/c10d/FileStore.hpp>
 #include <torch/csrc/distributed/c10d/TCPStore.hpp>
 
+#include <atomic>
 #include <chrono>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <thread>
 
 #include "module.h"
@@ -105,11 +107,20 @@ class ProcessGroup {
   virtual void Barrier() = 0;
   // 0 = healthy; a transport error code otherwise (NCCL: the communicator's asynchronous error).
   virtual int AsyncError() { return 0; }
+  // Failure handling (fault_tolerance.h).  Abort() may be called from another thread than the one inside a
+  // collective: it makes this group's pending and future calls end with an error instead of waiting for a
+  // peer that is gone.  A group waits abortably (in short slices, looking at the flag) once set_abortable(true)
+  // has been called; without it a wait costs one store round trip less.
+  virtual void Abort() { aborted_ = true; }
+  bool aborted() const { return aborted_; }
+  void set_abortable(bool on) { abortable_ = on; }
 
  protected:
+  void CheckNotAborted() const { TORCH_CHECK(!aborted_, "process group ", name_, " was aborted (a peer failed)"); }
   std::string name_;
   std::vector<int> ranks_;
   int group_rank_;
+  std::atomic<bool> aborted_{false}, abortable_{false};
 };
 
 inline Tensor Combine(const Tensor& acc, const Tensor& next, ReduceOp op) {
@@ -176,7 +187,10 @@ class StoreProcessGroup : public ProcessGroup {
     if (rank() == src) {
       // the source waits for every reader: nothing else holds it back, and its buffer must outlive them
       Publish(key, t);
-      while (store_->add(ack, 0) < size() - 1) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+      while (store_->add(ack, 0) < size() - 1) {
+        CheckNotAborted();
+        std::this_thread::sleep_for(std::chrono::milliseconds(1));
+      }
       store_->deleteKey(key);
       store_->deleteKey(ack);
     } else {
@@ -214,7 +228,10 @@ class StoreProcessGroup : public ProcessGroup {
   void Barrier() override {
     const std::string key = "itb/pg/" + name_ + "/bar/" + std::to_string(barrier_seq_++);
     store_->add(key, 1);
-    while (store_->add(key, 0) < size()) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    while (store_->add(key, 0) < size()) {
+      CheckNotAborted();
+      std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    }
   }
 
  private:
@@ -231,6 +248,16 @@ class StoreProcessGroup : public ProcessGroup {
     store_->set(key, std::vector<uint8_t>(p, p + t.nbytes()));
   }
   Tensor Fetch(const std::string& key, const Tensor& like) {
+    if (abortable_) {
+      // wait in slices so that Abort() from the watchdog thread ends the wait
+      const auto t0 = std::chrono::steady_clock::now();
+      while (!store_->check({key})) {
+        CheckNotAborted();
+        TORCH_CHECK(std::chrono::steady_clock::now() - t0 < store_->getTimeout(), "StoreProcessGroup ", name_, ": no rank published ", key);
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+      }
+    }
+    CheckNotAborted();
     auto bytes = store_->get(key);   // blocks until the key exists
     TORCH_CHECK(bytes.size() == like.nbytes(), "StoreProcessGroup ", name_, ": ranks disagree on the size of ", key);
     Tensor t = torch::empty_like(like);
@@ -257,7 +284,7 @@ class StoreProcessGroup : public ProcessGroup {
 // Work of a collective enqueued on the group's stream: a CUDA event recorded behind it.
 class CudaWork : public Work {
  public:
-  explicit CudaWork(ncclComm_t comm) : comm_(comm) {}
+  CudaWork(ncclComm_t comm, std::shared_ptr<std::atomic<bool>> comm_gone) : comm_(comm), comm_gone_(std::move(comm_gone)) {}
   void record(const c10::cuda::CUDAStream& s) { done_.record(s); }
   bool WaitBlocking(int64_t timeout_ms) override {
     const auto t0 = std::chrono::steady_clock::now();
@@ -274,6 +301,7 @@ class CudaWork : public Work {
   bool IsCompleted() const override { return done_.query(); }
   std::string error() const override {
     ncclResult_t st = ncclSuccess;
+    if (comm_gone_ && *comm_gone_) return "the communicator was aborted";
     if (comm_ && ncclCommGetAsyncError(comm_, &st) == ncclSuccess && st != ncclSuccess && st != ncclInProgress)
       return ncclGetErrorString(st);
     return std::string();
@@ -281,6 +309,7 @@ class CudaWork : public Work {
 
  private:
   ncclComm_t comm_;
+  std::shared_ptr<std::atomic<bool>> comm_gone_;   // set by the group's Abort(): comm_ must not be touched any more
   at::cuda::CUDAEvent done_;
 };
 
@@ -303,7 +332,13 @@ class NcclProcessGroup : public ProcessGroup {
     Check(ncclCommInitRank(&comm_, size(), id, rank()), "ncclCommInitRank");
   }
   ~NcclProcessGroup() override {
-    if (comm_) ncclCommDestroy(comm_);
+    if (comm_ && !*comm_gone_) ncclCommDestroy(comm_);
+  }
+  // ncclCommAbort ends the communicator's kernels that wait for a peer and frees it; the group is unusable afterwards.
+  void Abort() override {
+    if (aborted_.exchange(true)) return;
+    *comm_gone_ = true;
+    if (comm_) ncclCommAbort(comm_);
   }
   std::shared_ptr<Work> AllReduce(Tensor& t, ReduceOp op, bool async_op) override {
     return Run(async_op, {t}, [&](cudaStream_t s) {
@@ -366,6 +401,7 @@ class NcclProcessGroup : public ProcessGroup {
     at::cuda::getCurrentCUDAStream().synchronize();
   }
   int AsyncError() override {
+    if (*comm_gone_) return static_cast<int>(ncclInternalError);
     ncclResult_t st = ncclSuccess;
     ncclCommGetAsyncError(comm_, &st);
     return st == ncclInProgress ? 0 : static_cast<int>(st);
@@ -375,6 +411,7 @@ class NcclProcessGroup : public ProcessGroup {
   template <class F>
   std::shared_ptr<Work> Run(bool async_op, const TensorList& touched, F&& enqueue) {
     ITB_PROFILE("pg.nccl(" + name_ + ")", true);
+    CheckNotAborted();
     for (const Tensor& t : touched) TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "NcclProcessGroup: contiguous CUDA tensors");
     auto compute = at::cuda::getCurrentCUDAStream();
     at::cuda::CUDAEvent ready;
@@ -383,7 +420,7 @@ class NcclProcessGroup : public ProcessGroup {
     for (const Tensor& t : touched)             // the caching allocator must not recycle them under the collective
       c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), stream_);
     Check(enqueue(stream_.stream()), "NCCL collective");
-    auto work = std::make_shared<CudaWork>(comm_);
+    auto work = std::make_shared<CudaWork>(comm_, comm_gone_);
     work->record(stream_);
     if (!async_op) work->WaitNonBlocking();     // the compute stream waits; the host never does
     return work;
@@ -413,6 +450,7 @@ class NcclProcessGroup : public ProcessGroup {
   }
   static void Check(ncclResult_t r, const char* what) { TORCH_CHECK(r == ncclSuccess, what, ": ", ncclGetErrorString(r)); }
   ncclComm_t comm_ = nullptr;
+  std::shared_ptr<std::atomic<bool>> comm_gone_ = std::make_shared<std::atomic<bool>>(false);
   c10::cuda::CUDAStream stream_;
 };
 #endif  // ITB_WITH_CUDA
@@ -469,14 +507,29 @@ class ProcessGroupFactory {
       TORCH_CHECK(!device_.is_cuda(), "this build has no CUDA support");
       g = std::make_shared<StoreProcessGroup>(name, ranks, env().rank, store_);
     }
+    g->set_abortable(abortable_);
+    std::lock_guard<std::mutex> lock(mu_);
     groups_[name] = g;
     return g;
+  }
+  // Every group of the job, those created later included, waits in short slices so that Abort() (from a
+  // watchdog thread) ends a wait for a peer that is gone.
+  void SetAbortable(bool on) {
+    abortable_ = on;
+    for (auto& g : AllGroups()) g->set_abortable(on);
   }
   std::shared_ptr<ProcessGroup> Get(const std::string& name) const {
     auto it = groups_.find(name);
     return it == groups_.end() ? nullptr : it->second;
   }
   std::shared_ptr<ProcessGroup> GetDefaultProcessGroup() const { return Get("default"); }
+  // Every group created so far (what a watchdog aborts when a peer fails).
+  std::vector<std::shared_ptr<ProcessGroup>> AllGroups() const {
+    std::vector<std::shared_ptr<ProcessGroup>> out;
+    std::lock_guard<std::mutex> lock(mu_);
+    for (auto& [name, g] : groups_) out.push_back(g);
+    return out;
+  }
   // The group of this rank along one axis, or null when the axis has one rank.
   std::shared_ptr<ProcessGroup> AxisGroup(Axis axis) {
     if (env().layout.size(axis) <= 1 || !store_) return nullptr;
@@ -507,6 +560,8 @@ class ProcessGroupFactory {
  private:
   c10::intrusive_ptr<c10d::Store> store_;
   std::map<std::string, std::shared_ptr<ProcessGroup>> groups_;
+  mutable std::mutex mu_;   // AllGroups() may be called from a watchdog thread while the training thread creates a group
+  bool abortable_ = false;
   torch::Device device_ = torch::Device(torch::kCPU);
 };
 

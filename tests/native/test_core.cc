@@ -9,6 +9,8 @@
 #include <fstream>
 #include <sstream>
 
+#include <torch/csrc/distributed/c10d/HashStore.hpp>
+
 #include "itb/itb.h"
 
 using itb::Tensor;
@@ -431,6 +433,131 @@ ITB_TEST(Data, IdxFilesAndTheMnistDataset) {
   { std::ofstream cut(dir + "/short", std::ios::binary); be32(cut, 0x00000801); be32(cut, 100); cut << "abc"; }
   EXPECT_THROWS(itb::data::ReadIdxFile(dir + "/short"));
   EXPECT_THROWS(itb::data::ReadIdxFile(dir + "/absent"));
+}
+
+// ---- failure detection on the host: heartbeats, watchdog, abort, fault injection
+ITB_TEST(FaultTolerance, WatchdogSeesAStalePeerAndAbortsTheGroupsOfItsRank) {
+  using itb::utils::Heartbeat;
+  auto store = c10::make_intrusive<c10d::HashStore>();
+  // a group that only records that it was aborted
+  struct Probe : itb::parallel::ProcessGroup {
+    Probe() : ProcessGroup("probe", {0, 1}, 0) {}
+    using W = std::shared_ptr<itb::parallel::Work>;
+    W AllReduce(Tensor&, itb::parallel::ReduceOp, bool) override { return nullptr; }
+    W AllGather(Tensor&, const Tensor&, bool) override { return nullptr; }
+    W ReduceScatter(Tensor&, const Tensor&, itb::parallel::ReduceOp, bool) override { return nullptr; }
+    W BroadCast(Tensor&, int, bool) override { return nullptr; }
+    W Send(const itb::TensorList&, int, bool) override { return nullptr; }
+    W Recv(itb::TensorList&, int, bool) override { return nullptr; }
+    W BatchSendRecv(std::vector<itb::parallel::P2POp>&, bool) override { return nullptr; }
+    void Barrier() override {}
+  };
+  auto group = std::make_shared<Probe>();
+  Heartbeat a(store, 0, 2, /*timeout_s=*/0.3, /*poll_s=*/0.05, [&] { return std::vector<std::shared_ptr<itb::parallel::ProcessGroup>>{group}; });
+  Heartbeat b(store, 1, 2, 0.3, 0.05);
+  a.Start();
+  b.Beat(0);
+  for (int step = 1; step <= 3; ++step) {          // both alive: no report
+    a.Step(step), b.Step(step);
+    std::this_thread::sleep_for(std::chrono::milliseconds(60));
+  }
+  EXPECT(!a.failure() && !group->aborted());
+  // rank 1 falls silent; rank 0 goes on beating
+  const auto t0 = std::chrono::steady_clock::now();
+  while (!a.failure() && std::chrono::steady_clock::now() - t0 < std::chrono::seconds(5)) {
+    a.Beat(4);
+    std::this_thread::sleep_for(std::chrono::milliseconds(20));
+  }
+  EXPECT(a.failure() && a.failure()->kind == "stale_heartbeat" && a.failure()->rank == 1 && a.failure()->step == 3);
+  EXPECT(group->aborted());
+  EXPECT_THROWS(a.Step(5));
+  // rank 0 posted the reason: rank 1 reads it as a peer's abort, on a scan of its own and in WaitPeers
+  auto seen = b.Scan();
+  EXPECT(seen && seen->kind == "peer_abort" && seen->rank == 0 && seen->detail.find("stale_heartbeat of rank 1") != std::string::npos);
+  EXPECT_THROWS(b.WaitPeers(9, 0.2));
+  a.Stop();
+}
+
+ITB_TEST(FaultTolerance, ScanClockGracePeriodAndWaitPeers) {
+  using itb::utils::Heartbeat;
+  auto store = c10::make_intrusive<c10d::HashStore>();
+  Heartbeat a(store, 0, 3, 10.0, 0.05), b(store, 1, 3, 10.0, 0.05), c(store, 2, 3, 10.0, 0.05);
+  const double now = itb::utils::wall_seconds();
+  EXPECT(!a.Scan(now));                                   // nobody has beaten yet, inside the grace period
+  auto late = a.Scan(now + 11.0);
+  EXPECT(late && late->kind == "stale_heartbeat" && late->detail == "no heartbeat was ever published");
+  b.Beat(4), c.Beat(5);
+  EXPECT(!a.Scan(now + 5.0));
+  auto stale = a.Scan(now + 20.0);
+  EXPECT(stale && stale->rank == 1 && stale->step == 4);
+  a.WaitPeers(4, 1.0);                                    // both peers are at step 4 or later
+  std::thread slow([&] {
+    std::this_thread::sleep_for(std::chrono::milliseconds(100));
+    b.Beat(5);
+  });
+  a.WaitPeers(5, 2.0);                                    // returns once rank 1 arrives
+  slow.join();
+  bool threw = false;
+  try {
+    a.WaitPeers(6, 0.15);
+  } catch (const itb::utils::RankFailure& e) {
+    threw = std::string(e.what()).find("did not reach step 6") != std::string::npos;
+  }
+  EXPECT(threw);
+  // a status word of a kernel: zero passes, anything else is a timeout of a bounded wait
+  itb::utils::CheckKernelStatus([] { return 0; });
+  EXPECT_THROWS(itb::utils::CheckKernelStatus([] { return 7; }, "probe"));
+}
+
+ITB_TEST(FaultTolerance, InjectorFiresOnceOnItsRankAndStepAndRefusesToEndACudaRankUnderMulticast) {
+  using itb::utils::FaultInjector;
+  FaultInjector none(0, "");
+  EXPECT(!none.armed());
+  none.MaybeFire(1);
+  FaultInjector other(0, "1:3:raise");
+  EXPECT(!other.armed());
+  other.MaybeFire(3);                                      // another rank's fault
+  FaultInjector raise(1, "1:3:raise");
+  raise.MaybeFire(2);
+  EXPECT(!raise.fired());
+  EXPECT_THROWS(raise.MaybeFire(3));
+  raise.MaybeFire(3);                                      // once only
+  auto store = c10::make_intrusive<c10d::HashStore>();
+  itb::utils::Heartbeat hb(store, 0, 1);
+  FaultInjector mute(0, "0:2:mute", &hb);
+  hb.Beat(1);
+  mute.MaybeFire(2);
+  hb.Beat(2);                                              // muted: the store keeps step 1
+  auto raw = store->get("itb/hb/0");
+  EXPECT(std::string(raw.begin(), raw.end()).rfind("1:", 0) == 0);
+  FaultInjector stall(0, "0:1:stall:0.05");
+  const auto t0 = std::chrono::steady_clock::now();
+  stall.MaybeFire(1);
+  EXPECT(std::chrono::steady_clock::now() - t0 >= std::chrono::milliseconds(45));
+  EXPECT_THROWS(FaultInjector(0, "0:1"));
+  EXPECT_THROWS(FaultInjector(0, "0:1:explode"));
+  // a CUDA rank may be ended only with NVLink multicast off in NCCL and in this framework's kernels
+  unsetenv("ITB_NVLS"), unsetenv("NCCL_NVLS_ENABLE");
+  FaultInjector gpu_exit(0, "0:1:exit", nullptr, /*on_cuda=*/true);
+  EXPECT(!gpu_exit.ExitAllowed());
+  EXPECT_THROWS(gpu_exit.MaybeFire(1));
+  setenv("ITB_NVLS", "0", 1), setenv("NCCL_NVLS_ENABLE", "0", 1);
+  EXPECT(FaultInjector(0, "0:1:exit", nullptr, true).ExitAllowed());
+  unsetenv("ITB_NVLS"), unsetenv("NCCL_NVLS_ENABLE");
+  EXPECT(FaultInjector(0, "0:1:exit").ExitAllowed());     // CPU rank
+}
+
+ITB_TEST(FaultTolerance, ACorruptedCheckpointIsRefusedByTheLoader) {
+  const std::string dir = itbtest::temp_dir("corrupt");
+  std::map<std::string, Tensor> sd = {{"w", torch::arange(12, torch::kFloat32).view({3, 4})}, {"b", torch::ones({4})}};
+  itb::io::SaveStateDict(dir + "/model.ckpt", sd);
+  auto back = itb::io::LoadStateDict(dir + "/model.ckpt");
+  EXPECT(torch::equal(back.at("w"), sd.at("w")));
+  itb::utils::CorruptFile(dir + "/model.ckpt", 0, 4);      // the magic number
+  EXPECT_THROWS(itb::io::LoadStateDict(dir + "/model.ckpt"));
+  itb::utils::CorruptFile(dir + "/model.ckpt", 0, 4);      // flipping twice restores the file
+  EXPECT(torch::equal(itb::io::LoadStateDict(dir + "/model.ckpt").at("b"), sd.at("b")));
+  EXPECT_THROWS(itb::utils::CorruptFile(dir + "/absent", 0, 4));
 }
 
 ITB_TEST_MAIN()

@@ -6,6 +6,7 @@
 // (process_group.cc:118-249), the Reducer's bucket assignment and overlap (ddp/reducer.cc:56-438),
 // ZeRO-1 state partitioning (ddp/distributed_optimizer.cc:34-137) and the pipeline schedules
 // (pp/pipeline_schedule.cc:27-329) against the same computation done by one rank.
+
 #define ITB_TEST_WITH_TORCH
 #include "itb_test.h"
 
@@ -86,6 +87,41 @@ struct Stack : itb::Module {
 }  // namespace
 
 // ------------------------------------------------------------------ layout, names, stage partition
+// A rank that waits inside a collective for a peer that never arrives comes back with an error once
+// another thread (the watchdog of fault_tolerance.h) aborts its group; later calls fail at once.
+ITB_TEST(ProcessGroup, AbortEndsAWaitForAPeerThatIsGone) {
+  c10d::TCPStoreOptions server;
+  server.port = static_cast<uint16_t>(free_port());
+  server.isServer = true;
+  server.numWorkers = c10::nullopt;
+  server.waitWorkers = false;
+  server.timeout = std::chrono::milliseconds(60000);
+  auto store = c10::make_intrusive<c10d::TCPStore>("127.0.0.1", server);
+  auto pg = std::make_shared<par::StoreProcessGroup>("lonely", std::vector<int>{0, 1}, 0, store);
+  pg->set_abortable(true);
+  std::string error;
+  std::atomic<bool> returned{false};
+  std::thread rank0([&] {
+    try {
+      Tensor t = torch::ones({4});
+      pg->AllReduce(t, par::ReduceOp::kSum, false);   // rank 1 never publishes its part
+    } catch (const std::exception& e) {
+      error = e.what();
+    }
+    returned = true;
+  });
+  std::this_thread::sleep_for(std::chrono::milliseconds(150));
+  EXPECT(!returned);                          // still waiting
+  const auto t0 = std::chrono::steady_clock::now();
+  pg->Abort();
+  rank0.join();
+  EXPECT(std::chrono::steady_clock::now() - t0 < std::chrono::seconds(2));
+  EXPECT(error.find("was aborted") != std::string::npos && pg->aborted());
+  Tensor again = torch::ones({4});
+  EXPECT_THROWS(pg->AllReduce(again, par::ReduceOp::kSum, false));
+  EXPECT_THROWS(pg->Barrier());
+}
+
 ITB_TEST(Layout3D, TensorParallelRanksAreAdjacentThenDataThenPipeline) {
   par::Layout l;
   l.tp = 2, l.dp = 2, l.pp = 2;

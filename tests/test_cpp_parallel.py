@@ -247,3 +247,58 @@ def test_ranks_meet_through_a_shared_file_instead_of_a_tcp_store(binaries, files
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
     losses = _losses(r.stdout + r.stderr)
     assert len(losses) == 4 and max(abs(a - b) for a, b in zip(losses, single["llama3"])) <= 2e-5
+
+
+def _start_ranks(trainer, files, world, extra, env_extra, iters=6):
+    """The rank processes started directly (no launcher that would end the survivors itself)."""
+    port = _free_port()
+    procs = []
+    for rank in range(world):
+        env = {**ENV, "RANK": str(rank), "LOCAL_RANK": str(rank), "WORLD_SIZE": str(world), "MASTER_ADDR": "127.0.0.1",
+               "MASTER_PORT": str(port), **env_extra}
+        cmd = [trainer, "--family", "llama3", "--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin",
+               "--batch_size", "2", "--sequence_length", "64", "--total_batch_size", "1024", "--num_iteration", str(iters),
+               "--dtype", "float32", *LLAMA, *extra]
+        procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=files, env=env))
+    return procs
+
+
+@pytest.mark.parametrize("kind,flags", [("exit", ("--tensor_parallel", "2")), ("mute", ("--zero_stage", "1")),
+                                        ("stall:60", ("--pipeline_parallel", "2"))], ids=["exit_tp", "mute_zero1", "stall_pp"])
+def test_survivors_of_a_failed_rank_stop_with_a_report_instead_of_waiting(binaries, files, kind, flags):
+    """--heartbeat_timeout: rank 1 leaves, falls silent or stalls at step 3 (host-side injection, between
+    steps).  Rank 0 sits in a collective that will never complete; its watchdog sees the stale heartbeat,
+    aborts the process groups and the rank ends with exit code 3 and a report, within seconds."""
+    import time
+
+    _, trainer = binaries
+    t0 = time.time()
+    # the muted rank goes on training: the run must outlast the watchdog's patience
+    procs = _start_ranks(trainer, files, 2, (*flags, "--heartbeat_timeout", "2"), {"ITB_FAULT": f"1:3:{kind}"},
+                         iters=200 if kind == "mute" else 6)
+    try:
+        out0, _ = procs[0].communicate(timeout=120)
+    finally:
+        for p in procs:                        # the stalled rank is still asleep: end exactly the processes started here
+            if p.poll() is None:
+                p.kill()
+        out1, _ = procs[1].communicate(timeout=30)
+    elapsed = time.time() - t0
+    if kind == "mute":
+        # the muted rank keeps training; the watchdog of rank 0 cannot tell it from a dead one and stops the job
+        assert procs[0].returncode == 3 and "stale_heartbeat" in out0, out0[-2000:]
+    else:
+        assert procs[0].returncode == 3, (procs[0].returncode, out0[-2000:])
+        # a rank that waits inside a collective does not beat either: the stalled rank's own watchdog may be the
+        # first to call the abort, and rank 0 then reports that request
+        want = "rank 0 stops: rank 1: stale_heartbeat" if kind == "exit" else "rank 0 stops: rank 1: "
+        assert want in out0, out0[-2000:]
+    assert len(_losses(out0 + out1)) >= 2          # steps 1 and 2 were trained before the fault
+    if kind == "exit":
+        assert procs[1].returncode == 17
+    assert elapsed < 60, elapsed
+
+
+def test_heartbeats_cost_nothing_visible_and_an_unarmed_injector_does_nothing(binaries, files, single):
+    losses, _ = _train(binaries, files, "llama3", 2, *LLAMA, "--tensor_parallel", "2", "--heartbeat_timeout", "30")
+    assert max(abs(a - b) for a, b in zip(losses, single["llama3"])) <= 2e-5
