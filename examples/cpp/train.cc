@@ -7,6 +7,7 @@
 //             --device cpu|cuda --dtype float32|bfloat16 --optimizer sgd|adam|adamw
 //             [--lora_rank 8 --lora_alpha 16 --lora_target_modules c_attn,c_proj --lora_load_path F --lora_save_path F]
 //             [--save DIR --save_interval N --save_optimizer_state --max_checkpoint_keep K] [--load DIR/checkpoint_step_000004]
+//             [--elastic_resume]   --load a checkpoint written by another number of data-parallel ranks (ZeRO state is re-cut)
 //             [--tensor_parallel N --sequence_parallel --pipeline_parallel N --virtual_pipeline_parallel N
 //              --pipeline_schedule 1f1b|gpipe --zero_stage 0|1|2 --no_overlap_grad_reduce]
 //             [--overfit_single_batch] [--input_val_bin F --val_loss_every N --val_max_batches M] [--sample_every N]
@@ -195,19 +196,49 @@ int main(int argc, char** argv) {
   // which ranks hold state nobody else has: every model-parallel slice, and under ZeRO every shard of the optimizer state
   const bool own_state = model_parallel || (dp > 1 && zero_stage >= 1);
   if (!fl.get("load", "").empty()) {
-    std::string dir = fl.get("load", "");
+    const std::string root = fl.get("load", "");
+    std::string dir = root;
     if (std::filesystem::exists(dir + "/" + itb::io::RankDirName(env.rank))) dir += "/" + itb::io::RankDirName(env.rank);
+    // --elastic_resume: a checkpoint that another number of data-parallel ranks wrote (same tensor / pipeline
+    // layout).  Weights are the same on every data-parallel rank; the slices of a ZeRO optimizer state are put
+    // together from the old ranks' files and cut again for this rank.
+    const bool elastic = fl.getb("elastic_resume", false);
+    auto old_rank_dir = [&](int64_t old_dp, int64_t d) {   // the rank that held (tp_rank, d, pp_rank) in the old job
+      return root + "/" + itb::io::RankDirName(static_cast<int>(env.tp_rank + tp * (d + old_dp * env.pp_rank)));
+    };
+    if (elastic && !std::filesystem::exists(dir + "/trainer_state.json")) {
+      // this rank's number did not exist in the old job, or held other coordinates: read the layout from rank 0's state
+      auto probe = itb::io::LoadTrainerState(root + "/" + itb::io::RankDirName(0) + "/trainer_state.json");
+      dir = old_rank_dir(probe.ddp_size, 0);
+    }
     auto st = itb::io::LoadTrainerState(dir + "/trainer_state.json");
     TORCH_CHECK(st.n_layer == cfg.n_layer && st.n_embd == cfg.n_embd, "checkpoint and model shapes differ");
-    TORCH_CHECK(st.tp_size == tp && st.pp_size == pp && st.sp_size == env.sp() && (st.ddp_size == dp || !own_state),
+    const bool resized = st.ddp_size != dp;
+    TORCH_CHECK(st.tp_size == tp && st.pp_size == pp && st.sp_size == env.sp() && (!resized || !own_state || elastic),
                 "the checkpoint was written under another parallel layout (DP=", st.ddp_size, " TP=", st.tp_size, " SP=", st.sp_size,
-                " PP=", st.pp_size, ")");
+                " PP=", st.pp_size, "); --elastic_resume accepts another data-parallel size");
+    if (resized && own_state && std::filesystem::exists(old_rank_dir(st.ddp_size, 0))) dir = old_rank_dir(st.ddp_size, 0);
     model->LoadStateDict(itb::io::LoadStateDict(dir + "/model.ckpt"));
-    if (std::filesystem::exists(dir + "/optimizer.ckpt")) optimizer->LoadStateDict(itb::io::LoadStateDict(dir + "/optimizer.ckpt"));
+    if (std::filesystem::exists(dir + "/optimizer.ckpt")) {
+      if (resized && ddp && zero_stage >= 1) {
+        std::vector<std::map<std::string, itb::Tensor>> old_states;
+        for (int64_t d = 0; d < st.ddp_size; ++d) old_states.push_back(itb::io::LoadStateDict(old_rank_dir(st.ddp_size, d) + "/optimizer.ckpt"));
+        std::vector<int64_t> numels;
+        for (const auto& p : ddp->buffer()->params()) numels.push_back(p.numel());
+        optimizer->LoadStateDict(par::ReshardZeroState(old_states, {numels}, static_cast<int>(dp), env.dp_rank));
+        if (env.rank == 0)
+          std::fprintf(stderr, "[I] elastic resume: ZeRO optimizer state of %lld data-parallel ranks re-cut for %lld\n",
+                       (long long)st.ddp_size, (long long)dp);
+      } else {
+        optimizer->LoadStateDict(itb::io::LoadStateDict(dir + "/optimizer.ckpt"));
+      }
+    }
     start_step = st.global_step;
+    // a rank consumes 1/dp of the batches: keep the position in the token stream
+    const int64_t to_skip = resized ? st.consumed_batches * st.ddp_size / dp : st.consumed_batches;
     itb::Tensor x, y;
-    for (int64_t i = 0; i < st.consumed_batches; ++i) loader.next(&x, &y);
-    consumed = st.consumed_batches;
+    for (int64_t i = 0; i < to_skip; ++i) loader.next(&x, &y);
+    consumed = to_skip;
   }
   const int64_t save_interval = fl.geti("save_interval", 0);
   std::unique_ptr<itb::data::Tokenizer> tokenizer;

@@ -345,5 +345,59 @@ class DistributedOptimizer : public optim::Optimizer {
   TensorList shards_;
 };
 
+// Elastic resume: the state of a ZeRO optimizer that `old_states.size()` data-parallel ranks saved, re-cut for
+// rank `new_rank` of a job with `new_dp` data-parallel ranks (same model, same tensor / pipeline coordinates).
+// A saved state holds, per family of keys "<prefix>.<k>" (adam.m, adam.v), rank r's contiguous 1/dp slice of
+// flat bucket k; the bucket layout depends on dp (bucket ends are padded to lcm(dp, 128)), so the slices are
+// put back into the old flat layout, moved parameter by parameter into the new one and cut again.  Keys without
+// a bucket index (adam.t) are taken from the first rank.  `chunk_numels[c]` lists the parameter sizes of the
+// c-th wrapped module chunk in the order its ParamAndGradBuffer was built from.  The reference resumes only on
+// the topology that saved (checkpoint_manager.cc:56-63).
+inline std::map<std::string, Tensor> ReshardZeroState(const std::vector<std::map<std::string, Tensor>>& old_states,
+                                                      const std::vector<std::vector<int64_t>>& chunk_numels, int new_dp, int new_rank,
+                                                      int64_t bucket_elems = 1000000, bool pad_busbw = false) {
+  TORCH_CHECK(!old_states.empty() && new_dp >= 1 && new_rank >= 0 && new_rank < new_dp, "ReshardZeroState: bad arguments");
+  const int old_dp = static_cast<int>(old_states.size());
+  std::map<std::string, Tensor> out;
+  std::set<std::string> families;
+  for (const auto& [key, t] : old_states[0]) {
+    const size_t dot = key.rfind('.');
+    const bool indexed = dot != std::string::npos && dot + 1 < key.size() &&
+                         key.find_first_not_of("0123456789", dot + 1) == std::string::npos;
+    if (indexed) families.insert(key.substr(0, dot));
+    else out[key] = t.clone();
+  }
+  for (const auto& family : families) {
+    size_t k_old = 0, k_new = 0;
+    for (const auto& numels : chunk_numels) {
+      const FlatLayoutResult lo = PlanFlatLayout(numels, old_dp, true, bucket_elems, pad_busbw);
+      const FlatLayoutResult ln = PlanFlatLayout(numels, new_dp, true, bucket_elems, pad_busbw);
+      Tensor flat_old, flat_new;
+      for (size_t b = 0; b < lo.bucket_start.size(); ++b) {
+        const int64_t n = (lo.bucket_end[b] - lo.bucket_start[b]) / old_dp;
+        for (int r = 0; r < old_dp; ++r) {
+          auto it = old_states[r].find(family + "." + std::to_string(k_old + b));
+          TORCH_CHECK(it != old_states[r].end(), "ReshardZeroState: rank ", r, " has no ", family, ".", k_old + b);
+          TORCH_CHECK(it->second.numel() == n, "ReshardZeroState: ", family, ".", k_old + b, " of rank ", r, " holds ", it->second.numel(),
+                      " elements, the layout of ", old_dp, " ranks gives ", n, " (was the checkpoint written by another model?)");
+          if (!flat_old.defined()) {
+            flat_old = torch::zeros({lo.numel}, it->second.options().device(torch::kCPU));
+            flat_new = torch::zeros({ln.numel}, flat_old.options());
+          }
+          flat_old.narrow(0, lo.bucket_start[b] + r * n, n).copy_(it->second.view({-1}));
+        }
+      }
+      for (size_t i = 0; i < numels.size(); ++i)
+        flat_new.narrow(0, ln.param_start[i], numels[i]).copy_(flat_old.narrow(0, lo.param_start[i], numels[i]));
+      for (size_t b = 0; b < ln.bucket_start.size(); ++b) {
+        const int64_t n = (ln.bucket_end[b] - ln.bucket_start[b]) / new_dp;
+        out[family + "." + std::to_string(k_new + b)] = flat_new.narrow(0, ln.bucket_start[b] + new_rank * n, n).clone();
+      }
+      k_old += lo.bucket_start.size(), k_new += ln.bucket_start.size();
+    }
+  }
+  return out;
+}
+
 }  // namespace parallel
 }  // namespace itb

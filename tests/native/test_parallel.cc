@@ -122,6 +122,55 @@ ITB_TEST(ProcessGroup, AbortEndsAWaitForAPeerThatIsGone) {
   EXPECT_THROWS(pg->Barrier());
 }
 
+// The slices that `dp` ranks hold of a per-parameter state, cut directly from the flat layout of that size.
+static std::vector<std::map<std::string, Tensor>> ShardedState(const std::vector<std::vector<Tensor>>& chunks, int dp, int64_t bucket_elems) {
+  std::vector<std::map<std::string, Tensor>> out(dp);
+  size_t k = 0;
+  for (const auto& values : chunks) {
+    std::vector<int64_t> numels;
+    for (const auto& v : values) numels.push_back(v.numel());
+    auto lay = itb::PlanFlatLayout(numels, dp, true, bucket_elems, false);
+    Tensor flat = torch::zeros({lay.numel});
+    for (size_t i = 0; i < values.size(); ++i) flat.narrow(0, lay.param_start[i], numels[i]).copy_(values[i].view({-1}));
+    for (size_t b = 0; b < lay.bucket_start.size(); ++b, ++k) {
+      const int64_t n = (lay.bucket_end[b] - lay.bucket_start[b]) / dp;
+      for (int r = 0; r < dp; ++r) {
+        out[r]["adam.m." + std::to_string(k)] = flat.narrow(0, lay.bucket_start[b] + r * n, n).clone();
+        out[r]["adam.v." + std::to_string(k)] = flat.narrow(0, lay.bucket_start[b] + r * n, n).clone() * 2;
+        out[r]["adam.t"] = torch::tensor(static_cast<int64_t>(17), torch::kInt64);
+      }
+    }
+  }
+  return out;
+}
+
+ITB_TEST(ZeroReshard, StateOfOneDataParallelSizeRecutForAnotherEqualsCuttingItDirectly) {
+  // two module chunks, several buckets each (buckets close at 300 elements), sizes that need padding
+  std::vector<std::vector<Tensor>> chunks(2);
+  int64_t seed = 0;
+  for (int64_t n : {130, 257, 64, 301, 7, 190}) chunks[0].push_back(torch::arange(n, torch::kFloat32) + 1000.0f * static_cast<float>(++seed));
+  for (int64_t n : {512, 33, 95}) chunks[1].push_back(torch::arange(n, torch::kFloat32) + 1000.0f * static_cast<float>(++seed));
+  std::vector<std::vector<int64_t>> numels(2);
+  for (int c = 0; c < 2; ++c)
+    for (const auto& v : chunks[c]) numels[c].push_back(v.numel());
+  for (auto [old_dp, new_dp] : std::vector<std::pair<int, int>>{{4, 2}, {2, 4}, {3, 8}, {8, 1}, {1, 3}}) {
+    auto old_states = ShardedState(chunks, old_dp, 300);
+    auto want = ShardedState(chunks, new_dp, 300);
+    for (int r = 0; r < new_dp; ++r) {
+      auto got = par::ReshardZeroState(old_states, numels, new_dp, r, 300);
+      EXPECT(got.size() == want[r].size());
+      for (const auto& [key, t] : want[r]) {
+        EXPECT(got.count(key) == 1);
+        EXPECT(got.at(key).sizes() == t.sizes() && torch::equal(got.at(key), t));
+      }
+    }
+  }
+  // a state written for another model is refused with the size that was expected
+  auto other = ShardedState(chunks, 2, 300);
+  numels[0][0] += 1000;
+  EXPECT_THROWS(par::ReshardZeroState(other, numels, 4, 0, 300));
+}
+
 ITB_TEST(Layout3D, TensorParallelRanksAreAdjacentThenDataThenPipeline) {
   par::Layout l;
   l.tp = 2, l.dp = 2, l.pp = 2;

@@ -302,3 +302,35 @@ def test_survivors_of_a_failed_rank_stop_with_a_report_instead_of_waiting(binari
 def test_heartbeats_cost_nothing_visible_and_an_unarmed_injector_does_nothing(binaries, files, single):
     losses, _ = _train(binaries, files, "llama3", 2, *LLAMA, "--tensor_parallel", "2", "--heartbeat_timeout", "30")
     assert max(abs(a - b) for a, b in zip(losses, single["llama3"])) <= 2e-5
+
+
+@pytest.mark.parametrize("old_ranks,new_ranks,flags", [(4, 2, ("--zero_stage", "1")), (2, 4, ("--zero_stage", "2")),
+                                                       (4, 8, ("--zero_stage", "1", "--tensor_parallel", "2"))],
+                         ids=["zero1_4_to_2", "zero2_2_to_4", "tp2_zero1_dp2_to_dp4"])
+def test_elastic_resume_recuts_the_zero_state_for_another_data_parallel_size(binaries, files, tmp_path, old_ranks, new_ranks, flags):
+    """--elastic_resume: a ZeRO checkpoint of one data-parallel size continues on another.  The global batch
+    of a step is the same token range for both sizes, so the resumed run must follow the uninterrupted one."""
+    launcher, trainer = binaries
+
+    def run(ranks, iters, *extra):
+        cmd = [launcher, f"--nproc_per_node={ranks}", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", trainer, "--family", "llama3",
+               "--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin", "--batch_size", "2",
+               "--sequence_length", "64", "--total_batch_size", "1024", "--num_iteration", str(iters), "--dtype", "float32", *LLAMA,
+               *flags, *extra]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=files, env=ENV)
+        return r.returncode, r.stdout + r.stderr
+
+    rc, log = run(old_ranks, 5)
+    assert rc == 0, log[-3000:]
+    full = _losses(log)
+    rc, log = run(old_ranks, 3, "--save", str(tmp_path), "--save_interval", "3")
+    assert rc == 0, log[-3000:]
+    ckpt = tmp_path / "checkpoint_step_000003"
+    assert len(list(ckpt.iterdir())) == old_ranks
+    rc, log = run(new_ranks, 5, "--load", str(ckpt))                       # without the flag: refused, with the reason
+    assert rc != 0 and "--elastic_resume accepts another data-parallel size" in log, log[-2000:]
+    rc, log = run(new_ranks, 5, "--load", str(ckpt), "--elastic_resume")
+    assert rc == 0, log[-3000:]
+    resumed = _losses(log)
+    assert "elastic resume: ZeRO optimizer state" in log
+    assert len(resumed) == 2 and max(abs(a - b) for a, b in zip(resumed, full[3:])) <= 2e-5, (resumed, full)
