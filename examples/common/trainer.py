@@ -94,8 +94,8 @@ def build_parser(family: str) -> argparse.ArgumentParser:
     a("--vocab_size", type=int, default=0)
     a("--metrics_jsonl", default="", help="append one JSON record per step to this file (last rank)")
     a("--elastic_resume", action="store_true",
-      help="allow --load to resume a pure data-parallel checkpoint on a different number of ranks "
-           "(ZeRO optimizer state is re-sharded)")
+      help="allow --load to resume a checkpoint on a different number of data-parallel ranks, under the same "
+           "tensor / pipeline layout (ZeRO optimizer state is re-sharded)")
     a("--heartbeat_timeout", type=float, default=0.0,
       help="seconds without a peer's step heartbeat before the run stops with exit code 75 (0 = off); "
            "ITB_FAULT=<rank>:<step>:<raise|exit|stall|mute> injects a host-side fault")

@@ -6,8 +6,8 @@ A checkpoint directory holds ``model.ckpt``, ``optimizer.ckpt`` (optional) and
 ``rank_%06d``.  State-dict files use the reference's layout (magic 0x54504B43, version 1) and are
 written by the native runtime through a temporary file + rename.  ``trainer_state.json`` is valid JSON
 here (the reference omits a comma); the reader accepts both.  Resume validates the model shape and
-the (ddp, tp, sp, pp) topology; ``allow_dp_resize`` relaxes the data-parallel check for model-only
-restores.
+the (ddp, tp, sp, pp) topology; ``allow_dp_resize`` lets the data-parallel size differ (ZeRO optimizer
+state is re-sharded), under the same tensor / pipeline layout.
 """
 from __future__ import annotations
 
@@ -147,9 +147,10 @@ def SaveCheckpoint(checkpoint_root_dir: str, global_step: int, model, optimizer,
 
 
 def _resume_on_other_dp_size(resume_root: str, old_ranks, model, optimizer, load_optimizer_state: bool):
-    """Pure data parallelism saved by ``len(old_ranks)`` ranks, resumed by a different number: the
-    weights are replicated (any rank's file will do); ZeRO optimizer state is re-sharded from all the
-    old ranks' files (:mod:`reshard`), replicated optimizer state is taken from rank 0."""
+    """A data-parallel group saved by the ``len(old_ranks)`` ranks listed (the ranks that share this
+    rank's tensor / pipeline coordinates), resumed by a different number: the weights are replicated
+    over the group (the first rank's file will do); ZeRO optimizer state is re-sharded from all the old
+    ranks' files (:mod:`reshard`), replicated optimizer state is taken from the first."""
     from .reshard import reshard_zero_optimizer_state
 
     first = os.path.join(resume_root, old_ranks[0])
@@ -191,15 +192,28 @@ def ResumeFromCheckpoint(resume_root: str, model, optimizer, model_config, load_
     d = resume_root
     rd = os.path.join(resume_root, f"rank_{rank:06d}")
     old_ranks = sorted(x for x in os.listdir(resume_root) if x.startswith("rank_")) if os.path.isdir(resume_root) else []
-    if (allow_dp_resize and old_ranks and genv.GetTensorParallelSize() == 1 and genv.GetPipelineParallelSize() == 1
-            and len(old_ranks) != genv.GetWorldSize()):
-        st = _resume_on_other_dp_size(resume_root, old_ranks, model, optimizer, load_optimizer_state)
+    tp, pp = genv.GetTensorParallelSize(), genv.GetPipelineParallelSize()
+    if allow_dp_resize and old_ranks and len(old_ranks) != genv.GetWorldSize() and len(old_ranks) % (tp * pp) == 0:
+        # another data-parallel size under the same tensor / pipeline layout: the ranks that held this rank's
+        # (tp, pp) coordinates in the old job, by their data-parallel rank (TP fastest, then DP, then PP)
+        old_dp = len(old_ranks) // (tp * pp)
+        _, tp_rank, pp_rank = genv.GetCoordOf(rank)
+        mine = [f"rank_{tp_rank + tp * (d + old_dp * pp_rank):06d}" for d in range(old_dp)]
+        absent = [m for m in mine if m not in old_ranks]
+        if absent:
+            raise FileNotFoundError(f"{resume_root} has no {absent[0]}: was it written with TP={tp}, PP={pp}?")
+        head = Checkpoint.LoadTrainerState(os.path.join(resume_root, mine[0], "trainer_state.json"))
+        for k, cur in (("tp_size", tp), ("sp_size", genv.GetSequenceParallelSize()), ("pp_size", pp)):
+            if getattr(head, k) != cur:
+                raise ValueError(f"{k.upper()} mismatch: checkpoint has {getattr(head, k)}, but current run has {cur} "
+                                 "(only the data-parallel size may change)")
+        st = _resume_on_other_dp_size(resume_root, mine, model, optimizer, load_optimizer_state)
         for k in ("n_layer", "n_head", "n_kv_head", "n_embd", "vocab_size"):
             if getattr(st, k) != getattr(model_config, k):
                 raise ValueError(f"{k} mismatch: ckpt={getattr(st, k)}, config={getattr(model_config, k)}")
         # a rank consumes 1/dp of the batches: keep the position in the token stream
         res.global_step, res.last_lr = st.global_step, st.last_lr
-        res.consumed_batches = max(st.consumed_batches, 0) * len(old_ranks) // max(genv.GetWorldSize(), 1)
+        res.consumed_batches = max(st.consumed_batches, 0) * old_dp // max(genv.GetDataParallelSize(), 1)
         return res
     if genv.GetWorldSize() > 1 and os.path.isdir(rd):
         d = rd

@@ -115,6 +115,32 @@ def test_elastic_resume_on_fewer_ranks(tmp_path):
     assert r.returncode != 0
 
 
+def test_elastic_resume_under_tensor_parallelism_follows_the_uninterrupted_run(tmp_path):
+    """TP2 x DP2 with ZeRO-1 saves after step 2; TP2 x DP4 resumes with --elastic_resume.  A step's global
+    batch is the same token range under both sizes, so steps 3 and 4 must repeat the uninterrupted run's."""
+    import torch
+
+    from infinitrain_b200.data import write_token_file
+
+    g = torch.Generator().manual_seed(3)
+    write_token_file(str(tmp_path / "tokens.bin"), torch.randint(0, 512, (2 * 32 * 80 + 1,), generator=g).tolist(), llama3=True)
+    common = [sys.executable, "examples/llama3/main.py", "--device", "cpu", "--n_layer", "2", "--n_embd", "64", "--n_head", "4",
+              "--n_kv_head", "2", "--vocab_size", "512", "--batch_size", "2", "--sequence_length", "32", "--model", "llama3-1b",
+              "--input_bin", str(tmp_path / "tokens.bin"), "--learning_rate", "1e-2", "--zero_stage", "1", "--tensor_parallel", "2",
+              "--save_optimizer_state", "--total_batch_size", "512"]
+
+    def run(ranks, port, *extra):
+        return _losses(_run([_launcher(), f"--nproc_per_node={ranks}", f"--rdzv_endpoint=127.0.0.1:{port}", "--", *common, *extra],
+                            timeout=900))
+
+    full = run(4, 29931, "--num_iteration", "4")
+    first = run(4, 29932, "--num_iteration", "2", "--save", str(tmp_path / "ck"), "--save_interval", "2")
+    ckpt = os.path.join(tmp_path, "ck", "checkpoint_step_000002")
+    assert first == full[:2] and len(os.listdir(ckpt)) == 4
+    resumed = run(8, 29933, "--num_iteration", "4", "--load", ckpt, "--elastic_resume")
+    assert len(resumed) == 2 and max(abs(a - b) for a, b in zip(resumed, full[2:])) <= 2e-5, (resumed, full)
+
+
 def test_run_matrix_and_compare(tmp_path):
     """The configuration-matrix runner writes one log per run; comparing a matrix against itself
     passes (same seeds, deterministic CPU math)."""
