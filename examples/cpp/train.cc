@@ -13,7 +13,7 @@
 //             [--overfit_single_batch] [--input_val_bin F --val_loss_every N --val_max_batches M] [--sample_every N]
 //             [--heartbeat_timeout S]   step heartbeats through the job's store and a watchdog thread: when a peer is
 //                           silent for S seconds, or asks for an abort, the process groups are aborted and the rank
-//                           ends with exit code 3 instead of waiting inside a collective (0 = off, the default);
+//                           ends with exit code 75 instead of waiting inside a collective (0 = off, the default);
 //                           ITB_FAULT="<rank>:<step>:raise|exit|stall|mute[:arg]" injects a host-side fault
 //             [--profile]   per-op / per-collective records, written as <family>.report.rank<r>,
 //                           <family>.records.log.rank<r> and <family>.trace.rank<r>.json (Chrome trace) into
@@ -287,7 +287,7 @@ int main(int argc, char** argv) {
   auto rank_failed = [&](const std::string& why) {
     std::fprintf(stderr, "[E] rank %d stops: %s\n", env.rank, why.c_str());
     std::fflush(stderr);
-    std::_Exit(3);   // peers are gone: no ordered shutdown, no collective in a destructor
+    std::_Exit(75);   // EX_TEMPFAIL, as the Python trainer; peers are gone: no ordered shutdown, no collective in a destructor
   };
   for (int64_t step = start_step; step < iters; ++step) {
     injector.MaybeFire(step + 1);

@@ -268,7 +268,7 @@ def _start_ranks(trainer, files, world, extra, env_extra, iters=6):
 def test_survivors_of_a_failed_rank_stop_with_a_report_instead_of_waiting(binaries, files, kind, flags):
     """--heartbeat_timeout: rank 1 leaves, falls silent or stalls at step 3 (host-side injection, between
     steps).  Rank 0 sits in a collective that will never complete; its watchdog sees the stale heartbeat,
-    aborts the process groups and the rank ends with exit code 3 and a report, within seconds."""
+    aborts the process groups and the rank ends with exit code 75 and a report, within seconds."""
     import time
 
     _, trainer = binaries
@@ -286,9 +286,9 @@ def test_survivors_of_a_failed_rank_stop_with_a_report_instead_of_waiting(binari
     elapsed = time.time() - t0
     if kind == "mute":
         # the muted rank keeps training; the watchdog of rank 0 cannot tell it from a dead one and stops the job
-        assert procs[0].returncode == 3 and "stale_heartbeat" in out0, out0[-2000:]
+        assert procs[0].returncode == 75 and "stale_heartbeat" in out0, out0[-2000:]
     else:
-        assert procs[0].returncode == 3, (procs[0].returncode, out0[-2000:])
+        assert procs[0].returncode == 75, (procs[0].returncode, out0[-2000:])
         # a rank that waits inside a collective does not beat either: the stalled rank's own watchdog may be the
         # first to call the abort, and rank 0 then reports that request
         want = "rank 0 stops: rank 1: stale_heartbeat" if kind == "exit" else "rank 0 stops: rank 1: "
