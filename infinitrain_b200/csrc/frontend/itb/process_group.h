@@ -105,6 +105,55 @@ class ProcessGroup {
   // ranks match in list order.
   virtual std::shared_ptr<Work> BatchSendRecv(std::vector<P2POp>& ops, bool async_op = false) = 0;
   virtual void Barrier() = 0;
+
+  // ---- rooted collectives (reference: src/nn/parallel/process_group.cc:251-401, the legacy DataParallel's
+  // transport), built from the calls above so that every transport has them; NCCL overrides Reduce.
+  // The reduction of every rank's `t` lands in `t` on dst; the other ranks' tensors keep their values.
+  virtual std::shared_ptr<Work> Reduce(Tensor& t, int dst_group_rank, ReduceOp op = ReduceOp::kSum, bool async_op = false) {
+    Tensor tmp = t.clone();
+    auto w = AllReduce(tmp, op, false);
+    if (rank() == dst_group_rank) t.copy_(tmp);
+    (void)async_op;
+    return w;
+  }
+  // Sums every tensor of the list onto dst, one reduction per tensor.
+  void ReduceAddCoalesced(TensorList& ts, int dst_group_rank) {
+    for (Tensor& t : ts) Reduce(t, dst_group_rank, ReduceOp::kSum, false);
+  }
+  // out = chunk rank() of src's `in` split along `dim` into size() equal parts; `in` is read on src only.
+  void Scatter(Tensor& out, const Tensor& in, int src_group_rank, int64_t dim = 0) {
+    std::vector<P2POp> ops;
+    TensorList chunks;
+    if (rank() == src_group_rank) {
+      TORCH_CHECK(in.size(dim) % size() == 0, "Scatter: dimension ", dim, " of size ", in.size(dim), " does not split over ", size(), " ranks");
+      for (auto& c : in.chunk(size(), dim)) chunks.push_back(c.contiguous());
+      for (int r = 0; r < size(); ++r) {
+        if (r == rank()) out.copy_(chunks[r]);
+        else ops.push_back(P2POp{true, chunks[r], r});
+      }
+    } else {
+      TORCH_CHECK(out.is_contiguous(), "Scatter: contiguous output required");
+      ops.push_back(P2POp{false, out, src_group_rank});
+    }
+    if (!ops.empty()) BatchSendRecv(ops, false);
+  }
+  // On dst: the concatenation of every rank's `t` along `dim`, by group rank; an undefined tensor elsewhere.
+  Tensor Gather(const Tensor& t, int dst_group_rank, int64_t dim = 0) {
+    std::vector<P2POp> ops;
+    Tensor mine = t.contiguous();
+    if (rank() != dst_group_rank) {
+      ops.push_back(P2POp{true, mine, dst_group_rank});
+      BatchSendRecv(ops, false);
+      return Tensor();
+    }
+    TensorList parts(size());
+    for (int r = 0; r < size(); ++r) {
+      parts[r] = r == rank() ? mine : torch::empty_like(mine);
+      if (r != rank()) ops.push_back(P2POp{false, parts[r], r});
+    }
+    if (!ops.empty()) BatchSendRecv(ops, false);
+    return torch::cat(parts, dim);
+  }
   // 0 = healthy; a transport error code otherwise (NCCL: the communicator's asynchronous error).
   virtual int AsyncError() { return 0; }
   // Failure handling (fault_tolerance.h).  Abort() may be called from another thread than the one inside a
@@ -360,6 +409,11 @@ class NcclProcessGroup : public ProcessGroup {
   std::shared_ptr<Work> BroadCast(Tensor& t, int src, bool async_op) override {
     return Run(async_op, {t}, [&](cudaStream_t s) {
       return ncclBroadcast(t.data_ptr(), t.data_ptr(), t.nbytes(), ncclChar, src, comm_, s);
+    });
+  }
+  std::shared_ptr<Work> Reduce(Tensor& t, int dst, ReduceOp op, bool async_op) override {
+    return Run(async_op, {t}, [&](cudaStream_t s) {
+      return ncclReduce(t.data_ptr(), t.data_ptr(), t.numel(), Dtype(t), Op(op), dst, comm_, s);
     });
   }
   std::shared_ptr<Work> Send(const TensorList& ts, int dst, bool async_op) override {

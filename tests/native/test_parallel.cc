@@ -250,6 +250,26 @@ ITB_TEST(StoreGroup, CollectivesAndPointToPoint) {
   });
 }
 
+ITB_TEST(StoreGroup, RootedCollectivesReduceScatterGather) {
+  run_ranks(4, [](int rank, std::shared_ptr<par::ProcessGroup> pg) {
+    // Reduce: the sum lands on rank 2 only
+    Tensor t = torch::full({3}, static_cast<float>(rank + 1));
+    pg->Reduce(t, 2, par::ReduceOp::kSum, false);
+    EXPECT(t[0].item<float>() == (rank == 2 ? 10.0f : static_cast<float>(rank + 1)));
+    TensorList pair = {torch::full({2}, 1.0f), torch::full({1}, static_cast<float>(rank))};
+    pg->ReduceAddCoalesced(pair, 0);
+    if (rank == 0) EXPECT(pair[0][0].item<float>() == 4.0f && pair[1][0].item<float>() == 6.0f);
+    // Scatter from rank 1 along dimension 1, then Gather the pieces back on rank 3 along the same dimension
+    Tensor full = rank == 1 ? torch::arange(24, torch::kFloat32).view({3, 8}) : Tensor();
+    Tensor piece = torch::empty({3, 2});
+    pg->Scatter(piece, rank == 1 ? full : torch::empty({0}), 1, 1);
+    EXPECT(torch::equal(piece, torch::arange(24, torch::kFloat32).view({3, 8}).slice(1, 2 * rank, 2 * rank + 2)));
+    Tensor back = pg->Gather(piece, 3, 1);
+    if (rank == 3) EXPECT(torch::equal(back, torch::arange(24, torch::kFloat32).view({3, 8})));
+    else EXPECT(!back.defined());
+  });
+}
+
 ITB_TEST(StoreGroup, RanksThatDisagreeOnASizeGetAnErrorNotAHang) {
   bool threw = false;
   try {
