@@ -8,6 +8,7 @@
 // (src/nn/modules/transformer/mlp.cc:84-90), interleaved-pair RoPE
 // (src/nn/modules/transformer/utils.cc:9-29), mean cross-entropy (src/kernels/cpu/cross_entropy.cc:17-98).
 #pragma once
+#include <functional>
 #include <cmath>
 
 #include "module.h"
@@ -39,6 +40,38 @@ class AutocastGuard {
 
 namespace ops {
 
+// Function-level observation (the precision checker's level 2): when a hook is installed, every op below
+// reports its tensor arguments and its result once per call; an op that calls another op reports for itself only.
+using FunctionHook = std::function<void(const char* name, const TensorList& inputs, const Tensor& output)>;
+inline FunctionHook& function_hook() {
+  static FunctionHook h;
+  return h;
+}
+inline bool& inside_function_hook() {
+  static thread_local bool inside = false;
+  return inside;
+}
+inline bool function_hook_wanted() { return static_cast<bool>(function_hook()) && !inside_function_hook(); }
+struct FunctionHookScope {
+  FunctionHookScope() { inside_function_hook() = true; }
+  ~FunctionHookScope() { inside_function_hook() = false; }
+};
+inline Tensor report_function(const char* name, const TensorList& inputs, const Tensor& output) {
+  function_hook()(name, inputs, output);
+  return output;
+}
+inline Tensor or_undefined(const c10::optional<Tensor>& t) { return t.has_value() ? *t : Tensor(); }
+// Runs `call` with the hook off and reports (name, inputs, result).
+#define ITB_FUNCTION_HOOK(name, inputs, call)                                  \
+  if (::itb::ops::function_hook_wanted()) {                                     \
+    ::itb::Tensor itb_hook_out;                                                 \
+    {                                                                           \
+      ::itb::ops::FunctionHookScope itb_hook_scope;                             \
+      itb_hook_out = (call);                                                    \
+    }                                                                           \
+    return ::itb::ops::report_function(name, inputs, itb_hook_out);            \
+  }
+
 inline bool use_fused(const Tensor& x) {
 #ifdef ITB_WITH_CUDA
   return x.is_cuda() && (x.scalar_type() == torch::kBFloat16 ||
@@ -67,6 +100,7 @@ inline Tensor new_gelu(const Tensor& x) {
 // y = x W^T (+ bias) (+ gelu) (+ residual)
 inline Tensor linear(const Tensor& x, const Tensor& weight, const c10::optional<Tensor>& bias = c10::nullopt,
                      const c10::optional<Tensor>& residual = c10::nullopt, bool gelu = false) {
+  ITB_FUNCTION_HOOK("Linear", (TensorList{x, weight, or_undefined(bias), or_undefined(residual)}), ::itb::ops::linear(x, weight, bias, residual, gelu));
   ITB_PROFILE("linear", x);
 #ifdef ITB_WITH_CUDA
   if (use_fused(x) && x.size(-1) % 8 == 0 && weight.is_cuda()) return fused::linear(x, weight, bias, residual, gelu);
@@ -86,6 +120,7 @@ inline Tensor linear(const Tensor& x, const Tensor& weight, const c10::optional<
 }
 
 inline Tensor layernorm(const Tensor& x, const Tensor& gamma, const c10::optional<Tensor>& beta, double eps = 1e-5) {
+  ITB_FUNCTION_HOOK("LayerNorm", (TensorList{x, gamma, or_undefined(beta)}), ::itb::ops::layernorm(x, gamma, beta, eps));
   ITB_PROFILE("layernorm", x);
 #ifdef ITB_WITH_CUDA
   if (x.is_cuda() && gamma.scalar_type() == torch::kFloat32 && x.size(-1) % 8 == 0 && x.size(-1) <= 6144)
@@ -100,6 +135,7 @@ inline Tensor layernorm(const Tensor& x, const Tensor& gamma, const c10::optiona
 }
 
 inline Tensor rmsnorm(const Tensor& x, const Tensor& gamma, double eps = 1e-6) {
+  ITB_FUNCTION_HOOK("RMSNorm", (TensorList{x, gamma}), ::itb::ops::rmsnorm(x, gamma, eps));
   ITB_PROFILE("rmsnorm", x);
 #ifdef ITB_WITH_CUDA
   if (x.is_cuda() && gamma.scalar_type() == torch::kFloat32 && x.size(-1) % 8 == 0 && x.size(-1) <= 6144)
@@ -110,6 +146,7 @@ inline Tensor rmsnorm(const Tensor& x, const Tensor& gamma, double eps = 1e-6) {
 }
 
 inline Tensor gelu(const Tensor& x) {
+  ITB_FUNCTION_HOOK("Gelu", (TensorList{x}), ::itb::ops::gelu(x));
   ITB_PROFILE("gelu", x);
 #ifdef ITB_WITH_CUDA
   if (x.is_cuda() && (x.scalar_type() == torch::kFloat32 || x.scalar_type() == torch::kBFloat16))
@@ -119,6 +156,7 @@ inline Tensor gelu(const Tensor& x) {
 }
 
 inline Tensor swiglu(const Tensor& a, const Tensor& b) {
+  ITB_FUNCTION_HOOK("SwiGLU", (TensorList{a, b}), ::itb::ops::swiglu(a, b));
   ITB_PROFILE("swiglu", a);
 #ifdef ITB_WITH_CUDA
   if (a.is_cuda() && a.size(-1) % 8 == 0 && (a.scalar_type() == torch::kFloat32 || a.scalar_type() == torch::kBFloat16))
@@ -152,6 +190,7 @@ inline Tensor apply_rope(const Tensor& x, const Tensor& freqs, int64_t pos0 = 0)
 inline Tensor attention_packed(const Tensor& qkv, int64_t H, int64_t KV, int64_t D,
                                const c10::optional<Tensor>& freqs = c10::nullopt, int64_t pos0 = 0,
                                bool causal = true) {
+  ITB_FUNCTION_HOOK("Attention", (TensorList{qkv}), ::itb::ops::attention_packed(qkv, H, KV, D, freqs, pos0, causal));
   ITB_PROFILE("attention_packed", qkv);
 #ifdef ITB_WITH_CUDA
   if (qkv.is_cuda() && (D == 64 || D == 128) && use_fused(qkv))
@@ -182,6 +221,7 @@ inline Tensor attention_packed(const Tensor& qkv, int64_t H, int64_t KV, int64_t
 // Token (+ position) embedding.
 inline Tensor embedding(const Tensor& idx, const Tensor& wte, const c10::optional<Tensor>& wpe = c10::nullopt,
                         int64_t pos0 = 0) {
+  ITB_FUNCTION_HOOK("Embedding", (TensorList{wte, or_undefined(wpe)}), ::itb::ops::embedding(idx, wte, wpe, pos0));
   ITB_PROFILE("embedding", idx);
 #ifdef ITB_WITH_CUDA
   if (wte.is_cuda() && wte.scalar_type() == torch::kFloat32 && wte.size(1) % 8 == 0 && idx.dim() == 2)
@@ -196,6 +236,7 @@ inline Tensor embedding(const Tensor& idx, const Tensor& wte, const c10::optiona
 // Mean over rows of -log softmax(logits)[target]; targets are class indices as int64 or as uint8 (the
 // reference's loss takes both, src/kernels/cpu/cross_entropy.cc).
 inline Tensor cross_entropy(const Tensor& logits, const Tensor& target_in) {
+  ITB_FUNCTION_HOOK("CrossEntropy", (TensorList{logits}), ::itb::ops::cross_entropy(logits, target_in));
   ITB_PROFILE("cross_entropy", logits);
   const Tensor target = target_in.scalar_type() == torch::kLong ? target_in : target_in.to(torch::kLong);
 #ifdef ITB_WITH_CUDA

@@ -236,6 +236,48 @@ def test_per_module_records_line_up_with_the_reference(trainer, files):
                     r"mean=\S+ \[.*, \.\.\.\] \[NaN:0 Inf:0\]$", cpp_lines[0])
 
 
+def test_md5_records_and_function_level_of_the_cpp_precision_checker(trainer, files):
+    """format=md5 writes the digest of every recorded tensor's fp32 bytes (rounded to multiples of
+    md5_tolerance first, the reference's quantisation); level=2 adds one record per op input, output and
+    output gradient.  The digests are checked against hashlib over the dumped tensors, and against the
+    Python checker's own digest function."""
+    import glob
+    import hashlib
+
+    import numpy as np
+
+    from infinitrain_b200.utils.precision_checker import ComputeMD5
+
+    common = ["--family", "gpt2", "--device", "cpu", "--llmc_filepath", "gpt2.bin", "--input_bin", "tokens16.bin", "--batch_size", "2",
+              "--sequence_length", "64", "--total_batch_size", "128", "--num_iteration", "1", "--dtype", "float32",
+              "--learning_rate", "0.05", "--optimizer", "sgd"]
+    for tag, tol in (("plain", 0.0), ("quantised", 1e-3)):
+        cfg = f"level=2,format=md5,path=pc_md5_{tag},save_tensors=true" + (f",md5_tolerance={tol}" if tol else "")
+        _run([trainer, *common, "--precision_check", cfg], files)
+        (out,) = glob.glob(str(files / f"pc_md5_{tag}" / "*"))
+        lines = open(os.path.join(out, "precision_check_rank_0.log")).read().splitlines()
+        recs = [re.match(r"\[GAS-0\] \[L-0\] (\S+) tensor\[(\d+)\]: dtype=float32 shape=\(([\d,]*)\) md5=([0-9a-f]{32})$", ln) for ln in lines]
+        assert all(recs) and len(recs) > 100, [ln for ln, m in zip(lines, recs) if not m][:3]
+        names = [m.group(1) for m in recs]
+        # modules and functions, forward and backward
+        assert "transformer.h.0.attn.c_attn_forward" in names and "transformer.h.0.attn.c_attn_backward" in names
+        for fn in ("Linear", "LayerNorm", "Attention", "Embedding", "CrossEntropy"):
+            assert f"{fn}Function_forward" in names and any(n.startswith(f"{fn}Function") and n.endswith("_backward") for n in names), fn
+        checked = 0
+        for m in recs:
+            path = os.path.join(out, "rank_0", m.group(1) + ".npy")
+            if m.group(2) != "0" or names.count(m.group(1)) != 1:
+                continue                                   # several tensors of one record share a dump file name
+            a = np.load(path)
+            assert ",".join(str(d) for d in a.shape) == m.group(3)
+            import torch as _t
+            assert ComputeMD5(_t.from_numpy(a), tol) == m.group(4), m.group(1)
+            if not tol:
+                assert hashlib.md5(a.astype(np.float32).tobytes()).hexdigest() == m.group(4)
+            checked += 1
+        assert checked > 40
+
+
 def test_validation_loss_and_single_batch_overfit_match_python_trainer(trainer, files):
     """--input_val_bin / --val_loss_every / --val_max_batches and --overfit_single_batch: the C++ and the
     Python trainer log the same validation losses and the same single-batch trajectory."""
