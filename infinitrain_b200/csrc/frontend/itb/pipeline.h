@@ -86,6 +86,27 @@ class PipelineParallel {
   std::string ScheduleTable() const { return FormatScheduleTable(tasks_, cfg_.num_stages); }
   int64_t exchanges() const { return exchanges_; }
 
+  // One optimizer step on one batch (reference: PipelineParallel::TrainStep -> PipelineSchedule::Step,
+  // pp/pipeline_schedule.cc:275-295): the batch is cut into `num_micro_batches` equal parts along dimension 0
+  // (the input on the first stage, the target on the last; the other stages may pass undefined tensors),
+  // gradients are cleared, the schedule runs, the optimizer steps.  Returns the mean loss on the last stage.
+  double TrainStep(const Tensor& input, const Tensor& target, optim::Optimizer& optimizer, const LossFn& loss_fn,
+                   const BackwardNotice& notice = {}) {
+    const int n = cfg_.num_micro_batches;
+    auto split = [n](const Tensor& t, const char* what) {
+      std::vector<Tensor> parts(n);
+      if (!t.defined()) return parts;
+      TORCH_CHECK(t.size(0) % n == 0, "TrainStep: the ", what, " batch of ", t.size(0), " does not split into ", n, " micro-batches");
+      auto chunks = t.split(t.size(0) / n, 0);
+      for (int i = 0; i < n; ++i) parts[i] = chunks[i];
+      return parts;
+    };
+    optimizer.ZeroGrad();
+    const double loss = StepMicroBatches(split(input, "input"), split(target, "target"), loss_fn, notice);
+    optimizer.Step();
+    return loss;
+  }
+
   // One optimizer step's worth of micro-batches.  `inputs` matter on the first stage, `targets` on the
   // last; returns the mean loss over the micro-batches on the last stage, 0 elsewhere.
   double StepMicroBatches(const std::vector<Tensor>& inputs, const std::vector<Tensor>& targets, const LossFn& loss_fn,

@@ -449,6 +449,57 @@ ITB_TEST(Pipeline, InterleavedTwoStagesTwoChunks) { pipeline_case("1f1b", 2, 2, 
 ITB_TEST(Pipeline, InterleavedFourStagesTwoChunksGpipe) { pipeline_case("gpipe", 4, 2, 3); }
 ITB_TEST(Pipeline, OneStageWithChunksNeedsNoGroup) { pipeline_case("1f1b", 1, 3, 2); }
 
+// TrainStep = split the batch, clear gradients, run the schedule, step the optimizer: two stages trained for
+// three steps end with the weights of the whole stack trained on one rank with the same batches.
+ITB_TEST(Pipeline, TrainStepSplitsTheBatchAndStepsTheOptimizer) {
+  const int S = 2, n = 4;
+  const int64_t width = 8, layers = 4, B = 2;
+  torch::manual_seed(5);
+  Tensor xs = torch::randn({3, n * B, width}), ys = torch::randn({3, n * B, width});
+  auto ref = std::make_shared<Stack>(layers, width);
+  itb::optim::SGD ref_opt(ref->Parameters(), 0.1);
+  std::vector<double> ref_losses;
+  for (int step = 0; step < 3; ++step) {
+    ref_opt.ZeroGrad();
+    double total = 0;
+    for (int m = 0; m < n; ++m) {
+      Tensor l = (ref->forward(xs[step].slice(0, m * B, (m + 1) * B)) - ys[step].slice(0, m * B, (m + 1) * B)).pow(2).mean() / n;
+      total += l.item<double>();
+      l.backward();
+    }
+    ref_losses.push_back(total);
+    ref_opt.Step();
+  }
+  std::vector<double> err(S, 1.0);
+  std::vector<std::vector<double>> losses(S);
+  run_ranks(S, [&](int s, std::shared_ptr<par::ProcessGroup> pg) {
+    auto info = par::GetStageInfo(static_cast<int>(layers), S, s, 1);
+    auto full = std::make_shared<Stack>(layers, width);
+    itb::TensorList mine;
+    for (int i = info.layer_ranges_per_chunk[0].first; i < info.layer_ranges_per_chunk[0].second; ++i)
+      for (auto& p : full->blocks[i]->Parameters()) mine.push_back(p);
+    itb::optim::SGD opt(mine, 0.1);
+    par::PipelineConfig pc;
+    pc.num_stages = S, pc.stage = s, pc.vpp = 1, pc.num_micro_batches = n, pc.schedule = "1f1b";
+    pc.boundary_shape = {B, width};
+    par::PipelineParallel pipe(pc, [&](int64_t ci, const Tensor& in) {
+      Tensor x = in;
+      for (int i = info.layer_ranges_per_chunk[ci].first; i < info.layer_ranges_per_chunk[ci].second; ++i) x = full->blocks[i]->forward(x);
+      return x;
+    }, pg);
+    for (int step = 0; step < 3; ++step)
+      losses[s].push_back(pipe.TrainStep(s == 0 ? xs[step] : Tensor(), s == S - 1 ? ys[step] : Tensor(), opt,
+                                         [](const Tensor& out, const Tensor& y) { return (out - y).pow(2).mean(); }));
+    double e = 0;
+    for (int i = info.layer_ranges_per_chunk[0].first; i < info.layer_ranges_per_chunk[0].second; ++i)
+      e = std::max(e, max_abs_diff(full->blocks[i]->w1, ref->blocks[i]->w1));
+    err[s] = e;
+    if (s == 0) EXPECT_THROWS(pipe.TrainStep(torch::randn({7, width}), Tensor(), opt, [](const Tensor& o, const Tensor&) { return o.sum(); }));
+  });
+  for (int s = 0; s < S; ++s) EXPECT(err[s] < 1e-6);
+  for (int step = 0; step < 3; ++step) EXPECT_NEAR(losses[S - 1][step], ref_losses[step], 1e-6);
+}
+
 ITB_TEST(Pipeline, EveryTensorIsConsumedAfterTheStepThatProducesIt) {
   // the constructor checks the property the step-wise exchange relies on; sweep the planner
   for (const char* kind : {"gpipe", "1f1b"})
