@@ -18,27 +18,64 @@ inline std::mt19937& global_rng() {
 }
 inline void ManualSeed(uint32_t seed) { global_rng().seed(seed); }
 namespace init {
-inline void Uniform(Tensor t, float lo, float hi) {
+// Every draw comes from the global generator unless one is passed (reference: include/nn/init.h:17-54).
+inline void Uniform(Tensor t, float lo = 0.0f, float hi = 1.0f, std::mt19937* generator = nullptr) {
   torch::NoGradGuard g;
+  std::mt19937& rng = generator ? *generator : global_rng();
   auto host = torch::empty(t.sizes(), torch::kFloat32);
   std::uniform_real_distribution<float> d(lo, hi);
   float* p = host.data_ptr<float>();
-  for (int64_t i = 0; i < host.numel(); ++i) p[i] = d(global_rng());
+  for (int64_t i = 0; i < host.numel(); ++i) p[i] = d(rng);
   t.copy_(host);
 }
-inline void Normal(Tensor t, float mean, float std) {
+inline void Normal(Tensor t, float mean = 0.0f, float std = 1.0f, std::mt19937* generator = nullptr) {
   torch::NoGradGuard g;
+  std::mt19937& rng = generator ? *generator : global_rng();
   auto host = torch::empty(t.sizes(), torch::kFloat32);
   std::normal_distribution<float> d(mean, std);
   float* p = host.data_ptr<float>();
-  for (int64_t i = 0; i < host.numel(); ++i) p[i] = d(global_rng());
+  for (int64_t i = 0; i < host.numel(); ++i) p[i] = d(rng);
   t.copy_(host);
 }
-// Kaiming-uniform with a = sqrt(5): bound = 1 / sqrt(fan_in).
-inline void KaimingUniform(Tensor t) {
-  float fan_in = static_cast<float>(t.size(1));
-  float bound = 1.0f / std::sqrt(fan_in);
-  Uniform(t, -bound, bound);
+// (fan_in, fan_out) of a weight [out, in, receptive field...].
+inline std::pair<int64_t, int64_t> CalculateFanInAndFanOut(const Tensor& t) {
+  TORCH_CHECK(t.dim() >= 2, "fan in and fan out need a tensor of at least two dimensions");
+  int64_t receptive = 1;
+  for (int64_t d = 2; d < t.dim(); ++d) receptive *= t.size(d);
+  return {t.size(1) * receptive, t.size(0) * receptive};
+}
+enum class KaimingMode { kFanIn, kFanOut };
+enum class NonLinearityType { kLinear, kConv1D, kConv2D, kConv3D, kConvTransposed1d, kConvTransposed2d, kConvTransposed3d,
+                              kSigmoid, kTanh, kReLU, kLeakyReLU, kSELU };
+// The gain PyTorch and the reference recommend per non-linearity (`param` = the negative slope of a leaky ReLU).
+inline float CalculateGain(NonLinearityType nl, float param = 0.0f) {
+  switch (nl) {
+    case NonLinearityType::kTanh: return 5.0f / 3.0f;
+    case NonLinearityType::kReLU: return std::sqrt(2.0f);
+    case NonLinearityType::kLeakyReLU: return std::sqrt(2.0f / (1.0f + param * param));
+    case NonLinearityType::kSELU: return 0.75f;
+    default: return 1.0f;   // linear, convolutions, sigmoid
+  }
+}
+// U(-bound, bound) with bound = sqrt(3) * gain / sqrt(fan).  The defaults of Linear (a = sqrt(5), fan in, leaky ReLU)
+// give bound = 1 / sqrt(fan_in).
+inline void KaimingUniform(Tensor t, float a = std::sqrt(5.0f), KaimingMode mode = KaimingMode::kFanIn,
+                           NonLinearityType nl = NonLinearityType::kLeakyReLU, std::mt19937* generator = nullptr) {
+  auto fans = CalculateFanInAndFanOut(t);
+  const float fan = static_cast<float>(mode == KaimingMode::kFanIn ? fans.first : fans.second);
+  const float bound = std::sqrt(3.0f) * CalculateGain(nl, a) / std::sqrt(fan);
+  Uniform(t, -bound, bound, generator);
+}
+inline void Ones(Tensor t) {
+  torch::NoGradGuard g;
+  t.fill_(1);
+}
+inline void Zeros(Tensor t) {
+  torch::NoGradGuard g;
+  t.zero_();
+}
+inline Tensor Arange(int64_t start, int64_t end, torch::Dtype dtype = torch::kInt64, torch::Device device = torch::kCPU) {
+  return torch::arange(start, end, torch::TensorOptions().dtype(dtype).device(device));
 }
 }  // namespace init
 

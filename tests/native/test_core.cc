@@ -560,4 +560,35 @@ ITB_TEST(FaultTolerance, ACorruptedCheckpointIsRefusedByTheLoader) {
   EXPECT_THROWS(itb::utils::CorruptFile(dir + "/absent", 0, 4));
 }
 
+ITB_TEST(Init, FansGainsBoundsAndGenerators) {
+  namespace init = itb::nn::init;
+  Tensor w = torch::empty({6, 4, 3});
+  auto fans = init::CalculateFanInAndFanOut(w);
+  EXPECT(fans.first == 12 && fans.second == 18);
+  EXPECT_THROWS(init::CalculateFanInAndFanOut(torch::empty({5})));
+  EXPECT_NEAR(init::CalculateGain(init::NonLinearityType::kLeakyReLU, std::sqrt(5.0f)), std::sqrt(1.0f / 3.0f), 1e-6);
+  EXPECT_NEAR(init::CalculateGain(init::NonLinearityType::kReLU), std::sqrt(2.0f), 1e-6);
+  EXPECT(init::CalculateGain(init::NonLinearityType::kSigmoid) == 1.0f && init::CalculateGain(init::NonLinearityType::kTanh) > 1.6f);
+  // Linear's default: every value inside 1 / sqrt(fan_in), and the range is used
+  Tensor big = torch::empty({64, 100});
+  init::KaimingUniform(big);
+  EXPECT(big.abs().max().item<float>() <= 0.1f + 1e-6f && big.abs().max().item<float>() > 0.09f);
+  init::KaimingUniform(big, 0.0f, init::KaimingMode::kFanOut, init::NonLinearityType::kReLU);
+  const float bound = std::sqrt(3.0f) * std::sqrt(2.0f) / 8.0f;
+  EXPECT(big.abs().max().item<float>() <= bound + 1e-6f && big.abs().max().item<float>() > 0.9f * bound);
+  // a generator of the caller's: the same seed gives the same draws and leaves the global stream alone
+  itb::nn::ManualSeed(99);
+  Tensor g1 = torch::empty({8}), g2 = torch::empty({8}), a = torch::empty({8}), b = torch::empty({8});
+  init::Normal(g1, 0.0f, 1.0f);
+  itb::nn::ManualSeed(99);
+  std::mt19937 own(7), same(7);
+  init::Uniform(a, -1.0f, 1.0f, &own);
+  init::Uniform(b, -1.0f, 1.0f, &same);
+  init::Normal(g2, 0.0f, 1.0f);
+  EXPECT(torch::equal(a, b) && torch::equal(g1, g2));
+  init::Ones(a), init::Zeros(b);
+  EXPECT(a.sum().item<float>() == 8.0f && b.abs().sum().item<float>() == 0.0f);
+  EXPECT(torch::equal(init::Arange(2, 6), torch::tensor({2, 3, 4, 5}, torch::kInt64)));
+}
+
 ITB_TEST_MAIN()
