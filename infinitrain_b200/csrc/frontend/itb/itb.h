@@ -12,7 +12,6 @@
 #include "data_parallel.h"
 #include "datatype.h"
 #include "ddp.h"
-#include "distributed.h"
 #include "fault_tolerance.h"
 #include "functional.h"
 #include "io.h"
