@@ -12,6 +12,9 @@ throughput log, once more with the kernel profiler on (``--profile``; reports go
 then the comparison against an earlier round's logs (``--compare``).  Runs that need more GPUs than the
 machine has are skipped and listed.
 
+``--frontend cpp`` runs the same matrix through the C++ trainer (``examples/cpp/train.cc``), which takes the
+same flags and prints the same step line.
+
 The matrix file is JSON: ``{"common": {flag: value, ...}, "runs": [{"id": "...", "family": "gpt2" |
 "llama3", "nproc": N, "args": {flag: value, ...}}, ...]}``.  A run with ``nproc > 1`` goes through the
 ``infini_run`` launcher (one process per rank).  Flags are the trainers' own (``--help``); a boolean
@@ -41,6 +44,16 @@ def _flags(d):
     return out
 
 
+def _cpp_trainer(cuda: bool) -> str:
+    """Path of the C++ trainer, built when it is missing or older than its sources."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("itb_cpp_build", os.path.join(ROOT, "examples", "cpp", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return str(mod.build(cuda=cuda))
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("matrix")
@@ -52,6 +65,8 @@ def main(argv=None) -> int:
     ap.add_argument("--profile", action="store_true", help="run every configuration a second time with --profile")
     ap.add_argument("--ctest", default="", help="CMake build directory: build it and run its ctest suites first")
     ap.add_argument("--dry-run", action="store_true", help="print the commands without running them")
+    ap.add_argument("--frontend", default="python", choices=["python", "cpp"],
+                    help="cpp: run the matrix through the C++ trainer (examples/cpp/train.cc, built on demand)")
     args = ap.parse_args(argv)
     spec = json.load(open(args.matrix))
     os.makedirs(args.out, exist_ok=True)
@@ -85,7 +100,10 @@ def main(argv=None) -> int:
         flags = dict(spec.get("common", {}))
         flags.update(run.get("args", {}))
         flags.update(pass_flags)
-        cmd = [sys.executable, os.path.join(ROOT, "examples", family, "main.py"), *_flags(flags)]
+        if args.frontend == "cpp":
+            cmd = [_cpp_trainer(on_gpu and not args.dry_run), "--family", family, *_flags(flags)]
+        else:
+            cmd = [sys.executable, os.path.join(ROOT, "examples", family, "main.py"), *_flags(flags)]
         if nproc > 1:
             sys.path.insert(0, ROOT)
             from infinitrain_b200 import _ext
@@ -101,8 +119,12 @@ def main(argv=None) -> int:
         if args.dry_run:
             print(" ".join(cmd), ">", log)
             continue
+        env = dict(os.environ)
+        if not on_gpu and "OMP_NUM_THREADS" not in env:
+            # CPU ranks share the machine's cores: without a cap every rank starts one thread per core
+            env["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // nproc))
         with open(log, "w") as f:
-            r = subprocess.run(cmd, stdout=f, stderr=subprocess.STDOUT, cwd=out_dir if pass_name else ROOT)
+            r = subprocess.run(cmd, stdout=f, stderr=subprocess.STDOUT, cwd=out_dir if pass_name else ROOT, env=env)
         print(f"[{'ok' if r.returncode == 0 else 'FAIL'}] {family}_{run['id']} -> {log}", flush=True)
         if r.returncode != 0:
             failed.append(run["id"])

@@ -5,6 +5,8 @@
 //   itb_train --family gpt2 --llmc_filepath model.bin --input_bin tokens.bin --batch_size 4
 //             --sequence_length 64 --total_batch_size 256 --num_iteration 10 --learning_rate 1e-4
 //             --device cpu|cuda --dtype float32|bfloat16 --optimizer sgd|adam|adamw
+//             (without --llmc_filepath: a from-scratch --model d12|...|llama3-1b|llama3-8b, optionally reshaped by
+//              --n_layer --n_embd --n_head --n_kv_head --vocab_size; without --input_bin: synthetic token ids)
 //             [--lora_rank 8 --lora_alpha 16 --lora_target_modules c_attn,c_proj --lora_load_path F --lora_save_path F]
 //             [--save DIR --save_interval N --save_optimizer_state --max_checkpoint_keep K] [--load DIR/checkpoint_step_000004]
 //             [--elastic_resume]   --load a checkpoint written by another number of data-parallel ranks (ZeRO state is re-cut)
@@ -24,7 +26,9 @@
 #include <cstdio>
 #include <iostream>
 #include <map>
+#include <random>
 #include <string>
+#include <unistd.h>
 #include <thread>
 
 #include "itb/itb.h"
@@ -122,7 +126,13 @@ int main(int argc, char** argv) {
                              : itb::io::LoadLLaMA3FromLLMC(fl.get("llmc_filepath", ""));
   } else {
     auto cfg = from_scratch_config(family, fl.get("model", family == "gpt2" ? "d12" : "llama3-1b"));
+    // a from-scratch model of another shape (smoke runs, the configuration matrix)
     if (fl.kv.count("n_layer")) cfg.n_layer = fl.geti("n_layer", cfg.n_layer);
+    if (fl.kv.count("n_embd")) cfg.n_embd = fl.geti("n_embd", cfg.n_embd);
+    if (fl.kv.count("n_head")) cfg.n_head = cfg.n_kv_head = fl.geti("n_head", cfg.n_head);
+    if (fl.kv.count("n_kv_head")) cfg.n_kv_head = fl.geti("n_kv_head", cfg.n_kv_head);
+    if (fl.kv.count("vocab_size")) cfg.vocab_size = cfg.original_vocab_size = fl.geti("vocab_size", cfg.vocab_size);
+    TORCH_CHECK(cfg.n_embd % cfg.n_head == 0 && cfg.n_head % cfg.n_kv_head == 0, "n_embd / n_head / n_kv_head do not divide");
     model = std::make_shared<itb::nn::TransformerModel>(cfg);
   }
   model->To(device);
@@ -190,7 +200,17 @@ int main(int argc, char** argv) {
     if (env.rank == 0) std::fprintf(stderr, "[I] pipeline schedule (%s)\n%s", pc.schedule.c_str(), pipeline->ScheduleTable().c_str());
   }
 
-  itb::io::TokenLoader loader(fl.get("input_bin", ""), B, T, env.dp_rank, dp);
+  // without --input_bin: uniform random ids from a fixed seed in a token file of this rank's own, removed at the end
+  std::string data_path = fl.get("input_bin", ""), synthetic_path;
+  if (data_path.empty()) {
+    synthetic_path = data_path = "/tmp/itb_synth_" + family + "_" + std::to_string(::getpid()) + "_" + std::to_string(env.rank) + ".bin";
+    std::mt19937 gen(1234);
+    std::uniform_int_distribution<int64_t> draw(0, cfg.original_vocab_size - 1);
+    std::vector<int64_t> ids(static_cast<size_t>(std::max<int64_t>(B * T * (grad_accum * dp * (iters + 2) + 4), 4 * T)));
+    for (auto& id : ids) id = draw(gen);
+    itb::io::WriteTokenFile(data_path, ids, family != "gpt2");
+  }
+  itb::io::TokenLoader loader(data_path, B, T, env.dp_rank, dp);
   int64_t start_step = 0, consumed = 0;
   const bool model_parallel = tp * pp > 1;
   // which ranks hold state nobody else has: every model-parallel slice, and under ZeRO every shard of the optimizer state
@@ -418,6 +438,7 @@ int main(int argc, char** argv) {
   if (lora_rank > 0 && !fl.get("lora_save_path", "").empty() && env.dp_rank == 0 && (env.rank == 0 || model_parallel))
     itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", "") + (model_parallel ? ".rank" + std::to_string(env.rank) : ""));
   ddp.reset();
+  if (!synthetic_path.empty()) std::remove(synthetic_path.c_str());
   par::ProcessGroupFactory::Instance().Shutdown();
   return 0;
 }

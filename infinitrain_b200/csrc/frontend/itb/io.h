@@ -169,6 +169,26 @@ inline std::shared_ptr<nn::TransformerModel> LoadLLaMA3FromLLMC(const std::strin
 // ------------------------------------------------------------------ token files
 // Sequential batches (x, y = x shifted by one token) of an llm.c token file; this data-parallel rank
 // reads batches rank, rank + world, ...  A background thread keeps `depth` batches assembled ahead.
+// Writes an llm.c token file: a 1024-byte header (magic, version, token count as int32), then the ids as
+// uint16 (GPT-2: magic 20240520, version 1) or uint32 (LLaMA-3: magic 20240801, version 7)
+// (reference: example/common/tiny_shakespeare_dataset.cc:27-100 reads exactly this).
+inline void WriteTokenFile(const std::string& path, const std::vector<int64_t>& tokens, bool llama3 = false) {
+  std::ofstream f(path, std::ios::binary);
+  TORCH_CHECK(f.is_open(), "cannot write ", path);
+  int32_t header[256] = {llama3 ? 20240801 : 20240520, llama3 ? 7 : 1, static_cast<int32_t>(tokens.size())};
+  f.write(reinterpret_cast<const char*>(header), sizeof(header));
+  for (int64_t t : tokens) {
+    if (llama3) {
+      const uint32_t v = static_cast<uint32_t>(t);
+      f.write(reinterpret_cast<const char*>(&v), 4);
+    } else {
+      TORCH_CHECK(t >= 0 && t < 65536, "token ", t, " does not fit the 16-bit ids of a GPT-2 token file");
+      const uint16_t v = static_cast<uint16_t>(t);
+      f.write(reinterpret_cast<const char*>(&v), 2);
+    }
+  }
+}
+
 class TokenLoader {
  public:
   TokenLoader(const std::string& path, int64_t batch_size, int64_t sequence_length, int64_t ddp_rank = 0,

@@ -153,6 +153,20 @@ def test_run_matrix_and_compare(tmp_path):
     assert len(_losses(open(a / "llama3_zero1.log").read())) == 3
 
 
+def test_run_matrix_through_the_cpp_trainer(tmp_path):
+    """--frontend cpp: the same matrix file drives the C++ trainer (from-scratch model of the matrix's shape,
+    synthetic tokens); its logs carry the step line the comparison tools read."""
+    out = _run([sys.executable, "examples/common/run_matrix.py", "examples/common/matrix_smoke.json", "--out", str(tmp_path / "dry"),
+                "--frontend", "cpp", "--dry-run"], timeout=900)
+    lines = [ln for ln in out.splitlines() if "itb_train" in ln]
+    assert len(lines) == 4 and all("--family" in ln for ln in lines) and sum("infini_run" in ln for ln in lines) == 2
+    _run([sys.executable, "examples/common/run_matrix.py", "examples/common/matrix_smoke.json", "--out", str(tmp_path / "run"),
+          "--frontend", "cpp", "--only", "1,zero1", "--port", "29790"], timeout=900)
+    assert len(_losses(open(tmp_path / "run" / "gpt2_1.log").read())) == 3
+    zero1 = _losses(open(tmp_path / "run" / "llama3_zero1.log").read())
+    assert len(zero1) == 3 and zero1[-1] < zero1[0]
+
+
 def test_validation_loss_is_logged(tmp_path):
     import torch
 
