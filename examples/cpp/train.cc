@@ -155,13 +155,13 @@ int main(int argc, char** argv) {
     lora::LoRAConfig lc;
     lc.rank = lora_rank, lc.alpha = fl.getd("lora_alpha", 16.0);
     lc.target_modules = lora::ParseLoRATargetModules(fl.get("lora_target_modules", "c_attn,c_proj"));
-    // the adapters' draws must not depend on how many numbers the (layout-dependent) construction of the
-    // base model took from the stream: every layout starts them from the same state
-    itb::nn::ManualSeed(static_cast<uint32_t>(fl.geti("seed", 42)) ^ 0x4C6F5241u);
+    // the adapters' draws must not depend on the layout: every adapter draws from a generator of its own, keyed by
+    // its module's path in the whole model
+    lc.seed = (static_cast<uint32_t>(fl.geti("seed", 42)) ^ 0x4C6F5241u) | 1u;
     lora::GetLoRAModel(model, lc);
     model->To(device);
-    if (!fl.get("lora_load_path", "").empty())
-      lora::LoadLoRAWeights(model, fl.get("lora_load_path", "") + (tp * pp > 1 ? ".rank" + std::to_string(env.rank) : ""));
+    // one adapter file for the whole model: every rank keeps its own rows / columns / layers of it
+    if (!fl.get("lora_load_path", "").empty()) lora::LoadFullLoRAWeights(model, fl.get("lora_load_path", ""));
     std::fprintf(stderr, "[I] %s\n", lora::PrintLoRASummary(model).c_str());
   }
   // ---- data parallelism: the wrapper broadcasts rank 0's parameters and reduces gradients during backward
@@ -434,9 +434,9 @@ int main(int argc, char** argv) {
     prof.ExportChromeTrace(family + ".trace.rank" + std::to_string(env.rank) + ".json");
   }
   if (auto world = par::ProcessGroupFactory::Instance().GetDefaultProcessGroup()) world->Barrier();
-  // adapters of a model-parallel run are this rank's slices: one file per rank
-  if (lora_rank > 0 && !fl.get("lora_save_path", "").empty() && env.dp_rank == 0 && (env.rank == 0 || model_parallel))
-    itb::nn::lora::SaveLoRAWeights(model, fl.get("lora_save_path", "") + (model_parallel ? ".rank" + std::to_string(env.rank) : ""));
+  // the adapters of a model-parallel run are gathered into ONE ordinary adapter file (a collective over every
+  // tensor-parallel and pipeline group), loadable on any layout
+  if (lora_rank > 0 && !fl.get("lora_save_path", "").empty()) itb::nn::lora::SaveFullLoRAWeights(model, fl.get("lora_save_path", ""));
   ddp.reset();
   if (!synthetic_path.empty()) std::remove(synthetic_path.c_str());
   par::ProcessGroupFactory::Instance().Shutdown();

@@ -334,3 +334,66 @@ def test_elastic_resume_recuts_the_zero_state_for_another_data_parallel_size(bin
     resumed = _losses(log)
     assert "elastic resume: ZeRO optimizer state" in log
     assert len(resumed) == 2 and max(abs(a - b) for a, b in zip(resumed, full[3:])) <= 2e-5, (resumed, full)
+
+
+def _read_adapter(path):
+    import struct
+
+    import numpy as np
+
+    raw = open(path, "rb").read()
+    magic, version, count = struct.unpack_from("<III", raw, 0)
+    assert magic == 0x4C4F5241 and version == 1
+    at, out = 12, {}
+    for _ in range(count):
+        (n,) = struct.unpack_from("<I", raw, at)
+        name = raw[at + 4:at + 4 + n].decode()
+        at += 4 + n
+        (ndim,) = struct.unpack_from("<I", raw, at)
+        dims = struct.unpack_from(f"<{ndim}q", raw, at + 4)
+        at += 4 + 8 * ndim
+        size = int(np.prod(dims)) if ndim else 1
+        out[name] = np.frombuffer(raw, dtype="<f4", count=size, offset=at).reshape(dims)
+        at += 4 * size
+    assert at == len(raw)
+    return out
+
+
+def test_one_adapter_file_whatever_the_layout_that_trained_it(binaries, files, tmp_path):
+    """--lora_save_path under tensor + pipeline parallelism writes ONE ordinary adapter file (sharded factors
+    joined, the fused QKV rows back in Q | K | V order, global layer numbers); it equals the file of the
+    one-rank run, and either file loads on either layout and in the Python trainer."""
+    import sys
+
+    import numpy as np
+
+    lora = (*LLAMA, "--lora_rank", "4", "--lora_alpha", "8", "--lora_target_modules", "c_attn,c_proj,c_fc,c_fc2")
+    layout = ("--tensor_parallel", "2", "--sequence_parallel", "--pipeline_parallel", "2")
+    one_file, four_file = str(tmp_path / "one.lora"), str(tmp_path / "four.lora")
+    # plain SGD: Adam's normalised steps turn summation-order noise in near-zero gradients into visible differences
+    # between layouts, which says nothing about the files
+    sgd = ("--optimizer", "sgd", "--learning_rate", "0.5")
+    _train(binaries, files, "llama3", 1, *lora, *sgd, "--lora_save_path", one_file, iters=4)
+    _train(binaries, files, "llama3", 4, *lora, *layout, *sgd, "--lora_save_path", four_file, iters=4)
+    assert not (tmp_path / "four.lora.rank0").exists()
+    a, b = _read_adapter(one_file), _read_adapter(four_file)
+    assert sorted(a) == sorted(b) and len(a) == 4 * 5 * 2          # 4 layers, 5 adapted linears, two factors each
+    assert "transformer.h.3.attn.c_attn.lora_B" in a
+    for name in a:
+        assert a[name].shape == b[name].shape and np.abs(a[name] - b[name]).max() <= 2e-4, name
+    assert max(np.abs(v).max() for k, v in a.items() if k.endswith("lora_B")) > 1e-3      # the adapters did train
+    # either file on either layout: the frozen adapters give the same losses
+    frozen = ("--learning_rate", "0.0")
+    on_one, _ = _train(binaries, files, "llama3", 1, *lora, *frozen, "--lora_load_path", four_file, iters=2)
+    on_four, _ = _train(binaries, files, "llama3", 4, *lora, *layout, *frozen, "--lora_load_path", one_file, iters=2)
+    plain, _ = _train(binaries, files, "llama3", 1, *lora, *frozen, iters=2)
+    assert max(abs(x - y) for x, y in zip(on_one, on_four)) <= 3e-5, (on_one, on_four)
+    assert max(abs(x - y) for x, y in zip(on_one, plain)) > 1e-3                          # and they are not the untrained ones
+    # the Python trainer reads the file the four C++ ranks wrote
+    py = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "llama3", "main.py"), "--device", "cpu", "--llmc_filepath",
+                         "llama3.bin", "--input_bin", "tokens32.bin", "--batch_size", "2", "--sequence_length", "64",
+                         "--total_batch_size", "1024", "--num_iteration", "2", "--dtype", "float32", *lora, "--learning_rate", "0.0",
+                         "--optimizer", "adam", "--lora_load_path", four_file], capture_output=True, text=True, timeout=600, cwd=files,
+                        env=ENV)
+    assert py.returncode == 0, (py.stdout + py.stderr)[-3000:]
+    assert max(abs(x - y) for x, y in zip(_losses(py.stdout + py.stderr), on_one)) <= 3e-5
