@@ -397,3 +397,22 @@ def test_one_adapter_file_whatever_the_layout_that_trained_it(binaries, files, t
                         env=ENV)
     assert py.returncode == 0, (py.stdout + py.stderr)[-3000:]
     assert max(abs(x - y) for x, y in zip(_losses(py.stdout + py.stderr), on_one)) <= 3e-5
+
+
+def test_two_launchers_play_two_nodes(binaries, files, single):
+    """Multi-node start: one infini_run per node (--nnodes 2 --node_rank 0|1, two ranks each) against one
+    rendezvous endpoint; the four ranks (TP2 x DP2, the tensor-parallel pairs inside a node) follow the
+    one-rank trajectory."""
+    launcher, trainer = binaries
+    port = _free_port()
+    cmd = [trainer, "--family", "llama3", "--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin",
+           "--batch_size", "2", "--sequence_length", "64", "--total_batch_size", "1024", "--num_iteration", "4", "--dtype", "float32",
+           *LLAMA, "--tensor_parallel", "2", "--zero_stage", "1"]
+    nodes = [subprocess.Popen([launcher, "--nnodes=2", f"--node_rank={n}", "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{port}",
+                               "--", *cmd], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=files, env=ENV)
+             for n in (0, 1)]
+    outs = [p.communicate(timeout=600)[0] for p in nodes]
+    assert all(p.returncode == 0 for p in nodes), outs[0][-2000:] + outs[1][-2000:]
+    assert "world_size = 4" in outs[0] and not _losses(outs[0])          # the last rank logs: it lives on node 1
+    losses = _losses(outs[1])
+    assert len(losses) == 4 and max(abs(a - b) for a, b in zip(losses, single["llama3"])) <= 2e-5

@@ -253,6 +253,27 @@ def test_hybrid_parallel_runs_follow_the_one_rank_trajectory(llama_files, ranks,
     assert abs(one[0] - one[1]) > 1e-2
 
 
+def test_two_launchers_play_two_nodes(llama_files):
+    """One infini_run per node (--nnodes 2 --node_rank 0|1, two ranks each) against one rendezvous endpoint:
+    the four gloo ranks (TP2 x DP2 with ZeRO-1) follow the one-rank trajectory."""
+    import socket
+
+    common, one = llama_files
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    env = {**os.environ, "OMP_NUM_THREADS": "1"}
+    nodes = [subprocess.Popen([_launcher(), "--nnodes=2", f"--node_rank={n}", "--nproc_per_node=2",
+                               f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable, *common, "--tensor_parallel", "2",
+                               "--zero_stage", "1"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=ROOT, env=env)
+             for n in (0, 1)]
+    outs = [p.communicate(timeout=900)[0] for p in nodes]
+    assert all(p.returncode == 0 for p in nodes), outs[0][-2000:] + outs[1][-2000:]
+    got = _losses(outs[1])                                   # the last rank logs: it lives on node 1
+    assert len(got) == 3 and not _losses(outs[0])
+    assert max(abs(a - b) for a, b in zip(got, one)) <= 2e-5, list(zip(got, one))
+
+
 @pytest.mark.parametrize("ranks,flags", [
     (2, ["--tensor_parallel", "2"]),
     (8, ["--tensor_parallel", "2", "--sequence_parallel", "--pipeline_parallel", "2", "--virtual_pipeline_parallel", "2",
