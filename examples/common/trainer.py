@@ -183,8 +183,11 @@ def main(family: str, argv=None) -> int:
     model.to(dev)
     PrecisionChecker.BuildNameMap(model)
     if args.lora_rank > 0:
+        # every adapter draws its A from a generator keyed by its whole-model path: the start does not depend on
+        # the layout that builds the model
         lcfg = lora.LoRAConfig(rank=args.lora_rank, alpha=args.lora_alpha,
-                               target_modules=lora.ParseLoRATargetModules(args.lora_target_modules))
+                               target_modules=lora.ParseLoRATargetModules(args.lora_target_modules),
+                               seed=(args.seed ^ 0x4C6F5241) | 1)
         model = lora.GetLoRAModel(model, lcfg)
         if args.lora_load_path:
             lora.LoadFullLoRAWeights(model, args.lora_load_path)    # whole-model file, sharded on load

@@ -15,6 +15,11 @@ class LoRAConfig:
     target_modules: Set[str] = field(default_factory=lambda: {"c_attn", "c_proj"})
     use_kaiming_a: bool = True
     kaiming_a_param: float = math.sqrt(5.0)
+    # 0: A factors are drawn from the global stream in injection order (the reference's behaviour).  Otherwise every
+    # adapter draws its A at its whole-model shape from a generator of its own, seeded with this value and the
+    # module's whole-model path: freshly initialised adapters are then the same whatever layout (tensor / pipeline
+    # split) builds the model.
+    seed: int = 0
 
     def Scaling(self) -> float:
         return float(self.alpha) / float(self.rank)

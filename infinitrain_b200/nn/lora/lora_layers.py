@@ -24,11 +24,17 @@ from ..module import Module
 from .lora_config import LoRAConfig
 
 
-def _init_ab(A, B, config: LoRAConfig):
+def _init_ab(A, B, config: LoRAConfig, generator=None, a_full_shape=None, a_cols=None):
+    """``generator``: where A is drawn from (None: the global stream).  With ``a_full_shape`` the draw has
+    that shape (the factor of the unsharded layer) and ``a_cols = (begin, end)`` names this rank's columns."""
+    target = A if a_full_shape is None else torch.empty(a_full_shape, dtype=torch.float32)
     if config.use_kaiming_a:
-        init.KaimingUniform(A, a=config.kaiming_a_param)
+        init.KaimingUniform(target, a=config.kaiming_a_param, generator=generator)
     else:
-        init.Normal(A, 0.0, 0.02)
+        init.Normal(target, 0.0, 0.02, generator=generator)
+    if target is not A:
+        with torch.no_grad():
+            A.copy_(target[:, a_cols[0]:a_cols[1]].to(A.dtype))
     init.Zeros(B)
 
 
@@ -38,12 +44,12 @@ class _LoRAMixin:
     kParamLoraAName = "lora_A"
     kParamLoraBName = "lora_B"
 
-    def _setup_lora(self, config: LoRAConfig, a_shape, b_shape, device):
+    def _setup_lora(self, config: LoRAConfig, a_shape, b_shape, device, generator=None, a_full_shape=None, a_cols=None):
         self.config = config
         self.merged_ = False
         self.lora_A = torch.nn.Parameter(torch.empty(a_shape, device=device))
         self.lora_B = torch.nn.Parameter(torch.empty(b_shape, device=device))
-        _init_ab(self.lora_A, self.lora_B, config)
+        _init_ab(self.lora_A, self.lora_B, config, generator, a_full_shape, a_cols)
         self.weight.requires_grad_(False)
         if getattr(self, "bias", None) is not None:
             self.bias.requires_grad_(False)
@@ -95,7 +101,7 @@ class LoRALinear(_LoRAMixin, Linear):
     kType = "LoRALinear"
 
     def __init__(self, in_features=None, out_features=None, config: LoRAConfig = None, bias: bool = True, device=None,
-                 base_module: Linear = None):
+                 base_module: Linear = None, generator=None):
         if base_module is not None:
             Module.__init__(self, self.kType)
             self.in_features, self.out_features = base_module.in_features, base_module.out_features
@@ -104,7 +110,8 @@ class LoRALinear(_LoRAMixin, Linear):
         else:
             Linear.__init__(self, in_features, out_features, bias, device)
             self._type = self.kType
-        self._setup_lora(config or LoRAConfig(), (config.rank, self.in_features), (self.out_features, config.rank), device)
+        self._setup_lora(config or LoRAConfig(), (config.rank, self.in_features), (self.out_features, config.rank), device,
+                         generator)
 
     def Forward(self, x):
         self._check_forward_allowed()
@@ -119,14 +126,14 @@ class LoRAColumnParallelLinear(_LoRAMixin, ColumnParallelLinear):
 
     kType = "LoRAColumnParallelLinear"
 
-    def __init__(self, base_module: ColumnParallelLinear, config: LoRAConfig):
+    def __init__(self, base_module: ColumnParallelLinear, config: LoRAConfig, generator=None):
         Module.__init__(self, self.kType)
         for k in ("in_features", "out_features", "output_size_per_partition", "has_bias", "gather_output",
                   "input_is_parallel", "skip_bias_add", "sequence_parallel"):
             setattr(self, k, getattr(base_module, k))
         self.weight, self.bias = base_module.weight, base_module.bias
         self._setup_lora(config, (config.rank, self.in_features), (self.output_size_per_partition, config.rank),
-                         self.weight.device)
+                         self.weight.device, generator)
         # A is replicated but every rank back-propagates through its own shard of B: each holds one
         # term of A's gradient, with or without sequence parallelism; the terms are summed over the
         # tensor-parallel group before the optimizer step.
@@ -158,14 +165,22 @@ class LoRARowParallelLinear(_LoRAMixin, RowParallelLinear):
 
     kType = "LoRARowParallelLinear"
 
-    def __init__(self, base_module: RowParallelLinear, config: LoRAConfig):
+    def __init__(self, base_module: RowParallelLinear, config: LoRAConfig, generator=None):
         Module.__init__(self, self.kType)
         for k in ("in_features", "out_features", "input_size_per_partition", "has_bias", "reduce_output",
                   "input_is_parallel", "skip_bias_add", "sequence_parallel"):
             setattr(self, k, getattr(base_module, k))
         self.weight, self.bias = base_module.weight, base_module.bias
+        full, cols = None, None
+        if generator is not None and self.input_size_per_partition != self.in_features:
+            # a layout-independent start: the unsharded factor is drawn, this rank keeps its columns
+            from ...parallel import global_env as genv
+
+            r = genv.GetTensorParallelRank()
+            full = (config.rank, self.in_features)
+            cols = (r * self.input_size_per_partition, (r + 1) * self.input_size_per_partition)
         self._setup_lora(config, (config.rank, self.input_size_per_partition), (self.out_features, config.rank),
-                         self.weight.device)
+                         self.weight.device, generator, full, cols)
         # B is replicated but multiplies this rank's partial product x_r A_r^T: its gradient is one term
         # of a sum over the tensor-parallel group
         self.lora_B._itb_tp_partial_grad = True

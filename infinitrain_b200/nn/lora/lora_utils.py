@@ -27,15 +27,25 @@ def _is_lora(m) -> bool:
     return isinstance(m, _LORA_TYPES)
 
 
-def _wrap(m, config: LoRAConfig):
+def _adapter_generator(config: LoRAConfig, global_path: str):
+    """``config.seed`` and the FNV-1a hash of the module's whole-model path seed the adapter's own generator."""
+    if not config.seed:
+        return None
+    h = 2166136261
+    for c in global_path.encode():
+        h = ((h ^ c) * 16777619) & 0xFFFFFFFF
+    return torch.Generator().manual_seed((config.seed ^ h) & 0xFFFFFFFF)
+
+
+def _wrap(m, config: LoRAConfig, generator=None):
     if _is_lora(m):
         return None
     if isinstance(m, ColumnParallelLinear):
-        return LoRAColumnParallelLinear(m, config)
+        return LoRAColumnParallelLinear(m, config, generator)
     if isinstance(m, RowParallelLinear):
-        return LoRARowParallelLinear(m, config)
+        return LoRARowParallelLinear(m, config, generator)
     if isinstance(m, Linear):
-        return LoRALinear(config=config, base_module=m)
+        return LoRALinear(config=config, base_module=m, generator=generator)
     return None
 
 
@@ -76,6 +86,14 @@ def InjectLoRALayers(model: Module, config: LoRAConfig) -> Module:
                                                               root_type in config.target_modules):
         return _wrap(model, config)
     replaced: Dict[int, Module] = {}
+    # a module's whole-model name: its state-dict path (the pipeline's chunk aliases name the same modules under
+    # shorter paths) with the stage's local layer number turned into the global one
+    local_to_global = dict(enumerate(_global_layer_indices(model)))
+    state_path = {}
+    if config.seed:
+        for n, m in _modules_by_state_dict_path(model).items():
+            if not any(part.startswith("__pp") for part in n.split(".")):
+                state_path.setdefault(id(m), n)
     for path, parent, name, child in _named_children_paths(model):
         clean = ".".join(p for p in path.split(".") if not p.startswith("__pp"))
         if not config.ShouldApplyLoRA(clean) and not config.ShouldApplyLoRA(path):
@@ -83,7 +101,8 @@ def InjectLoRALayers(model: Module, config: LoRAConfig) -> Module:
         if id(child) in replaced:
             parent._modules[name] = replaced[id(child)]
             continue
-        new = _wrap(child, config)
+        whole = state_path.get(id(child), clean)
+        new = _wrap(child, config, _adapter_generator(config, _rename_layer(whole, local_to_global) if local_to_global else whole))
         if new is not None:
             replaced[id(child)] = new
             parent._modules[name] = new

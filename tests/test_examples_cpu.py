@@ -308,6 +308,26 @@ def test_lora_in_any_layout_follows_the_one_rank_run_and_writes_the_same_adapter
     assert max(float((a[k] - c[k]).abs().max()) for k in a) > 1e-4        # and training moved them
 
 
+def test_fresh_adapters_do_not_depend_on_the_layout(llama_files, tmp_path):
+    """No adapter file to start from: every adapter draws its A factor from a generator keyed by its
+    whole-model path (row-parallel factors at their unsharded shape), so one rank and TP2+SP x PP2 start from
+    the same adapters, follow the same losses and write the same adapter file."""
+    from infinitrain_b200.nn.lora.lora_utils import _read_lora_file
+
+    common, _ = llama_files
+    lora_flags = ["--lora_rank", "4", "--lora_alpha", "8", "--lora_target_modules", "c_attn,c_proj,c_fc,c_fc2", "--learning_rate", "0.5"]
+    one_out, par_out = str(tmp_path / "one.bin"), str(tmp_path / "par.bin")
+    one = _losses(_run([sys.executable, *common, *lora_flags, "--lora_save_path", one_out]))
+    par = _losses(_run([_launcher(), "--nproc_per_node=4", "--rdzv_endpoint=127.0.0.1:29981", "--", sys.executable, *common,
+                        *lora_flags, "--tensor_parallel", "2", "--sequence_parallel", "--pipeline_parallel", "2", "--lora_save_path",
+                        par_out], timeout=900))
+    assert len(one) == 3 and max(abs(a - b) for a, b in zip(one, par)) <= 2e-5, list(zip(one, par))
+    a, b = _read_lora_file(one_out), _read_lora_file(par_out)
+    assert sorted(a) == sorted(b) and len(a) == 4 * 5 * 2
+    assert max(float((a[k] - b[k]).abs().max()) for k in a) < 2e-4
+    assert max(float(a[k].abs().max()) for k in a if k.endswith("lora_B")) > 1e-3          # B left zero: they trained
+
+
 def test_gpu_regression_matrix_expands_to_the_references_runs(tmp_path):
     """examples/common/matrix_gpu.json is the reference's scripts/test_config.json (groups basic, zero,
     lora) for both model families and both dtypes; --dry-run prints the command of every run, --profile
