@@ -15,7 +15,8 @@
 //             [--overfit_single_batch] [--input_val_bin F --val_loss_every N --val_max_batches M] [--sample_every N]
 //             [--heartbeat_timeout S]   step heartbeats through the job's store and a watchdog thread: when a peer is
 //                           silent for S seconds, or asks for an abort, the process groups are aborted and the rank
-//                           ends with exit code 75 instead of waiting inside a collective (0 = off, the default);
+//                           ends with exit code 75 instead of waiting inside a collective (0 = off, the default;
+//                           S must exceed the longest healthy step, checkpoint writes included);
 //                           ITB_FAULT="<rank>:<step>:raise|exit|stall|mute[:arg]" injects a host-side fault
 //             [--profile]   per-op / per-collective records, written as <family>.report.rank<r>,
 //                           <family>.records.log.rank<r> and <family>.trace.rank<r>.json (Chrome trace) into

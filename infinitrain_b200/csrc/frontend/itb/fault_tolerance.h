@@ -10,6 +10,9 @@
 //     posts the abort reason for everybody else and calls Abort() on the process groups it was given (CPU
 //     ranks: a wait inside a collective ends with an error; NCCL: ncclCommAbort), so that the training thread
 //     comes back and finds the report at its next Heartbeat::Step();
+//     A heartbeat is a sign of progress, not only of life: a rank that sits in a collective, writes a large
+//     checkpoint or waits at a barrier does not beat, so `timeout_s` has to exceed the longest time a healthy
+//     step (with everything that happens between two steps) can take;
 //   * faults are injected on the host only (FaultInjector, ITB_FAULT="<rank>:<step>:<kind>[:<arg>]", kinds
 //     raise / exit / stall / mute), before the step launches anything, so no kernel or collective of the
 //     faulty rank is in flight when it goes away.  Nothing here makes a device fault, trap or hang.

@@ -84,7 +84,23 @@ def SaveAsNpy(t: torch.Tensor, path: str) -> None:
 
 
 def Print(t: torch.Tensor, file=None) -> None:
+    """torch-style text of the tensor (the reference prints in that style too, src/tensor.cc:784-975); the
+    options of :func:`SetPrintOptions` apply."""
     print(t, file=file)
+
+
+def SetPrintOptions(precision: Optional[int] = None, threshold: Optional[int] = None, edge_items: Optional[int] = None,
+                    linewidth: Optional[int] = None, profile: Optional[str] = None, sci_mode: Optional[bool] = None) -> None:
+    """``Tensor::SetPrintOptions`` (include/tensor.h:195-198): digits after the point, the element count
+    above which a tensor is summarised, how many items each end of a summarised dimension keeps, the line
+    width, a named profile (``default`` / ``short`` / ``full``) applied before the other arguments, and
+    scientific notation on, off or chosen by the values (``None``)."""
+    if profile is not None:
+        torch.set_printoptions(profile=profile)
+    kw = {k: v for k, v in (("precision", precision), ("threshold", threshold), ("edgeitems", edge_items),
+                            ("linewidth", linewidth)) if v is not None}
+    if kw or sci_mode is not None:
+        torch.set_printoptions(sci_mode=sci_mode, **kw)
 
 
 def RegisterPostAccumulateGradHook(t: torch.Tensor, hook):

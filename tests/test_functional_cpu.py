@@ -218,3 +218,24 @@ def test_autograd_hook_of_a_gradient_written_elsewhere_is_dropped():
     # a parameter nobody claimed is reported by autograd as before
     _Lin.apply(x, b).sum().backward()
     assert ready == ["written", "autograd"]
+
+
+def test_print_options_apply_to_print():
+    import io
+
+    t = torch.tensor([1.23456, 20000.5])
+    try:
+        T.SetPrintOptions(precision=2, sci_mode=False)
+        buf = io.StringIO()
+        T.Print(t, file=buf)
+        assert "1.23," in buf.getvalue() and "20000.50" in buf.getvalue()
+        T.SetPrintOptions(sci_mode=True)
+        buf = io.StringIO()
+        T.Print(t, file=buf)
+        assert "e+04" in buf.getvalue()
+        T.SetPrintOptions(threshold=3, edge_items=1)
+        buf = io.StringIO()
+        T.Print(torch.arange(10.0), file=buf)
+        assert "..." in buf.getvalue()
+    finally:
+        T.SetPrintOptions(profile="default", sci_mode=None)
