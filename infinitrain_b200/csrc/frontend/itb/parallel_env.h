@@ -130,6 +130,35 @@ struct GlobalEnv {
 
 inline GlobalEnv& env() { return GlobalEnv::Instance(); }
 
+// The reference's free-function accessors (include/nn/parallel/global.h:90-160) over the same state.  A worker is
+// a process here, so the thread count per process is 1 and the process ranks are the ranks; coordinates keep the
+// reference's (dp, tp, pp) argument order.
+namespace global {
+inline void InitAllEnv(int /*nthread_per_process*/, int tensor_parallel_size, bool sequence_parallel_enabled, int pipeline_parallel_size,
+                       int virtual_pipeline_parallel_size = 1) {
+  env().InitAllEnv(tensor_parallel_size, sequence_parallel_enabled, pipeline_parallel_size, virtual_pipeline_parallel_size);
+}
+inline int GetNnodes() { return GlobalEnv::EnvInt("NNODES", nullptr, 1); }
+inline int GetWorldSize() { return env().world; }
+inline int GetNprocPerNode() { return GlobalEnv::EnvInt("LOCAL_WORLD_SIZE", "NPROC_PER_NODE", env().world); }
+inline int GetNthreadPerProc() { return 1; }
+inline int GetGlobalProcRank() { return env().rank; }
+inline int GetLocalProcRank() { return env().local_rank; }
+inline int GetTensorParallelSize() { return env().tp(); }
+inline int GetSequenceParallelSize() { return env().sp(); }
+inline bool GetSequenceParallelEnabled() { return env().sequence_parallel; }
+inline int GetDataParallelSize() { return env().dp(); }
+inline int GetPipelineParallelSize() { return env().pp(); }
+inline int GetVirtualPipelineParallelSize() { return env().vpp; }
+inline int GetRankOf(int dp, int tp, int pp) { return env().layout.RankOf(tp, dp, pp); }
+inline void GetCoordOf(int rank, int& dp, int& tp, int& pp) { env().layout.CoordOf(rank, &tp, &dp, &pp); }
+inline int GetGroupId(Axis target, int rank) { return env().layout.GroupId(target, rank); }
+inline int GetGroupId(Axis target, int dp, int tp, int pp) { return GetGroupId(target, GetRankOf(dp, tp, pp)); }
+inline std::vector<int> GetGroupRanks(Axis target, int rank) { return env().layout.GroupRanks(target, rank); }
+inline std::vector<int> GetGroupRanks(Axis target, int dp, int tp, int pp) { return GetGroupRanks(target, GetRankOf(dp, tp, pp)); }
+inline std::string ProcessGroupOverview() { return env().ProcessGroupOverview(); }
+}  // namespace global
+
 // Who this worker is among the job's workers (reference: include/nn/parallel/rank.h).  The reference
 // counts processes on the node and threads inside a process (one thread per GPU); here a worker is a
 // process, so thread_rank is 0 and thread_size 1 unless a program sets them for threads of its own.

@@ -192,6 +192,23 @@ ITB_TEST(Layout3D, TensorParallelRanksAreAdjacentThenDataThenPipeline) {
   EXPECT(e.ProcessGroupOverview().find("TP3 (dp=1, tp=-, pp=1): [6, 7]") != std::string::npos);
 }
 
+ITB_TEST(Layout3D, ReferenceNamedAccessorsReadTheSameState) {
+  namespace g = par::global;
+  par::GlobalEnv saved = par::env();
+  par::env().Init(/*world=*/16, /*rank=*/13, /*tp=*/2, /*sp=*/true, /*pp=*/2, /*vpp=*/3);
+  EXPECT(g::GetWorldSize() == 16 && g::GetGlobalProcRank() == 13 && g::GetNthreadPerProc() == 1);
+  EXPECT(g::GetTensorParallelSize() == 2 && g::GetDataParallelSize() == 4 && g::GetPipelineParallelSize() == 2);
+  EXPECT(g::GetSequenceParallelEnabled() && g::GetSequenceParallelSize() == 2 && g::GetVirtualPipelineParallelSize() == 3);
+  int dp = -1, tp = -1, pp = -1;
+  g::GetCoordOf(13, dp, tp, pp);                       // TP fastest, then DP, then PP: 13 = 1 + 2 * (2 + 4 * 1)
+  EXPECT(tp == 1 && dp == 2 && pp == 1 && g::GetRankOf(dp, tp, pp) == 13);
+  EXPECT(g::GetGroupRanks(par::Axis::kDP, 13) == (std::vector<int>{9, 11, 13, 15}));
+  EXPECT(g::GetGroupRanks(par::Axis::kTP, 2, 0, 1) == (std::vector<int>{12, 13}));
+  EXPECT(g::GetGroupId(par::Axis::kTP, 13) == 6 && g::GetGroupId(par::Axis::kPP, 2, 1, 0) == g::GetGroupId(par::Axis::kPP, 13));
+  EXPECT(g::ProcessGroupOverview().find("world_size = 16") != std::string::npos);
+  par::env() = saved;
+}
+
 ITB_TEST(Layout3D, RankCountsProcessesAndThreads) {
   par::Rank r(2, 1, 4, 2);                       // process 2 of 4, thread 1 of 2
   EXPECT(r.GlobalRank() == 5 && r.IsParallel() && !r.IsMainRank() && !r.IsLastRank());
