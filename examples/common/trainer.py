@@ -148,7 +148,10 @@ def main(family: str, argv=None) -> int:
                               timeout=datetime.timedelta(seconds=60))
         heartbeat = Heartbeat(store, rank, world, timeout_s=args.heartbeat_timeout,
                               poll_s=min(0.5, args.heartbeat_timeout / 4)).start()
-        injector = FaultInjector(rank, heartbeat=heartbeat)
+    if os.environ.get("ITB_FAULT"):
+        from infinitrain_b200.utils.fault_tolerance import FaultInjector
+
+        injector = FaultInjector(rank, heartbeat=heartbeat)     # host-side fault injection, with or without heartbeats
     pc = PrecisionCheckConfig.Parse(args.precision_check)
     PrecisionCheckEnv.Instance().Init(pc, rank)
     if rank == 0:
@@ -244,6 +247,21 @@ def main(family: str, argv=None) -> int:
     # batches reach the device through the feeder: asynchronous copies out of the loader's pinned ring,
     # ordered against the ring's slot reuse (several micro-batches may be in flight before a host sync)
     it = DeviceFeeder(epochs(loader), dev)
+    # A job that its launcher started again after a failure (ITB_RESTART_COUNT > 0, infini_run --max_restarts) goes
+    # on from the newest checkpoint under --save that every rank finds complete, unless --load says otherwise.
+    restart_count = int(os.environ.get("ITB_RESTART_COUNT", "0") or 0)
+    if not args.load and restart_count > 0 and args.save:
+        from infinitrain_b200.checkpoint import NewestCompleteCheckpoint
+        import torch.distributed as dist
+
+        newest = torch.tensor([NewestCompleteCheckpoint(args.save)], dtype=torch.int64, device=dev)
+        if dist.is_initialized() and world > 1:
+            dist.all_reduce(newest, op=dist.ReduceOp.MIN)
+        if int(newest.item()) > 0:
+            args.load = os.path.join(args.save, f"checkpoint_step_{int(newest.item()):06d}")
+        if rank == 0:
+            LOG("INFO", f"restart {restart_count}: " + (f"resuming from {args.load}" if args.load else
+                                                         "no complete checkpoint yet, starting over"))
     if args.load:
         res = ResumeFromCheckpoint(args.load, model, optimizer, cfg, load_optimizer_state=args.save_optimizer_state,
                                    allow_dp_resize=args.elastic_resume)
@@ -259,11 +277,14 @@ def main(family: str, argv=None) -> int:
 
     metrics = None
     for step in range(start_step, args.num_iteration):
+        if injector is not None and heartbeat is None:
+            injector.maybe_fire(step)            # a faulty rank leaves here, with nothing of its own in flight
         if heartbeat is not None:
             from infinitrain_b200.utils.fault_tolerance import RankFailure
 
             try:
-                injector.maybe_fire(step)        # a faulty rank leaves here, with nothing of its own in flight
+                if injector is not None:
+                    injector.maybe_fire(step)    # a faulty rank leaves here, with nothing of its own in flight
                 heartbeat.step(step)
                 heartbeat.wait_peers(step)       # every peer is alive before this step's first collective
             except RankFailure as e:

@@ -216,29 +216,50 @@ int main(int argc, char** argv) {
   const bool model_parallel = tp * pp > 1;
   // which ranks hold state nobody else has: every model-parallel slice, and under ZeRO every shard of the optimizer state
   const bool own_state = model_parallel || (dp > 1 && zero_stage >= 1);
-  if (!fl.get("load", "").empty()) {
-    const std::string root = fl.get("load", "");
-    std::string dir = root;
-    if (std::filesystem::exists(dir + "/" + itb::io::RankDirName(env.rank))) dir += "/" + itb::io::RankDirName(env.rank);
-    // --elastic_resume: a checkpoint that another number of data-parallel ranks wrote (same tensor / pipeline
-    // layout).  Weights are the same on every data-parallel rank; the slices of a ZeRO optimizer state are put
-    // together from the old ranks' files and cut again for this rank.
-    const bool elastic = fl.getb("elastic_resume", false);
-    auto old_rank_dir = [&](int64_t old_dp, int64_t d) {   // the rank that held (tp_rank, d, pp_rank) in the old job
-      return root + "/" + itb::io::RankDirName(static_cast<int>(env.tp_rank + tp * (d + old_dp * env.pp_rank)));
-    };
-    if (elastic && !std::filesystem::exists(dir + "/trainer_state.json")) {
-      // this rank's number did not exist in the old job, or held other coordinates: read the layout from rank 0's state
-      auto probe = itb::io::LoadTrainerState(root + "/" + itb::io::RankDirName(0) + "/trainer_state.json");
-      dir = old_rank_dir(probe.ddp_size, 0);
+  // A job that its launcher started again after a failure (ITB_RESTART_COUNT > 0, infini_run --max_restarts) goes on
+  // from the newest checkpoint under --save that every rank finds complete, unless --load says otherwise.
+  std::string load_dir = fl.get("load", "");
+  const int restart_count = par::GlobalEnv::EnvInt("ITB_RESTART_COUNT", nullptr, 0);
+  if (load_dir.empty() && restart_count > 0 && !fl.get("save", "").empty()) {
+    // every rank looks at the directory it would read: its own when it saves, else that of data-parallel rank 0
+    const bool saves_own = own_state && (env.dp_rank == 0 || zero_stage >= 1);
+    const int probe = !own_state ? -1 : (saves_own ? env.rank : env.layout.RankOf(env.tp_rank, 0, env.pp_rank));
+    int64_t step = itb::io::NewestCompleteCheckpointStep(fl.get("save", ""), probe);
+    if (auto world_group = par::ProcessGroupFactory::Instance().GetDefaultProcessGroup()) {
+      itb::Tensor s = torch::full({1}, static_cast<double>(step), torch::dtype(torch::kFloat64).device(device));
+      world_group->AllReduce(s, par::ReduceOp::kMin);
+      step = static_cast<int64_t>(s.item<double>());
     }
-    auto st = itb::io::LoadTrainerState(dir + "/trainer_state.json");
+    if (step > 0) load_dir = itb::io::CheckpointDirOfStep(fl.get("save", ""), step);
+    if (env.rank == 0)
+      std::fprintf(stderr, "[I] restart %d: %s\n", restart_count,
+                   step > 0 ? ("resuming from " + load_dir).c_str() : "no complete checkpoint yet, starting over");
+  }
+  if (!load_dir.empty()) {
+    const std::string root = load_dir;
+    // Which directory this rank reads.  A one-rank or pure data-parallel job without ZeRO wrote into the step
+    // directory itself.  Otherwise the files are under rank_%06d of the rank that held this rank's (tensor,
+    // pipeline) coordinates in the job that saved: its own data-parallel rank when every data-parallel rank saved
+    // (ZeRO: optimizer shards) and the data-parallel size is unchanged, else data-parallel rank 0 (weights are the
+    // same on every data-parallel rank).  --elastic_resume: another data-parallel size (same tensor / pipeline
+    // layout); the slices of a ZeRO optimizer state are put together from the old ranks' files and cut again.
+    const bool elastic = fl.getb("elastic_resume", false);
+    const bool in_rank_dirs = !std::filesystem::exists(root + "/trainer_state.json");
+    auto st = itb::io::LoadTrainerState(in_rank_dirs ? root + "/" + itb::io::RankDirName(0) + "/trainer_state.json" : root + "/trainer_state.json");
     TORCH_CHECK(st.n_layer == cfg.n_layer && st.n_embd == cfg.n_embd, "checkpoint and model shapes differ");
     const bool resized = st.ddp_size != dp;
     TORCH_CHECK(st.tp_size == tp && st.pp_size == pp && st.sp_size == env.sp() && (!resized || !own_state || elastic),
                 "the checkpoint was written under another parallel layout (DP=", st.ddp_size, " TP=", st.tp_size, " SP=", st.sp_size,
                 " PP=", st.pp_size, "); --elastic_resume accepts another data-parallel size");
-    if (resized && own_state && std::filesystem::exists(old_rank_dir(st.ddp_size, 0))) dir = old_rank_dir(st.ddp_size, 0);
+    auto old_rank_dir = [&](int64_t old_dp, int64_t d) {   // the rank that held (tp_rank, d, pp_rank) in the job that saved
+      return root + "/" + itb::io::RankDirName(static_cast<int>(env.tp_rank + tp * (d + old_dp * env.pp_rank)));
+    };
+    std::string dir = root;
+    if (in_rank_dirs) {
+      dir = old_rank_dir(st.ddp_size, !resized && env.dp_rank < st.ddp_size ? env.dp_rank : 0);
+      if (!std::filesystem::exists(dir + "/model.ckpt")) dir = old_rank_dir(st.ddp_size, 0);   // only data-parallel rank 0 saved
+      st = itb::io::LoadTrainerState(dir + "/trainer_state.json");
+    }
     model->LoadStateDict(itb::io::LoadStateDict(dir + "/model.ckpt"));
     if (std::filesystem::exists(dir + "/optimizer.ckpt")) {
       if (resized && ddp && zero_stage >= 1) {

@@ -1,1 +1,1 @@
-from .checkpoint import (Checkpoint, ResumeFromCheckpoint, ResumeFromCheckpointResult, SaveCheckpoint, TrainerState)
+from .checkpoint import (Checkpoint, NewestCompleteCheckpoint, ResumeFromCheckpoint, ResumeFromCheckpointResult, SaveCheckpoint, TrainerState)

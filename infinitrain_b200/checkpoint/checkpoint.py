@@ -146,6 +146,28 @@ def SaveCheckpoint(checkpoint_root_dir: str, global_step: int, model, optimizer,
     return step_dir
 
 
+def NewestCompleteCheckpoint(checkpoint_root_dir: str, rank: Optional[int] = None) -> int:
+    """The newest step under ``<root>`` whose checkpoint is complete for this rank: its ``trainer_state.json``,
+    the file a rank writes last, is there, parses and names that step.  0 when there is none.  Ranks of one job
+    agree on a step by taking the minimum of what each of them finds (a job that its launcher restarted after
+    a failure resumes from there)."""
+    rank = genv.MyRank() if rank is None else rank
+    world = genv.GetWorldSize()
+    if not os.path.isdir(checkpoint_root_dir):
+        return 0
+    steps = sorted((int(m.group(1)), d) for d in os.listdir(checkpoint_root_dir)
+                   for m in [re.fullmatch(r"checkpoint_step_(\d+)", d)] if m)
+    for step, d in reversed(steps):
+        try:
+            st = Checkpoint.LoadTrainerState(os.path.join(_rank_dir(os.path.join(checkpoint_root_dir, d), rank, world),
+                                                          "trainer_state.json"))
+        except (OSError, ValueError, KeyError):
+            continue
+        if st.global_step == step:
+            return step
+    return 0
+
+
 def _resume_on_other_dp_size(resume_root: str, old_ranks, model, optimizer, load_optimizer_state: bool):
     """A data-parallel group saved by the ``len(old_ranks)`` ranks listed (the ranks that share this
     rank's tensor / pipeline coordinates), resumed by a different number: the weights are replicated

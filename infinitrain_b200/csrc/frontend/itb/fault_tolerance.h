@@ -250,6 +250,10 @@ class FaultInjector {
       : rank_(rank), heartbeat_(heartbeat), on_cuda_(on_cuda) {
     const char* env = spec ? spec : std::getenv("ITB_FAULT");
     if (!env || !*env) return;
+    // a fault from the environment belongs to a job's first attempt: the attempt that the launcher starts after it
+    // (ITB_RESTART_COUNT > 0) must be able to get past the step
+    const char* restarted = std::getenv("ITB_RESTART_COUNT");
+    if (!spec && restarted && std::atoi(restarted) > 0) return;
     std::vector<std::string> parts;
     std::string s(env);
     size_t begin = 0;

@@ -291,6 +291,42 @@ inline std::string SaveCheckpoint(const std::string& root, const TrainerState& s
   return dir.string();
 }
 
+// <root>/checkpoint_step_* directories by step, oldest first.
+inline std::vector<std::pair<int64_t, std::string>> ListCheckpoints(const std::string& root) {
+  std::vector<std::pair<int64_t, std::string>> out;
+  DIR* d = ::opendir(root.c_str());
+  if (!d) return out;
+  while (dirent* e = ::readdir(d)) {
+    const std::string name = e->d_name, prefix = "checkpoint_step_";
+    if (name.rfind(prefix, 0) != 0 || name.find_first_not_of("0123456789", prefix.size()) != std::string::npos) continue;
+    struct stat st;
+    if (::stat((root + "/" + name).c_str(), &st) == 0 && S_ISDIR(st.st_mode))
+      out.emplace_back(std::stoll(name.substr(prefix.size())), root + "/" + name);
+  }
+  ::closedir(d);
+  std::sort(out.begin(), out.end());
+  return out;
+}
+// The newest step under <root> whose checkpoint is complete for this rank -- its trainer_state.json, the file a
+// rank writes last, is there and parses (global_rank >= 0: under rank_%06d/, else in the step directory) -- or 0.
+// Ranks of one job agree on a step by taking the minimum of what each of them finds.
+inline int64_t NewestCompleteCheckpointStep(const std::string& root, int global_rank = -1) {
+  auto all = ListCheckpoints(root);
+  for (auto it = all.rbegin(); it != all.rend(); ++it) {
+    const std::string dir = global_rank >= 0 ? it->second + "/" + RankDirName(global_rank) : it->second;
+    try {
+      if (LoadTrainerState(dir + "/trainer_state.json").global_step == it->first) return it->first;
+    } catch (const std::exception&) {
+    }
+  }
+  return 0;
+}
+inline std::string CheckpointDirOfStep(const std::string& root, int64_t step) {
+  char name[64];
+  std::snprintf(name, sizeof(name), "checkpoint_step_%06lld", static_cast<long long>(step));
+  return root + "/" + name;
+}
+
 // Keeps the `keep` newest <root>/checkpoint_step_* directories (zero-padded names sort by step) and removes
 // the rest (reference: src/checkpoint/checkpoint_manager.cc:103-118).  Returns how many were removed.
 // Directory listing and recursive removal go through POSIX calls: std::filesystem's iterators are not

@@ -251,7 +251,10 @@ class FaultInjector:
         self.rank, self.heartbeat = rank, heartbeat
         self.target_rank = self.step = None
         self.kind, self.arg = "", ""
-        spec = os.environ.get("ITB_FAULT", "") if spec is None else spec
+        if spec is None:
+            # a fault from the environment belongs to a job's first attempt: the attempt that the launcher starts
+            # after it (ITB_RESTART_COUNT > 0) must be able to get past the step
+            spec = os.environ.get("ITB_FAULT", "") if int(os.environ.get("ITB_RESTART_COUNT", "0") or 0) == 0 else ""
         if spec:
             parts = spec.split(":")
             self.target_rank, self.step, self.kind = int(parts[0]), int(parts[1]), parts[2]

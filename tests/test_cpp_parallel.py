@@ -416,3 +416,47 @@ def test_two_launchers_play_two_nodes(binaries, files, single):
     assert "world_size = 4" in outs[0] and not _losses(outs[0])          # the last rank logs: it lives on node 1
     losses = _losses(outs[1])
     assert len(losses) == 4 and max(abs(a - b) for a, b in zip(losses, single["llama3"])) <= 2e-5
+
+
+def test_launcher_restarts_a_failed_job_from_its_newest_checkpoint(binaries, files, tmp_path):
+    """infini_run --max_restarts: rank 1 leaves at step 4 of the first attempt; the launcher ends rank 0, starts
+    both again with ITB_RESTART_COUNT=1, and the trainer goes on from the newest checkpoint every rank has
+    (step 2): the job ends with exit code 0 and its last steps repeat the uninterrupted run's."""
+    launcher, trainer = binaries
+    cmd = [trainer, "--family", "llama3", "--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin",
+           "--batch_size", "2", "--sequence_length", "64", "--total_batch_size", "1024", "--num_iteration", "6", "--dtype", "float32",
+           *LLAMA, "--zero_stage", "1"]
+    full, _ = _train(binaries, files, "llama3", 2, *LLAMA, "--zero_stage", "1", iters=6)
+    r = subprocess.run([launcher, "--nproc_per_node=2", "--max_restarts=1", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", *cmd,
+                        "--save", str(tmp_path), "--save_interval", "2"], capture_output=True, text=True, timeout=600, cwd=files,
+                       env={**ENV, "ITB_FAULT": "1:4:exit"})
+    log = r.stdout + r.stderr
+    assert r.returncode == 0, log[-3000:]
+    assert "attempt 0 ended with exit code 17; restarting (1 of 1)" in log
+    assert "restart 1: resuming from " in log and "checkpoint_step_000002" in log
+    steps = [int(m.group(1)) for m in re.finditer(r"step\s+(\d+)/6", log)]
+    assert steps == [1, 2, 3, 3, 4, 5, 6], steps
+    losses = _losses(log)
+    assert max(abs(a - b) for a, b in zip(losses[3:], full[2:])) <= 2e-5, (losses, full)
+    # without restarts left the failure is the job's exit code
+    r = subprocess.run([launcher, "--nproc_per_node=2", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", *cmd], capture_output=True,
+                       text=True, timeout=600, cwd=files, env={**ENV, "ITB_FAULT": "1:2:exit:9"})
+    assert r.returncode == 9
+
+
+def test_data_parallel_ranks_of_a_model_parallel_job_resume_from_their_groups_first_rank(binaries, files, tmp_path):
+    """TP2 x DP2 without ZeRO: only data-parallel rank 0 of every tensor-parallel slice saves; on resume the
+    other data-parallel ranks read that slice too, and the run continues the uninterrupted one."""
+    flags = (*LLAMA, "--tensor_parallel", "2")
+    full, _ = _train(binaries, files, "llama3", 4, *flags, iters=4)
+    _train(binaries, files, "llama3", 4, *flags, "--save", str(tmp_path), "--save_interval", "2", iters=2)
+    ckpt = tmp_path / "checkpoint_step_000002"
+    assert sorted(p.name for p in ckpt.iterdir()) == ["rank_000000", "rank_000001"]
+    launcher, trainer = binaries
+    r = subprocess.run([launcher, "--nproc_per_node=4", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", trainer, "--family", "llama3",
+                        "--device", "cpu", "--llmc_filepath", "llama3.bin", "--input_bin", "tokens32.bin", "--batch_size", "2",
+                        "--sequence_length", "64", "--total_batch_size", "1024", "--num_iteration", "4", "--dtype", "float32", *flags,
+                        "--load", str(ckpt)], capture_output=True, text=True, timeout=600, cwd=files, env=ENV)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    resumed = _losses(r.stdout + r.stderr)
+    assert len(resumed) == 2 and max(abs(a - b) for a, b in zip(resumed, full[2:])) <= 2e-5, (resumed, full)

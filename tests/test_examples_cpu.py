@@ -253,6 +253,31 @@ def test_hybrid_parallel_runs_follow_the_one_rank_trajectory(llama_files, ranks,
     assert abs(one[0] - one[1]) > 1e-2
 
 
+def test_launcher_restarts_a_failed_job_from_its_newest_checkpoint(llama_files, tmp_path):
+    """infini_run --max_restarts with the Python trainer: rank 1 leaves at step 4 of the first attempt; both ranks
+    are started again with ITB_RESTART_COUNT=1 and go on from the newest checkpoint every rank has (step 2): the
+    job ends with exit code 0 and its last steps repeat the uninterrupted run's."""
+    import socket
+
+    common, _ = llama_files
+    six = list(common)
+    six[six.index("--num_iteration") + 1] = "6"
+    flags = ["--zero_stage", "1", "--optimizer", "adam", "--learning_rate", "0.01", "--save_optimizer_state"]
+    full = _losses(_run([_launcher(), "--nproc_per_node=2", "--rdzv_endpoint=127.0.0.1:29941", "--", sys.executable, *six, *flags],
+                        timeout=900))
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    out = _run([_launcher(), "--nproc_per_node=2", "--max_restarts=1", f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable, *six,
+                *flags, "--save", str(tmp_path), "--save_interval", "2"], env={"ITB_FAULT": "1:3:exit"}, timeout=900)   # step index 3 = the fourth step
+    assert "attempt 0 ended with exit code 17; restarting (1 of 1)" in out
+    assert "restart 1: resuming from " in out and "checkpoint_step_000002" in out
+    steps = [int(m.group(1)) for m in re.finditer(r"step\s+(\d+)/6", out)]
+    assert steps == [1, 2, 3, 3, 4, 5, 6], steps
+    got = _losses(out)
+    assert max(abs(a - b) for a, b in zip(got[3:], full[2:])) <= 2e-5, (got, full)
+
+
 def test_two_launchers_play_two_nodes(llama_files):
     """One infini_run per node (--nnodes 2 --node_rank 0|1, two ranks each) against one rendezvous endpoint:
     the four gloo ranks (TP2 x DP2 with ZeRO-1) follow the one-rank trajectory."""
