@@ -98,7 +98,8 @@ def build_parser(family: str) -> argparse.ArgumentParser:
            "tensor / pipeline layout (ZeRO optimizer state is re-sharded)")
     a("--heartbeat_timeout", type=float, default=0.0,
       help="seconds without a peer's step heartbeat before the run stops with exit code 75 (0 = off); "
-           "ITB_FAULT=<rank>:<step>:<raise|exit|stall|mute> injects a host-side fault")
+           "ITB_FAULT=<rank>:<step>:<raise|exit|stall|mute> injects a host-side fault before that step (steps "
+           "count from 1, as in the log lines)")
     return p
 
 
@@ -278,13 +279,13 @@ def main(family: str, argv=None) -> int:
     metrics = None
     for step in range(start_step, args.num_iteration):
         if injector is not None and heartbeat is None:
-            injector.maybe_fire(step)            # a faulty rank leaves here, with nothing of its own in flight
+            injector.maybe_fire(step + 1)        # a faulty rank leaves here, with nothing of its own in flight
         if heartbeat is not None:
             from infinitrain_b200.utils.fault_tolerance import RankFailure
 
             try:
                 if injector is not None:
-                    injector.maybe_fire(step)    # a faulty rank leaves here, with nothing of its own in flight
+                    injector.maybe_fire(step + 1)   # (steps count from 1, as in the log lines and in the C++ trainer)
                 heartbeat.step(step)
                 heartbeat.wait_peers(step)       # every peer is alive before this step's first collective
             except RankFailure as e:

@@ -245,7 +245,9 @@ class FaultInjector:
     * ``mute``   -- the rank keeps training but stops publishing heartbeats.
 
     ``maybe_fire(step)`` is called by the training loop before it launches anything for the step,
-    so no kernel or collective of the faulty rank is in flight when it goes away."""
+    so no kernel or collective of the faulty rank is in flight when it goes away.  The trainers pass the
+    step number as it appears in their log lines (from 1).  A fault read from the environment belongs to
+    a job's first attempt: under ``ITB_RESTART_COUNT > 0`` (a job its launcher started again) it is ignored."""
 
     def __init__(self, rank: int, spec: Optional[str] = None, heartbeat: Optional[Heartbeat] = None):
         self.rank, self.heartbeat = rank, heartbeat

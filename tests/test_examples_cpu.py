@@ -80,7 +80,7 @@ def test_trainer_stops_when_a_peer_is_lost():
            "--total_batch_size", "128", "--num_iteration", "6", "--model", "llama3-1b", "--overfit_single_batch",
            "--learning_rate", "1e-3", "--heartbeat_timeout", "3"]
     e = dict(os.environ)
-    e.update(OMP_NUM_THREADS="1", ITB_FAULT="1:2:stall:120")
+    e.update(OMP_NUM_THREADS="1", ITB_FAULT="1:3:stall:120")
     t0 = time.time()
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=e, cwd=ROOT)
     out = r.stdout + r.stderr
@@ -269,7 +269,7 @@ def test_launcher_restarts_a_failed_job_from_its_newest_checkpoint(llama_files, 
         sock.bind(("127.0.0.1", 0))
         port = sock.getsockname()[1]
     out = _run([_launcher(), "--nproc_per_node=2", "--max_restarts=1", f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable, *six,
-                *flags, "--save", str(tmp_path), "--save_interval", "2"], env={"ITB_FAULT": "1:3:exit"}, timeout=900)   # step index 3 = the fourth step
+                *flags, "--save", str(tmp_path), "--save_interval", "2"], env={"ITB_FAULT": "1:4:exit"}, timeout=900)
     assert "attempt 0 ended with exit code 17; restarting (1 of 1)" in out
     assert "restart 1: resuming from " in out and "checkpoint_step_000002" in out
     steps = [int(m.group(1)) for m in re.finditer(r"step\s+(\d+)/6", out)]
