@@ -336,6 +336,7 @@ int main(int argc, char** argv) {
     if (heartbeat) {
       try {
         heartbeat->Step(step + 1);
+        heartbeat->WaitPeers(step + 1);   // every peer is alive and here before this step's first collective
       } catch (const itb::utils::RankFailure& e) {
         rank_failed(e.what());
       }
