@@ -294,7 +294,7 @@ class DistributedDataParallel : public Module {
 // all-gather every bucket's shards into the full parameter buffer.
 class DistributedOptimizer : public optim::Optimizer {
  public:
-  using Creator = std::function<std::unique_ptr<optim::Optimizer>(TensorList)>;
+  using Creator = optim::OptimizerCreator;
   DistributedOptimizer(const Creator& creator, std::vector<DistributedDataParallel*> chunks) : optim::Optimizer({}), chunks_(std::move(chunks)) {
     TensorList shards;
     for (auto* ddp : chunks_) {

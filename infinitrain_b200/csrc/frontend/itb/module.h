@@ -21,6 +21,10 @@ namespace itb {
 using Tensor = torch::Tensor;
 using TensorList = std::vector<Tensor>;
 
+namespace autograd {
+using NoGradGuard = torch::NoGradGuard;   // the reference's autograd::NoGradGuard
+}  // namespace autograd
+
 // Handle of a registered hook; Remove() unregisters it (reference: include/common/hook.h:7-28).
 class HookHandle {
  public:
@@ -152,6 +156,13 @@ class Module : public std::enable_shared_from_this<Module> {
   const std::vector<std::string>& child_names() const { return module_order_; }
   bool has_module(const std::string& name) const { return modules_.count(name) != 0; }
   Tensor& parameter(const std::string& name) { return parameters_.at(name); }
+  Tensor& mutable_parameter(const std::string& name) { return parameters_.at(name); }   // the reference's name
+  // this module and every module below it, pre-order, each once (reference: Module::modules())
+  std::vector<std::shared_ptr<Module>> modules() {
+    std::vector<std::shared_ptr<Module>> out;
+    for (auto& [path, m] : NamedModules()) out.push_back(m);
+    return out;
+  }
   const Tensor& parameter(const std::string& name) const { return parameters_.at(name); }
   bool has_parameter(const std::string& name) const { return parameters_.count(name) != 0; }
 

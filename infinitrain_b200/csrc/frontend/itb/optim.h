@@ -4,6 +4,8 @@
 // launch leaves the tensor's version alone, so the shadow stays marked fresh).
 #pragma once
 #include <cmath>
+#include <functional>
+#include <memory>
 
 #include "ops.h"
 
@@ -30,9 +32,16 @@ class Optimizer {
   TensorList params_;
 };
 
+// Builds an optimizer over a parameter list that is only known later (a ZeRO shard: DistributedOptimizer).
+using OptimizerCreator = std::function<std::unique_ptr<Optimizer>(TensorList)>;
+
 class SGD : public Optimizer {
  public:
   SGD(TensorList params, double lr) : Optimizer(std::move(params)), lr_(lr) {}
+  // reference: optimizers::SGD::Create(lr), include/optimizer.h:35-46
+  static OptimizerCreator Create(double lr) {
+    return [lr](TensorList params) -> std::unique_ptr<Optimizer> { return std::make_unique<SGD>(std::move(params), lr); };
+  }
   void Step() override {
     ITB_PROFILE("sgd.Step", params_.empty() ? Tensor() : params_[0]);
     torch::NoGradGuard g;
@@ -66,6 +75,12 @@ class Adam : public Optimizer {
       m_.push_back(torch::zeros_like(p, p.options().requires_grad(false)));
       v_.push_back(torch::zeros_like(p, p.options().requires_grad(false)));
     }
+  }
+  // reference: optimizers::Adam::Create(lr, beta1, beta2, eps), include/optimizer.h:48-68
+  static OptimizerCreator Create(double lr = 1e-3, double beta1 = 0.9, double beta2 = 0.999, double eps = 1e-8, double weight_decay = 0.0) {
+    return [=](TensorList params) -> std::unique_ptr<Optimizer> {
+      return std::make_unique<Adam>(std::move(params), lr, beta1, beta2, eps, weight_decay);
+    };
   }
   void Step() override {
     ITB_PROFILE("adam.Step", params_.empty() ? Tensor() : params_[0]);

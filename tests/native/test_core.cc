@@ -591,4 +591,25 @@ ITB_TEST(Init, FansGainsBoundsAndGenerators) {
   EXPECT(torch::equal(init::Arange(2, 6), torch::tensor({2, 3, 4, 5}, torch::kInt64)));
 }
 
+ITB_TEST(ApiNames, CreatorsModulesListAndGuards) {
+  using namespace itb::nn;
+  auto net = std::make_shared<Sequential>(std::vector<std::shared_ptr<itb::Module>>{std::make_shared<Linear>(3, 2), std::make_shared<Sigmoid>()});
+  EXPECT(net->modules().size() == 3 && net->modules()[0] == net);
+  EXPECT(net->at(0)->mutable_parameter("weight").data_ptr() == net->at(0)->parameter("weight").data_ptr());
+  // optimizer creators: the parameter list arrives later
+  auto sgd = itb::optim::SGD::Create(0.5)(net->Parameters());
+  auto adam = itb::optim::Adam::Create(1e-2, 0.9, 0.95)(net->Parameters());
+  Tensor before = net->Parameters()[0].clone();
+  (*net)(torch::ones({4, 3})).sum().backward();
+  sgd->Step();
+  EXPECT(!torch::equal(before, net->Parameters()[0].detach()));
+  adam->Step();
+  EXPECT(adam->StateDict().count("adam.t") == 1 && adam->StateDict().at("adam.t").item<int64_t>() == 1);
+  {
+    itb::autograd::NoGradGuard guard;
+    EXPECT(!(*net)(torch::ones({1, 3})).requires_grad());
+  }
+  EXPECT((*net)(torch::ones({1, 3})).requires_grad());
+}
+
 ITB_TEST_MAIN()
