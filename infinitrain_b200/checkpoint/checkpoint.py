@@ -64,8 +64,11 @@ class Checkpoint:
         order = ["n_layer", "n_head", "n_kv_head", "n_embd", "vocab_size", "global_step", "consumed_batches", "last_lr",
                  "ddp_size", "tp_size", "sp_size", "pp_size"]
         d = asdict(state)
-        with open(path, "w") as f:
+        # written last of a checkpoint's files and through a temporary file + rename: a trainer_state.json
+        # that exists is whole, and marks its directory as a complete checkpoint of its rank
+        with open(path + ".tmp", "w") as f:
             f.write("{\n" + ",\n".join(f'  "{k}": {d[k]}' for k in order) + "\n}\n")
+        os.replace(path + ".tmp", path)
 
     @staticmethod
     def LoadTrainerState(path: str) -> TrainerState:

@@ -240,13 +240,22 @@ inline std::map<std::string, Tensor> LoadStateDict(const std::string& path) {
   for (auto& [k, v] : load_state_dict(path)) out[k] = v;
   return out;
 }
+// Written last of a checkpoint's files and through a temporary file + rename: a trainer_state.json that exists is
+// whole, and marks its directory as a complete checkpoint of its rank.
 inline void SaveTrainerState(const std::string& path, const TrainerState& s) {
-  std::ofstream f(path);
-  f << "{\n  \"n_layer\": " << s.n_layer << ",\n  \"n_head\": " << s.n_head << ",\n  \"n_kv_head\": " << s.n_kv_head
-    << ",\n  \"n_embd\": " << s.n_embd << ",\n  \"vocab_size\": " << s.vocab_size << ",\n  \"global_step\": " << s.global_step
-    << ",\n  \"consumed_batches\": " << s.consumed_batches << ",\n  \"last_lr\": " << s.last_lr << ",\n  \"ddp_size\": "
-    << s.ddp_size << ",\n  \"tp_size\": " << s.tp_size << ",\n  \"sp_size\": " << s.sp_size << ",\n  \"pp_size\": " << s.pp_size
-    << "\n}\n";
+  const std::string tmp = path + ".tmp";
+  {
+    std::ofstream f(tmp);
+    TORCH_CHECK(f.is_open(), "cannot write ", tmp);
+    f << "{\n  \"n_layer\": " << s.n_layer << ",\n  \"n_head\": " << s.n_head << ",\n  \"n_kv_head\": " << s.n_kv_head
+      << ",\n  \"n_embd\": " << s.n_embd << ",\n  \"vocab_size\": " << s.vocab_size << ",\n  \"global_step\": " << s.global_step
+      << ",\n  \"consumed_batches\": " << s.consumed_batches << ",\n  \"last_lr\": " << s.last_lr << ",\n  \"ddp_size\": "
+      << s.ddp_size << ",\n  \"tp_size\": " << s.tp_size << ",\n  \"sp_size\": " << s.sp_size << ",\n  \"pp_size\": " << s.pp_size
+      << "\n}\n";
+    f.flush();
+    TORCH_CHECK(f.good(), "cannot write ", tmp);
+  }
+  TORCH_CHECK(std::rename(tmp.c_str(), path.c_str()) == 0, "cannot move ", tmp, " to ", path);
 }
 // Tolerant field scan (the reference's writer leaves out a comma after vocab_size).
 inline TrainerState LoadTrainerState(const std::string& path) {
