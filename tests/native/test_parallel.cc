@@ -21,21 +21,20 @@ namespace par = itb::parallel;
 
 namespace {
 
-int free_port() {
-  static std::atomic<int> next{0};
-  return 31000 + (static_cast<int>(::getpid()) % 2000) * 8 % 16000 + next++;
-}
-
+// The server store asks the system for a free port (port 0) and the clients read it back: a number computed here
+// can fall into the range the system hands to outgoing connections and meet a socket that still lingers there.
+//
 // Runs fn(rank, group) on `world` threads; the group spans all of them.  Exceptions of any rank fail
 // the calling test.
 void run_ranks(int world, const std::function<void(int, std::shared_ptr<par::ProcessGroup>)>& fn) {
   c10d::TCPStoreOptions server;
-  server.port = static_cast<uint16_t>(free_port());
+  server.port = 0;
   server.isServer = true;
   server.numWorkers = c10::nullopt;
   server.waitWorkers = false;
   server.timeout = std::chrono::milliseconds(60000);
   auto master = c10::make_intrusive<c10d::TCPStore>("127.0.0.1", server);
+  server.port = master->getPort();
   std::vector<std::string> errors(world);
   std::vector<std::thread> threads;
   std::vector<int> ranks(world);
@@ -91,7 +90,7 @@ struct Stack : itb::Module {
 // another thread (the watchdog of fault_tolerance.h) aborts its group; later calls fail at once.
 ITB_TEST(ProcessGroup, AbortEndsAWaitForAPeerThatIsGone) {
   c10d::TCPStoreOptions server;
-  server.port = static_cast<uint16_t>(free_port());
+  server.port = 0;   // any free port
   server.isServer = true;
   server.numWorkers = c10::nullopt;
   server.waitWorkers = false;
