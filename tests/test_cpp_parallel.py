@@ -427,7 +427,8 @@ def test_launcher_restarts_a_failed_job_from_its_newest_checkpoint(binaries, fil
            "--batch_size", "2", "--sequence_length", "64", "--total_batch_size", "1024", "--num_iteration", "6", "--dtype", "float32",
            *LLAMA, "--zero_stage", "1"]
     full, _ = _train(binaries, files, "llama3", 2, *LLAMA, "--zero_stage", "1", iters=6)
-    r = subprocess.run([launcher, "--nproc_per_node=2", "--max_restarts=1", f"--rdzv_endpoint=127.0.0.1:{_free_port()}", "--", *cmd,
+    # a fixed port below the range the system hands to outgoing connections: the second attempt listens on port + 1
+    r = subprocess.run([launcher, "--nproc_per_node=2", "--max_restarts=1", "--rdzv_endpoint=127.0.0.1:29961", "--", *cmd,
                         "--save", str(tmp_path), "--save_interval", "2"], capture_output=True, text=True, timeout=600, cwd=files,
                        env={**ENV, "ITB_FAULT": "1:4:exit"})
     log = r.stdout + r.stderr

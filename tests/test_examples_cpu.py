@@ -257,18 +257,14 @@ def test_launcher_restarts_a_failed_job_from_its_newest_checkpoint(llama_files, 
     """infini_run --max_restarts with the Python trainer: rank 1 leaves at step 4 of the first attempt; both ranks
     are started again with ITB_RESTART_COUNT=1 and go on from the newest checkpoint every rank has (step 2): the
     job ends with exit code 0 and its last steps repeat the uninterrupted run's."""
-    import socket
-
     common, _ = llama_files
     six = list(common)
     six[six.index("--num_iteration") + 1] = "6"
     flags = ["--zero_stage", "1", "--optimizer", "adam", "--learning_rate", "0.01", "--save_optimizer_state"]
     full = _losses(_run([_launcher(), "--nproc_per_node=2", "--rdzv_endpoint=127.0.0.1:29941", "--", sys.executable, *six, *flags],
                         timeout=900))
-    with socket.socket() as sock:
-        sock.bind(("127.0.0.1", 0))
-        port = sock.getsockname()[1]
-    out = _run([_launcher(), "--nproc_per_node=2", "--max_restarts=1", f"--rdzv_endpoint=127.0.0.1:{port}", "--", sys.executable, *six,
+    # a fixed port below the range the system hands to outgoing connections: the second attempt listens on port + 1
+    out = _run([_launcher(), "--nproc_per_node=2", "--max_restarts=1", "--rdzv_endpoint=127.0.0.1:29945", "--", sys.executable, *six,
                 *flags, "--save", str(tmp_path), "--save_interval", "2"], env={"ITB_FAULT": "1:4:exit"}, timeout=900)
     assert "attempt 0 ended with exit code 17; restarting (1 of 1)" in out
     assert "restart 1: resuming from " in out and "checkpoint_step_000002" in out
