@@ -142,8 +142,8 @@ def SaveCheckpoint(checkpoint_root_dir: str, global_step: int, model, optimizer,
                          genv.GetPipelineParallelSize())
     Checkpoint.Save(_rank_dir(step_dir, rank, world), model, optimizer, state, save_optimizer_state, reference_buffers)
     if rank == 0 and max_checkpoint_keep > 0 and os.path.isdir(checkpoint_root_dir):
-        ckpts = sorted(d for d in os.listdir(checkpoint_root_dir)
-                       if d.startswith("checkpoint_step_") and os.path.isdir(os.path.join(checkpoint_root_dir, d)))
+        ckpts = sorted(d for d in os.listdir(checkpoint_root_dir)       # numbered step directories only
+                       if re.fullmatch(r"checkpoint_step_\d+", d) and os.path.isdir(os.path.join(checkpoint_root_dir, d)))
         while len(ckpts) > max_checkpoint_keep:
             shutil.rmtree(os.path.join(checkpoint_root_dir, ckpts.pop(0)), ignore_errors=True)
     return step_dir

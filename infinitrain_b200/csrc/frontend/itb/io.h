@@ -342,22 +342,12 @@ inline std::string CheckpointDirOfStep(const std::string& root, int64_t step) {
 // ABI-stable across the libstdc++ the binary was compiled against and the one libtorch loads.
 inline int PruneCheckpoints(const std::string& root, int64_t keep) {
   if (keep <= 0) return 0;
-  DIR* d = ::opendir(root.c_str());
-  if (!d) return 0;
-  std::vector<std::string> dirs;
-  while (dirent* e = ::readdir(d)) {
-    const std::string name = e->d_name;
-    if (name.rfind("checkpoint_step_", 0) != 0) continue;
-    struct stat st;
-    if (::stat((root + "/" + name).c_str(), &st) == 0 && S_ISDIR(st.st_mode)) dirs.push_back(root + "/" + name);
-  }
-  ::closedir(d);
-  std::sort(dirs.begin(), dirs.end());
+  auto all = ListCheckpoints(root);   // numbered step directories only, oldest first
   int removed = 0;
-  while (static_cast<int64_t>(dirs.size()) > keep) {
-    ::nftw(dirs.front().c_str(), [](const char* path, const struct stat*, int, struct FTW*) { return ::remove(path); }, 16,
+  while (static_cast<int64_t>(all.size()) > keep) {
+    ::nftw(all.front().second.c_str(), [](const char* path, const struct stat*, int, struct FTW*) { return ::remove(path); }, 16,
            FTW_DEPTH | FTW_PHYS);
-    dirs.erase(dirs.begin());
+    all.erase(all.begin());
     ++removed;
   }
   return removed;

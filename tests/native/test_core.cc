@@ -6,6 +6,7 @@
 #include "itb_test.h"
 
 #include <algorithm>
+#include <filesystem>
 #include <fstream>
 #include <sstream>
 
@@ -610,6 +611,31 @@ ITB_TEST(ApiNames, CreatorsModulesListAndGuards) {
     EXPECT(!(*net)(torch::ones({1, 3})).requires_grad());
   }
   EXPECT((*net)(torch::ones({1, 3})).requires_grad());
+}
+
+ITB_TEST(Checkpoint, NewestCompleteStepSkipsWhatAFailureLeftHalfWritten) {
+  const std::string root = itbtest::temp_dir("ckpts");
+  EXPECT(itb::io::NewestCompleteCheckpointStep(root + "/absent") == 0 && itb::io::ListCheckpoints(root).empty());
+  for (int64_t step : {2, 4, 6}) {
+    const std::string dir = itb::io::CheckpointDirOfStep(root, step);
+    std::filesystem::create_directories(dir + "/rank_000001");
+    std::ofstream(dir + "/model.ckpt") << "x";
+    if (step == 6) continue;                              // the job died before this step's state file was written
+    itb::io::TrainerState st;
+    st.global_step = step;
+    itb::io::SaveTrainerState(dir + "/trainer_state.json", st);
+    if (step == 2) itb::io::SaveTrainerState(dir + "/rank_000001/trainer_state.json", st);
+  }
+  std::filesystem::create_directories(root + "/checkpoint_step_notanumber");
+  auto all = itb::io::ListCheckpoints(root);
+  EXPECT(all.size() == 3 && all.front().first == 2 && all.back().first == 6);
+  EXPECT(itb::io::NewestCompleteCheckpointStep(root) == 4);
+  EXPECT(itb::io::NewestCompleteCheckpointStep(root, /*global_rank=*/1) == 2);
+  EXPECT(itb::io::NewestCompleteCheckpointStep(root, 3) == 0);
+  std::ofstream(itb::io::CheckpointDirOfStep(root, 4) + "/trainer_state.json") << "{ \"global_step\": 3 }";   // another step's file
+  EXPECT(itb::io::NewestCompleteCheckpointStep(root) == 2);
+  EXPECT(!std::filesystem::exists(itb::io::CheckpointDirOfStep(root, 2) + "/trainer_state.json.tmp"));
+  EXPECT(itb::io::PruneCheckpoints(root, 1) == 2 && itb::io::ListCheckpoints(root).size() == 1);
 }
 
 ITB_TEST_MAIN()

@@ -213,3 +213,34 @@ def test_resume_reports_a_topology_mismatch_before_loading(tmp_path):
                                     TrainerState(2, 2, 1e-4, 1, 4, 4, 32, 64, ddp_size=1, tp_size=2, sp_size=1, pp_size=1))
     with pytest.raises(ValueError, match="TP_SIZE mismatch: checkpoint has 2, but current run has 1"):
         ResumeFromCheckpoint(str(tmp_path / "ck"), m, None, cfg)
+
+
+def test_newest_complete_checkpoint_skips_what_a_failure_left_half_written(tmp_path):
+    """A step directory counts for a rank only when its trainer_state.json (written last, through a
+    rename) is there, parses and names that step."""
+    from infinitrain_b200.checkpoint import Checkpoint, NewestCompleteCheckpoint, TrainerState
+    from infinitrain_b200.parallel import global_env as genv
+
+    genv.InitAllEnv(world_size=1, rank=0)
+    assert NewestCompleteCheckpoint(str(tmp_path / "absent")) == 0
+    for step in (2, 4, 6):
+        d = tmp_path / f"checkpoint_step_{step:06d}"
+        d.mkdir()
+        if step != 6:                                      # step 6: model written, the job died before the state file
+            Checkpoint.SaveTrainerState(str(d / "trainer_state.json"), TrainerState(global_step=step))
+        (d / "model.ckpt").write_bytes(b"x")
+    (tmp_path / "checkpoint_step_notanumber").mkdir()
+    assert NewestCompleteCheckpoint(str(tmp_path)) == 4
+    (tmp_path / "checkpoint_step_000004" / "trainer_state.json").write_text("{ \"global_step\": 3 }")   # another step's file
+    assert NewestCompleteCheckpoint(str(tmp_path)) == 2
+    assert not (tmp_path / "checkpoint_step_000002" / "trainer_state.json.tmp").exists()
+    # ranks of a larger job look into their own directories
+    genv.InitAllEnv(world_size=2, rank=1)
+    try:
+        assert NewestCompleteCheckpoint(str(tmp_path)) == 0
+        (tmp_path / "checkpoint_step_000002" / "rank_000001").mkdir()
+        Checkpoint.SaveTrainerState(str(tmp_path / "checkpoint_step_000002" / "rank_000001" / "trainer_state.json"),
+                                    TrainerState(global_step=2))
+        assert NewestCompleteCheckpoint(str(tmp_path)) == 2
+    finally:
+        genv.InitAllEnv(world_size=1, rank=0)
