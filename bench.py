@@ -804,6 +804,11 @@ def main():
         }
         if tp_paths is not None:
             out["config"]["tp_linear_paths"] = tp_paths
+        if dp > 1 and args.zero == 2:
+            # what "zero2" means on the fused NVLink path: sharded optimizer state and updates, full gradient buffer
+            out["config"]["zero2_memory"] = ("fused NVLink kernels: optimizer state and the weight update are sharded over the "
+                                             "data-parallel ranks, the fp32 gradient buffer stays whole on every rank (peers read "
+                                             "it in place): ZeRO-1 memory")
         if extra is not None:
             out["extra"] = extra
 
